@@ -1,0 +1,50 @@
+// Library identity and the packed-matmul entry point, which picks between the
+// GEMV kernels (one activation row per grid slice) and the tensor-core GEMM.
+#include "common.cuh"
+
+namespace aoto {
+int qgemv_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
+int qgemv_check(const aoto_qmatmul_args& a, bool pointers);
+const char* qgemv_variant(const aoto_qmatmul_args& a);
+}  // namespace aoto
+
+using namespace aoto;
+
+extern "C" int aoto_sm100_abi_version(void) { return AOTO_ABI_VERSION; }
+
+extern "C" int aoto_sm100_compiled_arch(void) { return 100; }
+
+extern "C" const char* aoto_sm100_status_string(int status) {
+  switch (status) {
+    case AOTO_OK: return "ok";
+    case AOTO_ERR_ARGUMENT: return "invalid argument (null pointer, bad size or misaligned buffer)";
+    case AOTO_ERR_UNSUPPORTED: return "no kernel variant for this request";
+    case AOTO_ERR_LAUNCH: return "the CUDA runtime refused the launch";
+    case AOTO_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int aoto_sm100_qmatmul_supported(const aoto_qmatmul_args* a) {
+  if (!a) return 0;
+  if (qgemv_check(*a, false) != AOTO_OK) return 0;
+  if (a->K > 49152) return 0;
+  return 1;
+}
+
+extern "C" int64_t aoto_sm100_qmatmul_scratch_bytes(const aoto_qmatmul_args* a) {
+  (void)a;
+  return 0;
+}
+
+extern "C" const char* aoto_sm100_qmatmul_variant(const aoto_qmatmul_args* a) {
+  if (!a) return "none";
+  return qgemv_variant(*a);
+}
+
+extern "C" int aoto_sm100_qmatmul(const aoto_qmatmul_args* a, void* stream) {
+  if (!a) return AOTO_ERR_ARGUMENT;
+  const int status = qgemv_check(*a, true);
+  if (status != AOTO_OK) return status;
+  return qgemv_launch(*a, (cudaStream_t)stream);
+}

@@ -1,0 +1,226 @@
+// Small streaming kernels of the decoder path: dequantize, RMS norm (+residual),
+// rotary embedding, row gathers, mask conversion, greedy argmax.
+#include "common.cuh"
+
+namespace aoto {
+
+// --------------------------------------------------------------------------
+// dequantize_i4: one thread per packed word, eight bf16 out (one 16-byte store)
+// --------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+dequantize_i4_kernel(const uint32_t* __restrict__ packed, const bf16* __restrict__ scales,
+                     bf16* __restrict__ out, int64_t words_total, int words_per_row, int group) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= words_total) return;
+  const int64_t row = idx / words_per_row;
+  const int j = (int)(idx - row * words_per_row);
+  const uint32_t word = __ldg(packed + idx);
+  const int groups_per_row = (words_per_row * 8) / group;
+  const bf16 scale = scales[row * groups_per_row + (j * 8) / group];
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c0 = ((int)(word << (28 - 8 * i))) >> 28;
+    const int c1 = ((int)(word << (24 - 8 * i))) >> 28;
+    // bf16(code) is exact; the product is rounded once to bf16
+    const bf16 v0 = __hmul(__int2bfloat16_rn(c0), scale);
+    const bf16 v1 = __hmul(__int2bfloat16_rn(c1), scale);
+    o[i] = (uint32_t)__bfloat16_as_ushort(v0) | ((uint32_t)__bfloat16_as_ushort(v1) << 16);
+  }
+  reinterpret_cast<uint4*>(out)[idx] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// --------------------------------------------------------------------------
+// rms_norm (+ residual): one CTA per row
+// --------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+rms_norm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual,
+                const bf16* __restrict__ weight, bf16* __restrict__ out, bf16* __restrict__ sum_out,
+                int H, float eps) {
+  extern __shared__ float row_cache[];  // H floats + 32
+  float* red = row_cache + H;
+  pdl_wait_for_producers();
+  pdl_release_dependents();
+  const size_t base = (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = __bfloat162float(x[base + i]);
+    if (residual != nullptr) {
+      // the sum is a bf16 value in the graph (add in the model dtype), so round it
+      v = round_bf16(v + __bfloat162float(residual[base + i]));
+      if (sum_out != nullptr) sum_out[base + i] = __float2bfloat16_rn(v);
+    }
+    row_cache[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const float total = block_sum(ss, red);
+  const float inv = rsqrtf(total / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = row_cache[i] * inv;
+    if (weight != nullptr) v *= __bfloat162float(weight[i]);
+    out[base + i] = __float2bfloat16_rn(v);
+  }
+}
+
+// --------------------------------------------------------------------------
+// rope: out = bf16(bf16(x*cos) + bf16(rot(x)*sin)), as three bf16 operations
+// --------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+rope_kernel(const bf16* __restrict__ x, const bf16* __restrict__ cos_t, const bf16* __restrict__ sin_t,
+            bf16* __restrict__ out, int heads, int T, int D, int64_t sb, int64_t sh, int64_t st,
+            int64_t total) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int d = (int)(idx % D);
+  const int64_t r = idx / D;
+  const int t = (int)(r % T);
+  const int64_t r2 = r / T;
+  const int h = (int)(r2 % heads);
+  const int64_t b = r2 / heads;
+  const bf16* src = x + b * sb + h * sh + t * st;
+  const int half = D >> 1;
+  const float v = __bfloat162float(src[d]);
+  const float partner = d < half ? -__bfloat162float(src[d + half]) : __bfloat162float(src[d - half]);
+  const float c = __bfloat162float(cos_t[(size_t)t * D + d]);
+  const float s = __bfloat162float(sin_t[(size_t)t * D + d]);
+  out[idx] = __float2bfloat16_rn(round_bf16(v * c) + round_bf16(partner * s));
+}
+
+// --------------------------------------------------------------------------
+// embedding: one CTA per gathered row
+// --------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+embedding_kernel(const bf16* __restrict__ table, const int64_t* __restrict__ ids, bf16* __restrict__ out,
+                 int64_t* __restrict__ bad_index, int rows, int width) {
+  pdl_wait_for_producers();
+  pdl_release_dependents();
+  const int i = blockIdx.x;
+  const int64_t id = ids[i];
+  const bool ok = id >= 0 && id < rows;
+  if (!ok && bad_index != nullptr && threadIdx.x == 0) {
+    // keep the first offending position
+    atomicCAS(reinterpret_cast<unsigned long long*>(bad_index), 0ull, (unsigned long long)(i + 1));
+  }
+  bf16* dst = out + (size_t)i * width;
+  const bf16* src = table + (size_t)(ok ? id : 0) * width;
+  if ((width & 7) == 0 && aligned_ptr16(src) && aligned_ptr16(dst)) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (int c = threadIdx.x; c < (width >> 3); c += blockDim.x)
+      d4[c] = ok ? s4[c] : make_uint4(0u, 0u, 0u, 0u);
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+      dst[c] = ok ? src[c] : __float2bfloat16_rn(0.f);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+mask_select_kernel(const uint8_t* __restrict__ mask, bf16* __restrict__ out, int64_t count,
+                   float on_true, float on_false) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < count) out[idx] = __float2bfloat16_rn(mask[idx] ? on_true : on_false);
+}
+
+// --------------------------------------------------------------------------
+// argmax: one CTA per row, first maximum wins (torch / numpy tie rule); NaN is
+// treated as the maximum, as torch.argmax does.
+// --------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const bf16* __restrict__ logits, int64_t* __restrict__ out, int width) {
+  __shared__ float best_v[32];
+  __shared__ int best_i[32];
+  pdl_wait_for_producers();
+  pdl_release_dependents();
+  const bf16* row = logits + (size_t)blockIdx.x * width;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  bool seen = false;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = __bfloat162float(row[i]);
+    if (v != v) v = INFINITY;  // NaN ranks highest
+    if (!seen || v > bv) { bv = v; bi = i; seen = true; }
+  }
+  // warp reduce (value desc, index asc)
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    const int warps = blockDim.x >> 5;
+    bv = lane < warps ? best_v[lane] : -INFINITY;
+    bi = lane < warps ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) out[blockIdx.x] = (int64_t)bi;
+  }
+}
+
+}  // namespace aoto
+
+using namespace aoto;
+
+extern "C" int aoto_sm100_dequantize_i4(const aoto_dequantize_args* a, void* stream) {
+  if (!a || !a->packed || !a->scales || !a->out) return AOTO_ERR_ARGUMENT;
+  if (a->N <= 0 || a->K <= 0 || a->group_size <= 0 || a->group_size % 8 != 0 ||
+      a->K % a->group_size != 0)
+    return AOTO_ERR_ARGUMENT;
+  if (!aligned_to(a->out, 16)) return AOTO_ERR_ARGUMENT;
+  const int words_per_row = a->K / 8;
+  const int64_t words = (int64_t)a->N * words_per_row;
+  const int64_t blocks = (words + 255) / 256;
+  dequantize_i4_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const uint32_t*)a->packed, (const bf16*)a->scales, (bf16*)a->out, words, words_per_row,
+      a->group_size);
+  return launch_status();
+}
+
+extern "C" int aoto_sm100_rms_norm(const aoto_rms_norm_args* a, void* stream) {
+  if (!a || !a->x || !a->out || a->rows <= 0 || a->H <= 0) return AOTO_ERR_ARGUMENT;
+  const size_t smem = (size_t)a->H * 4 + 32 * 4;
+  if (smem > 48 * 1024) return AOTO_ERR_UNSUPPORTED;
+  return launch_kernel(rms_norm_kernel, dim3(a->rows), dim3(256), smem, (cudaStream_t)stream, false,
+                       (const bf16*)a->x, (const bf16*)a->residual, (const bf16*)a->weight,
+                       (bf16*)a->out, (bf16*)a->sum_out, (int)a->H, a->eps);
+}
+
+extern "C" int aoto_sm100_rope(const aoto_rope_args* a, void* stream) {
+  if (!a || !a->x || !a->cos_table || !a->sin_table || !a->out) return AOTO_ERR_ARGUMENT;
+  if (a->B <= 0 || a->heads <= 0 || a->T <= 0 || a->D <= 0 || (a->D & 1)) return AOTO_ERR_ARGUMENT;
+  const int64_t total = (int64_t)a->B * a->heads * a->T * a->D;
+  const int64_t blocks = (total + 255) / 256;
+  rope_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)a->x, (const bf16*)a->cos_table, (const bf16*)a->sin_table, (bf16*)a->out,
+      a->heads, a->T, a->D, a->stride_b, a->stride_h, a->stride_t, total);
+  return launch_status();
+}
+
+extern "C" int aoto_sm100_embedding(const aoto_embedding_args* a, void* stream) {
+  if (!a || !a->table || !a->ids || !a->out || a->rows <= 0 || a->width <= 0 || a->count <= 0)
+    return AOTO_ERR_ARGUMENT;
+  return launch_kernel(embedding_kernel, dim3(a->count), dim3(128), 0, (cudaStream_t)stream, false,
+                       (const bf16*)a->table, a->ids, (bf16*)a->out, a->bad_index, (int)a->rows,
+                       (int)a->width);
+}
+
+extern "C" int aoto_sm100_mask_select(const aoto_mask_select_args* a, void* stream) {
+  if (!a || !a->mask || !a->out || a->count <= 0) return AOTO_ERR_ARGUMENT;
+  const int64_t blocks = (a->count + 255) / 256;
+  mask_select_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      a->mask, (bf16*)a->out, a->count, a->on_true, a->on_false);
+  return launch_status();
+}
+
+extern "C" int aoto_sm100_argmax(const aoto_argmax_args* a, void* stream) {
+  if (!a || !a->logits || !a->out || a->rows <= 0 || a->width <= 0) return AOTO_ERR_ARGUMENT;
+  return launch_kernel(argmax_kernel, dim3(a->rows), dim3(1024), 0, (cudaStream_t)stream, false,
+                       (const bf16*)a->logits, a->out, (int)a->width);
+}

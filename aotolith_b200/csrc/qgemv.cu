@@ -1,0 +1,450 @@
+// Packed 4-bit GEMV (single activation row per grid.y slice) for sm_100a.
+//
+// Two kernels:
+//
+//  * qgemv_mma_kernel  - group 64, K % 128 == 0. The weight stream is the only
+//    HBM traffic that matters, so the kernel is built around it: every lane
+//    issues 128-bit loads of packed words, nibbles are turned into bf16 values
+//    in registers with one logic op per code pair, and the multiply-accumulate
+//    runs on the tensor pipe (mma.sync m16n8k16, fp32 accumulate) so the ALU
+//    only pays for the decode. One warp owns a 16-row x 128-column block of W
+//    at a time; the warps of a CTA split K and reduce through shared memory in
+//    a fixed order, so results are deterministic.
+//
+//  * qgemv_generic_kernel - any group size that is a multiple of 8 and any K
+//    that is a multiple of it; one warp per output row, scalar decode. It is
+//    the shape-complete variant small test models and odd shapes use.
+//
+// Both apply the optional RMS-norm prologue to the activation row while
+// staging it in shared memory (fp32 statistics, x_hat rounded to bf16), and
+// the epilogues of the packed matmul/addmm operation.
+#include "common.cuh"
+
+namespace aoto {
+
+struct GemvParams {
+  const bf16* x;
+  const uint32_t* w0;
+  const bf16* s0;
+  const uint32_t* w1;
+  const bf16* s1;
+  const bf16* addend;
+  const bf16* gate;
+  const bf16* norm_w;
+  bf16* out;
+  int N, K, group;
+  int addend_kind, epilogue;
+  float alpha, beta, eps;
+};
+
+__device__ __forceinline__ void unpack8(const uint4 v, float (&f)[8]) {
+  f[0] = bf16x2_lo(v.x); f[1] = bf16x2_hi(v.x);
+  f[2] = bf16x2_lo(v.y); f[3] = bf16x2_hi(v.y);
+  f[4] = bf16x2_lo(v.z); f[5] = bf16x2_hi(v.z);
+  f[6] = bf16x2_lo(v.w); f[7] = bf16x2_hi(v.w);
+}
+
+// Stage one activation row (K bf16, K % 8 == 0) into shared memory, applying
+// the fused RMS norm if asked. With PERMUTE each run of eight values is stored
+// as [0,4,1,5,2,6,3,7], the order the mma B fragments want, and the sum of the
+// staged (rounded) values of every run of eight is written to `chunk_sum`.
+template <bool PERMUTE>
+__device__ __forceinline__ void stage_activation(const GemvParams& p, const bf16* x, uint4* xs,
+                                                 float* chunk_sum, float* red) {
+  const int chunks = p.K >> 3;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  const uint4* wv = reinterpret_cast<const uint4*>(p.norm_w);
+  float inv = 1.f;
+  if (p.norm_w != nullptr) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+      float f[8];
+      unpack8(xv[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+    }
+    const float total = block_sum(ss, red);
+    inv = rsqrtf(total / (float)p.K + p.eps);
+  }
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    float f[8];
+    unpack8(xv[c], f);
+    if (p.norm_w != nullptr) {
+      float w[8];
+      unpack8(wv[c], w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = round_bf16((f[i] * inv) * w[i]);
+    }
+    uint4 o;
+    if (PERMUTE) {
+      o.x = pack_bf16x2(f[0], f[4]);
+      o.y = pack_bf16x2(f[1], f[5]);
+      o.z = pack_bf16x2(f[2], f[6]);
+      o.w = pack_bf16x2(f[3], f[7]);
+      chunk_sum[c] = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
+    } else {
+      o.x = pack_bf16x2(f[0], f[1]);
+      o.y = pack_bf16x2(f[2], f[3]);
+      o.z = pack_bf16x2(f[4], f[5]);
+      o.w = pack_bf16x2(f[6], f[7]);
+    }
+    xs[c] = o;
+  }
+  __syncthreads();
+}
+
+// y = beta*addend + alpha*total, then the epilogue. `total2` is the second
+// (up) projection of the paired form.
+__device__ __forceinline__ float finish_output(const GemvParams& p, int m, int n, float total,
+                                               float total2) {
+  float y = p.alpha * total;
+  if (p.addend_kind == AOTO_ADDEND_VECTOR) {
+    y = fmaf(p.beta, __bfloat162float(p.addend[n]), y);
+  } else if (p.addend_kind == AOTO_ADDEND_FULL) {
+    y = fmaf(p.beta, __bfloat162float(p.addend[(size_t)m * p.N + n]), y);
+  }
+  if (p.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED) {
+    const float g = round_bf16(y);
+    y = (p.alpha * total2) * (g / (1.f + expf(-g)));
+  } else if (p.epilogue == AOTO_EPILOGUE_SILU_MUL) {
+    const float g = __bfloat162float(p.gate[(size_t)m * p.N + n]);
+    y = y * (g / (1.f + expf(-g)));
+  }
+  return y;
+}
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// (nibble k, nibble k+4) of a word -> two bf16 holding 136 + code (exact):
+// 0x4300 is 128.0 in bf16 with a unit ulp, and code + 8 == nibble ^ 8.
+#define AOTO_NIB(word, shift) ((((word) >> (shift)) & 0x000F000Fu) ^ 0x43084308u)
+
+struct WeightItem {
+  uint4 lo, hi;      // 32 codes of row g and of row g+8
+  uint32_t slo, shi; // the two group scales (bf16 pair) of each row
+};
+
+// Block = 16 rows x 128 columns of W (two groups of 64). Lane (g = lane/4,
+// t = lane%4) holds codes [32t, 32t+32) of rows g and g+8. The eight mma of a
+// block all accumulate into one C tile; B column parity separates the two
+// groups (even columns see only x of the first group, odd of the second), so
+// C[row][0] and C[row][1] are the two per-group code sums of that row.
+template <int RT, int UK, bool PAIRED>
+__global__ void __launch_bounds__(256)
+qgemv_mma_kernel(const GemvParams p) {
+  constexpr int MATS = PAIRED ? 2 : 1;
+  extern __shared__ uint4 smem[];
+  const int K = p.K, N = p.N;
+  const int nblocks = K >> 7, groups = K >> 6, chunks = K >> 3;
+  const int W = blockDim.x >> 5;
+  uint4* xs = smem;
+  float* xsum = reinterpret_cast<float*>(xs + chunks);
+  float* csum = xsum + groups;
+  float* part = csum + chunks;
+  float* red = part + MATS * RT * W * 16;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int m = blockIdx.y;
+  const int tile0 = blockIdx.x * RT;
+  const int per_rt = (nblocks + W - 1) / W;
+  const int row_u4 = K >> 5;   // uint4 per packed row
+  const int row_sc = K >> 6;   // scales per row
+
+  int rlo[RT], rhi[RT];
+#pragma unroll
+  for (int rt = 0; rt < RT; ++rt) {
+    rlo[rt] = min((tile0 + rt) * 16 + g, N - 1);
+    rhi[rt] = min((tile0 + rt) * 16 + g + 8, N - 1);
+  }
+
+  WeightItem item[MATS][RT][UK];
+  auto load_batch = [&](int step) {
+#pragma unroll
+    for (int u = 0; u < UK; ++u) {
+      const int kb = warp + (step + u) * W;
+      if (kb < nblocks) {
+#pragma unroll
+        for (int mat = 0; mat < MATS; ++mat) {
+          const uint4* wq = reinterpret_cast<const uint4*>(mat == 0 ? p.w0 : p.w1);
+          const bf16* sc = mat == 0 ? p.s0 : p.s1;
+#pragma unroll
+          for (int rt = 0; rt < RT; ++rt) {
+            WeightItem& it = item[mat][rt][u];
+            it.lo = ldg_nc_u4(wq + (size_t)rlo[rt] * row_u4 + kb * 4 + t);
+            it.hi = ldg_nc_u4(wq + (size_t)rhi[rt] * row_u4 + kb * 4 + t);
+            it.slo = __ldg(reinterpret_cast<const uint32_t*>(sc + (size_t)rlo[rt] * row_sc + kb * 2));
+            it.shi = __ldg(reinterpret_cast<const uint32_t*>(sc + (size_t)rhi[rt] * row_sc + kb * 2));
+          }
+        }
+      }
+    }
+  };
+
+  // Weights do not depend on the producer of x: start streaming them before
+  // waiting for it.
+  load_batch(0);
+  pdl_wait_for_producers();
+  pdl_release_dependents();
+
+  stage_activation<true>(p, p.x + (size_t)m * K, xs, csum, red);
+  for (int gidx = tid; gidx < groups; gidx += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) s += csum[gidx * 8 + c];
+    xsum[gidx] = 136.f * s;
+  }
+  __syncthreads();
+
+  float acc[MATS][RT][2];
+#pragma unroll
+  for (int mat = 0; mat < MATS; ++mat)
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt) acc[mat][rt][0] = acc[mat][rt][1] = 0.f;
+
+  // even B columns carry the first group of the block, odd ones the second
+  const bool keep = ((g & 1) == (t >> 1));
+
+  for (int step = 0; step < per_rt; step += UK) {
+    if (step > 0) load_batch(step);
+#pragma unroll
+    for (int u = 0; u < UK; ++u) {
+      const int kb = warp + (step + u) * W;
+      if (kb < nblocks) {
+        uint4 b[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          b[j] = xs[kb * 16 + t * 4 + j];
+          if (!keep) b[j] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        const float2 off = *reinterpret_cast<const float2*>(xsum + kb * 2);
+#pragma unroll
+        for (int mat = 0; mat < MATS; ++mat) {
+#pragma unroll
+          for (int rt = 0; rt < RT; ++rt) {
+            const WeightItem& it = item[mat][rt][u];
+            const uint32_t wl[4] = {it.lo.x, it.lo.y, it.lo.z, it.lo.w};
+            const uint32_t wh[4] = {it.hi.x, it.hi.y, it.hi.z, it.hi.w};
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              mma_16816(c, AOTO_NIB(wl[j], 0), AOTO_NIB(wh[j], 0), AOTO_NIB(wl[j], 4),
+                        AOTO_NIB(wh[j], 4), b[j].x, b[j].y);
+              mma_16816(c, AOTO_NIB(wl[j], 8), AOTO_NIB(wh[j], 8), AOTO_NIB(wl[j], 12),
+                        AOTO_NIB(wh[j], 12), b[j].z, b[j].w);
+            }
+            acc[mat][rt][0] += bf16x2_lo(it.slo) * (c[0] - off.x) + bf16x2_hi(it.slo) * (c[1] - off.y);
+            acc[mat][rt][1] += bf16x2_lo(it.shi) * (c[2] - off.x) + bf16x2_hi(it.shi) * (c[3] - off.y);
+          }
+        }
+      }
+    }
+  }
+
+  if (t == 0) {
+#pragma unroll
+    for (int mat = 0; mat < MATS; ++mat)
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+        float* dst = part + ((mat * RT + rt) * W + warp) * 16;
+        dst[g] = acc[mat][rt][0];
+        dst[g + 8] = acc[mat][rt][1];
+      }
+  }
+  __syncthreads();
+  if (tid < RT * 16) {
+    const int rt = tid >> 4, r = tid & 15;
+    const int n = (tile0 + rt) * 16 + r;
+    if (n < N) {
+      float total = 0.f, total2 = 0.f;
+      for (int w = 0; w < W; ++w) total += part[((0 * RT + rt) * W + w) * 16 + r];
+      if (PAIRED)
+        for (int w = 0; w < W; ++w) total2 += part[((1 * RT + rt) * W + w) * 16 + r];
+      p.out[(size_t)m * N + n] = __float2bfloat16_rn(finish_output(p, m, n, total, total2));
+    }
+  }
+}
+
+// One warp per output row; lanes stride over the packed words.
+__global__ void __launch_bounds__(256)
+qgemv_generic_kernel(const GemvParams p) {
+  extern __shared__ uint4 smem[];
+  const int K = p.K, N = p.N, chunks = K >> 3;
+  uint4* xs = smem;
+  float* red = reinterpret_cast<float*>(xs + chunks);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int W = blockDim.x >> 5;
+  const int m = blockIdx.y;
+  pdl_wait_for_producers();
+  pdl_release_dependents();
+  stage_activation<false>(p, p.x + (size_t)m * K, xs, nullptr, red);
+
+  const int n = blockIdx.x * W + warp;
+  if (n >= N) return;
+  const int words = K >> 3;
+  const int row_sc = K / p.group;
+  const bool paired = p.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED;
+  float acc = 0.f, acc2 = 0.f;
+  for (int j = lane; j < words; j += 32) {
+    float xf[8];
+    unpack8(xs[j], xf);
+    const int gidx = (j * 8) / p.group;
+    {
+      const uint32_t word = __ldg(p.w0 + (size_t)n * words + j);
+      const float scale = __bfloat162float(p.s0[(size_t)n * row_sc + gidx]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int code = ((int)(word << (28 - 4 * i))) >> 28;
+        acc = fmaf((float)code, xf[i] * scale, acc);
+      }
+    }
+    if (paired) {
+      const uint32_t word = __ldg(p.w1 + (size_t)n * words + j);
+      const float scale = __bfloat162float(p.s1[(size_t)n * row_sc + gidx]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int code = ((int)(word << (28 - 4 * i))) >> 28;
+        acc2 = fmaf((float)code, xf[i] * scale, acc2);
+      }
+    }
+  }
+  acc = warp_sum(acc);
+  acc2 = warp_sum(acc2);
+  if (lane == 0) p.out[(size_t)m * N + n] = __float2bfloat16_rn(finish_output(p, m, n, acc, acc2));
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+
+struct GemvPlan {
+  bool fast;
+  int W, RT, UK;
+  const char* name;
+};
+
+static GemvPlan plan_gemv(const aoto_qmatmul_args& a) {
+  GemvPlan plan = {false, 8, 1, 1, "qgemv_generic"};
+  const bool paired = a.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED;
+  if (a.group_size != 64 || (a.K % 128) != 0 || a.K > 32768) return plan;
+  plan.fast = true;
+  const int nblocks = a.K / 128;
+  int W = 8;
+  if (nblocks % 8 != 0) {
+    if (nblocks % 7 == 0) W = 7;
+    else if (nblocks % 6 == 0) W = 6;
+    else if (nblocks % 5 == 0) W = 5;
+  }
+  if (nblocks < W) W = nblocks;
+  plan.W = W;
+  const int per_rt = (nblocks + W - 1) / W;
+  const int tiles = (a.N + 15) / 16;
+  const bool big = tiles >= 148 * 16;
+  if (!paired) {
+    if (per_rt == 1) { plan.RT = big ? 4 : 1; plan.UK = 1; }
+    else if (per_rt >= 4) { plan.RT = 1; plan.UK = 4; }
+    else if (big) { plan.RT = 2; plan.UK = 2; }
+    else { plan.RT = 1; plan.UK = 2; }
+  } else {
+    if (per_rt == 1) { plan.RT = big ? 2 : 1; plan.UK = 1; }
+    else { plan.RT = 1; plan.UK = 2; }
+  }
+  plan.name = paired ? "qgemv_mma_paired" : "qgemv_mma";
+  return plan;
+}
+
+template <int RT, int UK, bool PAIRED>
+static int launch_mma(const GemvParams& p, const GemvPlan& plan, int M, cudaStream_t stream, bool pdl) {
+  constexpr int MATS = PAIRED ? 2 : 1;
+  const size_t smem = (size_t)p.K * 2 + (size_t)(p.K / 64) * 4 + (size_t)(p.K / 8) * 4 +
+                      (size_t)MATS * RT * plan.W * 16 * 4 + 32 * 4;
+  auto kernel = qgemv_mma_kernel<RT, UK, PAIRED>;
+  if (smem > 48 * 1024) {
+    static bool raised = false;  // idempotent; a race only repeats the call
+    if (!raised) {
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return AOTO_ERR_LAUNCH;
+      }
+      raised = true;
+    }
+  }
+  const int tiles = (p.N + 15) / 16;
+  dim3 grid((tiles + RT - 1) / RT, M), block(plan.W * 32);
+  return launch_kernel(kernel, grid, block, smem, stream, pdl, p);
+}
+
+static int check_args(const aoto_qmatmul_args& a, bool pointers) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.group_size <= 0) return AOTO_ERR_ARGUMENT;
+  if (a.group_size % 8 != 0 || a.K % a.group_size != 0) return AOTO_ERR_ARGUMENT;
+  if (a.addend_kind < AOTO_ADDEND_NONE || a.addend_kind > AOTO_ADDEND_FULL) return AOTO_ERR_ARGUMENT;
+  if (a.epilogue < AOTO_EPILOGUE_NONE || a.epilogue > AOTO_EPILOGUE_SILU_MUL_PAIRED) return AOTO_ERR_ARGUMENT;
+  if (!pointers) return AOTO_OK;
+  if (!a.x || !a.packed || !a.scales || !a.out) return AOTO_ERR_ARGUMENT;
+  if (a.addend_kind != AOTO_ADDEND_NONE && !a.addend) return AOTO_ERR_ARGUMENT;
+  if (a.epilogue == AOTO_EPILOGUE_SILU_MUL && !a.gate) return AOTO_ERR_ARGUMENT;
+  if (a.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED && (!a.packed2 || !a.scales2)) return AOTO_ERR_ARGUMENT;
+  if (!aligned_to(a.x, 16) || !aligned_to(a.packed, 16) || !aligned_to(a.scales, 4)) return AOTO_ERR_ARGUMENT;
+  if (a.norm_weight && !aligned_to(a.norm_weight, 16)) return AOTO_ERR_ARGUMENT;
+  if (a.packed2 && (!aligned_to(a.packed2, 16) || !aligned_to(a.scales2, 4))) return AOTO_ERR_ARGUMENT;
+  return AOTO_OK;
+}
+
+int qgemv_launch(const aoto_qmatmul_args& a, cudaStream_t stream) {
+  GemvParams p;
+  p.x = (const bf16*)a.x;
+  p.w0 = (const uint32_t*)a.packed;
+  p.s0 = (const bf16*)a.scales;
+  p.w1 = (const uint32_t*)a.packed2;
+  p.s1 = (const bf16*)a.scales2;
+  p.addend = (const bf16*)a.addend;
+  p.gate = (const bf16*)a.gate;
+  p.norm_w = (const bf16*)a.norm_weight;
+  p.out = (bf16*)a.out;
+  p.N = a.N; p.K = a.K; p.group = a.group_size;
+  p.addend_kind = a.addend_kind; p.epilogue = a.epilogue;
+  p.alpha = a.alpha; p.beta = a.beta; p.eps = a.rms_norm_eps;
+  const bool pdl = (a.flags & AOTO_FLAG_PDL) != 0;
+  const GemvPlan plan = plan_gemv(a);
+  if (!plan.fast) {
+    if (a.K > 49152) return AOTO_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)a.K * 2 + 32 * 4;
+    if (smem > 48 * 1024) {
+      static bool raised = false;
+      if (!raised) {
+        if (cudaFuncSetAttribute(qgemv_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess) {
+          (void)cudaGetLastError();
+          return AOTO_ERR_LAUNCH;
+        }
+        raised = true;
+      }
+    }
+    dim3 grid((a.N + 7) / 8, a.M), block(256);
+    return launch_kernel(qgemv_generic_kernel, grid, block, smem, stream, pdl, p);
+  }
+  const bool paired = a.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED;
+#define AOTO_CASE(rt, uk, pr) \
+  if (plan.RT == rt && plan.UK == uk && paired == pr) return launch_mma<rt, uk, pr>(p, plan, a.M, stream, pdl);
+  AOTO_CASE(1, 1, false)
+  AOTO_CASE(1, 2, false)
+  AOTO_CASE(1, 4, false)
+  AOTO_CASE(2, 2, false)
+  AOTO_CASE(4, 1, false)
+  AOTO_CASE(1, 1, true)
+  AOTO_CASE(1, 2, true)
+  AOTO_CASE(2, 1, true)
+#undef AOTO_CASE
+  return AOTO_ERR_UNSUPPORTED;
+}
+
+int qgemv_check(const aoto_qmatmul_args& a, bool pointers) { return check_args(a, pointers); }
+const char* qgemv_variant(const aoto_qmatmul_args& a) { return plan_gemv(a).name; }
+
+}  // namespace aoto

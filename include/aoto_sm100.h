@@ -1,0 +1,270 @@
+/*
+ * aoto_sm100.h - C ABI of the sm_100a (B200) kernel library behind the
+ * "cuda-sm100" compile target.
+ *
+ * Every entry point has the same shape:
+ *
+ *     int aoto_sm100_<kernel>(const aoto_<kernel>_args* args, void* stream);
+ *
+ * `stream` is a cudaStream_t passed as an opaque pointer (NULL = legacy default
+ * stream). All tensor pointers are DEVICE pointers owned by the caller; the
+ * library never allocates, frees, synchronises or throws. The return value is
+ * AOTO_OK (0) or one of the negative status codes below; a launch error leaves
+ * the CUDA error state cleared (it is consumed and reported as
+ * AOTO_ERR_LAUNCH). Entry points are re-entrant across streams and host
+ * threads. Element type of every activation / scale / table tensor is bfloat16
+ * unless a field says otherwise; packed weights are 32-bit words; indices are
+ * int64.
+ *
+ * Each entry point replaces one per-operation runtime of the reference
+ * compiler (paths are relative to the reference project root,
+ * src/aotolith/...). The reference dispatches an operation either to a Metal
+ * kernel emitted by `codegen/*` or to `runtime/mlx_ops/_evaluate_mlx_op`; the
+ * citation names both where both exist.
+ */
+#ifndef AOTO_SM100_H
+#define AOTO_SM100_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AOTO_ABI_VERSION 1
+
+/* status codes */
+#define AOTO_OK 0
+#define AOTO_ERR_ARGUMENT (-1)    /* null pointer, non-positive size, misaligned buffer */
+#define AOTO_ERR_UNSUPPORTED (-2) /* a legal request this library has no variant for     */
+#define AOTO_ERR_LAUNCH (-3)      /* the CUDA runtime refused the launch                 */
+#define AOTO_ERR_TIMEOUT (-4)     /* a bounded device-side wait ran out                  */
+
+/* Library identity: ABI version and the SM architecture it was compiled for. */
+int aoto_sm100_abi_version(void);
+int aoto_sm100_compiled_arch(void); /* 100 */
+const char* aoto_sm100_status_string(int status);
+
+/* ------------------------------------------------------------------------- */
+/* Packed 4-bit matmul / addmm                                               */
+/* ------------------------------------------------------------------------- */
+
+/* what `addend` is */
+#define AOTO_ADDEND_NONE 0
+#define AOTO_ADDEND_VECTOR 1 /* [N], broadcast over rows (a bias)        */
+#define AOTO_ADDEND_FULL 2   /* [M,N], same shape as the output (residual) */
+
+/* epilogue */
+#define AOTO_EPILOGUE_NONE 0
+#define AOTO_EPILOGUE_SILU_MUL 1        /* out = y * silu(gate[M,N])                   */
+#define AOTO_EPILOGUE_SILU_MUL_PAIRED 2 /* out = y2 * silu(y), y from packed, y2 packed2 */
+
+/*
+ * y[M,N] = beta*addend + alpha * (x_hat[M,K] . W[N,K]^T), W given as signed
+ * 4-bit codes (eight per 32-bit word, code k of a word at bit 4k, word j of a
+ * row = codes 8j..8j+7, two's complement) with one scale per `group_size`
+ * codes along K; x_hat = x, or rms_norm(x)*norm_weight rounded to bf16 when
+ * `norm_weight` is given.
+ *
+ * Replaces: packed `matmul` / `addmm` evaluation,
+ * runtime/mlx_ops/__init__.py:569-619 with runtime/mlx_ops/matmul.py:17-37,
+ * and the int4 streaming GEMV codegen/matmul.py:542-739. For M > 1 it
+ * replaces the `dequantize_i4` + dense `matmul`/`addmm{transpose_b}` pair
+ * (passes/quantize.py:62-71 keeps them apart when M != 1): the weight is
+ * rounded to bf16 as code*scale before it is multiplied, as
+ * codegen/quantize.py:41-63 materialises it.
+ */
+typedef struct aoto_qmatmul_args {
+  const void* x;            /* [M,K] bf16                                        */
+  const void* packed;       /* [N,K/8] int32 words                               */
+  const void* scales;       /* [N,K/group_size] bf16                             */
+  const void* packed2;      /* second weight for SILU_MUL_PAIRED, else NULL      */
+  const void* scales2;
+  const void* addend;       /* per addend_kind, else NULL                        */
+  const void* gate;         /* [M,N] bf16 for SILU_MUL, else NULL                */
+  const void* norm_weight;  /* [K] bf16: fused RMS-norm prologue, else NULL      */
+  void* out;                /* [M,N] bf16                                        */
+  void* scratch;            /* optional split-K workspace (see *_scratch_bytes)  */
+  int64_t scratch_bytes;
+  int32_t M, N, K;
+  int32_t group_size;
+  int32_t addend_kind;
+  int32_t epilogue;
+  float alpha, beta;
+  float rms_norm_eps;
+  int32_t flags;            /* AOTO_FLAG_* */
+} aoto_qmatmul_args;
+
+#define AOTO_FLAG_PDL 1 /* launch with programmatic dependent launch enabled */
+
+int aoto_sm100_qmatmul(const aoto_qmatmul_args* args, void* stream);
+/* 1 if a native variant exists for these shapes/flags, 0 if not (pointers ignored). */
+int aoto_sm100_qmatmul_supported(const aoto_qmatmul_args* args);
+/* Bytes of scratch the split-K variant wants for this shape (0 = none needed). */
+int64_t aoto_sm100_qmatmul_scratch_bytes(const aoto_qmatmul_args* args);
+/* Name of the kernel variant `aoto_sm100_qmatmul` would launch (static string). */
+const char* aoto_sm100_qmatmul_variant(const aoto_qmatmul_args* args);
+
+/*
+ * W[n, 8j+i] = bf16(code) * bf16(scale[n, (8j+i)/group]) rounded once to bf16.
+ * Replaces: `dequantize_i4`, models/quantized.py:61-76, quantize.py:216-234,
+ * codegen/quantize.py:27-63.
+ */
+typedef struct aoto_dequantize_args {
+  const void* packed; /* [N,K/8] int32 */
+  const void* scales; /* [N,K/group] bf16 */
+  void* out;          /* [N,K] bf16 */
+  int32_t N, K, group_size;
+} aoto_dequantize_args;
+int aoto_sm100_dequantize_i4(const aoto_dequantize_args* args, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Normalisation, rotary embedding, gathers                                  */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * out[r,:] = bf16( (x[r,:] (+ residual[r,:])) * rsqrt(mean(.^2)+eps) * weight ),
+ * fp32 statistics, one rounding. With `residual`, `sum_out` (optional) receives
+ * bf16(x+residual), the value the norm was taken of.
+ * Replaces: `rms_norm`, runtime/mlx_ops/normalization.py:73-119,
+ * codegen/norm.py:75-313.
+ */
+typedef struct aoto_rms_norm_args {
+  const void* x;        /* [rows, H] */
+  const void* residual; /* [rows, H] or NULL */
+  const void* weight;   /* [H] or NULL */
+  void* out;            /* [rows, H] */
+  void* sum_out;        /* [rows, H] or NULL */
+  int32_t rows, H;
+  float eps;
+} aoto_rms_norm_args;
+int aoto_sm100_rms_norm(const aoto_rms_norm_args* args, void* stream);
+
+/*
+ * out = x*cos + rotate_half(x)*sin over the last axis, x [B,heads,T,D] given
+ * with explicit element strides (so a transposed view of a projection row can
+ * be read in place), tables [T,D] (row t for step t, already gathered).
+ * Each product and the sum are rounded to bf16, as three separate bf16
+ * operations would. Output is contiguous [B,heads,T,D].
+ * Replaces: `rope`, runtime/mlx_ops/__init__.py:276-280, codegen/index.py:22-67.
+ */
+typedef struct aoto_rope_args {
+  const void* x;
+  const void* cos_table; /* [T,D] */
+  const void* sin_table; /* [T,D] */
+  void* out;
+  int32_t B, heads, T, D;
+  int64_t stride_b, stride_h, stride_t; /* element strides of x; last axis is unit */
+} aoto_rope_args;
+int aoto_sm100_rope(const aoto_rope_args* args, void* stream);
+
+/*
+ * out[i,:] = table[ids[i],:] for int64 ids. `bad_index` (optional, one int64
+ * on the device, caller-zeroed) receives 1 + the first offending position when
+ * an id is outside [0, rows); such rows are written as zeros, never read.
+ * Replaces: `embedding`, runtime/mlx_ops/__init__.py:281-283 with the bounds
+ * contract of runtime/bounds.py:96-106.
+ */
+typedef struct aoto_embedding_args {
+  const void* table;  /* [rows, width] bf16 */
+  const int64_t* ids; /* [count] */
+  void* out;          /* [count, width] */
+  int64_t* bad_index;
+  int32_t rows, width, count;
+} aoto_embedding_args;
+int aoto_sm100_embedding(const aoto_embedding_args* args, void* stream);
+
+/*
+ * out[i] = mask[i] ? on_true : on_false for a bool (uint8) mask, bf16 output.
+ * Replaces: the `fused_elementwise{scalar_tensor, scalar_tensor, where}` that
+ * turns the boolean attention mask into an additive one,
+ * runtime/mlx_ops/pointwise.py:38-42,101-102.
+ */
+typedef struct aoto_mask_select_args {
+  const uint8_t* mask;
+  void* out;
+  int64_t count;
+  float on_true, on_false;
+} aoto_mask_select_args;
+int aoto_sm100_mask_select(const aoto_mask_select_args* args, void* stream);
+
+/*
+ * out[r] = index of the first maximum of logits[r,:] (int64), the greedy
+ * token. Replaces the host `argmax(logits[:, -1, :])` of
+ * models/decoder.py:1054-1087.
+ */
+typedef struct aoto_argmax_args {
+  const void* logits; /* [rows, width] bf16 */
+  int64_t* out;       /* [rows] */
+  int32_t rows, width;
+} aoto_argmax_args;
+int aoto_sm100_argmax(const aoto_argmax_args* args, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Static KV cache                                                           */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * One layer's decode-step cache update. `row` is the packed q/k/v projection
+ * of the step, [1,1,(QH+2*KVH)*D]. Rotates the QH query heads (starting at
+ * query_start) and the KVH key heads (key_start) with the step's cos/sin row,
+ * copies the layer's window shifted left by one slot and writes the rotated
+ * key and the value (value_start) into the last slot.
+ *
+ * cache is [L,2,1,KVH,C,D]; new_pair is [2,1,KVH,C,D] (it may point into a
+ * slice of a larger [L,2,...] buffer); q_out is [1,QH,1,D]. With
+ * `rotate == 0` the key is taken from `key` ([1,KVH,1,D], already rotated) and
+ * no query is produced (`kv_cache_append`).
+ *
+ * Replaces: `rope_kv_cache_append` / `kv_cache_append`,
+ * runtime/mlx_ops/__init__.py:189-236, codegen/kv_cache.py:43-215.
+ */
+typedef struct aoto_kv_append_args {
+  const void* cache;
+  const void* row;
+  const void* key;       /* only when rotate == 0 */
+  const void* cos_row;   /* [D] */
+  const void* sin_row;   /* [D] */
+  void* q_out;
+  void* new_pair;
+  int32_t layer, layers, kv_heads, capacity, head_dim;
+  int32_t query_heads, query_start, key_start, value_start;
+  int32_t rotate;
+} aoto_kv_append_args;
+int aoto_sm100_kv_cache_append(const aoto_kv_append_args* args, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Attention                                                                 */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * Grouped-query scaled-dot-product attention, out = softmax(q.k^T*scale +
+ * mask).v with fp32 softmax statistics; a row whose keys are all masked
+ * yields zeros. q [1,QH,Lq,D], k/v [1,KVH,Lk,D] contiguous, mask additive
+ * bf16 [Lq,Lk] (0 / -inf) or NULL, `causal` adds the top-left aligned causal
+ * rule. out [1,QH,Lq,D]. Lq == 1 selects the split-KV decode kernel, which
+ * needs `scratch` of aoto_sm100_attention_scratch_bytes() when it splits.
+ *
+ * Replaces: `attention`, runtime/mlx_ops/attention.py:52-85,
+ * codegen/attention.py:447-657 (decode) and :68-422 (prefill),
+ * `_zero_fully_masked_rows` codegen/attention.py:660-667.
+ */
+typedef struct aoto_attention_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* mask;
+  void* out;
+  void* scratch;
+  int64_t scratch_bytes;
+  int32_t query_heads, kv_heads, q_len, kv_len, head_dim;
+  int32_t causal;
+  float scale;
+} aoto_attention_args;
+int aoto_sm100_attention(const aoto_attention_args* args, void* stream);
+int64_t aoto_sm100_attention_scratch_bytes(const aoto_attention_args* args);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AOTO_SM100_H */
