@@ -98,8 +98,15 @@ embedding_kernel(const bf16* __restrict__ table, const int64_t* __restrict__ ids
   const int64_t id = ids[i];
   const bool ok = id >= 0 && id < rows;
   if (!ok && bad_index != nullptr && threadIdx.x == 0) {
-    // keep the first offending position
-    atomicCAS(reinterpret_cast<unsigned long long*>(bad_index), 0ull, (unsigned long long)(i + 1));
+    // keep the lowest offending position (0 = none seen yet)
+    unsigned long long* slot = reinterpret_cast<unsigned long long*>(bad_index);
+    const unsigned long long mine = (unsigned long long)(i + 1);
+    unsigned long long seen = *slot;
+    while (seen == 0ull || seen > mine) {
+      const unsigned long long prior = atomicCAS(slot, seen, mine);
+      if (prior == seen) break;
+      seen = prior;
+    }
   }
   bf16* dst = out + (size_t)i * width;
   const bf16* src = table + (size_t)(ok ? id : 0) * width;
