@@ -104,6 +104,17 @@ class AttentionArgs(Structure):
     ]
 
 
+class StepInputsArgs(Structure):
+    _fields_ = [("counters", c_void_p), ("position", c_void_p), ("mask", c_void_p), ("capacity", c_int32)]
+
+
+class GreedyPickArgs(Structure):
+    _fields_ = [
+        ("logits", c_void_p), ("token", c_void_p), ("generated", c_void_p), ("counters", c_void_p),
+        ("width", c_int32), ("generated_capacity", c_int32),
+    ]
+
+
 #: symbol -> (restype, argtypes); one entry per declaration in include/aoto_sm100.h
 EXPORTS: dict[str, tuple] = {
     "aoto_sm100_abi_version": (c_int, []),
@@ -119,6 +130,8 @@ EXPORTS: dict[str, tuple] = {
     "aoto_sm100_embedding": (c_int, [POINTER(EmbeddingArgs), c_void_p]),
     "aoto_sm100_mask_select": (c_int, [POINTER(MaskSelectArgs), c_void_p]),
     "aoto_sm100_argmax": (c_int, [POINTER(ArgmaxArgs), c_void_p]),
+    "aoto_sm100_step_inputs": (c_int, [POINTER(StepInputsArgs), c_void_p]),
+    "aoto_sm100_greedy_pick": (c_int, [POINTER(GreedyPickArgs), c_void_p]),
     "aoto_sm100_kv_cache_append": (c_int, [POINTER(KvAppendArgs), c_void_p]),
     "aoto_sm100_attention": (c_int, [POINTER(AttentionArgs), c_void_p]),
     "aoto_sm100_attention_scratch_bytes": (c_int64, [POINTER(AttentionArgs)]),

@@ -171,9 +171,83 @@ argmax_kernel(const bf16* __restrict__ logits, int64_t* __restrict__ out, int wi
   }
 }
 
+// --------------------------------------------------------------------------
+// device-resident greedy loop: per-step inputs and the pick that closes a step
+// --------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+step_inputs_kernel(const int32_t* __restrict__ counters, int64_t* __restrict__ position,
+                   uint8_t* __restrict__ mask, int capacity) {
+  pdl_wait_for_producers();
+  pdl_release_dependents();
+  const int valid = counters[0];
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx == 0) position[0] = (int64_t)(valid - 1);
+  if (idx < capacity) mask[idx] = idx >= capacity - valid ? 1 : 0;
+}
+
+__global__ void __launch_bounds__(1024)
+greedy_pick_kernel(const bf16* __restrict__ logits, int64_t* __restrict__ token,
+                   int64_t* __restrict__ generated, int32_t* __restrict__ counters, int width,
+                   int generated_capacity) {
+  __shared__ float best_v[32];
+  __shared__ int best_i[32];
+  pdl_wait_for_producers();
+  pdl_release_dependents();
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  bool seen = false;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = __bfloat162float(logits[i]);
+    if (v != v) v = INFINITY;
+    if (!seen || v > bv) { bv = v; bi = i; seen = true; }
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    const int warps = blockDim.x >> 5;
+    bv = lane < warps ? best_v[lane] : -INFINITY;
+    bi = lane < warps ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) {
+      token[0] = (int64_t)bi;
+      const int step = counters[1];
+      if (step < generated_capacity) generated[step] = (int64_t)bi;
+      counters[0] += 1;
+      counters[1] = step + 1;
+    }
+  }
+}
+
 }  // namespace aoto
 
 using namespace aoto;
+
+extern "C" int aoto_sm100_step_inputs(const aoto_step_inputs_args* a, void* stream) {
+  if (!a || !a->counters || !a->position || !a->mask || a->capacity <= 0) return AOTO_ERR_ARGUMENT;
+  return launch_kernel(step_inputs_kernel, dim3((a->capacity + 255) / 256), dim3(256), 0,
+                       (cudaStream_t)stream, false, a->counters, a->position, a->mask, (int)a->capacity);
+}
+
+extern "C" int aoto_sm100_greedy_pick(const aoto_greedy_pick_args* a, void* stream) {
+  if (!a || !a->logits || !a->token || !a->generated || !a->counters || a->width <= 0 ||
+      a->generated_capacity <= 0)
+    return AOTO_ERR_ARGUMENT;
+  return launch_kernel(greedy_pick_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, false,
+                       (const bf16*)a->logits, a->token, a->generated, a->counters, (int)a->width,
+                       (int)a->generated_capacity);
+}
 
 extern "C" int aoto_sm100_dequantize_i4(const aoto_dequantize_args* a, void* stream) {
   if (!a || !a->packed || !a->scales || !a->out) return AOTO_ERR_ARGUMENT;

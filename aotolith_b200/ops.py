@@ -328,3 +328,26 @@ def attention(
         args.scratch, args.scratch_bytes = _ptr(scratch), need
     N.check(lib.aoto_sm100_attention(ctypes.byref(args), _stream()), "aoto_sm100_attention")
     return out
+
+
+def step_inputs(counters: torch.Tensor, position: torch.Tensor, mask: torch.Tensor) -> None:
+    """Write the coming step's rotary position and boolean window mask from the device counters."""
+
+    _need_cuda(counters, position, mask)
+    if counters.dtype != torch.int32 or position.dtype != torch.int64 or mask.dtype != torch.bool:
+        raise PlanInputError("step_inputs expects int32 counters, an int64 position and a bool mask")
+    args = N.StepInputsArgs(_ptr(counters), _ptr(position), _ptr(mask), mask.numel())
+    N.check(N.load().aoto_sm100_step_inputs(ctypes.byref(args), _stream()), "aoto_sm100_step_inputs")
+
+
+def greedy_pick(logits: torch.Tensor, token: torch.Tensor, generated: torch.Tensor, counters: torch.Tensor) -> None:
+    """Greedy token of one logits row into ``token`` and ``generated[counters[1]]``; advance the counters."""
+
+    _need_cuda(logits, token, generated, counters)
+    _bf16(logits, "logits")
+    if token.dtype != torch.int64 or generated.dtype != torch.int64 or counters.dtype != torch.int32:
+        raise PlanInputError("greedy_pick expects int64 token/generated buffers and int32 counters")
+    logits = _dense(logits)
+    args = N.GreedyPickArgs(_ptr(logits), _ptr(token), _ptr(generated), _ptr(counters),
+                            logits.numel(), generated.numel())
+    N.check(N.load().aoto_sm100_greedy_pick(ctypes.byref(args), _stream()), "aoto_sm100_greedy_pick")

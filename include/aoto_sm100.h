@@ -201,6 +201,43 @@ typedef struct aoto_argmax_args {
 int aoto_sm100_argmax(const aoto_argmax_args* args, void* stream);
 
 /* ------------------------------------------------------------------------- */
+/* Device-resident greedy loop                                               */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * The two pieces of host logic of the reference's greedy loop that sit between
+ * decode steps, as kernels, so that a whole step can be one recorded graph with
+ * no host round trip. `counters` is int32[2] on the device: counters[0] =
+ * valid_length (tokens the cache holds after the coming step), counters[1] =
+ * number of tokens generated so far by the loop.
+ *
+ * step_inputs: position[0] = valid_length - 1; mask[c] = (c >= capacity -
+ * valid_length) for c in [0, capacity). Replaces `decode_mask` and the position
+ * tensor of `decode_token` (models/decoder.py:889-932, :960-979).
+ *
+ * greedy_pick: token[0] = first argmax of logits[0..width); generated[counters[1]]
+ * = token (if counters[1] < generated_capacity); then counters[0] += 1 and
+ * counters[1] += 1. Replaces the argmax / append / `valid_length += 1` of
+ * `_greedy_tokens` (models/decoder.py:1054-1087).
+ */
+typedef struct aoto_step_inputs_args {
+  const int32_t* counters;
+  int64_t* position; /* [1] */
+  uint8_t* mask;     /* [capacity] bool */
+  int32_t capacity;
+} aoto_step_inputs_args;
+int aoto_sm100_step_inputs(const aoto_step_inputs_args* args, void* stream);
+
+typedef struct aoto_greedy_pick_args {
+  const void* logits; /* [width] bf16 */
+  int64_t* token;     /* [1] */
+  int64_t* generated; /* [generated_capacity] */
+  int32_t* counters;
+  int32_t width, generated_capacity;
+} aoto_greedy_pick_args;
+int aoto_sm100_greedy_pick(const aoto_greedy_pick_args* args, void* stream);
+
+/* ------------------------------------------------------------------------- */
 /* Static KV cache                                                           */
 /* ------------------------------------------------------------------------- */
 

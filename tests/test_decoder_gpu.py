@@ -1,0 +1,174 @@
+"""End-to-end parity of the compiled runtimes on the GPU with the CPU oracle.
+
+Logit tolerance is the target's: max-abs error <= 1e-2 * max|logit| against the
+oracle interpreter run over the same lowered graph, weights and inputs, plus a
+KL bound on the next-token distribution; greedy tokens must be identical (the
+top-2 gap of the oracle logits is reported when they are not, since ties are
+the one legitimate source of disagreement).
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import aotolith_b200 as aoto
+from aotolith_b200.errors import BucketRangeError, IndexBoundsError, PlanDTypeError, PlanInputError
+from aotolith_b200.models.synthetic import qwen25_05b_shaped, tiny_decoder
+from oracle.interp import OracleRuntime
+from tests.golden_util import GROUP, NEW, PROMPT, eager_fixture
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-2
+KL_TOL = 1e-3
+
+
+def rel_err(actual, expected):
+    expected = expected.float().cpu()
+    return float((actual.float().cpu() - expected).abs().max()) / max(float(expected.abs().max()), 1e-30)
+
+
+def kl(expected, actual):
+    p = torch.log_softmax(expected.float().cpu().reshape(-1), dim=-1)
+    q = torch.log_softmax(actual.float().cpu().reshape(-1), dim=-1)
+    return float((p.exp() * (p - q)).sum())
+
+
+def top2_gap(logits):
+    top = logits.float().reshape(-1).topk(2).values
+    return float(top[0] - top[1])
+
+
+@pytest.fixture(scope="module", params=["qwen2", "llama"])
+def toy(request, cuda):
+    model, data = eager_fixture(request.param)
+    runtime = aoto.models.compile_decoder_static_cache(
+        model, prompt_length=PROMPT, max_new_tokens=NEW, quantize=GROUP, family=request.param
+    )
+    return runtime, data
+
+
+def test_prefill_and_steps_match_oracle(toy):
+    runtime, data = toy
+    oracle = OracleRuntime(runtime)
+    prompt = torch.from_numpy(data["prompt"])
+    logits, compact = runtime.prefill_ids(prompt)
+    want_logits, want_cache = oracle.prefill(prompt)
+    assert rel_err(logits, want_logits) < REL_TOL and kl(want_logits, logits) < KL_TOL
+    cache = runtime.pad_cache(compact)
+    assert rel_err(cache, want_cache) < REL_TOL
+    assert rel_err(logits, torch.from_numpy(data["prefill_logits"])) < 3e-2  # the reference's eager adapters
+    token = torch.tensor([[int(want_logits[:, -1].float().argmax())]])
+    valid = PROMPT
+    for step in range(NEW - 1):
+        valid += 1
+        logits, cache = runtime.decode_token(token, cache, valid)
+        want_logits, want_cache = oracle.decode(token, want_cache, valid)
+        assert rel_err(logits, want_logits) < REL_TOL, f"step {step}"
+        assert kl(want_logits, logits) < KL_TOL
+        assert rel_err(cache, want_cache) < REL_TOL
+        token = torch.tensor([[int(want_logits[:, -1].float().argmax())]])
+
+
+def test_greedy_tokens_match_reference_and_oracle(toy):
+    runtime, data = toy
+    prompt = torch.from_numpy(data["prompt"])
+    tokens = runtime.greedy_generate(prompt).cpu()
+    assert tokens.shape == (1, NEW) and tokens.dtype == torch.int64
+    want, trace, _ = OracleRuntime(runtime).greedy(prompt, NEW)
+    gaps = [top2_gap(t) for t in trace]
+    assert tokens[0].tolist() == want, f"oracle top-2 gaps per step: {gaps}"
+    assert tokens[0].tolist() == data["tokens"].tolist()
+    stepped = runtime.greedy_generate(prompt, sync_each_step=True).cpu()
+    assert torch.equal(stepped, tokens)
+    assert runtime.greedy_generate(prompt, max_new_tokens=0).shape == (1, 0)
+    assert torch.equal(runtime.greedy_generate(prompt, max_new_tokens=3).cpu(), tokens[:, :3])
+    # the recorded stepper is reusable: a second request gives the same answer
+    assert torch.equal(runtime.greedy_generate(prompt).cpu(), tokens)
+
+
+def test_decode_is_functional(toy):
+    runtime, data = toy
+    _, compact = runtime.prefill_ids(torch.from_numpy(data["prompt"]))
+    cache = runtime.pad_cache(compact)
+    before = cache.clone()
+    token = torch.tensor([[7]])
+    first_logits, first_cache = runtime.decode_token(token, cache, PROMPT + 1)
+    second_logits, second_cache = runtime.decode_token(token, cache, PROMPT + 1)
+    assert torch.equal(cache, before)
+    assert torch.equal(first_logits, second_logits) and torch.equal(first_cache, second_cache)
+    assert torch.equal(first_cache[:, :, :, :, :-1], cache[:, :, :, :, 1:])
+    assert first_cache.data_ptr() != second_cache.data_ptr()
+
+
+def test_plan_call_contract(toy):
+    runtime, data = toy
+    device = runtime.device
+    with pytest.raises(PlanInputError):
+        runtime.prefill_ids(torch.zeros((1, PROMPT + 1), dtype=torch.int64))
+    with pytest.raises(PlanInputError):
+        runtime.decode(torch.zeros((1, 1), dtype=torch.int64))
+    cache = torch.zeros(runtime._cache_tensor_type().shape, dtype=torch.bfloat16, device=device)
+    mask = runtime.decode_mask(3)
+    with pytest.raises(PlanDTypeError):
+        runtime.decode(torch.zeros((1, 1), dtype=torch.int32, device=device),
+                       torch.zeros((1, 1), dtype=torch.int64, device=device), mask, cache)
+    with pytest.raises(IndexBoundsError):
+        runtime.decode_token(torch.tensor([[100000]]), cache, 3, verify_token=True)
+    with pytest.raises(IndexError):  # the builtin base class holds too
+        runtime.decode_token(torch.tensor([[-1]]), cache, 3, verify_token=True)
+    with pytest.raises(PlanInputError):
+        runtime.decode_token(torch.tensor([[1]]), cache, runtime.cache_capacity)
+    rows = runtime.decode_mask(2).reshape(-1).tolist()
+    assert rows == [False] * (runtime.cache_capacity - 2) + [True, True]
+
+
+def test_bucket_padding_is_invisible(cuda):
+    """A prompt served by a wider bucket decodes as it does on an exact-length plan."""
+
+    model = tiny_decoder("qwen2", seed=21)
+    bucketed = aoto.compile_qwen2_bucketed(model, prompt_lengths=[4, 8, 16], max_new_tokens=5, quantize=16)
+    assert bucketed.prompt_lengths == (4, 8, 16) and bucketed.family == "qwen2"
+    generator = torch.Generator().manual_seed(3)
+    for length in (1, 3, 4, 6, 11, 16):
+        prompt = torch.randint(0, 128, (1, length), generator=generator)
+        exact = aoto.compile_qwen2_static_cache(model, prompt_length=length, max_new_tokens=5, quantize=16)
+        want_logits, want_compact = exact.prefill_ids(prompt)
+        bucket = bucketed.bucket_for(length)
+        logits, compact = bucket.prefill_padded(prompt)
+        assert rel_err(logits, want_logits) < REL_TOL
+        assert rel_err(compact[:, :, :, :, bucket.prompt_length - length :], want_compact) < REL_TOL
+        assert torch.equal(bucketed.greedy_generate(prompt).cpu(), exact.greedy_generate(prompt).cpu())
+    with pytest.raises(BucketRangeError):
+        bucketed.greedy_generate(torch.zeros((1, 17), dtype=torch.int64))
+    # one copy of the weights for the whole set
+    pointers = {
+        name: tensor.data_ptr()
+        for name, tensor in zip(bucketed.buckets[0].decode.state_names, bucketed.buckets[0].decode._state_values)
+        if name.endswith("_packed")
+    }
+    for bucket in bucketed.buckets:
+        for plan in (bucket.prefill, bucket.decode):
+            for name, tensor in zip(plan.state_names, plan._state_values):
+                if name in pointers:
+                    assert tensor.data_ptr() == pointers[name]
+
+
+def test_qwen_shaped_layers_match_oracle(cuda):
+    """Two layers of the Qwen2.5-0.5B shape: the group-64 tensor-pipe kernels on real sizes."""
+
+    model = qwen25_05b_shaped(seed=5, layers=2)
+    runtime = aoto.compile_qwen2_static_cache(model, prompt_length=16, max_new_tokens=4, quantize=64)
+    kernels = {s.artifact_name for s in runtime.decode.plan.selections if s.kind in ("matmul", "addmm")}
+    assert kernels == {"aoto_sm100_qmatmul[qgemv_mma]", "aoto_sm100_qmatmul[qgemv_mma_paired]"}
+    prompt = torch.randint(0, 151936, (1, 16), generator=torch.Generator().manual_seed(9))
+    oracle = OracleRuntime(runtime)
+    want_tokens, trace, want_cache = oracle.greedy(prompt, 4)
+    logits, compact = runtime.prefill_ids(prompt)
+    assert rel_err(logits, trace[0]) < REL_TOL and kl(trace[0], logits) < KL_TOL
+    tokens = runtime.greedy_generate(prompt).cpu()
+    gaps = [top2_gap(t) for t in trace]
+    assert tokens[0].tolist() == want_tokens, f"oracle top-2 gaps per step: {gaps}"
+    footprint = runtime.memory_footprint()
+    assert footprint.cache_bytes == 2 * 2 * 2 * 20 * 64 * 2
+    assert footprint.step_peak_bytes > footprint.weights_bytes
