@@ -181,6 +181,7 @@ class _QuantizedDecoder(torch.nn.Module):
         group_size: int,
         weight_bits: int = 4,
         require: str | None = None,
+        packed_from: "_QuantizedDecoder | None" = None,
     ) -> None:
         super().__init__()
         config = model.config
@@ -211,7 +212,14 @@ class _QuantizedDecoder(torch.nn.Module):
         cosine, sine = rotary_tables(self.cache_capacity, self.head_dim, theta, dtype)
         self.register_buffer("cosine_table", cosine, persistent=False)
         self.register_buffer("sine_table", sine, persistent=False)
-        self._pack(model, dtype)
+        if isinstance(packed_from, _QuantizedDecoder) and packed_from.group_size == self.group_size:
+            # Packing is the expensive part of construction and does not depend on the
+            # capacity: adopt the buffers another adapter of the same model already packed.
+            for name, tensor in packed_from.named_buffers():
+                if name not in ("cosine_table", "sine_table"):
+                    self.register_buffer(name, tensor, persistent=False)
+        else:
+            self._pack(model, dtype)
 
     def _pack(self, model: torch.nn.Module, dtype: torch.dtype) -> None:
         def keep(name: str, tensor: torch.Tensor) -> None:

@@ -327,6 +327,7 @@ def _compile_bucket(
     family: str | None = None,
     target: str = DEFAULT_TARGET,
     memory: str = "latency",
+    _packed_from: Any = None,
 ) -> DecoderStaticCacheRuntime:
     if memory not in MEMORY_POLICIES:
         raise CompilationError(
@@ -360,8 +361,10 @@ def _compile_bucket(
         raise UnsupportedModelError("the cuda-sm100 target packs 4-bit weights only")
 
     settings = dict(cache_capacity=capacity, group_size=quantize, weight_bits=quantize_bits, require=family)
-    prefill_module = QuantizedDecoderPrefillModule(model, **settings).eval()
-    decode_module = QuantizedDecoderDecodeModule(model, **settings).eval()
+    prefill_module = QuantizedDecoderPrefillModule(model, packed_from=_packed_from, **settings).eval()
+    decode_module = QuantizedDecoderDecodeModule(model, packed_from=prefill_module, **settings).eval()
+    if isinstance(_packed_from, list):
+        _packed_from.append(prefill_module)
     options = dict(codegen_matmul=codegen_matmul, codegen_attention=codegen_attention,
                    autotune=autotune, target=target)
     mask = torch.from_numpy(prefill_mask(prompt_length, prompt_length))
@@ -507,10 +510,18 @@ def compile_decoder_bucketed(
         raise CompilationError(f"bucket widths must be positive, got {widths}")
     if widths != sorted(set(widths)):
         raise CompilationError(f"bucket widths must be strictly increasing, got {widths}")
-    runtimes = [
-        _compile_bucket(model, prompt_length=width, max_new_tokens=max_new_tokens, **options)
-        for width in widths
-    ]
+    runtimes = []
+    packed = None
+    for width in widths:
+        holder: list = []
+        runtimes.append(
+            _compile_bucket(
+                model, prompt_length=width, max_new_tokens=max_new_tokens,
+                _packed_from=packed if packed is not None else holder, **options,
+            )
+        )
+        if packed is None:
+            packed = holder[0]
     shared = share_plan_state([plan for rt in runtimes for plan in (rt.prefill, rt.decode)])
     buckets = tuple(
         replace(rt, prefill=shared[2 * i], decode=shared[2 * i + 1]) for i, rt in enumerate(runtimes)

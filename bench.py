@@ -1,0 +1,393 @@
+"""Benchmark of the static-KV-cache decoder path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workload (default ``qwen25_05b``): a Qwen2.5-0.5B-shaped decoder (hidden 896,
+MLP 4864, 24 layers, 14/2 heads, head dim 64, vocab 151936, tied embeddings,
+q/k/v bias, bf16), random-init from a seed, 4-bit group-64 packed, compiled
+through ``compile_qwen2_static_cache``; prompt = 128 uniform-random token ids,
+64 greedy tokens at batch 1. One *step* of the benchmark is one such request:
+prefill, then 63 decode steps on the device-resident stepper.
+
+The printed JSON line reports
+
+* ``value``    decode tok/s, whole job: decode steps of all ranks / device time of
+               the decode loops (CUDA events; prompt and weights resident in HBM);
+* ``e2e``      generated tok/s through ``runtime.greedy_generate`` from pinned host
+               prompt ids to host tokens (prefill, copies and the final read-back
+               inside the timed region);
+* ``roofline`` the largest single kernel of a decode step (the LM-head GEMV over
+               the packed vocabulary matrix), timed live with CUDA events on
+               rotating weight copies larger than L2, against the measured HBM peak;
+* ``step_roofline`` the same arithmetic for a whole decode step;
+* ``cpu_baseline`` the same decoder evaluated eagerly by PyTorch on the host cores
+               for a bounded sample (prefill + a few decode steps).
+
+``--impl reference`` times only that CPU arm. With ``--gpus N`` (launched by
+``torch.distributed.run``) every rank serves its own request stream on its own
+GPU - the path has no exchange step at this model size - and the line is the
+sum over ranks with the slowest rank's time.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PROMPT, NEW_TOKENS, GROUP = 128, 64, 64
+
+WORKLOADS = {
+    "qwen25_05b": dict(builder="qwen25_05b_shaped", family="qwen2", layers=24,
+                       description="Qwen2.5-0.5B-shaped, 4-bit g64, prompt 128, 64 greedy tokens, batch 1"),
+    "llama3_8b": dict(builder="llama3_8b_shaped", family="llama", layers=32,
+                      description="Llama-3-8B-shaped, 4-bit g64, prompt 128, 64 greedy tokens, batch 1"),
+}
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:  # noqa: BLE001
+            pass
+    return 6650.0, "fallback"
+
+
+def projection_bytes(n: int, k: int, *, bias=False, norm=False, residual=False, m: int = 1) -> int:
+    """Algorithmic bytes of one packed projection (codes, scales, x, y and optional operands)."""
+
+    total = n * k // 2 + n * (k // GROUP) * 2 + m * k * 2 + m * n * 2
+    total += n * 2 if bias else 0
+    total += k * 2 if norm else 0
+    total += m * n * 2 if residual else 0
+    return total
+
+
+def step_bytes(config, valid_length: int) -> int:
+    """Algorithmic HBM bytes of one decode step (weights once, KV window read, logits, cache write)."""
+
+    h, i, layers = config.hidden_size, config.intermediate_size, config.num_hidden_layers
+    qh, kvh, d, v = config.num_attention_heads, config.num_key_value_heads, config.head_dim, config.vocab_size
+    qkv = projection_bytes((qh + 2 * kvh) * d, h, bias=True, norm=True)
+    o = projection_bytes(h, qh * d, residual=True)
+    gate_up = 2 * (i * h // 2 + i * (h // GROUP) * 2) + h * 2 + h * 2 + i * 2
+    down = projection_bytes(h, i, residual=True)
+    head = projection_bytes(v, h, norm=True)
+    kv_read = 2 * kvh * d * 2 * valid_length
+    kv_write = 2 * kvh * d * 2
+    return layers * (qkv + o + gate_up + down + kv_read + kv_write) + head + h * 2
+
+
+class ClockSampler:
+    """Samples ``nvidia-smi`` clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) == 6:
+                    self.rows.append(parts)
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, reasons, peak = [], set(), None
+        for sm, sm_max, hw, hw_thermal, sw_thermal, power in self.rows:
+            try:
+                clocks.append(float(sm))
+                peak = float(sm_max)
+            except ValueError:
+                continue
+            for name, flag in (("hw_slowdown", hw), ("hw_thermal_slowdown", hw_thermal),
+                               ("sw_thermal_slowdown", sw_thermal), ("sw_power_cap", power)):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": peak,
+            "reasons": sorted(reasons),
+            "samples": len(clocks),
+        }
+
+
+def build_model(workload: str, seed: int):
+    from aotolith_b200.models import synthetic
+
+    spec = WORKLOADS[workload]
+    return getattr(synthetic, spec["builder"])(seed=seed), spec
+
+
+def seeded_prompt(vocab: int, seed: int) -> torch.Tensor:
+    return torch.randint(0, vocab, (1, PROMPT), generator=torch.Generator().manual_seed(seed), dtype=torch.int64)
+
+
+# ---------------------------------------------------------------------------
+# CPU arm
+# ---------------------------------------------------------------------------
+
+def cpu_sample(model, prompt, decode_steps: int) -> dict:
+    from oracle.eager import EagerCpuDecoder
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    decoder = EagerCpuDecoder(model, PROMPT, NEW_TOKENS, GROUP)
+    _, prefill_s, decode_s = decoder.run(prompt, decode_steps)
+    return {
+        "value": decode_steps / decode_s,
+        "unit": "tok/s",
+        "cores": torch.get_num_threads(),
+        "kind": "port",
+        "sample": f"prefill of {PROMPT} tokens ({prefill_s:.2f} s, not counted) then {decode_steps} "
+                  f"decode steps of the same decoder, PyTorch CPU bf16 eager ({decode_s:.2f} s)",
+        "prefill_tok_s": PROMPT / prefill_s,
+    }
+
+
+def run_reference(args) -> None:
+    """The CPU arm alone: one step = one greedy decode step on the host cores."""
+
+    from oracle.eager import EagerCpuDecoder
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    model, spec = build_model(args.workload, seed=0)
+    prompt = seeded_prompt(model.config.vocab_size, 1)
+    torch.set_num_threads(os.cpu_count() or 1)
+    decoder = EagerCpuDecoder(model, PROMPT, NEW_TOKENS, GROUP)
+    prefill_s = decoder.start(prompt)
+    for _ in range(args.warmup):
+        decoder.step()
+    seconds = [decoder.step() for _ in range(args.steps)]
+    value = len(seconds) / sum(seconds)
+    baseline = {
+        "value": value, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
+        "sample": f"{args.steps} decode steps after a {PROMPT}-token prefill ({prefill_s:.2f} s, not counted), "
+                  "PyTorch CPU bf16 eager over the same adapter modules",
+        "prefill_tok_s": PROMPT / prefill_s,
+    }
+    print(json.dumps({
+        "impl": "reference",
+        "metric": "batch-1 decode tok/s (4-bit g64 static cache)",
+        "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sum(seconds) * 1e3 / len(seconds), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": spec["description"], "arm": "host CPU cores, PyTorch eager",
+                   "step": "one decode step (one token) on the host"},
+        "cpu_baseline": baseline,
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+
+def time_lm_head(runtime, peak_gbs: float, peak_kind: str) -> dict:
+    """The LM-head GEMV alone, on rotating copies of its weight so every launch streams from HBM."""
+
+    from aotolith_b200 import ops
+
+    state = dict(zip(runtime.decode.state_names, runtime.decode._state_values))
+    packed, scales, norm = state["lm_head_0_packed"], state["lm_head_0_scales"], state["final_norm"]
+    n, words = packed.shape
+    k = words * 8
+    copies = max(3, int(400e6 // (packed.numel() * 4)) + 1)
+    packs = [packed.clone() for _ in range(copies)]
+    scale_copies = [scales.clone() for _ in range(copies)]
+    x = torch.randn(1, k, device=packed.device).bfloat16()
+    out = torch.empty(1, n, dtype=torch.bfloat16, device=packed.device)
+    for i in range(copies):
+        ops.qmatmul(x, packs[i], scale_copies[i], group_size=GROUP, norm_weight=norm, rms_norm_eps=1e-6, out=out)
+    torch.cuda.synchronize()
+    iterations = 60
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(iterations):
+        j = i % copies
+        ops.qmatmul(x, packs[j], scale_copies[j], group_size=GROUP, norm_weight=norm, rms_norm_eps=1e-6, out=out)
+    stop.record()
+    torch.cuda.synchronize()
+    seconds = start.elapsed_time(stop) / 1e3 / iterations
+    algorithmic = projection_bytes(n, k, norm=True)
+    achieved = algorithmic / seconds / 1e9
+    return {
+        "kernel": f"qgemv_mma_kernel (LM head, N={n}, K={k})", "bound": "hbm", "achieved": achieved,
+        "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs, "traffic": None,
+        "peak_source": peak_kind, "bytes_per_launch": algorithmic, "us_per_launch": seconds * 1e6,
+        "note": f"{iterations} launches over {copies} weight copies ({copies * packed.numel() * 4 / 1e6:.0f} MB > L2)",
+    }
+
+
+def run_ours(args) -> None:
+    import torch.distributed as dist
+
+    import aotolith_b200 as aoto
+    from aotolith_b200.models.session import decode_session
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the cuda-sm100 target has no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    model, spec = build_model(args.workload, seed=0)
+    compile_fn = aoto.compile_qwen2_static_cache if spec["family"] == "qwen2" else aoto.compile_llama_static_cache
+    runtime = compile_fn(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS, quantize=GROUP)
+    config = model.config
+    prompt_host = seeded_prompt(config.vocab_size, 1 + rank).pin_memory()
+    prompt_dev = prompt_host.to(device)
+    session = decode_session(runtime)
+    decode_steps = NEW_TOKENS - 1
+    kernels_per_token = sum(1 for s in runtime.decode.plan.selections if s.is_native) + 2
+    kernels_prefill = sum(1 for s in runtime.prefill.plan.selections
+                          if s.is_native and "weight operand" not in (s.artifact_name or "")) + 1
+
+    def request(ids):
+        """One request with device-resident inputs; returns (tokens, decode-loop milliseconds)."""
+        logits, compact = runtime.prefill_ids(ids)
+        cache = runtime.pad_cache(compact)
+        from aotolith_b200 import ops
+        token = ops.argmax(logits[:, -1, :]).reshape(1, 1)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        rest = session.run(token, cache, PROMPT, decode_steps)
+        end.record()
+        return rest, begin, end
+
+    for _ in range(max(args.warmup, 3)):
+        request(prompt_dev)
+        runtime.greedy_generate(prompt_host).cpu()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    wall_start = time.perf_counter()
+    events = []
+    for _ in range(args.steps):
+        _, begin, end = request(prompt_dev)
+        events.append((begin, end))
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - wall_start
+    decode_ms = sum(b.elapsed_time(e) for b, e in events)
+
+    # end to end through the public call: pinned host ids in, host tokens out
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e2e_start = time.perf_counter()
+    for _ in range(args.steps):
+        tokens_host = runtime.greedy_generate(prompt_host).cpu()
+    e2e_wall = time.perf_counter() - e2e_start
+    clocks = sampler.stop() if rank == 0 else None
+
+    timings = torch.tensor([decode_ms, wall, e2e_wall], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(timings, op=dist.ReduceOp.MAX)
+        dist.barrier()
+    decode_ms, wall, e2e_wall = (float(t) for t in timings.cpu())
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        tokens_total = world * args.steps * decode_steps
+        value = tokens_total / (decode_ms / 1e3)
+        per_token_us = decode_ms * 1e3 / (args.steps * decode_steps)
+        mean_valid = PROMPT + 1 + decode_steps // 2
+        bytes_step = step_bytes(config, mean_valid)
+        achieved_step = bytes_step / (per_token_us * 1e-6) / 1e9
+        line = {
+            "metric": "batch-1 decode tok/s (4-bit g64 static cache)",
+            "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": wall * 1e3 / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": spec["description"],
+                "step": "one request: prefill(128) + 63 decode steps; value counts the decode loop only",
+                "parallelism": f"{world} independent request stream(s), one runtime per GPU",
+                "l2": "inputs larger than L2: 262 MB of packed weights are streamed per token",
+                "e2e_definition": "64 generated tokens / wall time of greedy_generate(host ids) -> host tokens",
+            },
+            "decode_us_per_token": per_token_us,
+            "e2e": {"value": world * args.steps * NEW_TOKENS / e2e_wall, "unit": "tok/s",
+                    "h2d_bytes_per_step": PROMPT * 8, "d2h_bytes_per_step": NEW_TOKENS * 8},
+            "gpu_launches": args.steps * (kernels_prefill + decode_steps * kernels_per_token),
+            "clocks": clocks,
+            "step_roofline": {"bound": "hbm", "achieved": achieved_step, "peak": peak, "unit": "GB/s",
+                              "frac": achieved_step / peak, "bytes_per_step": bytes_step,
+                              "frac_of_8tbs": achieved_step / 8000.0, "peak_source": peak_kind},
+            "roofline": time_lm_head(runtime, peak, peak_kind),
+        }
+        if world == 1 and not args.skip_cpu:
+            line["cpu_baseline"] = cpu_sample(model, prompt_host, 3)
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--workload", choices=sorted(WORKLOADS), default="qwen25_05b")
+    parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
