@@ -82,7 +82,10 @@ class MaskSelectArgs(Structure):
 
 
 class ArgmaxArgs(Structure):
-    _fields_ = [("logits", c_void_p), ("out", c_void_p), ("rows", c_int32), ("width", c_int32)]
+    _fields_ = [
+        ("logits", c_void_p), ("out", c_void_p), ("scratch", c_void_p), ("scratch_bytes", c_int64),
+        ("rows", c_int32), ("width", c_int32),
+    ]
 
 
 class KvAppendArgs(Structure):
@@ -111,6 +114,7 @@ class StepInputsArgs(Structure):
 class GreedyPickArgs(Structure):
     _fields_ = [
         ("logits", c_void_p), ("token", c_void_p), ("generated", c_void_p), ("counters", c_void_p),
+        ("scratch", c_void_p), ("scratch_bytes", c_int64),
         ("width", c_int32), ("generated_capacity", c_int32),
     ]
 
@@ -130,6 +134,7 @@ EXPORTS: dict[str, tuple] = {
     "aoto_sm100_embedding": (c_int, [POINTER(EmbeddingArgs), c_void_p]),
     "aoto_sm100_mask_select": (c_int, [POINTER(MaskSelectArgs), c_void_p]),
     "aoto_sm100_argmax": (c_int, [POINTER(ArgmaxArgs), c_void_p]),
+    "aoto_sm100_argmax_scratch_bytes": (c_int64, [c_int32, c_int32]),
     "aoto_sm100_step_inputs": (c_int, [POINTER(StepInputsArgs), c_void_p]),
     "aoto_sm100_greedy_pick": (c_int, [POINTER(GreedyPickArgs), c_void_p]),
     "aoto_sm100_kv_cache_append": (c_int, [POINTER(KvAppendArgs), c_void_p]),

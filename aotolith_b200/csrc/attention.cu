@@ -1,10 +1,11 @@
 // Grouped-query attention over the static bf16 KV cache.
 //
-//  * decode (q_len == 1): FlashDecoding-style. grid = (query heads, key splits);
-//    each CTA scores its key range, keeps fp32 softmax statistics and a partial
-//    weighted sum of V. With one split the CTA writes the output row itself;
-//    with several it writes (max, sum, acc[D]) to scratch and a small combine
-//    kernel merges them in split order.
+//  * decode (q_len == 1): FlashDecoding-style. grid = (kv heads, key splits);
+//    each CTA stages its K/V tiles with async copies, scores them for every
+//    query head of the group, keeps fp32 softmax statistics and a partial
+//    weighted sum of V. With one split the CTA writes the output rows itself;
+//    with several it writes (max, sum, acc[D]) to scratch and the last CTA of
+//    the kv head to arrive merges them in split order.
 //  * prefill (q_len > 1): one warp per (head, query row), keys in tiles of 32
 //    with an online softmax.
 //
@@ -28,113 +29,155 @@ struct AttnParams {
 
 constexpr int DECODE_THREADS = 128;
 
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// Decode: one CTA per (kv head, key split). The CTA pulls its K and V tiles
+// into shared memory with 16-byte async copies issued all at once (a decode
+// step is latency bound: what matters is that every load of the CTA is in
+// flight together), scores them against ALL query heads of the group (the
+// tiles are read from HBM once per group, not once per query head), and keeps
+// fp32 softmax statistics. With several splits the partial (max, sum, acc[D])
+// of every query head goes to scratch and the last CTA of the kv head to
+// finish merges them in split order; the arrival counter it used is left at
+// zero for the next launch.
+//
+// Rows of the shared tiles are padded by 16 bytes so that a warp reading one
+// key per lane touches every bank once.
 __global__ void __launch_bounds__(DECODE_THREADS)
 attention_decode_kernel(const AttnParams p) {
-  extern __shared__ float sm[];
-  const int D = p.D;
-  float* qs = sm;                       // D
-  float* sc = qs + D;                   // keys_per_split
-  float* red = sc + p.keys_per_split;   // 32
-  float* pv = red + 32;                 // parts * D
+  extern __shared__ uint4 smem4[];
+  const int D = p.D, G = p.QH / p.KVH, TK = p.keys_per_split;
+  const int row_bytes = D * 2 + 16;
+  unsigned char* kt = reinterpret_cast<unsigned char*>(smem4);
+  unsigned char* vt = kt + (size_t)TK * row_bytes;
+  float* qs = reinterpret_cast<float*>(vt + (size_t)TK * row_bytes);  // G*D, scaled
+  float* sc = qs + G * D;                                             // G*TK scores -> weights
+  float* stat = sc + G * TK;                                          // G*2 (max, sum)
+  float* madd = stat + G * 2;                                         // TK additive mask
+  __shared__ int is_last;
+
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int head = blockIdx.x, split = blockIdx.y;
-  const int kvh = head / (p.QH / p.KVH);
-  const int k0 = split * p.keys_per_split;
-  const int k1 = min(p.Lk, k0 + p.keys_per_split);
-  const int nkeys = k1 - k0;
+  const int kvh = blockIdx.x, split = blockIdx.y;
+  const int k0 = split * TK;
+  const int nkeys = min(TK, p.Lk - k0);
   pdl_wait_for_producers();
   pdl_release_dependents();
 
-  for (int d = tid; d < D; d += DECODE_THREADS)
-    qs[d] = __bfloat162float(p.q[(size_t)head * D + d]) * p.scale;
+  // all loads of the tile first
+  const int chunks = D >> 3;  // 16-byte chunks per row
+  const bf16* kbase = p.k + ((size_t)kvh * p.Lk + k0) * D;
+  const bf16* vbase = p.v + ((size_t)kvh * p.Lk + k0) * D;
+  for (int c = tid; c < nkeys * chunks; c += DECODE_THREADS) {
+    const int r = c / chunks, j = c - r * chunks;
+    cp_async_16(kt + (size_t)r * row_bytes + j * 16, kbase + (size_t)r * D + j * 8);
+    cp_async_16(vt + (size_t)r * row_bytes + j * 16, vbase + (size_t)r * D + j * 8);
+  }
+  for (int i = tid; i < G * D; i += DECODE_THREADS)
+    qs[i] = __bfloat162float(p.q[(size_t)kvh * G * D + i]) * p.scale;
+  for (int i = tid; i < TK; i += DECODE_THREADS)
+    madd[i] = (i < nkeys) ? (p.mask ? __bfloat162float(p.mask[k0 + i]) : 0.f) : -INFINITY;
+  cp_async_wait_all();
   __syncthreads();
 
-  const bf16* kbase = p.k + (size_t)kvh * p.Lk * D;
-  const bf16* vbase = p.v + (size_t)kvh * p.Lk * D;
-
-  // scores: one warp per key, lanes over D (pairs)
-  float local_max = -INFINITY;
-  for (int i = warp; i < nkeys; i += DECODE_THREADS / 32) {
-    const int key = k0 + i;
-    float madd = 0.f;
-    if (p.mask != nullptr) madd = __bfloat162float(p.mask[key]);
+  // scores: thread <-> (key, head) pairs
+  for (int item = tid; item < G * TK; item += DECODE_THREADS) {
+    const int h = item / TK, key = item - h * TK;
     float s = -INFINITY;
-    if (madd != -INFINITY) {  // warp-uniform: skip masked keys without reading them
-      const uint32_t* krow = reinterpret_cast<const uint32_t*>(kbase + (size_t)key * D);
+    const float m_add = madd[key];
+    if (m_add != -INFINITY) {
+      const uint4* krow = reinterpret_cast<const uint4*>(kt + (size_t)key * row_bytes);
+      const float* qh = qs + h * D;
       float dot = 0.f;
-      for (int d2 = lane; d2 < (D >> 1); d2 += 32) {
-        const uint32_t kk = krow[d2];
-        dot = fmaf(bf16x2_lo(kk), qs[2 * d2], dot);
-        dot = fmaf(bf16x2_hi(kk), qs[2 * d2 + 1], dot);
+      for (int j = 0; j < chunks; ++j) {
+        const uint4 kk = krow[j];
+        const float* q8 = qh + j * 8;
+        dot = fmaf(bf16x2_lo(kk.x), q8[0], dot); dot = fmaf(bf16x2_hi(kk.x), q8[1], dot);
+        dot = fmaf(bf16x2_lo(kk.y), q8[2], dot); dot = fmaf(bf16x2_hi(kk.y), q8[3], dot);
+        dot = fmaf(bf16x2_lo(kk.z), q8[4], dot); dot = fmaf(bf16x2_hi(kk.z), q8[5], dot);
+        dot = fmaf(bf16x2_lo(kk.w), q8[6], dot); dot = fmaf(bf16x2_hi(kk.w), q8[7], dot);
       }
-      s = warp_sum(dot) + madd;
+      s = dot + m_add;
     }
-    if (lane == 0) sc[i] = s;
-    local_max = fmaxf(local_max, s);
+    sc[item] = s;
   }
-  // block max
   __syncthreads();
-  if (lane == 0) red[warp] = local_max;
-  __syncthreads();
-  float m = -INFINITY;
-  for (int w = 0; w < DECODE_THREADS / 32; ++w) m = fmaxf(m, red[w]);
-  const float m_safe = (m == -INFINITY) ? 0.f : m;
-
-  float lsum = 0.f;
-  for (int i = tid; i < nkeys; i += DECODE_THREADS) {
-    const float s = sc[i];
-    const float e = (s == -INFINITY) ? 0.f : expf(s - m_safe);
-    sc[i] = e;
-    lsum += e;
+  // per-head max and sum: one warp per head (round robin)
+  for (int h = warp; h < G; h += DECODE_THREADS / 32) {
+    float m = -INFINITY;
+    for (int key = lane; key < TK; key += 32) m = fmaxf(m, sc[h * TK + key]);
+    m = warp_max(m);
+    const float m_safe = (m == -INFINITY) ? 0.f : m;
+    float l = 0.f;
+    for (int key = lane; key < TK; key += 32) {
+      const float s = sc[h * TK + key];
+      const float e = (s == -INFINITY) ? 0.f : expf(s - m_safe);
+      sc[h * TK + key] = e;
+      l += e;
+    }
+    l = warp_sum(l);
+    if (lane == 0) { stat[2 * h] = m; stat[2 * h + 1] = l; }
   }
-  const float l = block_sum(lsum, red);  // also orders the sc[] writes
-
-  // P.V: threads_per_row lanes cover D in pairs; the remaining factor splits keys
-  const int tpr = D >> 1;
-  const int parts = DECODE_THREADS / tpr;  // >= 1 because D <= 256
-  const int part = tid / tpr, dpair = tid % tpr;
-  float a0 = 0.f, a1 = 0.f;
-  if (part < parts) {
-    for (int i = part; i < nkeys; i += parts) {
-      const float w = sc[i];
-      if (w != 0.f) {
-        const uint32_t vv = reinterpret_cast<const uint32_t*>(vbase + (size_t)(k0 + i) * D)[dpair];
-        a0 = fmaf(w, bf16x2_lo(vv), a0);
-        a1 = fmaf(w, bf16x2_hi(vv), a1);
+  __syncthreads();
+  // P.V: thread <-> (head, dim pair)
+  const int pairs = D >> 1;
+  for (int item = tid; item < G * pairs; item += DECODE_THREADS) {
+    const int h = item / pairs, dp = item - h * pairs;
+    float a0 = 0.f, a1 = 0.f;
+    const float* w = sc + h * TK;
+    for (int key = 0; key < nkeys; ++key) {
+      const float wk = w[key];
+      if (wk != 0.f) {
+        const uint32_t vv = *reinterpret_cast<const uint32_t*>(vt + (size_t)key * row_bytes + dp * 4);
+        a0 = fmaf(wk, bf16x2_lo(vv), a0);
+        a1 = fmaf(wk, bf16x2_hi(vv), a1);
       }
     }
-    pv[part * D + 2 * dpair] = a0;
-    pv[part * D + 2 * dpair + 1] = a1;
-  }
-  __syncthreads();
-  for (int d = tid; d < D; d += DECODE_THREADS) {
-    float acc = 0.f;
-    for (int q = 0; q < parts; ++q) acc += pv[q * D + d];
+    const int head = kvh * G + h;
     if (p.splits == 1) {
+      const float l = stat[2 * h + 1];
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      p.out[(size_t)head * D + d] = __float2bfloat16_rn(acc * inv);
+      *reinterpret_cast<uint32_t*>(p.out + (size_t)head * D + dp * 2) = pack_bf16x2(a0 * inv, a1 * inv);
     } else {
-      float* dst = p.scratch + ((size_t)head * p.splits + split) * (D + 2);
-      dst[2 + d] = acc;
-      if (d == 0) { dst[0] = m; dst[1] = l; }
+      float* dst = p.scratch + SCRATCH_HEADER_BYTES / 4 + ((size_t)head * p.splits + split) * (D + 2);
+      dst[2 + dp * 2] = a0;
+      dst[3 + dp * 2] = a1;
+      if (dp == 0) { dst[0] = stat[2 * h]; dst[1] = stat[2 * h + 1]; }
     }
   }
-}
+  if (p.splits == 1) return;
 
-__global__ void __launch_bounds__(128)
-attention_combine_kernel(const AttnParams p) {
-  const int head = blockIdx.x, D = p.D;
-  const float* base = p.scratch + (size_t)head * p.splits * (D + 2);
-  float m = -INFINITY;
-  for (int s = 0; s < p.splits; ++s) m = fmaxf(m, base[(size_t)s * (D + 2)]);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  // last CTA of this kv head merges the splits
+  int* counters = reinterpret_cast<int*>(p.scratch);
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int arrived = atomicAdd(counters + kvh, 1);
+    is_last = (arrived == p.splits - 1);
+    if (is_last) counters[kvh] = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int item = tid; item < G * D; item += DECODE_THREADS) {
+    const int h = item / D, d = item - h * D;
+    const int head = kvh * G + h;
+    const float* base = p.scratch + SCRATCH_HEADER_BYTES / 4 + (size_t)head * p.splits * (D + 2);
+    float m = -INFINITY;
+    for (int s2 = 0; s2 < p.splits; ++s2) m = fmaxf(m, __ldcg(base + (size_t)s2 * (D + 2)));
     float acc = 0.f, l = 0.f;
     if (m != -INFINITY) {
-      for (int s = 0; s < p.splits; ++s) {
-        const float* part = base + (size_t)s * (D + 2);
-        const float w = (part[0] == -INFINITY) ? 0.f : expf(part[0] - m);
-        acc = fmaf(w, part[2 + d], acc);
-        l = fmaf(w, part[1], l);
+      for (int s2 = 0; s2 < p.splits; ++s2) {
+        const float* part = base + (size_t)s2 * (D + 2);
+        const float pm = __ldcg(part);
+        const float w = (pm == -INFINITY) ? 0.f : expf(pm - m);
+        acc = fmaf(w, __ldcg(part + 2 + d), acc);
+        l = fmaf(w, __ldcg(part + 1), l);
       }
     }
     p.out[(size_t)head * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
@@ -216,11 +259,15 @@ attention_prefill_kernel(const AttnParams p) {
   }
 }
 
-static int decode_splits(const aoto_attention_args& a) {
-  // one split per 512 keys keeps every CTA's score buffer small and gives the
-  // long-context case enough CTAs to cover the machine
-  if (a.kv_len <= 1024) return 1;
-  return (a.kv_len + 511) / 512;
+// Keys per CTA and number of splits for the decode kernel. Short contexts are
+// latency bound: small tiles so that a handful of CTAs per kv head share the
+// window. Long contexts are bandwidth bound: enough CTAs to cover the machine,
+// tiles capped by shared memory.
+static void decode_tiling(const aoto_attention_args& a, int* keys_per_split, int* splits) {
+  int tile = a.head_dim <= 128 ? 64 : 32;
+  if (a.kv_len <= 32) tile = 32;
+  *keys_per_split = tile;
+  *splits = (a.kv_len + tile - 1) / tile;
 }
 
 }  // namespace aoto
@@ -228,10 +275,11 @@ static int decode_splits(const aoto_attention_args& a) {
 using namespace aoto;
 
 extern "C" int64_t aoto_sm100_attention_scratch_bytes(const aoto_attention_args* a) {
-  if (!a || a->q_len != 1) return 0;
-  const int splits = decode_splits(*a);
+  if (!a || a->q_len != 1 || a->kv_len <= 0 || a->head_dim <= 0) return 0;
+  int tile, splits;
+  decode_tiling(*a, &tile, &splits);
   if (splits == 1) return 0;
-  return (int64_t)a->query_heads * splits * (a->head_dim + 2) * 4;
+  return SCRATCH_HEADER_BYTES + (int64_t)a->query_heads * splits * (a->head_dim + 2) * 4;
 }
 
 extern "C" int aoto_sm100_attention(const aoto_attention_args* a, void* stream_) {
@@ -248,19 +296,31 @@ extern "C" int aoto_sm100_attention(const aoto_attention_args* a, void* stream_)
   p.QH = a->query_heads; p.KVH = a->kv_heads; p.Lq = a->q_len; p.Lk = a->kv_len; p.D = a->head_dim;
   p.causal = a->causal; p.scale = a->scale;
   if (a->q_len == 1) {
-    p.splits = decode_splits(*a);
-    p.keys_per_split = p.splits == 1 ? a->kv_len : 512;
+    if ((a->head_dim & 7) || !aligned_to(a->k, 16) || !aligned_to(a->v, 16)) return AOTO_ERR_UNSUPPORTED;
+    decode_tiling(*a, &p.keys_per_split, &p.splits);
     if (p.splits > 1) {
+      if (a->kv_heads > SCRATCH_MAX_COUNTERS) return AOTO_ERR_UNSUPPORTED;
       const int64_t need = aoto_sm100_attention_scratch_bytes(a);
-      if (!a->scratch || a->scratch_bytes < need) return AOTO_ERR_ARGUMENT;
+      if (!a->scratch || a->scratch_bytes < need || !aligned_to(a->scratch, 4)) return AOTO_ERR_ARGUMENT;
     }
-    const int tpr = a->head_dim / 2;
-    const int parts = DECODE_THREADS / tpr;
-    const size_t smem = ((size_t)a->head_dim + p.keys_per_split + 32 + (size_t)parts * a->head_dim) * 4;
-    int status = launch_kernel(attention_decode_kernel, dim3(a->query_heads, p.splits),
-                               dim3(DECODE_THREADS), smem, stream, false, p);
-    if (status != AOTO_OK || p.splits == 1) return status;
-    return launch_kernel(attention_combine_kernel, dim3(a->query_heads), dim3(128), 0, stream, false, p);
+    const int G = a->query_heads / a->kv_heads;
+    const size_t smem = (size_t)2 * p.keys_per_split * (a->head_dim * 2 + 16) +
+                        ((size_t)G * a->head_dim + (size_t)G * p.keys_per_split + (size_t)G * 2 +
+                         p.keys_per_split) * 4;
+    if (smem > 48 * 1024) {
+      static bool raised = false;
+      if (!raised) {
+        if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 160 * 1024) != cudaSuccess) {
+          (void)cudaGetLastError();
+          return AOTO_ERR_LAUNCH;
+        }
+        raised = true;
+      }
+      if (smem > 160 * 1024) return AOTO_ERR_UNSUPPORTED;
+    }
+    return launch_kernel(attention_decode_kernel, dim3(a->kv_heads, p.splits), dim3(DECODE_THREADS),
+                         smem, stream, false, p);
   }
   p.splits = 1;
   p.keys_per_split = 0;

@@ -75,6 +75,12 @@ __device__ __forceinline__ bool aligned_ptr16(const void* ptr) {
   return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0;
 }
 
+// Layout shared by every kernel that meets in scratch: arrival counters live in
+// the first SCRATCH_HEADER_BYTES (always zero between launches), payload after
+// them. A buffer can therefore be reused by different kernels and shapes.
+constexpr int SCRATCH_HEADER_BYTES = 4096;
+constexpr int SCRATCH_MAX_COUNTERS = SCRATCH_HEADER_BYTES / 4;
+
 inline int launch_status() {
   cudaError_t err = cudaGetLastError();
   return err == cudaSuccess ? AOTO_OK : AOTO_ERR_LAUNCH;

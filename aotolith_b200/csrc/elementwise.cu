@@ -129,46 +129,123 @@ mask_select_kernel(const uint8_t* __restrict__ mask, bf16* __restrict__ out, int
 }
 
 // --------------------------------------------------------------------------
-// argmax: one CTA per row, first maximum wins (torch / numpy tie rule); NaN is
-// treated as the maximum, as torch.argmax does.
+// argmax / greedy pick: the row is cut into parts, one CTA per part; every CTA
+// leaves its (value, index) in scratch and the last one to arrive picks the
+// winner - first maximum wins (torch / numpy tie rule), NaN ranks highest as in
+// torch.argmax - and, for the greedy pick, appends the token and advances the
+// loop counters. The arrival counter is left at zero for the next launch.
 // --------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024)
-argmax_kernel(const bf16* __restrict__ logits, int64_t* __restrict__ out, int width) {
-  __shared__ float best_v[32];
-  __shared__ int best_i[32];
+struct PickParams {
+  const bf16* logits;
+  int64_t* out;        // argmax: out[row]; greedy: token[0]
+  int64_t* generated;  // greedy only
+  int32_t* counters;   // greedy only
+  float* part_value;   // scratch: [rows][parts]
+  int* part_index;     // scratch: [rows][parts]
+  int* arrivals;       // scratch: [rows]
+  int width, parts, generated_capacity;
+};
+
+__device__ __forceinline__ void better(float& bv, int& bi, float ov, int oi) {
+  if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+}
+
+__device__ __forceinline__ void block_best(float& bv, int& bi, float* sv, int* si) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1)
+    better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, offset), __shfl_xor_sync(0xffffffffu, bi, offset));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  const int warps = blockDim.x >> 5;
+  bv = lane < warps ? sv[lane] : -INFINITY;
+  bi = lane < warps ? si[lane] : 0x7fffffff;
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1)
+    better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, offset), __shfl_xor_sync(0xffffffffu, bi, offset));
+}
+
+template <bool GREEDY>
+__global__ void __launch_bounds__(256)
+pick_kernel(const PickParams p) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ int is_last;
   pdl_wait_for_producers();
   pdl_release_dependents();
-  const bf16* row = logits + (size_t)blockIdx.x * width;
+  const int row = blockIdx.y, part = blockIdx.x;
+  const bf16* logits = p.logits + (size_t)row * p.width;
+  const int span = ((p.width + p.parts - 1) / p.parts + 7) & ~7;  // multiple of 8
+  const int begin = part * span, end = min(p.width, begin + span);
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  bool seen = false;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = __bfloat162float(row[i]);
-    if (v != v) v = INFINITY;  // NaN ranks highest
-    if (!seen || v > bv) { bv = v; bi = i; seen = true; }
-  }
-  // warp reduce (value desc, index asc)
-#pragma unroll
-  for (int offset = 16; offset > 0; offset >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
-    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-  }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
-  __syncthreads();
-  if (warp == 0) {
-    const int warps = blockDim.x >> 5;
-    bv = lane < warps ? best_v[lane] : -INFINITY;
-    bi = lane < warps ? best_i[lane] : 0x7fffffff;
-#pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  auto see = [&](float v, int i) {
+    if (v != v) v = INFINITY;
+    if (bi == 0x7fffffff || v > bv) { bv = v; bi = i; }
+  };
+  if (aligned_ptr16(logits)) {
+    for (int i = begin + threadIdx.x * 8; i < end; i += blockDim.x * 8) {
+      if (i + 8 <= end) {
+        const uint4 v = *reinterpret_cast<const uint4*>(logits + i);
+        see(bf16x2_lo(v.x), i); see(bf16x2_hi(v.x), i + 1); see(bf16x2_lo(v.y), i + 2); see(bf16x2_hi(v.y), i + 3);
+        see(bf16x2_lo(v.z), i + 4); see(bf16x2_hi(v.z), i + 5); see(bf16x2_lo(v.w), i + 6); see(bf16x2_hi(v.w), i + 7);
+      } else {
+        for (int j = i; j < end; ++j) see(__bfloat162float(logits[j]), j);
+      }
     }
-    if (lane == 0) out[blockIdx.x] = (int64_t)bi;
+  } else {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) see(__bfloat162float(logits[i]), i);
   }
+  block_best(bv, bi, sv, si);
+  if (p.parts > 1) {
+    if (threadIdx.x == 0) {
+      p.part_value[row * p.parts + part] = bv;
+      p.part_index[row * p.parts + part] = bi;
+      __threadfence();
+      const int arrived = atomicAdd(p.arrivals + row, 1);
+      is_last = arrived == p.parts - 1;
+      if (is_last) p.arrivals[row] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    bv = -INFINITY;
+    bi = 0x7fffffff;
+    for (int q = threadIdx.x; q < p.parts; q += blockDim.x)
+      better(bv, bi, __ldcg(p.part_value + row * p.parts + q), __ldcg(p.part_index + row * p.parts + q));
+    block_best(bv, bi, sv, si);
+  }
+  if (threadIdx.x == 0) {
+    p.out[GREEDY ? 0 : row] = (int64_t)bi;
+    if (GREEDY) {
+      const int step = p.counters[1];
+      if (step < p.generated_capacity) p.generated[step] = (int64_t)bi;
+      p.counters[0] += 1;
+      p.counters[1] = step + 1;
+    }
+  }
+}
+
+static int pick_parts(int rows, int width) {
+  if (width < 8192 || rows > SCRATCH_MAX_COUNTERS) return 1;
+  int parts = (width + 2047) / 2048;
+  return parts > 64 ? 64 : parts;
+}
+
+static int launch_pick(bool greedy, PickParams p, int rows, void* scratch, int64_t scratch_bytes,
+                       cudaStream_t stream) {
+  p.parts = pick_parts(rows, p.width);
+  if (p.parts > 1) {
+    const int64_t need = SCRATCH_HEADER_BYTES + (int64_t)rows * p.parts * 8;
+    if (!scratch || scratch_bytes < need || !aligned_to(scratch, 4)) return AOTO_ERR_ARGUMENT;
+    p.arrivals = reinterpret_cast<int*>(scratch);
+    p.part_value = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + SCRATCH_HEADER_BYTES);
+    p.part_index = reinterpret_cast<int*>(p.part_value + (size_t)rows * p.parts);
+  }
+  const dim3 grid(p.parts, rows), block(256);
+  if (greedy) return launch_kernel(pick_kernel<true>, grid, block, 0, stream, false, p);
+  return launch_kernel(pick_kernel<false>, grid, block, 0, stream, false, p);
 }
 
 // --------------------------------------------------------------------------
@@ -185,51 +262,6 @@ step_inputs_kernel(const int32_t* __restrict__ counters, int64_t* __restrict__ p
   if (idx < capacity) mask[idx] = idx >= capacity - valid ? 1 : 0;
 }
 
-__global__ void __launch_bounds__(1024)
-greedy_pick_kernel(const bf16* __restrict__ logits, int64_t* __restrict__ token,
-                   int64_t* __restrict__ generated, int32_t* __restrict__ counters, int width,
-                   int generated_capacity) {
-  __shared__ float best_v[32];
-  __shared__ int best_i[32];
-  pdl_wait_for_producers();
-  pdl_release_dependents();
-  float bv = -INFINITY;
-  int bi = 0x7fffffff;
-  bool seen = false;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = __bfloat162float(logits[i]);
-    if (v != v) v = INFINITY;
-    if (!seen || v > bv) { bv = v; bi = i; seen = true; }
-  }
-#pragma unroll
-  for (int offset = 16; offset > 0; offset >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
-    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-  }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
-  __syncthreads();
-  if (warp == 0) {
-    const int warps = blockDim.x >> 5;
-    bv = lane < warps ? best_v[lane] : -INFINITY;
-    bi = lane < warps ? best_i[lane] : 0x7fffffff;
-#pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
-    if (lane == 0) {
-      token[0] = (int64_t)bi;
-      const int step = counters[1];
-      if (step < generated_capacity) generated[step] = (int64_t)bi;
-      counters[0] += 1;
-      counters[1] = step + 1;
-    }
-  }
-}
-
 }  // namespace aoto
 
 using namespace aoto;
@@ -244,9 +276,14 @@ extern "C" int aoto_sm100_greedy_pick(const aoto_greedy_pick_args* a, void* stre
   if (!a || !a->logits || !a->token || !a->generated || !a->counters || a->width <= 0 ||
       a->generated_capacity <= 0)
     return AOTO_ERR_ARGUMENT;
-  return launch_kernel(greedy_pick_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, false,
-                       (const bf16*)a->logits, a->token, a->generated, a->counters, (int)a->width,
-                       (int)a->generated_capacity);
+  PickParams p = {};
+  p.logits = (const bf16*)a->logits;
+  p.out = a->token;
+  p.generated = a->generated;
+  p.counters = a->counters;
+  p.width = a->width;
+  p.generated_capacity = a->generated_capacity;
+  return launch_pick(true, p, 1, a->scratch, a->scratch_bytes, (cudaStream_t)stream);
 }
 
 extern "C" int aoto_sm100_dequantize_i4(const aoto_dequantize_args* a, void* stream) {
@@ -300,8 +337,17 @@ extern "C" int aoto_sm100_mask_select(const aoto_mask_select_args* a, void* stre
   return launch_status();
 }
 
+extern "C" int64_t aoto_sm100_argmax_scratch_bytes(int32_t rows, int32_t width) {
+  if (rows <= 0 || width <= 0) return 0;
+  const int parts = pick_parts(rows, width);
+  return parts > 1 ? SCRATCH_HEADER_BYTES + (int64_t)rows * parts * 8 : 0;
+}
+
 extern "C" int aoto_sm100_argmax(const aoto_argmax_args* a, void* stream) {
   if (!a || !a->logits || !a->out || a->rows <= 0 || a->width <= 0) return AOTO_ERR_ARGUMENT;
-  return launch_kernel(argmax_kernel, dim3(a->rows), dim3(1024), 0, (cudaStream_t)stream, false,
-                       (const bf16*)a->logits, a->out, (int)a->width);
+  PickParams p = {};
+  p.logits = (const bf16*)a->logits;
+  p.out = a->out;
+  p.width = a->width;
+  return launch_pick(false, p, a->rows, a->scratch, a->scratch_bytes, (cudaStream_t)stream);
 }

@@ -43,6 +43,27 @@ def _bf16(tensor: torch.Tensor | None, name: str) -> None:
         raise PlanInputError(f"{name} must be bfloat16 on this target, got {tensor.dtype}")
 
 
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """A zero-initialised scratch buffer for the current stream of ``device``.
+
+    Kernels that use it restore the parts that must start at zero (arrival
+    counters), so it is cleared only when it is created or has to grow. One
+    buffer per (device, stream): launches on one stream are ordered, launches
+    on different streams never share scratch.
+    """
+
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    buffer = _WORKSPACES.get(key)
+    if buffer is None or buffer.numel() < nbytes:
+        buffer = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = buffer
+    return buffer
+
+
 def _dense(tensor: torch.Tensor | None) -> torch.Tensor | None:
     if tensor is None or tensor.is_contiguous():
         return tensor
@@ -231,8 +252,11 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     rows = logits.numel() // width
     if out is None:
         out = torch.empty(logits.shape[:-1], dtype=torch.int64, device=logits.device)
-    args = N.ArgmaxArgs(_ptr(logits), _ptr(out), rows, width)
-    N.check(N.load().aoto_sm100_argmax(ctypes.byref(args), _stream()), "aoto_sm100_argmax")
+    lib = N.load()
+    need = lib.aoto_sm100_argmax_scratch_bytes(rows, width)
+    scratch = workspace(logits.device, need) if need else None
+    args = N.ArgmaxArgs(_ptr(logits), _ptr(out), _ptr(scratch), scratch.numel() if need else 0, rows, width)
+    N.check(lib.aoto_sm100_argmax(ctypes.byref(args), _stream()), "aoto_sm100_argmax")
     return out
 
 
@@ -322,10 +346,9 @@ def attention(
     args.scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
     lib = N.load()
     need = lib.aoto_sm100_attention_scratch_bytes(ctypes.byref(args))
-    scratch = None
     if need:
-        scratch = torch.empty(need, dtype=torch.uint8, device=query.device)
-        args.scratch, args.scratch_bytes = _ptr(scratch), need
+        scratch = workspace(query.device, need)
+        args.scratch, args.scratch_bytes = _ptr(scratch), scratch.numel()
     N.check(lib.aoto_sm100_attention(ctypes.byref(args), _stream()), "aoto_sm100_attention")
     return out
 
@@ -348,6 +371,10 @@ def greedy_pick(logits: torch.Tensor, token: torch.Tensor, generated: torch.Tens
     if token.dtype != torch.int64 or generated.dtype != torch.int64 or counters.dtype != torch.int32:
         raise PlanInputError("greedy_pick expects int64 token/generated buffers and int32 counters")
     logits = _dense(logits)
+    lib = N.load()
+    need = lib.aoto_sm100_argmax_scratch_bytes(1, logits.numel())
+    scratch = workspace(logits.device, need) if need else None
     args = N.GreedyPickArgs(_ptr(logits), _ptr(token), _ptr(generated), _ptr(counters),
+                            _ptr(scratch), scratch.numel() if need else 0,
                             logits.numel(), generated.numel())
-    N.check(N.load().aoto_sm100_greedy_pick(ctypes.byref(args), _stream()), "aoto_sm100_greedy_pick")
+    N.check(lib.aoto_sm100_greedy_pick(ctypes.byref(args), _stream()), "aoto_sm100_greedy_pick")

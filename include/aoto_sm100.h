@@ -196,9 +196,14 @@ int aoto_sm100_mask_select(const aoto_mask_select_args* args, void* stream);
 typedef struct aoto_argmax_args {
   const void* logits; /* [rows, width] bf16 */
   int64_t* out;       /* [rows] */
+  void* scratch;      /* aoto_sm100_argmax_scratch_bytes(rows, width) bytes, or NULL when 0 */
+  int64_t scratch_bytes;
   int32_t rows, width;
 } aoto_argmax_args;
 int aoto_sm100_argmax(const aoto_argmax_args* args, void* stream);
+/* Wide rows are scanned by several CTAs that meet in scratch (same zero-before-first-use,
+ * self-restoring contract as the attention scratch). 0 for narrow rows. */
+int64_t aoto_sm100_argmax_scratch_bytes(int32_t rows, int32_t width);
 
 /* ------------------------------------------------------------------------- */
 /* Device-resident greedy loop                                               */
@@ -233,6 +238,8 @@ typedef struct aoto_greedy_pick_args {
   int64_t* token;     /* [1] */
   int64_t* generated; /* [generated_capacity] */
   int32_t* counters;
+  void* scratch;      /* aoto_sm100_argmax_scratch_bytes(1, width) bytes */
+  int64_t scratch_bytes;
   int32_t width, generated_capacity;
 } aoto_greedy_pick_args;
 int aoto_sm100_greedy_pick(const aoto_greedy_pick_args* args, void* stream);
@@ -281,6 +288,13 @@ int aoto_sm100_kv_cache_append(const aoto_kv_append_args* args, void* stream);
  * bf16 [Lq,Lk] (0 / -inf) or NULL, `causal` adds the top-left aligned causal
  * rule. out [1,QH,Lq,D]. Lq == 1 selects the split-KV decode kernel, which
  * needs `scratch` of aoto_sm100_attention_scratch_bytes() when it splits.
+ *
+ * Scratch contract (the same for every entry point that takes `scratch`): the
+ * first 4096 bytes hold arrival counters and must be zero before the FIRST use;
+ * every launch leaves them at zero again, and the rest is payload that needs no
+ * initialisation. One buffer can therefore serve different kernels and shapes
+ * without clearing, as long as the launches that share it are ordered on one
+ * stream (two launches that overlap on the device must not share it).
  *
  * Replaces: `attention`, runtime/mlx_ops/attention.py:52-85,
  * codegen/attention.py:447-657 (decode) and :68-422 (prefill),

@@ -330,3 +330,38 @@ def test_attention_prefill(cuda, QH, KVH, P, D, length):
     if length == P:
         causal = ops.attention(q.to(cuda), k.to(cuda), v.to(cuda), None, scale=D ** -0.5, causal=True).cpu()
         assert rel_max_error(causal, want) < ORACLE_TOL
+
+
+def test_scratch_is_shared_between_kernels_and_shapes(cuda):
+    """Attention splits of different shapes and wide argmax reuse one per-stream scratch buffer."""
+
+    ops = _ops()
+    logits = activations(130, 1, 151936)
+    for C in (1280, 192, 700):
+        q = activations(131, 1, 14, 1, 64)
+        k = activations(132, 1, 2, C, 64)
+        v = activations(133, 1, 2, C, 64)
+        want = ref.attention(q, k, v, None, scale=0.125)
+        got = ops.attention(q.to(cuda), k.to(cuda), v.to(cuda), None, scale=0.125).cpu()
+        assert rel_max_error(got, want) < ORACLE_TOL
+        assert ops.argmax(logits.to(cuda)).cpu().tolist() == [int(logits.float().argmax())]
+
+
+def test_greedy_pick_and_step_inputs(cuda):
+    ops = _ops()
+    counters = torch.tensor([130, 0], dtype=torch.int32, device=cuda)
+    position = torch.zeros((1, 1), dtype=torch.int64, device=cuda)
+    mask = torch.zeros((1, 1, 1, 192), dtype=torch.bool, device=cuda)
+    token = torch.zeros((1, 1), dtype=torch.int64, device=cuda)
+    generated = torch.full((8,), -1, dtype=torch.int64, device=cuda)
+    picks = []
+    for step in range(3):
+        ops.step_inputs(counters, position, mask)
+        assert int(position.item()) == 129 + step
+        assert mask.reshape(-1).cpu().tolist() == [False] * (192 - 130 - step) + [True] * (130 + step)
+        logits = activations(140 + step, 151936)
+        picks.append(int(logits.float().argmax()))
+        ops.greedy_pick(logits.to(cuda), token, generated, counters)
+        assert int(token.item()) == picks[-1]
+    assert generated.cpu().tolist()[:3] == picks and int(generated[3]) == -1
+    assert counters.cpu().tolist() == [133, 3]
