@@ -34,6 +34,7 @@ from ..errors import CompilationError, UnsupportedDTypeError, UnsupportedOperati
 from ..ir import DType, Graph, Operation
 from ..planning import plan_storage
 from ..runtime.plan import TORCH_DTYPES, CompiledPlan, KernelArtifact, current_context
+from ..runtime.step_program import build_step_program
 from ..selection import COPY, CUDA_KERNEL, VIEW, KernelSelection
 
 TARGET = "cuda-sm100"
@@ -485,4 +486,5 @@ class CudaBackend:
             _callables=builder.callables,
             storage_plan=plan_storage(graph),
             device=device,
+            step_program=build_step_program(graph),
         )

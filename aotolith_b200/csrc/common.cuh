@@ -37,6 +37,14 @@ __device__ __forceinline__ uint4 ldg_nc_u4(const void* ptr) {
   return v;
 }
 
+// 16-bit load that bypasses L1 (L1 is not coherent across SMs: values another CTA
+// wrote during the same kernel must come from L2).
+__device__ __forceinline__ float ldcg_bf16(const __nv_bfloat16* ptr) {
+  unsigned short raw;
+  asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(raw) : "l"(ptr));
+  return __uint_as_float(((uint32_t)raw) << 16);
+}
+
 // Programmatic dependent launch. Both are no-ops when the kernel was launched
 // without the programmatic-serialization attribute.
 __device__ __forceinline__ void pdl_wait_for_producers() {

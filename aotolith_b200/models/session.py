@@ -1,19 +1,21 @@
-"""Device-resident greedy decoding: one recorded CUDA graph per decode step.
+"""Device-resident greedy decoding: the host's share of a decode step is one launch.
 
 The reference's greedy loop hands every step to MLX's asynchronous executor and
 synchronises once at the end (``src/aotolith/models/decoder.py:1054-1087``).
-The CUDA counterpart records a whole step - the inputs of the step, the decode
-plan's kernels, the greedy pick - into a graph, so the host's share of a step is
-one graph launch:
+Here a whole step - the step's inputs, the decode plan, the greedy pick - runs on
+the device without a host round trip:
 
-    step_inputs   position = valid_length - 1, mask = window of valid_length slots
+    step inputs   position = valid_length - 1, mask = window of valid_length slots
     decode plan   embedding ... projections ... logits, next cache
-    greedy_pick   token = argmax(logits); generated[n] = token; counters += 1
+    greedy pick   token = argmax(logits); generated[n] = token; counters += 1
 
-Two graphs are recorded over two cache buffers (A -> B, B -> A): the decode
-plan writes each layer's shifted window straight into the other buffer, so a
-step moves every window once and nothing is copied between steps. Tokens stay
-on the device until the caller reads the result.
+When the decode graph has the form of a stage program
+(:mod:`aotolith_b200.runtime.step_program`) the step is ONE launch of the
+persistent ``aoto_sm100_decode_step`` kernel; otherwise the per-operation plan is
+recorded into a CUDA graph and replayed. Either way two variants exist over two
+cache buffers (A -> B, B -> A): each layer's shifted window is written straight
+into the other buffer, so a step moves every window once and nothing is copied
+between steps. Tokens stay on the device until the caller reads the result.
 """
 
 from __future__ import annotations
@@ -21,10 +23,12 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..errors import PlanInputError
+from ..errors import DeviceError, PlanInputError
 
 
 class DecodeSession:
+    """Static buffers plus either the persistent step kernel or two recorded graphs."""
+
     def __init__(self, runtime) -> None:
         self.runtime = runtime
         module_plan = runtime.decode
@@ -47,8 +51,69 @@ class DecodeSession:
         self.generated = torch.zeros(max(runtime.max_new_tokens, 1), dtype=torch.int64, device=device)
         self.state = list(module_plan._state_values)
         self.graphs: list[torch.cuda.CUDAGraph] = []
-        self._record()
+        self.programs: list[torch.Tensor] = []
+        self.mode = "graphs"
+        if self.plan.step_program is not None and self._bind_program():
+            self.mode = "kernel"
+        else:
+            self._record()
 
+    # -- persistent kernel ---------------------------------------------------------
+    def _bind_program(self) -> bool:
+        """Resolve the stage program against this session's buffers; False if it does not fit."""
+
+        from ..runtime import step_program as sp
+
+        program = self.plan.step_program
+        graph = self.plan.graph
+        device = self.device
+        tensors = dict(zip(graph.inputs[4:], self.state))
+        tensors[program.token_input] = self.token
+        tensors[program.position_input] = self.position
+        tensors[program.mask_input] = self.mask
+        self.arena = torch.zeros(program.arena_bytes, dtype=torch.uint8, device=device)
+        self.logits = torch.zeros((1, 1, program.vocab), dtype=torch.bfloat16, device=device)
+        greedy = dict(
+            token=self.token.data_ptr(), generated=self.generated.data_ptr(),
+            counters=self.counters.data_ptr(), position=self.position.data_ptr(),
+            mask=self.mask.data_ptr(), generated_capacity=self.generated.numel(),
+        )
+        arrays = []
+        for source in (0, 1):
+            def resolve(ref, _source=source):
+                if ref.space == "arena":
+                    return self.arena.data_ptr() + program.arena_offsets[ref.key] + ref.offset
+                if ref.space == "output":
+                    base = self.logits if ref.key == 0 else self.caches[1 - _source]
+                    return base.data_ptr() + ref.offset
+                if ref.key == program.cache_input:
+                    return self.caches[_source].data_ptr() + ref.offset
+                return tensors[ref.key].data_ptr() + ref.offset
+
+            arrays.append(sp.stage_array(program, resolve, greedy=greedy))
+        if not sp.supported(arrays[0]):
+            return False
+        self.stage_count = len(arrays[0])
+        self.programs = [sp.to_device(array, device) for array in arrays]
+        self.sync_words = torch.zeros(2, dtype=torch.int64, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.scratch = torch.zeros(max(sp.scratch_bytes(arrays[0]), 1 << 16), dtype=torch.uint8, device=device)
+        self._launch = sp.launch
+        return True
+
+    def _check_status(self) -> None:
+        stage = int(self.status.item())
+        if stage:
+            self.status.zero_()
+            self.sync_words.zero_()
+            self.scratch.zero_()
+            raise DeviceError(
+                f"the decode-step kernel gave up waiting at its grid barrier before stage {stage}",
+                hint="the device could not keep every CTA of the cooperative launch resident, or a "
+                "previous launch left the barrier words in an inconsistent state; they were reset",
+            )
+
+    # -- recorded graphs (the per-operation plan, two cache directions) ---------------
     def _step(self, source: int) -> None:
         ops.step_inputs(self.counters, self.position, self.mask)
         target = self.caches[1 - source]
@@ -73,7 +138,7 @@ class DecodeSession:
         pool = None
         for source in (0, 1):
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, pool=pool):
+            with torch.cuda.graph(graph, pool=pool, stream=side):
                 self._step(source)
             pool = graph.pool()
             self.graphs.append(graph)
@@ -94,6 +159,12 @@ class DecodeSession:
         self.counters.copy_(
             torch.tensor([valid_length + 1, 0], dtype=torch.int32).pin_memory(), non_blocking=True
         )
+        if self.mode == "kernel":
+            for step in range(steps):
+                self._launch(self.programs[step & 1], self.stage_count, self.sync_words, self.status, self.scratch)
+            tokens = self.generated[:steps].clone()
+            self._check_status()
+            return tokens
         for step in range(steps):
             self.graphs[step & 1].replay()
         return self.generated[:steps].clone()

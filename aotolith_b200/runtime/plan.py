@@ -111,6 +111,8 @@ class CompiledPlan:
     device: Any = None
     #: leading inputs that change between calls; the rest (bound state) are used in place
     dynamic_inputs: int | None = None
+    #: the graph as a stage program of the persistent decode-step kernel, when it has that form
+    step_program: Any = None
     _program: list | None = field(default=None, repr=False)
     _slots: dict[str, int] | None = field(default=None, repr=False)
     _lock: threading.Lock = field(default_factory=threading.Lock, repr=False)

@@ -315,6 +315,87 @@ typedef struct aoto_attention_args {
 int aoto_sm100_attention(const aoto_attention_args* args, void* stream);
 int64_t aoto_sm100_attention_scratch_bytes(const aoto_attention_args* args);
 
+/* ------------------------------------------------------------------------- */
+/* A whole decode step as one persistent kernel                              */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * A decode step of the lowered graph is a chain of ~120 tiny operations, each
+ * depending on the previous one; launched one by one, launch latency and the
+ * cold start of every kernel dominate the step. aoto_sm100_decode_step runs the
+ * whole chain in ONE cooperative launch: the caller describes the step as a
+ * program of stages (below), every CTA of the grid walks the program, and the
+ * stages are separated by a grid-wide barrier (bounded: a wait that runs out
+ * stores 1 + the stage index in `status` and the kernel returns). Weights of
+ * the next projection are requested before the barrier is waited for, so the
+ * HBM stream does not stop at stage boundaries.
+ *
+ * The program is what the reference's unrolled plan runner executes operation
+ * by operation (runtime/plan.py:554-733) for the decode graph of
+ * models/decoder.py:565-615; each stage kind covers the operations named in its
+ * comment. All pointers in a stage are device pointers; `stages` itself is a
+ * device array.
+ */
+#define AOTO_STAGE_GEMV 1      /* packed matmul / addmm, M = 1 (+ embedding gather of its input) */
+#define AOTO_STAGE_ATTENTION 2 /* rope_kv_cache_append + mask conversion + attention of one layer */
+#define AOTO_STAGE_PICK 3      /* greedy token from the per-CTA maxima of the preceding GEMV       */
+
+#define AOTO_STAGE_FLAG_STEP_INPUTS 1  /* GEMV: one CTA also writes position/mask from counters    */
+#define AOTO_STAGE_FLAG_ARGMAX 2       /* GEMV: every CTA leaves its (max, index) in scratch       */
+
+typedef struct aoto_step_stage {
+  /* GEMV */
+  const void* x;             /* [K] bf16; with x_index: table [x_rows, K] and x = table[x_index[0]] */
+  const int64_t* x_index;
+  void* x_copy;              /* optional [K]: receives the (gathered) input row                     */
+  const void* packed;
+  const void* scales;
+  const void* packed2;
+  const void* scales2;
+  const void* addend;
+  const void* norm_weight;
+  void* out;                 /* [N] bf16 */
+  /* ATTENTION */
+  const void* row;           /* packed q/k/v projection of the step, [(QH+2*KVH)*D]               */
+  const void* cos_table;     /* [table_rows, D]; the row used is position[0]                        */
+  const void* sin_table;
+  const int64_t* position;
+  const void* cache_in;      /* this layer's pair [2,1,KVH,C,D] in the incoming cache              */
+  void* cache_out;           /* this layer's pair in the next cache                                 */
+  const uint8_t* mask;       /* bool [C]: true = attend                                            */
+  void* attn_out;            /* [QH*D] */
+  /* PICK and STEP_INPUTS */
+  int64_t* token;            /* [1] */
+  int64_t* generated;
+  int32_t* counters;         /* int32[2]: valid_length, tokens generated                            */
+  int64_t* position_out;     /* STEP_INPUTS: [1]                                                    */
+  uint8_t* mask_out;         /* STEP_INPUTS: bool [capacity]                                        */
+  int64_t x_rows;
+  int32_t kind, flags;
+  int32_t N, K, group_size, addend_kind, epilogue;
+  int32_t query_heads, kv_heads, capacity, head_dim;
+  int32_t query_start, key_start, value_start, table_rows;
+  int32_t generated_capacity, reserved;
+  float alpha, beta, rms_norm_eps, scale;
+} aoto_step_stage;
+
+typedef struct aoto_decode_step_args {
+  const aoto_step_stage* stages; /* device array */
+  int32_t stage_count;
+  int32_t ctas;                  /* 0 = one per SM */
+  uint64_t* sync_words;          /* device, uint64[2], zero before first use: barrier count, epoch */
+  int32_t* status;               /* device int32, zero = no error                                   */
+  void* scratch;                 /* same contract as the other entry points                         */
+  int64_t scratch_bytes;
+} aoto_decode_step_args;
+
+int aoto_sm100_decode_step(const aoto_decode_step_args* args, void* stream);
+/* Scratch bytes a program needs (host copy of the stages). */
+int64_t aoto_sm100_decode_step_scratch_bytes(const aoto_step_stage* host_stages, int32_t stage_count);
+/* 1 if every stage of the host copy is within the kernel's limits, else 0. */
+int aoto_sm100_decode_step_supported(const aoto_step_stage* host_stages, int32_t stage_count);
+int aoto_sm100_decode_step_stage_size(void); /* sizeof(aoto_step_stage), for binding checks */
+
 #ifdef __cplusplus
 }
 #endif

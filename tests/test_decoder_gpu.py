@@ -176,3 +176,44 @@ def test_qwen_shaped_layers_match_oracle(cuda):
     footprint = runtime.memory_footprint()
     assert footprint.cache_bytes == 2 * 2 * 2 * 20 * 64 * 2
     assert footprint.step_peak_bytes > footprint.weights_bytes
+
+
+def test_step_kernel_matches_per_operation_plan(cuda):
+    """The persistent decode-step kernel and the per-operation plan agree token for token.
+
+    Same weights, same prompt: one session runs the stage program in a single
+    cooperative launch per token, the other replays the recorded per-operation
+    graph. Logits of the last step and the final caches must agree to bf16
+    rounding; tokens must be identical.
+    """
+
+    from aotolith_b200.models.session import DecodeSession
+
+    model = qwen25_05b_shaped(seed=6, layers=3)
+    runtime = aoto.compile_qwen2_static_cache(model, prompt_length=24, max_new_tokens=9, quantize=64)
+    assert runtime.decode.plan.step_program is not None
+    prompt = torch.randint(0, 151936, (1, 24), generator=torch.Generator().manual_seed(10))
+    logits, compact = runtime.prefill_ids(prompt)
+    cache = runtime.pad_cache(compact)
+    from aotolith_b200 import ops
+
+    token = ops.argmax(logits[:, -1, :]).reshape(1, 1)
+    kernel = DecodeSession(runtime)
+    assert kernel.mode == "kernel"
+    program = runtime.decode.plan.step_program
+    runtime.decode.plan.step_program = None
+    try:
+        graphs = DecodeSession(runtime)
+    finally:
+        runtime.decode.plan.step_program = program
+    assert graphs.mode == "graphs"
+    for steps in (1, 8):
+        a = kernel.run(token, cache, 24, steps).cpu()
+        b = graphs.run(token, cache, 24, steps).cpu()
+        assert a.tolist() == b.tolist()
+        assert rel_err(kernel.final_cache(steps), graphs.final_cache(steps)) < REL_TOL
+    # and against the oracle
+    want, trace, _ = OracleRuntime(runtime).greedy(prompt, 9)
+    got = runtime.greedy_generate(prompt).cpu()[0].tolist()
+    assert got == want, f"oracle top-2 gaps: {[top2_gap(t) for t in trace]}"
+    assert rel_err(kernel.logits, trace[-1]) < REL_TOL
