@@ -123,16 +123,15 @@ class StepStage(Structure):
     """Mirror of ``aoto_step_stage`` (field order and types must match the header)."""
 
     _fields_ = [
-        ("x", c_void_p), ("x_index", c_void_p), ("x_copy", c_void_p),
+        ("x", c_void_p), ("x_index", c_void_p),
         ("packed", c_void_p), ("scales", c_void_p), ("packed2", c_void_p), ("scales2", c_void_p),
         ("addend", c_void_p), ("norm_weight", c_void_p), ("out", c_void_p),
         ("row", c_void_p), ("cos_table", c_void_p), ("sin_table", c_void_p), ("position", c_void_p),
         ("cache_in", c_void_p), ("cache_out", c_void_p), ("mask", c_void_p), ("attn_out", c_void_p),
         ("token", c_void_p), ("generated", c_void_p), ("counters", c_void_p),
-        ("position_out", c_void_p), ("mask_out", c_void_p),
         ("x_rows", c_int64),
         ("kind", c_int32), ("flags", c_int32),
-        ("N", c_int32), ("K", c_int32), ("group_size", c_int32), ("addend_kind", c_int32), ("epilogue", c_int32),
+        ("N", c_int32), ("K", c_int32), ("group_size", c_int32), ("addend_mode", c_int32), ("epilogue", c_int32),
         ("query_heads", c_int32), ("kv_heads", c_int32), ("capacity", c_int32), ("head_dim", c_int32),
         ("query_start", c_int32), ("key_start", c_int32), ("value_start", c_int32), ("table_rows", c_int32),
         ("generated_capacity", c_int32), ("reserved", c_int32),
@@ -143,12 +142,15 @@ class StepStage(Structure):
 class DecodeStepArgs(Structure):
     _fields_ = [
         ("stages", c_void_p), ("stage_count", c_int32), ("ctas", c_int32),
-        ("sync_words", c_void_p), ("status", c_void_p), ("scratch", c_void_p), ("scratch_bytes", c_int64),
+        ("epoch", ctypes.c_uint32), ("reserved", c_int32),
+        ("status", c_void_p), ("scratch", c_void_p), ("scratch_bytes", c_int64),
+        ("trace", c_void_p),
     ]
 
 
 STAGE_GEMV, STAGE_ATTENTION, STAGE_PICK = 1, 2, 3
-STAGE_FLAG_STEP_INPUTS, STAGE_FLAG_ARGMAX = 1, 2
+STAGE_FLAG_ARGMAX, STAGE_FLAG_WINDOW, STAGE_FLAG_OUT_PLAIN, STAGE_FLAG_X_GATHER = 2, 4, 8, 16
+STAGE_ADDEND_NONE, STAGE_ADDEND_PLAIN, STAGE_ADDEND_STAMPED, STAGE_ADDEND_GATHER = 0, 1, 2, 3
 
 
 #: symbol -> (restype, argtypes); one entry per declaration in include/aoto_sm100.h
@@ -173,6 +175,7 @@ EXPORTS: dict[str, tuple] = {
     "aoto_sm100_decode_step_scratch_bytes": (c_int64, [POINTER(StepStage), c_int32]),
     "aoto_sm100_decode_step_supported": (c_int, [POINTER(StepStage), c_int32]),
     "aoto_sm100_decode_step_stage_size": (c_int, []),
+    "aoto_sm100_stamped_bytes": (c_int64, [c_int64]),
     "aoto_sm100_kv_cache_append": (c_int, [POINTER(KvAppendArgs), c_void_p]),
     "aoto_sm100_attention": (c_int, [POINTER(AttentionArgs), c_void_p]),
     "aoto_sm100_attention_scratch_bytes": (c_int64, [POINTER(AttentionArgs)]),

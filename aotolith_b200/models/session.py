@@ -75,8 +75,7 @@ class DecodeSession:
         self.logits = torch.zeros((1, 1, program.vocab), dtype=torch.bfloat16, device=device)
         greedy = dict(
             token=self.token.data_ptr(), generated=self.generated.data_ptr(),
-            counters=self.counters.data_ptr(), position=self.position.data_ptr(),
-            mask=self.mask.data_ptr(), generated_capacity=self.generated.numel(),
+            counters=self.counters.data_ptr(), generated_capacity=self.generated.numel(),
         )
         arrays = []
         for source in (0, 1):
@@ -95,7 +94,7 @@ class DecodeSession:
             return False
         self.stage_count = len(arrays[0])
         self.programs = [sp.to_device(array, device) for array in arrays]
-        self.sync_words = torch.zeros(2, dtype=torch.int64, device=device)
+        self.epoch = 0
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.scratch = torch.zeros(max(sp.scratch_bytes(arrays[0]), 1 << 16), dtype=torch.uint8, device=device)
         self._launch = sp.launch
@@ -105,12 +104,12 @@ class DecodeSession:
         stage = int(self.status.item())
         if stage:
             self.status.zero_()
-            self.sync_words.zero_()
             self.scratch.zero_()
+            self.arena.zero_()
             raise DeviceError(
-                f"the decode-step kernel gave up waiting at its grid barrier before stage {stage}",
-                hint="the device could not keep every CTA of the cooperative launch resident, or a "
-                "previous launch left the barrier words in an inconsistent state; they were reset",
+                f"the decode-step kernel gave up polling for the inputs of stage {stage - 1}",
+                hint="the device could not keep every CTA of the cooperative launch resident; the "
+                "arena and scratch were cleared and the session can be used again",
             )
 
     # -- recorded graphs (the per-operation plan, two cache directions) ---------------
@@ -161,7 +160,8 @@ class DecodeSession:
         )
         if self.mode == "kernel":
             for step in range(steps):
-                self._launch(self.programs[step & 1], self.stage_count, self.sync_words, self.status, self.scratch)
+                self.epoch = self.epoch % 0xFFFFFFFE + 1
+                self._launch(self.programs[step & 1], self.stage_count, self.epoch, self.status, self.scratch)
             tokens = self.generated[:steps].clone()
             self._check_status()
             return tokens

@@ -119,7 +119,8 @@ def _build(graph: Graph) -> StepProgram:
         nonlocal arena_top
         if value_id not in offsets:
             offsets[value_id] = arena_top
-            arena_top += (value(value_id).type.nbytes + 255) // 256 * 256
+            # a stamped vector: 8 bytes per two bf16 values
+            arena_top += (value(value_id).type.numel * 4 + 255) // 256 * 256
         return Ref("arena", value_id, 0)
 
     stages: list[StageSpec] = []
@@ -127,7 +128,6 @@ def _build(graph: Graph) -> StepProgram:
     appended: dict[str, dict] = {}   # keys value id -> pending attention description
     pairs: dict[str, int] = {}       # new_pair value id -> layer
     cache_output = None
-    gather_copies: dict[str, Ref] = {}
 
     for index, op in enumerate(graph.ops):
         kind = op.op
@@ -178,12 +178,8 @@ def _build(graph: Graph) -> StepProgram:
                 spec.refs["x"] = Ref("input", table)
                 spec.refs["x_index"] = Ref("input", ids)
                 spec.ints["x_rows"] = value(table).type.shape[0]
+                spec.flags |= N.STAGE_FLAG_X_GATHER
                 token_input = ids
-                # the gathered row is needed again (the residual): materialise it once
-                producer = next(o for o in graph.ops if o.op == "embedding" and env.get(o.outputs[0]) == source)
-                copy = place(producer.outputs[0])
-                spec.refs["x_copy"] = copy
-                gather_copies[producer.outputs[0]] = copy
             else:
                 spec.refs["x"] = tensor_ref(x_id)
             spec.refs["packed"] = tensor_ref(op.inputs[base + 1])
@@ -204,7 +200,7 @@ def _build(graph: Graph) -> StepProgram:
             n_rows, words = value(op.inputs[base + 1]).type.shape
             if words * 8 != x_shape[-1]:
                 raise _Unsupported
-            addend_kind = N.ADDEND_NONE
+            addend_mode = N.STAGE_ADDEND_NONE
             if is_addmm:
                 addend_id = op.inputs[0]
                 if _numel(value(addend_id).type.shape) != n_rows:
@@ -213,17 +209,26 @@ def _build(graph: Graph) -> StepProgram:
                 if source is None:
                     raise _Unsupported
                 if source[0] == "gather":
-                    producer = next(o for o in graph.ops if o.op == "embedding" and env.get(o.outputs[0]) == source)
-                    copy = gather_copies.get(producer.outputs[0])
-                    if copy is None:
+                    # the residual of the first layer is the embedding row itself
+                    _, table, ids, _ = source
+                    if value(table).type.shape[1] != n_rows:
                         raise _Unsupported
-                    spec.refs["addend"] = copy
+                    spec.refs["addend"] = Ref("input", table)
+                    spec.refs.setdefault("x_index", Ref("input", ids))
+                    spec.ints.setdefault("x_rows", value(table).type.shape[0])
+                    if spec.refs["x_index"] != Ref("input", ids):
+                        raise _Unsupported
+                    addend_mode = N.STAGE_ADDEND_GATHER
                 else:
                     spec.refs["addend"] = tensor_ref(addend_id)
-                addend_kind = N.ADDEND_VECTOR
-            spec.ints.update(N=n_rows, K=words * 8, group_size=64, addend_kind=addend_kind, epilogue=epilogue)
+                    addend_mode = (
+                        N.STAGE_ADDEND_PLAIN if spec.refs["addend"].space == "input" else N.STAGE_ADDEND_STAMPED
+                    )
+            spec.ints.update(N=n_rows, K=words * 8, group_size=64, addend_mode=addend_mode, epilogue=epilogue)
             spec.floats.update(alpha=float(op.attrs.get("alpha", 1.0)), beta=float(op.attrs.get("beta", 1.0)))
             spec.refs["out"] = place(out)
+            if spec.refs["out"].space == "output":
+                spec.flags |= N.STAGE_FLAG_OUT_PLAIN
             env[out] = ("tensor", spec.refs["out"])
             stages.append(spec)
         elif kind == "rope_kv_cache_append":
@@ -320,9 +325,9 @@ def stage_array(program: StepProgram, resolve, *, greedy: dict | None = None):
     """ctypes array of ``aoto_step_stage`` for ``program``.
 
     ``resolve(ref) -> int`` maps a reference to a device address. ``greedy``
-    (``token``, ``generated``, ``counters``, ``position``, ``mask``,
-    ``generated_capacity`` device addresses/sizes) appends the pick stage and
-    makes the first stage derive the step's position and mask from the counters.
+    (``token``, ``generated``, ``counters`` device addresses and
+    ``generated_capacity``) appends the pick stage and makes every attention
+    stage derive the step's position and window from the counters.
     """
 
     count = len(program.stages) + (1 if greedy else 0)
@@ -338,13 +343,12 @@ def stage_array(program: StepProgram, resolve, *, greedy: dict | None = None):
         for name, number in spec.floats.items():
             setattr(stage, name, number)
     if greedy:
-        first, last = array[0], array[len(program.stages) - 1]
-        first.flags |= N.STAGE_FLAG_STEP_INPUTS
-        first.counters = greedy["counters"]
-        first.position_out = greedy["position"]
-        first.mask_out = greedy["mask"]
-        first.capacity = program.capacity
+        last = array[len(program.stages) - 1]
         last.flags |= N.STAGE_FLAG_ARGMAX
+        for slot, spec in enumerate(program.stages):
+            if spec.kind == N.STAGE_ATTENTION:
+                array[slot].flags |= N.STAGE_FLAG_WINDOW
+                array[slot].counters = greedy["counters"]
         pick = array[count - 1]
         pick.kind = N.STAGE_PICK
         pick.token = greedy["token"]
@@ -368,9 +372,13 @@ def scratch_bytes(array) -> int:
     return int(N.load().aoto_sm100_decode_step_scratch_bytes(array, len(array)))
 
 
-def launch(stages_dev: torch.Tensor, count: int, sync_words: torch.Tensor, status: torch.Tensor,
-           scratch: torch.Tensor, ctas: int = 0) -> None:
-    args = N.DecodeStepArgs(stages_dev.data_ptr(), count, ctas, sync_words.data_ptr(), status.data_ptr(),
-                            scratch.data_ptr(), scratch.numel())
+def launch(stages_dev: torch.Tensor, count: int, epoch: int, status: torch.Tensor,
+           scratch: torch.Tensor, ctas: int = 0, trace: torch.Tensor | None = None) -> None:
+    """One decode step. ``epoch`` must be non-zero and new for the arena; ``trace``
+    (int64 ``[count * 4]``) collects CTA 0's per-stage timestamps."""
+
+    args = N.DecodeStepArgs(stages_dev.data_ptr(), count, ctas, epoch & 0xFFFFFFFF or 1, 0, status.data_ptr(),
+                            scratch.data_ptr(), scratch.numel(),
+                            trace.data_ptr() if trace is not None else None)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     N.check(N.load().aoto_sm100_decode_step(ctypes.byref(args), stream), "aoto_sm100_decode_step")

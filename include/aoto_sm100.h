@@ -324,11 +324,20 @@ int64_t aoto_sm100_attention_scratch_bytes(const aoto_attention_args* args);
  * depending on the previous one; launched one by one, launch latency and the
  * cold start of every kernel dominate the step. aoto_sm100_decode_step runs the
  * whole chain in ONE cooperative launch: the caller describes the step as a
- * program of stages (below), every CTA of the grid walks the program, and the
- * stages are separated by a grid-wide barrier (bounded: a wait that runs out
- * stores 1 + the stage index in `status` and the kernel returns). Weights of
- * the next projection are requested before the barrier is waited for, so the
- * HBM stream does not stop at stage boundaries.
+ * program of stages (below) and every CTA of the grid walks the program.
+ *
+ * Stages are NOT separated by barriers. Every intermediate vector lives in the
+ * arena as 8-byte words {two bf16 values, 32-bit stamp}; a producer stores each
+ * word with one 8-byte store carrying the launch's `epoch` as stamp, and a
+ * consumer simply polls the words it needs until they carry that stamp. A stage
+ * therefore starts on a CTA as soon as ITS inputs have landed, one L2 round
+ * trip after they were produced, and the weights of a projection are requested
+ * before its input row is polled, so the HBM stream does not stop at stage
+ * boundaries. Polls are bounded: one that runs out stores 1 + the stage index
+ * in `status` and the CTA leaves the kernel (its consumers then run out too).
+ *
+ * `epoch` must be non-zero and differ from the epoch of every earlier launch
+ * that used the same arena (count launches). The arena needs no clearing.
  *
  * The program is what the reference's unrolled plan runner executes operation
  * by operation (runtime/plan.py:554-733) for the decode graph of
@@ -340,39 +349,45 @@ int64_t aoto_sm100_attention_scratch_bytes(const aoto_attention_args* args);
 #define AOTO_STAGE_ATTENTION 2 /* rope_kv_cache_append + mask conversion + attention of one layer */
 #define AOTO_STAGE_PICK 3      /* greedy token from the per-CTA maxima of the preceding GEMV       */
 
-#define AOTO_STAGE_FLAG_STEP_INPUTS 1  /* GEMV: one CTA also writes position/mask from counters    */
-#define AOTO_STAGE_FLAG_ARGMAX 2       /* GEMV: every CTA leaves its (max, index) in scratch       */
+#define AOTO_STAGE_FLAG_ARGMAX 2   /* GEMV: every CTA leaves its (max, index) in scratch for PICK  */
+#define AOTO_STAGE_FLAG_WINDOW 4   /* ATTENTION: position and mask come from `counters`            */
+#define AOTO_STAGE_FLAG_OUT_PLAIN 8 /* GEMV: `out` is a plain bf16 vector (a graph output)         */
+#define AOTO_STAGE_FLAG_X_GATHER 16 /* GEMV: `x` is a bf16 table [x_rows, K]; its row x_index[0] is
+                                       the input (an embedding folded into the projection)          */
+
+/* how a GEMV stage reads its addend */
+#define AOTO_STAGE_ADDEND_NONE 0
+#define AOTO_STAGE_ADDEND_PLAIN 1   /* constant bf16 vector (a bias)                                */
+#define AOTO_STAGE_ADDEND_STAMPED 2 /* an intermediate in the arena                                 */
+#define AOTO_STAGE_ADDEND_GATHER 3  /* row x_index[0] of the bf16 table `addend` (width N)          */
 
 typedef struct aoto_step_stage {
   /* GEMV */
-  const void* x;             /* [K] bf16; with x_index: table [x_rows, K] and x = table[x_index[0]] */
-  const int64_t* x_index;
-  void* x_copy;              /* optional [K]: receives the (gathered) input row                     */
+  const void* x;             /* stamped [K], or the table of AOTO_STAGE_FLAG_X_GATHER                */
+  const int64_t* x_index;    /* [1]: row index of the gathered input and/or of a gathered addend     */
   const void* packed;
   const void* scales;
   const void* packed2;
   const void* scales2;
   const void* addend;
   const void* norm_weight;
-  void* out;                 /* [N] bf16 */
+  void* out;                 /* stamped [N] (or plain bf16 with AOTO_STAGE_FLAG_OUT_PLAIN)            */
   /* ATTENTION */
-  const void* row;           /* packed q/k/v projection of the step, [(QH+2*KVH)*D]               */
-  const void* cos_table;     /* [table_rows, D]; the row used is position[0]                        */
+  const void* row;           /* stamped packed q/k/v projection of the step, [(QH+2*KVH)*D]        */
+  const void* cos_table;     /* bf16 [table_rows, D]; the row used is the step's position           */
   const void* sin_table;
-  const int64_t* position;
+  const int64_t* position;   /* [1] (ignored with AOTO_STAGE_FLAG_WINDOW)                           */
   const void* cache_in;      /* this layer's pair [2,1,KVH,C,D] in the incoming cache              */
   void* cache_out;           /* this layer's pair in the next cache                                 */
-  const uint8_t* mask;       /* bool [C]: true = attend                                            */
-  void* attn_out;            /* [QH*D] */
-  /* PICK and STEP_INPUTS */
+  const uint8_t* mask;       /* bool [C], true = attend (ignored with AOTO_STAGE_FLAG_WINDOW)       */
+  void* attn_out;            /* stamped [QH*D] */
+  /* PICK, and the window of ATTENTION */
   int64_t* token;            /* [1] */
   int64_t* generated;
-  int32_t* counters;         /* int32[2]: valid_length, tokens generated                            */
-  int64_t* position_out;     /* STEP_INPUTS: [1]                                                    */
-  uint8_t* mask_out;         /* STEP_INPUTS: bool [capacity]                                        */
+  int32_t* counters;         /* int32[2]: valid_length of the step, tokens generated so far         */
   int64_t x_rows;
   int32_t kind, flags;
-  int32_t N, K, group_size, addend_kind, epilogue;
+  int32_t N, K, group_size, addend_mode, epilogue;
   int32_t query_heads, kv_heads, capacity, head_dim;
   int32_t query_start, key_start, value_start, table_rows;
   int32_t generated_capacity, reserved;
@@ -383,10 +398,14 @@ typedef struct aoto_decode_step_args {
   const aoto_step_stage* stages; /* device array */
   int32_t stage_count;
   int32_t ctas;                  /* 0 = one per SM */
-  uint64_t* sync_words;          /* device, uint64[2], zero before first use: barrier count, epoch */
+  uint32_t epoch;                /* stamp of this launch, see above */
+  int32_t reserved;
   int32_t* status;               /* device int32, zero = no error                                   */
   void* scratch;                 /* same contract as the other entry points                         */
   int64_t scratch_bytes;
+  uint64_t* trace;               /* optional, device uint64[stage_count * 4]: per stage, CTA 0's
+                                    %globaltimer (ns) when it reached the stage, when its input was
+                                    complete, when its work was done and when its results were out */
 } aoto_decode_step_args;
 
 int aoto_sm100_decode_step(const aoto_decode_step_args* args, void* stream);
@@ -395,6 +414,8 @@ int64_t aoto_sm100_decode_step_scratch_bytes(const aoto_step_stage* host_stages,
 /* 1 if every stage of the host copy is within the kernel's limits, else 0. */
 int aoto_sm100_decode_step_supported(const aoto_step_stage* host_stages, int32_t stage_count);
 int aoto_sm100_decode_step_stage_size(void); /* sizeof(aoto_step_stage), for binding checks */
+/* Bytes of a stamped vector of `count` bf16 values (count even). */
+int64_t aoto_sm100_stamped_bytes(int64_t count);
 
 #ifdef __cplusplus
 }
