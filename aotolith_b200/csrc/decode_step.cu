@@ -39,7 +39,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 __device__ __forceinline__ void trace_mark(const StepControl& ctl, int stage, int which) {
-  if (ctl.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) ctl.trace[stage * 4 + which] = global_timer_ns();
+  if (ctl.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) ctl.trace[stage * 8 + which] = global_timer_ns();
 }
 
 // ---- stamped words ---------------------------------------------------------
@@ -150,13 +150,50 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
       if (it_ok[b]) load_item(st, tile, mat, kb, g, t, &items[b]);
     }
   };
-  if (rounds > 0) load_batch(0, 0);
+  // A stage with many tiles per CTA and few k blocks per tile (the LM head) runs "warp mode":
+  // every warp owns whole tiles, accumulates in registers and stores its rows itself, so the
+  // warps stream independently with no CTA-wide synchronisation between tiles.
+  const bool warp_mode = rp.per_tile <= 16 && rp.my_tiles >= STEP_WARPS &&
+                         st.addend_mode <= AOTO_STAGE_ADDEND_PLAIN;
+  auto load_owned = [&](int local_tile, int first_item) {
+#pragma unroll
+    for (int b = 0; b < STEP_BATCH; ++b) {
+      const int i = first_item + b;
+      it_ok[b] = local_tile < rp.my_tiles && i < rp.per_tile;
+      if (it_ok[b]) {
+        const int mat = i / rp.nblocks, kb = i - mat * rp.nblocks;
+        it_kb[b] = kb;
+        it_q[b] = mat;
+        load_item(st, blockIdx.x + local_tile * gridDim.x, mat, kb, g, t, &items[b]);
+      }
+    }
+  };
+  if (warp_mode) load_owned(warp, 0);
+  else if (rounds > 0) load_batch(0, 0);
 
   long long gather_row = 0;
   if (st.x_index != nullptr) {
     gather_row = *reinterpret_cast<const volatile long long*>(st.x_index);
     if (gather_row < 0) gather_row = 0;
     if (gather_row >= st.x_rows) gather_row = st.x_rows - 1;
+  }
+
+  // ---- the addend of the first round does not depend on the input row either ----
+  float addend0 = 0.f;
+  uint2 addend0_word = make_uint2(0u, 0u);
+  {
+    const int tl0 = tid >> 4, r0 = tid & 15;
+    const int tiles0 = min(rp.tiles_per_round, rp.my_tiles);
+    const int n0 = (blockIdx.x + tl0 * gridDim.x) * 16 + r0;
+    if (tl0 < tiles0 && n0 < N) {
+      if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN) {
+        addend0 = __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[n0]);
+      } else if (st.addend_mode == AOTO_STAGE_ADDEND_GATHER) {
+        addend0 = __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[(size_t)gather_row * N + n0]);
+      } else if (st.addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
+        addend0_word = ld_stamped(reinterpret_cast<const unsigned char*>(st.addend) + (size_t)(n0 >> 1) * 8);
+      }
+    }
   }
 
   // ---- input row: gather it, or poll its stamped words ----
@@ -243,16 +280,76 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
     sm.xsum[gi] = 136.f * s;
   }
   __syncthreads();
+  trace_mark(ctl, stage_index, 2);
 
   // ---- rounds: compute a batch, request the next one, then (at the end of a round) reduce ----
   bf16* out_plain = reinterpret_cast<bf16*>(st.out);
   unsigned char* out_words = reinterpret_cast<unsigned char*>(st.out);
-  const bool keep = ((g & 1) == (t >> 1));
+  const BSource bs = b_source(sm.xs, reinterpret_cast<const uint4*>(sm.flag) + 1, lane);
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
   int polls = 0;
 
-  for (int round = 0; round < rounds; ++round) {
+  if (warp_mode) {
+    float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    int local_tile = warp, first_item = 0;
+    bool marked = false;
+    while (local_tile < rp.my_tiles) {
+#pragma unroll
+      for (int b = 0; b < STEP_BATCH; ++b) {
+        if (!it_ok[b]) continue;
+        float lo, hi;
+        mma_block(items[b], bs, it_kb[b], sm.xsum, lo, hi);
+        if (it_q[b] == 0) { acc[0][0] += lo; acc[0][1] += hi; }
+        else { acc[1][0] += lo; acc[1][1] += hi; }
+      }
+      if (!marked) { trace_mark(ctl, stage_index, 3); marked = true; }
+      const int done_tile = local_tile;
+      first_item += STEP_BATCH;
+      const bool tile_done = first_item >= rp.per_tile;
+      if (tile_done) { local_tile += STEP_WARPS; first_item = 0; }
+      load_owned(local_tile, first_item);  // the next batch is in flight while this tile is finished
+      if (tile_done) {
+        const int tile = blockIdx.x + done_tile * gridDim.x;
+        uint32_t bits[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int n = tile * 16 + g + half * 8;
+          float y = st.alpha * acc[0][half];
+          if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN && n < N)
+            y = fmaf(st.beta, __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[n]), y);
+          if (st.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED) {
+            const float gate = round_bf16(y);
+            y = (st.alpha * acc[1][half]) * (gate / (1.f + expf(-gate)));
+          }
+          bits[half] = float_to_bf16_bits(y);
+        }
+        const uint32_t next_lo = __shfl_down_sync(0xffffffffu, bits[0], 4);
+        const uint32_t next_hi = __shfl_down_sync(0xffffffffu, bits[1], 4);
+        if (t == 0) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int n = tile * 16 + g + half * 8;
+            if (n >= N) continue;
+            if (st.flags & AOTO_STAGE_FLAG_OUT_PLAIN) {
+              out_plain[n] = __ushort_as_bfloat16((unsigned short)bits[half]);
+            } else if ((g & 1) == 0) {
+              st_stamped(out_words + (size_t)(n >> 1) * 8, bits[half] | ((half ? next_hi : next_lo) << 16), epoch);
+            }
+            if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
+              float v = __uint_as_float(bits[half] << 16);
+              if (v != v) v = INFINITY;
+              if (v > best_v || (v == best_v && n < best_i)) { best_v = v; best_i = n; }
+            }
+          }
+        }
+        acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = 0.f;
+      }
+    }
+    __syncthreads();
+  }
+
+  for (int round = 0; round < (warp_mode ? 0 : rounds); ++round) {
     const int tiles_here = min(rp.tiles_per_round, rp.my_tiles - round * rp.tiles_per_round);
     const int items_in_round = tiles_here * rp.per_tile;
     const int per_warp = (items_in_round + STEP_WARPS - 1) / STEP_WARPS;
@@ -262,28 +359,9 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
       for (int b = 0; b < STEP_BATCH; ++b) {
         r_lo[b] = r_hi[b] = 0.f;
         if (!it_ok[b]) continue;
-        const int kb = it_kb[b];
-        uint4 bf[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          bf[j] = sm.xs[kb * 16 + t * 4 + j];
-          if (!keep) bf[j] = make_uint4(0u, 0u, 0u, 0u);
-        }
-        const float2 off = *reinterpret_cast<const float2*>(sm.xsum + kb * 2);
-        const WeightItem& it = items[b];
-        const uint32_t wl[4] = {it.lo.x, it.lo.y, it.lo.z, it.lo.w};
-        const uint32_t wh[4] = {it.hi.x, it.hi.y, it.hi.z, it.hi.w};
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          mma_16816(c, AOTO_NIB(wl[j], 0), AOTO_NIB(wh[j], 0), AOTO_NIB(wl[j], 4), AOTO_NIB(wh[j], 4),
-                    bf[j].x, bf[j].y);
-          mma_16816(c, AOTO_NIB(wl[j], 8), AOTO_NIB(wh[j], 8), AOTO_NIB(wl[j], 12), AOTO_NIB(wh[j], 12),
-                    bf[j].z, bf[j].w);
-        }
-        r_lo[b] = bf16x2_lo(it.slo) * (c[0] - off.x) + bf16x2_hi(it.slo) * (c[1] - off.y);
-        r_hi[b] = bf16x2_lo(it.shi) * (c[2] - off.x) + bf16x2_hi(it.shi) * (c[3] - off.y);
+        mma_block(items[b], bs, it_kb[b], sm.xsum, r_lo[b], r_hi[b]);
       }
+      if (round == 0 && first == 0) trace_mark(ctl, stage_index, 3);
       // this batch's registers are free: request the next batch before touching shared memory
       int q_done[STEP_BATCH];
       bool ok_done[STEP_BATCH];
@@ -310,6 +388,7 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
       }
     }
     __syncthreads();
+    if (round == 0) trace_mark(ctl, stage_index, 4);
     // reduce over k blocks in a fixed order, epilogue, store
     const bool mine = tid < tiles_here * 16;
     const int tl = tid >> 4, r = tid & 15;
@@ -325,12 +404,16 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
         for (int kb = 0; kb < rp.nblocks; ++kb) total2 += p0[(rp.nblocks + kb) * 16];
       y = st.alpha * total;
       if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN) {
-        y = fmaf(st.beta, __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[n]), y);
+        const float a = round == 0 ? addend0 : __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[n]);
+        y = fmaf(st.beta, a, y);
       } else if (st.addend_mode == AOTO_STAGE_ADDEND_GATHER) {
-        y = fmaf(st.beta, __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[(size_t)gather_row * N + n]), y);
+        const float a = round == 0
+                            ? addend0
+                            : __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[(size_t)gather_row * N + n]);
+        y = fmaf(st.beta, a, y);
       } else if (st.addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
         const unsigned char* words = reinterpret_cast<const unsigned char*>(st.addend) + (size_t)(n >> 1) * 8;
-        uint2 w = ld_stamped(words);
+        uint2 w = round == 0 ? addend0_word : ld_stamped(words);
         while (w.y != epoch && ++polls <= POLL_LIMIT) w = ld_stamped(words);
         y = fmaf(st.beta, (n & 1) ? bf16x2_hi(w.x) : bf16x2_lo(w.x), y);
       }
@@ -353,10 +436,11 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
         if (v > best_v || (v == best_v && n < best_i)) { best_v = v; best_i = n; }
       }
     }
+    if (round == 0) trace_mark(ctl, stage_index, 5);
     __syncthreads();
   }
   if (__syncthreads_or(polls > POLL_LIMIT)) { give_up(ctl, stage_index); return false; }
-  trace_mark(ctl, stage_index, 2);
+  trace_mark(ctl, stage_index, 6);
 
   if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
     float* sv = sm.red;
@@ -377,7 +461,7 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
       st_stamped(payload + (size_t)blockIdx.x * 16 + 8, (uint32_t)best_i, epoch);
     }
   }
-  trace_mark(ctl, stage_index, 3);
+  trace_mark(ctl, stage_index, 7);
   return true;
 }
 
@@ -401,8 +485,8 @@ __device__ bool stage_attention(const aoto_step_stage& st, const StepSmem& sm, c
   trace_mark(ctl, stage_index, 0);
   if ((int)blockIdx.x >= total_items) {
     trace_mark(ctl, stage_index, 1);
-    trace_mark(ctl, stage_index, 2);
-    trace_mark(ctl, stage_index, 3);
+    trace_mark(ctl, stage_index, 6);
+    trace_mark(ctl, stage_index, 7);
     return true;
   }
   const uint32_t epoch = ctl.epoch;
@@ -633,8 +717,8 @@ __device__ bool stage_attention(const aoto_step_stage& st, const StepSmem& sm, c
     __syncthreads();
     first_item = false;
   }
-  trace_mark(ctl, stage_index, 2);
-  trace_mark(ctl, stage_index, 3);
+  trace_mark(ctl, stage_index, 6);
+  trace_mark(ctl, stage_index, 7);
   return true;
 }
 
@@ -680,15 +764,15 @@ __device__ bool stage_pick(const aoto_step_stage& st, const StepControl& ctl, in
     }
     if (threadIdx.x == 0 && failed) atomicCAS(ctl.status, 0, stage_index + 1);
   }
-  trace_mark(ctl, stage_index, 2);
-  trace_mark(ctl, stage_index, 3);
+  trace_mark(ctl, stage_index, 6);
+  trace_mark(ctl, stage_index, 7);
   return true;
 }
 
 __global__ void __launch_bounds__(STEP_THREADS, 1)
 decode_step_kernel(const aoto_step_stage* __restrict__ stages, int stage_count, StepControl ctl) {
   extern __shared__ uint4 smem_raw[];
-  __shared__ aoto_step_stage stage;
+  __shared__ aoto_step_stage stage_buffer[2];
   StepSmem sm;
   sm.xs = smem_raw;
   sm.xsum = reinterpret_cast<float*>(sm.xs + STEP_MAX_K / 8);
@@ -696,28 +780,33 @@ decode_step_kernel(const aoto_step_stage* __restrict__ stages, int stage_count, 
   sm.part = sm.csum + STEP_MAX_K / 8;
   sm.red = sm.part + STEP_MAX_ITEMS * 16;
   sm.flag = reinterpret_cast<int*>(sm.red + 64);
-  sm.tile = reinterpret_cast<unsigned char*>(sm.flag + 4);
+  sm.tile = reinterpret_cast<unsigned char*>(sm.flag + 8);
+  if (threadIdx.x == 0) *(reinterpret_cast<uint4*>(sm.flag) + 1) = make_uint4(0u, 0u, 0u, 0u);
 
+  // Stage descriptors are double buffered: the next one is requested while the current
+  // stage runs, so a stage never starts with a round trip for its own description.
+  constexpr int WORDS = sizeof(aoto_step_stage) / 4;
+  if (threadIdx.x < WORDS)
+    reinterpret_cast<uint32_t*>(&stage_buffer[0])[threadIdx.x] = __ldg(reinterpret_cast<const uint32_t*>(stages) + threadIdx.x);
+  __syncthreads();
   for (int s = 0; s < stage_count; ++s) {
-    __syncthreads();
-    {
-      const int words = sizeof(aoto_step_stage) / 4;
-      const uint32_t* src = reinterpret_cast<const uint32_t*>(stages + s);
-      uint32_t* dst = reinterpret_cast<uint32_t*>(&stage);
-      for (int i = threadIdx.x; i < words; i += STEP_THREADS) dst[i] = __ldg(src + i);
-    }
-    __syncthreads();
+    uint32_t next_word = 0;
+    if (threadIdx.x < WORDS && s + 1 < stage_count)
+      next_word = __ldg(reinterpret_cast<const uint32_t*>(stages + s + 1) + threadIdx.x);
+    const aoto_step_stage& stage = stage_buffer[s & 1];
     bool alive = true;
     if (stage.kind == AOTO_STAGE_GEMV) alive = stage_gemv(stage, sm, ctl, s);
     else if (stage.kind == AOTO_STAGE_ATTENTION) alive = stage_attention(stage, sm, ctl, s);
     else if (stage.kind == AOTO_STAGE_PICK) alive = stage_pick(stage, ctl, s);
     if (!alive) return;
+    if (threadIdx.x < WORDS) reinterpret_cast<uint32_t*>(&stage_buffer[(s + 1) & 1])[threadIdx.x] = next_word;
+    __syncthreads();
   }
 }
 
 static size_t step_smem_bytes() {
   const size_t fixed = (size_t)STEP_MAX_K / 8 * 16 + (size_t)STEP_MAX_K / 64 * 4 + (size_t)STEP_MAX_K / 8 * 4 +
-                       (size_t)STEP_MAX_ITEMS * 16 * 4 + 64 * 4 + 16;
+                       (size_t)STEP_MAX_ITEMS * 16 * 4 + 64 * 4 + 32;
   const size_t attention = (size_t)2 * ATT_TILE * (128 * 2 + 16) +
                            ((size_t)(MAX_GROUP + 2) * 128 + (size_t)MAX_GROUP * 128 + (size_t)MAX_GROUP * ATT_TILE +
                             (size_t)MAX_GROUP * 2 + ATT_TILE + (size_t)2 * MAX_GROUP * 128) * 4;

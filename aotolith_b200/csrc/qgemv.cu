@@ -36,7 +36,8 @@ qgemv_mma_kernel(const GemvParams p) {
   const int nblocks = K >> 7, groups = K >> 6, chunks = K >> 3;
   const int W = blockDim.x >> 5;
   uint4* xs = smem;
-  float* xsum = reinterpret_cast<float*>(xs + chunks);
+  uint4* zero16 = xs + chunks;  // directly after the 16-byte chunks, so it is 16-byte aligned
+  float* xsum = reinterpret_cast<float*>(zero16 + 1);
   float* csum = xsum + groups;
   float* part = csum + chunks;
   float* red = part + MATS * RT * W * 16;
@@ -44,6 +45,7 @@ qgemv_mma_kernel(const GemvParams p) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int m = blockIdx.y;
+  if (tid == 0) *zero16 = make_uint4(0u, 0u, 0u, 0u);
   const int tile0 = blockIdx.x * RT;
   const int per_rt = (nblocks + W - 1) / W;
   const int row_u4 = K >> 5;   // uint4 per packed row
@@ -101,7 +103,7 @@ qgemv_mma_kernel(const GemvParams p) {
     for (int rt = 0; rt < RT; ++rt) acc[mat][rt][0] = acc[mat][rt][1] = 0.f;
 
   // even B columns carry the first group of the block, odd ones the second
-  const bool keep = ((g & 1) == (t >> 1));
+  const BSource bs = b_source(xs, zero16, lane);
 
   for (int step = 0; step < per_rt; step += UK) {
     if (step > 0) load_batch(step);
@@ -109,30 +111,14 @@ qgemv_mma_kernel(const GemvParams p) {
     for (int u = 0; u < UK; ++u) {
       const int kb = warp + (step + u) * W;
       if (kb < nblocks) {
-        uint4 b[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          b[j] = xs[kb * 16 + t * 4 + j];
-          if (!keep) b[j] = make_uint4(0u, 0u, 0u, 0u);
-        }
-        const float2 off = *reinterpret_cast<const float2*>(xsum + kb * 2);
 #pragma unroll
         for (int mat = 0; mat < MATS; ++mat) {
 #pragma unroll
           for (int rt = 0; rt < RT; ++rt) {
-            const WeightItem& it = item[mat][rt][u];
-            const uint32_t wl[4] = {it.lo.x, it.lo.y, it.lo.z, it.lo.w};
-            const uint32_t wh[4] = {it.hi.x, it.hi.y, it.hi.z, it.hi.w};
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              mma_16816(c, AOTO_NIB(wl[j], 0), AOTO_NIB(wh[j], 0), AOTO_NIB(wl[j], 4),
-                        AOTO_NIB(wh[j], 4), b[j].x, b[j].y);
-              mma_16816(c, AOTO_NIB(wl[j], 8), AOTO_NIB(wh[j], 8), AOTO_NIB(wl[j], 12),
-                        AOTO_NIB(wh[j], 12), b[j].z, b[j].w);
-            }
-            acc[mat][rt][0] += bf16x2_lo(it.slo) * (c[0] - off.x) + bf16x2_hi(it.slo) * (c[1] - off.y);
-            acc[mat][rt][1] += bf16x2_lo(it.shi) * (c[2] - off.x) + bf16x2_hi(it.shi) * (c[3] - off.y);
+            float lo, hi;
+            mma_block(item[mat][rt][u], bs, kb, xsum, lo, hi);
+            acc[mat][rt][0] += lo;
+            acc[mat][rt][1] += hi;
           }
         }
       }
@@ -255,7 +241,7 @@ template <int RT, int UK, bool PAIRED>
 static int launch_mma(const GemvParams& p, const GemvPlan& plan, int M, cudaStream_t stream, bool pdl) {
   constexpr int MATS = PAIRED ? 2 : 1;
   const size_t smem = (size_t)p.K * 2 + (size_t)(p.K / 64) * 4 + (size_t)(p.K / 8) * 4 +
-                      (size_t)MATS * RT * plan.W * 16 * 4 + 32 * 4;
+                      (size_t)MATS * RT * plan.W * 16 * 4 + 32 * 4 + 16;
   auto kernel = qgemv_mma_kernel<RT, UK, PAIRED>;
   if (smem > 48 * 1024) {
     static bool raised = false;  // idempotent; a race only repeats the call

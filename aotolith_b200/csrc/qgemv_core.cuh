@@ -115,4 +115,41 @@ struct WeightItem {
   uint32_t slo, shi; // the two group scales (bf16 pair) of each row
 };
 
+// Where a lane reads its B fragments. B column parity separates the two groups of a
+// block: a lane either always reads the staged activation (`stride` 1) or always reads
+// zeros (`stride` 0, `base` a zeroed 16-byte word), so no per-fragment select is needed.
+struct BSource {
+  const uint4* base;
+  int stride;
+};
+
+__device__ __forceinline__ BSource b_source(const uint4* xs, const uint4* zero16, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const bool keep = ((g & 1) == (t >> 1));
+  BSource b;
+  b.base = keep ? xs + t * 4 : zero16;
+  b.stride = keep ? 1 : 0;
+  return b;
+}
+
+// One 16-row x 128-column block: eight mma into one C tile that starts at minus the
+// 136*sum(x) offsets of the two groups, then the per-row group scales. `lo` / `hi` are the
+// contributions to rows g and g+8 (identical on the four lanes of a quad).
+__device__ __forceinline__ void mma_block(const WeightItem& it, const BSource& bs, int kb,
+                                          const float* xsum, float& lo, float& hi) {
+  const uint4* bp = bs.base + kb * 16 * bs.stride;
+  const float2 off = *reinterpret_cast<const float2*>(xsum + kb * 2);
+  float c[4] = {-off.x, -off.y, -off.x, -off.y};
+  const uint32_t wl[4] = {it.lo.x, it.lo.y, it.lo.z, it.lo.w};
+  const uint32_t wh[4] = {it.hi.x, it.hi.y, it.hi.z, it.hi.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 b = bp[j * bs.stride];
+    mma_16816(c, AOTO_NIB(wl[j], 0), AOTO_NIB(wh[j], 0), AOTO_NIB(wl[j], 4), AOTO_NIB(wh[j], 4), b.x, b.y);
+    mma_16816(c, AOTO_NIB(wl[j], 8), AOTO_NIB(wh[j], 8), AOTO_NIB(wl[j], 12), AOTO_NIB(wh[j], 12), b.z, b.w);
+  }
+  lo = fmaf(bf16x2_lo(it.slo), c[0], bf16x2_hi(it.slo) * c[1]);
+  hi = fmaf(bf16x2_lo(it.shi), c[2], bf16x2_hi(it.shi) * c[3]);
+}
+
 }  // namespace aoto

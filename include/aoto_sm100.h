@@ -403,9 +403,11 @@ typedef struct aoto_decode_step_args {
   int32_t* status;               /* device int32, zero = no error                                   */
   void* scratch;                 /* same contract as the other entry points                         */
   int64_t scratch_bytes;
-  uint64_t* trace;               /* optional, device uint64[stage_count * 4]: per stage, CTA 0's
-                                    %globaltimer (ns) when it reached the stage, when its input was
-                                    complete, when its work was done and when its results were out */
+  uint64_t* trace;               /* optional, device uint64[stage_count * 8]: CTA 0's %globaltimer
+                                    (ns) per stage at: 0 stage reached, 1 input complete, 2 input
+                                    staged, 3 first weight batch multiplied, 4 first round reduced,
+                                    5 first round stored, 6 work done, 7 results out (stages other
+                                    than GEMV fill 0, 1, 6, 7)                                       */
 } aoto_decode_step_args;
 
 int aoto_sm100_decode_step(const aoto_decode_step_args* args, void* stream);
