@@ -17,11 +17,11 @@
 
 namespace aoto {
 
-constexpr int STEP_THREADS = 512;
+constexpr int STEP_THREADS = 256;
 constexpr int STEP_WARPS = STEP_THREADS / 32;
 constexpr int STEP_MAX_K = 16384;      // activation row staged in shared memory
 constexpr int STEP_MAX_ITEMS = 256;    // (tile, block) items of one round
-constexpr int STEP_BATCH = 4;          // items a warp holds in registers at once
+constexpr int STEP_BATCH = 8;          // items a warp holds in registers at once
 constexpr int POLL_LIMIT = 1 << 20;    // rounds of a bounded poll (each is >= one L2 round trip)
 constexpr int ATT_TILE = 64;           // keys per attention item
 constexpr int MAX_GROUP = 16;          // query heads per kv head
@@ -84,7 +84,10 @@ __device__ __forceinline__ void give_up(const StepControl& ctl, int stage) {
 // ---------------------------------------------------------------------------
 struct RoundPlan {
   int tiles, nblocks, mats, my_tiles, tiles_per_round, per_tile;
+  float inv_per_tile, inv_nblocks;  // exact for the small quotients taken here (< 2^10)
 };
+
+__device__ __forceinline__ int small_div(int a, float inv_b) { return __float2int_rd(((float)a + 0.5f) * inv_b); }
 
 __device__ __forceinline__ RoundPlan plan_rounds(const aoto_step_stage& st) {
   RoundPlan r;
@@ -98,15 +101,17 @@ __device__ __forceinline__ RoundPlan plan_rounds(const aoto_step_stage& st) {
   if (tpr < 1) tpr = 1;
   if (tpr > 8) tpr = 8;
   r.tiles_per_round = tpr;
+  r.inv_per_tile = 1.f / (float)r.per_tile;
+  r.inv_nblocks = 1.f / (float)r.nblocks;
   return r;
 }
 
 __device__ __forceinline__ bool item_of(const RoundPlan& r, int round, int q, int* tile, int* mat, int* kb) {
-  const int tl = q / r.per_tile;
+  const int tl = small_div(q, r.inv_per_tile);
   const int local = round * r.tiles_per_round + tl;
   if (tl >= r.tiles_per_round || local >= r.my_tiles) return false;
   const int rem = q - tl * r.per_tile;
-  *mat = rem / r.nblocks;
+  *mat = small_div(rem, r.inv_nblocks);
   *kb = rem - *mat * r.nblocks;
   *tile = blockIdx.x + local * gridDim.x;
   return true;
@@ -161,7 +166,7 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
       const int i = first_item + b;
       it_ok[b] = local_tile < rp.my_tiles && i < rp.per_tile;
       if (it_ok[b]) {
-        const int mat = i / rp.nblocks, kb = i - mat * rp.nblocks;
+        const int mat = small_div(i, rp.inv_nblocks), kb = i - mat * rp.nblocks;
         it_kb[b] = kb;
         it_q[b] = mat;
         load_item(st, blockIdx.x + local_tile * gridDim.x, mat, kb, g, t, &items[b]);
@@ -240,22 +245,37 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
   }
   trace_mark(ctl, stage_index, 1);
 
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < MAXC; ++i) {
-    const int c = tid + i * STEP_THREADS;
-    if (c < chunks) {
-      float f[8];
-      unpack8(xr[i], f);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
-    }
-  }
+  // Norm statistic: one shared-memory hop (per-warp partial sums, then every thread adds them
+  // in warp order). Stages alternate between the two halves of `red`, so no barrier is needed
+  // to protect it from the previous stage's readers.
   float inv = 1.f;
-  if (wv != nullptr) inv = rsqrtf(block_sum(ss, sm.red) / (float)K + st.rms_norm_eps);
+  if (wv != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = tid + i * STEP_THREADS;
+      if (c < chunks) {
+        float f[8];
+        unpack8(xr[i], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+      }
+    }
+    ss = warp_sum(ss);
+    float* slot = sm.red + (stage_index & 1) * 32;
+    if (lane == 0) slot[warp] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < STEP_WARPS; ++w) total += slot[w];
+    inv = rsqrtf(total / (float)K + st.rms_norm_eps);
+  }
+  // Normalise, store in fragment order, and sum each group of 64 (eight consecutive chunks,
+  // i.e. eight consecutive lanes) with three shuffles.
 #pragma unroll
   for (int i = 0; i < MAXC; ++i) {
     const int c = tid + i * STEP_THREADS;
+    float chunk_sum = 0.f;
     if (c < chunks) {
       float f[8];
       unpack8(xr[i], f);
@@ -268,16 +288,13 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
       uint4 o;
       o.x = pack_bf16x2(f[0], f[4]); o.y = pack_bf16x2(f[1], f[5]);
       o.z = pack_bf16x2(f[2], f[6]); o.w = pack_bf16x2(f[3], f[7]);
-      sm.csum[c] = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
+      chunk_sum = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
       sm.xs[c] = o;
     }
-  }
-  __syncthreads();
-  for (int gi = tid; gi < (K >> 6); gi += STEP_THREADS) {
-    float s = 0.f;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) s += sm.csum[gi * 8 + c];
-    sm.xsum[gi] = 136.f * s;
+    chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 1);
+    chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 2);
+    chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 4);
+    if (c < chunks && (lane & 7) == 0) sm.xsum[c >> 3] = 136.f * chunk_sum;
   }
   __syncthreads();
   trace_mark(ctl, stage_index, 2);
