@@ -25,6 +25,7 @@ ERR_ARGUMENT = -1
 ERR_UNSUPPORTED = -2
 ERR_LAUNCH = -3
 ERR_TIMEOUT = -4
+ERR_TOO_LARGE = -5
 
 ADDEND_NONE, ADDEND_VECTOR, ADDEND_FULL = 0, 1, 2
 EPILOGUE_NONE, EPILOGUE_SILU_MUL, EPILOGUE_SILU_MUL_PAIRED = 0, 1, 2
@@ -179,6 +180,8 @@ EXPORTS: dict[str, tuple] = {
     "aoto_sm100_kv_cache_append": (c_int, [POINTER(KvAppendArgs), c_void_p]),
     "aoto_sm100_attention": (c_int, [POINTER(AttentionArgs), c_void_p]),
     "aoto_sm100_attention_scratch_bytes": (c_int64, [POINTER(AttentionArgs)]),
+    "aoto_sm100_attention_decode_static": (c_int, [POINTER(AttentionArgs), c_void_p]),
+    "aoto_sm100_attention_static_scratch_limit": (c_int64, []),
 }
 
 _lib = None

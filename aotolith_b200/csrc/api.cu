@@ -21,6 +21,7 @@ extern "C" const char* aoto_sm100_status_string(int status) {
     case AOTO_ERR_UNSUPPORTED: return "no kernel variant for this request";
     case AOTO_ERR_LAUNCH: return "the CUDA runtime refused the launch";
     case AOTO_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case AOTO_ERR_TOO_LARGE: return "the request exceeds a fixed capacity of the library";
     default: return "unknown status";
   }
 }

@@ -329,3 +329,71 @@ extern "C" int aoto_sm100_attention(const aoto_attention_args* a, void* stream_)
   return launch_kernel(attention_prefill_kernel, dim3((unsigned)((rows + PREFILL_WARPS - 1) / PREFILL_WARPS)),
                        dim3(PREFILL_WARPS * 32), smem, stream, false, p);
 }
+
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that must not allocate
+// ---------------------------------------------------------------------------
+//
+// Some hosts of this library are not allowed to allocate device memory once they are running: a
+// serving process whose memory was carved up at start-up and which treats any later cudaMalloc
+// as a bug, an integrator that links the library into a runtime with its own sealed pool and no
+// way to hand a workspace through, a latency-critical loop where the allocator (which may
+// synchronise the whole device) is banned outright. The split-KV decode kernel needs a scratch
+// buffer for its per-split partial results, and every other route to it goes through a buffer
+// the caller allocates. This entry point gives such callers the same kernel with the scratch in
+// a fixed array that is part of the library image.
+//
+// The array is AOTO_STATIC_SCRATCH_BYTES long and every GPU that loads the library holds one
+// copy of it until the process exits. `static_scratch` below is the HOST-side handle of that
+// array, not a device address; the device address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and cached.
+static __device__ __align__(256) unsigned char static_scratch[AOTO_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+void* static_scratch_address[MAX_DEVICES] = {};
+
+// Device address of the static scratch array on the current device, or nullptr.
+void* static_scratch_on_current_device() {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  if (static_scratch_address[device] == nullptr) {
+    void* address = nullptr;
+    if (cudaGetSymbolAddress(&address, static_scratch) != cudaSuccess || address == nullptr) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    static_scratch_address[device] = address;  // racing first calls store the same value
+  }
+  return static_scratch_address[device];
+}
+}  // namespace
+
+extern "C" int64_t aoto_sm100_attention_static_scratch_limit(void) { return AOTO_STATIC_SCRATCH_BYTES; }
+
+extern "C" int aoto_sm100_attention_decode_static(const aoto_attention_args* a, void* stream_) {
+  if (!a) return AOTO_ERR_ARGUMENT;
+  if (a->q_len != 1) return AOTO_ERR_UNSUPPORTED;  // the prefill kernel uses no scratch: call aoto_sm100_attention
+  const int64_t need = aoto_sm100_attention_scratch_bytes(a);
+  if (need > AOTO_STATIC_SCRATCH_BYTES) return AOTO_ERR_TOO_LARGE;
+  void* scratch = static_scratch_on_current_device();
+  if (scratch == nullptr) return AOTO_ERR_LAUNCH;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (need > 0) {
+    // The arrival counters at the head of the array must be zero when the kernel starts. The
+    // kernel leaves them at zero, but the array is shared by every call and keeps whatever the
+    // last one left behind (an aborted launch included), so they are cleared on the stream.
+    if (cudaMemsetAsync(scratch, 0, SCRATCH_HEADER_BYTES, stream) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return AOTO_ERR_LAUNCH;
+    }
+  }
+  aoto_attention_args with_scratch = *a;
+  with_scratch.scratch = scratch;
+  with_scratch.scratch_bytes = AOTO_STATIC_SCRATCH_BYTES;
+  return aoto_sm100_attention(&with_scratch, stream_);
+}

@@ -39,6 +39,7 @@ extern "C" {
 #define AOTO_ERR_UNSUPPORTED (-2) /* a legal request this library has no variant for     */
 #define AOTO_ERR_LAUNCH (-3)      /* the CUDA runtime refused the launch                 */
 #define AOTO_ERR_TIMEOUT (-4)     /* a bounded device-side wait ran out                  */
+#define AOTO_ERR_TOO_LARGE (-5)   /* the request exceeds a fixed capacity of the library */
 
 /* Library identity: ABI version and the SM architecture it was compiled for. */
 int aoto_sm100_abi_version(void);
@@ -314,6 +315,36 @@ typedef struct aoto_attention_args {
 } aoto_attention_args;
 int aoto_sm100_attention(const aoto_attention_args* args, void* stream);
 int64_t aoto_sm100_attention_scratch_bytes(const aoto_attention_args* args);
+
+/*
+ * Single-query (decode) attention for callers that cannot allocate device memory.
+ *
+ * This entry point has no counterpart in the reference; it exists for hosts that are not allowed
+ * to call cudaMalloc (or any allocating library routine) once they are running - a serving
+ * process with a sealed memory budget, a runtime that embeds this library without a channel for
+ * workspaces, a latency-critical loop where allocator calls are banned because they may
+ * synchronise the device. It runs the same split-KV kernel as aoto_sm100_attention with
+ * q_len == 1, but takes the scratch for the per-split partial results from a fixed array inside
+ * the library instead of from `args->scratch` (which is ignored, as is `scratch_bytes`). The
+ * caller still passes q, k, v, mask and out. It allocates nothing and frees nothing.
+ *
+ * Limits and rules:
+ *  - the array is AOTO_STATIC_SCRATCH_BYTES (1 MiB) per GPU, held from the moment the library is
+ *    loaded on that GPU until the process exits; a request whose
+ *    aoto_sm100_attention_scratch_bytes() exceeds it returns AOTO_ERR_TOO_LARGE and launches
+ *    nothing (roughly: query_heads * ceil(kv_len / 64) * (head_dim + 2) * 4 bytes must fit);
+ *  - the first call on each device looks up the array's device address (a one-time, blocking
+ *    set-up call into the CUDA runtime); make that first call during start-up, before any stream
+ *    capture begins on that device;
+ *  - every call on a device shares the one array and the array keeps the previous call's
+ *    contents; the entry point clears the part that must start at zero on the given stream, but
+ *    two calls whose kernels can overlap on the GPU (different streams, no dependency) race on
+ *    it and must be serialised by the caller;
+ *  - q_len must be 1 (AOTO_ERR_UNSUPPORTED otherwise: the multi-query kernel needs no scratch).
+ */
+#define AOTO_STATIC_SCRATCH_BYTES (1 << 20)
+int aoto_sm100_attention_decode_static(const aoto_attention_args* args, void* stream);
+int64_t aoto_sm100_attention_static_scratch_limit(void);
 
 /* ------------------------------------------------------------------------- */
 /* A whole decode step as one persistent kernel                              */
