@@ -6,6 +6,8 @@ namespace aoto {
 int qgemv_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
 int qgemv_check(const aoto_qmatmul_args& a, bool pointers);
 const char* qgemv_variant(const aoto_qmatmul_args& a);
+bool qgemm_applies(const aoto_qmatmul_args& a);
+int qgemm_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
 }  // namespace aoto
 
 using namespace aoto;
@@ -40,6 +42,7 @@ extern "C" int64_t aoto_sm100_qmatmul_scratch_bytes(const aoto_qmatmul_args* a) 
 
 extern "C" const char* aoto_sm100_qmatmul_variant(const aoto_qmatmul_args* a) {
   if (!a) return "none";
+  if (qgemm_applies(*a)) return "gemm_mma";
   return qgemv_variant(*a);
 }
 
@@ -47,5 +50,6 @@ extern "C" int aoto_sm100_qmatmul(const aoto_qmatmul_args* a, void* stream) {
   if (!a) return AOTO_ERR_ARGUMENT;
   const int status = qgemv_check(*a, true);
   if (status != AOTO_OK) return status;
+  if (qgemm_applies(*a)) return qgemm_launch(*a, (cudaStream_t)stream);
   return qgemv_launch(*a, (cudaStream_t)stream);
 }

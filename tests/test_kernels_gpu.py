@@ -140,23 +140,45 @@ def test_qgemv_paired_silu_mul(cuda, K, N):
     assert rel_max_error(got, exact) < ORACLE_TOL
 
 
-@pytest.mark.parametrize("M", [2, 16])
-def test_qmatmul_rows(cuda, M):
+@pytest.mark.parametrize("M,K,N", [(2, 896, 1152), (16, 896, 1152), (128, 896, 1152), (200, 4864, 896),
+                                   (37, 896, 4864), (130, 256, 1000), (5, 64, 24)])
+def test_qmatmul_rows(cuda, M, K, N):
     """Several activation rows (prefill semantics: dequantise, then multiply)."""
 
     ops = _ops()
-    K, N = 896, 1152
-    packed, scales = packed_weight(30, N, K, 64)
+    group = 64 if K % 128 == 0 else 16
+    packed, scales = packed_weight(30, N, K, group)
     x = activations(31, M, K)
     bias = activations(32, N, std=0.5)
-    got = ops.qmatmul(x.to(cuda), packed.to(cuda), scales.to(cuda), group_size=64, addend=bias.to(cuda)).cpu()
-    want = ref.packed_matmul(x, packed, scales, 64, addend=bias)
+    if K % 128 == 0:
+        assert ops.qmatmul_variant(M, N, K, group) == "gemm_mma"
+    got = ops.qmatmul(x.to(cuda), packed.to(cuda), scales.to(cuda), group_size=group, addend=bias.to(cuda)).cpu()
+    want = ref.packed_matmul(x, packed, scales, group, addend=bias)
     assert got.shape == (M, N)
     assert rel_max_error(got, want) < ORACLE_TOL
+    assert rel_max_error(got, exact_packed_matmul(x, packed, scales, group) + bias.double()) < EXACT_TOL
     gate = activations(33, M, N)
-    got = ops.qmatmul(x.to(cuda), packed.to(cuda), scales.to(cuda), group_size=64, gate=gate.to(cuda)).cpu()
-    want = ref.packed_matmul(x, packed, scales, 64, gate=gate)
+    got = ops.qmatmul(x.to(cuda), packed.to(cuda), scales.to(cuda), group_size=group, gate=gate.to(cuda)).cpu()
+    want = ref.packed_matmul(x, packed, scales, group, gate=gate)
     assert rel_max_error(got, want) < ORACLE_TOL
+    resid = activations(34, M, N)
+    got = ops.qmatmul(x.to(cuda), packed.to(cuda), scales.to(cuda), group_size=group, addend=resid.to(cuda)).cpu()
+    want = ref.packed_matmul(x, packed, scales, group, addend=resid)
+    assert rel_max_error(got, want) < ORACLE_TOL
+
+
+def test_qmatmul_rows_match_single_rows(cuda):
+    """Every row of the multi-row product agrees with the decode kernel run on that row alone."""
+
+    ops = _ops()
+    M, K, N = 19, 896, 896
+    packed, scales = packed_weight(35, N, K, 64)
+    x = activations(36, M, K).to(cuda)
+    packed, scales = packed.to(cuda), scales.to(cuda)
+    together = ops.qmatmul(x, packed, scales, group_size=64).float()
+    alone = torch.cat([ops.qmatmul(x[i:i + 1], packed, scales, group_size=64) for i in range(M)]).float()
+    # the two kernels round the weight at different points (code*scale before / scale after the sum)
+    assert float((together - alone).abs().max()) <= ORACLE_TOL * float(alone.abs().max())
 
 
 def test_qgemv_deterministic(cuda):
