@@ -25,6 +25,8 @@ constexpr int STEP_BATCH = 8;          // items a warp holds in registers at onc
 constexpr int POLL_LIMIT = 1 << 20;    // rounds of a bounded poll (each is >= one L2 round trip)
 constexpr int ATT_TILE = 64;           // keys per attention item
 constexpr int MAX_GROUP = 16;          // query heads per kv head
+constexpr int RING_SLOT_BYTES = 7680;  // one 16-row weight tile with its scales (K <= 896)
+constexpr int RING_SLOTS = 2 * STEP_WARPS;
 
 struct StepControl {
   uint32_t epoch;
@@ -64,14 +66,37 @@ __device__ __forceinline__ void cp_async_16_cg(void* smem_dst, const void* gmem_
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
 }
 
+// ---- bulk copies into shared memory, completion counted by an mbarrier ----
+__device__ __forceinline__ uint32_t smem_address(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_address(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(done) : "r"(smem_address(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
+// global -> this CTA's shared memory; both addresses 16-byte aligned, bytes a multiple of 16
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_address(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_address(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 struct StepSmem {
   uint4* xs;            // STEP_MAX_K / 8 permuted activation chunks
   float* xsum;          // STEP_MAX_K / 64
-  float* csum;          // STEP_MAX_K / 8
   float* part;          // STEP_MAX_ITEMS * 16
   float* red;           // 64
   int* flag;            // 4
-  unsigned char* tile;  // attention tiles, scores, row values
+  unsigned long long* bars;  // RING_SLOTS mbarriers
+  uint32_t* ring_uses;       // completed phases of every ring slot
+  unsigned char* tile;  // attention tiles, scores, row values; or the weight ring of a GEMV stage
 };
 
 // A CTA gave up: remember where, once.
@@ -173,7 +198,53 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
       }
     }
   };
-  if (warp_mode) load_owned(warp, 0);
+  // Warp mode over small tiles (K <= 896: the LM head of the 0.5B shape) streams whole tiles
+  // through a ring in shared memory instead: a tile's 16 packed rows are one contiguous run of
+  // global memory, and so are its scales, so two bulk copies fetch a tile. Every warp owns two
+  // ring slots and keeps both in flight, which is what a single batch of register loads per warp
+  // cannot do.
+  const bool ring_mode = warp_mode && rp.mats == 1 && (N & 15) == 0 && 17 * K <= 2 * RING_SLOT_BYTES &&
+                         ((reinterpret_cast<uintptr_t>(st.packed) | reinterpret_cast<uintptr_t>(st.scales)) & 15) == 0;
+  unsigned char* my_ring = sm.tile + (size_t)warp * 2 * RING_SLOT_BYTES;
+  unsigned long long* my_bars = sm.bars + warp * 2;
+  uint32_t ring_uses[2] = {0u, 0u};
+  bool ring_pending[2] = {false, false};
+  auto ring_issue = [&](int local_tile, int slot) {
+    ring_pending[slot] = true;
+    if (lane == 0) {
+      const int tile = blockIdx.x + local_tile * gridDim.x;
+      const uint32_t weight_bytes = 16u * (uint32_t)(K >> 1), scale_bytes = 16u * (uint32_t)(K >> 5);
+      unsigned char* dst = my_ring + (size_t)slot * RING_SLOT_BYTES;
+      fence_async_proxy();  // earlier reads and writes of this slot come before the copy
+      mbar_expect_tx(my_bars + slot, weight_bytes + scale_bytes);
+      bulk_load(dst, reinterpret_cast<const unsigned char*>(st.packed) + (size_t)tile * weight_bytes, weight_bytes, my_bars + slot);
+      bulk_load(dst + weight_bytes, reinterpret_cast<const unsigned char*>(st.scales) + (size_t)tile * scale_bytes, scale_bytes, my_bars + slot);
+    }
+  };
+  // Bounded wait for a slot's copies; false if they never landed.
+  auto ring_wait = [&](int slot) {
+    const uint32_t parity = ring_uses[slot] & 1u;
+    int spins = 0;
+    while (!mbar_try_wait(my_bars + slot, parity))
+      if (++spins > POLL_LIMIT) return false;
+    ring_uses[slot] += 1u;
+    ring_pending[slot] = false;
+    return true;
+  };
+  // Leave nothing in flight into this CTA's shared memory (used on the way out after a failure).
+  auto ring_drain = [&]() {
+    bool ok = true;
+    for (int slot = 0; slot < 2; ++slot)
+      if (ring_pending[slot]) ok = ring_wait(slot) && ok;
+    if (lane == 0) { sm.ring_uses[warp * 2] = ring_uses[0]; sm.ring_uses[warp * 2 + 1] = ring_uses[1]; }
+    return ok;
+  };
+  if (ring_mode) {
+    ring_uses[0] = sm.ring_uses[warp * 2];
+    ring_uses[1] = sm.ring_uses[warp * 2 + 1];
+    if (warp < rp.my_tiles) ring_issue(warp, 0);
+    if (warp + STEP_WARPS < rp.my_tiles) ring_issue(warp + STEP_WARPS, 1);
+  } else if (warp_mode) load_owned(warp, 0);
   else if (rounds > 0) load_batch(0, 0);
 
   long long gather_row = 0;
@@ -240,7 +311,7 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
         }
       }
       if (__syncthreads_and(ready)) break;
-      if (++polls > POLL_LIMIT) { give_up(ctl, stage_index); return false; }
+      if (++polls > POLL_LIMIT) { ring_drain(); give_up(ctl, stage_index); return false; }
     }
   }
   trace_mark(ctl, stage_index, 1);
@@ -253,6 +324,7 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < MAXC; ++i) {
+      if (i * STEP_THREADS >= chunks) break;
       const int c = tid + i * STEP_THREADS;
       if (c < chunks) {
         float f[8];
@@ -274,6 +346,7 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
   // i.e. eight consecutive lanes) with three shuffles.
 #pragma unroll
   for (int i = 0; i < MAXC; ++i) {
+    if (i * STEP_THREADS >= chunks) break;  // uniform: short rows use the first slices only
     const int c = tid + i * STEP_THREADS;
     float chunk_sum = 0.f;
     if (c < chunks) {
@@ -307,7 +380,76 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
   int best_i = 0x7fffffff;
   int polls = 0;
 
-  if (warp_mode) {
+  // Epilogue and store of one warp-owned tile: lane (g, t = 0) holds rows g and g + 8.
+  auto finish_tile = [&](int tile, float gate_lo, float gate_hi, float up_lo, float up_hi) {
+    uint32_t bits[2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int n = tile * 16 + g + half * 8;
+      float y = st.alpha * (half ? gate_hi : gate_lo);
+      if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN && n < N)
+        y = fmaf(st.beta, __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[n]), y);
+      if (st.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED) {
+        const float gate = round_bf16(y);
+        y = (st.alpha * (half ? up_hi : up_lo)) * (gate / (1.f + expf(-gate)));
+      }
+      bits[half] = float_to_bf16_bits(y);
+    }
+    const uint32_t next_lo = __shfl_down_sync(0xffffffffu, bits[0], 4);
+    const uint32_t next_hi = __shfl_down_sync(0xffffffffu, bits[1], 4);
+    if (t == 0) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int n = tile * 16 + g + half * 8;
+        if (n >= N) continue;
+        if (st.flags & AOTO_STAGE_FLAG_OUT_PLAIN) {
+          out_plain[n] = __ushort_as_bfloat16((unsigned short)bits[half]);
+        } else if ((g & 1) == 0) {
+          st_stamped(out_words + (size_t)(n >> 1) * 8, bits[half] | ((half ? next_hi : next_lo) << 16), epoch);
+        }
+        if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
+          float v = __uint_as_float(bits[half] << 16);
+          if (v != v) v = INFINITY;
+          if (v > best_v || (v == best_v && n < best_i)) { best_v = v; best_i = n; }
+        }
+      }
+    }
+  };
+
+  if (ring_mode) {
+    const int row_u4 = K >> 5;    // 16-byte words of a packed row
+    const int scale_row = K >> 5;  // bytes of a row of scales
+    bool ring_ok = true;
+    bool marked = false;
+    int use = 0;
+    for (int local_tile = warp; local_tile < rp.my_tiles; local_tile += STEP_WARPS, ++use) {
+      const int slot = use & 1;
+      if (!ring_wait(slot)) { ring_ok = false; break; }
+      const unsigned char* base = my_ring + (size_t)slot * RING_SLOT_BYTES;
+      const uint4* wsm = reinterpret_cast<const uint4*>(base);
+      const unsigned char* ssm = base + 16 * (K >> 1);
+      float a_lo = 0.f, a_hi = 0.f;
+#pragma unroll 2
+      for (int kb = 0; kb < rp.nblocks; ++kb) {
+        WeightItem it;
+        it.lo = wsm[g * row_u4 + kb * 4 + t];
+        it.hi = wsm[(g + 8) * row_u4 + kb * 4 + t];
+        it.slo = *reinterpret_cast<const uint32_t*>(ssm + g * scale_row + kb * 4);
+        it.shi = *reinterpret_cast<const uint32_t*>(ssm + (g + 8) * scale_row + kb * 4);
+        float lo, hi;
+        mma_block(it, bs, kb, sm.xsum, lo, hi);
+        a_lo += lo;
+        a_hi += hi;
+      }
+      if (!marked) { trace_mark(ctl, stage_index, 3); marked = true; }
+      __syncwarp();  // every lane is done with the slot before it is refilled
+      if (local_tile + 2 * STEP_WARPS < rp.my_tiles) ring_issue(local_tile + 2 * STEP_WARPS, slot);
+      finish_tile(blockIdx.x + local_tile * gridDim.x, a_lo, a_hi, 0.f, 0.f);
+    }
+    if (!ring_ok) ring_drain();
+    if (lane == 0) { sm.ring_uses[warp * 2] = ring_uses[0]; sm.ring_uses[warp * 2 + 1] = ring_uses[1]; }
+    if (__syncthreads_or(!ring_ok)) { give_up(ctl, stage_index); return false; }
+  } else if (warp_mode) {
     float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     int local_tile = warp, first_item = 0;
     bool marked = false;
@@ -327,39 +469,7 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
       if (tile_done) { local_tile += STEP_WARPS; first_item = 0; }
       load_owned(local_tile, first_item);  // the next batch is in flight while this tile is finished
       if (tile_done) {
-        const int tile = blockIdx.x + done_tile * gridDim.x;
-        uint32_t bits[2];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int n = tile * 16 + g + half * 8;
-          float y = st.alpha * acc[0][half];
-          if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN && n < N)
-            y = fmaf(st.beta, __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[n]), y);
-          if (st.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED) {
-            const float gate = round_bf16(y);
-            y = (st.alpha * acc[1][half]) * (gate / (1.f + expf(-gate)));
-          }
-          bits[half] = float_to_bf16_bits(y);
-        }
-        const uint32_t next_lo = __shfl_down_sync(0xffffffffu, bits[0], 4);
-        const uint32_t next_hi = __shfl_down_sync(0xffffffffu, bits[1], 4);
-        if (t == 0) {
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const int n = tile * 16 + g + half * 8;
-            if (n >= N) continue;
-            if (st.flags & AOTO_STAGE_FLAG_OUT_PLAIN) {
-              out_plain[n] = __ushort_as_bfloat16((unsigned short)bits[half]);
-            } else if ((g & 1) == 0) {
-              st_stamped(out_words + (size_t)(n >> 1) * 8, bits[half] | ((half ? next_hi : next_lo) << 16), epoch);
-            }
-            if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
-              float v = __uint_as_float(bits[half] << 16);
-              if (v != v) v = INFINITY;
-              if (v > best_v || (v == best_v && n < best_i)) { best_v = v; best_i = n; }
-            }
-          }
-        }
+        finish_tile(blockIdx.x + done_tile * gridDim.x, acc[0][0], acc[0][1], acc[1][0], acc[1][1]);
         acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = 0.f;
       }
     }
@@ -793,12 +903,17 @@ decode_step_kernel(const aoto_step_stage* __restrict__ stages, int stage_count, 
   StepSmem sm;
   sm.xs = smem_raw;
   sm.xsum = reinterpret_cast<float*>(sm.xs + STEP_MAX_K / 8);
-  sm.csum = sm.xsum + STEP_MAX_K / 64;
-  sm.part = sm.csum + STEP_MAX_K / 8;
+  sm.part = sm.xsum + STEP_MAX_K / 64;
   sm.red = sm.part + STEP_MAX_ITEMS * 16;
   sm.flag = reinterpret_cast<int*>(sm.red + 64);
-  sm.tile = reinterpret_cast<unsigned char*>(sm.flag + 8);
-  if (threadIdx.x == 0) *(reinterpret_cast<uint4*>(sm.flag) + 1) = make_uint4(0u, 0u, 0u, 0u);
+  sm.bars = reinterpret_cast<unsigned long long*>(sm.flag + 8);
+  sm.ring_uses = reinterpret_cast<uint32_t*>(sm.bars + RING_SLOTS);
+  sm.tile = reinterpret_cast<unsigned char*>(sm.ring_uses + RING_SLOTS);
+  if (threadIdx.x == 0) {
+    *(reinterpret_cast<uint4*>(sm.flag) + 1) = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = 0; i < RING_SLOTS; ++i) { mbar_init(sm.bars + i, 1); sm.ring_uses[i] = 0u; }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
 
   // Stage descriptors are double buffered: the next one is requested while the current
   // stage runs, so a stage never starts with a round trip for its own description.
@@ -822,12 +937,13 @@ decode_step_kernel(const aoto_step_stage* __restrict__ stages, int stage_count, 
 }
 
 static size_t step_smem_bytes() {
-  const size_t fixed = (size_t)STEP_MAX_K / 8 * 16 + (size_t)STEP_MAX_K / 64 * 4 + (size_t)STEP_MAX_K / 8 * 4 +
-                       (size_t)STEP_MAX_ITEMS * 16 * 4 + 64 * 4 + 32;
+  const size_t fixed = (size_t)STEP_MAX_K / 8 * 16 + (size_t)STEP_MAX_K / 64 * 4 +
+                       (size_t)STEP_MAX_ITEMS * 16 * 4 + 64 * 4 + 32 + (size_t)RING_SLOTS * (8 + 4);
   const size_t attention = (size_t)2 * ATT_TILE * (128 * 2 + 16) +
                            ((size_t)(MAX_GROUP + 2) * 128 + (size_t)MAX_GROUP * 128 + (size_t)MAX_GROUP * ATT_TILE +
                             (size_t)MAX_GROUP * 2 + ATT_TILE + (size_t)2 * MAX_GROUP * 128) * 4;
-  return fixed + attention;
+  const size_t ring = (size_t)RING_SLOTS * RING_SLOT_BYTES;
+  return fixed + (attention > ring ? attention : ring);
 }
 
 static int check_stage(const aoto_step_stage& st) {

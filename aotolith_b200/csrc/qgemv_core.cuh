@@ -139,15 +139,19 @@ __device__ __forceinline__ void mma_block(const WeightItem& it, const BSource& b
                                           const float* xsum, float& lo, float& hi) {
   const uint4* bp = bs.base + kb * 16 * bs.stride;
   const float2 off = *reinterpret_cast<const float2*>(xsum + kb * 2);
+  // two accumulator tiles, so that the eight mma form two dependent chains of four
   float c[4] = {-off.x, -off.y, -off.x, -off.y};
+  float d[4] = {0.f, 0.f, 0.f, 0.f};
   const uint32_t wl[4] = {it.lo.x, it.lo.y, it.lo.z, it.lo.w};
   const uint32_t wh[4] = {it.hi.x, it.hi.y, it.hi.z, it.hi.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const uint4 b = bp[j * bs.stride];
     mma_16816(c, AOTO_NIB(wl[j], 0), AOTO_NIB(wh[j], 0), AOTO_NIB(wl[j], 4), AOTO_NIB(wh[j], 4), b.x, b.y);
-    mma_16816(c, AOTO_NIB(wl[j], 8), AOTO_NIB(wh[j], 8), AOTO_NIB(wl[j], 12), AOTO_NIB(wh[j], 12), b.z, b.w);
+    mma_16816(d, AOTO_NIB(wl[j], 8), AOTO_NIB(wh[j], 8), AOTO_NIB(wl[j], 12), AOTO_NIB(wh[j], 12), b.z, b.w);
   }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) c[i] += d[i];
   lo = fmaf(bf16x2_lo(it.slo), c[0], bf16x2_hi(it.slo) * c[1]);
   hi = fmaf(bf16x2_lo(it.shi), c[2], bf16x2_hi(it.shi) * c[3]);
 }
