@@ -37,6 +37,19 @@ __device__ __forceinline__ uint4 ldg_nc_u4(const void* ptr) {
   return v;
 }
 
+// Read-only loads the compiler must issue where they are written (it is free to sink an
+// ordinary load to its first use, which turns a prefetch into an exposed miss).
+__device__ __forceinline__ uint32_t ldg_nc_u32(const void* ptr) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(ptr));
+  return v;
+}
+__device__ __forceinline__ float ldg_nc_bf16(const __nv_bfloat16* ptr) {
+  unsigned short raw;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(raw) : "l"(ptr));
+  return __uint_as_float(((uint32_t)raw) << 16);
+}
+
 // 16-bit load that bypasses L1 (L1 is not coherent across SMs: values another CTA
 // wrote during the same kernel must come from L2).
 __device__ __forceinline__ float ldcg_bf16(const __nv_bfloat16* ptr) {

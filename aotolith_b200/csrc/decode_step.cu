@@ -21,7 +21,8 @@ constexpr int STEP_THREADS = 256;
 constexpr int STEP_WARPS = STEP_THREADS / 32;
 constexpr int STEP_MAX_K = 16384;      // activation row staged in shared memory
 constexpr int STEP_MAX_ITEMS = 256;    // (tile, block) items of one round
-constexpr int STEP_BATCH = 8;          // items a warp holds in registers at once
+constexpr int STEP_BATCH = 4;          // items a warp holds in registers at once
+constexpr int POLL_SLICES = 3;         // 32-byte chunks of the input row a thread polls at once
 constexpr int POLL_LIMIT = 1 << 20;    // rounds of a bounded poll (each is >= one L2 round trip)
 constexpr int ATT_TILE = 64;           // keys per attention item
 constexpr int MAX_GROUP = 16;          // query heads per kv head
@@ -90,6 +91,7 @@ __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.
 
 struct StepSmem {
   uint4* xs;            // STEP_MAX_K / 8 permuted activation chunks
+  uint4* nw;            // STEP_MAX_K / 8 chunks of the norm weight
   float* xsum;          // STEP_MAX_K / 64
   float* part;          // STEP_MAX_ITEMS * 16
   float* red;           // 64
@@ -151,8 +153,8 @@ __device__ __forceinline__ void load_item(const aoto_step_stage& st, int tile, i
   const bf16* sc = reinterpret_cast<const bf16*>(mat == 0 ? st.scales : st.scales2);
   it->lo = ldg_nc_u4(wq + (size_t)rlo * row_u4 + kb * 4 + t);
   it->hi = ldg_nc_u4(wq + (size_t)rhi * row_u4 + kb * 4 + t);
-  it->slo = __ldg(reinterpret_cast<const uint32_t*>(sc + (size_t)rlo * row_sc + kb * 2));
-  it->shi = __ldg(reinterpret_cast<const uint32_t*>(sc + (size_t)rhi * row_sc + kb * 2));
+  it->slo = ldg_nc_u32(sc + (size_t)rlo * row_sc + kb * 2);
+  it->shi = ldg_nc_u32(sc + (size_t)rhi * row_sc + kb * 2);
 }
 
 // Returns false when a poll ran out (the caller leaves the kernel).
@@ -180,30 +182,14 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
       if (it_ok[b]) load_item(st, tile, mat, kb, g, t, &items[b]);
     }
   };
-  // A stage with many tiles per CTA and few k blocks per tile (the LM head) runs "warp mode":
-  // every warp owns whole tiles, accumulates in registers and stores its rows itself, so the
-  // warps stream independently with no CTA-wide synchronisation between tiles.
-  const bool warp_mode = rp.per_tile <= 16 && rp.my_tiles >= STEP_WARPS &&
-                         st.addend_mode <= AOTO_STAGE_ADDEND_PLAIN;
-  auto load_owned = [&](int local_tile, int first_item) {
-#pragma unroll
-    for (int b = 0; b < STEP_BATCH; ++b) {
-      const int i = first_item + b;
-      it_ok[b] = local_tile < rp.my_tiles && i < rp.per_tile;
-      if (it_ok[b]) {
-        const int mat = small_div(i, rp.inv_nblocks), kb = i - mat * rp.nblocks;
-        it_kb[b] = kb;
-        it_q[b] = mat;
-        load_item(st, blockIdx.x + local_tile * gridDim.x, mat, kb, g, t, &items[b]);
-      }
-    }
-  };
-  // Warp mode over small tiles (K <= 896: the LM head of the 0.5B shape) streams whole tiles
-  // through a ring in shared memory instead: a tile's 16 packed rows are one contiguous run of
-  // global memory, and so are its scales, so two bulk copies fetch a tile. Every warp owns two
-  // ring slots and keeps both in flight, which is what a single batch of register loads per warp
-  // cannot do.
-  const bool ring_mode = warp_mode && rp.mats == 1 && (N & 15) == 0 && 17 * K <= 2 * RING_SLOT_BYTES &&
+  // A stage with many small tiles per CTA (K <= 896 and no second matrix: the LM head of the 0.5B
+  // shape) runs in "ring mode": every warp owns whole tiles and streams them through a ring in
+  // shared memory. A tile's 16 packed rows are one contiguous run of global memory, and so are
+  // its scales, so two bulk copies fetch a tile; every warp owns two ring slots and keeps both
+  // in flight, accumulates in registers and stores its rows itself, with no CTA-wide
+  // synchronisation between tiles.
+  const bool ring_mode = rp.my_tiles >= STEP_WARPS && st.addend_mode <= AOTO_STAGE_ADDEND_PLAIN &&
+                         rp.mats == 1 && (N & 15) == 0 && 17 * K <= 2 * RING_SLOT_BYTES &&
                          ((reinterpret_cast<uintptr_t>(st.packed) | reinterpret_cast<uintptr_t>(st.scales)) & 15) == 0;
   unsigned char* my_ring = sm.tile + (size_t)warp * 2 * RING_SLOT_BYTES;
   unsigned long long* my_bars = sm.bars + warp * 2;
@@ -244,8 +230,9 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
     ring_uses[1] = sm.ring_uses[warp * 2 + 1];
     if (warp < rp.my_tiles) ring_issue(warp, 0);
     if (warp + STEP_WARPS < rp.my_tiles) ring_issue(warp + STEP_WARPS, 1);
-  } else if (warp_mode) load_owned(warp, 0);
-  else if (rounds > 0) load_batch(0, 0);
+  } else if (rounds > 0) {
+    load_batch(0, 0);
+  }
 
   long long gather_row = 0;
   if (st.x_index != nullptr) {
@@ -263,55 +250,65 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
     const int n0 = (blockIdx.x + tl0 * gridDim.x) * 16 + r0;
     if (tl0 < tiles0 && n0 < N) {
       if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN) {
-        addend0 = __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[n0]);
+        addend0 = ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + n0);
       } else if (st.addend_mode == AOTO_STAGE_ADDEND_GATHER) {
-        addend0 = __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[(size_t)gather_row * N + n0]);
+        addend0 = ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + (size_t)gather_row * N + n0);
       } else if (st.addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
         addend0_word = ld_stamped(reinterpret_cast<const unsigned char*>(st.addend) + (size_t)(n0 >> 1) * 8);
       }
     }
   }
 
-  // ---- input row: gather it, or poll its stamped words ----
+  // ---- input row: gather it, or poll its stamped words; raw chunks go to shared memory ----
   const int chunks = K >> 3;
   const uint4* wv = reinterpret_cast<const uint4*>(st.norm_weight);
-  constexpr int MAXC = STEP_MAX_K / 8 / STEP_THREADS;
-  uint4 xr[MAXC], wr[MAXC];
-#pragma unroll
-  for (int i = 0; i < MAXC; ++i) {
-    const int c = tid + i * STEP_THREADS;
-    if (c < chunks && wv != nullptr) wr[i] = __ldg(wv + c);
+  if (wv != nullptr) {
+    for (int c = tid; c < chunks; c += STEP_THREADS) cp_async_16_cg(sm.nw + c, wv + c);
+    asm volatile("cp.async.commit_group;" ::: "memory");
   }
+  float ss = 0.f;
+  auto keep_chunk = [&](int c, const uint4 v) {
+    sm.xs[c] = v;
+    if (wv != nullptr) {
+      float f[8];
+      unpack8(v, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+    }
+  };
   if (st.flags & AOTO_STAGE_FLAG_X_GATHER) {
     const uint4* xrow = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(st.x) + (size_t)gather_row * K);
-#pragma unroll
-    for (int i = 0; i < MAXC; ++i) {
-      const int c = tid + i * STEP_THREADS;
-      if (c < chunks) xr[i] = __ldg(xrow + c);
-    }
+    for (int c = tid; c < chunks; c += STEP_THREADS) keep_chunk(c, ldg_nc_u4(xrow + c));
   } else {
     const unsigned char* xw = reinterpret_cast<const unsigned char*>(st.x);
-    bool done[MAXC];
-#pragma unroll
-    for (int i = 0; i < MAXC; ++i) done[i] = (tid + i * STEP_THREADS) >= chunks;
     int polls = 0;
-    while (true) {
-      bool ready = true;
+    for (int base = 0; base < chunks; base += POLL_SLICES * STEP_THREADS) {
+      bool done[POLL_SLICES];
 #pragma unroll
-      for (int i = 0; i < MAXC; ++i) {
-        if (done[i]) continue;
-        const int c = tid + i * STEP_THREADS;
-        const uint4 a = ld_stamped_pair(xw + (size_t)c * 32);
-        const uint4 b = ld_stamped_pair(xw + (size_t)c * 32 + 16);
-        if (a.y == epoch && a.w == epoch && b.y == epoch && b.w == epoch) {
-          xr[i] = make_uint4(a.x, a.z, b.x, b.z);
-          done[i] = true;
-        } else {
-          ready = false;
+      for (int i = 0; i < POLL_SLICES; ++i) done[i] = (base + tid + i * STEP_THREADS) >= chunks;
+      while (true) {
+        bool ready = true;
+        uint4 a[POLL_SLICES], b[POLL_SLICES];
+#pragma unroll
+        for (int i = 0; i < POLL_SLICES; ++i) {
+          if (done[i]) continue;
+          const int c = base + tid + i * STEP_THREADS;
+          a[i] = ld_stamped_pair(xw + (size_t)c * 32);
+          b[i] = ld_stamped_pair(xw + (size_t)c * 32 + 16);
         }
+#pragma unroll
+        for (int i = 0; i < POLL_SLICES; ++i) {
+          if (done[i]) continue;
+          if (a[i].y == epoch && a[i].w == epoch && b[i].y == epoch && b[i].w == epoch) {
+            keep_chunk(base + tid + i * STEP_THREADS, make_uint4(a[i].x, a[i].z, b[i].x, b[i].z));
+            done[i] = true;
+          } else {
+            ready = false;
+          }
+        }
+        if (__syncthreads_and(ready)) break;
+        if (++polls > POLL_LIMIT) { ring_drain(); give_up(ctl, stage_index); return false; }
       }
-      if (__syncthreads_and(ready)) break;
-      if (++polls > POLL_LIMIT) { ring_drain(); give_up(ctl, stage_index); return false; }
     }
   }
   trace_mark(ctl, stage_index, 1);
@@ -321,40 +318,28 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
   // to protect it from the previous stage's readers.
   float inv = 1.f;
   if (wv != nullptr) {
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < MAXC; ++i) {
-      if (i * STEP_THREADS >= chunks) break;
-      const int c = tid + i * STEP_THREADS;
-      if (c < chunks) {
-        float f[8];
-        unpack8(xr[i], f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
-      }
-    }
     ss = warp_sum(ss);
     float* slot = sm.red + (stage_index & 1) * 32;
     if (lane == 0) slot[warp] = ss;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     float total = 0.f;
 #pragma unroll
     for (int w = 0; w < STEP_WARPS; ++w) total += slot[w];
     inv = rsqrtf(total / (float)K + st.rms_norm_eps);
   }
-  // Normalise, store in fragment order, and sum each group of 64 (eight consecutive chunks,
-  // i.e. eight consecutive lanes) with three shuffles.
-#pragma unroll
-  for (int i = 0; i < MAXC; ++i) {
-    if (i * STEP_THREADS >= chunks) break;  // uniform: short rows use the first slices only
-    const int c = tid + i * STEP_THREADS;
+  // Normalise, store in fragment order (in place: a thread rewrites the chunks it wrote), and
+  // sum each group of 64 (eight consecutive chunks, i.e. eight consecutive lanes) with three
+  // shuffles.
+  for (int base = 0; base < chunks; base += STEP_THREADS) {
+    const int c = base + tid;
     float chunk_sum = 0.f;
     if (c < chunks) {
       float f[8];
-      unpack8(xr[i], f);
+      unpack8(sm.xs[c], f);
       if (wv != nullptr) {
         float w[8];
-        unpack8(wr[i], w);
+        unpack8(sm.nw[c], w);
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = round_bf16((f[j] * inv) * w[j]);
       }
@@ -449,34 +434,9 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
     if (!ring_ok) ring_drain();
     if (lane == 0) { sm.ring_uses[warp * 2] = ring_uses[0]; sm.ring_uses[warp * 2 + 1] = ring_uses[1]; }
     if (__syncthreads_or(!ring_ok)) { give_up(ctl, stage_index); return false; }
-  } else if (warp_mode) {
-    float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-    int local_tile = warp, first_item = 0;
-    bool marked = false;
-    while (local_tile < rp.my_tiles) {
-#pragma unroll
-      for (int b = 0; b < STEP_BATCH; ++b) {
-        if (!it_ok[b]) continue;
-        float lo, hi;
-        mma_block(items[b], bs, it_kb[b], sm.xsum, lo, hi);
-        if (it_q[b] == 0) { acc[0][0] += lo; acc[0][1] += hi; }
-        else { acc[1][0] += lo; acc[1][1] += hi; }
-      }
-      if (!marked) { trace_mark(ctl, stage_index, 3); marked = true; }
-      const int done_tile = local_tile;
-      first_item += STEP_BATCH;
-      const bool tile_done = first_item >= rp.per_tile;
-      if (tile_done) { local_tile += STEP_WARPS; first_item = 0; }
-      load_owned(local_tile, first_item);  // the next batch is in flight while this tile is finished
-      if (tile_done) {
-        finish_tile(blockIdx.x + done_tile * gridDim.x, acc[0][0], acc[0][1], acc[1][0], acc[1][1]);
-        acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = 0.f;
-      }
-    }
-    __syncthreads();
   }
 
-  for (int round = 0; round < (warp_mode ? 0 : rounds); ++round) {
+  for (int round = 0; round < (ring_mode ? 0 : rounds); ++round) {
     const int tiles_here = min(rp.tiles_per_round, rp.my_tiles - round * rp.tiles_per_round);
     const int items_in_round = tiles_here * rp.per_tile;
     const int per_warp = (items_in_round + STEP_WARPS - 1) / STEP_WARPS;
@@ -525,10 +485,18 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
     float y = 0.f;
     if (valid) {
       const float* p0 = sm.part + (tl * rp.per_tile) * 16 + r;
-      float total = 0.f, total2 = 0.f;
-      for (int kb = 0; kb < rp.nblocks; ++kb) total += p0[kb * 16];
-      if (rp.mats == 2)
-        for (int kb = 0; kb < rp.nblocks; ++kb) total2 += p0[(rp.nblocks + kb) * 16];
+      // fixed order: four interleaved partial sums over the k blocks, then their sum
+      auto sum_blocks = [&](const float* q) {
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        int kb = 0;
+        for (; kb + 4 <= rp.nblocks; kb += 4) {
+          s0 += q[kb * 16]; s1 += q[(kb + 1) * 16]; s2 += q[(kb + 2) * 16]; s3 += q[(kb + 3) * 16];
+        }
+        for (; kb < rp.nblocks; ++kb) s0 += q[kb * 16];
+        return (s0 + s1) + (s2 + s3);
+      };
+      const float total = sum_blocks(p0);
+      const float total2 = rp.mats == 2 ? sum_blocks(p0 + rp.nblocks * 16) : 0.f;
       y = st.alpha * total;
       if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN) {
         const float a = round == 0 ? addend0 : __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[n]);
@@ -902,7 +870,8 @@ decode_step_kernel(const aoto_step_stage* __restrict__ stages, int stage_count, 
   __shared__ aoto_step_stage stage_buffer[2];
   StepSmem sm;
   sm.xs = smem_raw;
-  sm.xsum = reinterpret_cast<float*>(sm.xs + STEP_MAX_K / 8);
+  sm.nw = sm.xs + STEP_MAX_K / 8;
+  sm.xsum = reinterpret_cast<float*>(sm.nw + STEP_MAX_K / 8);
   sm.part = sm.xsum + STEP_MAX_K / 64;
   sm.red = sm.part + STEP_MAX_ITEMS * 16;
   sm.flag = reinterpret_cast<int*>(sm.red + 64);
@@ -919,12 +888,12 @@ decode_step_kernel(const aoto_step_stage* __restrict__ stages, int stage_count, 
   // stage runs, so a stage never starts with a round trip for its own description.
   constexpr int WORDS = sizeof(aoto_step_stage) / 4;
   if (threadIdx.x < WORDS)
-    reinterpret_cast<uint32_t*>(&stage_buffer[0])[threadIdx.x] = __ldg(reinterpret_cast<const uint32_t*>(stages) + threadIdx.x);
+    reinterpret_cast<uint32_t*>(&stage_buffer[0])[threadIdx.x] = ldg_nc_u32(reinterpret_cast<const uint32_t*>(stages) + threadIdx.x);
   __syncthreads();
   for (int s = 0; s < stage_count; ++s) {
     uint32_t next_word = 0;
     if (threadIdx.x < WORDS && s + 1 < stage_count)
-      next_word = __ldg(reinterpret_cast<const uint32_t*>(stages + s + 1) + threadIdx.x);
+      next_word = ldg_nc_u32(reinterpret_cast<const uint32_t*>(stages + s + 1) + threadIdx.x);
     const aoto_step_stage& stage = stage_buffer[s & 1];
     bool alive = true;
     if (stage.kind == AOTO_STAGE_GEMV) alive = stage_gemv(stage, sm, ctl, s);
@@ -937,7 +906,7 @@ decode_step_kernel(const aoto_step_stage* __restrict__ stages, int stage_count, 
 }
 
 static size_t step_smem_bytes() {
-  const size_t fixed = (size_t)STEP_MAX_K / 8 * 16 + (size_t)STEP_MAX_K / 64 * 4 +
+  const size_t fixed = (size_t)STEP_MAX_K / 8 * 16 * 2 + (size_t)STEP_MAX_K / 64 * 4 +
                        (size_t)STEP_MAX_ITEMS * 16 * 4 + 64 * 4 + 32 + (size_t)RING_SLOTS * (8 + 4);
   const size_t attention = (size_t)2 * ATT_TILE * (128 * 2 + 16) +
                            ((size_t)(MAX_GROUP + 2) * 128 + (size_t)MAX_GROUP * 128 + (size_t)MAX_GROUP * ATT_TILE +
