@@ -163,6 +163,7 @@ EXPORTS: dict[str, tuple] = {
     "aoto_sm100_qmatmul_supported": (c_int, [POINTER(QMatmulArgs)]),
     "aoto_sm100_qmatmul_scratch_bytes": (c_int64, [POINTER(QMatmulArgs)]),
     "aoto_sm100_qmatmul_variant": (c_char_p, [POINTER(QMatmulArgs)]),
+    "aoto_sm100_qmatmul_take_timeout_flag": (c_int, []),
     "aoto_sm100_dequantize_i4": (c_int, [POINTER(DequantizeArgs), c_void_p]),
     "aoto_sm100_rms_norm": (c_int, [POINTER(RmsNormArgs), c_void_p]),
     "aoto_sm100_rope": (c_int, [POINTER(RopeArgs), c_void_p]),

@@ -27,7 +27,8 @@ constexpr int POLL_LIMIT = 1 << 20;    // rounds of a bounded poll (each is >= o
 constexpr int ATT_TILE = 64;           // keys per attention item
 constexpr int MAX_GROUP = 16;          // query heads per kv head
 constexpr int RING_SLOT_BYTES = 7680;  // one 16-row weight tile with its scales (K <= 896)
-constexpr int RING_SLOTS = 2 * STEP_WARPS;
+constexpr int RING_DEPTH = STEP_WARPS <= 8 ? 2 : 1;  // ring slots a warp owns
+constexpr int RING_SLOTS = RING_DEPTH * STEP_WARPS;
 
 struct StepControl {
   uint32_t epoch;
@@ -191,10 +192,12 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
   const bool ring_mode = rp.my_tiles >= STEP_WARPS && st.addend_mode <= AOTO_STAGE_ADDEND_PLAIN &&
                          rp.mats == 1 && (N & 15) == 0 && 17 * K <= 2 * RING_SLOT_BYTES &&
                          ((reinterpret_cast<uintptr_t>(st.packed) | reinterpret_cast<uintptr_t>(st.scales)) & 15) == 0;
-  unsigned char* my_ring = sm.tile + (size_t)warp * 2 * RING_SLOT_BYTES;
-  unsigned long long* my_bars = sm.bars + warp * 2;
-  uint32_t ring_uses[2] = {0u, 0u};
-  bool ring_pending[2] = {false, false};
+  unsigned char* my_ring = sm.tile + (size_t)warp * RING_DEPTH * RING_SLOT_BYTES;
+  unsigned long long* my_bars = sm.bars + warp * RING_DEPTH;
+  uint32_t ring_uses[RING_DEPTH];
+  bool ring_pending[RING_DEPTH];
+#pragma unroll
+  for (int d = 0; d < RING_DEPTH; ++d) { ring_uses[d] = 0u; ring_pending[d] = false; }
   auto ring_issue = [&](int local_tile, int slot) {
     ring_pending[slot] = true;
     if (lane == 0) {
@@ -220,16 +223,21 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
   // Leave nothing in flight into this CTA's shared memory (used on the way out after a failure).
   auto ring_drain = [&]() {
     bool ok = true;
-    for (int slot = 0; slot < 2; ++slot)
+#pragma unroll
+    for (int slot = 0; slot < RING_DEPTH; ++slot)
       if (ring_pending[slot]) ok = ring_wait(slot) && ok;
-    if (lane == 0) { sm.ring_uses[warp * 2] = ring_uses[0]; sm.ring_uses[warp * 2 + 1] = ring_uses[1]; }
+    if (lane == 0) {
+#pragma unroll
+      for (int d = 0; d < RING_DEPTH; ++d) sm.ring_uses[warp * RING_DEPTH + d] = ring_uses[d];
+    }
     return ok;
   };
   if (ring_mode) {
-    ring_uses[0] = sm.ring_uses[warp * 2];
-    ring_uses[1] = sm.ring_uses[warp * 2 + 1];
-    if (warp < rp.my_tiles) ring_issue(warp, 0);
-    if (warp + STEP_WARPS < rp.my_tiles) ring_issue(warp + STEP_WARPS, 1);
+#pragma unroll
+    for (int d = 0; d < RING_DEPTH; ++d) {
+      ring_uses[d] = sm.ring_uses[warp * RING_DEPTH + d];
+      if (warp + d * STEP_WARPS < rp.my_tiles) ring_issue(warp + d * STEP_WARPS, d);
+    }
   } else if (rounds > 0) {
     load_batch(0, 0);
   }
@@ -408,7 +416,7 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
     bool marked = false;
     int use = 0;
     for (int local_tile = warp; local_tile < rp.my_tiles; local_tile += STEP_WARPS, ++use) {
-      const int slot = use & 1;
+      const int slot = use % RING_DEPTH;
       if (!ring_wait(slot)) { ring_ok = false; break; }
       const unsigned char* base = my_ring + (size_t)slot * RING_SLOT_BYTES;
       const uint4* wsm = reinterpret_cast<const uint4*>(base);
@@ -428,11 +436,14 @@ __device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const 
       }
       if (!marked) { trace_mark(ctl, stage_index, 3); marked = true; }
       __syncwarp();  // every lane is done with the slot before it is refilled
-      if (local_tile + 2 * STEP_WARPS < rp.my_tiles) ring_issue(local_tile + 2 * STEP_WARPS, slot);
+      if (local_tile + RING_DEPTH * STEP_WARPS < rp.my_tiles) ring_issue(local_tile + RING_DEPTH * STEP_WARPS, slot);
       finish_tile(blockIdx.x + local_tile * gridDim.x, a_lo, a_hi, 0.f, 0.f);
     }
     if (!ring_ok) ring_drain();
-    if (lane == 0) { sm.ring_uses[warp * 2] = ring_uses[0]; sm.ring_uses[warp * 2 + 1] = ring_uses[1]; }
+    if (lane == 0) {
+#pragma unroll
+      for (int d = 0; d < RING_DEPTH; ++d) sm.ring_uses[warp * RING_DEPTH + d] = ring_uses[d];
+    }
     if (__syncthreads_or(!ring_ok)) { give_up(ctl, stage_index); return false; }
   }
 

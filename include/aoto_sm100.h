@@ -99,6 +99,14 @@ typedef struct aoto_qmatmul_args {
 #define AOTO_FLAG_PDL 1 /* launch with programmatic dependent launch enabled */
 
 int aoto_sm100_qmatmul(const aoto_qmatmul_args* args, void* stream);
+/*
+ * The tensor-core variant (several activation rows) waits on hardware barriers with a bound; a
+ * wait that runs out sets a flag on the device and the kernel exits with its tile unwritten.
+ * This call returns that flag (1 = a wait ran out since the last call, 0 = none, -1 = the
+ * query itself failed) and clears it. It synchronises the device: a diagnostic, not part of a
+ * step. No counterpart in the reference.
+ */
+int aoto_sm100_qmatmul_take_timeout_flag(void);
 /* 1 if a native variant exists for these shapes/flags, 0 if not (pointers ignored). */
 int aoto_sm100_qmatmul_supported(const aoto_qmatmul_args* args);
 /* Bytes of scratch the split-K variant wants for this shape (0 = none needed). */

@@ -83,7 +83,7 @@ def test_qmatmul_queries_are_host_only():
     assert lib.aoto_sm100_qmatmul_supported(ctypes.byref(_qargs(0, 16, 128, 64))) == 0
     assert lib.aoto_sm100_qmatmul_supported(None) == 0
     assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(_qargs(1, 1152, 896, 64))) == b"qgemv_mma"
-    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(_qargs(128, 1152, 896, 64))) == b"gemm_mma"
+    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(_qargs(16, 1152, 896, 64))) == b"gemm_mma"
     assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(_qargs(1, 24, 64, 16))) == b"qgemv_generic"
     assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(_qargs(1, 1152, 896, 64))) == 0
     # null pointers are refused before anything reaches the CUDA runtime

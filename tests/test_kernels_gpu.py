@@ -141,7 +141,8 @@ def test_qgemv_paired_silu_mul(cuda, K, N):
 
 
 @pytest.mark.parametrize("M,K,N", [(2, 896, 1152), (16, 896, 1152), (128, 896, 1152), (200, 4864, 896),
-                                   (37, 896, 4864), (130, 256, 1000), (5, 64, 24)])
+                                   (37, 896, 4864), (130, 256, 1000), (5, 64, 24),
+                                   (64, 896, 896), (256, 4864, 896), (128, 64, 72)])
 def test_qmatmul_rows(cuda, M, K, N):
     """Several activation rows (prefill semantics: dequantise, then multiply)."""
 
@@ -151,7 +152,7 @@ def test_qmatmul_rows(cuda, M, K, N):
     x = activations(31, M, K)
     bias = activations(32, N, std=0.5)
     if K % 128 == 0:
-        assert ops.qmatmul_variant(M, N, K, group) == "gemm_mma"
+        assert ops.qmatmul_variant(M, N, K, group) == ("gemm_tcgen05" if M >= 64 else "gemm_mma")
     got = ops.qmatmul(x.to(cuda), packed.to(cuda), scales.to(cuda), group_size=group, addend=bias.to(cuda)).cpu()
     want = ref.packed_matmul(x, packed, scales, group, addend=bias)
     assert got.shape == (M, N)
@@ -165,6 +166,8 @@ def test_qmatmul_rows(cuda, M, K, N):
     got = ops.qmatmul(x.to(cuda), packed.to(cuda), scales.to(cuda), group_size=group, addend=resid.to(cuda)).cpu()
     want = ref.packed_matmul(x, packed, scales, group, addend=resid)
     assert rel_max_error(got, want) < ORACLE_TOL
+    from aotolith_b200 import _native
+    assert _native.load().aoto_sm100_qmatmul_take_timeout_flag() == 0
 
 
 def test_qmatmul_rows_match_single_rows(cuda):
