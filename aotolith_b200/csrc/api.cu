@@ -8,6 +8,8 @@ int qgemv_check(const aoto_qmatmul_args& a, bool pointers);
 const char* qgemv_variant(const aoto_qmatmul_args& a);
 bool qgemm_applies(const aoto_qmatmul_args& a);
 bool qgemm_tc_applies(const aoto_qmatmul_args& a);
+bool qgemv_stream_applies(const aoto_qmatmul_args& a);
+int qgemv_stream_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
 int qgemm_tc_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
 int qgemm_tc_take_timeout_flag();
 int qgemm_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
@@ -46,6 +48,7 @@ extern "C" int64_t aoto_sm100_qmatmul_scratch_bytes(const aoto_qmatmul_args* a) 
 extern "C" const char* aoto_sm100_qmatmul_variant(const aoto_qmatmul_args* a) {
   if (!a) return "none";
   if (qgemm_tc_applies(*a)) return "gemm_tcgen05";
+  if (qgemv_stream_applies(*a)) return "qgemv_stream";
   if (qgemm_applies(*a)) return "gemm_mma";
   return qgemv_variant(*a);
 }
@@ -55,6 +58,7 @@ extern "C" int aoto_sm100_qmatmul(const aoto_qmatmul_args* a, void* stream) {
   const int status = qgemv_check(*a, true);
   if (status != AOTO_OK) return status;
   if (qgemm_tc_applies(*a)) return qgemm_tc_launch(*a, (cudaStream_t)stream);
+  if (qgemv_stream_applies(*a)) return qgemv_stream_launch(*a, (cudaStream_t)stream);
   if (qgemm_applies(*a)) return qgemm_launch(*a, (cudaStream_t)stream);
   return qgemv_launch(*a, (cudaStream_t)stream);
 }

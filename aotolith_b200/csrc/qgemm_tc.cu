@@ -22,6 +22,7 @@ constexpr int TC_STAGES = 4;
 constexpr int TC_THREADS = 192;
 constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 2;  // 16 KiB: one operand tile of one stage
 constexpr int TC_WAIT_LIMIT = 1 << 20;
+constexpr int TC_AHEAD = 4;  // k blocks of packed words a dequantising thread keeps in flight
 constexpr size_t TC_SMEM_BYTES = 1024 + (size_t)2 * TC_STAGES * TC_TILE_BYTES + 256;
 
 struct TcParams {
@@ -190,23 +191,33 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
     const bool row_valid = n < p.N;
     const uint4* wq = reinterpret_cast<const uint4*>(p.w) + (size_t)(row_valid ? n : 0) * (p.K >> 5);
     const bf16* sc = p.s + (size_t)(row_valid ? n : 0) * (p.K >> 6);
-    uint4 q0 = make_uint4(0u, 0u, 0u, 0u), q1 = q0;
-    uint32_t scale_bits = 0;
-    if (row_valid && blocks > 0) {
-      q0 = ldg_nc_u4(wq);
-      q1 = ldg_nc_u4(wq + 1);
-      scale_bits = (uint32_t)__bfloat16_as_ushort(sc[0]);
-    }
-    for (int kb = 0; kb < blocks && ok; ++kb) {
+    // The packed words of the next TC_AHEAD k blocks are always in flight (a register ring with
+    // static slots: the loop below is unrolled by TC_AHEAD).
+    uint4 q0[TC_AHEAD], q1[TC_AHEAD];
+    uint32_t scale_bits[TC_AHEAD];
+    auto request = [&](int slot, int kb) {
+      q0[slot] = q1[slot] = make_uint4(0u, 0u, 0u, 0u);
+      scale_bits[slot] = 0u;
+      if (row_valid && kb < blocks) {
+        q0[slot] = ldg_nc_u4(wq + (size_t)kb * 2);
+        q1[slot] = ldg_nc_u4(wq + (size_t)kb * 2 + 1);
+        unsigned short raw;
+        asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(raw) : "l"(sc + kb));
+        scale_bits[slot] = raw;
+      }
+    };
+#pragma unroll
+    for (int a = 0; a < TC_AHEAD; ++a) request(a, a);
+    for (int kb0 = 0; kb0 < blocks && ok; kb0 += TC_AHEAD) {
+#pragma unroll
+      for (int a = 0; a < TC_AHEAD; ++a) {
+      const int kb = kb0 + a;
+      if (kb >= blocks || !ok) break;
       const int s = kb % TC_STAGES;
       const uint32_t round = (uint32_t)(kb / TC_STAGES);
-      const uint4 c0 = q0, c1 = q1;
-      const __nv_bfloat162 scale2 = __bfloat162bfloat162(__ushort_as_bfloat16((unsigned short)scale_bits));
-      if (row_valid && kb + 1 < blocks) {  // next block's codes travel while this one is converted
-        q0 = ldg_nc_u4(wq + (size_t)(kb + 1) * 2);
-        q1 = ldg_nc_u4(wq + (size_t)(kb + 1) * 2 + 1);
-        scale_bits = (uint32_t)__bfloat16_as_ushort(sc[kb + 1]);
-      }
+      const uint4 c0 = q0[a], c1 = q1[a];
+      const __nv_bfloat162 scale2 = __bfloat162bfloat162(__ushort_as_bfloat16((unsigned short)scale_bits[a]));
+      request(a, kb + TC_AHEAD);
       ok = tc_bar_wait(empty + s, (round & 1u) ^ 1u);
       if (!ok) break;
       unsigned char* row = tile_b + (size_t)s * TC_TILE_BYTES + (size_t)r * 128;
@@ -228,6 +239,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads through the async proxy
       tc_bar_arrive(full_b + s);
+      }
     }
 
     // epilogue: warp q of a warpgroup may read tensor-memory lanes 32q..32q+31

@@ -139,23 +139,17 @@ __device__ __forceinline__ void mma_block(const WeightItem& it, const BSource& b
                                           const float* xsum, float& lo, float& hi) {
   const uint4* bp = bs.base + kb * 16 * bs.stride;
   const float2 off = *reinterpret_cast<const float2*>(xsum + kb * 2);
-  // four accumulator tiles: the eight mma form four dependent chains of two
-  float acc[4][4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  // One accumulator tile for the eight mma: the kernels built on this are bound by the number of
+  // instructions they issue, not by the length of this chain (other warps fill its gaps).
+  float c[4] = {-off.x, -off.y, -off.x, -off.y};
   const uint32_t wl[4] = {it.lo.x, it.lo.y, it.lo.z, it.lo.w};
   const uint32_t wh[4] = {it.hi.x, it.hi.y, it.hi.z, it.hi.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const uint4 b = bp[j * bs.stride];
-    mma_16816(acc[j], AOTO_NIB(wl[j], 0), AOTO_NIB(wh[j], 0), AOTO_NIB(wl[j], 4), AOTO_NIB(wh[j], 4), b.x, b.y);
-    mma_16816(acc[j], AOTO_NIB(wl[j], 8), AOTO_NIB(wh[j], 8), AOTO_NIB(wl[j], 12), AOTO_NIB(wh[j], 12), b.z, b.w);
+    mma_16816(c, AOTO_NIB(wl[j], 0), AOTO_NIB(wh[j], 0), AOTO_NIB(wl[j], 4), AOTO_NIB(wh[j], 4), b.x, b.y);
+    mma_16816(c, AOTO_NIB(wl[j], 8), AOTO_NIB(wh[j], 8), AOTO_NIB(wl[j], 12), AOTO_NIB(wh[j], 12), b.z, b.w);
   }
-  float c[4];
-  c[0] = ((acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0])) - off.x;
-  c[1] = ((acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1])) - off.y;
-  c[2] = ((acc[0][2] + acc[1][2]) + (acc[2][2] + acc[3][2])) - off.x;
-  c[3] = ((acc[0][3] + acc[1][3]) + (acc[2][3] + acc[3][3])) - off.y;
   lo = fmaf(bf16x2_lo(it.slo), c[0], bf16x2_hi(it.slo) * c[1]);
   hi = fmaf(bf16x2_lo(it.shi), c[2], bf16x2_hi(it.shi) * c[3]);
 }

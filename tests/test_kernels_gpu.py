@@ -47,7 +47,7 @@ def test_qgemv_plain(cuda, K, N):
     x = activations(7, 1, K)
     got = ops.qmatmul(x.to(cuda), packed.to(cuda), scales.to(cuda), group_size=64).cpu()
     assert got.shape == (1, N)
-    assert ops.qmatmul_variant(1, N, K, 64) == "qgemv_mma"
+    assert ops.qmatmul_variant(1, N, K, 64) == ("qgemv_stream" if N >= 65536 else "qgemv_mma")
     assert rel_max_error(got, ref.packed_matmul(x, packed, scales, 64)) < ORACLE_TOL
     assert rel_max_error(got, exact_packed_matmul(x, packed, scales, 64)) < EXACT_TOL
 
@@ -63,6 +63,7 @@ def test_qgemv_lm_head_shape(cuda):
     want = ref.packed_matmul(x, packed, scales, 64, norm_weight=norm_w, rms_norm_eps=1e-6)
     assert rel_max_error(got, want) < ORACLE_TOL
     assert int(got.float().argmax()) == int(want.float().argmax())
+    assert ops.qmatmul_variant(1, N, K, 64) == "qgemv_stream"
 
 
 def test_qgemv_extreme_codes(cuda):
