@@ -67,6 +67,15 @@ def measured_peaks() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
+def tensor_peak() -> float | None:
+    """Measured dense bf16 TFLOP/s of this pool's B200 (burst), if the driver wrote it."""
+
+    try:
+        return float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"])
+    except Exception:
+        return None
+
+
 def projection_bytes(n: int, k: int, *, bias=False, norm=False, residual=False, m: int = 1) -> int:
     """Algorithmic bytes of one packed projection (codes, scales, x, y and optional operands)."""
 
@@ -263,6 +272,68 @@ def time_lm_head(runtime, peak_gbs: float, peak_kind: str) -> dict:
     }
 
 
+SWEEP_SHAPES = [(896, 1152, True), (896, 896, False), (896, 4864, False), (4864, 896, False), (896, 151936, False)]
+SWEEP_ROWS = (1, 16, 128)
+
+
+def qmatmul_sweep(device, hbm_peak: float, tensor_peak: float | None) -> list[dict]:
+    """The packed-matmul sweep on the Qwen2.5-0.5B projection shapes, M in {1, 16, 128}.
+
+    Every point is timed as 24 launches recorded in one CUDA graph over rotating weight copies
+    (more than L2 in total), replayed four times between two CUDA events: the small shapes
+    take 3-20 us, below what a host can launch back to back.
+    """
+
+    from aotolith_b200 import ops
+
+    results = []
+    for K, N, bias in SWEEP_SHAPES:
+        generator = torch.Generator().manual_seed(K + N)
+        packed = torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, generator=generator).to(device)
+        scales = (torch.rand(N, K // 64, generator=generator) * 0.01 + 0.001).bfloat16().to(device)
+        copies = min(64, max(3, int(400e6 // (N * K // 2)) + 1))
+        packs = [packed.clone() for _ in range(copies)]
+        scale_copies = [scales.clone() for _ in range(copies)]
+        addend = torch.randn(N, generator=generator).bfloat16().to(device) if bias else None
+        for M in SWEEP_ROWS:
+            x = torch.randn(M, K, generator=generator).bfloat16().to(device)
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+
+            def launch(i):
+                ops.qmatmul(x, packs[i % copies], scale_copies[i % copies], group_size=GROUP, addend=addend, out=out)
+
+            for i in range(copies):
+                launch(i)
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(24):
+                    launch(i)
+            graph.replay()
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            for _ in range(4):
+                graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            us = begin.elapsed_time(end) * 1e3 / 96
+            nbytes = projection_bytes(N, K, bias=bias, m=M)
+            point = {
+                "K": K, "N": N, "M": M, "variant": ops.qmatmul_variant(M, N, K, GROUP), "us": round(us, 2),
+                "gbs": round(nbytes / us / 1e3, 1), "frac_hbm_measured": round(nbytes / us / 1e3 / hbm_peak, 4),
+                "frac_hbm_8tbs": round(nbytes / us / 1e3 / 8000.0, 4),
+                "tflops": round(2.0 * M * N * K / us / 1e6, 2),
+            }
+            if tensor_peak:
+                point["frac_tensor_measured"] = round(point["tflops"] / tensor_peak, 4)
+            results.append(point)
+            del graph
+    return results
+
+
 def run_ours(args) -> None:
     import torch.distributed as dist
 
@@ -312,6 +383,17 @@ def run_ours(args) -> None:
         request(prompt_dev)
         runtime.greedy_generate(prompt_host).cpu()
     torch.cuda.synchronize()
+
+    # prefill alone (128 tokens through the prefill plan), CUDA events, after the warm-up above
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(5):
+        runtime.prefill_ids(prompt_dev)
+    end.record()
+    torch.cuda.synchronize()
+    prefill_ms = begin.elapsed_time(end) / 5
+    prefill_stats = {"ms": prefill_ms, "tok_s": PROMPT / (prefill_ms / 1e3), "tokens": PROMPT,
+                     "launches": kernels_prefill}
 
     sampler = ClockSampler(local)
     if rank == 0:
@@ -390,6 +472,9 @@ def run_ours(args) -> None:
             line["roofline"], line["lm_head_roofline"] = step_roofline, lm_head
         else:
             line["roofline"], line["step_roofline"] = lm_head, step_roofline
+        line["prefill"] = prefill_stats
+        if world == 1:
+            line["qmatmul_sweep"] = qmatmul_sweep(device, peak, tensor_peak())
         if world == 1 and not args.skip_cpu:
             line["cpu_baseline"] = cpu_sample(model, prompt_host, 3)
         print(json.dumps(line))
