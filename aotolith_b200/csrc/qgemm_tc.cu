@@ -19,11 +19,12 @@ namespace aoto {
 
 constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64;
 constexpr int TC_STAGES = 4;
-constexpr int TC_THREADS = 192;
-constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 2;  // 16 KiB: one operand tile of one stage
+constexpr int TC_DEQUANT_WARPS = 8;                // two per weight row: each converts half a k block
+constexpr int TC_THREADS = 64 + TC_DEQUANT_WARPS * 32;
+constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 2;  // 16 KiB: one 128-row operand tile of one stage
 constexpr int TC_WAIT_LIMIT = 1 << 20;
 constexpr int TC_AHEAD = 4;  // k blocks of packed words a dequantising thread keeps in flight
-constexpr size_t TC_SMEM_BYTES = 1024 + (size_t)2 * TC_STAGES * TC_TILE_BYTES + 256;
+constexpr size_t tc_smem_bytes(int m_tiles) { return 1024 + (size_t)(m_tiles + 1) * TC_STAGES * TC_TILE_BYTES + 256; }
 
 struct TcParams {
   const uint32_t* w;
@@ -117,13 +118,17 @@ __device__ __forceinline__ uint32_t tc_scaled_pair(uint32_t biased, __nv_bfloat1
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// MT = 128-row activation tiles a CTA multiplies against every weight tile it converts (the
+// conversion is the scarce resource: with MT = 2 it is shared by twice the tensor-core work).
+template <int MT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
+  constexpr int A_BYTES = MT * TC_TILE_BYTES;
   extern __shared__ unsigned char tc_smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* tile_a = base;
-  unsigned char* tile_b = base + (size_t)TC_STAGES * TC_TILE_BYTES;
+  unsigned char* tile_b = base + (size_t)TC_STAGES * A_BYTES;
   unsigned long long* full_a = reinterpret_cast<unsigned long long*>(tile_b + (size_t)TC_STAGES * TC_TILE_BYTES);
   unsigned long long* full_b = full_a + TC_STAGES;
   unsigned long long* empty = full_b + TC_STAGES;
@@ -131,21 +136,21 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accumulated + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * TC_BM;
+  const int n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * TC_BM * MT;
   const int blocks = p.K / TC_BK;
   bool ok = true;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TC_STAGES; ++s) {
       tc_bar_init(full_a + s, 1);
-      tc_bar_init(full_b + s, 4 * 32);
+      tc_bar_init(full_b + s, TC_DEQUANT_WARPS * 32);
       tc_bar_init(empty + s, 1);
     }
     tc_bar_init(accumulated, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(tmem_slot)), "r"(TC_BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(tmem_slot)), "r"(TC_BN * MT) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -161,8 +166,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
         const uint32_t round = (uint32_t)(kb / TC_STAGES);
         ok = tc_bar_wait(empty + s, (round & 1u) ^ 1u);  // a fresh barrier passes the first round
         if (!ok) break;
-        tc_bar_expect(full_a + s, TC_TILE_BYTES);
-        tc_tma_load(tile_a + (size_t)s * TC_TILE_BYTES, &x_map, kb * TC_BK, m0, full_a + s);
+        tc_bar_expect(full_a + s, A_BYTES);
+        tc_tma_load(tile_a + (size_t)s * A_BYTES, &x_map, kb * TC_BK, m0, full_a + s);
       }
     }
   } else if (warp == 1) {
@@ -175,32 +180,36 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
         ok = tc_bar_wait(full_a + s, round & 1u) && tc_bar_wait(full_b + s, round & 1u);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t desc_a = tc_operand_descriptor(tc_smem(tile_a + (size_t)s * TC_TILE_BYTES));
         const uint64_t desc_b = tc_operand_descriptor(tc_smem(tile_b + (size_t)s * TC_TILE_BYTES));
 #pragma unroll
-        for (int k = 0; k < TC_BK / 16; ++k)  // 16 columns = 32 bytes further along the swizzled row
-          tc_mma(tmem_base, desc_a + (uint64_t)(k * 2), desc_b + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+        for (int mt = 0; mt < MT; ++mt) {  // activation tile mt accumulates in its own 128 columns
+          const uint64_t desc_a = tc_operand_descriptor(tc_smem(tile_a + (size_t)s * A_BYTES + (size_t)mt * TC_TILE_BYTES));
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k)  // 16 columns = 32 bytes further along the swizzled row
+            tc_mma(tmem_base + (uint32_t)(mt * TC_BN), desc_a + (uint64_t)(k * 2), desc_b + (uint64_t)(k * 2), idesc,
+                   (kb | k) != 0 ? 1u : 0u);
+        }
         tc_commit(empty + s);  // the stage is free once these mma have read it
       }
       if (ok) tc_commit(accumulated);
     }
   } else {
     // ---- weight tiles: packed codes -> bf16 in swizzled shared memory; then the epilogue ----
-    const int r = threadIdx.x - 64;  // weight row of the tile, 0..127
+    const int r = (threadIdx.x - 64) & 127;   // weight row of the tile
+    const int half = (threadIdx.x - 64) >> 7;  // which 32 codes of the row's k block
     const int n = n0 + r;
     const bool row_valid = n < p.N;
     const uint4* wq = reinterpret_cast<const uint4*>(p.w) + (size_t)(row_valid ? n : 0) * (p.K >> 5);
     const bf16* sc = p.s + (size_t)(row_valid ? n : 0) * (p.K >> 6);
     // The packed words of the next TC_AHEAD k blocks are always in flight (a register ring with
     // static slots: the loop below is unrolled by TC_AHEAD).
-    uint4 q0[TC_AHEAD], q1[TC_AHEAD];
+    uint4 q0[TC_AHEAD];
     uint32_t scale_bits[TC_AHEAD];
     auto request = [&](int slot, int kb) {
-      q0[slot] = q1[slot] = make_uint4(0u, 0u, 0u, 0u);
+      q0[slot] = make_uint4(0u, 0u, 0u, 0u);
       scale_bits[slot] = 0u;
       if (row_valid && kb < blocks) {
-        q0[slot] = ldg_nc_u4(wq + (size_t)kb * 2);
-        q1[slot] = ldg_nc_u4(wq + (size_t)kb * 2 + 1);
+        q0[slot] = ldg_nc_u4(wq + (size_t)kb * 2 + half);
         unsigned short raw;
         asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(raw) : "l"(sc + kb));
         scale_bits[slot] = raw;
@@ -215,21 +224,22 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
       if (kb >= blocks || !ok) break;
       const int s = kb % TC_STAGES;
       const uint32_t round = (uint32_t)(kb / TC_STAGES);
-      const uint4 c0 = q0[a], c1 = q1[a];
+      const uint4 c0 = q0[a];
       const __nv_bfloat162 scale2 = __bfloat162bfloat162(__ushort_as_bfloat16((unsigned short)scale_bits[a]));
       request(a, kb + TC_AHEAD);
       ok = tc_bar_wait(empty + s, (round & 1u) ^ 1u);
       if (!ok) break;
       unsigned char* row = tile_b + (size_t)s * TC_TILE_BYTES + (size_t)r * 128;
-      const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const uint32_t words[4] = {c0.x, c0.y, c0.z, c0.w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {  // word i = codes 8i..8i+7 = 16-byte chunk i of the row
+      for (int w = 0; w < 4; ++w) {  // word i = codes 8i..8i+7 = 16-byte chunk i of the row
+        const int i = half * 4 + w;
         uint4 o = make_uint4(0u, 0u, 0u, 0u);
         if (row_valid) {
-          const uint32_t v04 = tc_scaled_pair(AOTO_NIB(words[i], 0), scale2);
-          const uint32_t v15 = tc_scaled_pair(AOTO_NIB(words[i], 4), scale2);
-          const uint32_t v26 = tc_scaled_pair(AOTO_NIB(words[i], 8), scale2);
-          const uint32_t v37 = tc_scaled_pair(AOTO_NIB(words[i], 12), scale2);
+          const uint32_t v04 = tc_scaled_pair(AOTO_NIB(words[w], 0), scale2);
+          const uint32_t v15 = tc_scaled_pair(AOTO_NIB(words[w], 4), scale2);
+          const uint32_t v26 = tc_scaled_pair(AOTO_NIB(words[w], 8), scale2);
+          const uint32_t v37 = tc_scaled_pair(AOTO_NIB(words[w], 12), scale2);
           o.x = __byte_perm(v04, v15, 0x5410);
           o.y = __byte_perm(v26, v37, 0x5410);
           o.z = __byte_perm(v04, v15, 0x7632);
@@ -246,12 +256,15 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
     if (ok) ok = tc_bar_wait(accumulated, 0u);
     if (ok) {
       tc_fence_after();
+      // two warps share a lane quadrant: each takes half of the 128 columns of every tile
       const int quadrant = warp & 3;
-      const int m = m0 + quadrant * 32 + lane;
 #pragma unroll 1
-      for (int c = 0; c < TC_BN / 32; ++c) {
+      for (int cc = 0; cc < MT * 2; ++cc) {
+        const int mt = cc >> 1;
+        const int c = half * 2 + (cc & 1);
+        const int m = m0 + mt * TC_BM + quadrant * 32 + lane;
         uint32_t acc[32];
-        tc_load_32(tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(c * 32), acc);
+        tc_load_32(tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(mt * TC_BN + c * 32), acc);
         if (m >= p.M) continue;
         const int nbase = n0 + c * 32;
 #pragma unroll
@@ -288,7 +301,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_BN * MT) : "memory");
   }
 }
 
@@ -343,7 +356,9 @@ int* timeout_flag_on_current_device() {
 }  // namespace
 
 bool qgemm_tc_applies(const aoto_qmatmul_args& a) {
-  return a.M >= 64 && a.N >= 64 && a.group_size == 64 && (a.K % TC_BK) == 0 && a.norm_weight == nullptr &&
+  // a 128-row tile is the smallest the tensor core takes: worth it from 64 rows on, or from 8 rows
+  // when the weight is large enough that converting it dominates
+  return (a.M >= 64 || (a.M >= 8 && a.N >= 4096)) && a.N >= 64 && a.group_size == 64 && (a.K % TC_BK) == 0 && a.norm_weight == nullptr &&
          a.epilogue != AOTO_EPILOGUE_SILU_MUL_PAIRED && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 &&
          (reinterpret_cast<uintptr_t>(a.packed) & 15) == 0;
 }
@@ -355,7 +370,8 @@ int qgemm_tc_launch(const aoto_qmatmul_args& a, cudaStream_t stream) {
   CUtensorMap map;
   const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
   const cuuint64_t strides[1] = {(cuuint64_t)a.K * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BM};
+  const int m_tiles = a.M > TC_BM ? 2 : 1;
+  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)(TC_BM * m_tiles)};
   const cuuint32_t element_strides[2] = {1, 1};
   if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.x), dims, strides, box, element_strides,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -364,7 +380,8 @@ int qgemm_tc_launch(const aoto_qmatmul_args& a, cudaStream_t stream) {
 
   static bool raised = false;
   if (!raised) {
-    if (cudaFuncSetAttribute(qgemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES) != cudaSuccess) {
+    if (cudaFuncSetAttribute(qgemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(1)) != cudaSuccess ||
+        cudaFuncSetAttribute(qgemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(2)) != cudaSuccess) {
       (void)cudaGetLastError();
       return AOTO_ERR_LAUNCH;
     }
@@ -380,8 +397,9 @@ int qgemm_tc_launch(const aoto_qmatmul_args& a, cudaStream_t stream) {
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.addend_kind = a.addend_kind; p.epilogue = a.epilogue;
   p.alpha = a.alpha; p.beta = a.beta;
-  dim3 grid((a.N + TC_BN - 1) / TC_BN, (a.M + TC_BM - 1) / TC_BM), block(TC_THREADS);
-  return launch_kernel(qgemm_tc_kernel, grid, block, TC_SMEM_BYTES, stream, false, map, p);
+  dim3 grid((a.N + TC_BN - 1) / TC_BN, (a.M + TC_BM * m_tiles - 1) / (TC_BM * m_tiles)), block(TC_THREADS);
+  if (m_tiles == 2) return launch_kernel(qgemm_tc_kernel<2>, grid, block, tc_smem_bytes(2), stream, false, map, p);
+  return launch_kernel(qgemm_tc_kernel<1>, grid, block, tc_smem_bytes(1), stream, false, map, p);
 }
 
 // Reads and clears the flag a timed-out wait of the tensor-core GEMM sets. Synchronises the
