@@ -483,6 +483,56 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+def run_probe(name: str) -> None:
+    """Small fixed cases for a profiler: a handful of launches of one kernel, a few GB at most.
+
+    ``lm_head``  six packed GEMV launches over three copies of a [151936, 896] weight (RMS norm fused);
+    ``gemm``     six packed GEMM launches, K=4096 N=14336 M=1024, over five weight copies;
+    ``step``     a 4-layer Qwen2.5-0.5B-shaped decoder: prefill, then six launches of the step kernel.
+    """
+
+    from aotolith_b200 import ops
+
+    device = torch.device("cuda", 0)
+    generator = torch.Generator().manual_seed(1)
+    if name == "lm_head":
+        N, K = 151936, 896
+        packs = [torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, generator=generator).to(device) for _ in range(3)]
+        scales = [(torch.rand(N, K // 64, generator=generator) * 0.01 + 0.001).bfloat16().to(device) for _ in range(3)]
+        x = torch.randn(1, K, generator=generator).bfloat16().to(device)
+        norm = (torch.randn(K, generator=generator) * 0.1 + 1).bfloat16().to(device)
+        out = torch.empty(1, N, dtype=torch.bfloat16, device=device)
+        for i in range(6):
+            ops.qmatmul(x, packs[i % 3], scales[i % 3], group_size=GROUP, norm_weight=norm, rms_norm_eps=1e-6, out=out)
+        torch.cuda.synchronize()
+        print(json.dumps({"probe": name, "variant": ops.qmatmul_variant(1, N, K, GROUP), "max": float(out.float().abs().max())}))
+    elif name == "gemm":
+        K, N, M = 4096, 14336, 1024
+        packs = [torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, generator=generator).to(device) for _ in range(5)]
+        scales = [(torch.rand(N, K // 64, generator=generator) * 0.01 + 0.001).bfloat16().to(device) for _ in range(5)]
+        x = torch.randn(M, K, generator=generator).bfloat16().to(device)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+        for i in range(6):
+            ops.qmatmul(x, packs[i % 5], scales[i % 5], group_size=GROUP, out=out)
+        torch.cuda.synchronize()
+        print(json.dumps({"probe": name, "variant": ops.qmatmul_variant(M, N, K, GROUP), "max": float(out.float().abs().max())}))
+    else:
+        import aotolith_b200 as aoto
+        from aotolith_b200.models.session import decode_session
+        from aotolith_b200.models.synthetic import qwen25_05b_shaped
+
+        model = qwen25_05b_shaped(seed=0, layers=4)
+        runtime = aoto.compile_qwen2_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS, quantize=GROUP)
+        prompt = seeded_prompt(model.config.vocab_size, 1).to(device)
+        logits, compact = runtime.prefill_ids(prompt)
+        cache = runtime.pad_cache(compact)
+        token = ops.argmax(logits[:, -1, :]).reshape(1, 1)
+        session = decode_session(runtime)
+        tokens = session.run(token, cache, PROMPT, 6)
+        torch.cuda.synchronize()
+        print(json.dumps({"probe": name, "mode": session.mode, "tokens": tokens.tolist()}))
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
@@ -491,7 +541,12 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="qwen25_05b")
     parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
+    parser.add_argument("--probe", choices=("lm_head", "gemm", "step"), default=None,
+                        help="run a small fixed case of one kernel for a profiler instead of the benchmark")
     args = parser.parse_args()
+    if args.probe is not None:
+        run_probe(args.probe)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:
