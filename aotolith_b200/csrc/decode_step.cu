@@ -159,7 +159,10 @@ __device__ __forceinline__ void load_item(const aoto_step_stage& st, int tile, i
 }
 
 // Returns false when a poll ran out (the caller leaves the kernel).
-__device__ bool stage_gemv(const aoto_step_stage& st, const StepSmem& sm, const StepControl& ctl, int stage_index) {
+__device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& sm, const StepControl& ctl, int stage_index) {
+  // The descriptor lives in shared memory; a private copy keeps its fields in registers, so that
+  // they are not read again after every barrier and volatile access.
+  const aoto_step_stage st = shared_stage;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int K = st.K, N = st.N;
@@ -582,7 +585,8 @@ __device__ __forceinline__ float rotate_smem(const float* head, const bf16* cos_
                     round_bf16(partner * __bfloat162float(sin_row[d])));
 }
 
-__device__ bool stage_attention(const aoto_step_stage& st, const StepSmem& sm, const StepControl& ctl, int stage_index) {
+__device__ bool stage_attention(const aoto_step_stage& shared_stage, const StepSmem& sm, const StepControl& ctl, int stage_index) {
+  const aoto_step_stage st = shared_stage;
   const int D = st.head_dim, C = st.capacity, KVH = st.kv_heads, QH = st.query_heads;
   const int G = QH / KVH;
   const int TK = ATT_TILE;

@@ -23,7 +23,7 @@ constexpr int TC_DEQUANT_WARPS = 8;                // two per weight row: each c
 constexpr int TC_THREADS = 64 + TC_DEQUANT_WARPS * 32;
 constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 2;  // 16 KiB: one 128-row operand tile of one stage
 constexpr int TC_WAIT_LIMIT = 1 << 20;
-constexpr int TC_AHEAD = 8;  // k blocks of packed words a dequantising thread keeps in flight
+constexpr int TC_AHEAD = 4;  // k blocks of packed words a dequantising thread keeps in flight
 constexpr size_t tc_smem_bytes(int m_tiles) { return 1024 + (size_t)(m_tiles + 1) * TC_STAGES * TC_TILE_BYTES + 256; }
 
 struct TcParams {

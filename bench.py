@@ -483,12 +483,43 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+def print_stage_trace(runtime, session, token, cache) -> None:
+    """One step with the kernel's trace on: CTA 0 stamps the global timer at eight points of a stage."""
+
+    trace = torch.zeros(session.stage_count * 8, dtype=torch.int64, device=session.device)
+    session.token.copy_(token)
+    session.caches[0].copy_(cache)
+    session.counters.copy_(torch.tensor([PROMPT + 1, 0], dtype=torch.int32))
+    for step in range(6):
+        session.epoch = session.epoch % 0xFFFFFFFE + 1
+        session._launch(session.programs[step & 1], session.stage_count, session.epoch, session.status,
+                        session.scratch, trace=trace if step == 5 else None)
+    torch.cuda.synchronize()
+    table = trace.cpu().reshape(-1, 8).tolist()
+    origin = table[0][0]
+    kinds = [stage.kind for stage in runtime.decode.plan.step_program.stages] + [3]
+    previous_end = origin
+    for index, row in enumerate(table):
+        entered, polled, staged, first_batch, reduced, stored, done, left = row
+        if kinds[index] == 1 and index < len(table) - 2:
+            print(f"stage {index:3d} gemv      at {entered - origin:7d} ns  gap {entered - previous_end:5d} | poll {polled - entered:5d} "
+                  f"stage {staged - polled:5d} first batch {first_batch - staged:5d} rest+reduce {reduced - first_batch:5d} "
+                  f"epilogue {stored - reduced:5d} tail {left - stored:5d}")
+        else:
+            name = {1: "gemv(head)", 2: "attention", 3: "pick"}.get(kinds[index], "?")
+            print(f"stage {index:3d} {name:9s} at {entered - origin:7d} ns  gap {entered - previous_end:5d} | poll {polled - entered:5d} "
+                  f"work {left - polled:6d}")
+        previous_end = left
+    print(f"total {table[-1][7] - origin} ns, status {int(session.status.item())}")
+
+
 def run_probe(name: str) -> None:
     """Small fixed cases for a profiler: a handful of launches of one kernel, a few GB at most.
 
     ``lm_head``  six packed GEMV launches over three copies of a [151936, 896] weight (RMS norm fused);
     ``gemm``     six packed GEMM launches, K=4096 N=14336 M=1024, over five weight copies;
-    ``step``     a 4-layer Qwen2.5-0.5B-shaped decoder: prefill, then six launches of the step kernel.
+    ``step``     a 4-layer Qwen2.5-0.5B-shaped decoder: prefill, then six launches of the step kernel;
+    ``trace``    the same, then one more step with the kernel's own per-stage timeline printed.
     """
 
     from aotolith_b200 import ops
@@ -531,6 +562,8 @@ def run_probe(name: str) -> None:
         tokens = session.run(token, cache, PROMPT, 6)
         torch.cuda.synchronize()
         print(json.dumps({"probe": name, "mode": session.mode, "tokens": tokens.tolist()}))
+        if name == "trace" and session.mode == "kernel":
+            print_stage_trace(runtime, session, token, cache)
 
 
 def main() -> None:
@@ -541,7 +574,7 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="qwen25_05b")
     parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
-    parser.add_argument("--probe", choices=("lm_head", "gemm", "step"), default=None,
+    parser.add_argument("--probe", choices=("lm_head", "gemm", "step", "trace"), default=None,
                         help="run a small fixed case of one kernel for a profiler instead of the benchmark")
     args = parser.parse_args()
     if args.probe is not None:
