@@ -9,6 +9,7 @@ are the reference compiler's: ``compile_module`` / ``compile_callable`` /
 """
 
 from ._version import __version__
+from .artifact import ABI_VERSION, FORMAT_VERSION, load_compiled_module, read_artifact_manifest, save_compiled
 from .backends import TARGETS, Backend, CudaBackend
 from .compiler import (
     CompilationResult,
@@ -29,6 +30,7 @@ from .models import (
 from .selection import KernelBenchmark, KernelSelection
 
 __all__ = [
+    "ABI_VERSION", "FORMAT_VERSION", "load_compiled_module", "read_artifact_manifest", "save_compiled",
     "TARGETS", "Backend", "CudaBackend", "CompilationResult", "CompiledModulePlan", "DType",
     "Graph", "KernelBenchmark", "KernelSelection", "Operation", "TensorType", "Value",
     "backend_for", "compile_callable", "compile_graph", "compile_llama_bucketed",

@@ -1,0 +1,145 @@
+"""Artifact round trip for the cuda-sm100 target.
+
+CPU part: a compiled module plan is written and read back on a host without a
+GPU (state stays on the host, the plan is rebuilt and validated); the manifest
+carries the format/ABI/target fields the reference's loader checks
+(``src/aotolith/artifact.py:437-487``), and tampering is refused. GPU part: the
+loaded plan computes what the saved one did.
+"""
+
+import json
+import zipfile
+
+import pytest
+import torch
+
+import aotolith_b200 as aoto
+from aotolith_b200.artifact import decode_graph, encode_graph
+from aotolith_b200.errors import ArtifactCompatibilityError
+from aotolith_b200.models.synthetic import tiny_decoder
+
+
+def _runtime():
+    model = tiny_decoder("qwen2", seed=4)
+    return aoto.compile_qwen2_static_cache(model, prompt_length=8, max_new_tokens=4, quantize=16)
+
+
+def test_graph_json_round_trip_is_exact():
+    runtime = _runtime()
+    for plan in (runtime.prefill, runtime.decode):
+        graph = plan.plan.graph
+        again = decode_graph(json.loads(json.dumps(encode_graph(graph))))
+        assert again.inputs == graph.inputs and again.outputs == graph.outputs
+        assert [(o.op, o.inputs, o.outputs) for o in again.ops] == [(o.op, o.inputs, o.outputs) for o in graph.ops]
+        for a, b in zip(again.ops, graph.ops):
+            assert repr(a.attrs) == repr(b.attrs)
+        assert {k: (v.type.shape, v.type.dtype) for k, v in again.values.items()} == \
+               {k: (v.type.shape, v.type.dtype) for k, v in graph.values.items()}
+
+
+def test_save_and_load_without_a_gpu(tmp_path):
+    runtime = _runtime()
+    prefill_path, decode_path = runtime.save(tmp_path / "tiny")
+    assert prefill_path.name == "tiny.prefill.aoto" and decode_path.name == "tiny.decode.aoto"
+    manifest = aoto.read_artifact_manifest(decode_path)
+    assert manifest["format"] == "aotolith" and manifest["format_version"] == aoto.FORMAT_VERSION
+    assert manifest["abi_version"] == aoto.ABI_VERSION and manifest["target"] == "cuda-sm100"
+    assert manifest["entrypoint"]["kind"] == "module" and manifest["entrypoint"]["input_count"] == 4
+    names = [entry["name"] for entry in manifest["entrypoint"]["state"]]
+    assert names == list(runtime.decode.state_names)
+    # tensors that alias in memory (tied embeddings, shared packed buffers) share a payload
+    files = [entry["file"] for entry in manifest["entrypoint"]["state"]]
+    assert len(set(files)) <= len(files)
+
+    loaded = aoto.load_compiled_module(decode_path)
+    assert loaded.state_names == runtime.decode.state_names and loaded.input_count == 4
+    assert loaded.target == "cuda-sm100"
+    assert [s.artifact_name for s in loaded.plan.selections] == [s.artifact_name for s in runtime.decode.plan.selections]
+    for a, b in zip(loaded._state_values, runtime.decode._state_values):
+        assert a.dtype == b.dtype and tuple(a.shape) == tuple(b.shape)
+        assert torch.equal(a.cpu().view(torch.uint8), b.cpu().contiguous().view(torch.uint8))
+    # aliasing survives the round trip
+    pointers = {}
+    for name, tensor in zip(runtime.decode.state_names, runtime.decode._state_values):
+        pointers.setdefault(tensor.data_ptr(), []).append(name)
+    loaded_pointers = {}
+    for name, tensor in zip(loaded.state_names, loaded._state_values):
+        loaded_pointers.setdefault(tensor.data_ptr(), []).append(name)
+    assert sorted(map(tuple, pointers.values())) == sorted(map(tuple, loaded_pointers.values()))
+    # saving twice gives the same bytes
+    again = runtime.decode.save(tmp_path / "again.aoto")
+    assert again.read_bytes() == decode_path.read_bytes()
+
+
+def _rewrite(path, out, edit):
+    with zipfile.ZipFile(path) as src, zipfile.ZipFile(out, "w") as dst:
+        for item in src.infolist():
+            data = src.read(item.filename)
+            data = edit(item.filename, data)
+            if data is not None:
+                dst.writestr(item, data)
+
+
+def test_tampered_or_foreign_artifacts_are_refused(tmp_path):
+    runtime = _runtime()
+    path = runtime.decode.save(tmp_path / "d.aoto")
+
+    def manifest_edit(**changes):
+        def edit(name, data):
+            if name != "manifest.json":
+                return data
+            manifest = json.loads(data)
+            manifest.update(changes)
+            return json.dumps(manifest).encode()
+        return edit
+
+    for changes in ({"format": "other"}, {"format_version": 99}, {"abi_version": "0.1"}, {"target": "vulkan"}):
+        bad = tmp_path / "bad.aoto"
+        _rewrite(path, bad, manifest_edit(**changes))
+        with pytest.raises(ArtifactCompatibilityError):
+            aoto.load_compiled_module(bad)
+
+    def flip_state(name, data):
+        if name == "state/00000.bin":
+            return bytes([data[0] ^ 1]) + data[1:]
+        return data
+
+    bad = tmp_path / "flipped.aoto"
+    _rewrite(path, bad, flip_state)
+    with pytest.raises(ArtifactCompatibilityError, match="digest"):
+        aoto.load_compiled_module(bad)
+
+    def other_kernel(name, data):
+        if name == "selections.json":
+            return data.replace(b"qgemv_generic", b"qgemv_other")
+        return data
+
+    bad = tmp_path / "selection.aoto"
+    _rewrite(path, bad, other_kernel)
+    with pytest.raises(ArtifactCompatibilityError):
+        aoto.load_compiled_module(bad)
+
+    with pytest.raises(ArtifactCompatibilityError):
+        (tmp_path / "junk.aoto").write_bytes(b"not a zip")
+        aoto.load_compiled_module(tmp_path / "junk.aoto")
+
+
+@pytest.mark.gpu
+def test_loaded_plan_computes_what_the_saved_one_did(cuda, tmp_path):
+    runtime = _runtime()
+    prefill_path, decode_path = runtime.save(tmp_path / "tiny")
+    prefill = aoto.load_compiled_module(prefill_path)
+    decode = aoto.load_compiled_module(decode_path)
+    prompt = torch.randint(0, 64, (1, 8), generator=torch.Generator().manual_seed(2)).to(cuda)
+    positions = torch.arange(8, device=cuda)[None, :]
+    mask = runtime._prefill_mask
+    want_logits, want_cache = runtime.prefill(prompt, positions, mask)
+    got_logits, got_cache = prefill(prompt, positions, mask)
+    assert torch.equal(got_logits, want_logits) and torch.equal(got_cache, want_cache)
+    cache = runtime.pad_cache(want_cache)
+    token = want_logits[:, -1, :].float().argmax(-1, keepdim=True)
+    dmask = runtime.decode_mask(9)
+    position = torch.tensor([[8]], device=cuda)
+    want = runtime.decode(token, position, dmask, cache)
+    got = decode(token, position, dmask, cache)
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
