@@ -52,9 +52,13 @@ PROMPT, NEW_TOKENS, GROUP = 128, 64, 64
 WORKLOADS = {
     "qwen25_05b": dict(builder="qwen25_05b_shaped", family="qwen2", layers=24,
                        description="Qwen2.5-0.5B-shaped, 4-bit g64, prompt 128, 64 greedy tokens, batch 1"),
-    "llama3_8b": dict(builder="llama3_8b_shaped", family="llama", layers=32,
-                      description="Llama-3-8B-shaped, 4-bit g64, prompt 128, 64 greedy tokens, batch 1"),
+    "llama3_8b": dict(builder="llama3_8b_shaped", family="llama", layers=32, prompt=1024, new_tokens=256,
+                      description="Llama-3-8B-shaped, 4-bit g64, prompt 1024, 256 greedy tokens, batch 1"),
+    "qwen25_05b_bucketed": dict(builder="qwen25_05b_shaped", family="qwen2", layers=24,
+                                description="bucketed Qwen2.5-0.5B-shaped runtime, buckets {32,64,128,256}, "
+                                            "prompt lengths uniform in [1,256], 64 greedy tokens per request"),
 }
+BUCKETS = (32, 64, 128, 256)
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -263,7 +267,7 @@ def time_lm_head(runtime, peak_gbs: float, peak_kind: str) -> dict:
     algorithmic = projection_bytes(n, k, norm=True)
     achieved = algorithmic / seconds / 1e9
     return {
-        "kernel": f"qgemv_mma_kernel (LM head, N={n}, K={k})", "bound": "hbm", "achieved": achieved,
+        "kernel": f"{ops.qmatmul_variant(1, n, k, GROUP)} (LM head, N={n}, K={k})", "bound": "hbm", "achieved": achieved,
         "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape under ncu
         "traffic": 72_360_000 + 1_420_000,
@@ -444,10 +448,10 @@ def run_ours(args) -> None:
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {
                 "workload": spec["description"],
-                "step": "one request: prefill(128) + 63 decode steps; value counts the decode loop only",
+                "step": f"one request: prefill({PROMPT}) + {decode_steps} decode steps; value counts the decode loop only",
                 "parallelism": f"{world} independent request stream(s), one runtime per GPU",
-                "l2": "inputs larger than L2: 262 MB of packed weights are streamed per token",
-                "e2e_definition": "64 generated tokens / wall time of greedy_generate(host ids) -> host tokens",
+                "l2": f"inputs larger than L2: {bytes_step / 1e6:.0f} MB of packed weights are streamed per token",
+                "e2e_definition": f"{NEW_TOKENS} generated tokens / wall time of greedy_generate(host ids) -> host tokens",
             },
             "decode_us_per_token": per_token_us,
             "e2e": {"value": e2e_job.per_second, "unit": "tok/s",
@@ -511,6 +515,81 @@ def print_stage_trace(runtime, session, token, cache) -> None:
                   f"work {left - polled:6d}")
         previous_end = left
     print(f"total {table[-1][7] - origin} ns, status {int(session.status.item())}")
+
+
+def run_bucketed(args) -> None:
+    """Independent request streams over a bucketed runtime, one runtime per GPU.
+
+    The request list (prompt lengths uniform in [1, 256], ids uniform over the vocabulary) is the
+    same seeded list on every rank; rank r serves requests r, r + world, ... through the public
+    call ``greedy_generate(host ids) -> host tokens``. A step is 16 requests per rank.
+    """
+
+    import torch.distributed as dist
+
+    import aotolith_b200 as aoto
+    from aotolith_b200 import replicas
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the cuda-sm100 target has no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    model, spec = build_model(args.workload, seed=0)
+    runtime = aoto.compile_qwen2_bucketed(model, prompt_lengths=BUCKETS, max_new_tokens=NEW_TOKENS, quantize=GROUP)
+    vocab = model.config.vocab_size
+    per_rank = 16 * args.steps
+    generator = torch.Generator().manual_seed(7)
+    lengths = torch.randint(1, BUCKETS[-1] + 1, (per_rank * world,), generator=generator).tolist()
+    requests = [torch.randint(0, vocab, (1, n), generator=generator, dtype=torch.int64).pin_memory() for n in lengths]
+    mine = replicas.shard(requests, world, rank)
+    for ids in [requests[i] for i in range(min(len(requests), 4 * len(BUCKETS)))][: max(args.warmup, 3) * 4]:
+        runtime.greedy_generate(ids).cpu()
+    for bucket in BUCKETS:  # every bucket's stepper is recorded before the clock starts
+        runtime.greedy_generate(torch.randint(0, vocab, (1, bucket), dtype=torch.int64)).cpu()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    generated = 0
+    for ids in mine:
+        generated += int(runtime.greedy_generate(ids).cpu().numel())
+    end.record()
+    torch.cuda.synchronize()
+    local_ms = begin.elapsed_time(end)
+    clocks = sampler.stop() if rank == 0 else None
+    job = replicas.job_throughput(generated, local_ms, device if world > 1 else None)
+    prompt_tokens = replicas.job_throughput(sum(int(r.numel()) for r in mine), local_ms, device if world > 1 else None).units
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        line = {
+            "metric": "bucketed runtime generated tok/s (4-bit g64 static cache, independent request streams)",
+            "value": job.per_second, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": job.milliseconds / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": spec["description"], "requests": per_rank * world,
+                       "step": "16 requests per GPU, each prefill (left-padded to its bucket) + 64 greedy tokens",
+                       "parallelism": f"{world} independent request stream(s), one bucketed runtime per GPU",
+                       "l2": "inputs larger than L2: 262 MB of packed weights are streamed per token"},
+            "e2e": {"value": job.per_second, "unit": "tok/s",
+                    "h2d_bytes_per_step": int(8 * prompt_tokens / max(args.steps, 1) / world),
+                    "d2h_bytes_per_step": 16 * NEW_TOKENS * 8},
+            "prompt_tok_s": prompt_tokens / (job.milliseconds / 1e3),
+            "gpu_launches": None, "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_probe(name: str) -> None:
@@ -580,8 +659,13 @@ def main() -> None:
     if args.probe is not None:
         run_probe(args.probe)
         return
+    global PROMPT, NEW_TOKENS
+    PROMPT = WORKLOADS[args.workload].get("prompt", PROMPT)
+    NEW_TOKENS = WORKLOADS[args.workload].get("new_tokens", NEW_TOKENS)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "qwen25_05b_bucketed":
+        run_bucketed(args)
     else:
         run_ours(args)
 
