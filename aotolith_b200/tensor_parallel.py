@@ -1,0 +1,303 @@
+"""Tensor-parallel greedy decoding of a packed decoder over the GPUs of one node.
+
+Models whose weights do not leave room for speed on one GPU (the Llama-3-8B
+shape) shard the Megatron way, one process per GPU:
+
+* q/k/v, gate and up are split by output rows (q/k/v by head: every rank owns
+  ``QH/tp`` query heads and ``KVH/tp`` key/value heads, so attention and the KV
+  cache need no exchange);
+* o and down are split along K at multiples of the quantisation group, so a
+  rank's slice of the packed words and of the scales is exactly what packing
+  the whole matrix would have put there; every rank produces a partial sum and
+  ONE all-reduce per attention block and ONE per MLP block combines them. The
+  residual is folded into rank 0's partial (the GEMV/GEMM addend), so the
+  reduced tensor already is the new hidden state on every rank;
+* the LM head is split over the vocabulary; ranks all-gather their logits
+  slices and take the argmax of the whole row;
+* embeddings, norms and rotary tables are replicated.
+
+Every step's kernels are the single-GPU ones (``aotolith_b200.ops``) on the
+local shard; the collectives are NCCL calls on the same stream. A decode step
+(kernels and all-reduces) is recorded once into a CUDA graph per cache
+direction and replayed per token; tokens stay on the device until the caller
+reads them. The reference has no multi-device path: this follows the packed
+decoder adapter (``src/aotolith/models/decoder.py:524-737``) shard by shard.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from .errors import CompilationError, PlanInputError
+from .models.adapters import rotary_tables
+from .models.quantized import pack_weight
+
+
+# ---------------------------------------------------------------------------
+# sharding of weights (host side, testable without a GPU)
+# ---------------------------------------------------------------------------
+
+def check_divisible(name: str, value: int, world: int, multiple: int = 1) -> int:
+    if value % (world * multiple) != 0:
+        raise CompilationError(
+            f"{name} = {value} cannot be split over {world} ranks in multiples of {multiple}",
+            hint="choose a tensor-parallel degree that divides the heads, the MLP width and the vocabulary",
+        )
+    return value // world
+
+
+def rows_of(weight: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    """Rank ``rank``'s block of output rows (column parallelism)."""
+
+    share = check_divisible("rows", weight.shape[0], world)
+    return weight[rank * share:(rank + 1) * share]
+
+
+def columns_of(weight: torch.Tensor, world: int, rank: int, group_size: int) -> torch.Tensor:
+    """Rank ``rank``'s block of input columns (row parallelism), whole quantisation groups only."""
+
+    share = check_divisible("columns", weight.shape[1], world, group_size)
+    return weight[:, rank * share:(rank + 1) * share]
+
+
+def qkv_rows_of(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, *, heads: int, kv_heads: int,
+                head_dim: int, world: int, rank: int) -> torch.Tensor:
+    """The packed q/k/v matrix of one rank: its query heads, then its key heads, then its value heads."""
+
+    q_share = check_divisible("query heads", heads, world) * head_dim
+    kv_share = check_divisible("key/value heads", kv_heads, world) * head_dim
+    return torch.cat((
+        query[rank * q_share:(rank + 1) * q_share],
+        key[rank * kv_share:(rank + 1) * kv_share],
+        value[rank * kv_share:(rank + 1) * kv_share],
+    ), dim=0)
+
+
+def shard_packed_rows(packed: torch.Tensor, scales: torch.Tensor, world: int, rank: int):
+    """Row block of an already packed matrix (equals packing the row block)."""
+
+    return rows_of(packed, world, rank).contiguous(), rows_of(scales, world, rank).contiguous()
+
+
+def shard_packed_columns(packed: torch.Tensor, scales: torch.Tensor, world: int, rank: int, group_size: int):
+    """Column block of an already packed matrix: eight codes per word, one scale per group."""
+
+    k = packed.shape[1] * 8
+    share = check_divisible("columns", k, world, max(group_size, 8))
+    words, groups = share // 8, share // group_size
+    return (packed[:, rank * words:(rank + 1) * words].contiguous(),
+            scales[:, rank * groups:(rank + 1) * groups].contiguous())
+
+
+# ---------------------------------------------------------------------------
+# the sharded decoder
+# ---------------------------------------------------------------------------
+
+class TensorParallelDecoder:
+    """One rank's shard of a packed decoder plus the greedy loop over it."""
+
+    def __init__(self, model: torch.nn.Module, *, prompt_length: int, max_new_tokens: int, group_size: int = 64,
+                 world: int | None = None, rank: int | None = None, device: Any = None, group: Any = None) -> None:
+        from . import ops  # the CUDA path: fails loudly without the kernel library
+
+        self.ops = ops
+        self.group = group
+        self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
+        self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        config = model.config
+        self.hidden = int(config.hidden_size)
+        self.layers = int(config.num_hidden_layers)
+        self.heads = int(config.num_attention_heads)
+        self.kv_heads = int(config.num_key_value_heads)
+        self.head_dim = int(getattr(config, "head_dim", None) or self.hidden // self.heads)
+        self.vocab = int(config.vocab_size)
+        self.eps = float(config.rms_norm_eps)
+        self.group_size = int(group_size)
+        self.prompt_length, self.max_new_tokens = int(prompt_length), int(max_new_tokens)
+        self.capacity = self.prompt_length + self.max_new_tokens
+        tp = self.world
+        self.local_heads = check_divisible("query heads", self.heads, tp)
+        self.local_kv_heads = check_divisible("key/value heads", self.kv_heads, tp)
+        check_divisible("MLP width", int(config.intermediate_size), tp, self.group_size)
+        check_divisible("attention width", self.heads * self.head_dim, tp, self.group_size)
+        self.local_vocab = check_divisible("vocabulary", self.vocab, tp)
+        dtype = next(model.parameters()).dtype
+        if dtype != torch.bfloat16:
+            raise CompilationError("the cuda-sm100 kernels compute in bfloat16", hint="convert the model with .bfloat16()")
+
+        def put(tensor: torch.Tensor) -> torch.Tensor:
+            return tensor.detach().contiguous().to(self.device)
+
+        def pack(weight: torch.Tensor):
+            words, scales = pack_weight(weight, self.group_size)
+            return put(words), put(scales.to(dtype))
+
+        r, g = self.rank, self.group_size
+        self.embed = put(model.model.embed_tokens.weight)
+        self.final_norm = put(model.model.norm.weight)
+        self.lm_head = pack(rows_of(model.lm_head.weight, tp, r))
+        cosine, sine = rotary_tables(self.capacity, self.head_dim, float(config.rope_theta), dtype)
+        self.cosine, self.sine = put(cosine), put(sine)
+        self.blocks = []
+        for layer in model.model.layers:
+            attention, mlp = layer.self_attn, layer.mlp
+            qkv = qkv_rows_of(attention.q_proj.weight, attention.k_proj.weight, attention.v_proj.weight,
+                              heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim, world=tp, rank=r)
+            bias = None
+            if attention.q_proj.bias is not None:
+                bias = put(qkv_rows_of(attention.q_proj.bias, attention.k_proj.bias, attention.v_proj.bias,
+                                       heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim, world=tp, rank=r))
+            self.blocks.append(dict(
+                input_norm=put(layer.input_layernorm.weight), post_norm=put(layer.post_attention_layernorm.weight),
+                qkv=pack(qkv), qkv_bias=bias,
+                o=pack(columns_of(attention.o_proj.weight, tp, r, g)),
+                gate=pack(rows_of(mlp.gate_proj.weight, tp, r)), up=pack(rows_of(mlp.up_proj.weight, tp, r)),
+                down=pack(columns_of(mlp.down_proj.weight, tp, r, g)),
+            ))
+        cache_shape = (self.layers, 2, 1, self.local_kv_heads, self.capacity, self.head_dim)
+        self.caches = [torch.zeros(cache_shape, dtype=torch.bfloat16, device=self.device) for _ in range(2)]
+        self.token = torch.zeros((1, 1), dtype=torch.int64, device=self.device)
+        self.position = torch.zeros((1, 1), dtype=torch.int64, device=self.device)
+        self.mask = torch.zeros((1, 1, 1, self.capacity), dtype=torch.bool, device=self.device)
+        self.counters = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.generated = torch.zeros(max(self.max_new_tokens, 1), dtype=torch.int64, device=self.device)
+        self.logits = torch.zeros((1, self.vocab), dtype=torch.bfloat16, device=self.device)
+        self.graphs: list[torch.cuda.CUDAGraph] = []
+
+    # -- collectives -------------------------------------------------------------
+    def _all_reduce(self, tensor: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.group)
+        return tensor
+
+    def _gather_logits(self, local: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            self.logits.copy_(local.reshape(1, -1))
+        else:
+            dist.all_gather_into_tensor(self.logits.reshape(-1), local.reshape(-1).contiguous(), group=self.group)
+        return self.logits
+
+    def _residual(self, hidden: torch.Tensor) -> torch.Tensor | None:
+        return hidden if self.rank == 0 else None  # the residual enters the sum exactly once
+
+    # -- prefill -----------------------------------------------------------------
+    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
+        """Fill cache buffer 0 with the prompt's keys and values; returns the last position's logits."""
+
+        ops, P, D = self.ops, self.prompt_length, self.head_dim
+        ids = ids.to(self.device).reshape(1, -1)
+        if ids.shape[1] != P:
+            raise PlanInputError(f"expected a prompt of {P} tokens, got {ids.shape[1]}")
+        hidden = ops.embedding(self.embed, ids).reshape(P, self.hidden)
+        cosine, sine = self.cosine[:P][None, None], self.sine[:P][None, None]
+        causal = torch.ones((P, P), dtype=torch.bool, device=self.device).tril()[None, None]
+        mask = ops.mask_select(causal, 0.0, -math.inf)
+        cache = self.caches[0]
+        cache.zero_()
+        q_width, kv_width = self.local_heads * D, self.local_kv_heads * D
+        for index, block in enumerate(self.blocks):
+            normed = ops.rms_norm(hidden, block["input_norm"], self.eps)
+            row = ops.qmatmul(normed, *block["qkv"], group_size=self.group_size, addend=block["qkv_bias"])
+            query = row[:, :q_width].reshape(1, P, self.local_heads, D).transpose(1, 2)
+            key = row[:, q_width:q_width + kv_width].reshape(1, P, self.local_kv_heads, D).transpose(1, 2)
+            value = row[:, q_width + kv_width:].reshape(1, P, self.local_kv_heads, D).transpose(1, 2)
+            query, key = ops.rope(query.contiguous(), cosine, sine), ops.rope(key.contiguous(), cosine, sine)
+            cache[index, 0, 0, :, self.capacity - P:, :] = key[0]
+            cache[index, 1, 0, :, self.capacity - P:, :] = value[0]
+            attended = ops.attention(query, key, value.contiguous(), mask)
+            attended = attended.transpose(1, 2).reshape(P, q_width)
+            hidden = self._all_reduce(ops.qmatmul(attended, *block["o"], group_size=self.group_size,
+                                                  addend=self._residual(hidden)))
+            normed = ops.rms_norm(hidden, block["post_norm"], self.eps)
+            gate = ops.qmatmul(normed, *block["gate"], group_size=self.group_size)
+            act = ops.qmatmul(normed, *block["up"], group_size=self.group_size, gate=gate)
+            hidden = self._all_reduce(ops.qmatmul(act, *block["down"], group_size=self.group_size,
+                                                  addend=self._residual(hidden)))
+        local = ops.qmatmul(hidden[-1:], *self.lm_head, group_size=self.group_size,
+                            norm_weight=self.final_norm, rms_norm_eps=self.eps)
+        return self._gather_logits(local)
+
+    # -- decode ------------------------------------------------------------------
+    def _step(self, source: int) -> None:
+        """One decode step from cache buffer ``source`` into the other one (device-resident inputs)."""
+
+        ops, D = self.ops, self.head_dim
+        ops.step_inputs(self.counters, self.position, self.mask)
+        mask = ops.mask_select(self.mask, 0.0, -math.inf)
+        cosine = ops.embedding(self.cosine, self.position)
+        sine = ops.embedding(self.sine, self.position)
+        hidden = ops.embedding(self.embed, self.token).reshape(1, self.hidden)
+        q_width, kv_width = self.local_heads * D, self.local_kv_heads * D
+        old, new = self.caches[source], self.caches[1 - source]
+        for index, block in enumerate(self.blocks):
+            row = ops.qmatmul(hidden, *block["qkv"], group_size=self.group_size, addend=block["qkv_bias"],
+                              norm_weight=block["input_norm"], rms_norm_eps=self.eps)
+            query, _, keys, values = ops.rope_kv_cache_append(
+                old, row, cosine, sine, layer=index, query_start=0, key_start=q_width,
+                value_start=q_width + kv_width, query_heads=self.local_heads, new_pair=new[index])
+            attended = ops.attention(query, keys, values, mask).reshape(1, q_width)
+            hidden = self._all_reduce(ops.qmatmul(attended, *block["o"], group_size=self.group_size,
+                                                  addend=self._residual(hidden)))
+            act = ops.qmatmul(hidden, *block["gate"], group_size=self.group_size, packed2=block["up"][0],
+                              scales2=block["up"][1], norm_weight=block["post_norm"], rms_norm_eps=self.eps)
+            hidden = self._all_reduce(ops.qmatmul(act, *block["down"], group_size=self.group_size,
+                                                  addend=self._residual(hidden)))
+        local = ops.qmatmul(hidden, *self.lm_head, group_size=self.group_size,
+                            norm_weight=self.final_norm, rms_norm_eps=self.eps)
+        ops.greedy_pick(self._gather_logits(local).reshape(-1), self.token, self.generated, self.counters)
+
+    def _record(self) -> None:
+        """Two CUDA graphs (cache 0 -> 1, 1 -> 0); the collectives are part of the recording."""
+
+        saved = [cache.clone() for cache in self.caches]
+        state = (self.token.clone(), self.counters.clone(), self.generated.clone())
+        self.counters.copy_(torch.tensor([1, 0], dtype=torch.int32))
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self._step(0)
+            self._step(1)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        pool = None
+        for source in (0, 1):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=pool, stream=side):
+                self._step(source)
+            pool = graph.pool()
+            self.graphs.append(graph)
+        for cache, kept in zip(self.caches, saved):
+            cache.copy_(kept)
+        self.token.copy_(state[0]); self.counters.copy_(state[1]); self.generated.copy_(state[2])
+
+    def close(self) -> None:
+        """Drop the recorded graphs. Call before ``destroy_process_group``: a communicator cannot be
+        torn down while recorded graphs still hold its kernels (the teardown then never returns)."""
+
+        torch.cuda.synchronize(self.device)
+        self.graphs.clear()
+        torch.cuda.synchronize(self.device)
+
+    def greedy_generate(self, ids: torch.Tensor, *, max_new_tokens: int | None = None, use_graphs: bool = True) -> torch.Tensor:
+        """Prefill ``ids`` and decode greedily; every rank returns the same ``[1, steps]`` tokens."""
+
+        steps = self.max_new_tokens if max_new_tokens is None else int(max_new_tokens)
+        if not 0 < steps <= self.max_new_tokens:
+            raise PlanInputError(f"max_new_tokens must be in [1, {self.max_new_tokens}], got {steps}")
+        if use_graphs and not self.graphs:
+            self._record()
+        logits = self.prefill(ids)
+        first = self.ops.argmax(logits).reshape(1, 1)
+        self.token.copy_(first)
+        self.counters.copy_(torch.tensor([self.prompt_length + 1, 0], dtype=torch.int32).pin_memory(), non_blocking=True)
+        for step in range(steps - 1):
+            if use_graphs:
+                self.graphs[step & 1].replay()
+            else:
+                self._step(step & 1)
+        return torch.cat((first, self.generated[:steps - 1].reshape(1, -1)), dim=1)

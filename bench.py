@@ -54,6 +54,9 @@ WORKLOADS = {
                        description="Qwen2.5-0.5B-shaped, 4-bit g64, prompt 128, 64 greedy tokens, batch 1"),
     "llama3_8b": dict(builder="llama3_8b_shaped", family="llama", layers=32, prompt=1024, new_tokens=256,
                       description="Llama-3-8B-shaped, 4-bit g64, prompt 1024, 256 greedy tokens, batch 1"),
+    "llama3_8b_tp": dict(builder="llama3_8b_shaped", family="llama", layers=32, prompt=1024, new_tokens=256,
+                         description="Llama-3-8B-shaped, 4-bit g64, prompt 1024, 256 greedy tokens, batch 1, "
+                                     "tensor parallel over the GPUs of the run"),
     "qwen25_05b_bucketed": dict(builder="qwen25_05b_shaped", family="qwen2", layers=24,
                                 description="bucketed Qwen2.5-0.5B-shaped runtime, buckets {32,64,128,256}, "
                                             "prompt lengths uniform in [1,256], 64 greedy tokens per request"),
@@ -517,6 +520,98 @@ def print_stage_trace(runtime, session, token, cache) -> None:
     print(f"total {table[-1][7] - origin} ns, status {int(session.status.item())}")
 
 
+def run_tp(args) -> None:
+    """One request stream, the model sharded over all ranks (strong scaling).
+
+    Every rank builds the same seeded model on the host and packs only its shard. A step is
+    one request: prefill, then ``new_tokens - 1`` replays of the recorded decode step (kernels
+    plus two NCCL all-reduces per layer).
+    """
+
+    import torch.distributed as dist
+
+    from aotolith_b200 import replicas
+    from aotolith_b200.tensor_parallel import TensorParallelDecoder
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the cuda-sm100 target has no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    model, spec = build_model(args.workload, seed=0)
+    decoder = TensorParallelDecoder(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS, group_size=GROUP,
+                                    world=world, rank=rank, device=device)
+    config = model.config
+    del model
+    prompt = seeded_prompt(config.vocab_size, 1).pin_memory()
+    decode_steps = NEW_TOKENS - 1
+    for _ in range(max(args.warmup, 3)):
+        decoder.greedy_generate(prompt).cpu()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    decode_ms = prefill_ms = 0.0
+    e2e_start = time.perf_counter()
+    for _ in range(args.steps):
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        marks[0].record()
+        logits = decoder.prefill(prompt)
+        first = decoder.ops.argmax(logits).reshape(1, 1)
+        decoder.token.copy_(first)
+        decoder.counters.copy_(torch.tensor([PROMPT + 1, 0], dtype=torch.int32).pin_memory(), non_blocking=True)
+        marks[1].record()
+        for step in range(decode_steps):
+            decoder.graphs[step & 1].replay()
+        marks[2].record()
+        tokens_host = decoder.generated[:decode_steps].cpu()
+        prefill_ms += marks[0].elapsed_time(marks[1])
+        decode_ms += marks[1].elapsed_time(marks[2])
+    e2e_wall = time.perf_counter() - e2e_start
+    clocks = sampler.stop() if rank == 0 else None
+    group_device = device if world > 1 else None
+    decode_ms = replicas.job_throughput(0, decode_ms, group_device).milliseconds
+    prefill_ms = replicas.job_throughput(0, prefill_ms, group_device).milliseconds
+    e2e_ms = replicas.job_throughput(0, e2e_wall * 1e3, group_device).milliseconds
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        per_token_us = decode_ms * 1e3 / (args.steps * decode_steps)
+        bytes_step = step_bytes(config, PROMPT + 1 + decode_steps // 2)
+        achieved = bytes_step / (per_token_us * 1e-6) / 1e9
+        line = {
+            "metric": "batch-1 decode tok/s (4-bit g64 static cache)", "value": args.steps * decode_steps / (decode_ms / 1e3),
+            "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": e2e_ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": spec["description"], "parallelism": f"tp{world}: column-split q/k/v, gate, up and LM head; "
+                       "row-split o and down; two NCCL all-reduces per layer inside the recorded step",
+                       "step": f"one request: prefill({PROMPT}) + {decode_steps} decode steps; value counts the decode loop only",
+                       "l2": f"inputs larger than L2: {bytes_step / world / 1e6:.0f} MB of packed weights per GPU and token"},
+            "decode_us_per_token": per_token_us,
+            "prefill": {"ms": prefill_ms / args.steps, "tok_s": PROMPT / (prefill_ms / args.steps / 1e3), "tokens": PROMPT},
+            "e2e": {"value": args.steps * NEW_TOKENS / (e2e_ms / 1e3), "unit": "tok/s",
+                    "h2d_bytes_per_step": PROMPT * 8, "d2h_bytes_per_step": NEW_TOKENS * 8},
+            "gpu_launches": None, "clocks": clocks,
+            "roofline": {"kernel": "recorded decode step (per-operation kernels + NCCL)", "bound": "hbm",
+                         "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world),
+                         "traffic": None, "bytes_per_launch": bytes_step, "us_per_launch": per_token_us,
+                         "peak_source": peak_kind, "note": "whole-job bytes over whole-job peak (all GPUs)"},
+        }
+        print(json.dumps(line))
+    decoder.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_bucketed(args) -> None:
     """Independent request streams over a bucketed runtime, one runtime per GPU.
 
@@ -666,6 +761,8 @@ def main() -> None:
         run_reference(args)
     elif args.workload == "qwen25_05b_bucketed":
         run_bucketed(args)
+    elif args.workload == "llama3_8b_tp":
+        run_tp(args)
     else:
         run_ours(args)
 
