@@ -585,9 +585,208 @@ __device__ __forceinline__ float rotate_smem(const float* head, const bf16* cos_
                     round_bf16(partner * __bfloat162float(sin_row[d])));
 }
 
+// Bytes of the tile region the whole-window form of the attention stage needs.
+__host__ __device__ inline size_t window_attention_bytes(int capacity, int head_dim) {
+  const size_t tiles = (size_t)2 * capacity * (head_dim * 2 + 16);
+  const size_t floats = (size_t)3 * head_dim + head_dim + 2 * (size_t)capacity + (size_t)STEP_WARPS * 2 * head_dim + 64;
+  return tiles + floats * 4 + 64;
+}
+constexpr size_t STEP_TILE_REGION_BYTES = (size_t)RING_SLOTS * RING_SLOT_BYTES;
+
+// Attention stage, whole-window form: one CTA per QUERY head holds the whole window of its kv
+// head in shared memory, so a head is finished where it started - no split, no merge through
+// scratch, no second exchange. The CTAs of a group read the same window (from L2) and share the
+// write of the shifted window into the next cache. Used when the window fits the tile region.
+__device__ bool stage_attention_window(const aoto_step_stage& st, const StepSmem& sm, const StepControl& ctl, int stage_index) {
+  const int D = st.head_dim, C = st.capacity, KVH = st.kv_heads, QH = st.query_heads;
+  const int G = QH / KVH;
+  trace_mark(ctl, stage_index, 0);
+  if ((int)blockIdx.x >= QH) {
+    trace_mark(ctl, stage_index, 1);
+    trace_mark(ctl, stage_index, 6);
+    trace_mark(ctl, stage_index, 7);
+    return true;
+  }
+  const uint32_t epoch = ctl.epoch;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int head = blockIdx.x, kvh = head / G, member = head - kvh * G;
+  const int row_bytes = D * 2 + 16, chunks = D >> 3, pairs = D >> 1;
+  unsigned char* kt = sm.tile;
+  unsigned char* vt = kt + (size_t)C * row_bytes;
+  float* rowv = reinterpret_cast<float*>(vt + (size_t)C * row_bytes);  // raw q head, k, v of the step: 3*D
+  float* qs = rowv + 3 * D;                                            // rotated, scaled query: D
+  float* sc = qs + D;                                                  // scores / probabilities: C
+  float* madd = sc + C;                                                // additive mask: C
+  float* pv = madd + C;                                                // partial P.V: slices * D
+  float* red = pv + STEP_WARPS * 2 * D;                                // 64
+
+  int valid_length = 0;
+  long long pos;
+  if (st.flags & AOTO_STAGE_FLAG_WINDOW) {
+    valid_length = *reinterpret_cast<const volatile int*>(st.counters);
+    pos = valid_length - 1;
+  } else {
+    pos = *reinterpret_cast<const volatile long long*>(st.position);
+  }
+  if (pos < 0) pos = 0;
+  if (pos >= st.table_rows) pos = st.table_rows - 1;
+  const bf16* cos_row = reinterpret_cast<const bf16*>(st.cos_table) + (size_t)pos * D;
+  const bf16* sin_row = reinterpret_cast<const bf16*>(st.sin_table) + (size_t)pos * D;
+  const bf16* kin = reinterpret_cast<const bf16*>(st.cache_in) + (size_t)kvh * C * D;
+  const bf16* vin = reinterpret_cast<const bf16*>(st.cache_in) + ((size_t)KVH + kvh) * C * D;
+  bf16* kout = reinterpret_cast<bf16*>(st.cache_out) + (size_t)kvh * C * D;
+  bf16* vout = reinterpret_cast<bf16*>(st.cache_out) + ((size_t)KVH + kvh) * C * D;
+
+  // slot j of the new window is slot j + 1 of the old one; the last slot is this step's pair
+  for (int c = tid; c < (C - 1) * chunks; c += STEP_THREADS) {
+    const int r = c / chunks, j = c - r * chunks;
+    cp_async_16_cg(kt + (size_t)r * row_bytes + j * 16, kin + (size_t)(r + 1) * D + j * 8);
+    cp_async_16_cg(vt + (size_t)r * row_bytes + j * 16, vin + (size_t)(r + 1) * D + j * 8);
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  for (int i = tid; i < C; i += STEP_THREADS) {
+    const bool attend = (st.flags & AOTO_STAGE_FLAG_WINDOW) ? (i >= C - valid_length) : (st.mask[i] != 0);
+    madd[i] = attend ? 0.f : -INFINITY;
+  }
+
+  // this head's query and its kv head's key and value of the step: poll the stamped projection row
+  {
+    const unsigned char* row_words = reinterpret_cast<const unsigned char*>(st.row);
+    const int total_words = 3 * pairs;
+    int polls = 0;
+    bool pending = tid < total_words;
+    while (true) {
+      bool ready = true;
+      if (pending) {
+        int element;
+        if (tid < pairs) element = st.query_start + head * D + 2 * tid;
+        else if (tid < 2 * pairs) element = st.key_start + kvh * D + 2 * (tid - pairs);
+        else element = st.value_start + kvh * D + 2 * (tid - 2 * pairs);
+        const uint2 v = ld_stamped(row_words + (size_t)(element >> 1) * 8);
+        if (v.y == epoch) {
+          rowv[2 * tid] = bf16x2_lo(v.x);
+          rowv[2 * tid + 1] = bf16x2_hi(v.x);
+          pending = false;
+        } else {
+          ready = false;
+        }
+      }
+      if (__syncthreads_and(ready)) break;
+      if (++polls > POLL_LIMIT) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        give_up(ctl, stage_index);
+        return false;
+      }
+    }
+  }
+  trace_mark(ctl, stage_index, 1);
+
+  for (int d = tid; d < D; d += STEP_THREADS) {
+    qs[d] = rotate_smem(rowv, cos_row, sin_row, d, D) * st.scale;
+    reinterpret_cast<bf16*>(kt + (size_t)(C - 1) * row_bytes)[d] =
+        __float2bfloat16_rn(rotate_smem(rowv + D, cos_row, sin_row, d, D));
+    reinterpret_cast<bf16*>(vt + (size_t)(C - 1) * row_bytes)[d] = __float2bfloat16_rn(rowv[2 * D + d]);
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+
+  // the members of a group share the write of the shifted window into the next cache
+  {
+    const int share = (C + G - 1) / G;
+    const int first = member * share, last = min(C, first + share);
+    for (int c = tid; c < (last - first) * chunks; c += STEP_THREADS) {
+      const int r = first + c / chunks, j = c % chunks;
+      const size_t dst = (size_t)r * D + j * 8;
+      *reinterpret_cast<uint4*>(kout + dst) = *reinterpret_cast<const uint4*>(kt + (size_t)r * row_bytes + j * 16);
+      *reinterpret_cast<uint4*>(vout + dst) = *reinterpret_cast<const uint4*>(vt + (size_t)r * row_bytes + j * 16);
+    }
+  }
+
+  // scores: thread <-> key
+  float local_max = -INFINITY;
+  for (int key = tid; key < C; key += STEP_THREADS) {
+    float s = -INFINITY;
+    if (madd[key] != -INFINITY) {
+      const uint4* krow = reinterpret_cast<const uint4*>(kt + (size_t)key * row_bytes);
+      const float4* q4 = reinterpret_cast<const float4*>(qs);
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+      for (int j = 0; j < chunks; ++j) {
+        const uint4 kk = krow[j];
+        const float4 qa = q4[2 * j], qb = q4[2 * j + 1];
+        d0 = fmaf(bf16x2_lo(kk.x), qa.x, d0); d1 = fmaf(bf16x2_hi(kk.x), qa.y, d1);
+        d2 = fmaf(bf16x2_lo(kk.y), qa.z, d2); d3 = fmaf(bf16x2_hi(kk.y), qa.w, d3);
+        d0 = fmaf(bf16x2_lo(kk.z), qb.x, d0); d1 = fmaf(bf16x2_hi(kk.z), qb.y, d1);
+        d2 = fmaf(bf16x2_lo(kk.w), qb.z, d2); d3 = fmaf(bf16x2_hi(kk.w), qb.w, d3);
+      }
+      s = (d0 + d1) + (d2 + d3);
+    }
+    sc[key] = s;
+    local_max = fmaxf(local_max, s);
+  }
+  local_max = warp_max(local_max);
+  if (lane == 0) red[warp] = local_max;
+  __syncthreads();
+  float m = red[0];
+#pragma unroll
+  for (int w = 1; w < STEP_WARPS; ++w) m = fmaxf(m, red[w]);
+  const float m_safe = (m == -INFINITY) ? 0.f : m;
+  float local_sum = 0.f;
+  for (int key = tid; key < C; key += STEP_THREADS) {
+    const float s = sc[key];
+    const float e = (s == -INFINITY) ? 0.f : expf(s - m_safe);
+    sc[key] = e;
+    local_sum += e;
+  }
+  local_sum = warp_sum(local_sum);
+  if (lane == 0) red[32 + warp] = local_sum;
+  __syncthreads();
+  float l = 0.f;
+#pragma unroll
+  for (int w = 0; w < STEP_WARPS; ++w) l += red[32 + w];
+
+  // P.V: thread <-> (key slice, dim pair); the slices are summed in a fixed order afterwards
+  const int slices = STEP_THREADS / pairs;
+  const int per_slice = (C + slices - 1) / slices;
+  {
+    const int slice = tid / pairs, dp = tid - slice * pairs;
+    float a0 = 0.f, a1 = 0.f;
+    if (slice < slices) {
+      const int k_begin = slice * per_slice, k_end = min(C, k_begin + per_slice);
+      for (int key = k_begin; key < k_end; ++key) {
+        const float w = sc[key];
+        if (w != 0.f) {
+          const uint32_t v = *reinterpret_cast<const uint32_t*>(vt + (size_t)key * row_bytes + dp * 4);
+          a0 = fmaf(w, bf16x2_lo(v), a0);
+          a1 = fmaf(w, bf16x2_hi(v), a1);
+        }
+      }
+      pv[(slice * pairs + dp) * 2] = a0;
+      pv[(slice * pairs + dp) * 2 + 1] = a1;
+    }
+  }
+  __syncthreads();
+  if (tid < pairs) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int slice = 0; slice < slices; ++slice) {
+      a0 += pv[(slice * pairs + tid) * 2];
+      a1 += pv[(slice * pairs + tid) * 2 + 1];
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    unsigned char* out_words = reinterpret_cast<unsigned char*>(st.attn_out);
+    st_stamped(out_words + ((size_t)head * pairs + tid) * 8, pack_bf16x2(a0 * inv, a1 * inv), epoch);
+  }
+  __syncthreads();
+  trace_mark(ctl, stage_index, 6);
+  trace_mark(ctl, stage_index, 7);
+  return true;
+}
+
 __device__ bool stage_attention(const aoto_step_stage& shared_stage, const StepSmem& sm, const StepControl& ctl, int stage_index) {
   const aoto_step_stage st = shared_stage;
   const int D = st.head_dim, C = st.capacity, KVH = st.kv_heads, QH = st.query_heads;
+  if (window_attention_bytes(C, D) <= STEP_TILE_REGION_BYTES && QH <= (int)gridDim.x &&
+      STEP_THREADS >= 3 * (D >> 1) && STEP_THREADS % (D >> 1) == 0)
+    return stage_attention_window(st, sm, ctl, stage_index);
   const int G = QH / KVH;
   const int TK = ATT_TILE;
   const int splits = (C + TK - 1) / TK;
