@@ -21,11 +21,12 @@ constexpr int STEP_THREADS = 256;
 constexpr int STEP_WARPS = STEP_THREADS / 32;
 constexpr int STEP_MAX_K = 16384;      // activation row staged in shared memory
 constexpr int STEP_MAX_ITEMS = 256;    // (tile, block) items of one round
-constexpr int STEP_BATCH = 4;          // items a warp holds in registers at once
 constexpr int POLL_SLICES = 3;         // 32-byte chunks of the input row a thread polls at once
 constexpr int POLL_LIMIT = 1 << 20;    // rounds of a bounded poll (each is >= one L2 round trip)
 constexpr int ATT_TILE = 64;           // keys per attention item
 constexpr int MAX_GROUP = 16;          // query heads per kv head
+constexpr int ITEM_BYTES = 16 * 64 + 16 * 4;    // one 16-row x 128-column block: codes, then 16 scale pairs
+constexpr int ITEM_SLOTS = 14;                 // blocks a warp keeps in shared memory per round
 constexpr int RING_SLOT_BYTES = 7680;  // one 16-row weight tile with its scales (K <= 896)
 constexpr int RING_DEPTH = STEP_WARPS <= 8 ? 2 : 1;  // ring slots a warp owns
 constexpr int RING_SLOTS = RING_DEPTH * STEP_WARPS;
@@ -90,6 +91,11 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
 }
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem_src) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+
 struct StepSmem {
   uint4* xs;            // STEP_MAX_K / 8 permuted activation chunks
   uint4* nw;            // STEP_MAX_K / 8 chunks of the norm weight
@@ -125,7 +131,7 @@ __device__ __forceinline__ RoundPlan plan_rounds(const aoto_step_stage& st) {
   r.per_tile = r.nblocks * r.mats;
   const int c = blockIdx.x, G = gridDim.x;
   r.my_tiles = r.tiles > c ? (r.tiles - c + G - 1) / G : 0;
-  int tpr = 64 / r.per_tile;
+  int tpr = (ITEM_SLOTS * STEP_WARPS) / r.per_tile;  // a round's blocks fit the warps' slots
   if (tpr < 1) tpr = 1;
   if (tpr > 8) tpr = 8;
   r.tiles_per_round = tpr;
@@ -145,19 +151,6 @@ __device__ __forceinline__ bool item_of(const RoundPlan& r, int round, int q, in
   return true;
 }
 
-__device__ __forceinline__ void load_item(const aoto_step_stage& st, int tile, int mat, int kb,
-                                          int g, int t, WeightItem* it) {
-  const int K = st.K;
-  const int row_u4 = K >> 5, row_sc = K >> 6;
-  const int rlo = min(tile * 16 + g, st.N - 1), rhi = min(tile * 16 + g + 8, st.N - 1);
-  const uint4* wq = reinterpret_cast<const uint4*>(mat == 0 ? st.packed : st.packed2);
-  const bf16* sc = reinterpret_cast<const bf16*>(mat == 0 ? st.scales : st.scales2);
-  it->lo = ldg_nc_u4(wq + (size_t)rlo * row_u4 + kb * 4 + t);
-  it->hi = ldg_nc_u4(wq + (size_t)rhi * row_u4 + kb * 4 + t);
-  it->slo = ldg_nc_u32(sc + (size_t)rlo * row_sc + kb * 2);
-  it->shi = ldg_nc_u32(sc + (size_t)rhi * row_sc + kb * 2);
-}
-
 // Returns false when a poll ran out (the caller leaves the kernel).
 __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& sm, const StepControl& ctl, int stage_index) {
   // The descriptor lives in shared memory; a private copy keeps its fields in registers, so that
@@ -172,19 +165,28 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
   trace_mark(ctl, stage_index, 0);
 
   // ---- weights first: they do not depend on the input row ----
-  WeightItem items[STEP_BATCH];
-  int it_kb[STEP_BATCH], it_q[STEP_BATCH];
-  bool it_ok[STEP_BATCH];
-  auto load_batch = [&](int round, int first) {
-#pragma unroll
-    for (int b = 0; b < STEP_BATCH; ++b) {
-      const int q = warp + (first + b) * STEP_WARPS;
+  // Round mode: the blocks (tile, matrix, k block) of a round are dealt to the warps, block q to
+  // warp q % 8, and travel global -> shared memory with cp.async into the warp's own slots: all of
+  // a round's weights are in flight before anything waits, and none of it occupies registers.
+  unsigned char* my_slots = sm.tile + (size_t)warp * ITEM_SLOTS * ITEM_BYTES;
+  auto request_round = [&](int round) {
+    const int r = lane >> 1, half = lane & 1;
+    for (int i = 0; i < ITEM_SLOTS; ++i) {
       int tile = 0, mat = 0, kb = 0;
-      it_q[b] = q;
-      it_ok[b] = q < STEP_MAX_ITEMS && item_of(rp, round, q, &tile, &mat, &kb);
-      it_kb[b] = kb;
-      if (it_ok[b]) load_item(st, tile, mat, kb, g, t, &items[b]);
+      if (!item_of(rp, round, warp + i * STEP_WARPS, &tile, &mat, &kb)) break;
+      unsigned char* slot = my_slots + (size_t)i * ITEM_BYTES;
+      const unsigned char* wbytes = reinterpret_cast<const unsigned char*>(mat == 0 ? st.packed : st.packed2);
+      const unsigned char* sbytes = reinterpret_cast<const unsigned char*>(mat == 0 ? st.scales : st.scales2);
+      const int n = min(tile * 16 + r, N - 1);
+      const unsigned char* src = wbytes + (size_t)n * (K >> 1) + (size_t)kb * 64 + half * 32;
+      cp_async_16_cg(slot + r * 64 + half * 32, src);
+      cp_async_16_cg(slot + r * 64 + half * 32 + 16, src + 16);
+      if (lane < 16) {
+        const int ns = min(tile * 16 + lane, N - 1);
+        cp_async_4(slot + 1024 + lane * 4, sbytes + (size_t)ns * (K >> 5) + (size_t)kb * 4);
+      }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
   // A stage with many small tiles per CTA (K <= 896 and no second matrix: the LM head of the 0.5B
   // shape) runs in "ring mode": every warp owns whole tiles and streams them through a ring in
@@ -225,6 +227,7 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
   };
   // Leave nothing in flight into this CTA's shared memory (used on the way out after a failure).
   auto ring_drain = [&]() {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     bool ok = true;
 #pragma unroll
     for (int slot = 0; slot < RING_DEPTH; ++slot)
@@ -242,7 +245,7 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
       if (warp + d * STEP_WARPS < rp.my_tiles) ring_issue(warp + d * STEP_WARPS, d);
     }
   } else if (rounds > 0) {
-    load_batch(0, 0);
+    request_round(0);
   }
 
   long long gather_row = 0;
@@ -452,44 +455,31 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
 
   for (int round = 0; round < (ring_mode ? 0 : rounds); ++round) {
     const int tiles_here = min(rp.tiles_per_round, rp.my_tiles - round * rp.tiles_per_round);
-    const int items_in_round = tiles_here * rp.per_tile;
-    const int per_warp = (items_in_round + STEP_WARPS - 1) / STEP_WARPS;
-    for (int first = 0; first < per_warp; first += STEP_BATCH) {
-      float r_lo[STEP_BATCH], r_hi[STEP_BATCH];
-#pragma unroll
-      for (int b = 0; b < STEP_BATCH; ++b) {
-        r_lo[b] = r_hi[b] = 0.f;
-        if (!it_ok[b]) continue;
-        mma_block(items[b], bs, it_kb[b], sm.xsum, r_lo[b], r_hi[b]);
-      }
-      if (round == 0 && first == 0) trace_mark(ctl, stage_index, 3);
-      // this batch's registers are free: request the next batch before touching shared memory
-      int q_done[STEP_BATCH];
-      bool ok_done[STEP_BATCH];
-#pragma unroll
-      for (int b = 0; b < STEP_BATCH; ++b) { q_done[b] = it_q[b]; ok_done[b] = it_ok[b]; }
-      {
-        int next_round = round, next_first = first + STEP_BATCH;
-        if (next_first >= per_warp) { next_round = round + 1; next_first = 0; }
-        if (next_round < rounds) {
-          load_batch(next_round, next_first);
-        } else {
-#pragma unroll
-          for (int b = 0; b < STEP_BATCH; ++b) it_ok[b] = false;
-        }
-      }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    for (int i = 0; i < ITEM_SLOTS; ++i) {
+      const int q = warp + i * STEP_WARPS;
+      int tile = 0, mat = 0, kb = 0;
+      if (!item_of(rp, round, q, &tile, &mat, &kb)) break;
+      const unsigned char* slot = my_slots + (size_t)i * ITEM_BYTES;
+      WeightItem it;
+      it.lo = *reinterpret_cast<const uint4*>(slot + g * 64 + t * 16);
+      it.hi = *reinterpret_cast<const uint4*>(slot + (g + 8) * 64 + t * 16);
+      it.slo = *reinterpret_cast<const uint32_t*>(slot + 1024 + g * 4);
+      it.shi = *reinterpret_cast<const uint32_t*>(slot + 1024 + (g + 8) * 4);
+      float lo, hi;
+      mma_block(it, bs, kb, sm.xsum, lo, hi);
       if (t == 0) {
-#pragma unroll
-        for (int b = 0; b < STEP_BATCH; ++b) {
-          if (!ok_done[b]) continue;
-          float* dst = sm.part + q_done[b] * 16;
-          dst[g] = r_lo[b];
-          dst[g + 8] = r_hi[b];
-        }
+        float* dst = sm.part + q * 16;
+        dst[g] = lo;
+        dst[g + 8] = hi;
       }
     }
+    if (round == 0) trace_mark(ctl, stage_index, 3);
     __syncthreads();
     if (round == 0) trace_mark(ctl, stage_index, 4);
+    // every warp is done reading its slots: the next round's weights travel during the epilogue
+    if (round + 1 < rounds) request_round(round + 1);
     // reduce over k blocks in a fixed order, epilogue, store
     const bool mine = tid < tiles_here * 16;
     const int tl = tid >> 4, r = tid & 15;
@@ -1137,7 +1127,7 @@ static int check_stage(const aoto_step_stage& st) {
     if (st.addend_mode == AOTO_STAGE_ADDEND_GATHER && st.x_index == nullptr) return 0;
     if ((st.flags & AOTO_STAGE_FLAG_X_GATHER) && (st.x_index == nullptr || st.x_rows <= 0)) return 0;
     const int per_tile = (st.K >> 7) * (st.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED ? 2 : 1);
-    if (per_tile > STEP_MAX_ITEMS) return 0;
+    if (per_tile > ITEM_SLOTS * STEP_WARPS) return 0;  // a tile's blocks must fit one round of slots
     return 1;
   }
   if (st.kind == AOTO_STAGE_ATTENTION) {
