@@ -26,10 +26,6 @@ from .. import ops
 from ..errors import DeviceError, PlanInputError
 
 
-#: packed weight bytes of a decode plan up to which the persistent step kernel is used
-STEP_KERNEL_MAX_PACKED_BYTES = 1 << 30
-
-
 class DecodeSession:
     """Static buffers plus either the persistent step kernel or two recorded graphs."""
 
@@ -57,11 +53,7 @@ class DecodeSession:
         self.graphs: list[torch.cuda.CUDAGraph] = []
         self.programs: list[torch.Tensor] = []
         self.mode = "graphs"
-        # The persistent kernel wins where a step is a chain of short stages (0.5B: 770 us against
-        # 1 007 us per token); where a stage streams ~100 MB the per-operation kernels keep more
-        # bytes in flight and win (8B: 3.7 ms against 4.5 ms), so large plans are recorded instead.
-        packed_bytes = sum(t.numel() * t.element_size() for t in self.state if t.dtype == torch.int32)
-        if packed_bytes <= STEP_KERNEL_MAX_PACKED_BYTES and self.plan.step_program is not None and self._bind_program():
+        if self.plan.step_program is not None and self._bind_program():
             self.mode = "kernel"
         else:
             self._record()

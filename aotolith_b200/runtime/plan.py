@@ -255,12 +255,16 @@ class CompiledPlan:
         if memory not in MEMORY_POLICIES:
             raise PlanInputError(f"unknown memory policy {memory!r}; choose one of {MEMORY_POLICIES}")
         ready = self._coerce(inputs)
-        if memory == "latency" and not verify_index_bounds:
-            return self._replay(ready)
+        if memory == "latency":
+            return self._replay(ready, verify_index_bounds)
         return self.run_eager(ready, verify_index_bounds=verify_index_bounds)
 
     # -- CUDA-graph stepper --------------------------------------------------------
-    def _replay(self, inputs: list[torch.Tensor]) -> tuple[torch.Tensor, ...]:
+    def _replay(self, inputs: list[torch.Tensor], verify_index_bounds: bool = False) -> tuple[torch.Tensor, ...]:
+        """Replay the recorded plan. The recording always carries the gathers' bounds flag (it is
+        cleared at the head of the graph); it is read back - one synchronisation, as in an eager
+        verified call - only when the caller asks for verification."""
+
         with self._lock_graph():
             state = self._graph_state
             if state is None:
@@ -273,9 +277,18 @@ class CompiledPlan:
                 elif inputs[position].data_ptr() != state["pointers"][position]:
                     # bound state was replaced: the recorded graph no longer applies
                     self._graph_state = None
-                    return self._replay(inputs)
+                    return self._replay(inputs, verify_index_bounds)
             state["graph"].replay()
-            return tuple(out.clone() for out in state["outputs"])
+            outputs = tuple(out.clone() for out in state["outputs"])
+            if verify_index_bounds:
+                seen = int(state["bad_index"].item())
+                if seen:
+                    raise IndexBoundsError(
+                        f"index out of range at gather position {seen - 1}",
+                        hint="pass verify_index_bounds=False when the indices are known good "
+                        "(an argmax result, for example)",
+                    )
+            return outputs
 
     def _lock_graph(self):
         return _GRAPH_LOCK
@@ -295,10 +308,13 @@ class CompiledPlan:
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
         graph = torch.cuda.CUDAGraph()
+        context = CallContext(device, True)
         with torch.cuda.graph(graph):
-            outputs = self.run_eager(static, verify_index_bounds=False)
+            context.bad_index.zero_()
+            outputs = self._run(static, context)
         return {
             "graph": graph,
+            "bad_index": context.bad_index,
             "staging": staging,
             "outputs": outputs,
             "dynamic": dynamic,
