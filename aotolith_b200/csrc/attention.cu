@@ -11,21 +11,9 @@
 //
 // Softmax follows the "safe" rule of the reference: a row whose keys are all
 // masked produces zeros, never NaN.
-#include "common.cuh"
+#include "attention.cuh"
 
 namespace aoto {
-
-struct AttnParams {
-  const bf16* q;
-  const bf16* k;
-  const bf16* v;
-  const bf16* mask;
-  bf16* out;
-  float* scratch;
-  int QH, KVH, Lq, Lk, D;
-  int causal, splits, keys_per_split;
-  float scale;
-};
 
 constexpr int DECODE_THREADS = 128;
 
@@ -324,6 +312,7 @@ extern "C" int aoto_sm100_attention(const aoto_attention_args* a, void* stream_)
   }
   p.splits = 1;
   p.keys_per_split = 0;
+  if (attention_prefill_mma_applies(p)) return attention_prefill_mma_launch(p, stream);
   const int64_t rows = (int64_t)a->query_heads * a->q_len;
   const size_t smem = (size_t)PREFILL_WARPS * a->head_dim * 4;
   return launch_kernel(attention_prefill_kernel, dim3((unsigned)((rows + PREFILL_WARPS - 1) / PREFILL_WARPS)),

@@ -336,7 +336,8 @@ def test_attention_fully_masked_rows_are_zero(cuda):
     assert not got.any()
 
 
-@pytest.mark.parametrize("QH,KVH,P,D,length", [(14, 2, 128, 64, 128), (14, 2, 64, 64, 37), (32, 8, 96, 128, 96), (4, 2, 7, 8, 3)])
+@pytest.mark.parametrize("QH,KVH,P,D,length", [(14, 2, 128, 64, 128), (14, 2, 64, 64, 37), (32, 8, 96, 128, 96), (4, 2, 7, 8, 3),
+                                                  (8, 2, 200, 64, 131), (8, 4, 257, 128, 257), (2, 1, 16, 64, 16)])
 def test_attention_prefill(cuda, QH, KVH, P, D, length):
     """Prefill with the left-padded bucket mask; pad query rows are fully masked -> zero."""
 
