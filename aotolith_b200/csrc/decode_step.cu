@@ -20,13 +20,17 @@ namespace aoto {
 constexpr int STEP_THREADS = 256;
 constexpr int STEP_WARPS = STEP_THREADS / 32;
 constexpr int STEP_MAX_K = 16384;      // activation row staged in shared memory
-constexpr int STEP_MAX_ITEMS = 256;    // (tile, block) items of one round
+constexpr int STEP_MAX_ITEMS = 336;    // partial sums kept in shared memory (6 chunks of 56 blocks)
 constexpr int POLL_SLICES = 3;         // 32-byte chunks of the input row a thread polls at once
 constexpr int POLL_LIMIT = 1 << 20;    // rounds of a bounded poll (each is >= one L2 round trip)
 constexpr int ATT_TILE = 64;           // keys per attention item
 constexpr int MAX_GROUP = 16;          // query heads per kv head
 constexpr int ITEM_BYTES = 16 * 64 + 16 * 4;    // one 16-row x 128-column block: codes, then 16 scale pairs
-constexpr int ITEM_SLOTS = 14;                 // blocks a warp keeps in shared memory per round
+constexpr int ITEM_SLOTS = 14;                 // blocks a warp keeps in shared memory: two banks of seven
+constexpr int BANK_SLOTS = ITEM_SLOTS / 2;
+constexpr int CHUNK_ITEMS = BANK_SLOTS * STEP_WARPS;  // blocks of one chunk of a CTA's list
+constexpr int PART_ITEMS = 6 * CHUNK_ITEMS;    // ring of partial sums: a tile spans at most three chunks and a
+                                               // warp runs at most two chunks ahead of the last barrier
 constexpr int RING_SLOT_BYTES = 7680;  // one 16-row weight tile with its scales (K <= 896)
 constexpr int RING_DEPTH = STEP_WARPS <= 8 ? 2 : 1;  // ring slots a warp owns
 constexpr int RING_SLOTS = RING_DEPTH * STEP_WARPS;
@@ -117,12 +121,14 @@ __device__ __forceinline__ void give_up(const StepControl& ctl, int stage) {
 // GEMV stage
 // ---------------------------------------------------------------------------
 struct RoundPlan {
-  int tiles, nblocks, mats, my_tiles, tiles_per_round, per_tile;
+  int tiles, nblocks, mats, my_tiles, per_tile;
   float inv_per_tile, inv_nblocks;  // exact for the small quotients taken here (< 2^10)
 };
 
 __device__ __forceinline__ int small_div(int a, float inv_b) { return __float2int_rd(((float)a + 0.5f) * inv_b); }
 
+// Quotients here are small (< 2^10) and the operands below 2^20, where the reciprocal form is
+// exact; it replaces integer divisions that cost ~30 instructions each at the head of a stage.
 __device__ __forceinline__ RoundPlan plan_rounds(const aoto_step_stage& st) {
   RoundPlan r;
   r.tiles = (st.N + 15) >> 4;
@@ -130,25 +136,10 @@ __device__ __forceinline__ RoundPlan plan_rounds(const aoto_step_stage& st) {
   r.mats = st.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED ? 2 : 1;
   r.per_tile = r.nblocks * r.mats;
   const int c = blockIdx.x, G = gridDim.x;
-  r.my_tiles = r.tiles > c ? (r.tiles - c + G - 1) / G : 0;
-  int tpr = (ITEM_SLOTS * STEP_WARPS) / r.per_tile;  // a round's blocks fit the warps' slots
-  if (tpr < 1) tpr = 1;
-  if (tpr > 8) tpr = 8;
-  r.tiles_per_round = tpr;
-  r.inv_per_tile = 1.f / (float)r.per_tile;
-  r.inv_nblocks = 1.f / (float)r.nblocks;
+  r.inv_per_tile = __frcp_rn((float)r.per_tile);
+  r.inv_nblocks = __frcp_rn((float)r.nblocks);
+  r.my_tiles = r.tiles > c ? small_div(r.tiles - c + G - 1, __frcp_rn((float)G)) : 0;
   return r;
-}
-
-__device__ __forceinline__ bool item_of(const RoundPlan& r, int round, int q, int* tile, int* mat, int* kb) {
-  const int tl = small_div(q, r.inv_per_tile);
-  const int local = round * r.tiles_per_round + tl;
-  if (tl >= r.tiles_per_round || local >= r.my_tiles) return false;
-  const int rem = q - tl * r.per_tile;
-  *mat = small_div(rem, r.inv_nblocks);
-  *kb = rem - *mat * r.nblocks;
-  *tile = blockIdx.x + local * gridDim.x;
-  return true;
 }
 
 // Returns false when a poll ran out (the caller leaves the kernel).
@@ -161,32 +152,47 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
   const int K = st.K, N = st.N;
   const uint32_t epoch = ctl.epoch;
   const RoundPlan rp = plan_rounds(st);
-  const int rounds = (rp.my_tiles + rp.tiles_per_round - 1) / rp.tiles_per_round;
   trace_mark(ctl, stage_index, 0);
 
   // ---- weights first: they do not depend on the input row ----
-  // Round mode: the blocks (tile, matrix, k block) of a round are dealt to the warps, block q to
-  // warp q % 8, and travel global -> shared memory with cp.async into the warp's own slots: all of
-  // a round's weights are in flight before anything waits, and none of it occupies registers.
+  // Chunk mode: the CTA's blocks - (tile, matrix, k block), tile-major - form one list that is cut
+  // into chunks of 56; block i of a chunk belongs to warp i % 8 and travels global -> shared
+  // memory with cp.async into one of the warp's two banks of seven slots. Two chunks are in
+  // flight before anything waits; a bank is refilled by its warp as soon as the warp has
+  // multiplied it (no CTA-wide synchronisation for the ring), none of it occupies registers.
   unsigned char* my_slots = sm.tile + (size_t)warp * ITEM_SLOTS * ITEM_BYTES;
-  auto request_round = [&](int round) {
-    const int r = lane >> 1, half = lane & 1;
-    for (int i = 0; i < ITEM_SLOTS; ++i) {
-      int tile = 0, mat = 0, kb = 0;
-      if (!item_of(rp, round, warp + i * STEP_WARPS, &tile, &mat, &kb)) break;
-      unsigned char* slot = my_slots + (size_t)i * ITEM_BYTES;
-      const unsigned char* wbytes = reinterpret_cast<const unsigned char*>(mat == 0 ? st.packed : st.packed2);
-      const unsigned char* sbytes = reinterpret_cast<const unsigned char*>(mat == 0 ? st.scales : st.scales2);
-      const int n = min(tile * 16 + r, N - 1);
-      const unsigned char* src = wbytes + (size_t)n * (K >> 1) + (size_t)kb * 64 + half * 32;
-      cp_async_16_cg(slot + r * 64 + half * 32, src);
-      cp_async_16_cg(slot + r * 64 + half * 32 + 16, src + 16);
-      if (lane < 16) {
-        const int ns = min(tile * 16 + lane, N - 1);
-        cp_async_4(slot + 1024 + lane * 4, sbytes + (size_t)ns * (K >> 5) + (size_t)kb * 4);
+  const int total_items = rp.my_tiles * rp.per_tile;
+  const int chunks_total = (total_items + CHUNK_ITEMS - 1) / CHUNK_ITEMS;
+  auto locate = [&](int idx, int* tile, int* mat, int* kb) {
+    const int lt = small_div(idx, rp.inv_per_tile);
+    const int j = idx - lt * rp.per_tile;
+    *mat = small_div(j, rp.inv_nblocks);
+    *kb = j - *mat * rp.nblocks;
+    *tile = blockIdx.x + lt * gridDim.x;
+  };
+  auto request_chunk = [&](int chunk) {
+    if (chunk < chunks_total) {
+      const int r = lane >> 1, half = lane & 1;
+      unsigned char* bank = my_slots + (size_t)(chunk & 1) * BANK_SLOTS * ITEM_BYTES;
+      for (int i = 0; i < BANK_SLOTS; ++i) {
+        const int idx = chunk * CHUNK_ITEMS + warp + i * STEP_WARPS;
+        if (idx >= total_items) break;
+        int tile, mat, kb;
+        locate(idx, &tile, &mat, &kb);
+        unsigned char* slot = bank + (size_t)i * ITEM_BYTES;
+        const unsigned char* wbytes = reinterpret_cast<const unsigned char*>(mat == 0 ? st.packed : st.packed2);
+        const unsigned char* sbytes = reinterpret_cast<const unsigned char*>(mat == 0 ? st.scales : st.scales2);
+        const int n = min(tile * 16 + r, N - 1);
+        const unsigned char* src = wbytes + (size_t)n * (K >> 1) + (size_t)kb * 64 + half * 32;
+        cp_async_16_cg(slot + r * 64 + half * 32, src);
+        cp_async_16_cg(slot + r * 64 + half * 32 + 16, src + 16);
+        if (lane < 16) {
+          const int ns = min(tile * 16 + lane, N - 1);
+          cp_async_4(slot + 1024 + lane * 4, sbytes + (size_t)ns * (K >> 5) + (size_t)kb * 4);
+        }
       }
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");  // an empty group keeps the count uniform
   };
   // A stage with many small tiles per CTA (K <= 896 and no second matrix: the LM head of the 0.5B
   // shape) runs in "ring mode": every warp owns whole tiles and streams them through a ring in
@@ -244,8 +250,9 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
       ring_uses[d] = sm.ring_uses[warp * RING_DEPTH + d];
       if (warp + d * STEP_WARPS < rp.my_tiles) ring_issue(warp + d * STEP_WARPS, d);
     }
-  } else if (rounds > 0) {
-    request_round(0);
+  } else {
+    request_chunk(0);
+    request_chunk(1);
   }
 
   long long gather_row = 0;
@@ -260,7 +267,7 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
   uint2 addend0_word = make_uint2(0u, 0u);
   {
     const int tl0 = tid >> 4, r0 = tid & 15;
-    const int tiles0 = min(rp.tiles_per_round, rp.my_tiles);
+    const int tiles0 = min(STEP_THREADS / 16, rp.my_tiles);
     const int n0 = (blockIdx.x + tl0 * gridDim.x) * 16 + r0;
     if (tl0 < tiles0 && n0 < N) {
       if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN) {
@@ -371,7 +378,7 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
   __syncthreads();
   trace_mark(ctl, stage_index, 2);
 
-  // ---- rounds: compute a batch, request the next one, then (at the end of a round) reduce ----
+  // ---- chunks: multiply a bank, refill it, reduce the tiles that are complete ----
   bf16* out_plain = reinterpret_cast<bf16*>(st.out);
   unsigned char* out_words = reinterpret_cast<unsigned char*>(st.out);
   const BSource bs = b_source(sm.xs, reinterpret_cast<const uint4*>(sm.flag) + 1, lane);
@@ -453,15 +460,17 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
     if (__syncthreads_or(!ring_ok)) { give_up(ctl, stage_index); return false; }
   }
 
-  for (int round = 0; round < (ring_mode ? 0 : rounds); ++round) {
-    const int tiles_here = min(rp.tiles_per_round, rp.my_tiles - round * rp.tiles_per_round);
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  int finished = 0;  // local tiles whose epilogue has run
+  for (int chunk = 0; chunk < (ring_mode ? 0 : chunks_total); ++chunk) {
+    asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the newest group has landed
     __syncwarp();
-    for (int i = 0; i < ITEM_SLOTS; ++i) {
-      const int q = warp + i * STEP_WARPS;
-      int tile = 0, mat = 0, kb = 0;
-      if (!item_of(rp, round, q, &tile, &mat, &kb)) break;
-      const unsigned char* slot = my_slots + (size_t)i * ITEM_BYTES;
+    const unsigned char* bank = my_slots + (size_t)(chunk & 1) * BANK_SLOTS * ITEM_BYTES;
+    for (int i = 0; i < BANK_SLOTS; ++i) {
+      const int idx = chunk * CHUNK_ITEMS + warp + i * STEP_WARPS;
+      if (idx >= total_items) break;
+      int tile, mat, kb;
+      locate(idx, &tile, &mat, &kb);
+      const unsigned char* slot = bank + (size_t)i * ITEM_BYTES;
       WeightItem it;
       it.lo = *reinterpret_cast<const uint4*>(slot + g * 64 + t * 16);
       it.hi = *reinterpret_cast<const uint4*>(slot + (g + 8) * 64 + t * 16);
@@ -470,74 +479,80 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
       float lo, hi;
       mma_block(it, bs, kb, sm.xsum, lo, hi);
       if (t == 0) {
-        float* dst = sm.part + q * 16;
+        float* dst = sm.part + (idx % PART_ITEMS) * 16;
         dst[g] = lo;
         dst[g + 8] = hi;
       }
     }
-    if (round == 0) trace_mark(ctl, stage_index, 3);
+    __syncwarp();                // every lane has read the bank
+    request_chunk(chunk + 2);    // refill it
+    if (chunk == 0) trace_mark(ctl, stage_index, 3);
+    // tiles whose last block lies in this chunk are complete after the barrier
+    const int done_items = min(total_items, (chunk + 1) * CHUNK_ITEMS);
+    const int complete = small_div(done_items, rp.inv_per_tile);
+    if (complete == finished) continue;  // uniform: a long tile is still being summed
     __syncthreads();
-    if (round == 0) trace_mark(ctl, stage_index, 4);
-    // every warp is done reading its slots: the next round's weights travel during the epilogue
-    if (round + 1 < rounds) request_round(round + 1);
-    // reduce over k blocks in a fixed order, epilogue, store
-    const bool mine = tid < tiles_here * 16;
-    const int tl = tid >> 4, r = tid & 15;
-    const int tile = blockIdx.x + (round * rp.tiles_per_round + tl) * gridDim.x;
-    const int n = tile * 16 + r;
-    const bool valid = mine && n < N;
-    float y = 0.f;
-    if (valid) {
-      const float* p0 = sm.part + (tl * rp.per_tile) * 16 + r;
-      // fixed order: four interleaved partial sums over the k blocks, then their sum
-      auto sum_blocks = [&](const float* q) {
-        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-        int kb = 0;
-        for (; kb + 4 <= rp.nblocks; kb += 4) {
-          s0 += q[kb * 16]; s1 += q[(kb + 1) * 16]; s2 += q[(kb + 2) * 16]; s3 += q[(kb + 3) * 16];
+    if (chunk == 0) trace_mark(ctl, stage_index, 4);
+    for (int first = finished; first < complete; first += STEP_THREADS / 16) {
+      // reduce over k blocks in a fixed order, epilogue, store
+      const int tl = first + (tid >> 4), r = tid & 15;
+      const int tile = blockIdx.x + tl * gridDim.x;
+      const int n = tile * 16 + r;
+      const bool valid = tl < complete && n < N;
+      const bool prefetched = tl == (tid >> 4);  // the addend requested before the input was polled
+      float y = 0.f;
+      if (valid) {
+        int base = (tl * rp.per_tile) % PART_ITEMS;
+        // fixed order: four interleaved partial sums over the k blocks, then their sum
+        auto sum_blocks = [&]() {
+          float s[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int kb = 0; kb < rp.nblocks; ++kb) {
+            s[kb & 3] += sm.part[base * 16 + r];
+            if (++base == PART_ITEMS) base = 0;
+          }
+          return (s[0] + s[1]) + (s[2] + s[3]);
+        };
+        const float total = sum_blocks();
+        const float total2 = rp.mats == 2 ? sum_blocks() : 0.f;
+        y = st.alpha * total;
+        if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN) {
+          const float a = prefetched ? addend0 : __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[n]);
+          y = fmaf(st.beta, a, y);
+        } else if (st.addend_mode == AOTO_STAGE_ADDEND_GATHER) {
+          const float a = prefetched
+                              ? addend0
+                              : __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[(size_t)gather_row * N + n]);
+          y = fmaf(st.beta, a, y);
+        } else if (st.addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
+          const unsigned char* words = reinterpret_cast<const unsigned char*>(st.addend) + (size_t)(n >> 1) * 8;
+          uint2 w = prefetched ? addend0_word : ld_stamped(words);
+          while (w.y != epoch && ++polls <= POLL_LIMIT) w = ld_stamped(words);
+          y = fmaf(st.beta, (n & 1) ? bf16x2_hi(w.x) : bf16x2_lo(w.x), y);
         }
-        for (; kb < rp.nblocks; ++kb) s0 += q[kb * 16];
-        return (s0 + s1) + (s2 + s3);
-      };
-      const float total = sum_blocks(p0);
-      const float total2 = rp.mats == 2 ? sum_blocks(p0 + rp.nblocks * 16) : 0.f;
-      y = st.alpha * total;
-      if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN) {
-        const float a = round == 0 ? addend0 : __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[n]);
-        y = fmaf(st.beta, a, y);
-      } else if (st.addend_mode == AOTO_STAGE_ADDEND_GATHER) {
-        const float a = round == 0
-                            ? addend0
-                            : __bfloat162float(reinterpret_cast<const bf16*>(st.addend)[(size_t)gather_row * N + n]);
-        y = fmaf(st.beta, a, y);
-      } else if (st.addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
-        const unsigned char* words = reinterpret_cast<const unsigned char*>(st.addend) + (size_t)(n >> 1) * 8;
-        uint2 w = round == 0 ? addend0_word : ld_stamped(words);
-        while (w.y != epoch && ++polls <= POLL_LIMIT) w = ld_stamped(words);
-        y = fmaf(st.beta, (n & 1) ? bf16x2_hi(w.x) : bf16x2_lo(w.x), y);
+        if (st.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED) {
+          const float gate = round_bf16(y);
+          y = (st.alpha * total2) * (gate / (1.f + expf(-gate)));
+        }
       }
-      if (st.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED) {
-        const float gate = round_bf16(y);
-        y = (st.alpha * total2) * (gate / (1.f + expf(-gate)));
+      const uint32_t bits = float_to_bf16_bits(y);
+      const uint32_t neighbour = __shfl_down_sync(0xffffffffu, bits, 1);
+      if (valid) {
+        if (st.flags & AOTO_STAGE_FLAG_OUT_PLAIN) {
+          out_plain[n] = __ushort_as_bfloat16((unsigned short)bits);
+        } else if ((r & 1) == 0) {
+          st_stamped(out_words + (size_t)(n >> 1) * 8, bits | (neighbour << 16), epoch);
+        }
+        if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
+          float v = __uint_as_float(bits << 16);
+          if (v != v) v = INFINITY;
+          if (v > best_v || (v == best_v && n < best_i)) { best_v = v; best_i = n; }
+        }
       }
     }
-    const uint32_t bits = float_to_bf16_bits(y);
-    const uint32_t neighbour = __shfl_down_sync(0xffffffffu, bits, 1);
-    if (valid) {
-      if (st.flags & AOTO_STAGE_FLAG_OUT_PLAIN) {
-        out_plain[n] = __ushort_as_bfloat16((unsigned short)bits);
-      } else if ((r & 1) == 0) {
-        st_stamped(out_words + (size_t)(n >> 1) * 8, bits | (neighbour << 16), epoch);
-      }
-      if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
-        float v = __uint_as_float(bits << 16);
-        if (v != v) v = INFINITY;
-        if (v > best_v || (v == best_v && n < best_i)) { best_v = v; best_i = n; }
-      }
-    }
-    if (round == 0) trace_mark(ctl, stage_index, 5);
-    __syncthreads();
+    finished = complete;
+    if (chunk == 0) trace_mark(ctl, stage_index, 5);
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   if (__syncthreads_or(polls > POLL_LIMIT)) { give_up(ctl, stage_index); return false; }
   trace_mark(ctl, stage_index, 6);
 
