@@ -693,7 +693,8 @@ def run_probe(name: str) -> None:
     ``lm_head``  six packed GEMV launches over three copies of a [151936, 896] weight (RMS norm fused);
     ``gemm``     six packed GEMM launches, K=4096 N=14336 M=1024, over five weight copies;
     ``step``     a 4-layer Qwen2.5-0.5B-shaped decoder: prefill, then six launches of the step kernel;
-    ``trace``    the same, then one more step with the kernel's own per-stage timeline printed.
+    ``trace``    the same, then one more step with the kernel's own per-stage timeline printed;
+    ``trace_llama`` the timeline for a 2-layer cut of the Llama-3-8B shape (prompt 128).
     """
 
     from aotolith_b200 import ops
@@ -726,8 +727,14 @@ def run_probe(name: str) -> None:
         from aotolith_b200.models.session import decode_session
         from aotolith_b200.models.synthetic import qwen25_05b_shaped
 
-        model = qwen25_05b_shaped(seed=0, layers=4)
-        runtime = aoto.compile_qwen2_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS, quantize=GROUP)
+        if name == "trace_llama":
+            from aotolith_b200.models.synthetic import llama3_8b_shaped
+
+            model = llama3_8b_shaped(seed=0, layers=2)
+            runtime = aoto.compile_llama_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS, quantize=GROUP)
+        else:
+            model = qwen25_05b_shaped(seed=0, layers=4)
+            runtime = aoto.compile_qwen2_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS, quantize=GROUP)
         prompt = seeded_prompt(model.config.vocab_size, 1).to(device)
         logits, compact = runtime.prefill_ids(prompt)
         cache = runtime.pad_cache(compact)
@@ -736,7 +743,7 @@ def run_probe(name: str) -> None:
         tokens = session.run(token, cache, PROMPT, 6)
         torch.cuda.synchronize()
         print(json.dumps({"probe": name, "mode": session.mode, "tokens": tokens.tolist()}))
-        if name == "trace" and session.mode == "kernel":
+        if name in ("trace", "trace_llama") and session.mode == "kernel":
             print_stage_trace(runtime, session, token, cache)
 
 
@@ -748,7 +755,7 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="qwen25_05b")
     parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
-    parser.add_argument("--probe", choices=("lm_head", "gemm", "step", "trace"), default=None,
+    parser.add_argument("--probe", choices=("lm_head", "gemm", "step", "trace", "trace_llama"), default=None,
                         help="run a small fixed case of one kernel for a profiler instead of the benchmark")
     args = parser.parse_args()
     if args.probe is not None:
