@@ -12,6 +12,7 @@ bool qgemv_stream_applies(const aoto_qmatmul_args& a);
 int qgemv_stream_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
 int qgemm_tc_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
 int qgemm_tc_take_timeout_flag();
+int64_t qgemm_tc_scratch_bytes(const aoto_qmatmul_args& a);
 int qgemm_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
 }  // namespace aoto
 
@@ -41,7 +42,8 @@ extern "C" int aoto_sm100_qmatmul_supported(const aoto_qmatmul_args* a) {
 }
 
 extern "C" int64_t aoto_sm100_qmatmul_scratch_bytes(const aoto_qmatmul_args* a) {
-  (void)a;
+  if (!a) return 0;
+  if (qgemm_tc_applies(*a)) return qgemm_tc_scratch_bytes(*a);  // split-K partial tiles
   return 0;
 }
 

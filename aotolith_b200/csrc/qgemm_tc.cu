@@ -33,7 +33,9 @@ struct TcParams {
   const bf16* gate;
   bf16* out;
   int* status;
+  unsigned char* scratch;  // split-K: arrival counters (first 4096 bytes), then fp32 partial tiles
   int M, N, K;
+  int blocks_per_split;    // 64-column k blocks one CTA of a split walks
   int addend_kind, epilogue;
   float alpha, beta;
 };
@@ -134,10 +136,15 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
   unsigned long long* empty = full_b + TC_STAGES;
   unsigned long long* accumulated = empty + TC_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accumulated + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * TC_BM * MT;
-  const int blocks = p.K / TC_BK;
+  // Split-K: blockIdx.z walks its own range of k blocks; partial tiles meet in scratch and the
+  // CTA that arrives last adds them in a fixed order and runs the epilogue.
+  const int splits = gridDim.z;
+  const int kb_first = blockIdx.z * p.blocks_per_split;
+  const int blocks = min(p.blocks_per_split, p.K / TC_BK - kb_first);
   bool ok = true;
 
   if (threadIdx.x == 0) {
@@ -167,7 +174,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
         ok = tc_bar_wait(empty + s, (round & 1u) ^ 1u);  // a fresh barrier passes the first round
         if (!ok) break;
         tc_bar_expect(full_a + s, A_BYTES);
-        tc_tma_load(tile_a + (size_t)s * A_BYTES, &x_map, kb * TC_BK, m0, full_a + s);
+        tc_tma_load(tile_a + (size_t)s * A_BYTES, &x_map, (kb_first + kb) * TC_BK, m0, full_a + s);
       }
     }
   } else if (warp == 1) {
@@ -209,9 +216,9 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
       q0[slot] = make_uint4(0u, 0u, 0u, 0u);
       scale_bits[slot] = 0u;
       if (row_valid && kb < blocks) {
-        q0[slot] = ldg_nc_u4(wq + (size_t)kb * 2 + half);
+        q0[slot] = ldg_nc_u4(wq + (size_t)(kb_first + kb) * 2 + half);
         unsigned short raw;
-        asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(raw) : "l"(sc + kb));
+        asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(raw) : "l"(sc + kb_first + kb));
         scale_bits[slot] = raw;
       }
     };
@@ -252,45 +259,96 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
       }
     }
 
-    // epilogue: warp q of a warpgroup may read tensor-memory lanes 32q..32q+31
+    // epilogue: warp q of a warpgroup may read tensor-memory lanes 32q..32q+31; two warps share
+    // a lane quadrant and each takes half of the 128 columns of every tile
     if (ok) ok = tc_bar_wait(accumulated, 0u);
+    const int quadrant = warp & 3;
+    auto emit = [&](const float (&acc)[32], int m, int nbase) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        uint32_t packed_pair = 0;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int col = nbase + j + e;
+          float y = p.alpha * acc[j + e];
+          if (col < p.N) {
+            if (p.addend_kind == AOTO_ADDEND_VECTOR) y = fmaf(p.beta, __bfloat162float(p.addend[col]), y);
+            else if (p.addend_kind == AOTO_ADDEND_FULL) y = fmaf(p.beta, __bfloat162float(p.addend[(size_t)m * p.N + col]), y);
+            if (p.epilogue == AOTO_EPILOGUE_SILU_MUL) {
+              const float gate = __bfloat162float(p.gate[(size_t)m * p.N + col]);
+              y = y * (gate / (1.f + expf(-gate)));
+            }
+          }
+          packed_pair |= float_to_bf16_bits(y) << (16 * e);
+        }
+        const int col = nbase + j;
+        if (col + 1 < p.N && (p.N & 1) == 0) {
+          *reinterpret_cast<uint32_t*>(p.out + (size_t)m * p.N + col) = packed_pair;
+        } else {
+          if (col < p.N) p.out[(size_t)m * p.N + col] = __ushort_as_bfloat16((unsigned short)(packed_pair & 0xffffu));
+          if (col + 1 < p.N) p.out[(size_t)m * p.N + col + 1] = __ushort_as_bfloat16((unsigned short)(packed_pair >> 16));
+        }
+      }
+    };
+    // fp32 partial tiles: [split][padded row][padded column]
+    const size_t padded_cols = (size_t)gridDim.x * TC_BN, padded_rows = (size_t)gridDim.y * TC_BM * MT;
+    float* partials = reinterpret_cast<float*>(p.scratch + SCRATCH_HEADER_BYTES);
     if (ok) {
       tc_fence_after();
-      // two warps share a lane quadrant: each takes half of the 128 columns of every tile
-      const int quadrant = warp & 3;
 #pragma unroll 1
       for (int cc = 0; cc < MT * 2; ++cc) {
         const int mt = cc >> 1;
         const int c = half * 2 + (cc & 1);
         const int m = m0 + mt * TC_BM + quadrant * 32 + lane;
-        uint32_t acc[32];
-        tc_load_32(tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(mt * TC_BN + c * 32), acc);
-        if (m >= p.M) continue;
-        const int nbase = n0 + c * 32;
+        uint32_t raw[32];
+        tc_load_32(tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(mt * TC_BN + c * 32), raw);
+        if (splits == 1) {
+          if (m >= p.M) continue;
+          float acc[32];
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          uint32_t packed_pair = 0;
+          for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(raw[j]);
+          emit(acc, m, n0 + c * 32);
+        } else {
+          float4* dst = reinterpret_cast<float4*>(partials + ((size_t)blockIdx.z * padded_rows + m) * padded_cols + n0 + c * 32);
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = nbase + j + e;
-            float y = p.alpha * __uint_as_float(acc[j + e]);
-            if (col < p.N) {
-              if (p.addend_kind == AOTO_ADDEND_VECTOR) y = fmaf(p.beta, __bfloat162float(p.addend[col]), y);
-              else if (p.addend_kind == AOTO_ADDEND_FULL) y = fmaf(p.beta, __bfloat162float(p.addend[(size_t)m * p.N + col]), y);
-              if (p.epilogue == AOTO_EPILOGUE_SILU_MUL) {
-                const float gate = __bfloat162float(p.gate[(size_t)m * p.N + col]);
-                y = y * (gate / (1.f + expf(-gate)));
-              }
+          for (int j = 0; j < 8; ++j)
+            dst[j] = make_float4(__uint_as_float(raw[4 * j]), __uint_as_float(raw[4 * j + 1]),
+                                 __uint_as_float(raw[4 * j + 2]), __uint_as_float(raw[4 * j + 3]));
+        }
+      }
+    }
+    if (splits > 1) {
+      // the converting warps (256 threads) meet on their own barrier; one of them counts the arrival
+      int* counter = reinterpret_cast<int*>(p.scratch) + blockIdx.y * gridDim.x + blockIdx.x;
+      __threadfence();
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int arrived = atomicAdd(counter, 1);
+        const int last = arrived == splits - 1;
+        if (last) *counter = 0;  // counters are zero between launches
+        *last_flag = last;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (*last_flag && ok) {
+        __threadfence();
+#pragma unroll 1
+        for (int cc = 0; cc < MT * 2; ++cc) {
+          const int mt = cc >> 1;
+          const int c = half * 2 + (cc & 1);
+          const int m = m0 + mt * TC_BM + quadrant * 32 + lane;
+          if (m >= p.M) continue;
+          float acc[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+          for (int z = 0; z < splits; ++z) {  // fixed order: the result does not depend on arrival order
+            const float4* src = reinterpret_cast<const float4*>(partials + ((size_t)z * padded_rows + m) * padded_cols + n0 + c * 32);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 v = __ldcg(src + j);
+              acc[4 * j] += v.x; acc[4 * j + 1] += v.y; acc[4 * j + 2] += v.z; acc[4 * j + 3] += v.w;
             }
-            packed_pair |= float_to_bf16_bits(y) << (16 * e);
           }
-          const int col = nbase + j;
-          if (col + 1 < p.N && (p.N & 1) == 0) {
-            *reinterpret_cast<uint32_t*>(p.out + (size_t)m * p.N + col) = packed_pair;
-          } else {
-            if (col < p.N) p.out[(size_t)m * p.N + col] = __ushort_as_bfloat16((unsigned short)(packed_pair & 0xffffu));
-            if (col + 1 < p.N) p.out[(size_t)m * p.N + col + 1] = __ushort_as_bfloat16((unsigned short)(packed_pair >> 16));
-          }
+          emit(acc, m, n0 + c * 32);
         }
       }
     }
@@ -363,6 +421,36 @@ bool qgemm_tc_applies(const aoto_qmatmul_args& a) {
          (reinterpret_cast<uintptr_t>(a.packed) & 15) == 0;
 }
 
+// Grid of a request: activation tiles per CTA, output tiles, and - for outputs too narrow to
+// occupy the GPU - how many ways K is split (each split at least sixteen k blocks: below that the
+// fixed cost of a CTA and of the meeting in scratch outweighs the shorter loop; at most eight
+// splits, about one CTA per SM in total).
+struct TcPlan {
+  int m_tiles, grid_x, grid_y, splits, blocks_per_split;
+  int64_t scratch_bytes;
+};
+
+static TcPlan tc_plan(const aoto_qmatmul_args& a) {
+  TcPlan plan;
+  plan.m_tiles = a.M > TC_BM ? 2 : 1;
+  plan.grid_x = (a.N + TC_BN - 1) / TC_BN;
+  plan.grid_y = (a.M + TC_BM * plan.m_tiles - 1) / (TC_BM * plan.m_tiles);
+  const int tiles = plan.grid_x * plan.grid_y, blocks = a.K / TC_BK;
+  int splits = 148 / tiles;
+  if (splits > 8) splits = 8;
+  if (splits > blocks / 16) splits = blocks / 16;
+  // with many activation rows the partial tiles cost more to write and re-read than the split saves
+  if (splits < 1 || tiles > SCRATCH_MAX_COUNTERS || a.M > 256) splits = 1;
+  plan.blocks_per_split = (blocks + splits - 1) / splits;
+  plan.splits = (blocks + plan.blocks_per_split - 1) / plan.blocks_per_split;
+  plan.scratch_bytes = plan.splits > 1
+      ? SCRATCH_HEADER_BYTES + (int64_t)plan.splits * plan.grid_y * TC_BM * plan.m_tiles * plan.grid_x * TC_BN * 4
+      : 0;
+  return plan;
+}
+
+int64_t qgemm_tc_scratch_bytes(const aoto_qmatmul_args& a) { return tc_plan(a).scratch_bytes; }
+
 int qgemm_tc_launch(const aoto_qmatmul_args& a, cudaStream_t stream) {
   EncodeTiled encode = tensor_map_encoder();
   if (encode == nullptr) return AOTO_ERR_UNSUPPORTED;
@@ -370,7 +458,13 @@ int qgemm_tc_launch(const aoto_qmatmul_args& a, cudaStream_t stream) {
   CUtensorMap map;
   const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
   const cuuint64_t strides[1] = {(cuuint64_t)a.K * 2};
-  const int m_tiles = a.M > TC_BM ? 2 : 1;
+  TcPlan plan = tc_plan(a);
+  if (plan.splits > 1 && (a.scratch == nullptr || a.scratch_bytes < plan.scratch_bytes ||
+                          (reinterpret_cast<uintptr_t>(a.scratch) & 15) != 0)) {
+    plan.splits = 1;  // no workspace given: one CTA walks all of K
+    plan.blocks_per_split = a.K / TC_BK;
+  }
+  const int m_tiles = plan.m_tiles;
   const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)(TC_BM * m_tiles)};
   const cuuint32_t element_strides[2] = {1, 1};
   if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.x), dims, strides, box, element_strides,
@@ -394,10 +488,12 @@ int qgemm_tc_launch(const aoto_qmatmul_args& a, cudaStream_t stream) {
   p.gate = (const bf16*)a.gate;
   p.out = (bf16*)a.out;
   p.status = timeout_flag_on_current_device();
+  p.scratch = static_cast<unsigned char*>(a.scratch);
+  p.blocks_per_split = plan.blocks_per_split;
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.addend_kind = a.addend_kind; p.epilogue = a.epilogue;
   p.alpha = a.alpha; p.beta = a.beta;
-  dim3 grid((a.N + TC_BN - 1) / TC_BN, (a.M + TC_BM * m_tiles - 1) / (TC_BM * m_tiles)), block(TC_THREADS);
+  dim3 grid(plan.grid_x, plan.grid_y, plan.splits), block(TC_THREADS);
   if (m_tiles == 2) return launch_kernel(qgemm_tc_kernel<2>, grid, block, tc_smem_bytes(2), stream, false, map, p);
   return launch_kernel(qgemm_tc_kernel<1>, grid, block, tc_smem_bytes(1), stream, false, map, p);
 }

@@ -144,7 +144,13 @@ def qmatmul(
         args.gate = _ptr(gate)
         args.epilogue = N.EPILOGUE_SILU_MUL
         keep.append(gate)
-    N.check(N.load().aoto_sm100_qmatmul(ctypes.byref(args), _stream()), "aoto_sm100_qmatmul")
+    lib = N.load()
+    need = lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(args)) if M > 1 else 0
+    if need:
+        scratch = workspace(x.device, need)
+        args.scratch, args.scratch_bytes = _ptr(scratch), scratch.numel()
+        keep.append(scratch)
+    N.check(lib.aoto_sm100_qmatmul(ctypes.byref(args), _stream()), "aoto_sm100_qmatmul")
     return out
 
 

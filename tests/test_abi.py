@@ -86,6 +86,11 @@ def test_qmatmul_queries_are_host_only():
     assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(_qargs(16, 1152, 896, 64))) == b"gemm_mma"
     assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(_qargs(1, 24, 64, 16))) == b"qgemv_generic"
     assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(_qargs(1, 1152, 896, 64))) == 0
+    # narrow prefill products split K over several CTAs and ask for a workspace of partial tiles:
+    # 7 output tiles, 76 k blocks -> 4 splits of 128 x 896 fp32 behind the 4096-byte counter header
+    assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(_qargs(128, 896, 4864, 64))) == 4096 + 4 * 128 * 896 * 4
+    assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(_qargs(128, 896, 896, 64))) == 0      # 14 k blocks: too short to split
+    assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(_qargs(128, 151936, 896, 64))) == 0   # 1187 tiles fill the GPU
     # null pointers are refused before anything reaches the CUDA runtime
     assert lib.aoto_sm100_qmatmul(ctypes.byref(_qargs(1, 1152, 896, 64)), None) == N.ERR_ARGUMENT
     assert lib.aoto_sm100_qmatmul(None, None) == N.ERR_ARGUMENT
