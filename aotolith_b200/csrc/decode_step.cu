@@ -95,6 +95,47 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
 }
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Shared-memory accesses by 32-bit shared address. The kernel's shared-memory pointers travel
+// through a struct, where the compiler no longer knows their address space and falls back to
+// generic loads with 64-bit address arithmetic; the block loop states the space itself.
+__device__ __forceinline__ uint4 lds128(uint32_t address) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t address) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ float2 lds64f(uint32_t address) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ void sts32f(uint32_t address, float value) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(address), "f"(value) : "memory");
+}
+
+// One 16 x 128 block with every operand addressed in shared memory: `b_address` is where this
+// lane's B fragments of the block start (the staged row, or a zero page for the lanes whose
+// column belongs to the other group), `offset_address` the block's pair of 136*sum(x) values.
+__device__ __forceinline__ void mma_block_shared(const WeightItem& it, uint32_t b_address, uint32_t offset_address,
+                                                 float& lo, float& hi) {
+  const float2 off = lds64f(offset_address);
+  float c[4] = {-off.x, -off.y, -off.x, -off.y};
+  const uint32_t wl[4] = {it.lo.x, it.lo.y, it.lo.z, it.lo.w};
+  const uint32_t wh[4] = {it.hi.x, it.hi.y, it.hi.z, it.hi.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 b = lds128(b_address + j * 16);
+    mma_16816(c, AOTO_NIB(wl[j], 0), AOTO_NIB(wh[j], 0), AOTO_NIB(wl[j], 4), AOTO_NIB(wh[j], 4), b.x, b.y);
+    mma_16816(c, AOTO_NIB(wl[j], 8), AOTO_NIB(wh[j], 8), AOTO_NIB(wl[j], 12), AOTO_NIB(wh[j], 12), b.z, b.w);
+  }
+  lo = fmaf(bf16x2_lo(it.slo), c[0], bf16x2_hi(it.slo) * c[1]);
+  hi = fmaf(bf16x2_lo(it.shi), c[2], bf16x2_hi(it.shi) * c[3]);
+}
+
 __device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem_src) {
   const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(gmem_src) : "memory");
@@ -106,7 +147,7 @@ struct StepSmem {
   float* xsum;          // STEP_MAX_K / 64
   float* part;          // STEP_MAX_ITEMS * 16
   float* red;           // 64
-  int* flag;            // 4
+  int* flag;            // 4 ints, then a 64-byte zero page
   unsigned long long* bars;  // RING_SLOTS mbarriers
   uint32_t* ring_uses;       // completed phases of every ring slot
   unsigned char* tile;  // attention tiles, scores, row values; or the weight ring of a GEMV stage
@@ -382,6 +423,15 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
   bf16* out_plain = reinterpret_cast<bf16*>(st.out);
   unsigned char* out_words = reinterpret_cast<unsigned char*>(st.out);
   const BSource bs = b_source(sm.xs, reinterpret_cast<const uint4*>(sm.flag) + 1, lane);
+  // the same choice for the chunk loop, as shared addresses: lanes of the other group's column read
+  // a 64-byte zero page for every block, the others 64 bytes of the staged row per block
+  const bool keeps_x = ((g & 1) == (t >> 1));
+  const uint32_t b_address = keeps_x ? smem_address(sm.xs) + (uint32_t)t * 64 : smem_address(reinterpret_cast<const uint4*>(sm.flag) + 1);
+  const uint32_t b_step = keeps_x ? 256u : 0u;
+  const uint32_t xsum_address = smem_address(sm.xsum);
+  const uint32_t part_address = smem_address(sm.part) + (uint32_t)g * 4;
+  const uint32_t lane_item_offset = (uint32_t)(g * 64 + t * 16);   // codes of row g; row g + 8 is 512 bytes on
+  const uint32_t lane_scale_offset = 1024u + (uint32_t)g * 4 - lane_item_offset;  // relative to the slot address above
   float best_v = -INFINITY;
   int best_i = 0x7fffffff;
   int polls = 0;
@@ -464,24 +514,32 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
   for (int chunk = 0; chunk < (ring_mode ? 0 : chunks_total); ++chunk) {
     asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the newest group has landed
     __syncwarp();
-    const unsigned char* bank = my_slots + (size_t)(chunk & 1) * BANK_SLOTS * ITEM_BYTES;
-    for (int i = 0; i < BANK_SLOTS; ++i) {
-      const int idx = chunk * CHUNK_ITEMS + warp + i * STEP_WARPS;
-      if (idx >= total_items) break;
-      int tile, mat, kb;
-      locate(idx, &tile, &mat, &kb);
-      const unsigned char* slot = bank + (size_t)i * ITEM_BYTES;
-      WeightItem it;
-      it.lo = *reinterpret_cast<const uint4*>(slot + g * 64 + t * 16);
-      it.hi = *reinterpret_cast<const uint4*>(slot + (g + 8) * 64 + t * 16);
-      it.slo = *reinterpret_cast<const uint32_t*>(slot + 1024 + g * 4);
-      it.shi = *reinterpret_cast<const uint32_t*>(slot + 1024 + (g + 8) * 4);
-      float lo, hi;
-      mma_block(it, bs, kb, sm.xsum, lo, hi);
-      if (t == 0) {
-        float* dst = sm.part + (idx % PART_ITEMS) * 16;
-        dst[g] = lo;
-        dst[g + 8] = hi;
+    {
+      // this warp's blocks of the chunk are idx0, idx0 + 8, ...: position in the tile and in the
+      // ring of partial sums advance by eight per block, no division inside the loop
+      const int idx0 = chunk * CHUNK_ITEMS + warp;
+      const int count = idx0 < total_items ? min(BANK_SLOTS, (total_items - idx0 + STEP_WARPS - 1) / STEP_WARPS) : 0;
+      int j = idx0 - small_div(idx0, rp.inv_per_tile) * rp.per_tile;  // block within its tile
+      int pos = idx0 % PART_ITEMS;
+      uint32_t slot = smem_address(my_slots) + (uint32_t)((chunk & 1) * BANK_SLOTS * ITEM_BYTES) + lane_item_offset;
+      for (int i = 0; i < count; ++i) {
+        const int kb = j >= rp.nblocks ? j - rp.nblocks : j;
+        WeightItem it;
+        it.lo = lds128(slot);
+        it.hi = lds128(slot + 512);
+        it.slo = lds32(slot + lane_scale_offset);
+        it.shi = lds32(slot + lane_scale_offset + 32);
+        float lo, hi;
+        mma_block_shared(it, b_address + (uint32_t)kb * b_step, xsum_address + (uint32_t)kb * 8, lo, hi);
+        if (t == 0) {
+          sts32f(part_address + (uint32_t)pos * 64, lo);
+          sts32f(part_address + (uint32_t)pos * 64 + 32, hi);
+        }
+        slot += ITEM_BYTES;
+        j += STEP_WARPS;
+        while (j >= rp.per_tile) j -= rp.per_tile;
+        pos += STEP_WARPS;
+        if (pos >= PART_ITEMS) pos -= PART_ITEMS;
       }
     }
     __syncwarp();                // every lane has read the bank
@@ -1094,11 +1152,11 @@ decode_step_kernel(const aoto_step_stage* __restrict__ stages, int stage_count, 
   sm.part = sm.xsum + STEP_MAX_K / 64;
   sm.red = sm.part + STEP_MAX_ITEMS * 16;
   sm.flag = reinterpret_cast<int*>(sm.red + 64);
-  sm.bars = reinterpret_cast<unsigned long long*>(sm.flag + 8);
+  sm.bars = reinterpret_cast<unsigned long long*>(sm.flag + 20);
   sm.ring_uses = reinterpret_cast<uint32_t*>(sm.bars + RING_SLOTS);
   sm.tile = reinterpret_cast<unsigned char*>(sm.ring_uses + RING_SLOTS);
   if (threadIdx.x == 0) {
-    *(reinterpret_cast<uint4*>(sm.flag) + 1) = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = 1; i <= 4; ++i) *(reinterpret_cast<uint4*>(sm.flag) + i) = make_uint4(0u, 0u, 0u, 0u);
     for (int i = 0; i < RING_SLOTS; ++i) { mbar_init(sm.bars + i, 1); sm.ring_uses[i] = 0u; }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -1126,7 +1184,7 @@ decode_step_kernel(const aoto_step_stage* __restrict__ stages, int stage_count, 
 
 static size_t step_smem_bytes() {
   const size_t fixed = (size_t)STEP_MAX_K / 8 * 16 * 2 + (size_t)STEP_MAX_K / 64 * 4 +
-                       (size_t)STEP_MAX_ITEMS * 16 * 4 + 64 * 4 + 32 + (size_t)RING_SLOTS * (8 + 4);
+                       (size_t)STEP_MAX_ITEMS * 16 * 4 + 64 * 4 + 80 + (size_t)RING_SLOTS * (8 + 4);
   const size_t attention = (size_t)2 * ATT_TILE * (128 * 2 + 16) +
                            ((size_t)(MAX_GROUP + 2) * 128 + (size_t)MAX_GROUP * 128 + (size_t)MAX_GROUP * ATT_TILE +
                             (size_t)MAX_GROUP * 2 + ATT_TILE + (size_t)2 * MAX_GROUP * 128) * 4;
