@@ -481,21 +481,25 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
     for (int local_tile = warp; local_tile < rp.my_tiles; local_tile += STEP_WARPS, ++use) {
       const int slot = use % RING_DEPTH;
       if (!ring_wait(slot)) { ring_ok = false; break; }
-      const unsigned char* base = my_ring + (size_t)slot * RING_SLOT_BYTES;
-      const uint4* wsm = reinterpret_cast<const uint4*>(base);
-      const unsigned char* ssm = base + 16 * (K >> 1);
+      // shared addresses of this lane's codes (rows g and g + 8) and scale pairs in the slot
+      const uint32_t base = smem_address(my_ring) + (uint32_t)slot * RING_SLOT_BYTES;
+      uint32_t codes = base + (uint32_t)(g * row_u4 + t) * 16;
+      uint32_t pairs = base + 16u * (uint32_t)(K >> 1) + (uint32_t)(g * scale_row);
+      const uint32_t codes_hi = 8u * (uint32_t)row_u4 * 16, pairs_hi = 8u * (uint32_t)scale_row;
+      uint32_t b_at = b_address, x_at = xsum_address;
       float a_lo = 0.f, a_hi = 0.f;
 #pragma unroll 2
       for (int kb = 0; kb < rp.nblocks; ++kb) {
         WeightItem it;
-        it.lo = wsm[g * row_u4 + kb * 4 + t];
-        it.hi = wsm[(g + 8) * row_u4 + kb * 4 + t];
-        it.slo = *reinterpret_cast<const uint32_t*>(ssm + g * scale_row + kb * 4);
-        it.shi = *reinterpret_cast<const uint32_t*>(ssm + (g + 8) * scale_row + kb * 4);
+        it.lo = lds128(codes);
+        it.hi = lds128(codes + codes_hi);
+        it.slo = lds32(pairs);
+        it.shi = lds32(pairs + pairs_hi);
         float lo, hi;
-        mma_block(it, bs, kb, sm.xsum, lo, hi);
+        mma_block_shared(it, b_at, x_at, lo, hi);
         a_lo += lo;
         a_hi += hi;
+        codes += 64; pairs += 4; b_at += b_step; x_at += 8;
       }
       if (!marked) { trace_mark(ctl, stage_index, 3); marked = true; }
       __syncwarp();  // every lane is done with the slot before it is refilled
