@@ -565,14 +565,21 @@ __device__ bool stage_gemv(const aoto_step_stage& shared_stage, const StepSmem& 
       float y = 0.f;
       if (valid) {
         int base = (tl * rp.per_tile) % PART_ITEMS;
-        // fixed order: four interleaved partial sums over the k blocks, then their sum
+        const uint32_t row_address = smem_address(sm.part) + (uint32_t)r * 4;
+        // fixed order: four interleaved partial sums over the k blocks (in registers), then their sum
+        auto next = [&]() {
+          const float v = __uint_as_float(lds32(row_address + (uint32_t)base * 64));
+          if (++base == PART_ITEMS) base = 0;
+          return v;
+        };
         auto sum_blocks = [&]() {
-          float s[4] = {0.f, 0.f, 0.f, 0.f};
-          for (int kb = 0; kb < rp.nblocks; ++kb) {
-            s[kb & 3] += sm.part[base * 16 + r];
-            if (++base == PART_ITEMS) base = 0;
+          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+          int kb = 0;
+          for (; kb + 4 <= rp.nblocks; kb += 4) {
+            s0 += next(); s1 += next(); s2 += next(); s3 += next();
           }
-          return (s[0] + s[1]) + (s[2] + s[3]);
+          for (; kb < rp.nblocks; ++kb) s0 += next();
+          return (s0 + s1) + (s2 + s3);
         };
         const float total = sum_blocks();
         const float total2 = rp.mats == 2 ? sum_blocks() : 0.f;
