@@ -467,9 +467,9 @@ def run_ours(args) -> None:
             else "per-operation decode plan (CUDA graph of one step)",
             "bound": "hbm", "achieved": achieved_step, "peak": peak, "unit": "GB/s",
             "frac": achieved_step / peak,
-            # ncu on the same kernel over a 4-layer cut of this model read 105.2 MB of DRAM for
-            # 104.0 MB of algorithmic bytes; traffic grows with the layers like the bytes do
-            "traffic": int(bytes_step * 105.2 / 104.0),
+            # ncu on the same kernel over a 4-layer cut of this model moved 109.3 MB of DRAM (104.58 read
+            # + 4.73 written) for 104.0 MB of algorithmic bytes; traffic grows with the layers like the bytes
+            "traffic": int(bytes_step * 109.31 / 104.0),
             "bytes_per_launch": bytes_step, "us_per_launch": per_token_us,
             "frac_of_8tbs": achieved_step / 8000.0, "peak_source": peak_kind,
             "note": "launch duration = CUDA-event time of the decode loop / launches, inside the timed region",
