@@ -218,3 +218,44 @@ def test_step_kernel_matches_per_operation_plan(cuda):
     got = runtime.greedy_generate(prompt).cpu()[0].tolist()
     assert got == want, f"oracle top-2 gaps: {[top2_gap(t) for t in trace]}"
     assert rel_err(kernel.logits, trace[-1]) < REL_TOL
+
+
+def test_step_kernel_streams_long_block_lists(cuda):
+    """Stages whose block list per CTA spans several chunks (and tiles that span two chunks).
+
+    hidden 1024 and MLP 7168 with 8 x 128 heads and a 49 152-word vocabulary: the LM head
+    (K = 1024 is too wide for the ring form) gives every CTA ~21 tiles of 8 blocks = 3 chunks,
+    down has 56 blocks per tile, gate/up 16 per tile and 448 tiles. The persistent kernel and
+    the recorded per-operation plan must produce the same tokens and caches.
+    """
+
+    from aotolith_b200 import ops
+    from aotolith_b200.models.session import DecodeSession
+    from aotolith_b200.models.synthetic import SyntheticDecoder
+
+    model = SyntheticDecoder(
+        model_type="llama", vocab_size=49152, hidden_size=1024, intermediate_size=7168, num_hidden_layers=2,
+        num_attention_heads=8, num_key_value_heads=2, head_dim=128, max_position_embeddings=256, rope_theta=5e5,
+        rms_norm_eps=1e-5, attention_bias=False, tie_word_embeddings=False, seed=21,
+    )
+    runtime = aoto.compile_llama_static_cache(model, prompt_length=16, max_new_tokens=7, quantize=64)
+    assert runtime.decode.plan.step_program is not None
+    prompt = torch.randint(0, 49152, (1, 16), generator=torch.Generator().manual_seed(12))
+    logits, compact = runtime.prefill_ids(prompt)
+    cache = runtime.pad_cache(compact)
+    token = ops.argmax(logits[:, -1, :]).reshape(1, 1)
+    kernel = DecodeSession(runtime)
+    assert kernel.mode == "kernel"
+    program = runtime.decode.plan.step_program
+    runtime.decode.plan.step_program = None
+    try:
+        graphs = DecodeSession(runtime)
+    finally:
+        runtime.decode.plan.step_program = program
+    a = kernel.run(token, cache, 16, 6).cpu()
+    b = graphs.run(token, cache, 16, 6).cpu()
+    assert a.tolist() == b.tolist()
+    assert rel_err(kernel.final_cache(6), graphs.final_cache(6)) < REL_TOL
+    want, trace, _ = OracleRuntime(runtime).greedy(prompt, 7)
+    got = runtime.greedy_generate(prompt).cpu()[0].tolist()
+    assert got == want, f"oracle top-2 gaps: {[top2_gap(t) for t in trace]}"
