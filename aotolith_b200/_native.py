@@ -155,6 +155,14 @@ STAGE_ADDEND_NONE, STAGE_ADDEND_PLAIN, STAGE_ADDEND_STAMPED, STAGE_ADDEND_GATHER
 
 
 #: symbol -> (restype, argtypes); one entry per declaration in include/aoto_sm100.h
+class PeerSumArgs(Structure):
+    _fields_ = [
+        ("buffers", POINTER(c_void_p)), ("partial", c_void_p), ("out", c_void_p), ("epoch", c_void_p),
+        ("status", c_void_p),
+        ("world", c_int32), ("rank", c_int32), ("count", c_int32), ("capacity_words", c_int32),
+    ]
+
+
 EXPORTS: dict[str, tuple] = {
     "aoto_sm100_abi_version": (c_int, []),
     "aoto_sm100_compiled_arch": (c_int, []),
@@ -183,6 +191,8 @@ EXPORTS: dict[str, tuple] = {
     "aoto_sm100_attention_scratch_bytes": (c_int64, [POINTER(AttentionArgs)]),
     "aoto_sm100_attention_decode_static": (c_int, [POINTER(AttentionArgs), c_void_p]),
     "aoto_sm100_attention_static_scratch_limit": (c_int64, []),
+    "aoto_sm100_peer_sum": (c_int, [POINTER(PeerSumArgs), c_void_p]),
+    "aoto_sm100_peer_sum_buffer_bytes": (c_int64, [c_int32, c_int32]),
 }
 
 _lib = None

@@ -12,6 +12,9 @@ shape) shard the Megatron way, one process per GPU:
   ONE all-reduce per attention block and ONE per MLP block combines them. The
   residual is folded into rank 0's partial (the GEMV/GEMM addend), so the
   reduced tensor already is the new hidden state on every rank;
+* in decode that all-reduce is one launch of ``aoto_sm100_peer_sum`` per rank: stamped 8-byte
+  stores into every peer's receive buffer over NVLink and a poll of the own buffer, no library
+  collective (``aotolith_b200.peer``); prefill rows (megabytes) go through NCCL;
 * the LM head is split over the vocabulary; ranks all-gather their logits
   slices and take the argmax of the whole row;
 * embeddings, norms and rotary tables are replicated.
@@ -101,7 +104,8 @@ class TensorParallelDecoder:
     """One rank's shard of a packed decoder plus the greedy loop over it."""
 
     def __init__(self, model: torch.nn.Module, *, prompt_length: int, max_new_tokens: int, group_size: int = 64,
-                 world: int | None = None, rank: int | None = None, device: Any = None, group: Any = None) -> None:
+                 world: int | None = None, rank: int | None = None, device: Any = None, group: Any = None,
+                 peer_exchange: bool = True) -> None:
         from . import ops  # the CUDA path: fails loudly without the kernel library
 
         self.ops = ops
@@ -168,11 +172,21 @@ class TensorParallelDecoder:
         self.generated = torch.zeros(max(self.max_new_tokens, 1), dtype=torch.int64, device=self.device)
         self.logits = torch.zeros((1, self.vocab), dtype=torch.bfloat16, device=self.device)
         self.graphs: list[torch.cuda.CUDAGraph] = []
+        # Decode all-reduces move one hidden-state row (a few KB): a kernel of this library over
+        # peer memory replaces the NCCL call there; prefill rows (MBs) stay with NCCL.
+        self.peer = None
+        if peer_exchange and self.world > 1:
+            from .peer import PeerSum
+
+            self.peer = PeerSum(self.hidden, group=group, device=self.device)
 
     # -- collectives -------------------------------------------------------------
     def _all_reduce(self, tensor: torch.Tensor) -> torch.Tensor:
         if self.world > 1:
-            dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.group)
+            if self.peer is not None and tensor.numel() <= self.hidden and tensor.is_contiguous():
+                self.peer.sum_(tensor)
+            else:
+                dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.group)
         return tensor
 
     def _gather_logits(self, local: torch.Tensor) -> torch.Tensor:
@@ -282,6 +296,8 @@ class TensorParallelDecoder:
         torch.cuda.synchronize(self.device)
         self.graphs.clear()
         torch.cuda.synchronize(self.device)
+        if self.peer is not None:
+            self.peer.check()
 
     def greedy_generate(self, ids: torch.Tensor, *, max_new_tokens: int | None = None, use_graphs: bool = True) -> torch.Tensor:
         """Prefill ``ids`` and decode greedily; every rank returns the same ``[1, steps]`` tokens."""

@@ -355,6 +355,37 @@ int aoto_sm100_attention_decode_static(const aoto_attention_args* args, void* st
 int64_t aoto_sm100_attention_static_scratch_limit(void);
 
 /* ------------------------------------------------------------------------- */
+/* Small all-reduce over peer memory (tensor-parallel decode)                 */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * Sum of one bf16 row per rank, delivered to every rank, in one launch per rank and with no
+ * library collective: each rank stores its row as 8-byte stamped words (two values + the call's
+ * epoch) into a receive buffer of every peer and polls its own buffer for all contributions,
+ * which it adds in rank order in fp32. No counterpart in the reference (it has no multi-device
+ * path); it replaces an NCCL all-reduce where the payload is a few KB and latency is everything.
+ *
+ *  - `buffers[q]` is rank q's receive buffer AS MAPPED IN THE CALLING PROCESS (peer-accessible
+ *    memory, e.g. torch symmetric memory); every buffer is aoto_sm100_peer_sum_buffer_bytes()
+ *    long, 8-byte aligned, and zero before the first call;
+ *  - `epoch` is a device word, zero before the first call, that the kernel advances: all ranks
+ *    must make the same sequence of calls with the same `count`;
+ *  - every poll is bounded; when one runs out `*status` is set to 1 and the output is undefined;
+ *  - the ranks' kernels wait on one another: one rank per GPU, never several ranks on one GPU.
+ */
+typedef struct aoto_peer_sum_args {
+  void* const* buffers;   /* `world` device pointers (a host array)                 */
+  const void* partial;    /* bf16 [count], this rank's addend                        */
+  void* out;              /* bf16 [count], may alias partial                         */
+  void* epoch;            /* uint32 device word                                      */
+  void* status;           /* int32 device word or NULL                               */
+  int32_t world, rank, count, capacity_words;
+} aoto_peer_sum_args;
+
+int aoto_sm100_peer_sum(const aoto_peer_sum_args* args, void* stream);
+int64_t aoto_sm100_peer_sum_buffer_bytes(int32_t world, int32_t capacity_words);
+
+/* ------------------------------------------------------------------------- */
 /* A whole decode step as one persistent kernel                              */
 /* ------------------------------------------------------------------------- */
 

@@ -53,7 +53,7 @@ def test_library_exports_every_declared_function():
     ("aoto_step_stage", N.StepStage), ("aoto_decode_step_args", N.DecodeStepArgs),
     ("aoto_dequantize_args", N.DequantizeArgs), ("aoto_rms_norm_args", N.RmsNormArgs),
     ("aoto_rope_args", N.RopeArgs), ("aoto_embedding_args", N.EmbeddingArgs),
-    ("aoto_kv_append_args", N.KvAppendArgs),
+    ("aoto_kv_append_args", N.KvAppendArgs), ("aoto_peer_sum_args", N.PeerSumArgs),
 ])
 def test_struct_fields_follow_the_header(c_name, struct):
     assert [name for name, _ in struct._fields_] == _header_struct_fields(c_name)
@@ -94,6 +94,16 @@ def test_qmatmul_queries_are_host_only():
     # null pointers are refused before anything reaches the CUDA runtime
     assert lib.aoto_sm100_qmatmul(ctypes.byref(_qargs(1, 1152, 896, 64)), None) == N.ERR_ARGUMENT
     assert lib.aoto_sm100_qmatmul(None, None) == N.ERR_ARGUMENT
+
+
+def test_peer_sum_refuses_bad_requests_on_the_host():
+    lib = N.load()
+    assert lib.aoto_sm100_peer_sum_buffer_bytes(2, 2048) == 2 * 2 * 2048 * 8
+    assert lib.aoto_sm100_peer_sum_buffer_bytes(9, 2048) == 0      # at most eight ranks
+    assert lib.aoto_sm100_peer_sum(None, None) == N.ERR_ARGUMENT
+    args = N.PeerSumArgs()
+    args.world, args.rank, args.count, args.capacity_words = 2, 0, 4096, 2048
+    assert lib.aoto_sm100_peer_sum(ctypes.byref(args), None) == N.ERR_ARGUMENT   # null pointers
 
 
 def test_scratch_size_queries():

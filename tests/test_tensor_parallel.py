@@ -126,16 +126,28 @@ def test_world_of_one_matches_the_compiled_runtime(cuda):
 
 def _gpu_rank(rank, world, port, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
-                      NCCL_NVLS_ENABLE="0")
+                      NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         decoder = tp.TensorParallelDecoder(_tiny(), prompt_length=PROMPT, max_new_tokens=NEW, group_size=GROUP)
+        assert decoder.peer is not None
         tokens = decoder.greedy_generate(_prompt()).cpu()
         logits = decoder.prefill(_prompt()).float().cpu()
-        torch.save({"tokens": tokens, "logits": logits}, os.path.join(out_dir, f"gpu{rank}.pt"))
+        # the same steps with the library collective instead of the peer-memory kernel
+        plain = tp.TensorParallelDecoder(_tiny(), prompt_length=PROMPT, max_new_tokens=NEW, group_size=GROUP,
+                                         peer_exchange=False)
+        plain_tokens = plain.greedy_generate(_prompt()).cpu()
+        # the exchange alone: every rank contributes rank + 1 in every element
+        row = torch.full((1, 64), float(rank + 1), dtype=torch.bfloat16, device=f"cuda:{rank}")
+        for _ in range(5):
+            row.fill_(float(rank + 1))
+            decoder.peer.sum_(row)
+        torch.save({"tokens": tokens, "logits": logits, "plain_tokens": plain_tokens, "row": row.float().cpu()},
+                   os.path.join(out_dir, f"gpu{rank}.pt"))
         dist.barrier()
         decoder.close()
+        plain.close()
     finally:
         dist.destroy_process_group()
 
@@ -152,6 +164,9 @@ def test_two_nccl_ranks_generate_what_one_rank_does(cuda, tmp_path):
     mp.start_processes(_gpu_rank, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True, start_method="spawn")
     results = [torch.load(tmp_path / f"gpu{r}.pt", weights_only=False) for r in range(2)]
     assert torch.equal(results[0]["tokens"], results[1]["tokens"])
+    for result in results:
+        assert torch.equal(result["tokens"], result["plain_tokens"])     # same sum, different transport
+        assert torch.equal(result["row"], torch.full((1, 64), 3.0))       # 1 + 2 on every rank
     # partial sums are rounded to bf16 before the all-reduce: logits agree within the toy-model tolerance
     scale = float(want_logits.abs().max())
     assert float((results[0]["logits"] - want_logits).abs().max()) <= 3e-2 * scale
