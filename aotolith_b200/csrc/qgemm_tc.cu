@@ -415,8 +415,8 @@ int* timeout_flag_on_current_device() {
 
 bool qgemm_tc_applies(const aoto_qmatmul_args& a) {
   // a 128-row tile is the smallest the tensor core takes: worth it from 64 rows on, or from 8 rows
-  // when the weight is large enough that converting it dominates
-  return (a.M >= 64 || (a.M >= 8 && a.N >= 4096)) && a.N >= 64 && a.group_size == 64 && (a.K % TC_BK) == 0 && a.norm_weight == nullptr &&
+  // when the weight is large enough (many rows, or a long K) that converting it dominates
+  return (a.M >= 64 || (a.M >= 8 && (a.N >= 4096 || a.K >= 2048))) && a.N >= 64 && a.group_size == 64 && (a.K % TC_BK) == 0 && a.norm_weight == nullptr &&
          a.epilogue != AOTO_EPILOGUE_SILU_MUL_PAIRED && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 &&
          (reinterpret_cast<uintptr_t>(a.packed) & 15) == 0;
 }

@@ -153,7 +153,7 @@ def test_qmatmul_rows(cuda, M, K, N):
     x = activations(31, M, K)
     bias = activations(32, N, std=0.5)
     if K % 128 == 0:
-        assert ops.qmatmul_variant(M, N, K, group) == ("gemm_tcgen05" if M >= 64 or (M >= 8 and N >= 4096) else "gemm_mma")
+        assert ops.qmatmul_variant(M, N, K, group) == ("gemm_tcgen05" if M >= 64 or (M >= 8 and (N >= 4096 or K >= 2048)) else "gemm_mma")
     got = ops.qmatmul(x.to(cuda), packed.to(cuda), scales.to(cuda), group_size=group, addend=bias.to(cuda)).cpu()
     want = ref.packed_matmul(x, packed, scales, group, addend=bias)
     assert got.shape == (M, N)
