@@ -692,6 +692,7 @@ def run_probe(name: str) -> None:
 
     ``lm_head``  six packed GEMV launches over three copies of a [151936, 896] weight (RMS norm fused);
     ``gemm``     six packed GEMM launches, K=4096 N=14336 M=1024, over five weight copies;
+    ``attention`` six launches of prefill attention, 32 query / 8 kv heads, 1024 x 1024, D = 128, causal mask;
     ``step``     a 4-layer Qwen2.5-0.5B-shaped decoder: prefill, then six launches of the step kernel;
     ``trace``    the same, then one more step with the kernel's own per-stage timeline printed;
     ``trace_llama`` the timeline for a 2-layer cut of the Llama-3-8B shape (prompt 128).
@@ -712,6 +713,24 @@ def run_probe(name: str) -> None:
             ops.qmatmul(x, packs[i % 3], scales[i % 3], group_size=GROUP, norm_weight=norm, rms_norm_eps=1e-6, out=out)
         torch.cuda.synchronize()
         print(json.dumps({"probe": name, "variant": ops.qmatmul_variant(1, N, K, GROUP), "max": float(out.float().abs().max())}))
+    elif name == "attention":
+        heads, kv_heads, length, dim = 32, 8, 1024, 128
+        q = torch.randn(1, heads, length, dim, generator=generator).bfloat16().to(device)
+        k = torch.randn(1, kv_heads, length, dim, generator=generator).bfloat16().to(device)
+        v = torch.randn(1, kv_heads, length, dim, generator=generator).bfloat16().to(device)
+        causal = torch.ones((length, length), dtype=torch.bool).tril()[None, None].to(device)
+        mask = ops.mask_select(causal, 0.0, float("-inf"))
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(6):
+            if i == 1:
+                start.record()
+            out = ops.attention(q, k, v, mask, scale=dim ** -0.5)
+        stop.record()
+        torch.cuda.synchronize()
+        us = start.elapsed_time(stop) * 1e3 / 5
+        flops = 4.0 * heads * length * length * dim
+        print(json.dumps({"probe": name, "us": us, "tflops_dense": flops / us / 1e6, "tflops_causal_half": flops / 2 / us / 1e6,
+                          "max": float(out.float().abs().max())}))
     elif name == "gemm":
         K, N, M = 4096, 14336, 1024
         packs = [torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, generator=generator).to(device) for _ in range(5)]
@@ -755,7 +774,7 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="qwen25_05b")
     parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
-    parser.add_argument("--probe", choices=("lm_head", "gemm", "step", "trace", "trace_llama"), default=None,
+    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "step", "trace", "trace_llama"), default=None,
                         help="run a small fixed case of one kernel for a profiler instead of the benchmark")
     args = parser.parse_args()
     if args.probe is not None:
