@@ -263,7 +263,15 @@ static void decode_tiling(const aoto_attention_args& a, int* keys_per_split, int
 using namespace aoto;
 
 extern "C" int64_t aoto_sm100_attention_scratch_bytes(const aoto_attention_args* a) {
-  if (!a || a->q_len != 1 || a->kv_len <= 0 || a->head_dim <= 0) return 0;
+  if (!a || a->q_len <= 0 || a->kv_len <= 0 || a->head_dim <= 0) return 0;
+  if (a->q_len > 1) {
+    // the tiled prefill kernel classifies the tiles of a long mask into an optional workspace
+    AttnParams p = {};
+    p.q = (const bf16*)a->q; p.k = (const bf16*)a->k; p.v = (const bf16*)a->v;
+    p.mask = (const bf16*)a->mask; p.out = (bf16*)a->out;
+    p.Lq = a->q_len; p.Lk = a->kv_len; p.D = a->head_dim;
+    return attention_prefill_scratch_bytes(p);
+  }
   int tile, splits;
   decode_tiling(*a, &tile, &splits);
   if (splits == 1) return 0;
@@ -278,7 +286,7 @@ extern "C" int aoto_sm100_attention(const aoto_attention_args* a, void* stream_)
   if (a->query_heads % a->kv_heads != 0) return AOTO_ERR_ARGUMENT;
   if ((a->head_dim & 1) || a->head_dim > 256) return AOTO_ERR_UNSUPPORTED;
   if (!aligned_to(a->k, 4) || !aligned_to(a->v, 4)) return AOTO_ERR_ARGUMENT;
-  AttnParams p;
+  AttnParams p = {};
   p.q = (const bf16*)a->q; p.k = (const bf16*)a->k; p.v = (const bf16*)a->v;
   p.mask = (const bf16*)a->mask; p.out = (bf16*)a->out; p.scratch = (float*)a->scratch;
   p.QH = a->query_heads; p.KVH = a->kv_heads; p.Lq = a->q_len; p.Lk = a->kv_len; p.D = a->head_dim;
@@ -312,7 +320,7 @@ extern "C" int aoto_sm100_attention(const aoto_attention_args* a, void* stream_)
   }
   p.splits = 1;
   p.keys_per_split = 0;
-  if (attention_prefill_mma_applies(p)) return attention_prefill_mma_launch(p, stream);
+  if (attention_prefill_mma_applies(p)) return attention_prefill_mma_launch(p, a->scratch ? a->scratch_bytes : 0, stream);
   const int64_t rows = (int64_t)a->query_heads * a->q_len;
   const size_t smem = (size_t)PREFILL_WARPS * a->head_dim * 4;
   return launch_kernel(attention_prefill_kernel, dim3((unsigned)((rows + PREFILL_WARPS - 1) / PREFILL_WARPS)),
@@ -366,7 +374,7 @@ extern "C" int64_t aoto_sm100_attention_static_scratch_limit(void) { return AOTO
 
 extern "C" int aoto_sm100_attention_decode_static(const aoto_attention_args* a, void* stream_) {
   if (!a) return AOTO_ERR_ARGUMENT;
-  if (a->q_len != 1) return AOTO_ERR_UNSUPPORTED;  // the prefill kernel uses no scratch: call aoto_sm100_attention
+  if (a->q_len != 1) return AOTO_ERR_UNSUPPORTED;  // the prefill kernel runs without a workspace: call aoto_sm100_attention
   const int64_t need = aoto_sm100_attention_scratch_bytes(a);
   if (need > AOTO_STATIC_SCRATCH_BYTES) return AOTO_ERR_TOO_LARGE;
   void* scratch = static_scratch_on_current_device();

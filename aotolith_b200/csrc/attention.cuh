@@ -12,6 +12,8 @@ struct AttnParams {
   const bf16* mask;
   bf16* out;
   float* scratch;
+  const unsigned char* tile_classes;  // prefill: class of every (query tile, key tile) of the mask, or nullptr
+  int key_tiles;                      // prefill: key tiles per query tile in tile_classes
   int QH, KVH, Lq, Lk, D;
   int causal, splits, keys_per_split;
   float scale;
@@ -19,6 +21,7 @@ struct AttnParams {
 
 // Tiled tensor-pipe prefill attention (attention_prefill.cu).
 bool attention_prefill_mma_applies(const AttnParams& p);
-int attention_prefill_mma_launch(const AttnParams& p, cudaStream_t stream);
+int64_t attention_prefill_scratch_bytes(const AttnParams& p);
+int attention_prefill_mma_launch(const AttnParams& p, int64_t scratch_bytes, cudaStream_t stream);
 
 }  // namespace aoto

@@ -7,11 +7,18 @@
 // accumulators; V fragments are read with a transposing ldmatrix. Scores are scaled in fp32,
 // the additive mask (0 / -inf, any pattern: causal, left padding) is applied per element, rows
 // with no admitted key produce zeros.
+#include <type_traits>
+
 #include "attention.cuh"
 
 namespace aoto {
 
 constexpr int PF_BQ = 64, PF_BK = 64, PF_THREADS = 128;
+constexpr int PF_MAX_KEY_TILES = 1024;  // key tiles a CTA keeps classes for (65 536 keys)
+constexpr unsigned char PF_TILE_NONE = 0, PF_TILE_MIXED = 1, PF_TILE_ZERO = 2;
+constexpr int PF_CLASS_WARPS = 8;
+constexpr int PF_MASK_NONE = 0, PF_MASK_PAIRS = 1, PF_MASK_SINGLE = 2;
+constexpr int PF_CLASS_MIN_KEYS = 256;  // shorter windows have too few tiles to pay for the extra launch
 
 __device__ __forceinline__ void pf_cp16(void* smem_dst, const void* gmem_src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
@@ -29,6 +36,40 @@ __device__ __forceinline__ void pf_mma(float (&c)[4], const uint32_t (&a)[4], ui
 __device__ __forceinline__ void pf_ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* smem_row) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];"
                : "=r"(r0), "=r"(r1) : "r"((uint32_t)__cvta_generic_to_shared(smem_row)));
+}
+
+// One warp per (64 query rows, 64 keys) tile of the additive mask: 512 16-byte chunks, sixteen per
+// lane and all in flight at once. The class goes to classes[q_tile * key_tiles + key_tile].
+__global__ void __launch_bounds__(PF_CLASS_WARPS * 32)
+attention_mask_classes_kernel(const bf16* __restrict__ mask, unsigned char* __restrict__ classes,
+                              int Lq, int Lk, int q_tiles, int key_tiles) {
+  const int lane = threadIdx.x & 31;
+  const int tile = blockIdx.x * PF_CLASS_WARPS + (threadIdx.x >> 5);
+  if (tile >= q_tiles * key_tiles) return;
+  const int qt = tile / key_tiles, kt = tile - qt * key_tiles;
+  const int q0 = qt * PF_BQ, k0 = kt * PF_BK;
+  uint4 m[16];
+  bool inside[16];
+#pragma unroll
+  for (int u = 0; u < 16; ++u) {
+    const int c = lane + 32 * u;
+    const int row = q0 + (c >> 3), key = k0 + (c & 7) * 8;   // Lk is a multiple of 8: a chunk is inside or outside
+    inside[u] = row < Lq && key < Lk;
+    m[u] = make_uint4(0u, 0u, 0u, 0u);
+    if (inside[u]) m[u] = *reinterpret_cast<const uint4*>(mask + (size_t)row * Lk + key);
+  }
+  bool any_admitted = false, all_zero = true;
+#pragma unroll
+  for (int u = 0; u < 16; ++u) {
+    if (inside[u]) {
+      // -inf in bf16 is 0xFF80: a word of two excluded keys is 0xFF80FF80; two zeros are 0
+      any_admitted |= m[u].x != 0xFF80FF80u || m[u].y != 0xFF80FF80u || m[u].z != 0xFF80FF80u || m[u].w != 0xFF80FF80u;
+      all_zero &= (m[u].x | m[u].y | m[u].z | m[u].w) == 0u;
+    }
+  }
+  any_admitted = __any_sync(0xffffffffu, any_admitted);
+  all_zero = __all_sync(0xffffffffu, all_zero);
+  if (lane == 0) classes[tile] = !any_admitted ? PF_TILE_NONE : (all_zero ? PF_TILE_ZERO : PF_TILE_MIXED);
 }
 
 template <int D>
@@ -62,9 +103,32 @@ attention_prefill_mma_kernel(const AttnParams p) {
       else *reinterpret_cast<uint4*>(to) = make_uint4(0u, 0u, 0u, 0u);
     }
   };
+  // Classes of the key tiles for this tile of query rows, written by attention_mask_classes_kernel
+  // when the caller gave a workspace: 0 = no key admitted (the tile is neither loaded nor
+  // multiplied), 2 = the mask adds zero everywhere (no mask loads), 1 = mixed. With a causal
+  // prompt mask that halves the work and confines the mask loads to the diagonal tiles; with left
+  // padding it drops the padded keys.
+  __shared__ unsigned char tile_class[PF_MAX_KEY_TILES];
+  const bool classed = p.tile_classes != nullptr;
+  const bool mask_pairs = (Lk & 1) == 0 && (reinterpret_cast<uintptr_t>(p.mask) & 3) == 0;
+  if (classed) {
+    const unsigned char* mine = p.tile_classes + (size_t)blockIdx.x * p.key_tiles;
+    for (int i = tid; i < tiles; i += PF_THREADS) tile_class[i] = mine[i];
+    __syncthreads();
+  }
+  auto tile_admitted = [&](int j) { return !classed || tile_class[j] != PF_TILE_NONE; };
+  // the admitted tiles in order: `next_tile(j)` is the first admitted tile at or after j
+  auto next_tile = [&](int j) {
+    while (j < tiles && !tile_admitted(j)) ++j;
+    return j;
+  };
+  const int first = next_tile(0);
+
   load_rows(qs, qbase, q0, Lq);
-  load_rows(ks, kbase, 0, Lk);
-  load_rows(vs, vbase, 0, Lk);
+  if (first < tiles) {
+    load_rows(ks, kbase, first * PF_BK, Lk);
+    load_rows(vs, vbase, first * PF_BK, Lk);
+  }
   asm volatile("cp.async.commit_group;" ::: "memory");
 
   float o[DTILES][4];
@@ -74,18 +138,21 @@ attention_prefill_mma_kernel(const AttnParams p) {
   uint32_t qa[KSTEPS][4];
   const int row_lo = q0 + warp * 16 + g, row_hi = row_lo + 8;
 
-  for (int j = 0; j < tiles; ++j) {
-    const int stage = j & 1;
-    if (j + 1 < tiles) {
-      load_rows(ks + (size_t)(stage ^ 1) * PF_BK * PITCH, kbase, (j + 1) * PF_BK, Lk);
-      load_rows(vs + (size_t)(stage ^ 1) * PF_BK * PITCH, vbase, (j + 1) * PF_BK, Lk);
+  int stage = 0;
+  bool have_q = false;
+  for (int j = first; j < tiles; stage ^= 1) {
+    const int following = next_tile(j + 1);
+    if (following < tiles) {
+      load_rows(ks + (size_t)(stage ^ 1) * PF_BK * PITCH, kbase, following * PF_BK, Lk);
+      load_rows(vs + (size_t)(stage ^ 1) * PF_BK * PITCH, vbase, following * PF_BK, Lk);
       asm volatile("cp.async.commit_group;" ::: "memory");
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    if (j == 0) {
+    if (!have_q) {
+      have_q = true;
       const unsigned char* qlo = qs + (size_t)(warp * 16 + g) * PITCH;
       const unsigned char* qhi = qlo + 8 * PITCH;
 #pragma unroll
@@ -112,23 +179,44 @@ attention_prefill_mma_kernel(const AttnParams p) {
       }
     }
 
-    // scale, mask, running maximum
+    // Scale, mask, running maximum. Three forms of the mask term, chosen per tile and the same for
+    // the whole warp: none (no mask, or a tile where it adds zero everywhere), pairs of neighbouring
+    // keys in one 32-bit load (even window, 4-byte aligned mask), single elements.
     float tile_max[2] = {-INFINITY, -INFINITY};
+    auto scores = [&](auto mode_tag) {
+      constexpr int MODE = decltype(mode_tag)::value;
+      const int key_base = j * PF_BK + 2 * t;
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+      for (int h = 0; h < 2; ++h) {
+        const int row = h ? row_hi : row_lo;
+        const bf16* mask_row = MODE != PF_MASK_NONE ? p.mask + (size_t)row * Lk + key_base : nullptr;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int row = (e & 2) ? row_hi : row_lo;
-        const int key = j * PF_BK + n * 8 + 2 * t + (e & 1);
-        float value = -INFINITY;
-        if (row < Lq && key < Lk && !(p.causal && key > row)) {
-          const float add = p.mask ? __bfloat162float(p.mask[(size_t)row * Lk + key]) : 0.f;
-          value = s[n][e] * p.scale + add;
+        for (int n = 0; n < 8; ++n) {
+          const int key = key_base + n * 8;
+          float add0 = 0.f, add1 = 0.f;
+          if (MODE == PF_MASK_PAIRS) {
+            if (row < Lq && key < Lk) {  // the window is even: key + 1 is inside as well
+              const uint32_t pair = *reinterpret_cast<const uint32_t*>(mask_row + n * 8);
+              add0 = __uint_as_float(pair << 16);
+              add1 = __uint_as_float(pair & 0xFFFF0000u);
+            }
+          } else if (MODE == PF_MASK_SINGLE) {
+            if (row < Lq && key < Lk) add0 = __bfloat162float(mask_row[n * 8]);
+            if (row < Lq && key + 1 < Lk) add1 = __bfloat162float(mask_row[n * 8 + 1]);
+          }
+          const bool in0 = row < Lq && key < Lk && !(p.causal && key > row);
+          const bool in1 = row < Lq && key + 1 < Lk && !(p.causal && key + 1 > row);
+          const float v0 = in0 ? s[n][2 * h] * p.scale + add0 : -INFINITY;
+          const float v1 = in1 ? s[n][2 * h + 1] * p.scale + add1 : -INFINITY;
+          s[n][2 * h] = v0;
+          s[n][2 * h + 1] = v1;
+          tile_max[h] = fmaxf(tile_max[h], fmaxf(v0, v1));
         }
-        s[n][e] = value;
-        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], value);
       }
-    }
+    };
+    if (p.mask == nullptr || (classed && tile_class[j] == PF_TILE_ZERO)) scores(std::integral_constant<int, PF_MASK_NONE>());
+    else if (mask_pairs) scores(std::integral_constant<int, PF_MASK_PAIRS>());
+    else scores(std::integral_constant<int, PF_MASK_SINGLE>());
     float correction[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -171,6 +259,7 @@ attention_prefill_mma_kernel(const AttnParams p) {
       }
     }
     __syncthreads();  // the other stage is refilled at the top of the next iteration
+    j = following;
   }
 
 #pragma unroll
@@ -196,6 +285,17 @@ bool attention_prefill_mma_applies(const AttnParams& p) {
   return (p.D == 64 || p.D == 128) && p.Lq >= 16 && (bits & 15) == 0;
 }
 
+// Workspace the tile classes want (behind the counter header every workspace starts with), or 0
+// when the mask is absent, short or not addressable in 16-byte chunks.
+int64_t attention_prefill_scratch_bytes(const AttnParams& p) {
+  if (!attention_prefill_mma_applies(p) || p.mask == nullptr || p.Lk < PF_CLASS_MIN_KEYS || (p.Lk & 7) != 0 ||
+      (reinterpret_cast<uintptr_t>(p.mask) & 15) != 0)
+    return 0;
+  const int64_t q_tiles = (p.Lq + PF_BQ - 1) / PF_BQ, key_tiles = (p.Lk + PF_BK - 1) / PF_BK;
+  if (key_tiles > PF_MAX_KEY_TILES) return 0;
+  return SCRATCH_HEADER_BYTES + ((q_tiles * key_tiles + 15) & ~(int64_t)15);
+}
+
 template <int D>
 static int launch_prefill(const AttnParams& p, cudaStream_t stream) {
   constexpr size_t smem = (size_t)(PF_BQ + 4 * PF_BK) * (D * 2 + 16);
@@ -211,7 +311,22 @@ static int launch_prefill(const AttnParams& p, cudaStream_t stream) {
   return launch_kernel(attention_prefill_mma_kernel<D>, grid, dim3(PF_THREADS), smem, stream, false, p);
 }
 
-int attention_prefill_mma_launch(const AttnParams& p, cudaStream_t stream) {
+int attention_prefill_mma_launch(const AttnParams& given, int64_t scratch_bytes, cudaStream_t stream) {
+  AttnParams p = given;
+  p.tile_classes = nullptr;
+  p.key_tiles = 0;
+  // The workspace is optional: without it every tile is visited and the mask is read element by element.
+  const int64_t need = attention_prefill_scratch_bytes(p);
+  if (need > 0 && p.scratch != nullptr && scratch_bytes >= need) {
+    const int q_tiles = (p.Lq + PF_BQ - 1) / PF_BQ;
+    p.key_tiles = (p.Lk + PF_BK - 1) / PF_BK;
+    unsigned char* classes = reinterpret_cast<unsigned char*>(p.scratch) + SCRATCH_HEADER_BYTES;
+    p.tile_classes = classes;
+    const int warps = q_tiles * p.key_tiles;
+    const int status = launch_kernel(attention_mask_classes_kernel, dim3((warps + PF_CLASS_WARPS - 1) / PF_CLASS_WARPS),
+                                     dim3(PF_CLASS_WARPS * 32), 0, stream, false, p.mask, classes, p.Lq, p.Lk, q_tiles, p.key_tiles);
+    if (status != AOTO_OK) return status;
+  }
   return p.D == 64 ? launch_prefill<64>(p, stream) : launch_prefill<128>(p, stream);
 }
 

@@ -297,6 +297,12 @@ int aoto_sm100_kv_cache_append(const aoto_kv_append_args* args, void* stream);
  * bf16 [Lq,Lk] (0 / -inf) or NULL, `causal` adds the top-left aligned causal
  * rule. out [1,QH,Lq,D]. Lq == 1 selects the split-KV decode kernel, which
  * needs `scratch` of aoto_sm100_attention_scratch_bytes() when it splits.
+ * Lq > 1 with a mask over 256 or more keys can use a workspace of the same
+ * query's size: a small first kernel classifies every 64 x 64 tile of the mask
+ * (no key admitted / adds zero everywhere / mixed) and the attention kernel
+ * passes over the first kind and reads no mask in the second. That workspace is
+ * optional: with scratch NULL or too small the result is the same, every tile
+ * is visited and the mask is read element by element.
  *
  * Scratch contract (the same for every entry point that takes `scratch`): the
  * first 4096 bytes hold arrival counters and must be zero before the FIRST use;
@@ -348,7 +354,8 @@ int64_t aoto_sm100_attention_scratch_bytes(const aoto_attention_args* args);
  *    contents; the entry point clears the part that must start at zero on the given stream, but
  *    two calls whose kernels can overlap on the GPU (different streams, no dependency) race on
  *    it and must be serialised by the caller;
- *  - q_len must be 1 (AOTO_ERR_UNSUPPORTED otherwise: the multi-query kernel needs no scratch).
+ *  - q_len must be 1 (AOTO_ERR_UNSUPPORTED otherwise: the multi-query kernel runs without a
+ *    workspace through aoto_sm100_attention).
  */
 #define AOTO_STATIC_SCRATCH_BYTES (1 << 20)
 int aoto_sm100_attention_decode_static(const aoto_attention_args* args, void* stream);

@@ -114,7 +114,12 @@ def test_scratch_size_queries():
     args.kv_len = 64
     assert lib.aoto_sm100_attention_scratch_bytes(ctypes.byref(args)) == 0      # one split: no merge
     args.q_len, args.kv_len = 128, 128
-    assert lib.aoto_sm100_attention_scratch_bytes(ctypes.byref(args)) == 0      # prefill uses none
+    assert lib.aoto_sm100_attention_scratch_bytes(ctypes.byref(args)) == 0      # short prefill uses none
+    # a long masked prefill classifies the 64 x 64 tiles of its mask: one byte per tile behind the header
+    args.q_len, args.kv_len, args.mask = 1000, 1024, 4096
+    assert lib.aoto_sm100_attention_scratch_bytes(ctypes.byref(args)) == 4096 + 16 * 16
+    args.mask = None
+    assert lib.aoto_sm100_attention_scratch_bytes(ctypes.byref(args)) == 0      # nothing to classify
     assert lib.aoto_sm100_attention_static_scratch_limit() == 1 << 20
     assert lib.aoto_sm100_argmax_scratch_bytes(1, 151936) > 4096
     assert lib.aoto_sm100_stamped_bytes(896) == 896 * 4                          # 2 values per 8-byte word

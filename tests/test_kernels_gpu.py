@@ -337,7 +337,8 @@ def test_attention_fully_masked_rows_are_zero(cuda):
 
 
 @pytest.mark.parametrize("QH,KVH,P,D,length", [(14, 2, 128, 64, 128), (14, 2, 64, 64, 37), (32, 8, 96, 128, 96), (4, 2, 7, 8, 3),
-                                                  (8, 2, 200, 64, 131), (8, 4, 257, 128, 257), (2, 1, 16, 64, 16)])
+                                                  (8, 2, 200, 64, 131), (8, 4, 257, 128, 257), (2, 1, 16, 64, 16),
+                                                  (8, 2, 512, 64, 300), (8, 2, 1024, 128, 1024), (4, 4, 384, 128, 65)])
 def test_attention_prefill(cuda, QH, KVH, P, D, length):
     """Prefill with the left-padded bucket mask; pad query rows are fully masked -> zero."""
 
@@ -357,6 +358,27 @@ def test_attention_prefill(cuda, QH, KVH, P, D, length):
     if length == P:
         causal = ops.attention(q.to(cuda), k.to(cuda), v.to(cuda), None, scale=D ** -0.5, causal=True).cpu()
         assert rel_max_error(causal, want) < ORACLE_TOL
+
+
+@pytest.mark.parametrize("P,D,band", [(512, 64, 100), (320, 128, 1), (448, 64, 447)])
+def test_attention_prefill_skips_only_tiles_without_admitted_keys(cuda, P, D, band):
+    """A banded mask leaves whole key tiles without an admitted key before and after the band; the
+    kernel passes over them, and over nothing else. Some query rows admit no key at all."""
+
+    ops = _ops()
+    QH, KVH = 4, 2
+    q = activations(130, 1, QH, P, D)
+    k = activations(131, 1, KVH, P, D)
+    v = activations(132, 1, KVH, P, D)
+    query = torch.arange(P)[:, None]
+    key = torch.arange(P)[None, :]
+    allowed = (key <= query) & (key > query - band) & ((query < 70) | (query >= 140))
+    allowed[P - 1, 3] = True                      # a lone admitted key in a tile the band never reaches
+    mask = ref.mask_to_additive(allowed.reshape(1, 1, P, P), torch.bfloat16)
+    got = ops.attention(q.to(cuda), k.to(cuda), v.to(cuda), mask.to(cuda), scale=D ** -0.5).cpu()
+    want = ref.attention(q, k, v, mask, scale=D ** -0.5)
+    assert rel_max_error(got, want) < ORACLE_TOL
+    assert not got[:, :, 70:140].any()
 
 
 def test_scratch_is_shared_between_kernels_and_shapes(cuda):
