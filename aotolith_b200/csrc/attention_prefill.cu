@@ -72,6 +72,20 @@ attention_mask_classes_kernel(const bf16* __restrict__ mask, unsigned char* __re
   if (lane == 0) classes[tile] = !any_admitted ? PF_TILE_NONE : (all_zero ? PF_TILE_ZERO : PF_TILE_MIXED);
 }
 
+// Four 8x8 b16 matrices as they lie in shared memory (rows are keys, the fragment wants the pair
+// of dims 2t, 2t+1 of key g).
+__device__ __forceinline__ void pf_ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(smem_row)));
+}
+
+// 2^x on the special-function unit; -inf gives 0.
+__device__ __forceinline__ float pf_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int D>
 __global__ void __launch_bounds__(PF_THREADS)
 attention_prefill_mma_kernel(const AttnParams p) {
@@ -86,7 +100,10 @@ attention_prefill_mma_kernel(const AttnParams p) {
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int head = blockIdx.y, q0 = blockIdx.x * PF_BQ;
+  // The late query tiles of a causal prompt visit the most key tiles: they are launched first, so
+  // that the short ones fill in behind them.
+  const int q_tile = gridDim.x - 1 - blockIdx.x;
+  const int head = blockIdx.y, q0 = q_tile * PF_BQ;
   const int kvh = head / (p.QH / p.KVH);
   const int Lq = p.Lq, Lk = p.Lk;
   const bf16* qbase = p.q + (size_t)head * Lq * D;
@@ -112,7 +129,7 @@ attention_prefill_mma_kernel(const AttnParams p) {
   const bool classed = p.tile_classes != nullptr;
   const bool mask_pairs = (Lk & 1) == 0 && (reinterpret_cast<uintptr_t>(p.mask) & 3) == 0;
   if (classed) {
-    const unsigned char* mine = p.tile_classes + (size_t)blockIdx.x * p.key_tiles;
+    const unsigned char* mine = p.tile_classes + (size_t)q_tile * p.key_tiles;
     for (int i = tid; i < tiles; i += PF_THREADS) tile_class[i] = mine[i];
     __syncthreads();
   }
@@ -134,6 +151,9 @@ attention_prefill_mma_kernel(const AttnParams p) {
   float o[DTILES][4];
 #pragma unroll
   for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  // scores are kept in the base-2 domain: exp(x) = 2^(x * log2 e), one multiply folded into the scale
+  constexpr float LOG2E = 1.4426950408889634f;
+  const float scale_log2 = p.scale * LOG2E;
   float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
   uint32_t qa[KSTEPS][4];
   const int row_lo = q0 + warp * 16 + g, row_hi = row_lo + 8;
@@ -171,12 +191,17 @@ attention_prefill_mma_kernel(const AttnParams p) {
 #pragma unroll
     for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
 #pragma unroll
-    for (int kk = 0; kk < KSTEPS; ++kk) {
+    for (int kk = 0; kk < KSTEPS; kk += 2) {
+      // one ldmatrix.x4 per 8 keys fetches the B fragments of two k steps: lanes 8m..8m+7 address
+      // the rows of matrix m = (k step, low or high eight dims)
+      uint32_t b[8][4];
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        const unsigned char* krow = kt + (size_t)(n * 8 + g) * PITCH + (kk * 16 + 2 * t) * 2;
-        pf_mma(s[n], qa[kk], *reinterpret_cast<const uint32_t*>(krow), *reinterpret_cast<const uint32_t*>(krow + 16));
-      }
+      for (int n = 0; n < 8; ++n)
+        pf_ldmatrix_x4(b[n], kt + (size_t)(n * 8 + (lane & 7)) * PITCH + (kk * 16 + (lane >> 3) * 8) * 2);
+#pragma unroll
+      for (int n = 0; n < 8; ++n) pf_mma(s[n], qa[kk], b[n][0], b[n][1]);
+#pragma unroll
+      for (int n = 0; n < 8; ++n) pf_mma(s[n], qa[kk + 1], b[n][2], b[n][3]);
     }
 
     // Scale, mask, running maximum. Three forms of the mask term, chosen per tile and the same for
@@ -206,8 +231,8 @@ attention_prefill_mma_kernel(const AttnParams p) {
           }
           const bool in0 = row < Lq && key < Lk && !(p.causal && key > row);
           const bool in1 = row < Lq && key + 1 < Lk && !(p.causal && key + 1 > row);
-          const float v0 = in0 ? s[n][2 * h] * p.scale + add0 : -INFINITY;
-          const float v1 = in1 ? s[n][2 * h + 1] * p.scale + add1 : -INFINITY;
+          const float v0 = in0 ? s[n][2 * h] * scale_log2 + add0 * LOG2E : -INFINITY;
+          const float v1 = in1 ? s[n][2 * h + 1] * scale_log2 + add1 * LOG2E : -INFINITY;
           s[n][2 * h] = v0;
           s[n][2 * h + 1] = v1;
           tile_max[h] = fmaxf(tile_max[h], fmaxf(v0, v1));
@@ -224,7 +249,7 @@ attention_prefill_mma_kernel(const AttnParams p) {
       m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
       m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
       const float m_new = fmaxf(row_max[h], m);
-      correction[h] = (row_max[h] == -INFINITY) ? 0.f : expf(row_max[h] - m_new);
+      correction[h] = (row_max[h] == -INFINITY) ? 0.f : pf_exp2(row_max[h] - m_new);
       row_max[h] = m_new;
       row_sum[h] *= correction[h];
     }
@@ -236,7 +261,7 @@ attention_prefill_mma_kernel(const AttnParams p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float m = row_max[e >> 1];
-        e4[e] = (s[n][e] == -INFINITY) ? 0.f : expf(s[n][e] - m);
+        e4[e] = (s[n][e] == -INFINITY) ? 0.f : pf_exp2(s[n][e] - m);
         row_sum[e >> 1] += e4[e];
       }
       pa[n >> 1][(n & 1) * 2 + 0] = pack_bf16x2(e4[0], e4[1]);  // row g, keys 2t, 2t+1 of this n tile
