@@ -31,11 +31,11 @@ __device__ __forceinline__ void pf_mma(float (&c)[4], const uint32_t (&a)[4], ui
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Two 8x8 b16 matrices, transposed: rows are keys in shared memory, the fragment wants
+// Four 8x8 b16 matrices, transposed: rows are keys in shared memory, the fragment wants
 // (k = key, n = dim) pairs along k.
-__device__ __forceinline__ void pf_ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* smem_row) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];"
-               : "=r"(r0), "=r"(r1) : "r"((uint32_t)__cvta_generic_to_shared(smem_row)));
+__device__ __forceinline__ void pf_ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(smem_row)));
 }
 
 // One warp per (64 query rows, 64 keys) tile of the additive mask: 512 16-byte chunks, sixteen per
@@ -208,8 +208,9 @@ attention_prefill_mma_kernel(const AttnParams p) {
     // the whole warp: none (no mask, or a tile where it adds zero everywhere), pairs of neighbouring
     // keys in one 32-bit load (even window, 4-byte aligned mask), single elements.
     float tile_max[2] = {-INFINITY, -INFINITY};
-    auto scores = [&](auto mode_tag) {
+    auto scores = [&](auto mode_tag, auto edge_tag) {
       constexpr int MODE = decltype(mode_tag)::value;
+      constexpr bool EDGE = decltype(edge_tag)::value;  // false: every (row, key) of the warp's tile is in range and admitted by the causal rule
       const int key_base = j * PF_BK + 2 * t;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -220,17 +221,17 @@ attention_prefill_mma_kernel(const AttnParams p) {
           const int key = key_base + n * 8;
           float add0 = 0.f, add1 = 0.f;
           if (MODE == PF_MASK_PAIRS) {
-            if (row < Lq && key < Lk) {  // the window is even: key + 1 is inside as well
+            if (!EDGE || (row < Lq && key < Lk)) {  // the window is even: key + 1 is inside as well
               const uint32_t pair = *reinterpret_cast<const uint32_t*>(mask_row + n * 8);
               add0 = __uint_as_float(pair << 16);
               add1 = __uint_as_float(pair & 0xFFFF0000u);
             }
           } else if (MODE == PF_MASK_SINGLE) {
-            if (row < Lq && key < Lk) add0 = __bfloat162float(mask_row[n * 8]);
-            if (row < Lq && key + 1 < Lk) add1 = __bfloat162float(mask_row[n * 8 + 1]);
+            if (!EDGE || (row < Lq && key < Lk)) add0 = __bfloat162float(mask_row[n * 8]);
+            if (!EDGE || (row < Lq && key + 1 < Lk)) add1 = __bfloat162float(mask_row[n * 8 + 1]);
           }
-          const bool in0 = row < Lq && key < Lk && !(p.causal && key > row);
-          const bool in1 = row < Lq && key + 1 < Lk && !(p.causal && key + 1 > row);
+          const bool in0 = !EDGE || (row < Lq && key < Lk && !(p.causal && key > row));
+          const bool in1 = !EDGE || (row < Lq && key + 1 < Lk && !(p.causal && key + 1 > row));
           const float v0 = in0 ? s[n][2 * h] * scale_log2 + add0 * LOG2E : -INFINITY;
           const float v1 = in1 ? s[n][2 * h + 1] * scale_log2 + add1 * LOG2E : -INFINITY;
           s[n][2 * h] = v0;
@@ -239,9 +240,18 @@ attention_prefill_mma_kernel(const AttnParams p) {
         }
       }
     };
-    if (p.mask == nullptr || (classed && tile_class[j] == PF_TILE_ZERO)) scores(std::integral_constant<int, PF_MASK_NONE>());
-    else if (mask_pairs) scores(std::integral_constant<int, PF_MASK_PAIRS>());
-    else scores(std::integral_constant<int, PF_MASK_SINGLE>());
+    const bool edge = q0 + PF_BQ > Lq || (j + 1) * PF_BK > Lk || (p.causal && (j + 1) * PF_BK - 1 > q0 + warp * 16);
+    const int mode = (p.mask == nullptr || (classed && tile_class[j] == PF_TILE_ZERO)) ? PF_MASK_NONE
+                     : (mask_pairs ? PF_MASK_PAIRS : PF_MASK_SINGLE);
+    using Edge = std::true_type;
+    using Inner = std::false_type;
+    if (mode == PF_MASK_NONE) {
+      if (edge) scores(std::integral_constant<int, PF_MASK_NONE>(), Edge()); else scores(std::integral_constant<int, PF_MASK_NONE>(), Inner());
+    } else if (mode == PF_MASK_PAIRS) {
+      if (edge) scores(std::integral_constant<int, PF_MASK_PAIRS>(), Edge()); else scores(std::integral_constant<int, PF_MASK_PAIRS>(), Inner());
+    } else {
+      if (edge) scores(std::integral_constant<int, PF_MASK_SINGLE>(), Edge()); else scores(std::integral_constant<int, PF_MASK_SINGLE>(), Inner());
+    }
     float correction[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -267,20 +277,26 @@ attention_prefill_mma_kernel(const AttnParams p) {
       pa[n >> 1][(n & 1) * 2 + 0] = pack_bf16x2(e4[0], e4[1]);  // row g, keys 2t, 2t+1 of this n tile
       pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16x2(e4[2], e4[3]);  // row g + 8
     }
+    // after the first tiles the running maximum seldom moves: the accumulator is rescaled only
+    // when some row of the warp needs it
+    if (__any_sync(0xffffffffu, correction[0] != 1.f || correction[1] != 1.f)) {
 #pragma unroll
-    for (int i = 0; i < DTILES; ++i) {
-      o[i][0] *= correction[0]; o[i][1] *= correction[0];
-      o[i][2] *= correction[1]; o[i][3] *= correction[1];
+      for (int i = 0; i < DTILES; ++i) {
+        o[i][0] *= correction[0]; o[i][1] *= correction[0];
+        o[i][2] *= correction[1]; o[i][3] *= correction[1];
+      }
     }
     // O += P.V
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
       const unsigned char* vrow = vt + (size_t)(kk * 16 + (lane & 15)) * PITCH;
 #pragma unroll
-      for (int i = 0; i < DTILES; ++i) {
-        uint32_t b0, b1;
-        pf_ldmatrix_x2_trans(b0, b1, vrow + i * 16);
-        pf_mma(o[i], pa[kk], b0, b1);
+      for (int i = 0; i < DTILES; i += 2) {
+        // lanes 0-15 address the 16 keys at dims 8i.., lanes 16-31 the same keys at dims 8(i+1)..
+        uint32_t b[4];
+        pf_ldmatrix_x4_trans(b, vrow + (i + (lane >> 4)) * 16);
+        pf_mma(o[i], pa[kk], b[0], b[1]);
+        pf_mma(o[i + 1], pa[kk], b[2], b[3]);
       }
     }
     __syncthreads();  // the other stage is refilled at the top of the next iteration
