@@ -162,15 +162,15 @@ attention_prefill_mma_kernel(const AttnParams p) {
   bool have_q = false;
   for (int j = first; j < tiles; stage ^= 1) {
     const int following = next_tile(j + 1);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");  // tile j (and, the first time, Q)
+    __syncthreads();
+    // Every warp is past the products of the previous tile, so its stage is free: the next tile is
+    // requested now and lands while this one is multiplied. One barrier per tile.
     if (following < tiles) {
       load_rows(ks + (size_t)(stage ^ 1) * PF_BK * PITCH, kbase, following * PF_BK, Lk);
       load_rows(vs + (size_t)(stage ^ 1) * PF_BK * PITCH, vbase, following * PF_BK, Lk);
       asm volatile("cp.async.commit_group;" ::: "memory");
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
-    __syncthreads();
     if (!have_q) {
       have_q = true;
       const unsigned char* qlo = qs + (size_t)(warp * 16 + g) * PITCH;
@@ -264,14 +264,15 @@ attention_prefill_mma_kernel(const AttnParams p) {
       row_sum[h] *= correction[h];
     }
     // probabilities (bf16 A fragments of the second product) and the row sums of this tile
+    // a row with no admitted key so far has maximum -inf: subtract 0 instead, every term is 2^(-inf)
+    const float max_or_zero[2] = {row_max[0] == -INFINITY ? 0.f : row_max[0], row_max[1] == -INFINITY ? 0.f : row_max[1]};
     uint32_t pa[4][4];
 #pragma unroll
     for (int n = 0; n < 8; ++n) {
       float e4[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float m = row_max[e >> 1];
-        e4[e] = (s[n][e] == -INFINITY) ? 0.f : pf_exp2(s[n][e] - m);
+        e4[e] = pf_exp2(s[n][e] - max_or_zero[e >> 1]);  // 2^(-inf) = 0 for an excluded key
         row_sum[e >> 1] += e4[e];
       }
       pa[n >> 1][(n & 1) * 2 + 0] = pack_bf16x2(e4[0], e4[1]);  // row g, keys 2t, 2t+1 of this n tile
@@ -299,9 +300,9 @@ attention_prefill_mma_kernel(const AttnParams p) {
         pf_mma(o[i + 1], pa[kk], b[2], b[3]);
       }
     }
-    __syncthreads();  // the other stage is refilled at the top of the next iteration
     j = following;
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");  // a query tile with no admitted key tile never waited for Q
 
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
