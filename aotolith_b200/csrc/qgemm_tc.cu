@@ -262,33 +262,68 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
     // epilogue: warp q of a warpgroup may read tensor-memory lanes 32q..32q+31; two warps share
     // a lane quadrant and each takes half of the 128 columns of every tile
     if (ok) ok = tc_bar_wait(accumulated, 0u);
+    ok = __all_sync(0xffffffffu, ok);  // the epilogue below synchronises the warp: all lanes or none
     const int quadrant = warp & 3;
-    auto emit = [&](const float (&acc)[32], int m, int nbase) {
+    // A warp holds its chunk of the accumulator with one output ROW per lane; written that way
+    // every store instruction would touch 32 rows with 4 bytes each. The chunk is turned through
+    // shared memory instead (the operand stages are idle once `accumulated` has completed; each
+    // warp owns 32 rows of 33 floats there), so that a half-warp covers 32 neighbouring columns of
+    // one row: 64-byte runs for the output and for the addend and gate that come the same way.
+    float* turn = reinterpret_cast<float*>(tile_b) + (size_t)(warp - 2) * 32 * 33;
+    auto emit = [&](const float (&acc)[32], int m_first, int nbase) {  // called by the whole warp
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        uint32_t packed_pair = 0;
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int col = nbase + j + e;
-          float y = p.alpha * acc[j + e];
-          if (col < p.N) {
-            if (p.addend_kind == AOTO_ADDEND_VECTOR) y = fmaf(p.beta, __bfloat162float(p.addend[col]), y);
-            else if (p.addend_kind == AOTO_ADDEND_FULL) y = fmaf(p.beta, __bfloat162float(p.addend[(size_t)m * p.N + col]), y);
-            if (p.epilogue == AOTO_EPILOGUE_SILU_MUL) {
-              const float gate = __bfloat162float(p.gate[(size_t)m * p.N + col]);
-              y = y * (gate / (1.f + expf(-gate)));
-            }
+      for (int j = 0; j < 32; ++j) turn[lane * 33 + j] = acc[j];
+      __syncwarp();
+      const int col = nbase + 2 * (lane & 15);
+      const bool pairs = (p.N & 1) == 0;  // then (m * N + col) is even: 4-byte accesses are aligned
+      float bias0 = 0.f, bias1 = 0.f;
+      if (p.addend_kind == AOTO_ADDEND_VECTOR) {
+        if (col < p.N) bias0 = __bfloat162float(p.addend[col]);
+        if (col + 1 < p.N) bias1 = __bfloat162float(p.addend[col + 1]);
+      }
+#pragma unroll 4
+      for (int it = 0; it < 16; ++it) {
+        const int row = 2 * it + (lane >> 4);
+        const int m = m_first + row;
+        if (m >= p.M || col >= p.N) continue;
+        const bool both = col + 1 < p.N;
+        float y0 = p.alpha * turn[row * 33 + 2 * (lane & 15)];
+        float y1 = p.alpha * turn[row * 33 + 2 * (lane & 15) + 1];
+        const size_t at = (size_t)m * p.N + col;
+        auto fetch = [&](const bf16* src, float& v0, float& v1) {
+          if (pairs) {
+            const uint32_t two = *reinterpret_cast<const uint32_t*>(src + at);
+            v0 = __uint_as_float(two << 16);
+            v1 = __uint_as_float(two & 0xFFFF0000u);
+          } else {
+            v0 = __bfloat162float(src[at]);
+            v1 = both ? __bfloat162float(src[at + 1]) : 0.f;
           }
-          packed_pair |= float_to_bf16_bits(y) << (16 * e);
+        };
+        if (p.addend_kind == AOTO_ADDEND_VECTOR) {
+          y0 = fmaf(p.beta, bias0, y0);
+          y1 = fmaf(p.beta, bias1, y1);
+        } else if (p.addend_kind == AOTO_ADDEND_FULL) {
+          float a0, a1;
+          fetch(p.addend, a0, a1);
+          y0 = fmaf(p.beta, a0, y0);
+          y1 = fmaf(p.beta, a1, y1);
         }
-        const int col = nbase + j;
-        if (col + 1 < p.N && (p.N & 1) == 0) {
-          *reinterpret_cast<uint32_t*>(p.out + (size_t)m * p.N + col) = packed_pair;
+        if (p.epilogue == AOTO_EPILOGUE_SILU_MUL) {
+          float g0, g1;
+          fetch(p.gate, g0, g1);
+          y0 = y0 * (g0 / (1.f + expf(-g0)));
+          y1 = y1 * (g1 / (1.f + expf(-g1)));
+        }
+        const uint32_t packed_pair = float_to_bf16_bits(y0) | (float_to_bf16_bits(y1) << 16);
+        if (pairs) {
+          *reinterpret_cast<uint32_t*>(p.out + at) = packed_pair;
         } else {
-          if (col < p.N) p.out[(size_t)m * p.N + col] = __ushort_as_bfloat16((unsigned short)(packed_pair & 0xffffu));
-          if (col + 1 < p.N) p.out[(size_t)m * p.N + col + 1] = __ushort_as_bfloat16((unsigned short)(packed_pair >> 16));
+          p.out[at] = __ushort_as_bfloat16((unsigned short)(packed_pair & 0xffffu));
+          if (both) p.out[at + 1] = __ushort_as_bfloat16((unsigned short)(packed_pair >> 16));
         }
       }
+      __syncwarp();  // the next chunk overwrites the rows
     };
     // fp32 partial tiles: [split][padded row][padded column]
     const size_t padded_cols = (size_t)gridDim.x * TC_BN, padded_rows = (size_t)gridDim.y * TC_BM * MT;
@@ -303,11 +338,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
         uint32_t raw[32];
         tc_load_32(tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(mt * TC_BN + c * 32), raw);
         if (splits == 1) {
-          if (m >= p.M) continue;
           float acc[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(raw[j]);
-          emit(acc, m, n0 + c * 32);
+          emit(acc, m - lane, n0 + c * 32);
         } else {
           float4* dst = reinterpret_cast<float4*>(partials + ((size_t)blockIdx.z * padded_rows + m) * padded_cols + n0 + c * 32);
 #pragma unroll
@@ -336,11 +370,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
           const int mt = cc >> 1;
           const int c = half * 2 + (cc & 1);
           const int m = m0 + mt * TC_BM + quadrant * 32 + lane;
-          if (m >= p.M) continue;
           float acc[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-          for (int z = 0; z < splits; ++z) {  // fixed order: the result does not depend on arrival order
+          for (int z = 0; z < splits && m < p.M; ++z) {  // fixed order: the result does not depend on arrival order
             const float4* src = reinterpret_cast<const float4*>(partials + ((size_t)z * padded_rows + m) * padded_cols + n0 + c * 32);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -348,7 +381,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
               acc[4 * j] += v.x; acc[4 * j + 1] += v.y; acc[4 * j + 2] += v.z; acc[4 * j + 3] += v.w;
             }
           }
-          emit(acc, m, n0 + c * 32);
+          emit(acc, m - lane, n0 + c * 32);
         }
       }
     }

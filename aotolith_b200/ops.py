@@ -332,8 +332,13 @@ def attention(
     *,
     scale: float | None = None,
     causal: bool = False,
+    optional_workspace: bool = True,
 ) -> torch.Tensor:
-    """GQA scaled-dot-product attention, batch 1. ``mask`` is additive bf16 ``[1,1,Lq,Lk]``."""
+    """GQA scaled-dot-product attention, batch 1. ``mask`` is additive bf16 ``[1,1,Lq,Lk]``.
+
+    A split decode window needs a workspace; a long masked prefill only runs faster with one (the
+    mask tiles are classified first). ``optional_workspace=False`` withholds it in the second case.
+    """
 
     _need_cuda(query, key, value, mask)
     _bf16(query, "query"); _bf16(key, "key"); _bf16(value, "value"); _bf16(mask, "mask")
@@ -352,7 +357,7 @@ def attention(
     args.scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
     lib = N.load()
     need = lib.aoto_sm100_attention_scratch_bytes(ctypes.byref(args))
-    if need:
+    if need and (lq == 1 or optional_workspace):
         scratch = workspace(query.device, need)
         args.scratch, args.scratch_bytes = _ptr(scratch), scratch.numel()
     N.check(lib.aoto_sm100_attention(ctypes.byref(args), _stream()), "aoto_sm100_attention")

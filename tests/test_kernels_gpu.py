@@ -379,6 +379,9 @@ def test_attention_prefill_skips_only_tiles_without_admitted_keys(cuda, P, D, ba
     want = ref.attention(q, k, v, mask, scale=D ** -0.5)
     assert rel_max_error(got, want) < ORACLE_TOL
     assert not got[:, :, 70:140].any()
+    # the workspace for the tile classes is optional: without it every tile is visited, same result
+    plain = ops.attention(q.to(cuda), k.to(cuda), v.to(cuda), mask.to(cuda), scale=D ** -0.5, optional_workspace=False).cpu()
+    assert torch.equal(plain, got)
 
 
 def test_scratch_is_shared_between_kernels_and_shapes(cuda):
