@@ -30,6 +30,7 @@ ERR_TOO_LARGE = -5
 ADDEND_NONE, ADDEND_VECTOR, ADDEND_FULL = 0, 1, 2
 EPILOGUE_NONE, EPILOGUE_SILU_MUL, EPILOGUE_SILU_MUL_PAIRED = 0, 1, 2
 FLAG_PDL = 1
+FLAG_WEIGHT_BITS_8 = 2
 
 
 class QMatmulArgs(Structure):
@@ -173,6 +174,7 @@ EXPORTS: dict[str, tuple] = {
     "aoto_sm100_qmatmul_variant": (c_char_p, [POINTER(QMatmulArgs)]),
     "aoto_sm100_qmatmul_take_timeout_flag": (c_int, []),
     "aoto_sm100_dequantize_i4": (c_int, [POINTER(DequantizeArgs), c_void_p]),
+    "aoto_sm100_dequantize_i8": (c_int, [POINTER(DequantizeArgs), c_void_p]),
     "aoto_sm100_rms_norm": (c_int, [POINTER(RmsNormArgs), c_void_p]),
     "aoto_sm100_rope": (c_int, [POINTER(RopeArgs), c_void_p]),
     "aoto_sm100_embedding": (c_int, [POINTER(EmbeddingArgs), c_void_p]),

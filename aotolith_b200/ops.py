@@ -86,23 +86,29 @@ def qmatmul(
     beta: float = 1.0,
     out: torch.Tensor | None = None,
     pdl: bool = False,
+    weight_bits: int = 4,
 ) -> torch.Tensor:
-    """``beta*addend + alpha*(x_hat @ W^T)`` with a packed 4-bit ``W`` (+ epilogue).
+    """``beta*addend + alpha*(x_hat @ W^T)`` with a packed 4- or 8-bit ``W`` (+ epilogue).
 
     ``x`` is ``[..., K]``; the result is ``[..., N]``. ``addend`` is a bias ``[N]``
     or a residual shaped like the output. ``packed2/scales2`` select the paired
-    ``silu(y)*y2`` form, ``gate`` the ``y*silu(gate)`` form.
+    ``silu(y)*y2`` form, ``gate`` the ``y*silu(gate)`` form. ``weight_bits`` says how
+    the words are packed: eight codes a word (4) or four (8).
     """
+
+    if weight_bits not in (4, 8):
+        raise PlanInputError(f"weight_bits must be 4 or 8, got {weight_bits!r}")
+    per_word = 32 // weight_bits
 
     _need_cuda(x, packed, scales, addend, norm_weight, packed2, scales2, gate)
     _bf16(x, "x"); _bf16(scales, "scales"); _bf16(addend, "addend")
     _bf16(norm_weight, "norm_weight"); _bf16(gate, "gate")
     if packed.dtype != torch.int32 or packed.dim() != 2:
-        raise PlanInputError(f"packed weight must be int32 [N, K/8], got {packed.dtype} {tuple(packed.shape)}")
+        raise PlanInputError(f"packed weight must be int32 [N, K/{per_word}], got {packed.dtype} {tuple(packed.shape)}")
     K = x.shape[-1]
     n_rows, words = packed.shape
-    if words * 8 != K:
-        raise PlanInputError(f"x has K={K} but the packed weight holds {words * 8} codes per row")
+    if words * per_word != K:
+        raise PlanInputError(f"x has K={K} but the packed weight holds {words * per_word} codes per row")
     M = x.numel() // K
     x2 = _dense(x).reshape(M, K)
     packed, scales = _dense(packed), _dense(scales)
@@ -114,7 +120,7 @@ def qmatmul(
     args.out = _ptr(out)
     args.M, args.N, args.K, args.group_size = M, n_rows, K, group_size
     args.alpha, args.beta, args.rms_norm_eps = alpha, beta, rms_norm_eps
-    args.flags = N.FLAG_PDL if pdl else 0
+    args.flags = (N.FLAG_PDL if pdl else 0) | (N.FLAG_WEIGHT_BITS_8 if weight_bits == 8 else 0)
     keep = [x2, packed, scales]
     if addend is not None:
         addend = _dense(addend)
@@ -154,11 +160,12 @@ def qmatmul(
     return out
 
 
-def qmatmul_variant(M: int, n_rows: int, K: int, group_size: int, paired: bool = False) -> str:
+def qmatmul_variant(M: int, n_rows: int, K: int, group_size: int, paired: bool = False, weight_bits: int = 4) -> str:
     """Name of the kernel variant the library would launch for this shape."""
 
     args = N.QMatmulArgs()
     args.M, args.N, args.K, args.group_size = M, n_rows, K, group_size
+    args.flags = N.FLAG_WEIGHT_BITS_8 if weight_bits == 8 else 0
     args.epilogue = N.EPILOGUE_SILU_MUL_PAIRED if paired else N.EPILOGUE_NONE
     return N.load().aoto_sm100_qmatmul_variant(ctypes.byref(args)).decode()
 
@@ -173,6 +180,19 @@ def dequantize_i4(packed: torch.Tensor, scales: torch.Tensor, group_size: int) -
     out = torch.empty((n_rows, words * 8), dtype=torch.bfloat16, device=packed.device)
     args = N.DequantizeArgs(_ptr(packed), _ptr(scales), _ptr(out), n_rows, words * 8, group_size)
     N.check(N.load().aoto_sm100_dequantize_i4(ctypes.byref(args), _stream()), "aoto_sm100_dequantize_i4")
+    return out
+
+
+def dequantize_i8(packed: torch.Tensor, scales: torch.Tensor, group_size: int) -> torch.Tensor:
+    """``[N, K]`` bf16 weight of eight-bit codes (four a word): ``bf16(code) * scale`` rounded once."""
+
+    _need_cuda(packed, scales)
+    _bf16(scales, "scales")
+    packed, scales = _dense(packed), _dense(scales)
+    n_rows, words = packed.shape
+    out = torch.empty((n_rows, words * 4), dtype=torch.bfloat16, device=packed.device)
+    args = N.DequantizeArgs(_ptr(packed), _ptr(scales), _ptr(out), n_rows, words * 4, group_size)
+    N.check(N.load().aoto_sm100_dequantize_i8(ctypes.byref(args), _stream()), "aoto_sm100_dequantize_i8")
     return out
 
 

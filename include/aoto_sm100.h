@@ -97,6 +97,16 @@ typedef struct aoto_qmatmul_args {
 } aoto_qmatmul_args;
 
 #define AOTO_FLAG_PDL 1 /* launch with programmatic dependent launch enabled */
+/*
+ * The weight is packed with EIGHT bits a code: four codes per 32-bit word, code k of a word at
+ * bit 8k, word j of a row = codes 4j..4j+3, two's complement; `packed` is [N,K/4] (and 8-byte
+ * aligned), scales as before. Every weight is rounded to bf16 as code*scale before it is
+ * multiplied. K and group_size must be multiples of 8 and K <= 32768; the norm prologue and the
+ * paired epilogue need M == 1; no workspace. Variants "qgemv_i8" (M == 1) and "qgemm_i8_rows".
+ * Replaces: packed `matmul`/`addmm` with weight_bits == 8, runtime/mlx_ops/__init__.py:569-619
+ * (unpack by quantize.py:250-262), and the int8 GEMV codegen/matmul.py:742-929.
+ */
+#define AOTO_FLAG_WEIGHT_BITS_8 2
 
 int aoto_sm100_qmatmul(const aoto_qmatmul_args* args, void* stream);
 /*
@@ -126,6 +136,12 @@ typedef struct aoto_dequantize_args {
   int32_t N, K, group_size;
 } aoto_dequantize_args;
 int aoto_sm100_dequantize_i4(const aoto_dequantize_args* args, void* stream);
+/*
+ * The same for eight-bit codes: packed [N,K/4] int32 (8-byte aligned), K and group_size
+ * multiples of 8 (AOTO_ERR_UNSUPPORTED otherwise).
+ * Replaces: `dequantize_i8`, models/quantized.py:90-105, quantize.py:250-262.
+ */
+int aoto_sm100_dequantize_i8(const aoto_dequantize_args* args, void* stream);
 
 /* ------------------------------------------------------------------------- */
 /* Normalisation, rotary embedding, gathers                                  */

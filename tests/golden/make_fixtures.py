@@ -13,7 +13,10 @@ Writes, next to this file:
   per-step decode logits, greedy tokens and the final cache, following the host
   loop of ``src/aotolith/models/decoder.py:811-1087``;
 * ``quantize_kat.npz`` - packed words / scales / codes of the reference packer on
-  seeded matrices (including an all-zero group and a row of extreme values).
+  seeded matrices (including an all-zero group and a row of extreme values);
+* ``quantize_int8_kat.npz`` - the same for the eight-bit packer, plus what the
+  reference's torch operator ``aotolith::dequantize_i8`` returns for bf16 scales
+  (``python make_fixtures.py <reference> int8`` writes only this file).
 
 The reference package refuses to import off Apple silicon and needs MLX, so it
 is loaded by path with a permissive ``mlx`` stub; only its torch/NumPy code runs.
@@ -128,8 +131,38 @@ def toy(family: str):
     return tiny_decoder(FAMILIES[family]["model_type"], seed=FAMILIES[family]["seed"])
 
 
-def main(reference: str) -> None:
+def write_int8_kat() -> None:
+    """Known answers of the reference's eight-bit packer and of its torch unpack operator."""
+
+    import aotolith.quantize as Q
+    from aotolith.models.quantized import dequantize_i8
+
+    rng = np.random.default_rng(8)
+    mats = {}
+    for tag, (rows, inner, group) in {"a": (6, 128, 64), "b": (5, 64, 16), "c": (3, 96, 32)}.items():
+        weight = (rng.standard_normal((rows, inner)) * 0.05).astype(np.float32)
+        weight[0, :group] = 0.0
+        weight[1, :] = np.where(np.arange(inner) % 2 == 0, 1.0, -1.0) * 0.75
+        packed, scales = Q.quantize_int8(weight, group)
+        mats[f"{tag}_weight"], mats[f"{tag}_packed"], mats[f"{tag}_scales"] = weight, packed, scales
+        mats[f"{tag}_codes"] = Q.unpack_codes_int8(packed)
+        mats[f"{tag}_dequant"] = Q.dequantize_int8(packed, scales, group)
+        low = dequantize_i8(torch.from_numpy(packed), torch.from_numpy(scales).bfloat16(), group)
+        mats[f"{tag}_dequant_bf16"] = low.float().numpy()
+        mats[f"{tag}_group"] = np.array(group)
+    # every byte value once (byte k of word j is 4j + k), unpacked by the reference
+    words = np.arange(256, dtype=np.uint8).view("<i4").reshape(1, 64)
+    mats["all_words"] = words
+    mats["all_codes"] = Q.unpack_codes_int8(words)
+    np.savez_compressed(HERE / "quantize_int8_kat.npz", **mats)
+
+
+def main(reference: str, only: str | None = None) -> None:
     load_reference(reference)
+    if only == "int8":
+        write_int8_kat()
+        print("int8 fixtures written to", HERE)
+        return
     from torch.func import functional_call
 
     import aotolith.models.decoder as D
@@ -212,10 +245,11 @@ def main(reference: str) -> None:
         mats[f"{tag}_dequant"] = Q.dequantize_int4(packed, scales, group)
         mats[f"{tag}_group"] = np.array(group)
     np.savez_compressed(HERE / "quantize_kat.npz", **mats)
+    write_int8_kat()
     print("fixtures written to", HERE)
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        raise SystemExit("usage: python make_fixtures.py <path of a checkout of the reference project>")
-    main(sys.argv[1])
+    if len(sys.argv) not in (2, 3):
+        raise SystemExit("usage: python make_fixtures.py <path of a checkout of the reference project> [int8]")
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)

@@ -91,6 +91,17 @@ def test_qmatmul_queries_are_host_only():
     assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(_qargs(128, 896, 4864, 64))) == 4096 + 4 * 128 * 896 * 4
     assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(_qargs(128, 896, 896, 64))) == 0      # 14 k blocks: too short to split
     assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(_qargs(128, 151936, 896, 64))) == 0   # 1187 tiles fill the GPU
+    # eight-bit words (four codes a word) select their own kernels and never ask for a workspace
+    eight = _qargs(1, 1152, 896, 64)
+    eight.flags = N.FLAG_WEIGHT_BITS_8
+    assert lib.aoto_sm100_qmatmul_supported(ctypes.byref(eight)) == 1
+    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(eight)) == b"qgemv_i8"
+    eight.M = 128
+    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(eight)) == b"qgemm_i8_rows"
+    assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(eight)) == 0
+    eight.epilogue = N.EPILOGUE_SILU_MUL_PAIRED                       # the paired form needs a single row
+    assert lib.aoto_sm100_qmatmul_supported(ctypes.byref(eight)) == 0
+    assert lib.aoto_sm100_dequantize_i8(None, None) == N.ERR_ARGUMENT
     # null pointers are refused before anything reaches the CUDA runtime
     assert lib.aoto_sm100_qmatmul(ctypes.byref(_qargs(1, 1152, 896, 64)), None) == N.ERR_ARGUMENT
     assert lib.aoto_sm100_qmatmul(None, None) == N.ERR_ARGUMENT

@@ -103,3 +103,45 @@ def test_pack_weight_keeps_the_weight_dtype():
     codes = ref.unpack_codes(packed).float()
     explicit = (codes * scales.float().repeat_interleave(16, dim=-1)).bfloat16()
     assert torch.equal(want, explicit)
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_int8_matches_reference_packer_output(tag):
+    """Eight-bit packer, unpack and dequantise against the reference's own outputs."""
+
+    kat = np.load(GOLDEN / "quantize_int8_kat.npz")
+    group = int(kat[f"{tag}_group"])
+    packed, scales = Q.quantize_int8(kat[f"{tag}_weight"], group)
+    assert np.array_equal(packed, kat[f"{tag}_packed"])
+    assert np.array_equal(scales, kat[f"{tag}_scales"])
+    assert np.array_equal(Q.unpack_codes_int8(packed), kat[f"{tag}_codes"])
+    assert np.array_equal(Q.dequantize_int8(packed, scales, group), kat[f"{tag}_dequant"])
+    # the oracle's torch unpack and its bf16 dequantise agree with the reference's torch operator
+    assert np.array_equal(ref.unpack_codes_i8(torch.from_numpy(packed)).numpy(), kat[f"{tag}_codes"])
+    low = ref.dequantize_i8(torch.from_numpy(packed), torch.from_numpy(scales).bfloat16(), group)
+    assert low.dtype == torch.bfloat16
+    assert np.array_equal(low.float().numpy(), kat[f"{tag}_dequant_bf16"])
+
+
+def test_int8_unpack_of_every_byte_value():
+    kat = np.load(GOLDEN / "quantize_int8_kat.npz")
+    assert np.array_equal(Q.unpack_codes_int8(kat["all_words"]), kat["all_codes"])
+    assert np.array_equal(ref.unpack_codes_i8(torch.from_numpy(kat["all_words"])).numpy(), kat["all_codes"])
+    assert kat["all_codes"].reshape(-1).tolist() == [b if b < 128 else b - 256 for b in range(256)]
+
+
+def test_oracle_int8_packed_matmul_is_dequantise_then_matmul():
+    rng = np.random.default_rng(4)
+    weight = (rng.standard_normal((12, 64)) * 0.05).astype(np.float32)
+    packed_np, scales_np = Q.quantize_int8(weight, 16)
+    packed, scales = torch.from_numpy(packed_np), torch.from_numpy(scales_np).bfloat16()
+    x = torch.from_numpy(rng.standard_normal((3, 64)).astype(np.float32)).bfloat16()
+    bias = torch.from_numpy(rng.standard_normal(12).astype(np.float32)).bfloat16()
+    got = ref.packed_matmul(x, packed, scales, 16, addend=bias, weight_bits=8)
+    dense = ref.dequantize_i8(packed, scales, 16)
+    want = 1.0 * bias + 1.0 * (x.float() @ dense.float().T).bfloat16()
+    assert got.dtype == torch.bfloat16 and torch.equal(got, want)
+    # eight bits are far closer to the weight than four (tests/test_quantize.py:205-214 of the reference)
+    four = Q.dequantize_int4(*Q.quantize_int4(weight, 16), 16)
+    eight = Q.dequantize_int8(packed_np, scales_np, 16)
+    assert np.abs(eight - weight).max() < np.abs(four - weight).max() / 8
