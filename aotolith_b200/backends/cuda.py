@@ -43,11 +43,15 @@ ARCHITECTURE = "sm_100a"
 
 @dataclass(frozen=True, slots=True)
 class PackedWeight:
-    """A ``dequantize_i4`` result that was never materialised."""
+    """A ``dequantize_i4`` / ``dequantize_i8`` result that was never materialised."""
 
     packed: torch.Tensor
     scales: torch.Tensor
     group_size: int
+    bits: int = 4
+
+
+_UNPACK_BITS = {"dequantize_i4": 4, "dequantize_i8": 8}
 
 
 def _device_name() -> str:
@@ -75,7 +79,7 @@ class _Builder:
     def _find_folded_weights(self) -> set[str]:
         folded: set[str] = set()
         for op in self.graph.ops:
-            if op.op != "dequantize_i4":
+            if op.op not in _UNPACK_BITS:
                 continue
             out = op.outputs[0]
             readers = self.users.get(out, [])
@@ -329,18 +333,22 @@ def _lower_rms_norm(b: _Builder, index: int, op: Operation) -> None:
 
 def _lower_dequantize(b: _Builder, index: int, op: Operation) -> None:
     group = int(op.attrs["group_size"])
+    bits = _UNPACK_BITS[op.op]
     if b.dtype_of(op.inputs[1]) != DType.BF16:
-        raise UnsupportedDTypeError("dequantize_i4: scales must be bfloat16 on this target")
+        raise UnsupportedDTypeError(f"{op.op}: scales must be bfloat16 on this target")
     if op.outputs[0] in b.folded_weights:
-        fn = lambda packed, scales, _g=group: PackedWeight(packed, scales, _g)
+        fn = lambda packed, scales, _g=group, _b=bits: PackedWeight(packed, scales, _g, _b)
         readers = [str(b.graph.ops.index(r)) for r in b.users[op.outputs[0]]]
         b.record(index, op, CUDA_KERNEL,
                  "not materialised: unpacked inside the GEMM of operation " + ", ".join(readers), fn,
-                 "aoto_sm100_qmatmul[weight operand]", (("group_size", group),))
+                 "aoto_sm100_qmatmul[weight operand]", (("group_size", group), ("weight_bits", bits)))
         return
-    fn = lambda packed, scales, _g=group: ops.dequantize_i4(packed, scales, _g)
+    if bits == 8:
+        fn = lambda packed, scales, _g=group: ops.dequantize_i8(packed, scales, _g)
+    else:
+        fn = lambda packed, scales, _g=group: ops.dequantize_i4(packed, scales, _g)
     b.record(index, op, CUDA_KERNEL, "streaming unpack, one rounding per element", fn,
-             "aoto_sm100_dequantize_i4", (("group_size", group),))
+             f"aoto_sm100_{op.op}", (("group_size", group),))
 
 
 def _lower_projection(b: _Builder, index: int, op: Operation) -> None:
@@ -363,8 +371,9 @@ def _lower_projection(b: _Builder, index: int, op: Operation) -> None:
         rows *= dim
 
     if "weight_group_size" in attrs:
-        if int(attrs.get("weight_bits", 4)) != 4:
-            raise UnsupportedOperationError("packed projections with 8-bit weights have no cuda-sm100 kernel yet")
+        bits = int(attrs.get("weight_bits", 4))
+        if bits not in (4, 8):
+            raise UnsupportedOperationError(f"packed projections with {bits}-bit weights have no cuda-sm100 kernel")
         group = int(attrs["weight_group_size"])
         position = base + 3
         paired = epilogue == "silu_mul_paired"
@@ -388,20 +397,24 @@ def _lower_projection(b: _Builder, index: int, op: Operation) -> None:
                 norm_weight=args[norm_at] if norm_at is not None else None, rms_norm_eps=eps,
                 packed2=args[second[0]] if second else None, scales2=args[second[1]] if second else None,
                 gate=args[gate_at] if gate_at is not None else None, alpha=alpha, beta=beta,
+                weight_bits=bits,
             )
             return out.reshape(_s)
 
         n_rows, words = b.shape_of(inputs[base + 1])
-        variant = ops.qmatmul_variant(rows, n_rows, words * 8, group, paired)
+        per_word = 32 // bits
+        variant = ops.qmatmul_variant(rows, n_rows, words * per_word, group, paired, weight_bits=bits)
         reason = "streamed packed words, in-register decode, tensor-pipe accumulate"
         if variant == "qgemv_generic":
             reason = "shape outside the fast variant (group 64, K % 128 == 0): one warp per row"
+        if bits == 8:
+            reason = "eight-bit words: one warp per weight row, weights rounded to bf16 as code*scale"
         if has_norm:
             reason += "; RMS norm applied while staging the activation"
         if paired:
             reason += "; gate/up pair with the SiLU-mul epilogue"
         b.record(index, op, CUDA_KERNEL, reason, fn, f"aoto_sm100_qmatmul[{variant}]",
-                 (("M", rows), ("N", n_rows), ("K", words * 8), ("group_size", group)))
+                 (("M", rows), ("N", n_rows), ("K", words * per_word), ("group_size", group), ("weight_bits", bits)))
         return
 
     weight_id = inputs[base + 1]
@@ -419,12 +432,15 @@ def _lower_projection(b: _Builder, index: int, op: Operation) -> None:
             args[base], weight.packed, weight.scales, group_size=weight.group_size,
             addend=args[0] if is_addmm else None,
             gate=args[gate_at] if gate_at is not None else None, alpha=alpha, beta=beta,
+            weight_bits=weight.bits,
         )
         return out.reshape(_s)
 
     unpack = b.producer[weight_id]
     n_rows, words = b.shape_of(unpack.inputs[0])
-    variant = ops.qmatmul_variant(rows, n_rows, words * 8, int(unpack.attrs["group_size"]))
+    unpack_bits = _UNPACK_BITS[unpack.op]
+    variant = ops.qmatmul_variant(rows, n_rows, words * (32 // unpack_bits), int(unpack.attrs["group_size"]),
+                                  weight_bits=unpack_bits)
     b.record(index, op, CUDA_KERNEL,
              "multi-row projection over a packed weight: unpacked to bf16 on the fly, never stored",
              fn, f"aoto_sm100_qmatmul[{variant}]",
@@ -461,7 +477,7 @@ class CudaBackend:
                 _lower_rope(builder, index, op)
             elif kind == "rms_norm":
                 _lower_rms_norm(builder, index, op)
-            elif kind == "dequantize_i4":
+            elif kind in _UNPACK_BITS:
                 _lower_dequantize(builder, index, op)
             elif kind in ("matmul", "addmm"):
                 _lower_projection(builder, index, op)

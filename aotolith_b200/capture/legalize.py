@@ -4,7 +4,7 @@ The handlers cover what tracing the static-cache adapters produces: embedding,
 the decomposed ``F.rms_norm``, ``F.linear`` in its 2-D (``t`` + ``mm`` /
 ``addmm``) and 3-D (``expand`` + ``bmm``) spellings, views, ``split`` /
 ``slice`` / ``select``, ``cat`` / ``stack``, the rotary arithmetic, the boolean
-mask conversion, SDPA and the ``dequantize_i4`` operator. The emitted spelling
+mask conversion, SDPA and the ``dequantize_i4`` / ``dequantize_i8`` operators. The emitted spelling
 (op names, attribute names, operand orders) is the one the reference's
 legaliser produces (``src/aotolith/legalize/``): ``aten.t`` becomes
 ``transpose{dim0:1, dim1:0}``, ``torch.stack`` becomes ``unsqueeze`` x n +
@@ -357,6 +357,14 @@ def _dequantize_i4(lw, node):
     )
 
 
+def _dequantize_i8(lw, node):
+    packed, scales, group_size = node.args
+    lw.ids[node] = lw.emit(
+        "dequantize_i8", (lw.arg(packed), lw.arg(scales)), lw.node_type(node),
+        {"group_size": int(group_size)},
+    )
+
+
 def _alias(lw, node):
     lw.ids[node] = lw.arg(node.args[0])
 
@@ -397,7 +405,7 @@ HANDLERS = {
 }
 
 #: custom operators are matched by suffix so the namespace can change
-_SUFFIX_HANDLERS = {".dequantize_i4.default": _dequantize_i4}
+_SUFFIX_HANDLERS = {".dequantize_i4.default": _dequantize_i4, ".dequantize_i8.default": _dequantize_i8}
 
 
 def _constant(traced, node):

@@ -10,12 +10,12 @@ from .decoder import (
     prefill_mask,
 )
 from .llama import compile_llama_bucketed, compile_llama_static_cache
-from .quantized import dequantize_i4, pack_weight
+from .quantized import dequantize_i4, dequantize_i8, pack_weight
 from .qwen2 import compile_qwen2_bucketed, compile_qwen2_static_cache
 
 __all__ = [
     "FAMILIES", "DecoderBucketedRuntime", "DecoderFamily", "DecoderMemoryFootprint",
     "DecoderStaticCacheRuntime", "compile_decoder_bucketed", "compile_decoder_static_cache",
     "compile_llama_bucketed", "compile_llama_static_cache", "compile_qwen2_bucketed",
-    "compile_qwen2_static_cache", "dequantize_i4", "family_for", "pack_weight", "prefill_mask",
+    "compile_qwen2_static_cache", "dequantize_i4", "dequantize_i8", "family_for", "pack_weight", "prefill_mask",
 ]

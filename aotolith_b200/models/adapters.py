@@ -31,7 +31,7 @@ import torch
 import torch.nn.functional as F
 
 from ..errors import UnsupportedModelError
-from .quantized import dequantize_i4, pack_weight
+from .quantized import dequantize_i4, dequantize_i8, pack_weight
 
 
 @dataclass(frozen=True, slots=True)
@@ -171,7 +171,7 @@ _PER_LAYER = (("o_proj", "self_attn"), ("gate_proj", "mlp"), ("up_proj", "mlp"),
 
 
 class _QuantizedDecoder(torch.nn.Module):
-    """Weights of a decoder, packed to 4 bits, plus the shared forward pieces."""
+    """Weights of a decoder, packed to 4 or 8 bits, plus the shared forward pieces."""
 
     def __init__(
         self,
@@ -192,15 +192,15 @@ class _QuantizedDecoder(torch.nn.Module):
                 f"{self.family.label} RoPE scaling is not supported yet",
                 hint="the adapter builds one rotary table from rope_theta",
             )
-        if weight_bits != 4:
+        if weight_bits not in (4, 8):
             raise UnsupportedModelError(
-                f"the cuda-sm100 target packs 4-bit weights only, got weight_bits={weight_bits}"
+                f"the cuda-sm100 target packs 4- or 8-bit weights, got weight_bits={weight_bits}"
             )
         _check_activation(model)
         _check_attention_is_causal_only(model)
         self.cache_capacity = int(cache_capacity)
         self.group_size = int(group_size)
-        self.weight_bits = 4
+        self.weight_bits = int(weight_bits)
         self.hidden_size = int(config.hidden_size)
         self.num_layers = int(config.num_hidden_layers)
         self.num_heads = int(config.num_attention_heads)
@@ -212,7 +212,8 @@ class _QuantizedDecoder(torch.nn.Module):
         cosine, sine = rotary_tables(self.cache_capacity, self.head_dim, theta, dtype)
         self.register_buffer("cosine_table", cosine, persistent=False)
         self.register_buffer("sine_table", sine, persistent=False)
-        if isinstance(packed_from, _QuantizedDecoder) and packed_from.group_size == self.group_size:
+        if (isinstance(packed_from, _QuantizedDecoder) and packed_from.group_size == self.group_size
+                and packed_from.weight_bits == self.weight_bits):
             # Packing is the expensive part of construction and does not depend on the
             # capacity: adopt the buffers another adapter of the same model already packed.
             for name, tensor in packed_from.named_buffers():
@@ -226,7 +227,7 @@ class _QuantizedDecoder(torch.nn.Module):
             self.register_buffer(name, tensor.detach(), persistent=False)
 
         def pack(name: str, weight: torch.Tensor) -> None:
-            words, scales = pack_weight(weight, self.group_size)
+            words, scales = pack_weight(weight, self.group_size, self.weight_bits)
             keep(f"{name}_packed", words)
             keep(f"{name}_scales", scales.to(dtype).contiguous())
 
@@ -258,7 +259,8 @@ class _QuantizedDecoder(torch.nn.Module):
     # -- shared forward pieces -------------------------------------------------
 
     def _weight(self, name: str, index: int) -> torch.Tensor:
-        return dequantize_i4(
+        unpack = dequantize_i8 if self.weight_bits == 8 else dequantize_i4
+        return unpack(
             self.get_buffer(f"{name}_{index}_packed"),
             self.get_buffer(f"{name}_{index}_scales"),
             self.group_size,

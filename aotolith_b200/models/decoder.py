@@ -353,13 +353,10 @@ def _compile_bucket(
     _check_quantize_bits(quantize, quantize_bits)
     if quantize is None:
         raise UnsupportedModelError(
-            "the cuda-sm100 target compiles 4-bit packed decoders; dense projections have no "
+            "the cuda-sm100 target compiles 4- and 8-bit packed decoders; dense projections have no "
             "kernel on it yet",
             hint="pass quantize=64",
         )
-    if quantize_bits != 4:
-        raise UnsupportedModelError("the cuda-sm100 target packs 4-bit weights only")
-
     settings = dict(cache_capacity=capacity, group_size=quantize, weight_bits=quantize_bits, require=family)
     prefill_module = QuantizedDecoderPrefillModule(model, packed_from=_packed_from, **settings).eval()
     decode_module = QuantizedDecoderDecodeModule(model, packed_from=prefill_module, **settings).eval()

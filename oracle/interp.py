@@ -52,6 +52,7 @@ def _projection(op, args):
             flat, args[base + 1], args[base + 2], group, addend=addend, alpha=alpha, beta=beta,
             norm_weight=norm_weight, rms_norm_eps=eps, packed2=packed2, scales2=scales2,
             gate=None if gate is None else gate.reshape(flat.shape[0], -1),
+            weight_bits=int(attrs.get("weight_bits", 4)),
         )
         return out
     # dense form (the weight is a materialised tensor)
@@ -127,6 +128,8 @@ def evaluate(graph, op, env):
         return ref.rms_norm(args[0], weight, float(op.attrs.get("eps", 1e-5))).to(out_dtype)
     if kind == "dequantize_i4":
         return ref.dequantize_i4(args[0], args[1], int(op.attrs["group_size"]))
+    if kind == "dequantize_i8":
+        return ref.dequantize_i8(args[0], args[1], int(op.attrs["group_size"]))
     if kind in ("matmul", "addmm"):
         return _projection(op, args).reshape(out_type.shape)
     if kind == "rope":

@@ -16,7 +16,10 @@ Writes, next to this file:
   seeded matrices (including an all-zero group and a row of extreme values);
 * ``quantize_int8_kat.npz`` - the same for the eight-bit packer, plus what the
   reference's torch operator ``aotolith::dequantize_i8`` returns for bf16 scales
-  (``python make_fixtures.py <reference> int8`` writes only this file).
+  (``python make_fixtures.py <reference> int8`` writes only the eight-bit files);
+* ``lowered_graphs_int8.json``, ``adapter_eager_int8_<family>.npz`` - the lowered graphs and
+  eager outputs of the same toy decoders packed with eight bits (the weights are the ones stored
+  in ``adapter_eager_<family>.npz``).
 
 The reference package refuses to import off Apple silicon and needs MLX, so it
 is loaded by path with a permissive ``mlx`` stub; only its torch/NumPy code runs.
@@ -131,6 +134,87 @@ def toy(family: str):
     return tiny_decoder(FAMILIES[family]["model_type"], seed=FAMILIES[family]["seed"])
 
 
+def run_family(family: str, bits: int):
+    """Lowered graphs and eager outputs of the reference's adapters for one toy decoder."""
+
+    from torch.func import functional_call
+
+    import aotolith.models.decoder as D
+    from aotolith.capture import capture_fx
+    from aotolith.passes import rewrite
+
+    model = toy(family)
+    capacity = PROMPT + NEW
+    settings = dict(cache_capacity=capacity, group_size=GROUP, weight_bits=bits, require=family)
+    prefill = D.QuantizedDecoderPrefillModule(model, **settings).eval()
+    decode = D.QuantizedDecoderDecodeModule(model, **settings).eval()
+
+    def lowered(module, examples):
+        state = {**dict(module.named_parameters(remove_duplicate=False)),
+                 **dict(module.named_buffers(remove_duplicate=False))}
+        names = list(state)
+
+        def fn(*flat):
+            return functional_call(module, dict(zip(names, flat[len(examples):])), flat[: len(examples)])
+
+        return rewrite(capture_fx(fn, (*examples, *state.values()), promoted_constants=[])), names
+
+    cfg = model.config
+    cache_shape = (cfg.num_hidden_layers, 2, 1, cfg.num_key_value_heads, capacity, cfg.head_dim)
+    pre_graph, pre_names = lowered(prefill, (
+        torch.zeros((1, PROMPT), dtype=torch.int64), torch.arange(PROMPT)[None, :],
+        torch.from_numpy(D.prefill_mask(PROMPT, PROMPT))))
+    dec_graph, dec_names = lowered(decode, (
+        torch.zeros((1, 1), dtype=torch.int64), torch.zeros((1, 1), dtype=torch.int64),
+        torch.ones((1, 1, 1, capacity), dtype=torch.bool), torch.zeros(cache_shape, dtype=torch.bfloat16)))
+    entry = {
+        "prefill": canonical_graph(pre_graph), "decode": canonical_graph(dec_graph),
+        "prefill_state": pre_names, "decode_state": dec_names,
+    }
+
+    # eager run of the reference adapters (the host loop of decoder.py:811-1087)
+    generator = torch.Generator().manual_seed(100 + FAMILIES[family]["seed"])
+    prompt = torch.randint(0, cfg.vocab_size, (1, PROMPT), generator=generator)
+    with torch.no_grad():
+        logits, compact = prefill(prompt, torch.arange(PROMPT)[None, :], torch.from_numpy(D.prefill_mask(PROMPT, PROMPT)))
+        cache = torch.cat((torch.zeros(compact.shape[:4] + (NEW,) + compact.shape[5:], dtype=compact.dtype), compact), dim=4)
+        prefill_logits = logits.float().numpy()
+        token = logits[:, -1, :].float().argmax(dim=-1, keepdim=True)
+        tokens, step_logits = [int(token)], []
+        valid = PROMPT
+        for _ in range(NEW - 1):
+            valid += 1
+            mask = (torch.arange(capacity) >= capacity - valid).reshape(1, 1, 1, capacity)
+            logits, cache = decode(token, torch.tensor([[valid - 1]]), mask, cache)
+            step_logits.append(logits.float().numpy())
+            token = logits[:, -1, :].float().argmax(dim=-1, keepdim=True)
+            tokens.append(int(token))
+        # a short, left-padded prompt through the same prefill module (bucket semantics)
+        short = prompt[:, : PROMPT - 3]
+        pad = PROMPT - short.shape[1]
+        padded_logits, _ = prefill(
+            torch.cat((torch.zeros((1, pad), dtype=torch.int64), short), dim=1),
+            torch.cat((torch.zeros((1, pad), dtype=torch.int64), torch.arange(short.shape[1])[None, :]), dim=1),
+            torch.from_numpy(D.prefill_mask(short.shape[1], PROMPT)))
+    arrays = dict(prompt=prompt.numpy(), prefill_logits=prefill_logits, step_logits=np.stack(step_logits),
+                  tokens=np.array(tokens), final_cache=cache.float().numpy(),
+                  padded_prefill_logits=padded_logits.float().numpy())
+    if bits == 4:  # the eight-bit files reuse the weights stored beside the four-bit outputs
+        arrays.update({f"w::{k}": v.detach().float().numpy() for k, v in model.state_dict().items()})
+    print(family, bits, "bits: tokens", tokens)
+    return entry, arrays
+
+
+def write_int8_decoders() -> None:
+    """The toy decoders packed with eight bits: the reference's lowered graphs and eager outputs."""
+
+    graphs = {}
+    for family in FAMILIES:
+        graphs[family], arrays = run_family(family, 8)
+        np.savez_compressed(HERE / f"adapter_eager_int8_{family}.npz", **arrays)
+    (HERE / "lowered_graphs_int8.json").write_text(json.dumps(graphs, indent=1, sort_keys=True))
+
+
 def write_int8_kat() -> None:
     """Known answers of the reference's eight-bit packer and of its torch unpack operator."""
 
@@ -161,76 +245,15 @@ def main(reference: str, only: str | None = None) -> None:
     load_reference(reference)
     if only == "int8":
         write_int8_kat()
+        write_int8_decoders()
         print("int8 fixtures written to", HERE)
         return
-    from torch.func import functional_call
-
-    import aotolith.models.decoder as D
     import aotolith.quantize as Q
-    from aotolith.capture import capture_fx
-    from aotolith.passes import rewrite
 
     graphs = {}
     for family in FAMILIES:
-        model = toy(family)
-        capacity = PROMPT + NEW
-        settings = dict(cache_capacity=capacity, group_size=GROUP, weight_bits=4, require=family)
-        prefill = D.QuantizedDecoderPrefillModule(model, **settings).eval()
-        decode = D.QuantizedDecoderDecodeModule(model, **settings).eval()
-
-        def lowered(module, examples):
-            state = {**dict(module.named_parameters(remove_duplicate=False)),
-                     **dict(module.named_buffers(remove_duplicate=False))}
-            names = list(state)
-
-            def fn(*flat):
-                return functional_call(module, dict(zip(names, flat[len(examples):])), flat[: len(examples)])
-
-            return rewrite(capture_fx(fn, (*examples, *state.values()), promoted_constants=[])), names
-
-        cfg = model.config
-        cache_shape = (cfg.num_hidden_layers, 2, 1, cfg.num_key_value_heads, capacity, cfg.head_dim)
-        pre_graph, pre_names = lowered(prefill, (
-            torch.zeros((1, PROMPT), dtype=torch.int64), torch.arange(PROMPT)[None, :],
-            torch.from_numpy(D.prefill_mask(PROMPT, PROMPT))))
-        dec_graph, dec_names = lowered(decode, (
-            torch.zeros((1, 1), dtype=torch.int64), torch.zeros((1, 1), dtype=torch.int64),
-            torch.ones((1, 1, 1, capacity), dtype=torch.bool), torch.zeros(cache_shape, dtype=torch.bfloat16)))
-        graphs[family] = {
-            "prefill": canonical_graph(pre_graph), "decode": canonical_graph(dec_graph),
-            "prefill_state": pre_names, "decode_state": dec_names,
-        }
-
-        # eager run of the reference adapters (the host loop of decoder.py:811-1087)
-        generator = torch.Generator().manual_seed(100 + FAMILIES[family]["seed"])
-        prompt = torch.randint(0, cfg.vocab_size, (1, PROMPT), generator=generator)
-        with torch.no_grad():
-            logits, compact = prefill(prompt, torch.arange(PROMPT)[None, :], torch.from_numpy(D.prefill_mask(PROMPT, PROMPT)))
-            cache = torch.cat((torch.zeros(compact.shape[:4] + (NEW,) + compact.shape[5:], dtype=compact.dtype), compact), dim=4)
-            prefill_logits = logits.float().numpy()
-            token = logits[:, -1, :].float().argmax(dim=-1, keepdim=True)
-            tokens, step_logits = [int(token)], []
-            valid = PROMPT
-            for _ in range(NEW - 1):
-                valid += 1
-                mask = (torch.arange(capacity) >= capacity - valid).reshape(1, 1, 1, capacity)
-                logits, cache = decode(token, torch.tensor([[valid - 1]]), mask, cache)
-                step_logits.append(logits.float().numpy())
-                token = logits[:, -1, :].float().argmax(dim=-1, keepdim=True)
-                tokens.append(int(token))
-            # a short, left-padded prompt through the same prefill module (bucket semantics)
-            short = prompt[:, : PROMPT - 3]
-            pad = PROMPT - short.shape[1]
-            padded_logits, _ = prefill(
-                torch.cat((torch.zeros((1, pad), dtype=torch.int64), short), dim=1),
-                torch.cat((torch.zeros((1, pad), dtype=torch.int64), torch.arange(short.shape[1])[None, :]), dim=1),
-                torch.from_numpy(D.prefill_mask(short.shape[1], PROMPT)))
-        weights = {f"w::{k}": v.detach().float().numpy() for k, v in model.state_dict().items()}
-        np.savez_compressed(
-            HERE / f"adapter_eager_{family}.npz", prompt=prompt.numpy(), prefill_logits=prefill_logits,
-            step_logits=np.stack(step_logits), tokens=np.array(tokens), final_cache=cache.float().numpy(),
-            padded_prefill_logits=padded_logits.float().numpy(), **weights)
-        print(family, "tokens", tokens)
+        graphs[family], arrays = run_family(family, 4)
+        np.savez_compressed(HERE / f"adapter_eager_{family}.npz", **arrays)
     (HERE / "lowered_graphs.json").write_text(json.dumps(graphs, indent=1, sort_keys=True))
 
     rng = np.random.default_rng(5)
@@ -246,6 +269,7 @@ def main(reference: str, only: str | None = None) -> None:
         mats[f"{tag}_group"] = np.array(group)
     np.savez_compressed(HERE / "quantize_kat.npz", **mats)
     write_int8_kat()
+    write_int8_decoders()
     print("fixtures written to", HERE)
 
 

@@ -179,3 +179,48 @@ def test_qmatmul_i8_refuses_what_it_cannot_do(cuda):
                     norm_weight=norm_w.to(cuda), rms_norm_eps=1e-6)
     with pytest.raises(AotolithError):   # four codes a word: K = 4 * words
         ops.qmatmul(x.to(cuda), packed[:, :16].contiguous().to(cuda), scales.to(cuda), group_size=64, weight_bits=8)
+
+
+# ---------------------------------------------------------------------------
+# whole decoders packed with eight bits
+# ---------------------------------------------------------------------------
+
+def _rel_err(actual, expected):
+    expected = expected.float().cpu()
+    return float((actual.float().cpu() - expected).abs().max() / expected.abs().max().clamp_min(1e-6))
+
+
+@pytest.mark.parametrize("family", ["qwen2", "llama"])
+def test_int8_decoder_matches_oracle_and_reference(cuda, family):
+    """Prefill, decode steps and greedy tokens of a toy decoder compiled with quantize_bits=8."""
+
+    import aotolith_b200 as aoto
+    from oracle.interp import OracleRuntime
+    from tests.golden_util import GROUP, NEW, PROMPT, eager_fixture
+
+    model, _ = eager_fixture(family)
+    data = np.load(GOLDEN / f"adapter_eager_int8_{family}.npz")
+    runtime = aoto.models.compile_decoder_static_cache(
+        model, prompt_length=PROMPT, max_new_tokens=NEW, quantize=GROUP, quantize_bits=8, family=family
+    )
+    oracle = OracleRuntime(runtime)
+    prompt = torch.from_numpy(data["prompt"])
+    logits, compact = runtime.prefill_ids(prompt)
+    want_logits, want_cache = oracle.prefill(prompt)
+    assert _rel_err(logits, want_logits) < 2e-2
+    assert _rel_err(logits, torch.from_numpy(data["prefill_logits"])) < 3e-2   # the reference's eager adapters
+    cache = runtime.pad_cache(compact)
+    assert _rel_err(cache, want_cache) < 2e-2
+    token = torch.tensor([[int(want_logits[:, -1].float().argmax())]])
+    valid = PROMPT
+    for step in range(NEW - 1):
+        valid += 1
+        logits, cache = runtime.decode_token(token, cache, valid)
+        want_logits, want_cache = oracle.decode(token, want_cache, valid)
+        assert _rel_err(logits, want_logits) < 2e-2, f"step {step}"
+        assert _rel_err(cache, want_cache) < 2e-2
+        token = torch.tensor([[int(want_logits[:, -1].float().argmax())]])
+    tokens = runtime.greedy_generate(prompt).cpu()
+    assert tokens.shape == (1, NEW)
+    assert tokens[0].tolist() == data["tokens"].tolist()
+    assert torch.equal(runtime.greedy_generate(prompt).cpu(), tokens)   # the stepper is reusable
