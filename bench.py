@@ -693,6 +693,7 @@ def run_probe(name: str) -> None:
     ``lm_head``  six packed GEMV launches over three copies of a [151936, 896] weight (RMS norm fused);
     ``gemm``     six packed GEMM launches, K=4096 N=14336 M=1024, over five weight copies;
     ``attention`` six launches of prefill attention, 32 query / 8 kv heads, 1024 x 1024, D = 128, causal mask;
+    ``i8``       eight-bit packed projections of the 0.5B shape, timed with CUDA events;
     ``step``     a 4-layer Qwen2.5-0.5B-shaped decoder: prefill, then six launches of the step kernel;
     ``trace``    the same, then one more step with the kernel's own per-stage timeline printed;
     ``trace_llama`` the timeline for a 2-layer cut of the Llama-3-8B shape (prompt 128).
@@ -731,6 +732,29 @@ def run_probe(name: str) -> None:
         flops = 4.0 * heads * length * length * dim
         print(json.dumps({"probe": name, "us": us, "tflops_dense": flops / us / 1e6, "tflops_causal_half": flops / 2 / us / 1e6,
                           "max": float(out.float().abs().max())}))
+    elif name == "i8":
+        # eight-bit words (four codes a word): the Qwen-0.5B projections of one decode step, and the prompt rows
+        results = []
+        for K, N, M in ((896, 1152, 1), (896, 4864, 1), (4864, 896, 1), (896, 151936, 1), (896, 4864, 128)):
+            copies = max(3, min(48, int(300e6 // (N * K)) + 1))
+            packs = [torch.randint(-2**31, 2**31 - 1, (N, K // 4), dtype=torch.int32, generator=generator).to(device)
+                     for _ in range(copies)]
+            scales = [(torch.rand(N, K // GROUP, generator=generator) * 0.001 + 0.0001).bfloat16().to(device) for _ in range(copies)]
+            x = torch.randn(M, K, generator=generator).bfloat16().to(device)
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            rounds = 4
+            for i in range(copies * (rounds + 1)):
+                if i == copies:
+                    start.record()
+                ops.qmatmul(x, packs[i % copies], scales[i % copies], group_size=GROUP, out=out, weight_bits=8)
+            stop.record()
+            torch.cuda.synchronize()
+            us = start.elapsed_time(stop) * 1e3 / (copies * rounds)
+            nbytes = N * K + N * (K // GROUP) * 2 + M * K * 2 + M * N * 2
+            results.append({"K": K, "N": N, "M": M, "variant": ops.qmatmul_variant(M, N, K, GROUP, weight_bits=8),
+                            "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1)})
+        print(json.dumps({"probe": name, "note": "back-to-back launches over rotating weight copies larger than L2", "results": results}))
     elif name == "gemm":
         K, N, M = 4096, 14336, 1024
         packs = [torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, generator=generator).to(device) for _ in range(5)]
@@ -774,7 +798,7 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="qwen25_05b")
     parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
-    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "step", "trace", "trace_llama"), default=None,
+    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "step", "trace", "trace_llama"), default=None,
                         help="run a small fixed case of one kernel for a profiler instead of the benchmark")
     args = parser.parse_args()
     if args.probe is not None:
