@@ -1,9 +1,10 @@
 // Packed 8-bit projections: y[M,N] = x[M,K] . W[N,K]^T with W as signed 8-bit codes, four to a
 // 32-bit word (code k of a word at bit 8k, two's complement), one scale per group along K.
 //
-// First kernel of the eight-bit path: one warp per weight row, the lanes stride over units of
-// eight codes (two words, one 8-byte load), MR activation rows of the CTA staged in shared
-// memory so that a decoded weight is used MR times. Every weight is rounded to bf16 as
+// First kernel of the eight-bit path: a warp per weight row (a few CTAs per SM, each warp walking
+// rows a grid stride apart), the lanes stride over units of eight codes (two words, one 8-byte
+// load), MR activation rows of the CTA staged in shared memory so that a decoded weight is used
+// MR times. Every weight is rounded to bf16 as
 // code * scale before it is multiplied - the value the dequantise-then-multiply form of the
 // reference materialises - and products accumulate in fp32. The single-row form (MR = 1) takes
 // the fused RMS-norm prologue and the paired gate/up epilogue like the four-bit GEMV.
@@ -45,39 +46,67 @@ qmatmul_i8_kernel(const GemvParams p, const int M) {
     __syncthreads();
   }
 
-  const int n = blockIdx.x * I8_WARPS + warp;
-  if (n >= N) return;
   const int row_sc = K / p.group;
   const bool paired = p.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED;
+  // The grid is a few CTAs per SM, not one per eight rows: a warp walks rows n, n + stride, ...
+  // so that staging the activation is paid once per CTA and not once per 8 x K bytes of weight.
+  for (int n = blockIdx.x * I8_WARPS + warp; n < N; n += gridDim.x * I8_WARPS) {
   const uint2* w0 = reinterpret_cast<const uint2*>(p.w0) + (size_t)n * chunks;
   const uint2* w1 = reinterpret_cast<const uint2*>(p.w1) + (size_t)n * chunks;
   float acc[MR], acc2[MR];
 #pragma unroll
   for (int r = 0; r < MR; ++r) acc[r] = acc2[r] = 0.f;
-  for (int j = lane; j < chunks; j += 32) {
-    const int gidx = (j * 8) / p.group;
-    float w[8], v[8];
-    i8_decode8(__ldg(w0 + j), __bfloat162float(p.s0[(size_t)n * row_sc + gidx]), w);
-    if (paired) i8_decode8(__ldg(w1 + j), __bfloat162float(p.s1[(size_t)n * row_sc + gidx]), v);
+  // With a single activation row several units of a lane are requested before the first is used
+  // (a row is short, K bytes); with staged rows the registers go to the accumulators instead.
+  constexpr int AHEAD = MR == 1 ? 4 : 1;
+  const bf16* sc0 = p.s0 + (size_t)n * row_sc;
+  const bf16* sc1 = paired ? p.s1 + (size_t)n * row_sc : sc0;
+  for (int j0 = lane; j0 < chunks; j0 += 32 * AHEAD) {
+    uint2 q0[AHEAD], q1[AHEAD];
+    float scale0[AHEAD], scale1[AHEAD];
 #pragma unroll
-    for (int r = 0; r < MR; ++r) {
-      float xf[8];
-      unpack8(xs[(size_t)r * chunks + j], xf);
+    for (int a = 0; a < AHEAD; ++a) {
+      const int j = j0 + 32 * a;
+      q0[a] = q1[a] = make_uint2(0u, 0u);
+      scale0[a] = scale1[a] = 0.f;
+      if (j < chunks) {
+        const int gidx = (j * 8) / p.group;
+        q0[a] = __ldg(w0 + j);
+        scale0[a] = ldg_nc_bf16(sc0 + gidx);
+        if (paired) {
+          q1[a] = __ldg(w1 + j);
+          scale1[a] = ldg_nc_bf16(sc1 + gidx);
+        }
+      }
+    }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[r] = fmaf(w[i], xf[i], acc[r]);
-      if (paired) {
+    for (int a = 0; a < AHEAD; ++a) {
+      const int j = j0 + 32 * a;
+      if (j >= chunks) break;
+      float w[8], v[8];
+      i8_decode8(q0[a], scale0[a], w);
+      if (paired) i8_decode8(q1[a], scale1[a], v);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc2[r] = fmaf(v[i], xf[i], acc2[r]);
+      for (int r = 0; r < MR; ++r) {
+        float xf[8];
+        unpack8(xs[(size_t)r * chunks + j], xf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[r] = fmaf(w[i], xf[i], acc[r]);
+        if (paired) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc2[r] = fmaf(v[i], xf[i], acc2[r]);
+        }
       }
     }
   }
 #pragma unroll
   for (int r = 0; r < MR; ++r) {
     const float total = warp_sum(acc[r]);
-    const float total2 = warp_sum(acc2[r]);
+    const float total2 = paired ? warp_sum(acc2[r]) : 0.f;
     const int m = m0 + r;
     if (lane == 0 && m < M) p.out[(size_t)m * N + n] = __float2bfloat16_rn(finish_output(p, m, n, total, total2));
   }
+  }  // rows of this warp
 }
 
 // W[n, 4j+i] = bf16(code) * bf16(scale[n, (4j+i)/group]) rounded once to bf16; a thread per unit
@@ -124,7 +153,10 @@ static int launch_i8(const GemvParams& p, int M, cudaStream_t stream, bool pdl) 
     }
     if (smem > 160 * 1024) return AOTO_ERR_UNSUPPORTED;
   }
-  dim3 grid((p.N + I8_WARPS - 1) / I8_WARPS, (M + MR - 1) / MR), block(I8_WARPS * 32);
+  const int row_groups = (M + MR - 1) / MR;
+  const int wanted = (p.N + I8_WARPS - 1) / I8_WARPS;
+  const int per_group = 148 * 6 / (row_groups < 6 ? row_groups : 6);  // about six CTAs per SM in all
+  dim3 grid(wanted < per_group ? wanted : per_group, row_groups), block(I8_WARPS * 32);
   return launch_kernel(kernel, grid, block, smem, stream, pdl, p, M);
 }
 
