@@ -694,6 +694,7 @@ def run_probe(name: str) -> None:
     ``gemm``     six packed GEMM launches, K=4096 N=14336 M=1024, over five weight copies;
     ``attention`` six launches of prefill attention, 32 query / 8 kv heads, 1024 x 1024, D = 128, causal mask;
     ``i8``       eight-bit packed projections of the 0.5B shape, timed with CUDA events;
+    ``i8_decoder`` one request of the default workload with the decoder packed with eight bits;
     ``step``     a 4-layer Qwen2.5-0.5B-shaped decoder: prefill, then six launches of the step kernel;
     ``trace``    the same, then one more step with the kernel's own per-stage timeline printed;
     ``trace_llama`` the timeline for a 2-layer cut of the Llama-3-8B shape (prompt 128).
@@ -755,6 +756,32 @@ def run_probe(name: str) -> None:
             results.append({"K": K, "N": N, "M": M, "variant": ops.qmatmul_variant(M, N, K, GROUP, weight_bits=8),
                             "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1)})
         print(json.dumps({"probe": name, "note": "back-to-back launches over rotating weight copies larger than L2", "results": results}))
+    elif name == "i8_decoder":
+        # the whole decoder packed with eight bits: one request of the default workload, timed with CUDA events
+        import aotolith_b200 as aoto
+        from aotolith_b200.models.synthetic import qwen25_05b_shaped
+
+        model = qwen25_05b_shaped(seed=0)
+        runtime = aoto.compile_qwen2_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS,
+                                                  quantize=GROUP, quantize_bits=8)
+        prompt = seeded_prompt(model.config.vocab_size, 1).to(device)
+        runtime.greedy_generate(prompt)
+        torch.cuda.synchronize()
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        marks[0].record()
+        logits, compact = runtime.prefill_ids(prompt)
+        cache = runtime.pad_cache(compact)
+        marks[1].record()
+        tokens = runtime.greedy_generate(prompt)
+        marks[2].record()
+        torch.cuda.synchronize()
+        prefill_ms = marks[0].elapsed_time(marks[1])
+        request_ms = marks[1].elapsed_time(marks[2])
+        decode_us = (request_ms - prefill_ms) * 1e3 / (NEW_TOKENS - 1)
+        print(json.dumps({"probe": "i8_decoder", "workload": "Qwen2.5-0.5B-shaped, 8-bit g64, prompt 128, 64 greedy tokens",
+                          "prefill_ms": round(prefill_ms, 3), "request_ms": round(request_ms, 3),
+                          "decode_us_per_token": round(decode_us, 1), "decode_tok_s": round(1e6 / decode_us, 1),
+                          "tokens": int(tokens.numel())}))
     elif name == "gemm":
         K, N, M = 4096, 14336, 1024
         packs = [torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, generator=generator).to(device) for _ in range(5)]
@@ -798,7 +825,7 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="qwen25_05b")
     parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
-    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "step", "trace", "trace_llama"), default=None,
+    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "i8_decoder", "step", "trace", "trace_llama"), default=None,
                         help="run a small fixed case of one kernel for a profiler instead of the benchmark")
     args = parser.parse_args()
     if args.probe is not None:
