@@ -53,6 +53,12 @@ def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     counters), so it is cleared only when it is created or has to grow. One
     buffer per (device, stream): launches on one stream are ordered, launches
     on different streams never share scratch.
+
+    While a CUDA graph is being recorded the key is the recording stream, so
+    recorded launches get a buffer of their own: its zero fill becomes a node of
+    the graph that first needed it (and runs again with every replay, which is
+    harmless), and the registry keeps the buffer alive after that graph is gone,
+    so later recordings on the same stream can go on using it.
     """
 
     key = (device.index if device.index is not None else torch.cuda.current_device(),
