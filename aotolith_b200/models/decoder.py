@@ -451,6 +451,8 @@ class DecoderBucketedRuntime:
         return self.buckets[-1].prompt_length
 
     def bucket_for(self, prompt_length: int) -> DecoderStaticCacheRuntime:
+        if prompt_length <= 0:
+            raise PlanInputError(f"prompt length must be positive, got {prompt_length}")
         for bucket in self.buckets:
             if prompt_length <= bucket.prompt_length:
                 return bucket
