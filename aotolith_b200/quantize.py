@@ -4,7 +4,8 @@ The format is the reference compiler's (``src/aotolith/quantize.py:1-37``):
 
 * a weight is ``[out, in]``; the ``in`` axis is cut into groups of
   ``group_size`` values that share one scale ``max|w| / magnitude`` (7 for four
-  bits, 127 for eight); an all-zero group gets unit scale;
+  bits, 127 for eight); an all-zero group is scaled as if its magnitude were one
+  (scale ``1 / magnitude``), which keeps the division finite and its codes zero;
 * codes are ``clip(rint(w / scale), lowest, magnitude)`` (round half to even),
   stored two's complement;
 * 32-bit words hold eight nibbles (or four bytes), code ``k`` of a word at bit
