@@ -143,3 +143,106 @@ def test_loaded_plan_computes_what_the_saved_one_did(cuda, tmp_path):
     want = runtime.decode(token, position, dmask, cache)
     got = decode(token, position, dmask, cache)
     assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+
+
+def _edit_manifest(path, out, edit):
+    def apply(name, data):
+        if name != "manifest.json":
+            return data
+        manifest = json.loads(data)
+        edit(manifest)
+        return json.dumps(manifest).encode()
+
+    _rewrite(path, out, apply)
+
+
+def test_state_that_does_not_fit_its_graph_input_is_refused(tmp_path):
+    """A manifest whose state entry claims another shape or dtype than the graph input it binds
+    (tests/test_artifact.py:333-387 of the reference)."""
+
+    path = _runtime().decode.save(tmp_path / "d.aoto")
+    manifest = aoto.read_artifact_manifest(path)
+    index = next(i for i, item in enumerate(manifest["entrypoint"]["state"]) if item["name"] == "final_norm")
+
+    def other_shape(m):
+        m["entrypoint"]["state"][index]["shape"] = [32, 2]           # same bytes, another shape
+
+    def other_dtype(m):
+        m["entrypoint"]["state"][index]["dtype"] = "float16"          # same bytes, another dtype
+
+    def unknown_dtype(m):
+        m["entrypoint"]["state"][index]["dtype"] = "float8"
+
+    def short_payload(m):
+        m["entrypoint"]["state"][index]["shape"] = [65]               # one element more than the payload holds
+
+    for edit in (other_shape, other_dtype, unknown_dtype, short_payload):
+        bad = tmp_path / f"{edit.__name__}.aoto"
+        _edit_manifest(path, bad, edit)
+        with pytest.raises(ArtifactCompatibilityError):
+            aoto.load_compiled_module(bad)
+
+
+def test_tampered_tables_and_missing_payloads_are_refused(tmp_path):
+    path = _runtime().decode.save(tmp_path / "d.aoto")
+    for member, needle in (("kernels.json", b"aoto_sm100_embedding"), ("lowered_graph.json", b"addmm"),
+                           ("input_graph.json", b"arg0"), ("storage_plan.json", b"arena_size_bytes")):
+        def edit(name, data, member=member, needle=needle):
+            if name == member:
+                assert needle in data
+                return data.replace(needle, needle[:-1] + b"_", 1)
+            return data
+
+        bad = tmp_path / f"tampered_{member}.aoto"
+        _rewrite(path, bad, edit)
+        with pytest.raises(ArtifactCompatibilityError, match="digest"):
+            aoto.load_compiled_module(bad)
+
+        def drop(name, data, member=member):
+            return None if name == member else data
+
+        bad = tmp_path / f"without_{member}.aoto"
+        _rewrite(path, bad, drop)
+        with pytest.raises(ArtifactCompatibilityError, match="missing"):
+            aoto.load_compiled_module(bad)
+
+
+def test_a_manifest_that_disagrees_with_its_graph_is_refused(tmp_path):
+    path = _runtime().decode.save(tmp_path / "d.aoto")
+
+    def fewer_inputs(m):
+        m["entrypoint"]["input_count"] = 3
+
+    def other_outputs(m):
+        m["graph"]["outputs"] = list(reversed(m["graph"]["outputs"]))
+
+    for edit in (fewer_inputs, other_outputs):
+        bad = tmp_path / f"{edit.__name__}.aoto"
+        _edit_manifest(path, bad, edit)
+        with pytest.raises(ArtifactCompatibilityError):
+            aoto.load_compiled_module(bad)
+
+
+def test_an_artifact_loads_in_a_new_process(tmp_path):
+    """Nothing of the compiling process is needed to read an artifact back: a fresh interpreter
+    rebuilds the plan and finds the same selections and state."""
+
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    runtime = _runtime()
+    path = runtime.decode.save(tmp_path / "d.aoto")
+    expected = [s.artifact_name for s in runtime.decode.plan.selections]
+    script = (
+        "import json, sys, aotolith_b200 as aoto\n"
+        f"plan = aoto.load_compiled_module({str(path)!r})\n"
+        "print(json.dumps({'names': list(plan.state_names), 'inputs': plan.input_count, 'target': plan.target,\n"
+        "                  'selections': [s.artifact_name for s in plan.plan.selections]}))\n"
+    )
+    root = Path(__file__).resolve().parent.parent
+    done = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, cwd=root, timeout=300)
+    assert done.returncode == 0, done.stderr[-2000:]
+    report = json.loads(done.stdout.strip().splitlines()[-1])
+    assert report["names"] == list(runtime.decode.state_names) and report["inputs"] == 4
+    assert report["target"] == "cuda-sm100" and report["selections"] == expected
