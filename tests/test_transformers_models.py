@@ -121,3 +121,55 @@ def test_a_llama_model_is_refused_by_the_qwen2_entry_point():
 
     with pytest.raises(UnsupportedModelError):
         aoto.compile_qwen2_static_cache(_build("llama"), prompt_length=PROMPT, max_new_tokens=NEW, quantize=GROUP)
+
+
+@pytest.mark.parametrize("kv_heads", [1, 2, 4])
+def test_llama_accepts_grouped_and_plain_attention(kv_heads):
+    """One kv head for all query heads, grouped, and one per query head
+    (tests/test_llama_static_cache.py:170-192 of the reference)."""
+
+    torch.manual_seed(20 + kv_heads)
+    config = transformers.LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                      num_attention_heads=4, num_key_value_heads=kv_heads,
+                                      max_position_embeddings=64, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    model = transformers.LlamaForCausalLM(config).to(torch.bfloat16).eval()
+    runtime = aoto.compile_llama_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW, quantize=GROUP,
+                                              quantize_bits=8)
+    assert runtime.num_key_value_heads == kv_heads and runtime.head_dim == 16
+    twin = _round_tripped(model, 8)
+    prompt = torch.randint(0, 128, (1, PROMPT), generator=torch.Generator().manual_seed(3))
+    oracle = OracleRuntime(runtime)
+    logits, cache = oracle.prefill(prompt)
+    with torch.no_grad():
+        want = twin(prompt).logits[:, -1:, :]
+    assert _rel(logits, want) < TOL
+    token = want[:, -1].float().argmax(dim=-1, keepdim=True)
+    logits, _ = oracle.decode(token, cache, PROMPT + 1)
+    with torch.no_grad():
+        want = twin(torch.cat((prompt, token), dim=1)).logits[:, -1:, :]
+    assert _rel(logits, want) < TOL
+
+
+def test_a_short_prompt_in_a_wide_bucket_matches_the_checkpoint():
+    """Left padding is invisible to the model's answer: prompt of 5 in a bucket of 8, eight bits
+    (close to lossless), against the round-tripped checkpoint on the unpadded prompt."""
+
+    model = _build("qwen2")
+    runtime = aoto.compile_qwen2_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW, quantize=GROUP,
+                                              quantize_bits=8)
+    twin = _round_tripped(model, 8)
+    prompt = torch.randint(0, 128, (1, 5), generator=torch.Generator().manual_seed(9))
+    oracle = OracleRuntime(runtime)
+    logits, cache = oracle.prefill(prompt)
+    with torch.no_grad():
+        want = twin(prompt).logits[:, -1:, :]
+    assert _rel(logits, want) < TOL
+    ids, valid = prompt, 5
+    for step in range(NEW - 1):
+        token = want[:, -1].float().argmax(dim=-1, keepdim=True)
+        ids = torch.cat((ids, token), dim=1)
+        valid += 1
+        logits, cache = oracle.decode(token, cache, valid)
+        with torch.no_grad():
+            want = twin(ids).logits[:, -1:, :]
+        assert _rel(logits, want) < TOL, f"decode step {step}"
