@@ -1,12 +1,18 @@
 // Prefill attention, tiled: one CTA per (64 query rows, query head), four warps of 16 rows.
 //
 // K and V of the head's kv head stream through shared memory in tiles of 64 keys (cp.async,
-// two stages); S = Q.K^T and O += P.V run on the tensor pipe (mma.sync m16n8k16, fp32
-// accumulate) with the running row maximum and sum of the online softmax in registers. The
-// probabilities go back into the second product as bf16 A fragments straight from the S
-// accumulators; V fragments are read with a transposing ldmatrix. Scores are scaled in fp32,
-// the additive mask (0 / -inf, any pattern: causal, left padding) is applied per element, rows
-// with no admitted key produce zeros.
+// two stages, one barrier per tile); S = Q.K^T and O += P.V run on the tensor pipe (mma.sync
+// m16n8k16, fp32 accumulate, B fragments by ldmatrix.x4) with the running row maximum and sum of
+// the online softmax in registers. Scores are kept in the base-2 domain (the scale carries
+// log2 e, exponentials are ex2.approx). The probabilities go back into the second product as bf16
+// A fragments straight from the S accumulators; V fragments are read with a transposing ldmatrix.
+// The additive mask (0 / -inf, any pattern: causal, left padding, banded) is applied per element;
+// rows with no admitted key produce zeros.
+//
+// With a workspace, attention_mask_classes_kernel first sorts the 64 x 64 tiles of the mask into
+// "no key admitted", "adds zero everywhere" and "mixed": the first kind is neither loaded nor
+// multiplied, the second reads no mask. Without one every tile is visited, same result. The query
+// tiles of a head are launched last-first, because under a causal mask the late ones are the long ones.
 #include <type_traits>
 
 #include "attention.cuh"
