@@ -4,12 +4,14 @@
 //   warp 0      one lane issues TMA tile loads of x (128 rows x 64 columns, 128-byte swizzle),
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (M=128, N=128, K=16) with
 //               both operands in shared memory and the fp32 accumulator in tensor memory,
-//   warps 2-5   turn packed codes into bf16 weights - bf16(code * scale), the very weight the
+//   warps 2-9   turn packed codes into bf16 weights - bf16(code * scale), the very weight the
 //               reference materialises - and store them into shared memory in the same swizzled
-//               K-major layout the TMA produces; afterwards they read the accumulator back with
-//               tcgen05.ld (each warp its own 32-lane quadrant) and run the epilogue.
+//               K-major layout the TMA produces (two warps per 32 weight rows, each half a k
+//               block); afterwards they read the accumulator back with tcgen05.ld (a warp may
+//               read its own 32-lane quadrant), turn each chunk through shared memory so that
+//               stores, addend and gate run along output rows, and run the epilogue.
 // A ring of four stages decouples the three roles; every hand-over is an mbarrier (TMA bytes,
-// 128 dequantising threads, tcgen05.commit). Every wait is bounded: a wait that runs out sets a
+// 256 dequantising threads, tcgen05.commit). Every wait is bounded: a wait that runs out sets a
 // status word, the roles fall through to the common exit and tensor memory is released.
 #include <cuda.h>
 
