@@ -212,8 +212,8 @@ def _decode_storage(entry: dict) -> StoragePlan:
 # ---------------------------------------------------------------------------
 
 def _tensor_bytes(tensor: torch.Tensor) -> bytes:
-    host = tensor.detach().to("cpu").contiguous()
-    return host.view(torch.uint8).reshape(-1).numpy().tobytes() if host.numel() else b""
+    host = tensor.detach().to("cpu").contiguous().reshape(-1)  # a 0-dim tensor has no byte view
+    return host.view(torch.uint8).numpy().tobytes() if host.numel() else b""
 
 
 def _tensor_from_bytes(payload: bytes, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
@@ -352,7 +352,17 @@ def _open(path: Path) -> zipfile.ZipFile:
         raise ArtifactCompatibilityError(f"{path} is not a readable artifact: {error}") from error
 
 
+def _safe_payload_name(name: Any) -> str:
+    """A payload name from the manifest: a relative path inside the archive, nothing else."""
+
+    if (not isinstance(name, str) or not name or name.startswith(("/", "\\")) or "\\" in name or ":" in name
+            or any(part in ("", ".", "..") for part in name.split("/"))):
+        raise ArtifactCompatibilityError(f"artifact payload name {name!r} is not a plain relative path")
+    return name
+
+
 def _read(archive: zipfile.ZipFile, name: str) -> bytes:
+    name = _safe_payload_name(name)
     try:
         return archive.read(name)
     except KeyError as error:
@@ -395,9 +405,16 @@ def read_artifact_manifest(path: str | os.PathLike[str]) -> dict:
     """The validated manifest of an artifact, without touching its payloads."""
 
     with _open(Path(path)) as archive:
-        manifest = json.loads(_read(archive, "manifest.json"))
+        manifest = _json(_read(archive, "manifest.json"), "manifest")
     _validate_manifest(manifest, require_device_match=False)
     return manifest
+
+
+def _json(payload: bytes, label: str) -> Any:
+    try:
+        return json.loads(payload)
+    except (ValueError, UnicodeDecodeError) as error:
+        raise ArtifactCompatibilityError(f"artifact {label} is not valid JSON: {error}") from error
 
 
 def load_compiled_module(
@@ -412,12 +429,27 @@ def load_compiled_module(
     stored lowered graph; the result must select what the stored records say
     (same implementation, kind and kernel variant per operation), else the
     artifact is refused: it was produced by a library whose selection rules differ.
+    A malformed artifact (broken JSON, a missing key, a field of the wrong type) is
+    refused with :class:`ArtifactCompatibilityError` like any other mismatch.
     """
+
+    try:
+        return _load_compiled_module(path, require_device_match=require_device_match, device=device)
+    except ArtifactCompatibilityError:
+        raise
+    except (KeyError, TypeError, ValueError, IndexError, AttributeError) as error:
+        raise ArtifactCompatibilityError(
+            f"{path} is malformed: {type(error).__name__}: {error}",
+            hint="the artifact was truncated, edited or written by an incompatible library",
+        ) from error
+
+
+def _load_compiled_module(path, *, require_device_match: bool, device: Any):
 
     from .compiler import CompilationResult, CompiledModulePlan, _to_device_once, backend_for
 
     with _open(Path(path)) as archive:
-        manifest = json.loads(_read(archive, "manifest.json"))
+        manifest = _json(_read(archive, "manifest.json"), "manifest")
         _validate_manifest(manifest, require_device_match=require_device_match)
         names = manifest["payloads"]
         lowered_bytes = _read(archive, names["lowered_graph"])
@@ -430,8 +462,8 @@ def load_compiled_module(
         _check_digest(kernels_bytes, manifest["payload_digests"].get("kernels"), "kernel table")
         _check_digest(selections_bytes, manifest["payload_digests"].get("selections"), "selections")
         _check_digest(storage_bytes, manifest["payload_digests"].get("storage_plan"), "storage plan")
-        lowered = decode_graph(json.loads(lowered_bytes))
-        captured = decode_graph(json.loads(input_bytes))
+        lowered = decode_graph(_json(lowered_bytes, "lowered graph"))
+        captured = decode_graph(_json(input_bytes, "input graph"))
         if list(lowered.inputs) != manifest["graph"].get("inputs") or list(lowered.outputs) != manifest["graph"].get("outputs"):
             raise ArtifactCompatibilityError("manifest graph inputs or outputs do not match the stored graph")
         entry = manifest["entrypoint"]
@@ -451,8 +483,8 @@ def load_compiled_module(
                 loaded[file_name] = tensor
             state_values.append(tensor)
 
-    stored_selections = tuple(_decode_selection(s) for s in json.loads(selections_bytes))
-    stored_storage = _decode_storage(json.loads(storage_bytes))
+    stored_selections = tuple(_decode_selection(s) for s in _json(selections_bytes, "selections"))
+    stored_storage = _decode_storage(_json(storage_bytes, "storage plan"))
     options = manifest["compile_options"]
     target = str(manifest["target"])
     backend = backend_for(target, codegen_matmul=bool(options.get("codegen_matmul")),

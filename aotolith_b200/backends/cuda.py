@@ -444,7 +444,7 @@ def _lower_projection(b: _Builder, index: int, op: Operation) -> None:
     b.record(index, op, CUDA_KERNEL,
              "multi-row projection over a packed weight: unpacked to bf16 on the fly, never stored",
              fn, f"aoto_sm100_qmatmul[{variant}]",
-             (("M", rows), ("N", n_rows), ("K", words * 8)))
+             (("M", rows), ("N", n_rows), ("K", words * (32 // unpack_bits)), ("weight_bits", unpack_bits)))
 
 
 class CudaBackend:

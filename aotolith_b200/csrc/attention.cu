@@ -291,7 +291,10 @@ extern "C" int aoto_sm100_attention(const aoto_attention_args* a, void* stream_)
   p.mask = (const bf16*)a->mask; p.out = (bf16*)a->out; p.scratch = (float*)a->scratch;
   p.QH = a->query_heads; p.KVH = a->kv_heads; p.Lq = a->q_len; p.Lk = a->kv_len; p.D = a->head_dim;
   p.causal = a->causal; p.scale = a->scale;
-  if (a->q_len == 1) {
+  // One query under the top-left aligned causal rule sees key 0 only; the split-KV decode kernel
+  // attends the whole window, so that case goes to the prefill kernels, which apply the rule.
+  const bool causal_single = a->causal && a->kv_len > 1;
+  if (a->q_len == 1 && !causal_single) {
     if ((a->head_dim & 7) || !aligned_to(a->k, 16) || !aligned_to(a->v, 16)) return AOTO_ERR_UNSUPPORTED;
     decode_tiling(*a, &p.keys_per_split, &p.splits);
     if (p.splits > 1) {
@@ -304,15 +307,8 @@ extern "C" int aoto_sm100_attention(const aoto_attention_args* a, void* stream_)
                         ((size_t)G * a->head_dim + (size_t)G * p.keys_per_split + (size_t)G * 2 +
                          p.keys_per_split) * 4;
     if (smem > 48 * 1024) {
-      static bool raised = false;
-      if (!raised) {
-        if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 160 * 1024) != cudaSuccess) {
-          (void)cudaGetLastError();
-          return AOTO_ERR_LAUNCH;
-        }
-        raised = true;
-      }
+      static PerDeviceOnce raised;
+      if (raise_dynamic_smem(attention_decode_kernel, 160 * 1024, raised) != AOTO_OK) return AOTO_ERR_LAUNCH;
       if (smem > 160 * 1024) return AOTO_ERR_UNSUPPORTED;
     }
     return launch_kernel(attention_decode_kernel, dim3(a->kv_heads, p.splits), dim3(DECODE_THREADS),
@@ -348,7 +344,6 @@ extern "C" int aoto_sm100_attention(const aoto_attention_args* a, void* stream_)
 static __device__ __align__(256) unsigned char static_scratch[AOTO_STATIC_SCRATCH_BYTES];
 
 namespace {
-constexpr int MAX_DEVICES = 64;
 void* static_scratch_address[MAX_DEVICES] = {};
 
 // Device address of the static scratch array on the current device, or nullptr.

@@ -347,14 +347,8 @@ int64_t attention_prefill_scratch_bytes(const AttnParams& p) {
 template <int D>
 static int launch_prefill(const AttnParams& p, cudaStream_t stream) {
   constexpr size_t smem = (size_t)(PF_BQ + 4 * PF_BK) * (D * 2 + 16);
-  static bool raised = false;
-  if (!raised) {
-    if (cudaFuncSetAttribute(attention_prefill_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return AOTO_ERR_LAUNCH;
-    }
-    raised = true;
-  }
+  static PerDeviceOnce raised;
+  if (raise_dynamic_smem(attention_prefill_mma_kernel<D>, smem, raised) != AOTO_OK) return AOTO_ERR_LAUNCH;
   dim3 grid((p.Lq + PF_BQ - 1) / PF_BQ, p.QH);
   return launch_kernel(attention_prefill_mma_kernel<D>, grid, dim3(PF_THREADS), smem, stream, false, p);
 }

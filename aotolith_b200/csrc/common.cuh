@@ -111,6 +111,30 @@ inline bool aligned_to(const void* ptr, size_t bytes) {
   return (reinterpret_cast<uintptr_t>(ptr) % bytes) == 0;
 }
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) belongs to (function, device): a process that
+// drives several GPUs must make the call once on each of them. One flag per device ordinal; a
+// race between host threads only repeats the idempotent call.
+constexpr int MAX_DEVICES = 64;
+struct PerDeviceOnce {
+  bool done[MAX_DEVICES] = {};
+};
+template <typename Kernel>
+inline int raise_dynamic_smem(Kernel kernel, size_t bytes, PerDeviceOnce& once) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return AOTO_ERR_LAUNCH;
+  }
+  const bool tracked = device >= 0 && device < MAX_DEVICES;
+  if (tracked && once.done[device]) return AOTO_OK;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return AOTO_ERR_LAUNCH;
+  }
+  if (tracked) once.done[device] = true;
+  return AOTO_OK;
+}
+
 // Launch with or without the programmatic-dependent-launch attribute.
 template <typename Kernel, typename... Args>
 inline int launch_kernel(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

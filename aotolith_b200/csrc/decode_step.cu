@@ -1264,14 +1264,8 @@ extern "C" int aoto_sm100_decode_step(const aoto_decode_step_args* a, void* stre
   cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device);
   if (!coop) return AOTO_ERR_UNSUPPORTED;
   const size_t smem = step_smem_bytes();
-  static bool raised = false;
-  if (!raised) {
-    if (cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return AOTO_ERR_LAUNCH;
-    }
-    raised = true;
-  }
+  static PerDeviceOnce raised;
+  if (raise_dynamic_smem(decode_step_kernel, smem, raised) != AOTO_OK) return AOTO_ERR_LAUNCH;
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel, STEP_THREADS, smem) != cudaSuccess ||
       per_sm < 1) {

@@ -171,14 +171,8 @@ template <int WN, int WM>
 static int launch_gemm(const GemmParams& p, cudaStream_t stream) {
   auto kernel = qgemm_mma_kernel<WN, WM>;
   const size_t smem = 2 * (size_t)GEMM_STAGE_BYTES;
-  static bool raised = false;
-  if (!raised) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return AOTO_ERR_LAUNCH;
-    }
-    raised = true;
-  }
+  static PerDeviceOnce raised;
+  if (raise_dynamic_smem(kernel, smem, raised) != AOTO_OK) return AOTO_ERR_LAUNCH;
   const int tiles = (p.N + 15) / 16;
   dim3 grid((tiles + WN - 1) / WN, (p.M + GEMM_M_TILE - 1) / GEMM_M_TILE), block(WN * WM * 32);
   return launch_kernel(kernel, grid, block, smem, stream, false, p);

@@ -507,15 +507,10 @@ int qgemm_tc_launch(const aoto_qmatmul_args& a, cudaStream_t stream) {
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return AOTO_ERR_ARGUMENT;
 
-  static bool raised = false;
-  if (!raised) {
-    if (cudaFuncSetAttribute(qgemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(1)) != cudaSuccess ||
-        cudaFuncSetAttribute(qgemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(2)) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return AOTO_ERR_LAUNCH;
-    }
-    raised = true;
-  }
+  static PerDeviceOnce raised1, raised2;
+  if (raise_dynamic_smem(qgemm_tc_kernel<1>, tc_smem_bytes(1), raised1) != AOTO_OK ||
+      raise_dynamic_smem(qgemm_tc_kernel<2>, tc_smem_bytes(2), raised2) != AOTO_OK)
+    return AOTO_ERR_LAUNCH;
   TcParams p;
   p.w = (const uint32_t*)a.packed;
   p.s = (const bf16*)a.scales;

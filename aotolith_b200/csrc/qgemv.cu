@@ -244,14 +244,8 @@ static int launch_mma(const GemvParams& p, const GemvPlan& plan, int M, cudaStre
                       (size_t)MATS * RT * plan.W * 16 * 4 + 32 * 4 + 16;
   auto kernel = qgemv_mma_kernel<RT, UK, PAIRED>;
   if (smem > 48 * 1024) {
-    static bool raised = false;  // idempotent; a race only repeats the call
-    if (!raised) {
-      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return AOTO_ERR_LAUNCH;
-      }
-      raised = true;
-    }
+    static PerDeviceOnce raised;
+    if (raise_dynamic_smem(kernel, 100 * 1024, raised) != AOTO_OK) return AOTO_ERR_LAUNCH;
   }
   const int tiles = (p.N + 15) / 16;
   dim3 grid((tiles + RT - 1) / RT, M), block(plan.W * 32);
@@ -294,14 +288,8 @@ int qgemv_launch(const aoto_qmatmul_args& a, cudaStream_t stream) {
     if (a.K > 49152) return AOTO_ERR_UNSUPPORTED;
     const size_t smem = (size_t)a.K * 2 + 32 * 4;
     if (smem > 48 * 1024) {
-      static bool raised = false;
-      if (!raised) {
-        if (cudaFuncSetAttribute(qgemv_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess) {
-          (void)cudaGetLastError();
-          return AOTO_ERR_LAUNCH;
-        }
-        raised = true;
-      }
+      static PerDeviceOnce raised;
+      if (raise_dynamic_smem(qgemv_generic_kernel, 100 * 1024, raised) != AOTO_OK) return AOTO_ERR_LAUNCH;
     }
     dim3 grid((a.N + 7) / 8, a.M), block(256);
     return launch_kernel(qgemv_generic_kernel, grid, block, smem, stream, pdl, p);

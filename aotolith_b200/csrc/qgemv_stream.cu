@@ -160,25 +160,15 @@ int qgemv_stream_launch(const aoto_qmatmul_args& a, cudaStream_t stream) {
   p.N = a.N; p.K = a.K; p.group = a.group_size;
   p.addend_kind = a.addend_kind; p.epilogue = a.epilogue;
   p.alpha = a.alpha; p.beta = a.beta; p.eps = a.rms_norm_eps;
-  static int sms = 0;
-  static bool raised = false;
-  if (sms == 0) {
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
-      (void)cudaGetLastError();
-      sms = 0;
-      return AOTO_ERR_LAUNCH;
-    }
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
+    (void)cudaGetLastError();
+    return AOTO_ERR_LAUNCH;
   }
-  const size_t smem = stream_smem_bytes(STREAM_MAX_K, WARPS);
-  if (!raised) {
-    if (cudaFuncSetAttribute(qgemv_stream_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return AOTO_ERR_LAUNCH;
-    }
-    raised = true;
-  }
+  static PerDeviceOnce raised;
+  if (raise_dynamic_smem(qgemv_stream_kernel<WARPS>, stream_smem_bytes(STREAM_MAX_K, WARPS), raised) != AOTO_OK)
+    return AOTO_ERR_LAUNCH;
   const int tiles = (a.N + 15) / 16;
   const int ctas = min(sms, (tiles + WARPS - 1) / WARPS);
   return launch_kernel(qgemv_stream_kernel<WARPS>, dim3(ctas), dim3(WARPS * 32), stream_smem_bytes(a.K, WARPS), stream,

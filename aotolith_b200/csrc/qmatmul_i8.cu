@@ -143,14 +143,8 @@ static int launch_i8(const GemvParams& p, int M, cudaStream_t stream, bool pdl) 
   const size_t smem = (size_t)MR * p.K * 2 + 32 * 4;
   auto kernel = qmatmul_i8_kernel<MR>;
   if (smem > 48 * 1024) {
-    static bool raised = false;  // idempotent; a race only repeats the call
-    if (!raised) {
-      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return AOTO_ERR_LAUNCH;
-      }
-      raised = true;
-    }
+    static PerDeviceOnce raised;
+    if (raise_dynamic_smem(kernel, 160 * 1024, raised) != AOTO_OK) return AOTO_ERR_LAUNCH;
     if (smem > 160 * 1024) return AOTO_ERR_UNSUPPORTED;
   }
   const int row_groups = (M + MR - 1) / MR;

@@ -53,10 +53,11 @@ class DecodeSession:
         self.graphs: list[torch.cuda.CUDAGraph] = []
         self.programs: list[torch.Tensor] = []
         self.mode = "graphs"
-        if self.plan.step_program is not None and self._bind_program():
-            self.mode = "kernel"
-        else:
-            self._record()
+        with torch.cuda.device(device):
+            if self.plan.step_program is not None and self._bind_program():
+                self.mode = "kernel"
+            else:
+                self._record()
 
     # -- persistent kernel ---------------------------------------------------------
     def _bind_program(self) -> bool:
@@ -153,6 +154,10 @@ class DecodeSession:
             raise PlanInputError(f"steps must be in [0, {self.generated.numel()}], got {steps}")
         if valid_length + steps >= self.runtime.cache_capacity + 1:
             raise PlanInputError("the requested steps do not fit the cache capacity")
+        with torch.cuda.device(self.device):  # launches go to the current device's stream
+            return self._run(token, cache, valid_length, steps)
+
+    def _run(self, token: torch.Tensor, cache: torch.Tensor, valid_length: int, steps: int) -> torch.Tensor:
         self.token.copy_(token.reshape(1, 1))
         self.caches[0].copy_(cache)
         self.counters.copy_(

@@ -28,14 +28,40 @@ def _ptr(tensor: torch.Tensor | None) -> int | None:
     return None if tensor is None else tensor.data_ptr()
 
 
-def _need_cuda(*tensors: torch.Tensor | None) -> None:
-    for tensor in tensors:
-        if tensor is not None and not tensor.is_cuda:
+def check_operand_devices(devices, current_index: int) -> None:
+    """Refuse operands that are not all on the current CUDA device.
+
+    The kernels are launched on the current device's current stream and never
+    look at which device a pointer belongs to: an operand of another GPU would be
+    dereferenced on the wrong one. ``devices`` are the operands' ``torch.device``s.
+    """
+
+    seen = []
+    for device in devices:
+        if device.type != "cuda":
             raise DeviceError(
-                "the cuda-sm100 kernels take CUDA tensors; got a tensor on "
-                f"{tensor.device}",
+                f"the cuda-sm100 kernels take CUDA tensors; got a tensor on {device}",
                 hint="there is no CPU path on this target; move the operands to the GPU",
             )
+        index = current_index if device.index is None else device.index
+        if index not in seen:
+            seen.append(index)
+    if len(seen) > 1:
+        raise DeviceError(
+            f"the operands of one kernel sit on different GPUs: cuda:{seen[0]} and cuda:{seen[1]}",
+            hint="move every operand to the device the plan was compiled for",
+        )
+    if seen and seen[0] != current_index:
+        raise DeviceError(
+            f"the operands are on cuda:{seen[0]} but the current CUDA device is cuda:{current_index}",
+            hint="run the call under `with torch.cuda.device(tensor.device):`",
+        )
+
+
+def _need_cuda(*tensors: torch.Tensor | None) -> None:
+    devices = [tensor.device for tensor in tensors if tensor is not None]
+    on_gpu = bool(devices) and all(device.type == "cuda" for device in devices)
+    check_operand_devices(devices, torch.cuda.current_device() if on_gpu else -1)
 
 
 def _bf16(tensor: torch.Tensor | None, name: str) -> None:

@@ -254,10 +254,12 @@ class CompiledPlan:
     ) -> tuple[torch.Tensor, ...]:
         if memory not in MEMORY_POLICIES:
             raise PlanInputError(f"unknown memory policy {memory!r}; choose one of {MEMORY_POLICIES}")
-        ready = self._coerce(inputs)
-        if memory == "latency":
-            return self._replay(ready, verify_index_bounds)
-        return self.run_eager(ready, verify_index_bounds=verify_index_bounds)
+        # the kernels launch on the CURRENT device's stream: make the plan's device current
+        with torch.cuda.device(self._device()):
+            ready = self._coerce(inputs)
+            if memory == "latency":
+                return self._replay(ready, verify_index_bounds)
+            return self.run_eager(ready, verify_index_bounds=verify_index_bounds)
 
     # -- CUDA-graph stepper --------------------------------------------------------
     def _replay(self, inputs: list[torch.Tensor], verify_index_bounds: bool = False) -> tuple[torch.Tensor, ...]:

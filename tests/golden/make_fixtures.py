@@ -19,7 +19,12 @@ Writes, next to this file:
   (``python make_fixtures.py <reference> int8`` writes only the eight-bit files);
 * ``lowered_graphs_int8.json``, ``adapter_eager_int8_<family>.npz`` - the lowered graphs and
   eager outputs of the same toy decoders packed with eight bits (the weights are the ones stored
-  in ``adapter_eager_<family>.npz``).
+  in ``adapter_eager_<family>.npz``);
+* ``adapter_eager_qwen05b_cut.npz`` - a two-layer cut of the Qwen2.5-0.5B shape (hidden 896, MLP
+  4864, 14/2 heads of 64, vocabulary 151 936, group 64; weights from
+  ``qwen25_05b_shaped(seed=7, layers=2)``, not stored): prompt, the reference adapters' prefill
+  logits of the last prompt position, per-step decode logits (bf16 bit patterns) and greedy tokens
+  (``python make_fixtures.py <reference> real`` writes only this file).
 
 The reference package refuses to import off Apple silicon and needs MLX, so it
 is loaded by path with a permissive ``mlx`` stub; only its torch/NumPy code runs.
@@ -205,6 +210,47 @@ def run_family(family: str, bits: int):
     return entry, arrays
 
 
+REAL_PROMPT, REAL_NEW, REAL_GROUP, REAL_SEED = 16, 6, 64, 7
+
+
+def write_real_shape_cut() -> None:
+    """Two layers of the Qwen2.5-0.5B shape through the reference's quantized adapters, eagerly."""
+
+    import aotolith.models.decoder as D
+    from aotolith_b200.models.synthetic import qwen25_05b_shaped
+
+    model = qwen25_05b_shaped(seed=REAL_SEED, layers=2)
+    capacity = REAL_PROMPT + REAL_NEW
+    settings = dict(cache_capacity=capacity, group_size=REAL_GROUP, weight_bits=4, require="qwen2")
+    prefill = D.QuantizedDecoderPrefillModule(model, **settings).eval()
+    decode = D.QuantizedDecoderDecodeModule(model, **settings).eval()
+    prompt = torch.randint(0, model.config.vocab_size, (1, REAL_PROMPT), generator=torch.Generator().manual_seed(107))
+    with torch.no_grad():
+        logits, compact = prefill(prompt, torch.arange(REAL_PROMPT)[None, :],
+                                  torch.from_numpy(D.prefill_mask(REAL_PROMPT, REAL_PROMPT)))
+        cache = torch.cat((torch.zeros(compact.shape[:4] + (REAL_NEW,) + compact.shape[5:], dtype=compact.dtype),
+                           compact), dim=4)
+        rows = [logits[0, -1, :]]
+        token = logits[:, -1, :].float().argmax(dim=-1, keepdim=True)
+        tokens = [int(token)]
+        valid = REAL_PROMPT
+        for _ in range(REAL_NEW - 1):
+            valid += 1
+            mask = (torch.arange(capacity) >= capacity - valid).reshape(1, 1, 1, capacity)
+            logits, cache = decode(token, torch.tensor([[valid - 1]]), mask, cache)
+            rows.append(logits[0, -1, :])
+            token = logits[:, -1, :].float().argmax(dim=-1, keepdim=True)
+            tokens.append(int(token))
+    stacked = torch.stack(rows)
+    assert stacked.dtype == torch.bfloat16
+    np.savez_compressed(
+        HERE / "adapter_eager_qwen05b_cut.npz", prompt=prompt.numpy(), tokens=np.array(tokens),
+        logits_bf16_bits=stacked.view(torch.int16).numpy(),
+        final_cache_bf16_bits=cache.contiguous().view(torch.int16).numpy(),
+        settings=np.array([REAL_PROMPT, REAL_NEW, REAL_GROUP, REAL_SEED]))
+    print("qwen05b cut: tokens", tokens)
+
+
 def write_int8_decoders() -> None:
     """The toy decoders packed with eight bits: the reference's lowered graphs and eager outputs."""
 
@@ -243,6 +289,9 @@ def write_int8_kat() -> None:
 
 def main(reference: str, only: str | None = None) -> None:
     load_reference(reference)
+    if only == "real":
+        write_real_shape_cut()
+        return
     if only == "int8":
         write_int8_kat()
         write_int8_decoders()
@@ -270,10 +319,11 @@ def main(reference: str, only: str | None = None) -> None:
     np.savez_compressed(HERE / "quantize_kat.npz", **mats)
     write_int8_kat()
     write_int8_decoders()
+    write_real_shape_cut()
     print("fixtures written to", HERE)
 
 
 if __name__ == "__main__":
     if len(sys.argv) not in (2, 3):
-        raise SystemExit("usage: python make_fixtures.py <path of a checkout of the reference project> [int8]")
+        raise SystemExit("usage: python make_fixtures.py <path of a checkout of the reference project> [int8|real]")
     main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)

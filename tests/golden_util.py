@@ -73,3 +73,17 @@ def canonical_graph(graph) -> dict:
             "output_types": [[list(graph.value(v).type.shape), graph.value(v).type.dtype.value] for v in op.outputs],
         })
     return {"inputs": len(graph.inputs), "ops": ops, "outputs": [name(v) for v in graph.outputs]}
+
+
+def real_shape_fixture():
+    """``(model, arrays)`` of the two-layer cut of the Qwen2.5-0.5B shape (weights from the seed)."""
+
+    from aotolith_b200.models.synthetic import qwen25_05b_shaped
+
+    data = dict(np.load(GOLDEN / "adapter_eager_qwen05b_cut.npz"))
+    prompt_length, new_tokens, group, seed = (int(v) for v in data["settings"])
+    model = qwen25_05b_shaped(seed=seed, layers=2)
+    data["logits"] = torch.from_numpy(data["logits_bf16_bits"]).view(torch.bfloat16).float()
+    data["final_cache"] = torch.from_numpy(data["final_cache_bf16_bits"]).view(torch.bfloat16).float()
+    data.update(prompt_length=prompt_length, new_tokens=new_tokens, group=group)
+    return model, data

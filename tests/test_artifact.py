@@ -223,6 +223,55 @@ def test_a_manifest_that_disagrees_with_its_graph_is_refused(tmp_path):
             aoto.load_compiled_module(bad)
 
 
+def test_malformed_artifacts_are_refused_with_the_coded_error(tmp_path):
+    """Broken JSON, missing keys, wrong field types and unsafe payload names never escape as raw
+    KeyError / TypeError / JSONDecodeError."""
+
+    path = _runtime().decode.save(tmp_path / "d.aoto")
+
+    def truncated_manifest(name, data):
+        return data[: len(data) // 2] if name == "manifest.json" else data
+
+    def broken_selections(name, data):
+        return b"[{" if name == "selections.json" else data
+
+    for index, edit in enumerate((truncated_manifest, broken_selections)):
+        bad = tmp_path / f"broken_{index}.aoto"
+        _rewrite(path, bad, edit)
+        with pytest.raises(ArtifactCompatibilityError):
+            aoto.load_compiled_module(bad)
+
+    def no_state_file(m):
+        del m["entrypoint"]["state"][0]["file"]
+
+    def no_input_count(m):
+        del m["entrypoint"]["input_count"]
+
+    def shape_of_wrong_type(m):
+        m["entrypoint"]["state"][0]["shape"] = "wide"
+
+    def escaping_payload(m):
+        m["payloads"]["kernels"] = "../kernels.json"
+
+    def no_payload_table(m):
+        del m["payloads"]
+
+    for edit in (no_state_file, no_input_count, shape_of_wrong_type, escaping_payload, no_payload_table):
+        bad = tmp_path / f"{edit.__name__}.aoto"
+        _edit_manifest(path, bad, edit)
+        with pytest.raises(ArtifactCompatibilityError):
+            aoto.load_compiled_module(bad)
+
+
+def test_scalar_state_has_a_byte_payload():
+    from aotolith_b200.artifact import _tensor_bytes, _tensor_from_bytes
+
+    for value in (torch.tensor(1.5, dtype=torch.bfloat16), torch.tensor(-2.0), torch.zeros((), dtype=torch.int64)):
+        data = _tensor_bytes(value)
+        assert len(data) == value.element_size()
+        assert torch.equal(_tensor_from_bytes(data, (), value.dtype), value)
+
+
 def test_an_artifact_loads_in_a_new_process(tmp_path):
     """Nothing of the compiling process is needed to read an artifact back: a fresh interpreter
     rebuilds the plan and finds the same selections and state."""

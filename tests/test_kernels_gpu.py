@@ -336,6 +336,24 @@ def test_attention_fully_masked_rows_are_zero(cuda):
     assert not got.any()
 
 
+@pytest.mark.parametrize("QH,KVH,C,D", [(14, 2, 192, 64), (4, 2, 40, 16), (8, 8, 1, 64)])
+def test_attention_single_query_causal_sees_key_zero_only(cuda, QH, KVH, C, D):
+    """Top-left aligned causal rule with one query row: only key 0 is admitted (the oracle's
+    and the reference's ``_causal_mask``); the split-KV decode kernel must not serve this case."""
+
+    ops = _ops()
+    q = activations(140, 1, QH, 1, D)
+    k = activations(141, 1, KVH, C, D)
+    v = activations(142, 1, KVH, C, D)
+    got = ops.attention(q.to(cuda), k.to(cuda), v.to(cuda), None, scale=D ** -0.5, causal=True).cpu()
+    want = ref.attention(q, k, v, None, scale=D ** -0.5, causal=True)
+    assert rel_max_error(got, want) < ORACLE_TOL
+    # with one admitted key the result is that key's value row, head by head
+    group = QH // KVH
+    for head in range(QH):
+        assert torch.equal(got[0, head, 0], v[0, head // group, 0])
+
+
 @pytest.mark.parametrize("QH,KVH,P,D,length", [(14, 2, 128, 64, 128), (14, 2, 64, 64, 37), (32, 8, 96, 128, 96), (4, 2, 7, 8, 3),
                                                   (8, 2, 200, 64, 131), (8, 4, 257, 128, 257), (2, 1, 16, 64, 16),
                                                   (8, 2, 512, 64, 300), (8, 2, 1024, 128, 1024), (4, 4, 384, 128, 65)])
