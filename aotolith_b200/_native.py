@@ -150,6 +150,37 @@ class DecodeStepArgs(Structure):
     ]
 
 
+class StreamStage(Structure):
+    """Mirror of ``aoto_stream_stage`` (64 bytes)."""
+
+    _fields_ = [
+        ("x", c_void_p), ("out", c_void_p), ("addend", c_void_p), ("norm_weight", c_void_p),
+        ("N", c_int32), ("K", c_int32),
+        ("alpha", c_float), ("beta", c_float), ("rms_norm_eps", c_float),
+        ("kind", ctypes.c_uint8), ("epilogue", ctypes.c_uint8), ("addend_mode", ctypes.c_uint8), ("flags", ctypes.c_uint8),
+        ("next_attention", c_int32), ("reserved", c_int32),
+    ]
+
+
+class StreamStepArgs(Structure):
+    """Mirror of ``aoto_stream_step_args``."""
+
+    _fields_ = [
+        ("stages", c_void_p), ("cta_table", c_void_p), ("starts", c_void_p), ("stream", c_void_p),
+        ("stream_bytes", c_int64),
+        ("stage_count", c_int32), ("ctas", c_int32), ("ring_depth", c_int32), ("max_k", c_int32),
+        ("query_heads", c_int32), ("kv_heads", c_int32), ("capacity", c_int32), ("head_dim", c_int32),
+        ("query_start", c_int32), ("key_start", c_int32), ("value_start", c_int32), ("table_rows", c_int32),
+        ("scale", c_float), ("first_attention", c_int32),
+        ("cos_table", c_void_p), ("sin_table", c_void_p), ("position", c_void_p), ("mask", c_void_p),
+        ("x_index", c_void_p), ("x_rows", c_int64),
+        ("token", c_void_p), ("generated", c_void_p), ("counters", c_void_p),
+        ("generated_capacity", c_int32), ("window", c_int32),
+        ("epoch", ctypes.c_uint32), ("reserved", c_int32),
+        ("status", c_void_p), ("scratch", c_void_p), ("scratch_bytes", c_int64), ("trace", c_void_p),
+    ]
+
+
 STAGE_GEMV, STAGE_ATTENTION, STAGE_PICK = 1, 2, 3
 STAGE_FLAG_ARGMAX, STAGE_FLAG_WINDOW, STAGE_FLAG_OUT_PLAIN, STAGE_FLAG_X_GATHER = 2, 4, 8, 16
 STAGE_ADDEND_NONE, STAGE_ADDEND_PLAIN, STAGE_ADDEND_STAMPED, STAGE_ADDEND_GATHER = 0, 1, 2, 3
@@ -188,6 +219,10 @@ EXPORTS: dict[str, tuple] = {
     "aoto_sm100_decode_step_supported": (c_int, [POINTER(StepStage), c_int32]),
     "aoto_sm100_decode_step_stage_size": (c_int, []),
     "aoto_sm100_stamped_bytes": (c_int64, [c_int64]),
+    "aoto_sm100_stream_step": (c_int, [POINTER(StreamStepArgs), c_void_p]),
+    "aoto_sm100_stream_step_smem_bytes": (c_int64, [POINTER(StreamStepArgs)]),
+    "aoto_sm100_stream_step_scratch_bytes": (c_int64, [c_int32]),
+    "aoto_sm100_stream_stage_size": (c_int, []),
     "aoto_sm100_kv_cache_append": (c_int, [POINTER(KvAppendArgs), c_void_p]),
     "aoto_sm100_attention": (c_int, [POINTER(AttentionArgs), c_void_p]),
     "aoto_sm100_attention_scratch_bytes": (c_int64, [POINTER(AttentionArgs)]),
@@ -233,6 +268,12 @@ def load() -> ctypes.CDLL:
             raise DeviceError(
                 "the stage descriptor of the kernel library and of this binding differ in size "
                 f"({lib.aoto_sm100_decode_step_stage_size()} vs {ctypes.sizeof(StepStage)})",
+                hint="rebuild with `python -m aotolith_b200.csrc.build --force`",
+            )
+        if lib.aoto_sm100_stream_stage_size() != ctypes.sizeof(StreamStage):
+            raise DeviceError(
+                "the streamed-step stage descriptor of the kernel library and of this binding differ in size "
+                f"({lib.aoto_sm100_stream_stage_size()} vs {ctypes.sizeof(StreamStage)})",
                 hint="rebuild with `python -m aotolith_b200.csrc.build --force`",
             )
         if lib.aoto_sm100_abi_version() != ABI_VERSION:

@@ -1,0 +1,1025 @@
+// One decode step as one persistent kernel whose weights run ahead of the dependency chain.
+//
+// The grid is one CTA of sixteen warps per SM. The host lays the packed weights out ONCE as
+// one byte stream per (CTA, warp): the 16 x 128 blocks the warp will multiply, stage after
+// stage, already in tensor-core fragment order, cut into pieces of at most three blocks with a
+// 16-byte header each. A warp keeps `ring_depth` pieces in flight into its own ring in shared
+// memory with bulk copies (cp.async.bulk + mbarrier, no multicast) and refills a slot the
+// moment it has multiplied it, across stage boundaries. When the input row of a stage arrives,
+// its weights have been resident for several stages.
+//
+// Stages exchange their vectors as 8-byte stamped words {two bf16, launch epoch} through L2;
+// a consumer polls the words it needs until they carry the epoch. No grid-wide barrier exists.
+// Every wait - on a stamped word or on an mbarrier - is bounded: a CTA whose wait runs out
+// records the stage in `status`, waits (bounded) for its own copies in flight and returns.
+#include "qgemv_core.cuh"
+
+namespace aoto {
+
+constexpr int SS_WARPS = AOTO_STREAM_WARPS;
+constexpr int SS_THREADS = SS_WARPS * 32;
+constexpr int SS_BLOCK_BYTES = AOTO_STREAM_BLOCK_BYTES;
+constexpr int SS_SLOT_BYTES = AOTO_STREAM_SLOT_BYTES;
+constexpr int SS_MAX_K = 16384;
+constexpr int SS_MAX_CHUNKS = SS_MAX_K / 8 / SS_THREADS;  // 8-value chunks of the input row per thread
+constexpr int SS_POLL_LIMIT = 1 << 20;  // rounds of a bounded poll (each is at least one L2 round trip)
+constexpr int SS_PART_SLOTS = AOTO_STREAM_PART_SLOTS + SS_WARPS;  // shared tiles, then one private slot per warp
+constexpr int SS_PART_BYTES = 128;      // [matrix][row] floats of one share
+constexpr int SS_MAX_WINDOW_KEYS = 16;  // keys per warp in the one-CTA-per-head attention form
+
+// ---------------------------------------------------------------------------
+// shared-memory layout, computed identically on both sides
+// ---------------------------------------------------------------------------
+struct SSLayout {
+  uint32_t ring, bars, kvbars, stages, table, work, xs, xsum, part, red, kv, total;
+  int keys_per_warp;
+};
+
+__host__ __device__ inline uint32_t ss_align(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+__host__ __device__ inline SSLayout ss_layout(int stage_count, int max_k, int depth, int capacity, int head_dim,
+                                              bool has_attention) {
+  SSLayout L;
+  uint32_t off = 0;
+  L.ring = off; off += (uint32_t)SS_WARPS * depth * SS_SLOT_BYTES;
+  L.bars = off; off += (uint32_t)SS_WARPS * AOTO_STREAM_MAX_RING * 8;
+  L.kvbars = off; off += (uint32_t)SS_WARPS * 8;
+  L.stages = off; off += (uint32_t)stage_count * (uint32_t)sizeof(aoto_stream_stage);
+  L.table = off; off += ss_align((uint32_t)stage_count * 4, 16);
+  // work region: the staged row, its group sums and the partial sums of a GEMV stage; an
+  // attention stage uses the same bytes for its row values, query and per-warp results
+  L.work = off;
+  L.xs = off;
+  const uint32_t xs_bytes = (uint32_t)max_k * 2;
+  L.xsum = L.xs + xs_bytes;
+  const uint32_t xsum_bytes = ss_align((uint32_t)(max_k / 128) * 8, 16);
+  L.part = L.xsum + xsum_bytes;
+  uint32_t work_bytes = xs_bytes + xsum_bytes + (uint32_t)SS_PART_SLOTS * SS_PART_BYTES;
+  const uint32_t attention_bytes = has_attention ? (uint32_t)(4 * head_dim + SS_WARPS * (head_dim + 2)) * 4 : 0;
+  if (attention_bytes > work_bytes) work_bytes = attention_bytes;
+  off += ss_align(work_bytes, 16);
+  L.red = off; off += 64 * 4;
+  L.keys_per_warp = has_attention ? (capacity + SS_WARPS - 1) / SS_WARPS : 0;
+  L.kv = off; off += has_attention ? (uint32_t)SS_WARPS * 2 * L.keys_per_warp * head_dim * 2 : 0;
+  L.total = off;
+  return L;
+}
+
+// ---------------------------------------------------------------------------
+// small device helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t ss_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void ss_st_stamped(void* ptr, uint32_t data, uint32_t stamp) {
+  const unsigned long long word = (unsigned long long)data | ((unsigned long long)stamp << 32);
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(ptr), "l"(word) : "memory");
+}
+__device__ __forceinline__ uint2 ss_ld_stamped(const void* ptr) {
+  unsigned long long word;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(word) : "l"(ptr) : "memory");
+  return make_uint2((uint32_t)word, (uint32_t)(word >> 32));
+}
+// two consecutive stamped words; each carries its own stamp, so the pair needs no atomicity
+__device__ __forceinline__ uint4 ss_ld_stamped_pair(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ss_ld_status(const int* status) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(status) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void ss_mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void ss_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool ss_mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+// Bounded wait for a phase of an mbarrier; false if it never completed.
+__device__ __forceinline__ bool ss_mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int spins = 0; spins < SS_POLL_LIMIT / 8; ++spins)  // a try_wait may itself block for a while
+    if (ss_mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// global -> this CTA's shared memory; both addresses 16-byte aligned, bytes a multiple of 16
+__device__ __forceinline__ void ss_bulk_load(uint32_t smem_dst, const void* gmem_src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void ss_fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory accesses by 32-bit shared address. They are ordinary (not volatile) loads: the
+// compiler may schedule them freely between the barriers and fences that carry "memory".
+__device__ __forceinline__ uint4 ss_lds128(uint32_t address) {
+  uint4 v;
+  asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ss_lds32(uint32_t address) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(address) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ss_ldsf(uint32_t address) { return __uint_as_float(ss_lds32(address)); }
+__device__ __forceinline__ float2 ss_lds64f(uint32_t address) {
+  float2 v;
+  asm("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(address) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ss_lds128f(uint32_t address) {
+  float4 v;
+  asm("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(address) : "memory");
+  return v;
+}
+__device__ __forceinline__ void ss_sts32(uint32_t address, uint32_t value) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(address), "r"(value) : "memory");
+}
+__device__ __forceinline__ void ss_stsf(uint32_t address, float value) { ss_sts32(address, __float_as_uint(value)); }
+
+__device__ __forceinline__ void ss_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ unsigned long long ss_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// ---------------------------------------------------------------------------
+// kernel state
+// ---------------------------------------------------------------------------
+struct SSParams {
+  aoto_stream_step_args a;
+  SSLayout L;
+};
+
+// A warp's view of its stream. Uniform over the lanes of the warp.
+struct WarpStream {
+  unsigned long long issue_offset;  // byte offset in the stream of the next piece to request
+  uint32_t ring;                    // shared address of the warp's first slot
+  uint32_t bars;                    // shared address of the warp's first mbarrier
+  uint32_t next_stage;              // stage of the next piece to multiply
+  uint32_t slot, parity;            // where that piece is (or will be)
+  uint32_t issue_slot;              // slot the next request goes to
+  int in_flight;                    // pieces requested and not yet multiplied
+};
+
+__device__ __forceinline__ void ss_trace(const SSParams& p, int stage, int which) {
+  if (p.a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.a.trace[stage * 8 + which] = ss_timer_ns();
+}
+
+__device__ __forceinline__ void ss_give_up(const SSParams& p, int stage) {
+  if (threadIdx.x == 0) atomicCAS(p.a.status, 0, stage + 1);
+}
+
+// Request one piece of `bytes` into the warp's next slot (lane 0 only issues).
+__device__ __forceinline__ void ss_request(const SSParams& p, WarpStream& ws, uint32_t bytes, int lane) {
+  if (lane == 0) {
+    const uint32_t bar = ws.bars + ws.issue_slot * 8;
+    ss_fence_async_proxy();  // this warp's earlier reads of the slot come before the copy
+    ss_mbar_expect_tx(bar, bytes);
+    ss_bulk_load(ws.ring + ws.issue_slot * SS_SLOT_BYTES,
+                 reinterpret_cast<const unsigned char*>(p.a.stream) + ws.issue_offset, bytes, bar);
+  }
+  ws.issue_offset += bytes;
+  ws.issue_slot = ws.issue_slot + 1 == (uint32_t)p.a.ring_depth ? 0u : ws.issue_slot + 1;
+  ws.in_flight += 1;
+}
+
+// Leave nothing in flight into this warp's ring (on the way out after a failure).
+__device__ __forceinline__ void ss_drain(const SSParams& p, WarpStream& ws) {
+  while (ws.in_flight > 0) {
+    ss_mbar_wait(ws.bars + ws.slot * 8, ws.parity);
+    ws.slot += 1;
+    if (ws.slot == (uint32_t)p.a.ring_depth) { ws.slot = 0; ws.parity ^= 1u; }
+    ws.in_flight -= 1;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// one 16 x 128 block from shared memory
+// ---------------------------------------------------------------------------
+// `block` is the shared address of the block, `xb` of this lane's B fragments of the block's
+// columns (the staged row in fragment order), `sums` of the block's two 136*sum(x) values.
+// Returns the contributions to rows g (lo) and g + 8 (hi), identical on the four lanes of a quad.
+#define SS_NIB(word, shift) ((((word) >> (shift)) & 0x000F000Fu) ^ 0x43084308u)
+
+__device__ __forceinline__ void ss_block(uint32_t block, uint32_t xb, uint32_t sums, int lane, float& lo, float& hi) {
+  const int g = lane >> 2;
+  const uint4 wl = ss_lds128(block + (uint32_t)lane * 16);
+  const uint4 wh = ss_lds128(block + 512 + (uint32_t)lane * 16);
+  const uint32_t slo = ss_lds32(block + 1024 + (uint32_t)g * 4);
+  const uint32_t shi = ss_lds32(block + 1024 + 32 + (uint32_t)g * 4);
+  const float2 off = ss_lds64f(sums);
+  float ca[4] = {-off.x, -off.x, -off.x, -off.x};
+  float cb[4] = {-off.y, -off.y, -off.y, -off.y};
+  {
+    const uint4 b = ss_lds128(xb);
+    ss_mma(ca, SS_NIB(wl.x, 0), SS_NIB(wh.x, 0), SS_NIB(wl.x, 4), SS_NIB(wh.x, 4), b.x, b.y);
+    ss_mma(ca, SS_NIB(wl.x, 8), SS_NIB(wh.x, 8), SS_NIB(wl.x, 12), SS_NIB(wh.x, 12), b.z, b.w);
+  }
+  {
+    const uint4 b = ss_lds128(xb + 64);
+    ss_mma(ca, SS_NIB(wl.y, 0), SS_NIB(wh.y, 0), SS_NIB(wl.y, 4), SS_NIB(wh.y, 4), b.x, b.y);
+    ss_mma(ca, SS_NIB(wl.y, 8), SS_NIB(wh.y, 8), SS_NIB(wl.y, 12), SS_NIB(wh.y, 12), b.z, b.w);
+  }
+  {
+    const uint4 b = ss_lds128(xb + 128);
+    ss_mma(cb, SS_NIB(wl.z, 0), SS_NIB(wh.z, 0), SS_NIB(wl.z, 4), SS_NIB(wh.z, 4), b.x, b.y);
+    ss_mma(cb, SS_NIB(wl.z, 8), SS_NIB(wh.z, 8), SS_NIB(wl.z, 12), SS_NIB(wh.z, 12), b.z, b.w);
+  }
+  {
+    const uint4 b = ss_lds128(xb + 192);
+    ss_mma(cb, SS_NIB(wl.w, 0), SS_NIB(wh.w, 0), SS_NIB(wl.w, 4), SS_NIB(wh.w, 4), b.x, b.y);
+    ss_mma(cb, SS_NIB(wl.w, 8), SS_NIB(wh.w, 8), SS_NIB(wl.w, 12), SS_NIB(wh.w, 12), b.z, b.w);
+  }
+  lo = fmaf(bf16x2_lo(slo), ca[0], bf16x2_hi(slo) * cb[0]);
+  hi = fmaf(bf16x2_lo(shi), ca[2], bf16x2_hi(shi) * cb[2]);
+}
+
+// ---------------------------------------------------------------------------
+// GEMV stage
+// ---------------------------------------------------------------------------
+struct Best {
+  float value;
+  int index;
+};
+
+// Stage the input row in fragment order. Chunk c holds columns 8c..8c+7: k step (c & 15) >> 1 of
+// block c >> 4, slots 0-7 or 8-15 of that step. Lane t of a quad wants, per pair of steps q, the
+// 16 bytes {b0(2q), b1(2q), b0(2q+1), b1(2q+1)} where b0 = slots (2t, 2t+1), b1 = (2t+8, 2t+9).
+__device__ __forceinline__ void ss_store_chunk(uint32_t xs, int c, uint32_t p0, uint32_t p1, uint32_t p2, uint32_t p3) {
+  const uint32_t base = xs + (uint32_t)(c >> 4) * 256 + (uint32_t)((c & 15) >> 2) * 64 + (uint32_t)(c & 3) * 4;
+  ss_sts32(base, p0);
+  ss_sts32(base + 16, p1);
+  ss_sts32(base + 32, p2);
+  ss_sts32(base + 48, p3);
+}
+
+// Returns false when a wait ran out (every thread of the CTA gets the same answer).
+__device__ bool ss_gemv(const SSParams& p, const aoto_stream_stage& st, int stage_index, uint32_t entry,
+                        WarpStream& ws, Best& best, unsigned char* smem) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int K = st.K, N = st.N;
+  const uint32_t epoch = p.a.epoch;
+  const int tile0 = (int)(entry & 0xFFFFu);
+  const bool shares_tiles = (entry >> 31) != 0;
+  const uint32_t xs = ss_smem(smem + p.L.xs), xsum = ss_smem(smem + p.L.xsum), part = ss_smem(smem + p.L.part);
+  float* red = reinterpret_cast<float*>(smem + p.L.red);
+  ss_trace(p, stage_index, 0);
+
+  long long gather_row = 0;
+  if (st.flags & AOTO_STAGE_FLAG_X_GATHER || st.addend_mode == AOTO_STAGE_ADDEND_GATHER) {
+    gather_row = *reinterpret_cast<const volatile long long*>(p.a.x_index);
+    if (gather_row < 0) gather_row = 0;
+    if (gather_row >= p.a.x_rows) gather_row = p.a.x_rows - 1;
+  }
+
+  // ---- the input row: gather it, or poll its stamped words ----
+  const int chunks = K >> 3;
+  const uint4* wv = reinterpret_cast<const uint4*>(st.norm_weight);
+  uint4 raw[SS_MAX_CHUNKS], nw[SS_MAX_CHUNKS];
+#pragma unroll
+  for (int i = 0; i < SS_MAX_CHUNKS; ++i) {
+    const int c = tid + i * SS_THREADS;
+    nw[i] = make_uint4(0u, 0u, 0u, 0u);
+    raw[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (wv != nullptr && c < chunks) nw[i] = ldg_nc_u4(wv + c);  // does not depend on the row: requested first
+  }
+  if (st.flags & AOTO_STAGE_FLAG_X_GATHER) {
+    const uint4* row = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(st.x) + (size_t)gather_row * K);
+#pragma unroll
+    for (int i = 0; i < SS_MAX_CHUNKS; ++i) {
+      const int c = tid + i * SS_THREADS;
+      if (c < chunks) raw[i] = ldg_nc_u4(row + c);
+    }
+  } else {
+    const unsigned char* words = reinterpret_cast<const unsigned char*>(st.x);
+    bool have[SS_MAX_CHUNKS];
+#pragma unroll
+    for (int i = 0; i < SS_MAX_CHUNKS; ++i) have[i] = tid + i * SS_THREADS >= chunks;
+    int rounds = 0;
+    while (true) {
+      bool ready = true;
+      uint4 a[SS_MAX_CHUNKS], b[SS_MAX_CHUNKS];
+#pragma unroll
+      for (int i = 0; i < SS_MAX_CHUNKS; ++i) {
+        if (have[i]) continue;
+        const size_t at = (size_t)(tid + i * SS_THREADS) * 32;
+        a[i] = ss_ld_stamped_pair(words + at);
+        b[i] = ss_ld_stamped_pair(words + at + 16);
+      }
+#pragma unroll
+      for (int i = 0; i < SS_MAX_CHUNKS; ++i) {
+        if (have[i]) continue;
+        if (a[i].y == epoch && a[i].w == epoch && b[i].y == epoch && b[i].w == epoch) {
+          raw[i] = make_uint4(a[i].x, a[i].z, b[i].x, b[i].z);
+          have[i] = true;
+        } else {
+          ready = false;
+        }
+      }
+      if (__syncthreads_and(ready)) break;
+      ++rounds;
+      // a CTA that already gave up elsewhere ends every other wait early
+      const bool stop = rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0);
+      if (__syncthreads_or(stop)) {
+        ss_give_up(p, stage_index);
+        return false;
+      }
+    }
+  }
+  ss_trace(p, stage_index, 1);
+
+  // ---- norm statistic, normalisation, fragment order, group sums ----
+  float inv = 1.f;
+  if (wv != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < SS_MAX_CHUNKS; ++i) {
+      float f[8];
+      unpack8(raw[i], f);  // zero where the thread has no chunk
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+    }
+    ss = warp_sum(ss);
+    float* slot = red + (stage_index & 1) * 32;  // stages alternate: no barrier guards the slot against old readers
+    if (lane == 0) slot[warp] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < SS_WARPS; ++w) total += slot[w];
+    inv = rsqrtf(total / (float)K + st.rms_norm_eps);
+  }
+  const int per_thread = (chunks + SS_THREADS - 1) / SS_THREADS;
+#pragma unroll
+  for (int i = 0; i < SS_MAX_CHUNKS; ++i) {
+    if (i >= per_thread) break;  // uniform
+    const int c = tid + i * SS_THREADS;
+    float f[8];
+    unpack8(raw[i], f);
+    uint4 o = raw[i];
+    if (wv != nullptr) {
+      float w[8];
+      unpack8(nw[i], w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = round_bf16((f[j] * inv) * w[j]);
+      o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+      o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+    }
+    float chunk_sum = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
+    if (c < chunks) ss_store_chunk(xs, c, o.x, o.y, o.z, o.w);
+    // a group of 64 columns is eight consecutive chunks, i.e. eight consecutive lanes
+    chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 1);
+    chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 2);
+    chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 4);
+    if (c < chunks && (lane & 7) == 0) ss_stsf(xsum + (uint32_t)(c >> 3) * 4, 136.f * chunk_sum);
+  }
+  __syncthreads();
+  ss_trace(p, stage_index, 2);
+
+  // ---- this warp's pieces of the stage ----
+  const bool paired = st.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED;
+  const uint32_t xb = xs + (uint32_t)t * 16;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};  // [matrix][lo, hi]
+  int duty_tile = -1, duty_first = 0, duty_parts = 0;  // the shared tile this warp finishes after the barrier
+  uint2 duty_addend = make_uint2(0u, 0u);
+  bool alive = true;
+
+  // y of row n from the two totals: alpha, addend, paired SiLU
+  auto epilogue_value = [&](int n, float total0, float total1, uint2 stamped_addend) {
+    float y = st.alpha * total0;
+    if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN) {
+      y = fmaf(st.beta, ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + n), y);
+    } else if (st.addend_mode == AOTO_STAGE_ADDEND_GATHER) {
+      y = fmaf(st.beta, ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + (size_t)gather_row * N + n), y);
+    } else if (st.addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
+      y = fmaf(st.beta, (n & 1) ? bf16x2_hi(stamped_addend.x) : bf16x2_lo(stamped_addend.x), y);
+    }
+    if (paired) {
+      const float gate = round_bf16(y);
+      y = (st.alpha * total1) * (gate / (1.f + expf(-gate)));
+    }
+    return y;
+  };
+  // Stamped addend word of row n (an intermediate produced stages ago; the poll is a formality).
+  auto addend_word = [&](int n, bool& ok) {
+    uint2 w = make_uint2(0u, 0u);
+    if (st.addend_mode != AOTO_STAGE_ADDEND_STAMPED || n >= N) return w;
+    const unsigned char* at = reinterpret_cast<const unsigned char*>(st.addend) + (size_t)(n >> 1) * 8;
+    w = ss_ld_stamped(at);
+    for (int polls = 0; w.y != epoch; ++polls) {
+      if (polls > SS_POLL_LIMIT) { ok = false; break; }
+      w = ss_ld_stamped(at);
+    }
+    return w;
+  };
+  // Lanes 0-15 hold rows 0-15 of `tile`: round, store (stamped pairs or plain), track the maximum.
+  auto store_rows = [&](int tile, float y) {
+    const int n = tile * 16 + lane;
+    const uint32_t bits = float_to_bf16_bits(y);
+    const uint32_t neighbour = __shfl_down_sync(0xffffffffu, bits, 1);
+    if (lane < 16 && n < N) {
+      if (st.flags & AOTO_STAGE_FLAG_OUT_PLAIN) {
+        reinterpret_cast<bf16*>(st.out)[n] = __ushort_as_bfloat16((unsigned short)bits);
+      } else if ((lane & 1) == 0) {
+        ss_st_stamped(reinterpret_cast<unsigned char*>(st.out) + (size_t)(n >> 1) * 8, bits | (neighbour << 16), epoch);
+      }
+      if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
+        float v = __uint_as_float(bits << 16);
+        if (v != v) v = INFINITY;
+        if (v > best.value || (v == best.value && n < best.index)) { best.value = v; best.index = n; }
+      }
+    }
+  };
+
+  bool first_piece = true;
+  while (ws.next_stage == (uint32_t)stage_index) {
+    if (!ss_mbar_wait(ws.bars + ws.slot * 8, ws.parity)) { alive = false; break; }
+    const uint32_t slot = ws.ring + ws.slot * SS_SLOT_BYTES;
+    const uint4 h = ss_lds128(slot);
+    // header: {stage, next_stage} {tile, kb0} {nblocks, mat, flags, nparts} {part_slot, ahead_size16}
+    const int tile_local = (int)(h.y & 0xFFFFu), kb0 = (int)(h.y >> 16);
+    const int nblocks = (int)(h.z & 0xFFu), mat = (int)((h.z >> 8) & 0xFFu);
+    const uint32_t flags = (h.z >> 16) & 0xFFu;
+    const int nparts = (int)(h.z >> 24);
+    const int part_slot = (int)(h.w & 0xFFFFu);
+    const uint32_t ahead = (h.w >> 16) * 16u;
+    float lo_sum = 0.f, hi_sum = 0.f;
+#pragma unroll 1
+    for (int b = 0; b < nblocks; ++b) {
+      float lo, hi;
+      ss_block(slot + 16 + (uint32_t)b * SS_BLOCK_BYTES, xb + (uint32_t)(kb0 + b) * 256, xsum + (uint32_t)(kb0 + b) * 8,
+               lane, lo, hi);
+      lo_sum += lo;
+      hi_sum += hi;
+    }
+    if (mat == 0) { acc[0] += lo_sum; acc[1] += hi_sum; } else { acc[2] += lo_sum; acc[3] += hi_sum; }
+    __syncwarp();  // every lane is done with the slot before it is refilled
+    ws.next_stage = h.x >> 16;
+    ws.slot += 1;
+    if (ws.slot == (uint32_t)p.a.ring_depth) { ws.slot = 0; ws.parity ^= 1u; }
+    ws.in_flight -= 1;
+    if (ahead != 0) ss_request(p, ws, ahead, lane);
+    if (first_piece) { ss_trace(p, stage_index, 3); first_piece = false; }
+
+    if (flags & AOTO_PIECE_SEG_END) {
+      // the share's sums go to a partial slot: a shared one, or the warp's own for a whole tile
+      const bool whole = (flags & AOTO_PIECE_WHOLE) != 0;
+      const int my_slot = whole ? AOTO_STREAM_PART_SLOTS + warp : part_slot;
+      const uint32_t at = part + (uint32_t)my_slot * SS_PART_BYTES;
+      if (t == 0) {
+        ss_stsf(at + (uint32_t)g * 4, acc[0]);
+        ss_stsf(at + (uint32_t)(g + 8) * 4, acc[1]);
+        if (paired) {
+          ss_stsf(at + 64 + (uint32_t)g * 4, acc[2]);
+          ss_stsf(at + 64 + (uint32_t)(g + 8) * 4, acc[3]);
+        }
+      }
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      const int tile = tile0 + tile_local;
+      if (whole) {
+        __syncwarp();
+        bool ok = true;
+        const uint2 addend = lane < 16 ? addend_word(tile * 16 + lane, ok) : make_uint2(0u, 0u);
+        float y = 0.f;
+        if (lane < 16) {
+          const float total0 = ss_ldsf(at + (uint32_t)lane * 4);
+          const float total1 = paired ? ss_ldsf(at + 64 + (uint32_t)lane * 4) : 0.f;
+          if (tile * 16 + lane < N) y = epilogue_value(tile * 16 + lane, total0, total1, addend);
+        }
+        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+        store_rows(tile, y);
+        __syncwarp();  // the private slot is read before the next whole tile overwrites it
+      } else if (flags & AOTO_PIECE_FINISHER) {
+        duty_tile = tile;
+        duty_first = part_slot - (nparts - 1);
+        duty_parts = nparts;
+        bool ok = true;  // the addend is requested now, it is not on the critical path after the barrier
+        duty_addend = lane < 16 ? addend_word(tile * 16 + lane, ok) : make_uint2(0u, 0u);
+        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+      }
+    }
+  }
+  ss_trace(p, stage_index, 4);
+
+  // ---- tiles shared between warps: meet, then the finisher sums the shares in a fixed order ----
+  if (shares_tiles) {
+    if (__syncthreads_or(!alive)) {
+      ss_give_up(p, stage_index);
+      return false;
+    }
+    if (duty_tile >= 0) {
+      float y = 0.f;
+      if (lane < 16) {
+        float total0 = 0.f, total1 = 0.f;
+        for (int i = 0; i < duty_parts; ++i) {
+          const uint32_t at = part + (uint32_t)(duty_first + i) * SS_PART_BYTES + (uint32_t)lane * 4;
+          total0 += ss_ldsf(at);
+          if (paired) total1 += ss_ldsf(at + 64);
+        }
+        if (duty_tile * 16 + lane < N) y = epilogue_value(duty_tile * 16 + lane, total0, total1, duty_addend);
+      }
+      store_rows(duty_tile, y);
+    }
+  } else if (__syncthreads_or(!alive)) {  // also keeps the staged row alive until every warp has used it
+    ss_give_up(p, stage_index);
+    return false;
+  }
+  ss_trace(p, stage_index, 5);
+
+  if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
+    float* sv = red;
+    int* si = reinterpret_cast<int*>(red + 32);
+    float bv = best.value;
+    int bi = best.index;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    __syncthreads();  // the finishers' maxima are in; `red` is free of the norm statistic
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (tid == 0) {
+      for (int w = 1; w < SS_WARPS; ++w)
+        if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+      unsigned char* payload = reinterpret_cast<unsigned char*>(p.a.scratch);
+      ss_st_stamped(payload + (size_t)blockIdx.x * 16, __float_as_uint(bv), epoch);
+      ss_st_stamped(payload + (size_t)blockIdx.x * 16 + 8, (uint32_t)bi, epoch);
+    }
+  }
+  ss_trace(p, stage_index, 6);
+  ss_trace(p, stage_index, 7);
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// attention stage: one CTA per query head over the whole window
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float ss_rotate(const float* head, const bf16* cos_row, const bf16* sin_row, int d, int D) {
+  const int half = D >> 1;
+  const float v = head[d];
+  const float partner = d < half ? -head[d + half] : head[d - half];
+  return round_bf16(round_bf16(v * __bfloat162float(cos_row[d])) + round_bf16(partner * __bfloat162float(sin_row[d])));
+}
+
+// Key range [k0, k1) of the new window a warp attends, and how many of them come from the old cache.
+struct KeyRange {
+  int first, per, k0, k1, old_keys;
+};
+__device__ __forceinline__ KeyRange ss_key_range(const SSParams& p, int warp, int valid_length) {
+  const int C = p.a.capacity;
+  KeyRange r;
+  r.first = p.a.window ? max(0, C - valid_length) : 0;
+  r.per = (C - r.first + SS_WARPS - 1) / SS_WARPS;
+  r.k0 = min(C, r.first + warp * r.per);
+  r.k1 = min(C, r.k0 + r.per);
+  r.old_keys = max(0, min(r.k1, C - 1) - r.k0);  // slot C - 1 is this step's key
+  return r;
+}
+
+// Request this warp's share of a layer's window: new slot j is old slot j + 1.
+__device__ __forceinline__ void ss_request_window(const SSParams& p, const aoto_stream_stage& st, int warp, int lane,
+                                                  int valid_length, unsigned char* smem) {
+  const int head = blockIdx.x;
+  if (head >= p.a.query_heads) return;
+  const int D = p.a.head_dim, C = p.a.capacity, KVH = p.a.kv_heads;
+  const int kvh = head / (p.a.query_heads / KVH);
+  const KeyRange r = ss_key_range(p, warp, valid_length);
+  if (r.old_keys <= 0 || lane != 0) return;
+  const bf16* kin = reinterpret_cast<const bf16*>(st.addend) + (size_t)kvh * C * D;
+  const bf16* vin = reinterpret_cast<const bf16*>(st.addend) + ((size_t)KVH + kvh) * C * D;
+  const uint32_t bytes = (uint32_t)r.old_keys * D * 2;
+  const uint32_t bar = ss_smem(smem + p.L.kvbars) + (uint32_t)warp * 8;
+  const uint32_t kbuf = ss_smem(smem + p.L.kv) + (uint32_t)warp * 2 * p.L.keys_per_warp * D * 2;
+  const uint32_t vbuf = kbuf + (uint32_t)p.L.keys_per_warp * D * 2;
+  ss_fence_async_proxy();
+  ss_mbar_expect_tx(bar, 2 * bytes);
+  ss_bulk_load(kbuf, kin + (size_t)(r.k0 + 1) * D, bytes, bar);
+  ss_bulk_load(vbuf, vin + (size_t)(r.k0 + 1) * D, bytes, bar);
+}
+
+__device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int stage_index, int valid_length,
+                             long long position, uint32_t& kv_parity, bool& kv_pending, unsigned char* smem) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int D = p.a.head_dim, C = p.a.capacity, KVH = p.a.kv_heads, QH = p.a.query_heads;
+  const int G = QH / KVH;
+  const uint32_t epoch = p.a.epoch;
+  ss_trace(p, stage_index, 0);
+
+  // Moving the window (slot j of the next cache is slot j + 1 of this one) touches nothing the
+  // step computes with: the CTAs without a head do it, or every CTA when each one has a head.
+  const int helpers = (int)gridDim.x - QH;
+  auto move_window = [&](int me, int movers) {
+    const int chunks = D >> 3;
+    const long long total = (long long)2 * KVH * (C - 1) * chunks;
+    const uint4* src = reinterpret_cast<const uint4*>(st.addend);
+    uint4* dst = reinterpret_cast<uint4*>(const_cast<void*>(st.norm_weight));
+    for (long long i = (long long)me * SS_THREADS + tid; i < total; i += (long long)movers * SS_THREADS) {
+      const long long plane = i / ((long long)(C - 1) * chunks), rest = i - plane * (C - 1) * chunks;
+      dst[plane * C * chunks + rest] = ldg_nc_u4(src + plane * C * chunks + chunks + rest);
+    }
+  };
+  if ((int)blockIdx.x >= QH) {
+    move_window((int)blockIdx.x - QH, helpers);
+    ss_trace(p, stage_index, 1);
+    ss_trace(p, stage_index, 6);
+    ss_trace(p, stage_index, 7);
+    return true;
+  }
+
+  const int head = blockIdx.x, kvh = head / G, member = head - kvh * G;
+  const int pairs = D >> 1;
+  __syncthreads();  // the previous stage's last readers of the work region are done
+  float* rowv = reinterpret_cast<float*>(smem + p.L.work);  // raw q head, k, v of the step: 3 * D
+  float* qs = rowv + 3 * D;                                 // rotated, scaled query: D
+  float* merge = qs + D;                                    // per warp: m, l, then D sums
+  long long pos = position;
+  if (pos < 0) pos = 0;
+  if (pos >= p.a.table_rows) pos = p.a.table_rows - 1;
+  const bf16* cos_row = reinterpret_cast<const bf16*>(p.a.cos_table) + (size_t)pos * D;
+  const bf16* sin_row = reinterpret_cast<const bf16*>(p.a.sin_table) + (size_t)pos * D;
+  const KeyRange r = ss_key_range(p, warp, valid_length);
+  unsigned char* kbuf = smem + p.L.kv + (size_t)warp * 2 * p.L.keys_per_warp * D * 2;
+  unsigned char* vbuf = kbuf + (size_t)p.L.keys_per_warp * D * 2;
+
+  // this head's query and its kv head's key and value of the step: poll the stamped projection row
+  {
+    const unsigned char* row_words = reinterpret_cast<const unsigned char*>(st.x);
+    const int total_words = 3 * pairs;
+    int element = 0;
+    if (tid < pairs) element = p.a.query_start + head * D + 2 * tid;
+    else if (tid < 2 * pairs) element = p.a.key_start + kvh * D + 2 * (tid - pairs);
+    else element = p.a.value_start + kvh * D + 2 * (tid - 2 * pairs);
+    bool pending = tid < total_words;
+    int rounds = 0;
+    while (true) {
+      bool ready = true;
+      if (pending) {
+        const uint2 v = ss_ld_stamped(row_words + (size_t)(element >> 1) * 8);
+        if (v.y == epoch) {
+          rowv[2 * tid] = bf16x2_lo(v.x);
+          rowv[2 * tid + 1] = bf16x2_hi(v.x);
+          pending = false;
+        } else {
+          ready = false;
+        }
+      }
+      if (__syncthreads_and(ready)) break;
+      ++rounds;
+      const bool stop = rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0);
+      if (__syncthreads_or(stop)) {
+        ss_give_up(p, stage_index);
+        return false;
+      }
+    }
+  }
+  ss_trace(p, stage_index, 1);
+
+  // rotate; this step's key and value join the window of the warp that owns the last slot
+  {
+    const int owner = r.per > 0 ? (C - 1 - r.first) / r.per : 0;
+    const KeyRange ro = ss_key_range(p, owner, valid_length);
+    unsigned char* okbuf = smem + p.L.kv + (size_t)owner * 2 * p.L.keys_per_warp * D * 2;
+    unsigned char* ovbuf = okbuf + (size_t)p.L.keys_per_warp * D * 2;
+    const int at = C - 1 - ro.k0;
+    bf16* kout = reinterpret_cast<bf16*>(const_cast<void*>(st.norm_weight)) + ((size_t)kvh * C + (C - 1)) * D;
+    bf16* vout = reinterpret_cast<bf16*>(const_cast<void*>(st.norm_weight)) + (((size_t)KVH + kvh) * C + (C - 1)) * D;
+    for (int d = tid; d < D; d += SS_THREADS) {
+      qs[d] = ss_rotate(rowv, cos_row, sin_row, d, D) * p.a.scale;
+      const bf16 key = __float2bfloat16_rn(ss_rotate(rowv + D, cos_row, sin_row, d, D));
+      const bf16 value = __float2bfloat16_rn(rowv[2 * D + d]);
+      reinterpret_cast<bf16*>(okbuf)[(size_t)at * D + d] = key;
+      reinterpret_cast<bf16*>(ovbuf)[(size_t)at * D + d] = value;
+      if (member == 0) { kout[d] = key; vout[d] = value; }
+    }
+  }
+  __syncthreads();
+
+  // every warp attends its keys: two lanes per key for the scores, the lanes split the head
+  // dimension for the weighted sum of values
+  bool alive = true;
+  if (kv_pending && r.old_keys > 0) {
+    alive = ss_mbar_wait(ss_smem(smem + p.L.kvbars) + (uint32_t)warp * 8, kv_parity);
+  }
+  {
+    const int key = lane >> 1, half = lane & 1;
+    const int nkeys = r.k1 - r.k0;
+    const int half_chunks = D >> 4;  // 16-byte chunks of half a row
+    float s = -INFINITY;
+    bool attend = false;
+    if (alive && key < nkeys) {
+      const int slot = r.k0 + key;
+      attend = p.a.window ? slot >= C - valid_length : p.a.mask[slot] != 0;
+    }
+    if (attend) {
+      const uint32_t krow = ss_smem(kbuf) + (uint32_t)key * D * 2 + (uint32_t)half * D;
+      const uint32_t qrow = ss_smem(qs) + (uint32_t)half * (D >> 1) * 4;
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+      for (int i = 0; i < half_chunks; ++i) {
+        const int ci = (i + key) & (half_chunks - 1);  // rows are 2*D bytes apart: rotate the chunk order by key
+        const uint4 kk = ss_lds128(krow + (uint32_t)ci * 16);
+        const float4 qa = ss_lds128f(qrow + (uint32_t)ci * 32), qb = ss_lds128f(qrow + (uint32_t)ci * 32 + 16);
+        d0 = fmaf(bf16x2_lo(kk.x), qa.x, d0); d1 = fmaf(bf16x2_hi(kk.x), qa.y, d1);
+        d2 = fmaf(bf16x2_lo(kk.y), qa.z, d2); d3 = fmaf(bf16x2_hi(kk.y), qa.w, d3);
+        d0 = fmaf(bf16x2_lo(kk.z), qb.x, d0); d1 = fmaf(bf16x2_hi(kk.z), qb.y, d1);
+        d2 = fmaf(bf16x2_lo(kk.w), qb.z, d2); d3 = fmaf(bf16x2_hi(kk.w), qb.w, d3);
+      }
+      s = (d0 + d1) + (d2 + d3);
+    }
+    const float other = __shfl_xor_sync(0xffffffffu, s, 1);
+    s = attend ? s + other : -INFINITY;
+    const float m = warp_max(s);
+    const float m_safe = m == -INFINITY ? 0.f : m;
+    const float e = s == -INFINITY ? 0.f : expf(s - m_safe);
+    const float l = warp_sum(half == 0 ? e : 0.f);
+    // weighted values: lane holds D / 32 consecutive dimensions
+    const int dims = D >> 5;  // 2 or 4
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    const uint32_t vrow = ss_smem(vbuf) + (uint32_t)lane * dims * 2;
+    for (int j = 0; j < nkeys; ++j) {
+      const float w = __shfl_sync(0xffffffffu, e, 2 * j);
+      if (w != 0.f) {  // uniform over the warp
+        if (dims == 2) {
+          const uint32_t v = ss_lds32(vrow + (uint32_t)j * D * 2);
+          a0 = fmaf(w, bf16x2_lo(v), a0);
+          a1 = fmaf(w, bf16x2_hi(v), a1);
+        } else {
+          const uint32_t v0 = ss_lds32(vrow + (uint32_t)j * D * 2), v1 = ss_lds32(vrow + (uint32_t)j * D * 2 + 4);
+          a0 = fmaf(w, bf16x2_lo(v0), a0); a1 = fmaf(w, bf16x2_hi(v0), a1);
+          a2 = fmaf(w, bf16x2_lo(v1), a2); a3 = fmaf(w, bf16x2_hi(v1), a3);
+        }
+      }
+    }
+    float* mine = merge + warp * (D + 2);
+    if (lane == 0) { mine[0] = m; mine[1] = l; }
+    mine[2 + lane * dims] = a0;
+    mine[3 + lane * dims] = a1;
+    if (dims == 4) { mine[4 + lane * dims] = a2; mine[5 + lane * dims] = a3; }
+  }
+  if (__syncthreads_or(!alive)) {
+    ss_give_up(p, stage_index);
+    return false;
+  }
+  if (kv_pending) { kv_parity ^= 1u; kv_pending = false; }
+
+  // the next layer's window can start travelling now: every warp is done with its buffers
+  if (st.next_attention >= 0) {
+    const aoto_stream_stage* all = reinterpret_cast<const aoto_stream_stage*>(smem + p.L.stages);
+    ss_request_window(p, all[st.next_attention], warp, lane, valid_length, smem);
+    kv_pending = true;
+  }
+
+  // merge the warps' results in a fixed order
+  if (tid < D) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < SS_WARPS; ++w) m = fmaxf(m, merge[w * (D + 2)]);
+    float num = 0.f, den = 0.f;
+    if (m != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < SS_WARPS; ++w) {
+        const float wm = merge[w * (D + 2)];
+        const float scale = wm == -INFINITY ? 0.f : expf(wm - m);
+        num = fmaf(scale, merge[w * (D + 2) + 2 + tid], num);
+        den = fmaf(scale, merge[w * (D + 2) + 1], den);
+      }
+    }
+    const float out = den > 0.f ? num / den : 0.f;
+    const uint32_t bits = float_to_bf16_bits(out);
+    const uint32_t neighbour = __shfl_down_sync(0xffffffffu, bits, 1);
+    if ((tid & 1) == 0)
+      ss_st_stamped(reinterpret_cast<unsigned char*>(st.out) + ((size_t)head * pairs + (tid >> 1)) * 8,
+                    bits | (neighbour << 16), epoch);
+  }
+  if (helpers <= 0) move_window(head, QH);
+  __syncthreads();  // the work region is free for the next stage
+  ss_trace(p, stage_index, 6);
+  ss_trace(p, stage_index, 7);
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// pick stage: CTA 0 polls the per-CTA maxima the ARGMAX stage left
+// ---------------------------------------------------------------------------
+__device__ void ss_pick(const SSParams& p, int stage_index) {
+  ss_trace(p, stage_index, 0);
+  if (blockIdx.x != 0 || threadIdx.x >= 32) return;
+  const unsigned char* payload = reinterpret_cast<const unsigned char*>(p.a.scratch);
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  int polls = 0;
+  bool failed = false;
+  for (int c = threadIdx.x; c < (int)gridDim.x && !failed; c += 32) {
+    uint2 a = ss_ld_stamped(payload + (size_t)c * 16), b = ss_ld_stamped(payload + (size_t)c * 16 + 8);
+    while (a.y != p.a.epoch || b.y != p.a.epoch) {
+      if (++polls > SS_POLL_LIMIT) { failed = true; break; }
+      a = ss_ld_stamped(payload + (size_t)c * 16);
+      b = ss_ld_stamped(payload + (size_t)c * 16 + 8);
+    }
+    const float v = __uint_as_float(a.x);
+    const int i = (int)b.x;
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+  failed = __any_sync(0xffffffffu, failed);
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  ss_trace(p, stage_index, 1);
+  if (threadIdx.x == 0 && !failed) {
+    p.a.token[0] = (long long)bi;
+    if (p.a.counters != nullptr) {
+      const int step = p.a.counters[1];
+      if (p.a.generated != nullptr && step < p.a.generated_capacity) p.a.generated[step] = (long long)bi;
+      p.a.counters[0] += 1;
+      p.a.counters[1] = step + 1;
+    }
+  }
+  if (threadIdx.x == 0 && failed) atomicCAS(p.a.status, 0, stage_index + 1);
+  ss_trace(p, stage_index, 6);
+  ss_trace(p, stage_index, 7);
+}
+
+__global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid_constant__ SSParams p) {
+  extern __shared__ uint4 ss_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(ss_raw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int depth = p.a.ring_depth;
+
+  // stage descriptors and this CTA's column of the table live in shared memory for the whole step
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(p.a.stages);
+    uint4* dst = reinterpret_cast<uint4*>(smem + p.L.stages);
+    const int words = p.a.stage_count * (int)(sizeof(aoto_stream_stage) / 16);
+    for (int i = tid; i < words; i += SS_THREADS) dst[i] = ldg_nc_u4(src + i);
+    uint32_t* table = reinterpret_cast<uint32_t*>(smem + p.L.table);
+    for (int s = tid; s < p.a.stage_count; s += SS_THREADS)
+      table[s] = ldg_nc_u32(p.a.cta_table + (size_t)s * gridDim.x + blockIdx.x);
+  }
+  if (tid == 0) {
+    for (int i = 0; i < SS_WARPS * AOTO_STREAM_MAX_RING; ++i) ss_mbar_init(ss_smem(smem + p.L.bars) + i * 8, 1);
+    for (int i = 0; i < SS_WARPS; ++i) ss_mbar_init(ss_smem(smem + p.L.kvbars) + i * 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  // the step's position and window
+  int valid_length = 0;
+  long long position = 0;
+  if (p.a.window) {
+    valid_length = *reinterpret_cast<const volatile int*>(p.a.counters);
+    position = valid_length - 1;
+  } else if (p.a.position != nullptr) {
+    position = *reinterpret_cast<const volatile long long*>(p.a.position);
+  }
+
+  // every warp starts its stream: `depth` pieces in flight before anything is awaited
+  WarpStream ws;
+  {
+    const uint4 start = ldg_nc_u4(reinterpret_cast<const uint4*>(p.a.starts) + (size_t)blockIdx.x * SS_WARPS + warp);
+    ws.issue_offset = (unsigned long long)start.x * 16ull;
+    ws.ring = ss_smem(smem + p.L.ring) + (uint32_t)warp * depth * SS_SLOT_BYTES;
+    ws.bars = ss_smem(smem + p.L.bars) + (uint32_t)warp * AOTO_STREAM_MAX_RING * 8;
+    ws.next_stage = start.z >> 16;
+    ws.slot = 0; ws.parity = 0; ws.issue_slot = 0; ws.in_flight = 0;
+    const uint32_t sizes[3] = {(start.y & 0xFFFFu) * 16u, (start.y >> 16) * 16u, (start.z & 0xFFFFu) * 16u};
+#pragma unroll
+    for (int i = 0; i < AOTO_STREAM_MAX_RING; ++i)
+      if (i < depth && sizes[i] != 0) ss_request(p, ws, sizes[i], lane);
+  }
+  uint32_t kv_parity = 0;
+  bool kv_pending = false;
+  const aoto_stream_stage* stages = reinterpret_cast<const aoto_stream_stage*>(smem + p.L.stages);
+  if (p.a.first_attention >= 0) {
+    ss_request_window(p, stages[p.a.first_attention], warp, lane, valid_length, smem);
+    kv_pending = true;
+  }
+
+  Best best;
+  best.value = -INFINITY;
+  best.index = 0x7fffffff;
+  const uint32_t* table = reinterpret_cast<const uint32_t*>(smem + p.L.table);
+  bool alive = true;
+  for (int s = 0; s < p.a.stage_count && alive; ++s) {
+    const aoto_stream_stage& st = stages[s];
+    if (st.kind == AOTO_STAGE_GEMV) {
+      const uint32_t entry = table[s];
+      if (((entry >> 16) & 0x7FFFu) != 0) {
+        alive = ss_gemv(p, st, s, entry, ws, best, smem);
+      } else if ((st.flags & AOTO_STAGE_FLAG_ARGMAX) && tid == 0) {
+        // a CTA without rows of the last projection still answers the pick stage's poll
+        unsigned char* payload = reinterpret_cast<unsigned char*>(p.a.scratch);
+        ss_st_stamped(payload + (size_t)blockIdx.x * 16, __float_as_uint(-INFINITY), p.a.epoch);
+        ss_st_stamped(payload + (size_t)blockIdx.x * 16 + 8, 0x7fffffffu, p.a.epoch);
+      }
+    } else if (st.kind == AOTO_STAGE_ATTENTION) {
+      alive = ss_attention(p, st, s, valid_length, position, kv_parity, kv_pending, smem);
+    } else if (st.kind == AOTO_STAGE_PICK) {
+      ss_pick(p, s);
+    }
+  }
+  if (!alive) {
+    // a wait ran out: nothing may still be travelling into this CTA's shared memory when it leaves
+    ss_drain(p, ws);
+    if (kv_pending) {
+      const KeyRange r = ss_key_range(p, warp, valid_length);
+      if ((int)blockIdx.x < p.a.query_heads && r.old_keys > 0)
+        ss_mbar_wait(ss_smem(smem + p.L.kvbars) + (uint32_t)warp * 8, kv_parity);
+    }
+  }
+}
+
+static int ss_check(const aoto_stream_step_args& a, SSLayout* layout) {
+  if (a.stage_count <= 0 || a.stage_count >= (int)AOTO_STREAM_NO_STAGE || a.ctas <= 0 || a.ctas > 1024) return 0;
+  if (a.ring_depth < 2 || a.ring_depth > AOTO_STREAM_MAX_RING) return 0;
+  if (a.max_k <= 0 || a.max_k > SS_MAX_K || (a.max_k & 127)) return 0;
+  const bool has_attention = a.first_attention >= 0;
+  if (has_attention) {
+    if (a.head_dim != 64 && a.head_dim != 128) return 0;
+    if (a.kv_heads <= 0 || a.query_heads <= 0 || a.query_heads % a.kv_heads) return 0;
+    if (a.query_heads > a.ctas || a.capacity < 2) return 0;
+    if ((a.capacity + SS_WARPS - 1) / SS_WARPS > SS_MAX_WINDOW_KEYS) return 0;  // longer windows need the split form
+    if (3 * (a.head_dim >> 1) > SS_THREADS) return 0;
+    if ((a.query_start | a.key_start | a.value_start) & 1) return 0;
+    if (a.table_rows <= 0) return 0;
+  }
+  *layout = ss_layout(a.stage_count, a.max_k, a.ring_depth, a.capacity, a.head_dim, has_attention);
+  return 1;
+}
+
+}  // namespace aoto
+
+using namespace aoto;
+
+extern "C" int aoto_sm100_stream_stage_size(void) { return (int)sizeof(aoto_stream_stage); }
+
+extern "C" int64_t aoto_sm100_stream_step_scratch_bytes(int32_t ctas) { return ctas > 0 ? (int64_t)ctas * 16 : 0; }
+
+extern "C" int64_t aoto_sm100_stream_step_smem_bytes(const aoto_stream_step_args* a) {
+  SSLayout L;
+  if (!a || !ss_check(*a, &L)) return -1;
+  return (int64_t)L.total;
+}
+
+extern "C" int aoto_sm100_stream_step(const aoto_stream_step_args* a, void* stream_) {
+  if (!a || !a->stages || !a->cta_table || !a->starts || !a->stream || !a->status || !a->scratch || a->epoch == 0)
+    return AOTO_ERR_ARGUMENT;
+  if (!aligned_to(a->stream, 16) || !aligned_to(a->stages, 16) || !aligned_to(a->starts, 16)) return AOTO_ERR_ARGUMENT;
+  if (a->scratch_bytes < aoto_sm100_stream_step_scratch_bytes(a->ctas)) return AOTO_ERR_ARGUMENT;
+  SSParams params;
+  params.a = *a;
+  if (!ss_check(*a, &params.L)) return AOTO_ERR_UNSUPPORTED;
+  int device = 0, sms = 0, coop = 0, smem_limit = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return AOTO_ERR_LAUNCH;
+  }
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device);
+  cudaDeviceGetAttribute(&smem_limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+  if (!coop || (int64_t)params.L.total > (int64_t)smem_limit) return AOTO_ERR_UNSUPPORTED;
+  static PerDeviceOnce raised;
+  if (raise_dynamic_smem(stream_step_kernel, (size_t)smem_limit, raised) != AOTO_OK) return AOTO_ERR_LAUNCH;
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, stream_step_kernel, SS_THREADS, params.L.total) != cudaSuccess ||
+      per_sm < 1) {
+    (void)cudaGetLastError();
+    return AOTO_ERR_UNSUPPORTED;
+  }
+  if (a->ctas > sms * per_sm) return AOTO_ERR_UNSUPPORTED;  // every CTA must be resident: they wait on one another
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(a->ctas);
+  config.blockDim = dim3(SS_THREADS);
+  config.dynamicSmemBytes = params.L.total;
+  config.stream = (cudaStream_t)stream_;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeCooperative;
+  attribute[0].val.cooperative = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  if (cudaLaunchKernelEx(&config, stream_step_kernel, params) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return AOTO_ERR_LAUNCH;
+  }
+  return AOTO_OK;
+}

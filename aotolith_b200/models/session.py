@@ -26,6 +26,10 @@ from .. import ops
 from ..errors import DeviceError, PlanInputError
 
 
+#: set to route every session to the kernel that reads the weights in place (tests compare the two)
+STREAM_STEP_DISABLED = False
+
+
 class DecodeSession:
     """Static buffers plus either the persistent step kernel or two recorded graphs."""
 
@@ -53,13 +57,93 @@ class DecodeSession:
         self.graphs: list[torch.cuda.CUDAGraph] = []
         self.programs: list[torch.Tensor] = []
         self.mode = "graphs"
+        self.kernel_name = None
         with torch.cuda.device(device):
-            if self.plan.step_program is not None and self._bind_program():
-                self.mode = "kernel"
+            if self.plan.step_program is not None and self._bind_stream():
+                self.mode, self.kernel_name = "kernel", "stream_step_kernel"
+            elif self.plan.step_program is not None and self._bind_program():
+                self.mode, self.kernel_name = "kernel", "decode_step_kernel"
             else:
                 self._record()
 
-    # -- persistent kernel ---------------------------------------------------------
+    # -- persistent kernel, weights streamed ahead -------------------------------------
+    def _bind_stream(self) -> bool:
+        """Lay the packed weights out as per-warp streams and bind the streamed step kernel.
+
+        False if the kernel has no form for the program (the caller then tries the kernel
+        that reads the weights in place).
+        """
+
+        from .. import _native as N
+        from ..runtime import step_program
+        from ..runtime import stream_plan as sp
+
+        if STREAM_STEP_DISABLED:
+            return False
+        program = self.plan.step_program
+        graph = self.plan.graph
+        device = self.device
+        properties = torch.cuda.get_device_properties(device)
+        ctas = properties.multi_processor_count
+        depth = sp.choose_ring_depth(program, ctas, properties.shared_memory_per_block_optin)
+        if depth == 0:
+            return False
+        tensors = dict(zip(graph.inputs[4:], self.state))
+        tensors[program.token_input] = self.token
+        tensors[program.position_input] = self.position
+        tensors[program.mask_input] = self.mask
+        layout, stream, table, starts = sp.device_stream(program, tensors, device, ctas, depth)
+        self.arena = torch.zeros(program.arena_bytes, dtype=torch.uint8, device=device)
+        self.logits = torch.zeros((1, 1, program.vocab), dtype=torch.bfloat16, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        lib = N.load()
+        self.scratch = torch.zeros(max(int(lib.aoto_sm100_stream_step_scratch_bytes(ctas)), 1 << 12),
+                                   dtype=torch.uint8, device=device)
+        self.stage_count = len(program.stages) + 1
+        self._stream_keep = (stream, table, starts)
+        self._stream_args = []
+        self.programs = []
+        geo = sp.geometry(program)
+        for source in (0, 1):
+            def resolve(ref, _source=source):
+                if ref.space == "arena":
+                    return self.arena.data_ptr() + program.arena_offsets[ref.key] + ref.offset
+                if ref.space == "output":
+                    base = self.logits if ref.key == 0 else self.caches[1 - _source]
+                    return base.data_ptr() + ref.offset
+                if ref.key == program.cache_input:
+                    return self.caches[_source].data_ptr() + ref.offset
+                return tensors[ref.key].data_ptr() + ref.offset
+
+            stages = step_program.to_device(sp.stage_array(program, resolve), device)
+            self.programs.append(stages)
+            args = sp.base_args(program, ctas, depth)
+            args.stages = stages.data_ptr()
+            args.cta_table, args.starts = table.data_ptr(), starts.data_ptr()
+            args.stream, args.stream_bytes = stream.data_ptr(), stream.numel()
+            if geo is not None:
+                args.cos_table, args.sin_table = resolve(geo["cos_table"]), resolve(geo["sin_table"])
+                args.position, args.mask = resolve(geo["position"]), resolve(geo["mask"])
+            args.x_index = self.token.data_ptr()
+            args.x_rows = self._embedding_rows(program, graph)
+            args.token, args.generated = self.token.data_ptr(), self.generated.data_ptr()
+            args.counters, args.generated_capacity = self.counters.data_ptr(), self.generated.numel()
+            args.window = 1
+            args.status, args.scratch = self.status.data_ptr(), self.scratch.data_ptr()
+            args.scratch_bytes = self.scratch.numel()
+            self._stream_args.append(args)
+        self.epoch = 0
+        self._launch = None
+        return True
+
+    @staticmethod
+    def _embedding_rows(program, graph) -> int:
+        for spec in program.stages:
+            if "x_rows" in spec.ints:
+                return int(spec.ints["x_rows"])
+        return 0
+
+    # -- persistent kernel, weights read in place ----------------------------------------
     def _bind_program(self) -> bool:
         """Resolve the stage program against this session's buffers; False if it does not fit."""
 
@@ -165,14 +249,24 @@ class DecodeSession:
         )
         if self.mode == "kernel":
             for step in range(steps):
-                self.epoch = self.epoch % 0xFFFFFFFE + 1
-                self._launch(self.programs[step & 1], self.stage_count, self.epoch, self.status, self.scratch)
+                self.launch_step(step & 1)
             tokens = self.generated[:steps].clone()
             self._check_status()
             return tokens
         for step in range(steps):
             self.graphs[step & 1].replay()
         return self.generated[:steps].clone()
+
+    def launch_step(self, source: int, trace: torch.Tensor | None = None) -> None:
+        """One launch of the persistent kernel reading cache ``source`` and writing the other."""
+
+        self.epoch = self.epoch % 0xFFFFFFFE + 1
+        if self.kernel_name == "stream_step_kernel":
+            from ..runtime import stream_plan as sp
+
+            sp.launch(self._stream_args[source], self.epoch, trace)
+        else:
+            self._launch(self.programs[source], self.stage_count, self.epoch, self.status, self.scratch, trace=trace)
 
     def final_cache(self, steps: int) -> torch.Tensor:
         """The cache after the last ``run`` of ``steps`` steps (a copy)."""

@@ -463,7 +463,7 @@ def run_ours(args) -> None:
             "clocks": clocks,
         }
         step_roofline = {
-            "kernel": "decode_step_kernel (one launch = one decode step)" if session.mode == "kernel"
+            "kernel": f"{session.kernel_name} (one launch = one decode step)" if session.mode == "kernel"
             else "per-operation decode plan (CUDA graph of one step)",
             "bound": "hbm", "achieved": achieved_step, "peak": peak, "unit": "GB/s",
             "frac": achieved_step / peak,
@@ -498,9 +498,7 @@ def print_stage_trace(runtime, session, token, cache) -> None:
     session.caches[0].copy_(cache)
     session.counters.copy_(torch.tensor([PROMPT + 1, 0], dtype=torch.int32))
     for step in range(6):
-        session.epoch = session.epoch % 0xFFFFFFFE + 1
-        session._launch(session.programs[step & 1], session.stage_count, session.epoch, session.status,
-                        session.scratch, trace=trace if step == 5 else None)
+        session.launch_step(step & 1, trace=trace if step == 5 else None)
     torch.cuda.synchronize()
     table = trace.cpu().reshape(-1, 8).tolist()
     origin = table[0][0]

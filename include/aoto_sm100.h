@@ -512,6 +512,144 @@ int aoto_sm100_decode_step_stage_size(void); /* sizeof(aoto_step_stage), for bin
 /* Bytes of a stamped vector of `count` bf16 values (count even). */
 int64_t aoto_sm100_stamped_bytes(int64_t count);
 
+/* ------------------------------------------------------------------------- */
+/* A whole decode step, weights streamed ahead of the dependency chain        */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * aoto_sm100_stream_step runs the same chain of stages as aoto_sm100_decode_step (same
+ * stamped-word exchange between stages, same bounded polls, same replacement of
+ * runtime/plan.py:554-733 over the decode graph of models/decoder.py:565-615), but takes the
+ * weights from a STREAM the caller lays out once per model for the grid it will launch:
+ *
+ *  - the grid is one CTA of AOTO_STREAM_WARPS warps per SM; the caller decides, per stage, which
+ *    contiguous range of 16-row weight tiles every CTA owns (`cta_table`) and cuts the CTA's
+ *    blocks of the stage - (tile, matrix, 128-column block), tile-major - into one contiguous
+ *    share per warp;
+ *  - every warp has its own byte stream: the blocks of all its shares, stage after stage, in
+ *    the order it will multiply them, cut into pieces of at most AOTO_STREAM_PIECE_BLOCKS
+ *    blocks. A piece is a 16-byte header (aoto_stream_piece) followed by its blocks;
+ *  - a block is AOTO_STREAM_BLOCK_BYTES of the packed weight in the order the tensor-core
+ *    fragments want it (below), so one bulk copy brings a piece into the warp's ring in shared
+ *    memory and the warp multiplies it from there with conflict-free 128-bit loads.
+ *
+ * A warp keeps `ring_depth` pieces in flight at all times, ACROSS stage boundaries: the weights
+ * of a stage have normally been resident for several stages when its input row arrives, so a
+ * stage on the critical path costs one poll, the staging of the row and a few blocks per warp.
+ * Nothing but the warp itself touches its ring: no CTA-wide synchronisation manages it.
+ *
+ * Block layout (16 rows r0..r0+15 of one matrix, columns c0..c0+127, group size 64):
+ *   bytes [0,512)     lane L = 4g+t (g = 0..7, t = 0..3): four 32-bit words for row r0+g;
+ *   bytes [512,1024)  the same for row r0+g+8;
+ *   bytes [1024,1088) row r: bf16 scale of columns c0..c0+63, then of c0+64..c0+127.
+ *   Nibble n (bits 4n..4n+3) of word j holds the two's-complement code of column
+ *   c0 + 16*(2j + ((n & 3) >> 1)) + 2t + 8*(n & 1) + (n >> 2): the k-th m16n8k16 step of a
+ *   block (k = 0..7) covers columns c0+16k..c0+16k+15, so steps 0-3 belong to the first scale
+ *   group and steps 4-7 to the second. Rows past N are zero.
+ *
+ * Layer-wise attention (rope_kv_cache_append + mask + attention, one CTA per query head) takes
+ * the cache window the same way: every warp bulk-copies its share of the keys and values of
+ * the NEXT layer while the current one is still being computed.
+ */
+#define AOTO_STREAM_WARPS 16
+#define AOTO_STREAM_BLOCK_BYTES 1088
+#define AOTO_STREAM_PIECE_BLOCKS 3
+#define AOTO_STREAM_SLOT_BYTES (16 + AOTO_STREAM_PIECE_BLOCKS * AOTO_STREAM_BLOCK_BYTES)
+#define AOTO_STREAM_MAX_RING 3
+#define AOTO_STREAM_PART_SLOTS 32   /* partial sums of tiles shared between warps, per CTA and stage */
+#define AOTO_STREAM_NO_STAGE 0xFFFFu
+
+#define AOTO_PIECE_SEG_END 1  /* last piece of this warp's share of the tile                      */
+#define AOTO_PIECE_WHOLE 2    /* the share is the whole tile: the warp finishes it by itself      */
+#define AOTO_PIECE_FINISHER 4 /* the share holds the tile's last block: the warp sums the parts   */
+
+typedef struct aoto_stream_piece {
+  uint16_t stage;        /* stage this piece belongs to                                            */
+  uint16_t next_stage;   /* stage of the warp's next piece, AOTO_STREAM_NO_STAGE after the last    */
+  uint16_t tile;         /* tile, counted from the first tile the CTA owns in this stage           */
+  uint16_t kb0;          /* first 128-column block                                                 */
+  uint8_t nblocks;       /* 1..AOTO_STREAM_PIECE_BLOCKS                                            */
+  uint8_t mat;           /* 0, or 1 for the second matrix of the paired form                       */
+  uint8_t flags;         /* AOTO_PIECE_*                                                           */
+  uint8_t nparts;        /* FINISHER: shares the tile was cut into                                 */
+  uint16_t part_slot;    /* slot of this share's partial sums; a tile's slots are consecutive      */
+  uint16_t ahead_size16; /* size / 16 of the piece `ring_depth` pieces later in this stream, 0 = none */
+} aoto_stream_piece;
+
+typedef struct aoto_stream_warp_start {
+  uint32_t offset16;     /* where the warp's stream starts in `stream`, in units of 16 bytes       */
+  uint16_t size16[3];    /* sizes / 16 of its first pieces (0 = the stream has fewer)              */
+  uint16_t first_stage;  /* stage of its first piece, AOTO_STREAM_NO_STAGE for an empty stream     */
+  uint32_t reserved;
+} aoto_stream_warp_start;
+
+/* One entry per (stage, CTA): tile range of the CTA and whether it shares a tile between warps. */
+#define AOTO_STREAM_CTA_ENTRY(tile0, tiles, shared) \
+  ((uint32_t)(tile0) | ((uint32_t)(tiles) << 16) | ((uint32_t)((shared) ? 1u : 0u) << 31))
+
+typedef struct aoto_stream_stage {
+  const void* x;           /* GEMV: stamped [K] (or the table of AOTO_STAGE_FLAG_X_GATHER)
+                              ATTENTION: stamped packed q/k/v projection of the step              */
+  void* out;               /* GEMV: stamped [N] (plain bf16 with AOTO_STAGE_FLAG_OUT_PLAIN)
+                              ATTENTION: stamped [query_heads * head_dim]                          */
+  const void* addend;      /* GEMV: per addend_mode; ATTENTION: this layer's pair in the incoming cache */
+  const void* norm_weight; /* GEMV: [K] or NULL;     ATTENTION: this layer's pair in the next cache */
+  int32_t N, K;            /* GEMV                                                                 */
+  float alpha, beta, rms_norm_eps;
+  uint8_t kind;            /* AOTO_STAGE_GEMV / ATTENTION / PICK                                   */
+  uint8_t epilogue;        /* AOTO_EPILOGUE_NONE or AOTO_EPILOGUE_SILU_MUL_PAIRED                  */
+  uint8_t addend_mode;     /* AOTO_STAGE_ADDEND_*                                                  */
+  uint8_t flags;           /* AOTO_STAGE_FLAG_*                                                    */
+  int32_t next_attention;  /* ATTENTION: index of the next ATTENTION stage, -1 after the last      */
+  int32_t reserved;
+} aoto_stream_stage;
+
+typedef struct aoto_stream_step_args {
+  const aoto_stream_stage* stages;      /* device array [stage_count]                              */
+  const uint32_t* cta_table;            /* device [stage_count * ctas], AOTO_STREAM_CTA_ENTRY      */
+  const aoto_stream_warp_start* starts; /* device [ctas * AOTO_STREAM_WARPS]                       */
+  const void* stream;                   /* device, 16-byte aligned                                 */
+  int64_t stream_bytes;
+  int32_t stage_count;
+  int32_t ctas;                         /* the grid the stream was laid out for                    */
+  int32_t ring_depth;                   /* 2..AOTO_STREAM_MAX_RING, as the piece headers assume    */
+  int32_t max_k;                        /* largest K of a GEMV stage                               */
+  /* attention geometry, the same for every layer */
+  int32_t query_heads, kv_heads, capacity, head_dim;
+  int32_t query_start, key_start, value_start, table_rows;
+  float scale;
+  int32_t first_attention;              /* index of the first ATTENTION stage, -1 = none           */
+  const void* cos_table;                /* bf16 [table_rows, head_dim]                             */
+  const void* sin_table;
+  const int64_t* position;              /* [1], ignored with `window`                              */
+  const uint8_t* mask;                  /* bool [capacity], ignored with `window`                  */
+  /* the step's token: row index of the gathered input / addend                                    */
+  const int64_t* x_index;
+  int64_t x_rows;
+  /* greedy pick */
+  int64_t* token;
+  int64_t* generated;
+  int32_t* counters;                    /* int32[2]: valid_length of the step, tokens generated    */
+  int32_t generated_capacity;
+  int32_t window;                       /* 1: position and mask come from `counters`               */
+  uint32_t epoch;                       /* as for aoto_sm100_decode_step                           */
+  int32_t reserved;
+  int32_t* status;
+  void* scratch;                        /* per-CTA maxima of the ARGMAX stage: 16 bytes per CTA    */
+  int64_t scratch_bytes;
+  uint64_t* trace;                      /* optional, uint64[stage_count * 8], as for decode_step   */
+} aoto_stream_step_args;
+
+int aoto_sm100_stream_step(const aoto_stream_step_args* args, void* stream);
+/*
+ * Dynamic shared memory the kernel needs for this geometry, or -1 if it has no form for it
+ * (K not a multiple of 128 or above 16384, head_dim not 64/128 or a window that does not fit
+ * one CTA per query head). Pointers of `args` are ignored.
+ */
+int64_t aoto_sm100_stream_step_smem_bytes(const aoto_stream_step_args* args);
+int64_t aoto_sm100_stream_step_scratch_bytes(int32_t ctas);
+int aoto_sm100_stream_stage_size(void); /* sizeof(aoto_stream_stage), for binding checks */
+
 #ifdef __cplusplus
 }
 #endif

@@ -92,15 +92,20 @@ def _pointwise(op, args, out_dtype):
     raise NotImplementedError(f"oracle has no pointwise rule for {kind}")
 
 
-def evaluate(graph, op, env):
+def _dtype_of(name: str, unrounded: bool):
+    dtype = _TORCH[name]
+    return torch.float64 if unrounded and dtype.is_floating_point else dtype
+
+
+def evaluate(graph, op, env, unrounded: bool = False):
     args = [env[v] for v in op.inputs]
     kind = op.op
     out_type = graph.value(op.outputs[0]).type
-    out_dtype = _TORCH[out_type.dtype.value]
+    out_dtype = _dtype_of(out_type.dtype.value, unrounded)
     if kind == "fused_elementwise":
         local = dict(env)
         for item in op.attrs["body"]:
-            item_dtype = _TORCH[graph.value(item.outputs[0]).type.dtype.value]
+            item_dtype = _dtype_of(graph.value(item.outputs[0]).type.dtype.value, unrounded)
             local[item.outputs[0]] = _pointwise(item, [local[v] for v in item.inputs], item_dtype)
         return local[op.outputs[0]]
     if kind == "embedding":
@@ -145,14 +150,22 @@ def evaluate(graph, op, env):
     return _pointwise(op, args, out_dtype)
 
 
-def run_graph(graph, inputs):
-    """Execute ``graph`` on CPU tensors in operation order; returns the outputs as a tuple."""
+def run_graph(graph, inputs, unrounded: bool = False):
+    """Execute ``graph`` on CPU tensors in operation order; returns the outputs as a tuple.
+
+    ``unrounded`` evaluates the same operations on the same stored values (bf16 weights, scales
+    and tables widened exactly) in float64 with no intermediate rounding to the graph's dtypes.
+    It is not the reference's arithmetic: it is the yardstick that says how far a bf16 pipeline -
+    the oracle's or the GPU's - sits from the value both approximate.
+    """
 
     if len(inputs) != len(graph.inputs):
         raise ValueError(f"expected {len(graph.inputs)} inputs, received {len(inputs)}")
     env = {value: tensor.detach().cpu() for value, tensor in zip(graph.inputs, inputs)}
+    if unrounded:
+        env = {k: (t.double() if t.dtype.is_floating_point else t) for k, t in env.items()}
     for op in graph.ops:
-        result = evaluate(graph, op, env)
+        result = evaluate(graph, op, env, unrounded)
         if len(op.outputs) == 1:
             env[op.outputs[0]] = result
         else:
@@ -161,18 +174,19 @@ def run_graph(graph, inputs):
     return tuple(env[v] for v in graph.outputs)
 
 
-def run_module_plan(module_plan, *inputs):
+def run_module_plan(module_plan, *inputs, unrounded: bool = False):
     """Run a ``CompiledModulePlan``'s lowered graph on the CPU with its bound state."""
 
     state = [t.detach().cpu() for t in module_plan._state_values]
-    return run_graph(module_plan.plan.graph, [*(torch.as_tensor(i) for i in inputs), *state])
+    return run_graph(module_plan.plan.graph, [*(torch.as_tensor(i) for i in inputs), *state], unrounded)
 
 
 class OracleRuntime:
     """The greedy loop of ``models/decoder.py:811-1087`` over the oracle interpreter."""
 
-    def __init__(self, runtime) -> None:
+    def __init__(self, runtime, unrounded: bool = False) -> None:
         self.rt = runtime
+        self.unrounded = unrounded
 
     def prefill(self, ids, length=None):
         from aotolith_b200.models.decoder import prefill_mask
@@ -184,7 +198,7 @@ class OracleRuntime:
         padded = torch.cat((torch.zeros((1, pad), dtype=torch.int64), ids), dim=1)
         positions = torch.cat((torch.zeros((1, pad), dtype=torch.int64), torch.arange(length)[None, :]), dim=1)
         mask = torch.from_numpy(prefill_mask(length, rt.prompt_length))
-        logits, compact = run_module_plan(rt.prefill, padded, positions, mask)
+        logits, compact = run_module_plan(rt.prefill, padded, positions, mask, unrounded=self.unrounded)
         zeros = torch.zeros(compact.shape[:4] + (rt.cache_capacity - rt.prompt_length,) + compact.shape[5:], dtype=compact.dtype)
         return logits, torch.cat((zeros, compact), dim=4)
 
@@ -193,7 +207,7 @@ class OracleRuntime:
         mask = (torch.arange(rt.cache_capacity) >= rt.cache_capacity - valid_length).reshape(1, 1, 1, -1)
         return run_module_plan(
             rt.decode, torch.as_tensor(token, dtype=torch.int64).reshape(1, 1),
-            torch.tensor([[valid_length - 1]], dtype=torch.int64), mask, cache,
+            torch.tensor([[valid_length - 1]], dtype=torch.int64), mask, cache, unrounded=self.unrounded,
         )
 
     def greedy(self, ids, steps):
