@@ -166,7 +166,7 @@ class StreamStepArgs(Structure):
     """Mirror of ``aoto_stream_step_args``."""
 
     _fields_ = [
-        ("stages", c_void_p), ("cta_table", c_void_p), ("starts", c_void_p), ("stream", c_void_p),
+        ("stages", c_void_p), ("cta_table", c_void_p), ("duties", c_void_p), ("starts", c_void_p), ("stream", c_void_p),
         ("stream_bytes", c_int64),
         ("stage_count", c_int32), ("ctas", c_int32), ("ring_depth", c_int32), ("max_k", c_int32),
         ("query_heads", c_int32), ("kv_heads", c_int32), ("capacity", c_int32), ("head_dim", c_int32),

@@ -31,7 +31,7 @@ constexpr int SS_MAX_WINDOW_KEYS = 16;  // keys per warp in the one-CTA-per-head
 // shared-memory layout, computed identically on both sides
 // ---------------------------------------------------------------------------
 struct SSLayout {
-  uint32_t ring, bars, kvbars, stages, table, work, xs, xsum, part, red, kv, total;
+  uint32_t ring, bars, kvbars, stages, table, work, xs, xsum, part, red, rotary, kv, total;
   int keys_per_warp;
 };
 
@@ -55,10 +55,12 @@ __host__ __device__ inline SSLayout ss_layout(int stage_count, int max_k, int de
   const uint32_t xsum_bytes = ss_align((uint32_t)(max_k / 128) * 8, 16);
   L.part = L.xsum + xsum_bytes;
   uint32_t work_bytes = xs_bytes + xsum_bytes + (uint32_t)SS_PART_SLOTS * SS_PART_BYTES;
-  const uint32_t attention_bytes = has_attention ? (uint32_t)(4 * head_dim + SS_WARPS * (head_dim + 2)) * 4 : 0;
+  const uint32_t attention_bytes =
+      has_attention ? (uint32_t)(4 * head_dim + SS_WARPS * (head_dim + 2) + SS_WARPS * 16 + 4 * 16) * 4 : 0;
   if (attention_bytes > work_bytes) work_bytes = attention_bytes;
   off += ss_align(work_bytes, 16);
   L.red = off; off += 64 * 4;
+  L.rotary = off; off += has_attention ? (uint32_t)head_dim * 4 : 0;  // cos row, sin row of the step's position
   L.keys_per_warp = has_attention ? (capacity + SS_WARPS - 1) / SS_WARPS : 0;
   L.kv = off; off += has_attention ? (uint32_t)SS_WARPS * 2 * L.keys_per_warp * head_dim * 2 : 0;
   L.total = off;
@@ -153,9 +155,21 @@ __device__ __forceinline__ void ss_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The SM's own cycle counter: reading it costs a few cycles, so the marks do not stretch what
+// they measure (the global nanosecond timer takes hundreds of cycles per read).
+// Maximum of a float over the warp with one integer reduction: IEEE floats order like
+// sign-magnitude integers, so flipping the magnitude bits of negatives gives a monotonic key.
+__device__ __forceinline__ float ss_warp_max(float v) {
+  int key = __float_as_int(v);
+  key ^= (key >> 31) & 0x7fffffff;
+  key = __reduce_max_sync(0xffffffffu, key);
+  key ^= (key >> 31) & 0x7fffffff;
+  return __int_as_float(key);
+}
+
 __device__ __forceinline__ unsigned long long ss_timer_ns() {
   unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
   return t;
 }
 
@@ -189,8 +203,9 @@ __device__ __forceinline__ void ss_give_up(const SSParams& p, int stage) {
 // Request one piece of `bytes` into the warp's next slot (lane 0 only issues).
 __device__ __forceinline__ void ss_request(const SSParams& p, WarpStream& ws, uint32_t bytes, int lane) {
   if (lane == 0) {
+    // the slot was only READ through the generic proxy, and __syncwarp ordered those reads before
+    // this point: a write by the async proxy needs no proxy fence after reads
     const uint32_t bar = ws.bars + ws.issue_slot * 8;
-    ss_fence_async_proxy();  // this warp's earlier reads of the slot come before the copy
     ss_mbar_expect_tx(bar, bytes);
     ss_bulk_load(ws.ring + ws.issue_slot * SS_SLOT_BYTES,
                  reinterpret_cast<const unsigned char*>(p.a.stream) + ws.issue_offset, bytes, bar);
@@ -211,44 +226,54 @@ __device__ __forceinline__ void ss_drain(const SSParams& p, WarpStream& ws) {
 }
 
 // ---------------------------------------------------------------------------
-// one 16 x 128 block from shared memory
+// the blocks of a piece, from shared memory
 // ---------------------------------------------------------------------------
-// `block` is the shared address of the block, `xb` of this lane's B fragments of the block's
-// columns (the staged row in fragment order), `sums` of the block's two 136*sum(x) values.
-// Returns the contributions to rows g (lo) and g + 8 (hi), identical on the four lanes of a quad.
+// `block` is the shared address of the first block, `xb` of this lane's B fragments of the
+// blocks' columns (the staged row in fragment order: 256 bytes a block), `sums` of the blocks'
+// pairs of 136*sum(x) values. A block is two accumulator chains of four mma (one per scale
+// group); the NB blocks of a piece are issued interleaved, so up to six chains are in flight
+// and the latency of one mma is hidden by the others. Returns the contributions to rows g (lo)
+// and g + 8 (hi), identical on the four lanes of a quad.
 #define SS_NIB(word, shift) ((((word) >> (shift)) & 0x000F000Fu) ^ 0x43084308u)
 
-__device__ __forceinline__ void ss_block(uint32_t block, uint32_t xb, uint32_t sums, int lane, float& lo, float& hi) {
+template <int NB>
+__device__ __forceinline__ void ss_blocks(uint32_t block, uint32_t xb, uint32_t sums, int lane, float& lo, float& hi) {
   const int g = lane >> 2;
-  const uint4 wl = ss_lds128(block + (uint32_t)lane * 16);
-  const uint4 wh = ss_lds128(block + 512 + (uint32_t)lane * 16);
-  const uint32_t slo = ss_lds32(block + 1024 + (uint32_t)g * 4);
-  const uint32_t shi = ss_lds32(block + 1024 + 32 + (uint32_t)g * 4);
-  const float2 off = ss_lds64f(sums);
-  float ca[4] = {-off.x, -off.x, -off.x, -off.x};
-  float cb[4] = {-off.y, -off.y, -off.y, -off.y};
-  {
-    const uint4 b = ss_lds128(xb);
-    ss_mma(ca, SS_NIB(wl.x, 0), SS_NIB(wh.x, 0), SS_NIB(wl.x, 4), SS_NIB(wh.x, 4), b.x, b.y);
-    ss_mma(ca, SS_NIB(wl.x, 8), SS_NIB(wh.x, 8), SS_NIB(wl.x, 12), SS_NIB(wh.x, 12), b.z, b.w);
+  uint32_t wl[NB][4], wh[NB][4], slo[NB], shi[NB];
+  float ca[NB][4], cb[NB][4];
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    const uint32_t at = block + (uint32_t)b * SS_BLOCK_BYTES;
+    const uint4 l = ss_lds128(at + (uint32_t)lane * 16);
+    const uint4 h = ss_lds128(at + 512 + (uint32_t)lane * 16);
+    wl[b][0] = l.x; wl[b][1] = l.y; wl[b][2] = l.z; wl[b][3] = l.w;
+    wh[b][0] = h.x; wh[b][1] = h.y; wh[b][2] = h.z; wh[b][3] = h.w;
+    slo[b] = ss_lds32(at + 1024 + (uint32_t)g * 4);
+    shi[b] = ss_lds32(at + 1024 + 32 + (uint32_t)g * 4);
+    const float2 off = ss_lds64f(sums + (uint32_t)b * 8);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { ca[b][i] = -off.x; cb[b][i] = -off.y; }
   }
-  {
-    const uint4 b = ss_lds128(xb + 64);
-    ss_mma(ca, SS_NIB(wl.y, 0), SS_NIB(wh.y, 0), SS_NIB(wl.y, 4), SS_NIB(wh.y, 4), b.x, b.y);
-    ss_mma(ca, SS_NIB(wl.y, 8), SS_NIB(wh.y, 8), SS_NIB(wl.y, 12), SS_NIB(wh.y, 12), b.z, b.w);
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {  // words q (first scale group) and q + 2 (second) of every block
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+      const uint4 ba = ss_lds128(xb + (uint32_t)b * 256 + (uint32_t)q * 64);
+      const uint4 bb = ss_lds128(xb + (uint32_t)b * 256 + (uint32_t)(q + 2) * 64);
+      const uint32_t la = wl[b][q], ha = wh[b][q], lb = wl[b][q + 2], hb = wh[b][q + 2];
+      ss_mma(ca[b], SS_NIB(la, 0), SS_NIB(ha, 0), SS_NIB(la, 4), SS_NIB(ha, 4), ba.x, ba.y);
+      ss_mma(cb[b], SS_NIB(lb, 0), SS_NIB(hb, 0), SS_NIB(lb, 4), SS_NIB(hb, 4), bb.x, bb.y);
+      ss_mma(ca[b], SS_NIB(la, 8), SS_NIB(ha, 8), SS_NIB(la, 12), SS_NIB(ha, 12), ba.z, ba.w);
+      ss_mma(cb[b], SS_NIB(lb, 8), SS_NIB(hb, 8), SS_NIB(lb, 12), SS_NIB(hb, 12), bb.z, bb.w);
+    }
   }
-  {
-    const uint4 b = ss_lds128(xb + 128);
-    ss_mma(cb, SS_NIB(wl.z, 0), SS_NIB(wh.z, 0), SS_NIB(wl.z, 4), SS_NIB(wh.z, 4), b.x, b.y);
-    ss_mma(cb, SS_NIB(wl.z, 8), SS_NIB(wh.z, 8), SS_NIB(wl.z, 12), SS_NIB(wh.z, 12), b.z, b.w);
+  lo = 0.f;
+  hi = 0.f;
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    lo += fmaf(bf16x2_lo(slo[b]), ca[b][0], bf16x2_hi(slo[b]) * cb[b][0]);
+    hi += fmaf(bf16x2_lo(shi[b]), ca[b][2], bf16x2_hi(shi[b]) * cb[b][2]);
   }
-  {
-    const uint4 b = ss_lds128(xb + 192);
-    ss_mma(cb, SS_NIB(wl.w, 0), SS_NIB(wh.w, 0), SS_NIB(wl.w, 4), SS_NIB(wh.w, 4), b.x, b.y);
-    ss_mma(cb, SS_NIB(wl.w, 8), SS_NIB(wh.w, 8), SS_NIB(wl.w, 12), SS_NIB(wh.w, 12), b.z, b.w);
-  }
-  lo = fmaf(bf16x2_lo(slo), ca[0], bf16x2_hi(slo) * cb[0]);
-  hi = fmaf(bf16x2_lo(shi), ca[2], bf16x2_hi(shi) * cb[2]);
 }
 
 // ---------------------------------------------------------------------------
@@ -270,7 +295,19 @@ __device__ __forceinline__ void ss_store_chunk(uint32_t xs, int c, uint32_t p0, 
   ss_sts32(base + 48, p3);
 }
 
+// Where chunk c (columns 8c..8c+7) of the staged row lives: the address of its first pair; the
+// other three pairs follow at 16-byte steps (see ss_store_chunk).
+__device__ __forceinline__ uint32_t ss_chunk_address(uint32_t xs, int c) {
+  return xs + (uint32_t)(c >> 4) * 256 + (uint32_t)((c & 15) >> 2) * 64 + (uint32_t)(c & 3) * 4;
+}
+
 // Returns false when a wait ran out (every thread of the CTA gets the same answer).
+//
+// Only the work that must be done by every warp is done by every warp: the row is fetched,
+// normalised and staged by the warps that own chunks of it (four for K = 896), a tile shared
+// between warps is finished by the one warp whose duty it is, and a warp with nothing to do
+// in a phase waits at the barrier and leaves the issue slots to the others.
+template <bool TRACE>
 __device__ bool ss_gemv(const SSParams& p, const aoto_stream_stage& st, int stage_index, uint32_t entry,
                         WarpStream& ws, Best& best, unsigned char* smem) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -280,272 +317,261 @@ __device__ bool ss_gemv(const SSParams& p, const aoto_stream_stage& st, int stag
   const int tile0 = (int)(entry & 0xFFFFu);
   const bool shares_tiles = (entry >> 31) != 0;
   const uint32_t xs = ss_smem(smem + p.L.xs), xsum = ss_smem(smem + p.L.xsum), part = ss_smem(smem + p.L.part);
-  float* red = reinterpret_cast<float*>(smem + p.L.red);
-  ss_trace(p, stage_index, 0);
+  float* stat = reinterpret_cast<float*>(smem + p.L.red) + (stage_index & 1) * 32;  // stages alternate halves
+  if (TRACE) ss_trace(p, stage_index, 0);
 
   long long gather_row = 0;
-  if (st.flags & AOTO_STAGE_FLAG_X_GATHER || st.addend_mode == AOTO_STAGE_ADDEND_GATHER) {
+  if ((st.flags & AOTO_STAGE_FLAG_X_GATHER) || st.addend_mode == AOTO_STAGE_ADDEND_GATHER) {
     gather_row = *reinterpret_cast<const volatile long long*>(p.a.x_index);
     if (gather_row < 0) gather_row = 0;
     if (gather_row >= p.a.x_rows) gather_row = p.a.x_rows - 1;
   }
+  // which shared tile this warp finishes after the multiply (requested now, needed much later)
+  uint32_t duty = 0;
+  if (shares_tiles)
+    duty = ldg_nc_u32(p.a.duties + ((size_t)stage_index * gridDim.x + blockIdx.x) * SS_WARPS + warp);
 
-  // ---- the input row: gather it, or poll its stamped words ----
+  // ---- the input row ----
   const int chunks = K >> 3;
   const uint4* wv = reinterpret_cast<const uint4*>(st.norm_weight);
-  uint4 raw[SS_MAX_CHUNKS], nw[SS_MAX_CHUNKS];
-#pragma unroll
-  for (int i = 0; i < SS_MAX_CHUNKS; ++i) {
-    const int c = tid + i * SS_THREADS;
-    nw[i] = make_uint4(0u, 0u, 0u, 0u);
-    raw[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (wv != nullptr && c < chunks) nw[i] = ldg_nc_u4(wv + c);  // does not depend on the row: requested first
-  }
-  if (st.flags & AOTO_STAGE_FLAG_X_GATHER) {
-    const uint4* row = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(st.x) + (size_t)gather_row * K);
-#pragma unroll
-    for (int i = 0; i < SS_MAX_CHUNKS; ++i) {
-      const int c = tid + i * SS_THREADS;
-      if (c < chunks) raw[i] = ldg_nc_u4(row + c);
-    }
-  } else {
+  const bool has_norm = wv != nullptr;
+  const bool stager = warp * 32 < chunks;
+  const int per_thread = (chunks + SS_THREADS - 1) / SS_THREADS;
+  bool failed = false;
+  uint4 nw0 = make_uint4(0u, 0u, 0u, 0u);
+  if (stager) {
+    if (has_norm && tid < chunks) nw0 = ldg_nc_u4(wv + tid);  // does not depend on the row: requested first
     const unsigned char* words = reinterpret_cast<const unsigned char*>(st.x);
-    bool have[SS_MAX_CHUNKS];
-#pragma unroll
-    for (int i = 0; i < SS_MAX_CHUNKS; ++i) have[i] = tid + i * SS_THREADS >= chunks;
+    const uint4* gathered = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(st.x) + (size_t)gather_row * K);
+    float s0 = 0.f, s1 = 0.f;
     int rounds = 0;
-    while (true) {
-      bool ready = true;
-      uint4 a[SS_MAX_CHUNKS], b[SS_MAX_CHUNKS];
-#pragma unroll
-      for (int i = 0; i < SS_MAX_CHUNKS; ++i) {
-        if (have[i]) continue;
-        const size_t at = (size_t)(tid + i * SS_THREADS) * 32;
-        a[i] = ss_ld_stamped_pair(words + at);
-        b[i] = ss_ld_stamped_pair(words + at + 16);
-      }
-#pragma unroll
-      for (int i = 0; i < SS_MAX_CHUNKS; ++i) {
-        if (have[i]) continue;
-        if (a[i].y == epoch && a[i].w == epoch && b[i].y == epoch && b[i].w == epoch) {
-          raw[i] = make_uint4(a[i].x, a[i].z, b[i].x, b[i].z);
-          have[i] = true;
-        } else {
-          ready = false;
+#pragma unroll 1
+    for (int i = 0; i < per_thread; ++i) {
+      const int c = tid + i * SS_THREADS;
+      const bool mine = c < chunks;
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (st.flags & AOTO_STAGE_FLAG_X_GATHER) {
+        if (mine) raw = ldg_nc_u4(gathered + c);
+      } else {
+        const size_t at = (size_t)min(c, chunks - 1) * 32;
+        while (!failed) {
+          const uint4 a = ss_ld_stamped_pair(words + at), b = ss_ld_stamped_pair(words + at + 16);
+          const bool ready = a.y == epoch && a.w == epoch && b.y == epoch && b.w == epoch;
+          if (ready && mine) raw = make_uint4(a.x, a.z, b.x, b.z);
+          if (__all_sync(0xffffffffu, ready)) break;
+          ++rounds;
+          // a CTA that gave up elsewhere ends every other wait early
+          if (rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0)) failed = true;
         }
       }
-      if (__syncthreads_and(ready)) break;
-      ++rounds;
-      // a CTA that already gave up elsewhere ends every other wait early
-      const bool stop = rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0);
-      if (__syncthreads_or(stop)) {
-        ss_give_up(p, stage_index);
-        return false;
+      float f[8];
+      unpack8(raw, f);
+      if (has_norm) {
+        s0 = fmaf(f[0], f[0], s0); s1 = fmaf(f[1], f[1], s1);
+        s0 = fmaf(f[2], f[2], s0); s1 = fmaf(f[3], f[3], s1);
+        s0 = fmaf(f[4], f[4], s0); s1 = fmaf(f[5], f[5], s1);
+        s0 = fmaf(f[6], f[6], s0); s1 = fmaf(f[7], f[7], s1);
+        if (mine) ss_store_chunk(xs, c, raw.x, raw.y, raw.z, raw.w);  // raw: normalised in place below
+      } else {
+        if (mine) ss_store_chunk(xs, c, raw.x, raw.y, raw.z, raw.w);
+        // a group of 64 columns is eight consecutive chunks, i.e. eight consecutive lanes
+        float chunk_sum = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
+        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 1);
+        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 2);
+        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 4);
+        if (mine && (lane & 7) == 0) ss_stsf(xsum + (uint32_t)(c >> 3) * 4, 136.f * chunk_sum);
       }
     }
-  }
-  ss_trace(p, stage_index, 1);
-
-  // ---- norm statistic, normalisation, fragment order, group sums ----
-  float inv = 1.f;
-  if (wv != nullptr) {
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < SS_MAX_CHUNKS; ++i) {
-      float f[8];
-      unpack8(raw[i], f);  // zero where the thread has no chunk
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+    if (has_norm) {
+      const float ss = warp_sum(s0 + s1);
+      if (lane == 0) stat[warp] = ss;
     }
-    ss = warp_sum(ss);
-    float* slot = red + (stage_index & 1) * 32;  // stages alternate: no barrier guards the slot against old readers
-    if (lane == 0) slot[warp] = ss;
+  } else if (has_norm && lane == 0) {
+    stat[warp] = 0.f;
+  }
+  if (__syncthreads_or(failed)) {
+    ss_give_up(p, stage_index);
+    return false;
+  }
+  if (TRACE) { ss_trace(p, stage_index, 1); ss_trace(p, stage_index, 2); }
+  if (has_norm) {
+    if (stager) {
+      // the warps' sums in a fixed order (a tree: the result does not depend on timing)
+      const float4 a = *reinterpret_cast<const float4*>(stat), b = *reinterpret_cast<const float4*>(stat + 4);
+      const float4 c4 = *reinterpret_cast<const float4*>(stat + 8), d = *reinterpret_cast<const float4*>(stat + 12);
+      const float total = (((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w))) +
+                          (((c4.x + c4.y) + (c4.z + c4.w)) + ((d.x + d.y) + (d.z + d.w)));
+      const float inv = rsqrtf(total / (float)K + st.rms_norm_eps);
+#pragma unroll 1
+      for (int i = 0; i < per_thread; ++i) {
+        const int c = tid + i * SS_THREADS;
+        const bool mine = c < chunks;
+        const uint32_t at = ss_chunk_address(xs, min(c, chunks - 1));
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (mine) raw = make_uint4(ss_lds32(at), ss_lds32(at + 16), ss_lds32(at + 32), ss_lds32(at + 48));
+        const uint4 weights = i == 0 ? nw0 : (mine ? ldg_nc_u4(wv + c) : make_uint4(0u, 0u, 0u, 0u));
+        float f[8], w[8];
+        unpack8(raw, f);
+        unpack8(weights, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = (f[j] * inv) * w[j];
+        uint4 o;
+        o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+        o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+        unpack8(o, f);  // the rounded values are what is multiplied and what is summed
+        if (mine) ss_store_chunk(xs, c, o.x, o.y, o.z, o.w);
+        float chunk_sum = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
+        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 1);
+        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 2);
+        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 4);
+        if (mine && (lane & 7) == 0) ss_stsf(xsum + (uint32_t)(c >> 3) * 4, 136.f * chunk_sum);
+      }
+    }
     __syncthreads();
-    float total = 0.f;
-#pragma unroll
-    for (int w = 0; w < SS_WARPS; ++w) total += slot[w];
-    inv = rsqrtf(total / (float)K + st.rms_norm_eps);
   }
-  const int per_thread = (chunks + SS_THREADS - 1) / SS_THREADS;
-#pragma unroll
-  for (int i = 0; i < SS_MAX_CHUNKS; ++i) {
-    if (i >= per_thread) break;  // uniform
-    const int c = tid + i * SS_THREADS;
-    float f[8];
-    unpack8(raw[i], f);
-    uint4 o = raw[i];
-    if (wv != nullptr) {
-      float w[8];
-      unpack8(nw[i], w);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = round_bf16((f[j] * inv) * w[j]);
-      o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
-      o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
-    }
-    float chunk_sum = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
-    if (c < chunks) ss_store_chunk(xs, c, o.x, o.y, o.z, o.w);
-    // a group of 64 columns is eight consecutive chunks, i.e. eight consecutive lanes
-    chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 1);
-    chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 2);
-    chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 4);
-    if (c < chunks && (lane & 7) == 0) ss_stsf(xsum + (uint32_t)(c >> 3) * 4, 136.f * chunk_sum);
-  }
-  __syncthreads();
-  ss_trace(p, stage_index, 2);
+  if (TRACE) ss_trace(p, stage_index, 3);
 
-  // ---- this warp's pieces of the stage ----
+  // ---- the multiply, then (one site for both) the finishing of a tile ----
   const bool paired = st.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED;
   const uint32_t xb = xs + (uint32_t)t * 16;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};  // [matrix][lo, hi]
-  int duty_tile = -1, duty_first = 0, duty_parts = 0;  // the shared tile this warp finishes after the barrier
-  uint2 duty_addend = make_uint2(0u, 0u);
-  bool alive = true;
-
-  // y of row n from the two totals: alpha, addend, paired SiLU
-  auto epilogue_value = [&](int n, float total0, float total1, uint2 stamped_addend) {
-    float y = st.alpha * total0;
-    if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN) {
-      y = fmaf(st.beta, ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + n), y);
-    } else if (st.addend_mode == AOTO_STAGE_ADDEND_GATHER) {
-      y = fmaf(st.beta, ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + (size_t)gather_row * N + n), y);
-    } else if (st.addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
-      y = fmaf(st.beta, (n & 1) ? bf16x2_hi(stamped_addend.x) : bf16x2_lo(stamped_addend.x), y);
-    }
-    if (paired) {
-      const float gate = round_bf16(y);
-      y = (st.alpha * total1) * (gate / (1.f + expf(-gate)));
-    }
-    return y;
-  };
-  // Stamped addend word of row n (an intermediate produced stages ago; the poll is a formality).
-  auto addend_word = [&](int n, bool& ok) {
-    uint2 w = make_uint2(0u, 0u);
-    if (st.addend_mode != AOTO_STAGE_ADDEND_STAMPED || n >= N) return w;
+  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;  // [matrix][rows g, g + 8]
+  bool alive = true, met = false;
+  // The addend of row n: a bias, a row of the gathered table, or an intermediate that was
+  // produced stages ago (its poll is a formality).
+  auto addend_of = [&](int n) {
+    if (st.addend_mode == AOTO_STAGE_ADDEND_NONE || n >= N) return 0.f;
+    if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN) return ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + n);
+    if (st.addend_mode == AOTO_STAGE_ADDEND_GATHER)
+      return ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + (size_t)gather_row * N + n);
     const unsigned char* at = reinterpret_cast<const unsigned char*>(st.addend) + (size_t)(n >> 1) * 8;
-    w = ss_ld_stamped(at);
+    uint2 w = ss_ld_stamped(at);
     for (int polls = 0; w.y != epoch; ++polls) {
-      if (polls > SS_POLL_LIMIT) { ok = false; break; }
+      if (polls > SS_POLL_LIMIT) { alive = false; break; }
       w = ss_ld_stamped(at);
     }
-    return w;
+    return (n & 1) ? bf16x2_hi(w.x) : bf16x2_lo(w.x);
   };
-  // Lanes 0-15 hold rows 0-15 of `tile`: round, store (stamped pairs or plain), track the maximum.
-  auto store_rows = [&](int tile, float y) {
-    const int n = tile * 16 + lane;
-    const uint32_t bits = float_to_bf16_bits(y);
-    const uint32_t neighbour = __shfl_down_sync(0xffffffffu, bits, 1);
-    if (lane < 16 && n < N) {
-      if (st.flags & AOTO_STAGE_FLAG_OUT_PLAIN) {
-        reinterpret_cast<bf16*>(st.out)[n] = __ushort_as_bfloat16((unsigned short)bits);
-      } else if ((lane & 1) == 0) {
-        ss_st_stamped(reinterpret_cast<unsigned char*>(st.out) + (size_t)(n >> 1) * 8, bits | (neighbour << 16), epoch);
-      }
-      if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
-        float v = __uint_as_float(bits << 16);
-        if (v != v) v = INFINITY;
-        if (v > best.value || (v == best.value && n < best.index)) { best.value = v; best.index = n; }
-      }
-    }
-  };
+  float duty_addend = 0.f;
+  if (duty != 0 && lane < 16) duty_addend = addend_of((tile0 + (int)(duty & 0x7FFFu)) * 16 + lane);
 
   bool first_piece = true;
-  while (ws.next_stage == (uint32_t)stage_index) {
-    if (!ss_mbar_wait(ws.bars + ws.slot * 8, ws.parity)) { alive = false; break; }
-    const uint32_t slot = ws.ring + ws.slot * SS_SLOT_BYTES;
-    const uint4 h = ss_lds128(slot);
-    // header: {stage, next_stage} {tile, kb0} {nblocks, mat, flags, nparts} {part_slot, ahead_size16}
-    const int tile_local = (int)(h.y & 0xFFFFu), kb0 = (int)(h.y >> 16);
-    const int nblocks = (int)(h.z & 0xFFu), mat = (int)((h.z >> 8) & 0xFFu);
-    const uint32_t flags = (h.z >> 16) & 0xFFu;
-    const int nparts = (int)(h.z >> 24);
-    const int part_slot = (int)(h.w & 0xFFFFu);
-    const uint32_t ahead = (h.w >> 16) * 16u;
-    float lo_sum = 0.f, hi_sum = 0.f;
+  while (true) {
+    int finish_tile = -1, finish_parts = 0;
+    uint32_t finish_first = 0;
+    float finish_addend = 0.f;
+    if (ws.next_stage == (uint32_t)stage_index) {
+      if (!ss_mbar_wait(ws.bars + ws.slot * 8, ws.parity)) { alive = false; break; }
+      const uint32_t slot = ws.ring + ws.slot * SS_SLOT_BYTES;
+      // header: {next_stage | nblocks << 16 | flags << 24} {byte offset of the columns in the staged row}
+      //         {byte offset of the partial slot | tile << 16} {bytes of the piece ring_depth ahead}
+      const uint4 h = ss_lds128(slot);
+      const int nblocks = (int)((h.x >> 16) & 0xFFu);
+      const uint32_t flags = h.x >> 24;
+      float lo_sum = 0.f, hi_sum = 0.f;
 #pragma unroll 1
-    for (int b = 0; b < nblocks; ++b) {
-      float lo, hi;
-      ss_block(slot + 16 + (uint32_t)b * SS_BLOCK_BYTES, xb + (uint32_t)(kb0 + b) * 256, xsum + (uint32_t)(kb0 + b) * 8,
-               lane, lo, hi);
-      lo_sum += lo;
-      hi_sum += hi;
+      for (int b = 0; b < nblocks; ++b) {
+        float lo, hi;
+        ss_blocks<1>(slot + 16 + (uint32_t)b * SS_BLOCK_BYTES, xb + h.y + (uint32_t)b * 256,
+                     xsum + (h.y >> 5) + (uint32_t)b * 8, lane, lo, hi);
+        lo_sum += lo;
+        hi_sum += hi;
+      }
+      if (flags & AOTO_PIECE_MAT1) { acc2 += lo_sum; acc3 += hi_sum; } else { acc0 += lo_sum; acc1 += hi_sum; }
+      __syncwarp();  // every lane is done with the slot before it is refilled
+      ws.next_stage = h.x & 0xFFFFu;
+      ws.slot += 1;
+      if (ws.slot == (uint32_t)p.a.ring_depth) { ws.slot = 0; ws.parity ^= 1u; }
+      ws.in_flight -= 1;
+      if (h.w != 0) ss_request(p, ws, h.w, lane);
+      if (TRACE && first_piece) { ss_trace(p, stage_index, 4); first_piece = false; }
+      if (flags & AOTO_PIECE_SEG_END) {
+        // the share's sums go to its partial slot (a whole tile has a slot of the warp's own)
+        const uint32_t at = part + (h.z & 0xFFFFu);
+        if (t == 0) {
+          ss_stsf(at + (uint32_t)g * 4, acc0);
+          ss_stsf(at + (uint32_t)(g + 8) * 4, acc1);
+          if (paired) {
+            ss_stsf(at + 64 + (uint32_t)g * 4, acc2);
+            ss_stsf(at + 64 + (uint32_t)(g + 8) * 4, acc3);
+          }
+        }
+        acc0 = acc1 = acc2 = acc3 = 0.f;
+        if (flags & AOTO_PIECE_WHOLE) {
+          finish_tile = tile0 + (int)(h.z >> 16);
+          finish_first = at;
+          finish_parts = 1;
+          if (lane < 16) finish_addend = addend_of(finish_tile * 16 + lane);
+        }
+      }
+    } else if (!met) {
+      // tiles shared between warps: meet, then the warp whose duty it is sums the shares
+      if (TRACE) ss_trace(p, stage_index, 5);
+      met = true;
+      if (shares_tiles) {
+        if (__syncthreads_or(!alive)) {
+          ss_give_up(p, stage_index);
+          return false;
+        }
+        if (TRACE) ss_trace(p, stage_index, 6);
+        if (duty != 0) {
+          finish_tile = tile0 + (int)(duty & 0x7FFFu);
+          finish_first = part + ((duty >> 16) & 0xFFu) * SS_PART_BYTES;
+          finish_parts = (int)(duty >> 24);
+          finish_addend = duty_addend;
+        }
+      }
+    } else {
+      break;
     }
-    if (mat == 0) { acc[0] += lo_sum; acc[1] += hi_sum; } else { acc[2] += lo_sum; acc[3] += hi_sum; }
-    __syncwarp();  // every lane is done with the slot before it is refilled
-    ws.next_stage = h.x >> 16;
-    ws.slot += 1;
-    if (ws.slot == (uint32_t)p.a.ring_depth) { ws.slot = 0; ws.parity ^= 1u; }
-    ws.in_flight -= 1;
-    if (ahead != 0) ss_request(p, ws, ahead, lane);
-    if (first_piece) { ss_trace(p, stage_index, 3); first_piece = false; }
-
-    if (flags & AOTO_PIECE_SEG_END) {
-      // the share's sums go to a partial slot: a shared one, or the warp's own for a whole tile
-      const bool whole = (flags & AOTO_PIECE_WHOLE) != 0;
-      const int my_slot = whole ? AOTO_STREAM_PART_SLOTS + warp : part_slot;
-      const uint32_t at = part + (uint32_t)my_slot * SS_PART_BYTES;
-      if (t == 0) {
-        ss_stsf(at + (uint32_t)g * 4, acc[0]);
-        ss_stsf(at + (uint32_t)(g + 8) * 4, acc[1]);
+    if (finish_tile >= 0) {
+      // lanes 0-15 hold rows 0-15 of the tile: sum the shares in a fixed order, alpha, addend,
+      // paired SiLU, round, store (stamped pairs or plain), track the maximum
+      __syncwarp();
+      const int n = finish_tile * 16 + lane;
+      float y = 0.f;
+      if (lane < 16) {
+        float total0 = 0.f, total1 = 0.f;
+        for (int i = 0; i < finish_parts; ++i) {
+          const uint32_t at = finish_first + (uint32_t)i * SS_PART_BYTES + (uint32_t)lane * 4;
+          total0 += ss_ldsf(at);
+          if (paired) total1 += ss_ldsf(at + 64);
+        }
+        y = st.alpha * total0;
+        if (st.addend_mode != AOTO_STAGE_ADDEND_NONE) y = fmaf(st.beta, finish_addend, y);
         if (paired) {
-          ss_stsf(at + 64 + (uint32_t)g * 4, acc[2]);
-          ss_stsf(at + 64 + (uint32_t)(g + 8) * 4, acc[3]);
+          const float gate = round_bf16(y);
+          y = (st.alpha * total1) * (gate / (1.f + expf(-gate)));
+        }
+        if (n >= N) y = 0.f;
+      }
+      const uint32_t bits = float_to_bf16_bits(y);
+      const uint32_t neighbour = __shfl_down_sync(0xffffffffu, bits, 1);
+      if (lane < 16 && n < N) {
+        if (st.flags & AOTO_STAGE_FLAG_OUT_PLAIN) {
+          reinterpret_cast<bf16*>(st.out)[n] = __ushort_as_bfloat16((unsigned short)bits);
+        } else if ((lane & 1) == 0) {
+          ss_st_stamped(reinterpret_cast<unsigned char*>(st.out) + (size_t)(n >> 1) * 8, bits | (neighbour << 16), epoch);
+        }
+        if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
+          float v = __uint_as_float(bits << 16);
+          if (v != v) v = INFINITY;
+          if (v > best.value || (v == best.value && n < best.index)) { best.value = v; best.index = n; }
         }
       }
-      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-      const int tile = tile0 + tile_local;
-      if (whole) {
-        __syncwarp();
-        bool ok = true;
-        const uint2 addend = lane < 16 ? addend_word(tile * 16 + lane, ok) : make_uint2(0u, 0u);
-        float y = 0.f;
-        if (lane < 16) {
-          const float total0 = ss_ldsf(at + (uint32_t)lane * 4);
-          const float total1 = paired ? ss_ldsf(at + 64 + (uint32_t)lane * 4) : 0.f;
-          if (tile * 16 + lane < N) y = epilogue_value(tile * 16 + lane, total0, total1, addend);
-        }
-        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-        store_rows(tile, y);
-        __syncwarp();  // the private slot is read before the next whole tile overwrites it
-      } else if (flags & AOTO_PIECE_FINISHER) {
-        duty_tile = tile;
-        duty_first = part_slot - (nparts - 1);
-        duty_parts = nparts;
-        bool ok = true;  // the addend is requested now, it is not on the critical path after the barrier
-        duty_addend = lane < 16 ? addend_word(tile * 16 + lane, ok) : make_uint2(0u, 0u);
-        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-      }
+      __syncwarp();  // a warp's own slot is read before its next whole tile overwrites it
     }
   }
-  ss_trace(p, stage_index, 4);
-
-  // ---- tiles shared between warps: meet, then the finisher sums the shares in a fixed order ----
-  if (shares_tiles) {
+  // a stage without shared tiles still meets once: the staged row stays until every warp has used it
+  if (!shares_tiles || !alive) {
     if (__syncthreads_or(!alive)) {
       ss_give_up(p, stage_index);
       return false;
     }
-    if (duty_tile >= 0) {
-      float y = 0.f;
-      if (lane < 16) {
-        float total0 = 0.f, total1 = 0.f;
-        for (int i = 0; i < duty_parts; ++i) {
-          const uint32_t at = part + (uint32_t)(duty_first + i) * SS_PART_BYTES + (uint32_t)lane * 4;
-          total0 += ss_ldsf(at);
-          if (paired) total1 += ss_ldsf(at + 64);
-        }
-        if (duty_tile * 16 + lane < N) y = epilogue_value(duty_tile * 16 + lane, total0, total1, duty_addend);
-      }
-      store_rows(duty_tile, y);
-    }
-  } else if (__syncthreads_or(!alive)) {  // also keeps the staged row alive until every warp has used it
-    ss_give_up(p, stage_index);
-    return false;
   }
-  ss_trace(p, stage_index, 5);
 
   if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
-    float* sv = red;
-    int* si = reinterpret_cast<int*>(red + 32);
+    float* sv = reinterpret_cast<float*>(smem + p.L.red);
+    int* si = reinterpret_cast<int*>(sv + 32);
     float bv = best.value;
     int bi = best.index;
 #pragma unroll
@@ -565,8 +591,7 @@ __device__ bool ss_gemv(const SSParams& p, const aoto_stream_stage& st, int stag
       ss_st_stamped(payload + (size_t)blockIdx.x * 16 + 8, (uint32_t)bi, epoch);
     }
   }
-  ss_trace(p, stage_index, 6);
-  ss_trace(p, stage_index, 7);
+  if (TRACE) ss_trace(p, stage_index, 7);
   return true;
 }
 
@@ -616,13 +641,14 @@ __device__ __forceinline__ void ss_request_window(const SSParams& p, const aoto_
   ss_bulk_load(vbuf, vin + (size_t)(r.k0 + 1) * D, bytes, bar);
 }
 
+template <bool TRACE>
 __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int stage_index, int valid_length,
-                             long long position, uint32_t& kv_parity, bool& kv_pending, unsigned char* smem) {
+                             uint32_t& kv_parity, bool& kv_pending, unsigned char* smem) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int D = p.a.head_dim, C = p.a.capacity, KVH = p.a.kv_heads, QH = p.a.query_heads;
   const int G = QH / KVH;
   const uint32_t epoch = p.a.epoch;
-  ss_trace(p, stage_index, 0);
+  if (TRACE) ss_trace(p, stage_index, 0);
 
   // Moving the window (slot j of the next cache is slot j + 1 of this one) touches nothing the
   // step computes with: the CTAs without a head do it, or every CTA when each one has a head.
@@ -639,9 +665,9 @@ __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int
   };
   if ((int)blockIdx.x >= QH) {
     move_window((int)blockIdx.x - QH, helpers);
-    ss_trace(p, stage_index, 1);
-    ss_trace(p, stage_index, 6);
-    ss_trace(p, stage_index, 7);
+    if (TRACE) ss_trace(p, stage_index, 1);
+    if (TRACE) ss_trace(p, stage_index, 6);
+    if (TRACE) ss_trace(p, stage_index, 7);
     return true;
   }
 
@@ -651,11 +677,8 @@ __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int
   float* rowv = reinterpret_cast<float*>(smem + p.L.work);  // raw q head, k, v of the step: 3 * D
   float* qs = rowv + 3 * D;                                 // rotated, scaled query: D
   float* merge = qs + D;                                    // per warp: m, l, then D sums
-  long long pos = position;
-  if (pos < 0) pos = 0;
-  if (pos >= p.a.table_rows) pos = p.a.table_rows - 1;
-  const bf16* cos_row = reinterpret_cast<const bf16*>(p.a.cos_table) + (size_t)pos * D;
-  const bf16* sin_row = reinterpret_cast<const bf16*>(p.a.sin_table) + (size_t)pos * D;
+  const bf16* cos_row = reinterpret_cast<const bf16*>(smem + p.L.rotary);
+  const bf16* sin_row = cos_row + D;
   const KeyRange r = ss_key_range(p, warp, valid_length);
   unsigned char* kbuf = smem + p.L.kv + (size_t)warp * 2 * p.L.keys_per_warp * D * 2;
   unsigned char* vbuf = kbuf + (size_t)p.L.keys_per_warp * D * 2;
@@ -691,7 +714,7 @@ __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int
       }
     }
   }
-  ss_trace(p, stage_index, 1);
+  if (TRACE) ss_trace(p, stage_index, 1);
 
   // rotate; this step's key and value join the window of the warp that owns the last slot
   {
@@ -712,6 +735,7 @@ __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int
     }
   }
   __syncthreads();
+  if (TRACE) ss_trace(p, stage_index, 2);
 
   // every warp attends its keys: two lanes per key for the scores, the lanes split the head
   // dimension for the weighted sum of values
@@ -719,6 +743,7 @@ __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int
   if (kv_pending && r.old_keys > 0) {
     alive = ss_mbar_wait(ss_smem(smem + p.L.kvbars) + (uint32_t)warp * 8, kv_parity);
   }
+  if (TRACE) ss_trace(p, stage_index, 3);
   {
     const int key = lane >> 1, half = lane & 1;
     const int nkeys = r.k1 - r.k0;
@@ -746,26 +771,36 @@ __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int
     }
     const float other = __shfl_xor_sync(0xffffffffu, s, 1);
     s = attend ? s + other : -INFINITY;
-    const float m = warp_max(s);
+    const float m = ss_warp_max(s);
     const float m_safe = m == -INFINITY ? 0.f : m;
     const float e = s == -INFINITY ? 0.f : expf(s - m_safe);
-    const float l = warp_sum(half == 0 ? e : 0.f);
-    // weighted values: lane holds D / 32 consecutive dimensions
+    // the warp's weights go through shared memory: the weighted sum below reads them as
+    // broadcasts and needs no shuffle per key
+    float* weights = merge + SS_WARPS * (D + 2) + warp * 16;
+    if (half == 0) weights[key] = e;
+    __syncwarp();
+    // weighted values: lane holds D / 32 consecutive dimensions; every lane also sums the weights
     const int dims = D >> 5;  // 2 or 4
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, l = 0.f;
     const uint32_t vrow = ss_smem(vbuf) + (uint32_t)lane * dims * 2;
-    for (int j = 0; j < nkeys; ++j) {
-      const float w = __shfl_sync(0xffffffffu, e, 2 * j);
-      if (w != 0.f) {  // uniform over the warp
-        if (dims == 2) {
-          const uint32_t v = ss_lds32(vrow + (uint32_t)j * D * 2);
-          a0 = fmaf(w, bf16x2_lo(v), a0);
-          a1 = fmaf(w, bf16x2_hi(v), a1);
-        } else {
-          const uint32_t v0 = ss_lds32(vrow + (uint32_t)j * D * 2), v1 = ss_lds32(vrow + (uint32_t)j * D * 2 + 4);
-          a0 = fmaf(w, bf16x2_lo(v0), a0); a1 = fmaf(w, bf16x2_hi(v0), a1);
-          a2 = fmaf(w, bf16x2_lo(v1), a2); a3 = fmaf(w, bf16x2_hi(v1), a3);
-        }
+    const uint32_t wrow = ss_smem(weights);
+    if (dims == 2) {
+#pragma unroll 4
+      for (int j = 0; j < nkeys; ++j) {
+        const float w = ss_ldsf(wrow + (uint32_t)j * 4);
+        const uint32_t v = ss_lds32(vrow + (uint32_t)j * D * 2);
+        a0 = fmaf(w, bf16x2_lo(v), a0);
+        a1 = fmaf(w, bf16x2_hi(v), a1);
+        l += w;
+      }
+    } else {
+#pragma unroll 4
+      for (int j = 0; j < nkeys; ++j) {
+        const float w = ss_ldsf(wrow + (uint32_t)j * 4);
+        const uint32_t v0 = ss_lds32(vrow + (uint32_t)j * D * 2), v1 = ss_lds32(vrow + (uint32_t)j * D * 2 + 4);
+        a0 = fmaf(w, bf16x2_lo(v0), a0); a1 = fmaf(w, bf16x2_hi(v0), a1);
+        a2 = fmaf(w, bf16x2_lo(v1), a2); a3 = fmaf(w, bf16x2_hi(v1), a3);
+        l += w;
       }
     }
     float* mine = merge + warp * (D + 2);
@@ -774,10 +809,12 @@ __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int
     mine[3 + lane * dims] = a1;
     if (dims == 4) { mine[4 + lane * dims] = a2; mine[5 + lane * dims] = a3; }
   }
+  if (TRACE) ss_trace(p, stage_index, 4);
   if (__syncthreads_or(!alive)) {
     ss_give_up(p, stage_index);
     return false;
   }
+  if (TRACE) ss_trace(p, stage_index, 5);
   if (kv_pending) { kv_parity ^= 1u; kv_pending = false; }
 
   // the next layer's window can start travelling now: every warp is done with its buffers
@@ -787,40 +824,43 @@ __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int
     kv_pending = true;
   }
 
-  // merge the warps' results in a fixed order
+  // merge the warps' results in a fixed order; the sixteen rescaling factors are computed once
+  // per merging warp (one lane each) instead of once per output dimension
   if (tid < D) {
-    float m = -INFINITY;
+    float* factors = merge + SS_WARPS * (D + 2) + SS_WARPS * 16 + warp * 16;
+    const float wm = lane < SS_WARPS ? merge[lane * (D + 2)] : -INFINITY;
+    const float wl = lane < SS_WARPS ? merge[lane * (D + 2) + 1] : 0.f;
+    const float m = ss_warp_max(wm);
+    const float factor = wm == -INFINITY ? 0.f : expf(wm - m);
+    if (lane < SS_WARPS) factors[lane] = factor;
+    const float den = warp_sum(factor * wl);
+    __syncwarp();
+    float n0 = 0.f, n1 = 0.f;
 #pragma unroll
-    for (int w = 0; w < SS_WARPS; ++w) m = fmaxf(m, merge[w * (D + 2)]);
-    float num = 0.f, den = 0.f;
-    if (m != -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < SS_WARPS; ++w) {
-        const float wm = merge[w * (D + 2)];
-        const float scale = wm == -INFINITY ? 0.f : expf(wm - m);
-        num = fmaf(scale, merge[w * (D + 2) + 2 + tid], num);
-        den = fmaf(scale, merge[w * (D + 2) + 1], den);
-      }
+    for (int w = 0; w < SS_WARPS; w += 2) {
+      n0 = fmaf(factors[w], merge[w * (D + 2) + 2 + tid], n0);
+      n1 = fmaf(factors[w + 1], merge[(w + 1) * (D + 2) + 2 + tid], n1);
     }
-    const float out = den > 0.f ? num / den : 0.f;
+    const float out = den > 0.f ? (n0 + n1) / den : 0.f;
     const uint32_t bits = float_to_bf16_bits(out);
     const uint32_t neighbour = __shfl_down_sync(0xffffffffu, bits, 1);
     if ((tid & 1) == 0)
       ss_st_stamped(reinterpret_cast<unsigned char*>(st.out) + ((size_t)head * pairs + (tid >> 1)) * 8,
                     bits | (neighbour << 16), epoch);
   }
+  if (TRACE) ss_trace(p, stage_index, 6);
   if (helpers <= 0) move_window(head, QH);
   __syncthreads();  // the work region is free for the next stage
-  ss_trace(p, stage_index, 6);
-  ss_trace(p, stage_index, 7);
+  if (TRACE) ss_trace(p, stage_index, 7);
   return true;
 }
 
 // ---------------------------------------------------------------------------
 // pick stage: CTA 0 polls the per-CTA maxima the ARGMAX stage left
 // ---------------------------------------------------------------------------
+template <bool TRACE>
 __device__ void ss_pick(const SSParams& p, int stage_index) {
-  ss_trace(p, stage_index, 0);
+  if (TRACE) ss_trace(p, stage_index, 0);
   if (blockIdx.x != 0 || threadIdx.x >= 32) return;
   const unsigned char* payload = reinterpret_cast<const unsigned char*>(p.a.scratch);
   float bv = -INFINITY;
@@ -845,7 +885,7 @@ __device__ void ss_pick(const SSParams& p, int stage_index) {
     const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
     if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
   }
-  ss_trace(p, stage_index, 1);
+  if (TRACE) ss_trace(p, stage_index, 1);
   if (threadIdx.x == 0 && !failed) {
     p.a.token[0] = (long long)bi;
     if (p.a.counters != nullptr) {
@@ -856,10 +896,11 @@ __device__ void ss_pick(const SSParams& p, int stage_index) {
     }
   }
   if (threadIdx.x == 0 && failed) atomicCAS(p.a.status, 0, stage_index + 1);
-  ss_trace(p, stage_index, 6);
-  ss_trace(p, stage_index, 7);
+  if (TRACE) ss_trace(p, stage_index, 6);
+  if (TRACE) ss_trace(p, stage_index, 7);
 }
 
+template <bool TRACE>
 __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid_constant__ SSParams p) {
   extern __shared__ uint4 ss_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(ss_raw);
@@ -910,6 +951,15 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
   uint32_t kv_parity = 0;
   bool kv_pending = false;
   const aoto_stream_stage* stages = reinterpret_cast<const aoto_stream_stage*>(smem + p.L.stages);
+  if (p.a.first_attention >= 0 && (int)blockIdx.x < p.a.query_heads && tid < 2 * p.a.head_dim) {
+    // the rotary rows of the step's position: fetched once, off every layer's critical path
+    long long pos = position;
+    if (pos < 0) pos = 0;
+    if (pos >= p.a.table_rows) pos = p.a.table_rows - 1;
+    const int D = p.a.head_dim;
+    const bf16* table = reinterpret_cast<const bf16*>(tid < D ? p.a.cos_table : p.a.sin_table);
+    reinterpret_cast<bf16*>(smem + p.L.rotary)[tid] = table[(size_t)pos * D + (tid < D ? tid : tid - D)];
+  }
   if (p.a.first_attention >= 0) {
     ss_request_window(p, stages[p.a.first_attention], warp, lane, valid_length, smem);
     kv_pending = true;
@@ -925,7 +975,7 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
     if (st.kind == AOTO_STAGE_GEMV) {
       const uint32_t entry = table[s];
       if (((entry >> 16) & 0x7FFFu) != 0) {
-        alive = ss_gemv(p, st, s, entry, ws, best, smem);
+        alive = ss_gemv<TRACE>(p, st, s, entry, ws, best, smem);
       } else if ((st.flags & AOTO_STAGE_FLAG_ARGMAX) && tid == 0) {
         // a CTA without rows of the last projection still answers the pick stage's poll
         unsigned char* payload = reinterpret_cast<unsigned char*>(p.a.scratch);
@@ -933,9 +983,9 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
         ss_st_stamped(payload + (size_t)blockIdx.x * 16 + 8, 0x7fffffffu, p.a.epoch);
       }
     } else if (st.kind == AOTO_STAGE_ATTENTION) {
-      alive = ss_attention(p, st, s, valid_length, position, kv_parity, kv_pending, smem);
+      alive = ss_attention<TRACE>(p, st, s, valid_length, kv_parity, kv_pending, smem);
     } else if (st.kind == AOTO_STAGE_PICK) {
-      ss_pick(p, s);
+      ss_pick<TRACE>(p, s);
     }
   }
   if (!alive) {
@@ -982,7 +1032,8 @@ extern "C" int64_t aoto_sm100_stream_step_smem_bytes(const aoto_stream_step_args
 }
 
 extern "C" int aoto_sm100_stream_step(const aoto_stream_step_args* a, void* stream_) {
-  if (!a || !a->stages || !a->cta_table || !a->starts || !a->stream || !a->status || !a->scratch || a->epoch == 0)
+  if (!a || !a->stages || !a->cta_table || !a->duties || !a->starts || !a->stream || !a->status || !a->scratch ||
+      a->epoch == 0)
     return AOTO_ERR_ARGUMENT;
   if (!aligned_to(a->stream, 16) || !aligned_to(a->stages, 16) || !aligned_to(a->starts, 16)) return AOTO_ERR_ARGUMENT;
   if (a->scratch_bytes < aoto_sm100_stream_step_scratch_bytes(a->ctas)) return AOTO_ERR_ARGUMENT;
@@ -998,10 +1049,14 @@ extern "C" int aoto_sm100_stream_step(const aoto_stream_step_args* a, void* stre
   cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device);
   cudaDeviceGetAttribute(&smem_limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
   if (!coop || (int64_t)params.L.total > (int64_t)smem_limit) return AOTO_ERR_UNSUPPORTED;
-  static PerDeviceOnce raised;
-  if (raise_dynamic_smem(stream_step_kernel, (size_t)smem_limit, raised) != AOTO_OK) return AOTO_ERR_LAUNCH;
+  // two instantiations: the marks of the per-stage timeline cost issue slots, so the kernel that
+  // serves requests carries none
+  auto kernel = a->trace != nullptr ? stream_step_kernel<true> : stream_step_kernel<false>;
+  static PerDeviceOnce raised_plain, raised_traced;
+  if (raise_dynamic_smem(kernel, (size_t)smem_limit, a->trace != nullptr ? raised_traced : raised_plain) != AOTO_OK)
+    return AOTO_ERR_LAUNCH;
   int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, stream_step_kernel, SS_THREADS, params.L.total) != cudaSuccess ||
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, SS_THREADS, params.L.total) != cudaSuccess ||
       per_sm < 1) {
     (void)cudaGetLastError();
     return AOTO_ERR_UNSUPPORTED;
@@ -1017,7 +1072,7 @@ extern "C" int aoto_sm100_stream_step(const aoto_stream_step_args* a, void* stre
   attribute[0].val.cooperative = 1;
   config.attrs = attribute;
   config.numAttrs = 1;
-  if (cudaLaunchKernelEx(&config, stream_step_kernel, params) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&config, kernel, params) != cudaSuccess) {
     (void)cudaGetLastError();
     return AOTO_ERR_LAUNCH;
   }

@@ -92,7 +92,7 @@ class DecodeSession:
         tensors[program.token_input] = self.token
         tensors[program.position_input] = self.position
         tensors[program.mask_input] = self.mask
-        layout, stream, table, starts = sp.device_stream(program, tensors, device, ctas, depth)
+        layout, stream, table, starts, duties = sp.device_stream(program, tensors, device, ctas, depth)
         self.arena = torch.zeros(program.arena_bytes, dtype=torch.uint8, device=device)
         self.logits = torch.zeros((1, 1, program.vocab), dtype=torch.bfloat16, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
@@ -100,7 +100,7 @@ class DecodeSession:
         self.scratch = torch.zeros(max(int(lib.aoto_sm100_stream_step_scratch_bytes(ctas)), 1 << 12),
                                    dtype=torch.uint8, device=device)
         self.stage_count = len(program.stages) + 1
-        self._stream_keep = (stream, table, starts)
+        self._stream_keep = (stream, table, starts, duties)
         self._stream_args = []
         self.programs = []
         geo = sp.geometry(program)
@@ -119,7 +119,7 @@ class DecodeSession:
             self.programs.append(stages)
             args = sp.base_args(program, ctas, depth)
             args.stages = stages.data_ptr()
-            args.cta_table, args.starts = table.data_ptr(), starts.data_ptr()
+            args.cta_table, args.starts, args.duties = table.data_ptr(), starts.data_ptr(), duties.data_ptr()
             args.stream, args.stream_bytes = stream.data_ptr(), stream.numel()
             if geo is not None:
                 args.cos_table, args.sin_table = resolve(geo["cos_table"]), resolve(geo["sin_table"])

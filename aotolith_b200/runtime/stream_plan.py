@@ -36,12 +36,11 @@ HEADER_BYTES = 16
 SLOT_BYTES = HEADER_BYTES + PIECE_BLOCKS * BLOCK_BYTES
 PART_SLOTS = 32
 NO_STAGE = 0xFFFF
-SEG_END, WHOLE, FINISHER = 1, 2, 4
+SEG_END, WHOLE, MAT1 = 1, 2, 4
 
 PIECE_DTYPE = np.dtype([
-    ("stage", "<u2"), ("next_stage", "<u2"), ("tile", "<u2"), ("kb0", "<u2"),
-    ("nblocks", "u1"), ("mat", "u1"), ("flags", "u1"), ("nparts", "u1"),
-    ("part_slot", "<u2"), ("ahead_size16", "<u2"),
+    ("next_stage", "<u2"), ("nblocks", "u1"), ("flags", "u1"), ("column_bytes", "<u4"),
+    ("part_bytes", "<u2"), ("tile", "<u2"), ("ahead_bytes", "<u4"),
 ])
 START_DTYPE = np.dtype([("offset16", "<u4"), ("size16", "<u2", (3,)), ("first_stage", "<u2"), ("reserved", "<u4")])
 assert PIECE_DTYPE.itemsize == 16 and START_DTYPE.itemsize == 16
@@ -86,14 +85,18 @@ def assign_tiles(tiles: int, per_tile: int, ctas: int, first_cta: int) -> list[t
 def plan_stage(stage: int, tiles: int, nb: int, mats: int, ctas: int, first_cta: int):
     """Pieces of one GEMV stage.
 
-    Returns ``(table_row, pieces)``: the ``uint32[ctas]`` entries of the stage and a list of
-    ``(cta, warp, tile_local, mat, kb0, nblocks, flags, nparts, part_slot)`` in the order
-    every warp multiplies its pieces.
+    Returns ``(table_row, duties, pieces)``: the ``uint32[ctas]`` entries of the stage, the
+    ``uint32[ctas, 16]`` finishing duties, and a list of
+    ``(cta, warp, tile_local, mat, kb0, nblocks, flags, part_slot)`` in the order every warp
+    multiplies its pieces. A tile cut across warps gets consecutive partial slots in block
+    order and is finished by the warp that holds its last block; a tile held by one warp uses
+    that warp's own slot (``PART_SLOTS + warp``) and is finished as soon as it is multiplied.
     """
 
     per_tile = mats * nb
     ranges = assign_tiles(tiles, per_tile, ctas, first_cta)
     table = np.zeros(ctas, dtype=np.uint32)
+    duties = np.zeros((ctas, WARPS), dtype=np.uint32)
     pieces: list[tuple] = []
     for cta, (tile0, count) in enumerate(ranges):
         if count == 0:
@@ -108,7 +111,6 @@ def plan_stage(stage: int, tiles: int, nb: int, mats: int, ctas: int, first_cta:
                 take = min(hi - lo, per_tile - inside)
                 segments.append((warp, tile_local, inside, take))
                 lo += take
-        # shares of a tile cut across warps get consecutive partial slots, in block order
         parts_of_tile: dict[int, int] = {}
         for _, tile_local, _, take in segments:
             if take != per_tile:
@@ -119,7 +121,7 @@ def plan_stage(stage: int, tiles: int, nb: int, mats: int, ctas: int, first_cta:
         for warp, tile_local, inside, take in segments:
             whole = take == per_tile
             flags_end = SEG_END | (WHOLE if whole else 0)
-            nparts = part_slot = 0
+            part_slot = PART_SLOTS + warp
             if not whole:
                 if tile_local not in first_slot:
                     first_slot[tile_local] = next_slot
@@ -127,24 +129,25 @@ def plan_stage(stage: int, tiles: int, nb: int, mats: int, ctas: int, first_cta:
                     seen[tile_local] = 0
                 part_slot = first_slot[tile_local] + seen[tile_local]
                 seen[tile_local] += 1
-                nparts = parts_of_tile[tile_local]
                 if inside + take == per_tile:
-                    flags_end |= FINISHER
+                    if duties[cta, warp]:
+                        raise ValueError(f"stage {stage}: warp {warp} of CTA {cta} would finish two shared tiles")
+                    duties[cta, warp] = (tile_local | 0x8000 | (first_slot[tile_local] << 16)
+                                         | (parts_of_tile[tile_local] << 24))
             # pieces never cross a matrix boundary and hold at most PIECE_BLOCKS blocks
             at, end = inside, inside + take
             while at < end:
                 mat, kb0 = divmod(at, nb)
                 n = min(PIECE_BLOCKS, end - at, nb - kb0)
                 last = at + n == end
-                pieces.append((cta, warp, tile_local, mat, kb0, n, flags_end if last else 0,
-                               nparts if last else 0, part_slot))
+                pieces.append((cta, warp, tile_local, mat, kb0, n, flags_end if last else 0, part_slot))
                 at += n
         if next_slot > PART_SLOTS:
             raise ValueError(f"stage {stage}: {next_slot} shared-tile partial sums in one CTA exceed {PART_SLOTS}")
         if tile0 > 0xFFFF or count > 0x7FFF:
             raise ValueError(f"stage {stage}: tile range ({tile0}, {count}) does not fit the table entry")
         table[cta] = tile0 | (count << 16) | ((1 << 31) if next_slot else 0)
-    return table, pieces
+    return table, duties, pieces
 
 
 # ---------------------------------------------------------------------------
@@ -213,8 +216,12 @@ class StreamLayout:
     ring_depth: int
     stage_count: int
     table: np.ndarray            # uint32 [stage_count, ctas]
+    duties: np.ndarray           # uint32 [stage_count, ctas, WARPS]
     starts: np.ndarray           # START_DTYPE [ctas * WARPS]
     headers: np.ndarray          # PIECE_DTYPE [pieces], in stream order
+    piece_stage: np.ndarray      # what the headers no longer say: stage, matrix and first block
+    piece_mat: np.ndarray
+    piece_kb0: np.ndarray
     piece_offset16: np.ndarray   # int64 [pieces]
     piece_cta: np.ndarray
     piece_warp: np.ndarray
@@ -225,12 +232,13 @@ def layout_streams(shapes: list[GemvShape], stage_count: int, ctas: int, ring_de
     """Plan every GEMV stage and lay the pieces out as one stream per (CTA, warp)."""
 
     table = np.zeros((stage_count, ctas), dtype=np.uint32)
+    duties = np.zeros((stage_count, ctas, WARPS), dtype=np.uint32)
     records: list[tuple] = []
     cursor = 0
     for shape in shapes:
         tiles, nb = -(-shape.n_rows // 16), shape.K // 128
-        row, pieces = plan_stage(shape.stage, tiles, nb, shape.mats, ctas, cursor)
-        table[shape.stage] = row
+        row, duty, pieces = plan_stage(shape.stage, tiles, nb, shape.mats, ctas, cursor)
+        table[shape.stage], duties[shape.stage] = row, duty
         used = int(np.count_nonzero(row))
         if used < ctas:
             cursor = (cursor + used) % ctas  # small stages take turns over the grid
@@ -238,11 +246,11 @@ def layout_streams(shapes: list[GemvShape], stage_count: int, ctas: int, ring_de
     if not records:
         raise ValueError("a stage program without packed projections has no stream")
     fields = np.array(records, dtype=np.int64)
-    stage, cta, warp, tile, mat, kb0, nblocks, flags, nparts, part_slot = fields.T
+    stage, cta, warp, tile, mat, kb0, nblocks, flags, part_slot = fields.T
     # stream order: by (cta, warp), stages ascending, planning order within a stage (stable sort)
     order = np.lexsort((np.arange(len(stage)), stage, warp, cta))
-    stage, cta, warp, tile, mat, kb0, nblocks, flags, nparts, part_slot = (
-        column[order] for column in (stage, cta, warp, tile, mat, kb0, nblocks, flags, nparts, part_slot))
+    stage, cta, warp, tile, mat, kb0, nblocks, flags, part_slot = (
+        column[order] for column in (stage, cta, warp, tile, mat, kb0, nblocks, flags, part_slot))
     size16 = 1 + nblocks * (BLOCK_BYTES // 16)
     offset16 = np.concatenate(([0], np.cumsum(size16)[:-1]))
     owner = cta * WARPS + warp
@@ -250,15 +258,15 @@ def layout_streams(shapes: list[GemvShape], stage_count: int, ctas: int, ring_de
     index = np.arange(count)
     first_of_owner = np.concatenate(([True], owner[1:] != owner[:-1]))
     headers = np.zeros(count, dtype=PIECE_DTYPE)
-    headers["stage"], headers["tile"], headers["kb0"] = stage, tile, kb0
-    headers["nblocks"], headers["mat"], headers["flags"], headers["nparts"] = nblocks, mat, flags, nparts
-    headers["part_slot"] = part_slot
+    headers["nblocks"], headers["flags"] = nblocks, flags | np.where(mat == 1, MAT1, 0)
+    headers["column_bytes"], headers["tile"] = kb0 * 256, tile
+    headers["part_bytes"] = part_slot * 128
     same_next = np.concatenate((owner[1:] == owner[:-1], [False]))
     headers["next_stage"] = np.where(same_next, np.concatenate((stage[1:], [0])), NO_STAGE)
     ahead = index + ring_depth
     valid = ahead < count
     ahead_owner = np.where(valid, owner[np.minimum(ahead, count - 1)], -1)
-    headers["ahead_size16"] = np.where(ahead_owner == owner, size16[np.minimum(ahead, count - 1)], 0)
+    headers["ahead_bytes"] = np.where(ahead_owner == owner, size16[np.minimum(ahead, count - 1)] * 16, 0)
 
     starts = np.zeros(ctas * WARPS, dtype=START_DTYPE)
     starts["first_stage"] = NO_STAGE
@@ -273,8 +281,9 @@ def layout_streams(shapes: list[GemvShape], stage_count: int, ctas: int, ring_de
     if offset16[-1] + size16[-1] >= 2 ** 32:
         raise ValueError("the stream exceeds 64 GiB")
     return StreamLayout(
-        ctas=ctas, ring_depth=ring_depth, stage_count=stage_count, table=table, starts=starts, headers=headers,
-        piece_offset16=offset16, piece_cta=cta, piece_warp=warp, stream_bytes=int((offset16[-1] + size16[-1]) * 16),
+        ctas=ctas, ring_depth=ring_depth, stage_count=stage_count, table=table, duties=duties, starts=starts,
+        headers=headers, piece_stage=stage, piece_mat=mat, piece_kb0=kb0, piece_offset16=offset16, piece_cta=cta,
+        piece_warp=warp, stream_bytes=int((offset16[-1] + size16[-1]) * 16),
     )
 
 
@@ -289,7 +298,7 @@ def fill_stream(layout: StreamLayout, shapes: list[GemvShape], weights: dict[int
     per_block = BLOCK_BYTES // 16
     headers = layout.headers
     for shape in shapes:
-        selected = np.nonzero(headers["stage"] == shape.stage)[0]
+        selected = np.nonzero(layout.piece_stage == shape.stage)[0]
         if len(selected) == 0:
             continue
         tiles, nb = -(-shape.n_rows // 16), shape.K // 128
@@ -299,9 +308,9 @@ def fill_stream(layout: StreamLayout, shapes: list[GemvShape], weights: dict[int
         counts = headers["nblocks"][selected].astype(np.int64)
         repeat = np.repeat(np.arange(len(selected)), counts)
         within = np.arange(counts.sum()) - np.repeat(np.cumsum(counts) - counts, counts)
-        source = ((headers["mat"][selected][repeat].astype(np.int64) * tiles
-                   + tile0[repeat] + headers["tile"][selected][repeat]) * nb
-                  + headers["kb0"][selected][repeat] + within)
+        source = ((layout.piece_mat[selected][repeat] * tiles + tile0[repeat]
+                   + headers["tile"][selected][repeat].astype(np.int64)) * nb
+                  + layout.piece_kb0[selected][repeat] + within)
         target = layout.piece_offset16[selected][repeat] + 1 + within * per_block
         lanes = torch.arange(per_block, device=device)
         source_rows = (torch.from_numpy(source).to(device)[:, None] * per_block + lanes).reshape(-1)
@@ -418,7 +427,7 @@ _STREAM_CACHE_ENTRIES = 4
 
 
 def device_stream(program, tensors: dict, device: torch.device, ctas: int, ring_depth: int):
-    """``(layout, stream, table, starts)`` on ``device`` for the program's packed weights.
+    """``(layout, stream, table, starts, duties)`` on ``device`` for the program's packed weights.
 
     Laying out a stream costs a pass over every packed weight, and the result depends only on
     the weights and the grid, so programs over the same weights (the buckets of one model, the
@@ -440,15 +449,16 @@ def device_stream(program, tensors: dict, device: torch.device, ctas: int, ring_
     hit = _STREAMS.get(key)
     if hit is not None:
         _STREAMS[key] = _STREAMS.pop(key)  # most recently used last
-        return hit[:4]
+        return hit[:5]
     layout = layout_streams(shapes, len(program.stages) + 1, ctas, ring_depth)
     stream = fill_stream(layout, shapes, weights, layout.table, device)
     table = torch.from_numpy(layout.table.view(np.int32).copy()).to(device)
     starts = torch.from_numpy(layout.starts.view(np.uint8).copy()).to(device)
-    _STREAMS[key] = (layout, stream, table, starts, weights)
+    duties = torch.from_numpy(layout.duties.view(np.int32).copy()).to(device)
+    _STREAMS[key] = (layout, stream, table, starts, duties, weights)
     while len(_STREAMS) > _STREAM_CACHE_ENTRIES:
         _STREAMS.pop(next(iter(_STREAMS)))
-    return layout, stream, table, starts
+    return layout, stream, table, starts, duties
 
 
 def launch(args: "N.StreamStepArgs", epoch: int, trace: torch.Tensor | None = None) -> None:

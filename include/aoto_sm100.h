@@ -561,20 +561,28 @@ int64_t aoto_sm100_stamped_bytes(int64_t count);
 
 #define AOTO_PIECE_SEG_END 1  /* last piece of this warp's share of the tile                      */
 #define AOTO_PIECE_WHOLE 2    /* the share is the whole tile: the warp finishes it by itself      */
-#define AOTO_PIECE_FINISHER 4 /* the share holds the tile's last block: the warp sums the parts   */
+#define AOTO_PIECE_MAT1 4     /* the blocks belong to the second matrix of the paired form        */
 
+/* 16 bytes in front of the blocks of every piece, in the form the kernel consumes them. */
 typedef struct aoto_stream_piece {
-  uint16_t stage;        /* stage this piece belongs to                                            */
   uint16_t next_stage;   /* stage of the warp's next piece, AOTO_STREAM_NO_STAGE after the last    */
-  uint16_t tile;         /* tile, counted from the first tile the CTA owns in this stage           */
-  uint16_t kb0;          /* first 128-column block                                                 */
   uint8_t nblocks;       /* 1..AOTO_STREAM_PIECE_BLOCKS                                            */
-  uint8_t mat;           /* 0, or 1 for the second matrix of the paired form                       */
   uint8_t flags;         /* AOTO_PIECE_*                                                           */
-  uint8_t nparts;        /* FINISHER: shares the tile was cut into                                 */
-  uint16_t part_slot;    /* slot of this share's partial sums; a tile's slots are consecutive      */
-  uint16_t ahead_size16; /* size / 16 of the piece `ring_depth` pieces later in this stream, 0 = none */
+  uint32_t column_bytes; /* 256 * (first 128-column block): where the blocks' columns start in the
+                            staged row                                                             */
+  uint16_t part_bytes;   /* SEG_END: 128 * (slot of this share's partial sums). Shares of a tile cut
+                            across warps have consecutive slots below AOTO_STREAM_PART_SLOTS; a whole
+                            tile uses slot AOTO_STREAM_PART_SLOTS + warp                            */
+  uint16_t tile;         /* tile, counted from the first tile the CTA owns in this stage           */
+  uint32_t ahead_bytes;  /* size of the piece `ring_depth` pieces later in this stream, 0 = none   */
 } aoto_stream_piece;
+
+/*
+ * One entry per (stage, CTA, warp): the tile shared between warps that this warp finishes once
+ * all shares have met (it holds the tile's last block), or 0.
+ */
+#define AOTO_STREAM_DUTY(tile, first_slot, nparts) \
+  ((uint32_t)(tile) | 0x8000u | ((uint32_t)(first_slot) << 16) | ((uint32_t)(nparts) << 24))
 
 typedef struct aoto_stream_warp_start {
   uint32_t offset16;     /* where the warp's stream starts in `stream`, in units of 16 bytes       */
@@ -607,6 +615,7 @@ typedef struct aoto_stream_stage {
 typedef struct aoto_stream_step_args {
   const aoto_stream_stage* stages;      /* device array [stage_count]                              */
   const uint32_t* cta_table;            /* device [stage_count * ctas], AOTO_STREAM_CTA_ENTRY      */
+  const uint32_t* duties;               /* device [stage_count * ctas * AOTO_STREAM_WARPS], AOTO_STREAM_DUTY */
   const aoto_stream_warp_start* starts; /* device [ctas * AOTO_STREAM_WARPS]                       */
   const void* stream;                   /* device, 16-byte aligned                                 */
   int64_t stream_bytes;
@@ -637,7 +646,8 @@ typedef struct aoto_stream_step_args {
   int32_t* status;
   void* scratch;                        /* per-CTA maxima of the ARGMAX stage: 16 bytes per CTA    */
   int64_t scratch_bytes;
-  uint64_t* trace;                      /* optional, uint64[stage_count * 8], as for decode_step   */
+  uint64_t* trace;                      /* optional, uint64[stage_count * 8]: CTA 0's SM cycle counter
+                                           (%clock64) at the eight points decode_step marks          */
 } aoto_stream_step_args;
 
 int aoto_sm100_stream_step(const aoto_stream_step_args* args, void* stream);

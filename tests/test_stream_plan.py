@@ -6,7 +6,7 @@ piece after piece, headers telling what a piece is and how large the piece ``rin
 ahead will be - decodes every block by the layout the C header documents, multiplies, and
 compares with the exact product of the same packed weights. It also checks the partition
 itself: every block of every stage is multiplied exactly once, partial-sum slots of a tile are
-consecutive and the warp with the tile's last block finishes it.
+consecutive and the warp with the tile's last block has the duty of finishing it.
 """
 
 import numpy as np
@@ -46,7 +46,6 @@ def run_stage(layout, stream: np.ndarray, stage: int, shape: sp.GemvShape, x: np
         entry = int(layout.table[stage, cta])
         tile0, count, shared = entry & 0xFFFF, (entry >> 16) & 0x7FFF, entry >> 31
         parts: dict[int, np.ndarray] = {}
-        duties = []
         for warp in range(sp.WARPS):
             state = cursors[(cta, warp)]
             acc = np.zeros((2, 16))
@@ -54,36 +53,47 @@ def run_stage(layout, stream: np.ndarray, stage: int, shape: sp.GemvShape, x: np
                 assert count > 0, "a CTA without tiles has no pieces"
                 at = state["offset"]
                 header = stream[at: at + 16].view(sp.PIECE_DTYPE)[0]
-                assert header["stage"] == stage
                 size = 16 + int(header["nblocks"]) * sp.BLOCK_BYTES
                 assert state["sizes"].pop(0) == size  # what the ring was told to fetch
+                flags = int(header["flags"])
+                mat = 1 if flags & sp.MAT1 else 0
+                assert int(header["column_bytes"]) % 256 == 0
                 for b in range(int(header["nblocks"])):
                     block = stream[at + 16 + b * sp.BLOCK_BYTES: at + 16 + (b + 1) * sp.BLOCK_BYTES]
-                    kb = int(header["kb0"]) + b
-                    acc[int(header["mat"])] += block_weights(block) @ x[kb * 128:(kb + 1) * 128]
-                    covered[int(header["mat"]), tile0 + int(header["tile"]), kb] += 1
-                if header["ahead_size16"]:
-                    state["sizes"].append(int(header["ahead_size16"]) * 16)
+                    kb = int(header["column_bytes"]) // 256 + b
+                    acc[mat] += block_weights(block) @ x[kb * 128:(kb + 1) * 128]
+                    covered[mat, tile0 + int(header["tile"]), kb] += 1
+                if header["ahead_bytes"]:
+                    state["sizes"].append(int(header["ahead_bytes"]))
                 state["offset"] += size
                 state["next_stage"] = int(header["next_stage"])
-                flags = int(header["flags"])
                 if flags & sp.SEG_END:
-                    tile = tile0 + int(header["tile"])
                     assert int(header["tile"]) < count
+                    slot, rest = divmod(int(header["part_bytes"]), 128)
+                    assert rest == 0 and slot not in parts
+                    parts[slot] = acc.copy()
                     if flags & sp.WHOLE:
+                        assert slot == sp.PART_SLOTS + warp  # the warp's own slot
+                        tile = tile0 + int(header["tile"])
                         result[:, tile * 16:(tile + 1) * 16] = acc[: shape.mats]
+                        del parts[slot]
                     else:
-                        assert shared and int(header["part_slot"]) < sp.PART_SLOTS
-                        assert int(header["part_slot"]) not in parts
-                        parts[int(header["part_slot"])] = acc.copy()
-                        if flags & sp.FINISHER:
-                            duties.append((tile, int(header["part_slot"]) - (int(header["nparts"]) - 1), int(header["nparts"])))
+                        assert shared and slot < sp.PART_SLOTS
                     acc = np.zeros((2, 16))
             assert not acc.any(), "a share ended without SEG_END"
-        for tile, first, nparts in duties:  # after the CTA barrier
-            total = sum(parts[first + i] for i in range(nparts))
+        finished = 0
+        for warp in range(sp.WARPS):  # after the CTA barrier: every warp looks up its duty
+            duty = int(layout.duties[stage, cta, warp])
+            if duty == 0:
+                continue
+            assert shared and duty & 0x8000
+            tile, first, nparts = tile0 + (duty & 0x7FFF), (duty >> 16) & 0xFF, duty >> 24
+            total = sum(parts.pop(first + i) for i in range(nparts))
             result[:, tile * 16:(tile + 1) * 16] = total[: shape.mats]
-        assert len(duties) <= sp.WARPS
+            finished += 1
+        assert not parts, "every partial sum belongs to a tile somebody finishes"
+        if not shared:
+            assert finished == 0
     assert (covered == 1).all(), "every block of the stage is multiplied exactly once"
     return result
 
@@ -132,14 +142,14 @@ def test_stage_partition_keeps_the_critical_path_short():
 
     assert sp.tiles_per_cta(72, 7, 148) == 2      # q/k/v of the 0.5B shape: 14 of 16 warps, one block each
     assert sp.tiles_per_cta(56, 38, 148) == 1     # down: 38 blocks over 16 warps is already three a warp
-    table, pieces = sp.plan_stage(0, 304, 7, 2, 148, 0)  # gate/up: 304 paired tiles over 148 CTAs
+    table, _, pieces = sp.plan_stage(0, 304, 7, 2, 148, 0)  # gate/up: 304 paired tiles over 148 CTAs
     counts = (table >> 16) & 0x7FFF
     assert counts.sum() == 304 and counts.max() == 3 and counts.min() == 2
     per_warp = {}
     for cta, warp, *_rest in pieces:
         per_warp[(cta, warp)] = per_warp.get((cta, warp), 0) + _rest[3]
     assert max(per_warp.values()) == 3  # ceil(42 / 16)
-    table, _ = sp.plan_stage(0, 9496, 7, 1, 148, 0)  # LM head
+    table, _, _ = sp.plan_stage(0, 9496, 7, 1, 148, 0)  # LM head
     counts = (table >> 16) & 0x7FFF
     assert counts.sum() == 9496 and counts.max() - counts.min() <= 1
 

@@ -58,8 +58,10 @@ def test_streamed_and_in_place_kernels_agree(cuda, layers, prompt_length, new_to
         assert rel_err(streamed.final_cache(steps), in_place.final_cache(steps)) < REL_TOL
     # the window is moved bit for bit: every slot but the last of the next cache is a copy
     streamed.run(token, cache, prompt_length, 1)
+    in_place.run(token, cache, prompt_length, 1)
     assert torch.equal(streamed.final_cache(1)[:, :, :, :, :-1], cache[:, :, :, :, 1:])
-    assert torch.equal(streamed.final_cache(1), in_place.final_cache(1))
+    # the appended slot is a projection result: the kernels may round it an ulp apart
+    assert rel_err(streamed.final_cache(1)[:, :, :, :, -1], in_place.final_cache(1)[:, :, :, :, -1]) < REL_TOL
 
 
 def test_streamed_kernel_matches_oracle_step_by_step(cuda):
