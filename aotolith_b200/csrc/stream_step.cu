@@ -21,7 +21,6 @@ constexpr int SS_THREADS = SS_WARPS * 32;
 constexpr int SS_BLOCK_BYTES = AOTO_STREAM_BLOCK_BYTES;
 constexpr int SS_SLOT_BYTES = AOTO_STREAM_SLOT_BYTES;
 constexpr int SS_MAX_K = 16384;
-constexpr int SS_MAX_CHUNKS = SS_MAX_K / 8 / SS_THREADS;  // 8-value chunks of the input row per thread
 constexpr int SS_POLL_LIMIT = 1 << 20;  // rounds of a bounded poll (each is at least one L2 round trip)
 constexpr int SS_PART_SLOTS = AOTO_STREAM_PART_SLOTS + SS_WARPS;  // shared tiles, then one private slot per warp
 constexpr int SS_PART_BYTES = 128;      // [matrix][row] floats of one share
@@ -60,6 +59,7 @@ __host__ __device__ inline SSLayout ss_layout(int stage_count, int max_k, int de
   if (attention_bytes > work_bytes) work_bytes = attention_bytes;
   off += ss_align(work_bytes, 16);
   L.red = off; off += 64 * 4;
+  L.rotary = off; off += has_attention ? (uint32_t)head_dim * 4 : 0;  // cos row, sin row of the step's position
   L.rotary = off; off += has_attention ? (uint32_t)head_dim * 4 : 0;  // cos row, sin row of the step's position
   L.keys_per_warp = has_attention ? (capacity + SS_WARPS - 1) / SS_WARPS : 0;
   L.kv = off; off += has_attention ? (uint32_t)SS_WARPS * 2 * L.keys_per_warp * head_dim * 2 : 0;
@@ -167,15 +167,14 @@ __device__ __forceinline__ float ss_warp_max(float v) {
   return __int_as_float(key);
 }
 
-__device__ __forceinline__ unsigned long long ss_timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
-  return t;
-}
-
 // ---------------------------------------------------------------------------
 // kernel state
 // ---------------------------------------------------------------------------
+// The SM's instruction cache holds 32 KB (measured on this part: a loop body of 2048
+// instructions issues at 1.0 cycles per instruction, one of 2560 at 2.7, and every jump into
+// code that is not resident costs an L2 round trip). A step walks the same code ~120 times,
+// so the whole kernel is kept inside the cache: one code path per stage kind, loops instead of
+// unrolled copies, approximate intrinsics where the result is rounded to bf16 anyway.
 struct SSParams {
   aoto_stream_step_args a;
   SSLayout L;
@@ -192,19 +191,24 @@ struct WarpStream {
   int in_flight;                    // pieces requested and not yet multiplied
 };
 
-__device__ __forceinline__ void ss_trace(const SSParams& p, int stage, int which) {
-  if (p.a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.a.trace[stage * 8 + which] = ss_timer_ns();
+// Every CTA's per-stage timeline on the one clock all SMs share (slow to read: the traced
+// instantiation of the kernel is for diagnosis, never for timing).
+__device__ __noinline__ void ss_trace(const SSParams& p, int stage, int which) {
+  if (threadIdx.x != 0) return;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  p.a.trace[((size_t)blockIdx.x * p.a.stage_count + stage) * 8 + which] = t;
 }
 
-__device__ __forceinline__ void ss_give_up(const SSParams& p, int stage) {
+__device__ __noinline__ void ss_give_up(const SSParams& p, int stage) {
   if (threadIdx.x == 0) atomicCAS(p.a.status, 0, stage + 1);
 }
 
-// Request one piece of `bytes` into the warp's next slot (lane 0 only issues).
+// Request one piece of `bytes` into the warp's next slot (lane 0 only issues). The slot was
+// only READ through the generic proxy and __syncwarp ordered those reads before this point: a
+// write by the async proxy needs no proxy fence after reads.
 __device__ __forceinline__ void ss_request(const SSParams& p, WarpStream& ws, uint32_t bytes, int lane) {
   if (lane == 0) {
-    // the slot was only READ through the generic proxy, and __syncwarp ordered those reads before
-    // this point: a write by the async proxy needs no proxy fence after reads
     const uint32_t bar = ws.bars + ws.issue_slot * 8;
     ss_mbar_expect_tx(bar, bytes);
     ss_bulk_load(ws.ring + ws.issue_slot * SS_SLOT_BYTES,
@@ -215,65 +219,36 @@ __device__ __forceinline__ void ss_request(const SSParams& p, WarpStream& ws, ui
   ws.in_flight += 1;
 }
 
-// Leave nothing in flight into this warp's ring (on the way out after a failure).
-__device__ __forceinline__ void ss_drain(const SSParams& p, WarpStream& ws) {
-  while (ws.in_flight > 0) {
-    ss_mbar_wait(ws.bars + ws.slot * 8, ws.parity);
-    ws.slot += 1;
-    if (ws.slot == (uint32_t)p.a.ring_depth) { ws.slot = 0; ws.parity ^= 1u; }
-    ws.in_flight -= 1;
-  }
-}
-
 // ---------------------------------------------------------------------------
-// the blocks of a piece, from shared memory
+// one 16 x 128 block from shared memory
 // ---------------------------------------------------------------------------
-// `block` is the shared address of the first block, `xb` of this lane's B fragments of the
-// blocks' columns (the staged row in fragment order: 256 bytes a block), `sums` of the blocks'
-// pairs of 136*sum(x) values. A block is two accumulator chains of four mma (one per scale
-// group); the NB blocks of a piece are issued interleaved, so up to six chains are in flight
-// and the latency of one mma is hidden by the others. Returns the contributions to rows g (lo)
-// and g + 8 (hi), identical on the four lanes of a quad.
+// `block` is the shared address of the block, `xb` of this lane's B fragments of the block's
+// columns (the staged row in fragment order: 256 bytes a block), `sums` of the block's pair of
+// 136*sum(x) values. The two scale groups of a block are independent accumulator chains of
+// four mma each, issued alternately. Returns the contributions to rows g (lo) and g + 8 (hi),
+// identical on the four lanes of a quad.
 #define SS_NIB(word, shift) ((((word) >> (shift)) & 0x000F000Fu) ^ 0x43084308u)
 
-template <int NB>
-__device__ __forceinline__ void ss_blocks(uint32_t block, uint32_t xb, uint32_t sums, int lane, float& lo, float& hi) {
-  const int g = lane >> 2;
-  uint32_t wl[NB][4], wh[NB][4], slo[NB], shi[NB];
-  float ca[NB][4], cb[NB][4];
-#pragma unroll
-  for (int b = 0; b < NB; ++b) {
-    const uint32_t at = block + (uint32_t)b * SS_BLOCK_BYTES;
-    const uint4 l = ss_lds128(at + (uint32_t)lane * 16);
-    const uint4 h = ss_lds128(at + 512 + (uint32_t)lane * 16);
-    wl[b][0] = l.x; wl[b][1] = l.y; wl[b][2] = l.z; wl[b][3] = l.w;
-    wh[b][0] = h.x; wh[b][1] = h.y; wh[b][2] = h.z; wh[b][3] = h.w;
-    slo[b] = ss_lds32(at + 1024 + (uint32_t)g * 4);
-    shi[b] = ss_lds32(at + 1024 + 32 + (uint32_t)g * 4);
-    const float2 off = ss_lds64f(sums + (uint32_t)b * 8);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { ca[b][i] = -off.x; cb[b][i] = -off.y; }
-  }
-#pragma unroll
-  for (int q = 0; q < 2; ++q) {  // words q (first scale group) and q + 2 (second) of every block
-#pragma unroll
-    for (int b = 0; b < NB; ++b) {
-      const uint4 ba = ss_lds128(xb + (uint32_t)b * 256 + (uint32_t)q * 64);
-      const uint4 bb = ss_lds128(xb + (uint32_t)b * 256 + (uint32_t)(q + 2) * 64);
-      const uint32_t la = wl[b][q], ha = wh[b][q], lb = wl[b][q + 2], hb = wh[b][q + 2];
-      ss_mma(ca[b], SS_NIB(la, 0), SS_NIB(ha, 0), SS_NIB(la, 4), SS_NIB(ha, 4), ba.x, ba.y);
-      ss_mma(cb[b], SS_NIB(lb, 0), SS_NIB(hb, 0), SS_NIB(lb, 4), SS_NIB(hb, 4), bb.x, bb.y);
-      ss_mma(ca[b], SS_NIB(la, 8), SS_NIB(ha, 8), SS_NIB(la, 12), SS_NIB(ha, 12), ba.z, ba.w);
-      ss_mma(cb[b], SS_NIB(lb, 8), SS_NIB(hb, 8), SS_NIB(lb, 12), SS_NIB(hb, 12), bb.z, bb.w);
-    }
-  }
-  lo = 0.f;
-  hi = 0.f;
-#pragma unroll
-  for (int b = 0; b < NB; ++b) {
-    lo += fmaf(bf16x2_lo(slo[b]), ca[b][0], bf16x2_hi(slo[b]) * cb[b][0]);
-    hi += fmaf(bf16x2_lo(shi[b]), ca[b][2], bf16x2_hi(shi[b]) * cb[b][2]);
-  }
+__device__ __forceinline__ void ss_block(uint32_t block, uint32_t xb, uint32_t sums, int lane, float& lo, float& hi) {
+  const uint4 l = ss_lds128(block + (uint32_t)lane * 16);
+  const uint4 h = ss_lds128(block + 512 + (uint32_t)lane * 16);
+  const uint32_t slo = ss_lds32(block + 1024 + (uint32_t)(lane >> 2) * 4);
+  const uint32_t shi = ss_lds32(block + 1056 + (uint32_t)(lane >> 2) * 4);
+  const float2 off = ss_lds64f(sums);
+  float ca[4] = {-off.x, -off.x, -off.x, -off.x};
+  float cb[4] = {-off.y, -off.y, -off.y, -off.y};
+  const uint4 b0 = ss_lds128(xb), b2 = ss_lds128(xb + 128);
+  ss_mma(ca, SS_NIB(l.x, 0), SS_NIB(h.x, 0), SS_NIB(l.x, 4), SS_NIB(h.x, 4), b0.x, b0.y);
+  ss_mma(cb, SS_NIB(l.z, 0), SS_NIB(h.z, 0), SS_NIB(l.z, 4), SS_NIB(h.z, 4), b2.x, b2.y);
+  ss_mma(ca, SS_NIB(l.x, 8), SS_NIB(h.x, 8), SS_NIB(l.x, 12), SS_NIB(h.x, 12), b0.z, b0.w);
+  ss_mma(cb, SS_NIB(l.z, 8), SS_NIB(h.z, 8), SS_NIB(l.z, 12), SS_NIB(h.z, 12), b2.z, b2.w);
+  const uint4 b1 = ss_lds128(xb + 64), b3 = ss_lds128(xb + 192);
+  ss_mma(ca, SS_NIB(l.y, 0), SS_NIB(h.y, 0), SS_NIB(l.y, 4), SS_NIB(h.y, 4), b1.x, b1.y);
+  ss_mma(cb, SS_NIB(l.w, 0), SS_NIB(h.w, 0), SS_NIB(l.w, 4), SS_NIB(h.w, 4), b3.x, b3.y);
+  ss_mma(ca, SS_NIB(l.y, 8), SS_NIB(h.y, 8), SS_NIB(l.y, 12), SS_NIB(h.y, 12), b1.z, b1.w);
+  ss_mma(cb, SS_NIB(l.w, 8), SS_NIB(h.w, 8), SS_NIB(l.w, 12), SS_NIB(h.w, 12), b3.z, b3.w);
+  lo = fmaf(bf16x2_lo(slo), ca[0], bf16x2_hi(slo) * cb[0]);
+  hi = fmaf(bf16x2_lo(shi), ca[2], bf16x2_hi(shi) * cb[2]);
 }
 
 // ---------------------------------------------------------------------------
@@ -284,177 +259,178 @@ struct Best {
   int index;
 };
 
-// Stage the input row in fragment order. Chunk c holds columns 8c..8c+7: k step (c & 15) >> 1 of
-// block c >> 4, slots 0-7 or 8-15 of that step. Lane t of a quad wants, per pair of steps q, the
-// 16 bytes {b0(2q), b1(2q), b0(2q+1), b1(2q+1)} where b0 = slots (2t, 2t+1), b1 = (2t+8, 2t+9).
-__device__ __forceinline__ void ss_store_chunk(uint32_t xs, int c, uint32_t p0, uint32_t p1, uint32_t p2, uint32_t p3) {
-  const uint32_t base = xs + (uint32_t)(c >> 4) * 256 + (uint32_t)((c & 15) >> 2) * 64 + (uint32_t)(c & 3) * 4;
-  ss_sts32(base, p0);
-  ss_sts32(base + 16, p1);
-  ss_sts32(base + 32, p2);
-  ss_sts32(base + 48, p3);
-}
-
-// Where chunk c (columns 8c..8c+7) of the staged row lives: the address of its first pair; the
-// other three pairs follow at 16-byte steps (see ss_store_chunk).
+// Where chunk c (columns 8c..8c+7) of the staged row lives: k step (c & 15) >> 1 of block
+// c >> 4, slots 0-7 or 8-15 of that step. Lane t of a quad wants, per pair of steps q, the 16
+// bytes {b0(2q), b1(2q), b0(2q+1), b1(2q+1)} where b0 = slots (2t, 2t+1), b1 = (2t+8, 2t+9):
+// the chunk's four pairs go to this address and the three 16-byte steps after it.
 __device__ __forceinline__ uint32_t ss_chunk_address(uint32_t xs, int c) {
   return xs + (uint32_t)(c >> 4) * 256 + (uint32_t)((c & 15) >> 2) * 64 + (uint32_t)(c & 3) * 4;
+}
+
+// The CTA's largest logit (first index on ties) for the pick stage: once per step, out of line.
+__device__ __noinline__ void ss_publish_best(const SSParams& p, float bv, int bi, unsigned char* smem) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float* sv = reinterpret_cast<float*>(smem + p.L.red);
+  int* si = reinterpret_cast<int*>(sv + 32);
+#pragma unroll 1
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  __syncthreads();  // the finishers' maxima are in; `red` is free of the norm statistic
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (tid == 0) {
+#pragma unroll 1
+    for (int w = 1; w < SS_WARPS; ++w)
+      if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+    unsigned char* payload = reinterpret_cast<unsigned char*>(p.a.scratch);
+    ss_st_stamped(payload + (size_t)blockIdx.x * 16, __float_as_uint(bv), p.a.epoch);
+    ss_st_stamped(payload + (size_t)blockIdx.x * 16 + 8, (uint32_t)bi, p.a.epoch);
+  }
 }
 
 // Returns false when a wait ran out (every thread of the CTA gets the same answer).
 //
 // Only the work that must be done by every warp is done by every warp: the row is fetched,
 // normalised and staged by the warps that own chunks of it (four for K = 896), a tile shared
-// between warps is finished by the one warp whose duty it is, and a warp with nothing to do
-// in a phase waits at the barrier and leaves the issue slots to the others.
+// between warps is finished by the one warp whose duty it is, and a warp with nothing to do in
+// a phase waits at the barrier and leaves the issue slots to the others.
 template <bool TRACE>
-__device__ bool ss_gemv(const SSParams& p, const aoto_stream_stage& st, int stage_index, uint32_t entry,
-                        WarpStream& ws, Best& best, unsigned char* smem) {
+__device__ __forceinline__ bool ss_gemv(const SSParams& p, const aoto_stream_stage& st, int stage_index, uint32_t entry,
+                                        WarpStream& ws, Best& best, unsigned char* smem) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int g = lane >> 2, t = lane & 3;
   const int K = st.K, N = st.N;
   const uint32_t epoch = p.a.epoch;
+  const uint32_t stage_flags = st.flags, addend_mode = st.addend_mode;
   const int tile0 = (int)(entry & 0xFFFFu);
   const bool shares_tiles = (entry >> 31) != 0;
   const uint32_t xs = ss_smem(smem + p.L.xs), xsum = ss_smem(smem + p.L.xsum), part = ss_smem(smem + p.L.part);
-  float* stat = reinterpret_cast<float*>(smem + p.L.red) + (stage_index & 1) * 32;  // stages alternate halves
+  const uint32_t stat = ss_smem(smem + p.L.red) + (uint32_t)(stage_index & 1) * 128;  // stages alternate halves
   if (TRACE) ss_trace(p, stage_index, 0);
 
   long long gather_row = 0;
-  if ((st.flags & AOTO_STAGE_FLAG_X_GATHER) || st.addend_mode == AOTO_STAGE_ADDEND_GATHER) {
+  if ((stage_flags & AOTO_STAGE_FLAG_X_GATHER) || addend_mode == AOTO_STAGE_ADDEND_GATHER) {
     gather_row = *reinterpret_cast<const volatile long long*>(p.a.x_index);
-    if (gather_row < 0) gather_row = 0;
-    if (gather_row >= p.a.x_rows) gather_row = p.a.x_rows - 1;
+    gather_row = max(0ll, min(gather_row, (long long)p.a.x_rows - 1));
   }
-  // which shared tile this warp finishes after the multiply (requested now, needed much later)
+  // which shared tile this warp finishes after the multiply, and that tile's addend: both loads
+  // are off the critical path here (the row is still being fetched) and on it later
   uint32_t duty = 0;
-  if (shares_tiles)
-    duty = ldg_nc_u32(p.a.duties + ((size_t)stage_index * gridDim.x + blockIdx.x) * SS_WARPS + warp);
+  if (shares_tiles) duty = ldg_nc_u32(p.a.duties + ((size_t)stage_index * gridDim.x + blockIdx.x) * SS_WARPS + warp);
 
   // ---- the input row ----
+  // Pass 1 (the warps that own chunks of the row): fetch the chunk, park it in its place in the
+  // staged row, add up its squares. Pass 2, after the warps' sums have met: normalise the chunk
+  // in place (if the stage has a norm) and publish the group sums the multiply subtracts.
   const int chunks = K >> 3;
   const uint4* wv = reinterpret_cast<const uint4*>(st.norm_weight);
   const bool has_norm = wv != nullptr;
   const bool stager = warp * 32 < chunks;
   const int per_thread = (chunks + SS_THREADS - 1) / SS_THREADS;
   bool failed = false;
-  uint4 nw0 = make_uint4(0u, 0u, 0u, 0u);
   if (stager) {
-    if (has_norm && tid < chunks) nw0 = ldg_nc_u4(wv + tid);  // does not depend on the row: requested first
     const unsigned char* words = reinterpret_cast<const unsigned char*>(st.x);
-    const uint4* gathered = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(st.x) + (size_t)gather_row * K);
-    float s0 = 0.f, s1 = 0.f;
+    const bool gathers = (stage_flags & AOTO_STAGE_FLAG_X_GATHER) != 0;
+    if (gathers) words += (size_t)gather_row * K * 2;
+    float squares = 0.f;
     int rounds = 0;
+#pragma unroll 1
+    for (int i = 0; i < per_thread; ++i) {
+      const int c = min(tid + i * SS_THREADS, chunks - 1);  // lanes past the row repeat its last chunk
+      uint4 raw;
+      if (gathers) {
+        raw = ldg_nc_u4(reinterpret_cast<const uint4*>(words) + c);
+      } else {
+        while (true) {
+          const uint4 a = ss_ld_stamped_pair(words + (size_t)c * 32), b = ss_ld_stamped_pair(words + (size_t)c * 32 + 16);
+          raw = make_uint4(a.x, a.z, b.x, b.z);
+          if (__all_sync(0xffffffffu, a.y == epoch && a.w == epoch && b.y == epoch && b.w == epoch)) break;
+          // a CTA that gave up elsewhere ends every other wait early
+          if (++rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0)) { failed = true; break; }
+        }
+      }
+      const uint32_t at = ss_chunk_address(xs, c);
+      ss_sts32(at, raw.x); ss_sts32(at + 16, raw.y); ss_sts32(at + 32, raw.z); ss_sts32(at + 48, raw.w);
+      if (tid + i * SS_THREADS < chunks) {
+        squares = fmaf(bf16x2_lo(raw.x), bf16x2_lo(raw.x), squares); squares = fmaf(bf16x2_hi(raw.x), bf16x2_hi(raw.x), squares);
+        squares = fmaf(bf16x2_lo(raw.y), bf16x2_lo(raw.y), squares); squares = fmaf(bf16x2_hi(raw.y), bf16x2_hi(raw.y), squares);
+        squares = fmaf(bf16x2_lo(raw.z), bf16x2_lo(raw.z), squares); squares = fmaf(bf16x2_hi(raw.z), bf16x2_hi(raw.z), squares);
+        squares = fmaf(bf16x2_lo(raw.w), bf16x2_lo(raw.w), squares); squares = fmaf(bf16x2_hi(raw.w), bf16x2_hi(raw.w), squares);
+      }
+    }
+    squares = warp_sum(squares);
+    if (lane == 0) ss_stsf(stat + (uint32_t)warp * 4, squares);
+  } else if (lane == 0) {
+    ss_stsf(stat + (uint32_t)warp * 4, 0.f);
+  }
+  float duty_addend = 0.f;
+  bool alive = true;
+  if (duty != 0 && lane < 16 && addend_mode != AOTO_STAGE_ADDEND_NONE) {
+    const int n = min((tile0 + (int)(duty & 0x7FFFu)) * 16 + lane, N - 1);
+    if (addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
+      // an intermediate that was produced stages ago: its poll is a formality
+      const unsigned char* at = reinterpret_cast<const unsigned char*>(st.addend) + (size_t)(n >> 1) * 8;
+      uint2 w = ss_ld_stamped(at);
+      for (int polls = 0; w.y != epoch && alive; ++polls) {
+        if (polls > SS_POLL_LIMIT) alive = false;
+        w = ss_ld_stamped(at);
+      }
+      duty_addend = (n & 1) ? bf16x2_hi(w.x) : bf16x2_lo(w.x);
+    } else {
+      const size_t row = addend_mode == AOTO_STAGE_ADDEND_GATHER ? (size_t)gather_row * N : 0;
+      duty_addend = ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + row + n);
+    }
+  }
+  if (__syncthreads_or(failed)) {  // the warps' sums of squares meet
+    ss_give_up(p, stage_index);
+    return false;
+  }
+  if (TRACE) ss_trace(p, stage_index, 1);
+  if (stager) {
+    float inv = 1.f;
+    if (has_norm) {
+      // the sixteen sums in a fixed order (a tree: the result does not depend on timing)
+      const float4 a = ss_lds128f(stat), b = ss_lds128f(stat + 16), c4 = ss_lds128f(stat + 32), d = ss_lds128f(stat + 48);
+      const float total = (((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w))) +
+                          (((c4.x + c4.y) + (c4.z + c4.w)) + ((d.x + d.y) + (d.z + d.w)));
+      inv = rsqrtf(__fdividef(total, (float)K) + st.rms_norm_eps);
+    }
 #pragma unroll 1
     for (int i = 0; i < per_thread; ++i) {
       const int c = tid + i * SS_THREADS;
       const bool mine = c < chunks;
-      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-      if (st.flags & AOTO_STAGE_FLAG_X_GATHER) {
-        if (mine) raw = ldg_nc_u4(gathered + c);
-      } else {
-        const size_t at = (size_t)min(c, chunks - 1) * 32;
-        while (!failed) {
-          const uint4 a = ss_ld_stamped_pair(words + at), b = ss_ld_stamped_pair(words + at + 16);
-          const bool ready = a.y == epoch && a.w == epoch && b.y == epoch && b.w == epoch;
-          if (ready && mine) raw = make_uint4(a.x, a.z, b.x, b.z);
-          if (__all_sync(0xffffffffu, ready)) break;
-          ++rounds;
-          // a CTA that gave up elsewhere ends every other wait early
-          if (rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0)) failed = true;
-        }
-      }
-      float f[8];
-      unpack8(raw, f);
+      const uint32_t at = ss_chunk_address(xs, min(c, chunks - 1));
+      uint4 o = make_uint4(ss_lds32(at), ss_lds32(at + 16), ss_lds32(at + 32), ss_lds32(at + 48));
       if (has_norm) {
-        s0 = fmaf(f[0], f[0], s0); s1 = fmaf(f[1], f[1], s1);
-        s0 = fmaf(f[2], f[2], s0); s1 = fmaf(f[3], f[3], s1);
-        s0 = fmaf(f[4], f[4], s0); s1 = fmaf(f[5], f[5], s1);
-        s0 = fmaf(f[6], f[6], s0); s1 = fmaf(f[7], f[7], s1);
-        if (mine) ss_store_chunk(xs, c, raw.x, raw.y, raw.z, raw.w);  // raw: normalised in place below
-      } else {
-        if (mine) ss_store_chunk(xs, c, raw.x, raw.y, raw.z, raw.w);
-        // a group of 64 columns is eight consecutive chunks, i.e. eight consecutive lanes
-        float chunk_sum = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
-        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 1);
-        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 2);
-        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 4);
-        if (mine && (lane & 7) == 0) ss_stsf(xsum + (uint32_t)(c >> 3) * 4, 136.f * chunk_sum);
+        const uint4 w = ldg_nc_u4(wv + min(c, chunks - 1));
+        o.x = pack_bf16x2((bf16x2_lo(o.x) * inv) * bf16x2_lo(w.x), (bf16x2_hi(o.x) * inv) * bf16x2_hi(w.x));
+        o.y = pack_bf16x2((bf16x2_lo(o.y) * inv) * bf16x2_lo(w.y), (bf16x2_hi(o.y) * inv) * bf16x2_hi(w.y));
+        o.z = pack_bf16x2((bf16x2_lo(o.z) * inv) * bf16x2_lo(w.z), (bf16x2_hi(o.z) * inv) * bf16x2_hi(w.z));
+        o.w = pack_bf16x2((bf16x2_lo(o.w) * inv) * bf16x2_lo(w.w), (bf16x2_hi(o.w) * inv) * bf16x2_hi(w.w));
+        if (mine) { ss_sts32(at, o.x); ss_sts32(at + 16, o.y); ss_sts32(at + 32, o.z); ss_sts32(at + 48, o.w); }
       }
+      // the rounded values are what is multiplied and what is summed; a group of 64 columns is
+      // eight consecutive chunks, i.e. eight consecutive lanes
+      float chunk_sum = ((bf16x2_lo(o.x) + bf16x2_hi(o.x)) + (bf16x2_lo(o.y) + bf16x2_hi(o.y))) +
+                        ((bf16x2_lo(o.z) + bf16x2_hi(o.z)) + (bf16x2_lo(o.w) + bf16x2_hi(o.w)));
+      if (!mine) chunk_sum = 0.f;
+      chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 1);
+      chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 2);
+      chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 4);
+      if (mine && (lane & 7) == 0) ss_stsf(xsum + (uint32_t)(c >> 3) * 4, 136.f * chunk_sum);
     }
-    if (has_norm) {
-      const float ss = warp_sum(s0 + s1);
-      if (lane == 0) stat[warp] = ss;
-    }
-  } else if (has_norm && lane == 0) {
-    stat[warp] = 0.f;
   }
-  if (__syncthreads_or(failed)) {
-    ss_give_up(p, stage_index);
-    return false;
-  }
-  if (TRACE) { ss_trace(p, stage_index, 1); ss_trace(p, stage_index, 2); }
-  if (has_norm) {
-    if (stager) {
-      // the warps' sums in a fixed order (a tree: the result does not depend on timing)
-      const float4 a = *reinterpret_cast<const float4*>(stat), b = *reinterpret_cast<const float4*>(stat + 4);
-      const float4 c4 = *reinterpret_cast<const float4*>(stat + 8), d = *reinterpret_cast<const float4*>(stat + 12);
-      const float total = (((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w))) +
-                          (((c4.x + c4.y) + (c4.z + c4.w)) + ((d.x + d.y) + (d.z + d.w)));
-      const float inv = rsqrtf(total / (float)K + st.rms_norm_eps);
-#pragma unroll 1
-      for (int i = 0; i < per_thread; ++i) {
-        const int c = tid + i * SS_THREADS;
-        const bool mine = c < chunks;
-        const uint32_t at = ss_chunk_address(xs, min(c, chunks - 1));
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (mine) raw = make_uint4(ss_lds32(at), ss_lds32(at + 16), ss_lds32(at + 32), ss_lds32(at + 48));
-        const uint4 weights = i == 0 ? nw0 : (mine ? ldg_nc_u4(wv + c) : make_uint4(0u, 0u, 0u, 0u));
-        float f[8], w[8];
-        unpack8(raw, f);
-        unpack8(weights, w);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = (f[j] * inv) * w[j];
-        uint4 o;
-        o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
-        o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
-        unpack8(o, f);  // the rounded values are what is multiplied and what is summed
-        if (mine) ss_store_chunk(xs, c, o.x, o.y, o.z, o.w);
-        float chunk_sum = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
-        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 1);
-        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 2);
-        chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, 4);
-        if (mine && (lane & 7) == 0) ss_stsf(xsum + (uint32_t)(c >> 3) * 4, 136.f * chunk_sum);
-      }
-    }
-    __syncthreads();
-  }
+  __syncthreads();
   if (TRACE) ss_trace(p, stage_index, 3);
 
   // ---- the multiply, then (one site for both) the finishing of a tile ----
   const bool paired = st.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED;
-  const uint32_t xb = xs + (uint32_t)t * 16;
+  const uint32_t xb = xs + (uint32_t)(lane & 3) * 16;
   float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;  // [matrix][rows g, g + 8]
-  bool alive = true, met = false;
-  // The addend of row n: a bias, a row of the gathered table, or an intermediate that was
-  // produced stages ago (its poll is a formality).
-  auto addend_of = [&](int n) {
-    if (st.addend_mode == AOTO_STAGE_ADDEND_NONE || n >= N) return 0.f;
-    if (st.addend_mode == AOTO_STAGE_ADDEND_PLAIN) return ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + n);
-    if (st.addend_mode == AOTO_STAGE_ADDEND_GATHER)
-      return ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + (size_t)gather_row * N + n);
-    const unsigned char* at = reinterpret_cast<const unsigned char*>(st.addend) + (size_t)(n >> 1) * 8;
-    uint2 w = ss_ld_stamped(at);
-    for (int polls = 0; w.y != epoch; ++polls) {
-      if (polls > SS_POLL_LIMIT) { alive = false; break; }
-      w = ss_ld_stamped(at);
-    }
-    return (n & 1) ? bf16x2_hi(w.x) : bf16x2_lo(w.x);
-  };
-  float duty_addend = 0.f;
-  if (duty != 0 && lane < 16) duty_addend = addend_of((tile0 + (int)(duty & 0x7FFFu)) * 16 + lane);
-
-  bool first_piece = true;
+  bool met = false, first_piece = true;
+#pragma unroll 1
   while (true) {
     int finish_tile = -1, finish_parts = 0;
     uint32_t finish_first = 0;
@@ -471,8 +447,8 @@ __device__ bool ss_gemv(const SSParams& p, const aoto_stream_stage& st, int stag
 #pragma unroll 1
       for (int b = 0; b < nblocks; ++b) {
         float lo, hi;
-        ss_blocks<1>(slot + 16 + (uint32_t)b * SS_BLOCK_BYTES, xb + h.y + (uint32_t)b * 256,
-                     xsum + (h.y >> 5) + (uint32_t)b * 8, lane, lo, hi);
+        ss_block(slot + 16 + (uint32_t)b * SS_BLOCK_BYTES, xb + h.y + (uint32_t)b * 256, xsum + (h.y >> 5) + (uint32_t)b * 8,
+                 lane, lo, hi);
         lo_sum += lo;
         hi_sum += hi;
       }
@@ -486,21 +462,30 @@ __device__ bool ss_gemv(const SSParams& p, const aoto_stream_stage& st, int stag
       if (TRACE && first_piece) { ss_trace(p, stage_index, 4); first_piece = false; }
       if (flags & AOTO_PIECE_SEG_END) {
         // the share's sums go to its partial slot (a whole tile has a slot of the warp's own)
-        const uint32_t at = part + (h.z & 0xFFFFu);
-        if (t == 0) {
-          ss_stsf(at + (uint32_t)g * 4, acc0);
-          ss_stsf(at + (uint32_t)(g + 8) * 4, acc1);
-          if (paired) {
-            ss_stsf(at + 64 + (uint32_t)g * 4, acc2);
-            ss_stsf(at + 64 + (uint32_t)(g + 8) * 4, acc3);
-          }
+        const uint32_t at = part + (h.z & 0xFFFFu) + (uint32_t)(lane >> 2) * 4;
+        if ((lane & 3) == 0) {
+          ss_stsf(at, acc0);
+          ss_stsf(at + 32, acc1);
+          ss_stsf(at + 64, acc2);
+          ss_stsf(at + 96, acc3);
         }
         acc0 = acc1 = acc2 = acc3 = 0.f;
         if (flags & AOTO_PIECE_WHOLE) {
           finish_tile = tile0 + (int)(h.z >> 16);
-          finish_first = at;
+          finish_first = part + (h.z & 0xFFFFu);
           finish_parts = 1;
-          if (lane < 16) finish_addend = addend_of(finish_tile * 16 + lane);
+          if (lane < 16 && addend_mode != AOTO_STAGE_ADDEND_NONE) {
+            // whole tiles carry a residual only in large models, where the load hides behind other warps
+            const int n = min(finish_tile * 16 + lane, N - 1);
+            if (addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
+              const uint2 w = ss_ld_stamped(reinterpret_cast<const unsigned char*>(st.addend) + (size_t)(n >> 1) * 8);
+              if (w.y != epoch) alive = false;  // produced stages ago: absent means something gave up
+              finish_addend = (n & 1) ? bf16x2_hi(w.x) : bf16x2_lo(w.x);
+            } else {
+              const size_t row = addend_mode == AOTO_STAGE_ADDEND_GATHER ? (size_t)gather_row * N : 0;
+              finish_addend = ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + row + n);
+            }
+          }
         }
       }
     } else if (!met) {
@@ -508,10 +493,7 @@ __device__ bool ss_gemv(const SSParams& p, const aoto_stream_stage& st, int stag
       if (TRACE) ss_trace(p, stage_index, 5);
       met = true;
       if (shares_tiles) {
-        if (__syncthreads_or(!alive)) {
-          ss_give_up(p, stage_index);
-          return false;
-        }
+        if (__syncthreads_or(!alive)) break;
         if (TRACE) ss_trace(p, stage_index, 6);
         if (duty != 0) {
           finish_tile = tile0 + (int)(duty & 0x7FFFu);
@@ -524,73 +506,46 @@ __device__ bool ss_gemv(const SSParams& p, const aoto_stream_stage& st, int stag
       break;
     }
     if (finish_tile >= 0) {
-      // lanes 0-15 hold rows 0-15 of the tile: sum the shares in a fixed order, alpha, addend,
-      // paired SiLU, round, store (stamped pairs or plain), track the maximum
+      // lanes 0-15 hold rows 0-15 of the tile (lanes 16-31 the same rows of the second matrix):
+      // sum the shares in a fixed order, alpha, addend, paired SiLU, round, store, track the maximum
       __syncwarp();
-      const int n = finish_tile * 16 + lane;
-      float y = 0.f;
-      if (lane < 16) {
-        float total0 = 0.f, total1 = 0.f;
-        for (int i = 0; i < finish_parts; ++i) {
-          const uint32_t at = finish_first + (uint32_t)i * SS_PART_BYTES + (uint32_t)lane * 4;
-          total0 += ss_ldsf(at);
-          if (paired) total1 += ss_ldsf(at + 64);
-        }
-        y = st.alpha * total0;
-        if (st.addend_mode != AOTO_STAGE_ADDEND_NONE) y = fmaf(st.beta, finish_addend, y);
-        if (paired) {
-          const float gate = round_bf16(y);
-          y = (st.alpha * total1) * (gate / (1.f + expf(-gate)));
-        }
-        if (n >= N) y = 0.f;
+      const int n = finish_tile * 16 + (lane & 15);
+      float total = 0.f;
+      {
+        const uint32_t at = finish_first + (uint32_t)lane * 4;  // [matrix][row] floats of a share
+#pragma unroll 1
+        for (int i = 0; i < finish_parts; ++i) total += ss_ldsf(at + (uint32_t)i * SS_PART_BYTES);
+      }
+      const float second = __shfl_down_sync(0xffffffffu, total, 16);
+      float y = st.alpha * total;
+      if (addend_mode != AOTO_STAGE_ADDEND_NONE) y = fmaf(st.beta, finish_addend, y);
+      if (paired) {
+        const float gate = round_bf16(y);
+        y = (st.alpha * second) * __fdividef(gate, 1.f + __expf(-gate));
       }
       const uint32_t bits = float_to_bf16_bits(y);
       const uint32_t neighbour = __shfl_down_sync(0xffffffffu, bits, 1);
       if (lane < 16 && n < N) {
-        if (st.flags & AOTO_STAGE_FLAG_OUT_PLAIN) {
+        if (stage_flags & AOTO_STAGE_FLAG_OUT_PLAIN) {
           reinterpret_cast<bf16*>(st.out)[n] = __ushort_as_bfloat16((unsigned short)bits);
-        } else if ((lane & 1) == 0) {
-          ss_st_stamped(reinterpret_cast<unsigned char*>(st.out) + (size_t)(n >> 1) * 8, bits | (neighbour << 16), epoch);
-        }
-        if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
           float v = __uint_as_float(bits << 16);
           if (v != v) v = INFINITY;
           if (v > best.value || (v == best.value && n < best.index)) { best.value = v; best.index = n; }
+        } else if ((lane & 1) == 0) {
+          ss_st_stamped(reinterpret_cast<unsigned char*>(st.out) + (size_t)(n >> 1) * 8, bits | (neighbour << 16), epoch);
         }
       }
       __syncwarp();  // a warp's own slot is read before its next whole tile overwrites it
     }
   }
-  // a stage without shared tiles still meets once: the staged row stays until every warp has used it
-  if (!shares_tiles || !alive) {
-    if (__syncthreads_or(!alive)) {
-      ss_give_up(p, stage_index);
-      return false;
-    }
+  // a stage without shared tiles still meets once (the staged row stays until every warp has
+  // used it); so does a warp that left the loop because a wait ran out
+  if (!shares_tiles || !alive) alive = !__syncthreads_or(!alive);
+  if (!alive) {
+    ss_give_up(p, stage_index);
+    return false;
   }
-
-  if (st.flags & AOTO_STAGE_FLAG_ARGMAX) {
-    float* sv = reinterpret_cast<float*>(smem + p.L.red);
-    int* si = reinterpret_cast<int*>(sv + 32);
-    float bv = best.value;
-    int bi = best.index;
-#pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
-    __syncthreads();  // the finishers' maxima are in; `red` is free of the norm statistic
-    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
-    __syncthreads();
-    if (tid == 0) {
-      for (int w = 1; w < SS_WARPS; ++w)
-        if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
-      unsigned char* payload = reinterpret_cast<unsigned char*>(p.a.scratch);
-      ss_st_stamped(payload + (size_t)blockIdx.x * 16, __float_as_uint(bv), epoch);
-      ss_st_stamped(payload + (size_t)blockIdx.x * 16 + 8, (uint32_t)bi, epoch);
-    }
-  }
+  if (stage_flags & AOTO_STAGE_FLAG_ARGMAX) ss_publish_best(p, best.value, best.index, smem);
   if (TRACE) ss_trace(p, stage_index, 7);
   return true;
 }
@@ -598,140 +553,138 @@ __device__ bool ss_gemv(const SSParams& p, const aoto_stream_stage& st, int stag
 // ---------------------------------------------------------------------------
 // attention stage: one CTA per query head over the whole window
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ float ss_rotate(const float* head, const bf16* cos_row, const bf16* sin_row, int d, int D) {
-  const int half = D >> 1;
-  const float v = head[d];
-  const float partner = d < half ? -head[d + half] : head[d - half];
-  return round_bf16(round_bf16(v * __bfloat162float(cos_row[d])) + round_bf16(partner * __bfloat162float(sin_row[d])));
-}
-
-// Key range [k0, k1) of the new window a warp attends, and how many of them come from the old cache.
-struct KeyRange {
-  int first, per, k0, k1, old_keys;
+// What a warp of a head CTA needs to know about its share of the window. The same for every
+// layer of a launch (the window length is a property of the step), so it is worked out once.
+struct WindowShare {
+  int head, kvh, member;    // this CTA's query head (-1: none), its kv head, the head's rank in the group
+  int k0, nkeys, old_keys;  // keys [k0, k0 + nkeys) of the new window; the first old_keys come from the cache
+  int first_valid;          // slots below it are outside the window (window mode)
+  uint32_t kbuf, vbuf, bar; // shared addresses of the warp's key rows, value rows and mbarrier
+  uint32_t new_key, new_value;  // where this step's rotated key / value rows go (the owner warp's buffers)
 };
-__device__ __forceinline__ KeyRange ss_key_range(const SSParams& p, int warp, int valid_length) {
-  const int C = p.a.capacity;
-  KeyRange r;
-  r.first = p.a.window ? max(0, C - valid_length) : 0;
-  r.per = (C - r.first + SS_WARPS - 1) / SS_WARPS;
-  r.k0 = min(C, r.first + warp * r.per);
-  r.k1 = min(C, r.k0 + r.per);
-  r.old_keys = max(0, min(r.k1, C - 1) - r.k0);  // slot C - 1 is this step's key
-  return r;
+
+__device__ __noinline__ WindowShare ss_window_share(const SSParams& p, int warp, int valid_length, unsigned char* smem) {
+  WindowShare w;
+  const int C = p.a.capacity, D = p.a.head_dim, QH = p.a.query_heads;
+  w.head = (int)blockIdx.x < QH && p.a.first_attention >= 0 ? (int)blockIdx.x : -1;
+  const int G = QH / max(p.a.kv_heads, 1);
+  w.kvh = max(w.head, 0) / max(G, 1);
+  w.member = max(w.head, 0) - w.kvh * G;
+  w.first_valid = p.a.window ? max(0, C - valid_length) : 0;
+  const int per = max(1, (C - w.first_valid + SS_WARPS - 1) / SS_WARPS);
+  w.k0 = min(C, w.first_valid + warp * per);
+  w.nkeys = min(C, w.k0 + per) - w.k0;
+  w.old_keys = max(0, min(w.k0 + w.nkeys, C - 1) - w.k0);  // slot C - 1 is this step's key
+  const uint32_t rows = (uint32_t)p.L.keys_per_warp * D * 2;
+  const uint32_t kv = ss_smem(smem + p.L.kv);
+  w.kbuf = kv + (uint32_t)warp * 2 * rows;
+  w.vbuf = w.kbuf + rows;
+  w.bar = ss_smem(smem + p.L.kvbars) + (uint32_t)warp * 8;
+  const int owner = (C - 1 - w.first_valid) / per;
+  const int owner_k0 = w.first_valid + owner * per;
+  w.new_key = kv + (uint32_t)owner * 2 * rows + (uint32_t)(C - 1 - owner_k0) * D * 2;
+  w.new_value = w.new_key + rows;
+  return w;
 }
 
 // Request this warp's share of a layer's window: new slot j is old slot j + 1.
-__device__ __forceinline__ void ss_request_window(const SSParams& p, const aoto_stream_stage& st, int warp, int lane,
-                                                  int valid_length, unsigned char* smem) {
-  const int head = blockIdx.x;
-  if (head >= p.a.query_heads) return;
-  const int D = p.a.head_dim, C = p.a.capacity, KVH = p.a.kv_heads;
-  const int kvh = head / (p.a.query_heads / KVH);
-  const KeyRange r = ss_key_range(p, warp, valid_length);
-  if (r.old_keys <= 0 || lane != 0) return;
-  const bf16* kin = reinterpret_cast<const bf16*>(st.addend) + (size_t)kvh * C * D;
-  const bf16* vin = reinterpret_cast<const bf16*>(st.addend) + ((size_t)KVH + kvh) * C * D;
-  const uint32_t bytes = (uint32_t)r.old_keys * D * 2;
-  const uint32_t bar = ss_smem(smem + p.L.kvbars) + (uint32_t)warp * 8;
-  const uint32_t kbuf = ss_smem(smem + p.L.kv) + (uint32_t)warp * 2 * p.L.keys_per_warp * D * 2;
-  const uint32_t vbuf = kbuf + (uint32_t)p.L.keys_per_warp * D * 2;
-  ss_fence_async_proxy();
-  ss_mbar_expect_tx(bar, 2 * bytes);
-  ss_bulk_load(kbuf, kin + (size_t)(r.k0 + 1) * D, bytes, bar);
-  ss_bulk_load(vbuf, vin + (size_t)(r.k0 + 1) * D, bytes, bar);
+__device__ __forceinline__ void ss_request_window(const SSParams& p, const aoto_stream_stage& st, const WindowShare& w,
+                                                  int lane) {
+  if (w.head < 0 || w.old_keys <= 0 || lane != 0) return;
+  const int D = p.a.head_dim, C = p.a.capacity;
+  const bf16* kin = reinterpret_cast<const bf16*>(st.addend) + ((size_t)w.kvh * C + w.k0 + 1) * D;
+  const bf16* vin = kin + (size_t)p.a.kv_heads * C * D;
+  const uint32_t bytes = (uint32_t)w.old_keys * D * 2;
+  ss_fence_async_proxy();  // this step's key row was written into the buffers through the generic proxy
+  ss_mbar_expect_tx(w.bar, 2 * bytes);
+  ss_bulk_load(w.kbuf, kin, bytes, w.bar);
+  ss_bulk_load(w.vbuf, vin, bytes, w.bar);
+}
+
+// Slot j of the next cache is slot j + 1 of this one, for every key and value plane of the
+// layer: a plain copy that touches nothing the step computes with. `me` of `movers` CTAs.
+__device__ __noinline__ void ss_move_window(const void* cache_in, void* cache_out, int planes, int capacity, int chunks,
+                                            int me, int movers) {
+  const uint4* src = reinterpret_cast<const uint4*>(cache_in);
+  uint4* dst = reinterpret_cast<uint4*>(cache_out);
+  const int per_plane = (capacity - 1) * chunks;
+  for (int plane = 0; plane < planes; ++plane) {
+    const size_t base = (size_t)plane * capacity * chunks;
+    for (int i = me * SS_THREADS + (int)threadIdx.x; i < per_plane; i += movers * SS_THREADS)
+      dst[base + i] = ldg_nc_u4(src + base + chunks + i);
+  }
 }
 
 template <bool TRACE>
-__device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int stage_index, int valid_length,
-                             uint32_t& kv_parity, bool& kv_pending, unsigned char* smem) {
+__device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int stage_index,
+                                             const WindowShare& w, uint32_t& kv_parity, bool& kv_pending,
+                                             unsigned char* smem) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int D = p.a.head_dim, C = p.a.capacity, KVH = p.a.kv_heads, QH = p.a.query_heads;
-  const int G = QH / KVH;
   const uint32_t epoch = p.a.epoch;
   if (TRACE) ss_trace(p, stage_index, 0);
 
-  // Moving the window (slot j of the next cache is slot j + 1 of this one) touches nothing the
-  // step computes with: the CTAs without a head do it, or every CTA when each one has a head.
+  // the CTAs without a head move the window (every CTA does when each one has a head)
   const int helpers = (int)gridDim.x - QH;
-  auto move_window = [&](int me, int movers) {
-    const int chunks = D >> 3;
-    const long long total = (long long)2 * KVH * (C - 1) * chunks;
-    const uint4* src = reinterpret_cast<const uint4*>(st.addend);
-    uint4* dst = reinterpret_cast<uint4*>(const_cast<void*>(st.norm_weight));
-    for (long long i = (long long)me * SS_THREADS + tid; i < total; i += (long long)movers * SS_THREADS) {
-      const long long plane = i / ((long long)(C - 1) * chunks), rest = i - plane * (C - 1) * chunks;
-      dst[plane * C * chunks + rest] = ldg_nc_u4(src + plane * C * chunks + chunks + rest);
-    }
-  };
-  if ((int)blockIdx.x >= QH) {
-    move_window((int)blockIdx.x - QH, helpers);
-    if (TRACE) ss_trace(p, stage_index, 1);
-    if (TRACE) ss_trace(p, stage_index, 6);
+  if (w.head < 0) {
+    ss_move_window(st.addend, const_cast<void*>(st.norm_weight), 2 * KVH, C, D >> 3, (int)blockIdx.x - QH, helpers);
     if (TRACE) ss_trace(p, stage_index, 7);
     return true;
   }
 
-  const int head = blockIdx.x, kvh = head / G, member = head - kvh * G;
   const int pairs = D >> 1;
   __syncthreads();  // the previous stage's last readers of the work region are done
-  float* rowv = reinterpret_cast<float*>(smem + p.L.work);  // raw q head, k, v of the step: 3 * D
-  float* qs = rowv + 3 * D;                                 // rotated, scaled query: D
-  float* merge = qs + D;                                    // per warp: m, l, then D sums
-  const bf16* cos_row = reinterpret_cast<const bf16*>(smem + p.L.rotary);
-  const bf16* sin_row = cos_row + D;
-  const KeyRange r = ss_key_range(p, warp, valid_length);
-  unsigned char* kbuf = smem + p.L.kv + (size_t)warp * 2 * p.L.keys_per_warp * D * 2;
-  unsigned char* vbuf = kbuf + (size_t)p.L.keys_per_warp * D * 2;
+  const uint32_t rowv = ss_smem(smem + p.L.work);  // raw q head, k, v of the step: 3 * D floats
+  const uint32_t qs = rowv + (uint32_t)3 * D * 4;  // rotated, scaled query: D floats
+  const uint32_t merge = qs + (uint32_t)D * 4;     // per warp: m, l, then D sums
+  const uint32_t weights = merge + (uint32_t)SS_WARPS * (D + 2) * 4 + (uint32_t)warp * 64;  // this warp's key weights
+  const uint32_t rotary = ss_smem(smem + p.L.rotary);  // cos row, sin row (bf16)
 
-  // this head's query and its kv head's key and value of the step: poll the stamped projection row
-  {
-    const unsigned char* row_words = reinterpret_cast<const unsigned char*>(st.x);
-    const int total_words = 3 * pairs;
-    int element = 0;
-    if (tid < pairs) element = p.a.query_start + head * D + 2 * tid;
-    else if (tid < 2 * pairs) element = p.a.key_start + kvh * D + 2 * (tid - pairs);
-    else element = p.a.value_start + kvh * D + 2 * (tid - 2 * pairs);
-    bool pending = tid < total_words;
-    int rounds = 0;
-    while (true) {
-      bool ready = true;
-      if (pending) {
-        const uint2 v = ss_ld_stamped(row_words + (size_t)(element >> 1) * 8);
-        if (v.y == epoch) {
-          rowv[2 * tid] = bf16x2_lo(v.x);
-          rowv[2 * tid + 1] = bf16x2_hi(v.x);
-          pending = false;
-        } else {
-          ready = false;
-        }
+  // this head's query and its kv head's key and value of the step: the warps that own words of
+  // the stamped projection row poll them, the others go straight to the barrier
+  bool failed = false;
+  if (tid < ((3 * pairs + 31) & ~31)) {
+    const bool mine = tid < 3 * pairs;
+    int element = p.a.query_start + w.head * D + 2 * tid;
+    if (tid >= 2 * pairs) element = p.a.value_start + w.kvh * D + 2 * (tid - 2 * pairs);
+    else if (tid >= pairs) element = p.a.key_start + w.kvh * D + 2 * (tid - pairs);
+    const unsigned char* at = reinterpret_cast<const unsigned char*>(st.x) + (size_t)(element >> 1) * 8;
+#pragma unroll 1
+    for (int rounds = 1;; ++rounds) {
+      const uint2 v = mine ? ss_ld_stamped(at) : make_uint2(0u, epoch);
+      if (v.y == epoch && mine) {
+        ss_stsf(rowv + (uint32_t)tid * 8, bf16x2_lo(v.x));
+        ss_stsf(rowv + (uint32_t)tid * 8 + 4, bf16x2_hi(v.x));
       }
-      if (__syncthreads_and(ready)) break;
-      ++rounds;
-      const bool stop = rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0);
-      if (__syncthreads_or(stop)) {
-        ss_give_up(p, stage_index);
-        return false;
-      }
+      if (__all_sync(0xffffffffu, v.y == epoch)) break;
+      if (rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0)) { failed = true; break; }
     }
+  }
+  if (__syncthreads_or(failed)) {
+    ss_give_up(p, stage_index);
+    return false;
   }
   if (TRACE) ss_trace(p, stage_index, 1);
 
   // rotate; this step's key and value join the window of the warp that owns the last slot
-  {
-    const int owner = r.per > 0 ? (C - 1 - r.first) / r.per : 0;
-    const KeyRange ro = ss_key_range(p, owner, valid_length);
-    unsigned char* okbuf = smem + p.L.kv + (size_t)owner * 2 * p.L.keys_per_warp * D * 2;
-    unsigned char* ovbuf = okbuf + (size_t)p.L.keys_per_warp * D * 2;
-    const int at = C - 1 - ro.k0;
-    bf16* kout = reinterpret_cast<bf16*>(const_cast<void*>(st.norm_weight)) + ((size_t)kvh * C + (C - 1)) * D;
-    bf16* vout = reinterpret_cast<bf16*>(const_cast<void*>(st.norm_weight)) + (((size_t)KVH + kvh) * C + (C - 1)) * D;
-    for (int d = tid; d < D; d += SS_THREADS) {
-      qs[d] = ss_rotate(rowv, cos_row, sin_row, d, D) * p.a.scale;
-      const bf16 key = __float2bfloat16_rn(ss_rotate(rowv + D, cos_row, sin_row, d, D));
-      const bf16 value = __float2bfloat16_rn(rowv[2 * D + d]);
-      reinterpret_cast<bf16*>(okbuf)[(size_t)at * D + d] = key;
-      reinterpret_cast<bf16*>(ovbuf)[(size_t)at * D + d] = value;
-      if (member == 0) { kout[d] = key; vout[d] = value; }
+  if (tid < D) {
+    const int half = D >> 1;
+    const uint32_t cs = ss_lds32(rotary + (uint32_t)(tid & ~1) * 2), sn = ss_lds32(rotary + (uint32_t)(D + (tid & ~1)) * 2);
+    const float c = (tid & 1) ? bf16x2_hi(cs) : bf16x2_lo(cs), sine = (tid & 1) ? bf16x2_hi(sn) : bf16x2_lo(sn);
+    const int other = tid < half ? tid + half : tid - half;
+    const float sign = tid < half ? -1.f : 1.f;
+    const float q = round_bf16(round_bf16(ss_ldsf(rowv + (uint32_t)tid * 4) * c) +
+                               round_bf16(sign * ss_ldsf(rowv + (uint32_t)other * 4) * sine));
+    const float k = round_bf16(round_bf16(ss_ldsf(rowv + (uint32_t)(D + tid) * 4) * c) +
+                               round_bf16(sign * ss_ldsf(rowv + (uint32_t)(D + other) * 4) * sine));
+    ss_stsf(qs + (uint32_t)tid * 4, q * p.a.scale);
+    const uint32_t key_bits = float_to_bf16_bits(k), value_bits = float_to_bf16_bits(ss_ldsf(rowv + (uint32_t)(2 * D + tid) * 4));
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(w.new_key + (uint32_t)tid * 2), "h"((unsigned short)key_bits) : "memory");
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(w.new_value + (uint32_t)tid * 2), "h"((unsigned short)value_bits) : "memory");
+    if (w.member == 0) {
+      bf16* kout = reinterpret_cast<bf16*>(const_cast<void*>(st.norm_weight)) + ((size_t)w.kvh * C + (C - 1)) * D;
+      kout[tid] = __ushort_as_bfloat16((unsigned short)key_bits);
+      kout[(size_t)KVH * C * D + tid] = __ushort_as_bfloat16((unsigned short)value_bits);
     }
   }
   __syncthreads();
@@ -740,24 +693,19 @@ __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int
   // every warp attends its keys: two lanes per key for the scores, the lanes split the head
   // dimension for the weighted sum of values
   bool alive = true;
-  if (kv_pending && r.old_keys > 0) {
-    alive = ss_mbar_wait(ss_smem(smem + p.L.kvbars) + (uint32_t)warp * 8, kv_parity);
-  }
+  if (kv_pending && w.old_keys > 0) alive = ss_mbar_wait(w.bar, kv_parity);
   if (TRACE) ss_trace(p, stage_index, 3);
   {
     const int key = lane >> 1, half = lane & 1;
-    const int nkeys = r.k1 - r.k0;
     const int half_chunks = D >> 4;  // 16-byte chunks of half a row
     float s = -INFINITY;
     bool attend = false;
-    if (alive && key < nkeys) {
-      const int slot = r.k0 + key;
-      attend = p.a.window ? slot >= C - valid_length : p.a.mask[slot] != 0;
-    }
+    if (alive && key < w.nkeys) attend = p.a.window ? w.k0 + key >= w.first_valid : p.a.mask[w.k0 + key] != 0;
     if (attend) {
-      const uint32_t krow = ss_smem(kbuf) + (uint32_t)key * D * 2 + (uint32_t)half * D;
-      const uint32_t qrow = ss_smem(qs) + (uint32_t)half * (D >> 1) * 4;
+      const uint32_t krow = w.kbuf + (uint32_t)key * D * 2 + (uint32_t)half * D;
+      const uint32_t qrow = qs + (uint32_t)half * (D >> 1) * 4;
       float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll 1
       for (int i = 0; i < half_chunks; ++i) {
         const int ci = (i + key) & (half_chunks - 1);  // rows are 2*D bytes apart: rotate the chunk order by key
         const uint4 kk = ss_lds128(krow + (uint32_t)ci * 16);
@@ -772,42 +720,33 @@ __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int
     const float other = __shfl_xor_sync(0xffffffffu, s, 1);
     s = attend ? s + other : -INFINITY;
     const float m = ss_warp_max(s);
-    const float m_safe = m == -INFINITY ? 0.f : m;
-    const float e = s == -INFINITY ? 0.f : expf(s - m_safe);
+    const float e = s == -INFINITY ? 0.f : __expf(s - m);
     // the warp's weights go through shared memory: the weighted sum below reads them as
     // broadcasts and needs no shuffle per key
-    float* weights = merge + SS_WARPS * (D + 2) + warp * 16;
-    if (half == 0) weights[key] = e;
+    if (half == 0) ss_stsf(weights + (uint32_t)key * 4, e);
     __syncwarp();
     // weighted values: lane holds D / 32 consecutive dimensions; every lane also sums the weights
     const int dims = D >> 5;  // 2 or 4
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, l = 0.f;
-    const uint32_t vrow = ss_smem(vbuf) + (uint32_t)lane * dims * 2;
-    const uint32_t wrow = ss_smem(weights);
-    if (dims == 2) {
-#pragma unroll 4
-      for (int j = 0; j < nkeys; ++j) {
-        const float w = ss_ldsf(wrow + (uint32_t)j * 4);
-        const uint32_t v = ss_lds32(vrow + (uint32_t)j * D * 2);
-        a0 = fmaf(w, bf16x2_lo(v), a0);
-        a1 = fmaf(w, bf16x2_hi(v), a1);
-        l += w;
+    const uint32_t vrow = w.vbuf + (uint32_t)lane * dims * 2;
+#pragma unroll 2
+    for (int j = 0; j < w.nkeys; ++j) {
+      const float wt = ss_ldsf(weights + (uint32_t)j * 4);
+      const uint32_t v0 = ss_lds32(vrow + (uint32_t)j * D * 2);
+      a0 = fmaf(wt, bf16x2_lo(v0), a0);
+      a1 = fmaf(wt, bf16x2_hi(v0), a1);
+      if (dims == 4) {
+        const uint32_t v1 = ss_lds32(vrow + (uint32_t)j * D * 2 + 4);
+        a2 = fmaf(wt, bf16x2_lo(v1), a2);
+        a3 = fmaf(wt, bf16x2_hi(v1), a3);
       }
-    } else {
-#pragma unroll 4
-      for (int j = 0; j < nkeys; ++j) {
-        const float w = ss_ldsf(wrow + (uint32_t)j * 4);
-        const uint32_t v0 = ss_lds32(vrow + (uint32_t)j * D * 2), v1 = ss_lds32(vrow + (uint32_t)j * D * 2 + 4);
-        a0 = fmaf(w, bf16x2_lo(v0), a0); a1 = fmaf(w, bf16x2_hi(v0), a1);
-        a2 = fmaf(w, bf16x2_lo(v1), a2); a3 = fmaf(w, bf16x2_hi(v1), a3);
-        l += w;
-      }
+      l += wt;
     }
-    float* mine = merge + warp * (D + 2);
-    if (lane == 0) { mine[0] = m; mine[1] = l; }
-    mine[2 + lane * dims] = a0;
-    mine[3 + lane * dims] = a1;
-    if (dims == 4) { mine[4 + lane * dims] = a2; mine[5 + lane * dims] = a3; }
+    const uint32_t mine = merge + (uint32_t)warp * (D + 2) * 4;
+    if (lane == 0) { ss_stsf(mine, m); ss_stsf(mine + 4, l); }
+    ss_stsf(mine + 8 + (uint32_t)lane * dims * 4, a0);
+    ss_stsf(mine + 12 + (uint32_t)lane * dims * 4, a1);
+    if (dims == 4) { ss_stsf(mine + 16 + (uint32_t)lane * dims * 4, a2); ss_stsf(mine + 20 + (uint32_t)lane * dims * 4, a3); }
   }
   if (TRACE) ss_trace(p, stage_index, 4);
   if (__syncthreads_or(!alive)) {
@@ -817,39 +756,40 @@ __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int
   if (TRACE) ss_trace(p, stage_index, 5);
   if (kv_pending) { kv_parity ^= 1u; kv_pending = false; }
 
-  // the next layer's window can start travelling now: every warp is done with its buffers
-  if (st.next_attention >= 0) {
-    const aoto_stream_stage* all = reinterpret_cast<const aoto_stream_stage*>(smem + p.L.stages);
-    ss_request_window(p, all[st.next_attention], warp, lane, valid_length, smem);
-    kv_pending = true;
-  }
-
   // merge the warps' results in a fixed order; the sixteen rescaling factors are computed once
   // per merging warp (one lane each) instead of once per output dimension
   if (tid < D) {
-    float* factors = merge + SS_WARPS * (D + 2) + SS_WARPS * 16 + warp * 16;
-    const float wm = lane < SS_WARPS ? merge[lane * (D + 2)] : -INFINITY;
-    const float wl = lane < SS_WARPS ? merge[lane * (D + 2) + 1] : 0.f;
+    const uint32_t factors = merge + (uint32_t)SS_WARPS * (D + 2) * 4 + SS_WARPS * 64 + (uint32_t)warp * 64;
+    const uint32_t row = merge + (uint32_t)(lane & (SS_WARPS - 1)) * (D + 2) * 4;
+    const float wm = lane < SS_WARPS ? ss_ldsf(row) : -INFINITY;
+    const float wl = lane < SS_WARPS ? ss_ldsf(row + 4) : 0.f;
     const float m = ss_warp_max(wm);
-    const float factor = wm == -INFINITY ? 0.f : expf(wm - m);
-    if (lane < SS_WARPS) factors[lane] = factor;
+    const float factor = wm == -INFINITY ? 0.f : __expf(wm - m);
+    if (lane < SS_WARPS) ss_stsf(factors + (uint32_t)lane * 4, factor);
     const float den = warp_sum(factor * wl);
     __syncwarp();
     float n0 = 0.f, n1 = 0.f;
-#pragma unroll
-    for (int w = 0; w < SS_WARPS; w += 2) {
-      n0 = fmaf(factors[w], merge[w * (D + 2) + 2 + tid], n0);
-      n1 = fmaf(factors[w + 1], merge[(w + 1) * (D + 2) + 2 + tid], n1);
+#pragma unroll 2
+    for (int i = 0; i < SS_WARPS; i += 2) {
+      n0 = fmaf(ss_ldsf(factors + (uint32_t)i * 4), ss_ldsf(merge + (uint32_t)(i * (D + 2) + 2 + tid) * 4), n0);
+      n1 = fmaf(ss_ldsf(factors + (uint32_t)i * 4 + 4), ss_ldsf(merge + (uint32_t)((i + 1) * (D + 2) + 2 + tid) * 4), n1);
     }
-    const float out = den > 0.f ? (n0 + n1) / den : 0.f;
+    const float out = den > 0.f ? __fdividef(n0 + n1, den) : 0.f;
     const uint32_t bits = float_to_bf16_bits(out);
     const uint32_t neighbour = __shfl_down_sync(0xffffffffu, bits, 1);
     if ((tid & 1) == 0)
-      ss_st_stamped(reinterpret_cast<unsigned char*>(st.out) + ((size_t)head * pairs + (tid >> 1)) * 8,
+      ss_st_stamped(reinterpret_cast<unsigned char*>(st.out) + ((size_t)w.head * pairs + (tid >> 1)) * 8,
                     bits | (neighbour << 16), epoch);
   }
   if (TRACE) ss_trace(p, stage_index, 6);
-  if (helpers <= 0) move_window(head, QH);
+
+  // the next layer's window starts travelling: every warp is done with its buffers
+  if (st.next_attention >= 0) {
+    const aoto_stream_stage* all = reinterpret_cast<const aoto_stream_stage*>(smem + p.L.stages);
+    ss_request_window(p, all[st.next_attention], w, lane);
+    kv_pending = true;
+  }
+  if (helpers <= 0) ss_move_window(st.addend, const_cast<void*>(st.norm_weight), 2 * KVH, C, D >> 3, w.head, QH);
   __syncthreads();  // the work region is free for the next stage
   if (TRACE) ss_trace(p, stage_index, 7);
   return true;
@@ -858,15 +798,14 @@ __device__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int
 // ---------------------------------------------------------------------------
 // pick stage: CTA 0 polls the per-CTA maxima the ARGMAX stage left
 // ---------------------------------------------------------------------------
-template <bool TRACE>
-__device__ void ss_pick(const SSParams& p, int stage_index) {
-  if (TRACE) ss_trace(p, stage_index, 0);
+__device__ __noinline__ void ss_pick(const SSParams& p, int stage_index) {
   if (blockIdx.x != 0 || threadIdx.x >= 32) return;
   const unsigned char* payload = reinterpret_cast<const unsigned char*>(p.a.scratch);
   float bv = -INFINITY;
   int bi = 0x7fffffff;
   int polls = 0;
   bool failed = false;
+#pragma unroll 1
   for (int c = threadIdx.x; c < (int)gridDim.x && !failed; c += 32) {
     uint2 a = ss_ld_stamped(payload + (size_t)c * 16), b = ss_ld_stamped(payload + (size_t)c * 16 + 8);
     while (a.y != p.a.epoch || b.y != p.a.epoch) {
@@ -879,13 +818,12 @@ __device__ void ss_pick(const SSParams& p, int stage_index) {
     if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
   }
   failed = __any_sync(0xffffffffu, failed);
-#pragma unroll
+#pragma unroll 1
   for (int offset = 16; offset > 0; offset >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
     const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
     if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
   }
-  if (TRACE) ss_trace(p, stage_index, 1);
   if (threadIdx.x == 0 && !failed) {
     p.a.token[0] = (long long)bi;
     if (p.a.counters != nullptr) {
@@ -896,18 +834,14 @@ __device__ void ss_pick(const SSParams& p, int stage_index) {
     }
   }
   if (threadIdx.x == 0 && failed) atomicCAS(p.a.status, 0, stage_index + 1);
-  if (TRACE) ss_trace(p, stage_index, 6);
-  if (TRACE) ss_trace(p, stage_index, 7);
 }
 
-template <bool TRACE>
-__global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid_constant__ SSParams p) {
-  extern __shared__ uint4 ss_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>(ss_raw);
+// Everything a CTA sets up once per launch: descriptors and its column of the table into shared
+// memory, barriers, the rotary rows of the step's position, and every warp's first requests.
+__device__ __noinline__ void ss_start(const SSParams& p, unsigned char* smem, WarpStream& ws, int valid_length,
+                                      long long position) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int depth = p.a.ring_depth;
-
-  // stage descriptors and this CTA's column of the table live in shared memory for the whole step
   {
     const uint4* src = reinterpret_cast<const uint4*>(p.a.stages);
     uint4* dst = reinterpret_cast<uint4*>(smem + p.L.stages);
@@ -922,7 +856,32 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
     for (int i = 0; i < SS_WARPS; ++i) ss_mbar_init(ss_smem(smem + p.L.kvbars) + i * 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (p.a.first_attention >= 0 && (int)blockIdx.x < p.a.query_heads && tid < 2 * p.a.head_dim) {
+    // the rotary rows of the step's position: fetched once, off every layer's critical path
+    long long pos = max(0ll, min(position, (long long)p.a.table_rows - 1));
+    const int D = p.a.head_dim;
+    const bf16* table = reinterpret_cast<const bf16*>(tid < D ? p.a.cos_table : p.a.sin_table);
+    reinterpret_cast<bf16*>(smem + p.L.rotary)[tid] = table[(size_t)pos * D + (tid < D ? tid : tid - D)];
+  }
   __syncthreads();
+  // every warp starts its stream: `depth` pieces in flight before anything is awaited
+  const uint4 start = ldg_nc_u4(reinterpret_cast<const uint4*>(p.a.starts) + (size_t)blockIdx.x * SS_WARPS + warp);
+  ws.issue_offset = (unsigned long long)start.x * 16ull;
+  ws.ring = ss_smem(smem + p.L.ring) + (uint32_t)warp * depth * SS_SLOT_BYTES;
+  ws.bars = ss_smem(smem + p.L.bars) + (uint32_t)warp * AOTO_STREAM_MAX_RING * 8;
+  ws.next_stage = start.z >> 16;
+  ws.slot = 0; ws.parity = 0; ws.issue_slot = 0; ws.in_flight = 0;
+  const uint32_t sizes[3] = {(start.y & 0xFFFFu) * 16u, (start.y >> 16) * 16u, (start.z & 0xFFFFu) * 16u};
+#pragma unroll
+  for (int i = 0; i < AOTO_STREAM_MAX_RING; ++i)
+    if (i < depth && sizes[i] != 0) ss_request(p, ws, sizes[i], lane);
+}
+
+template <bool TRACE>
+__global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid_constant__ SSParams p) {
+  extern __shared__ uint4 ss_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(ss_raw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   // the step's position and window
   int valid_length = 0;
@@ -933,35 +892,14 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
   } else if (p.a.position != nullptr) {
     position = *reinterpret_cast<const volatile long long*>(p.a.position);
   }
-
-  // every warp starts its stream: `depth` pieces in flight before anything is awaited
   WarpStream ws;
-  {
-    const uint4 start = ldg_nc_u4(reinterpret_cast<const uint4*>(p.a.starts) + (size_t)blockIdx.x * SS_WARPS + warp);
-    ws.issue_offset = (unsigned long long)start.x * 16ull;
-    ws.ring = ss_smem(smem + p.L.ring) + (uint32_t)warp * depth * SS_SLOT_BYTES;
-    ws.bars = ss_smem(smem + p.L.bars) + (uint32_t)warp * AOTO_STREAM_MAX_RING * 8;
-    ws.next_stage = start.z >> 16;
-    ws.slot = 0; ws.parity = 0; ws.issue_slot = 0; ws.in_flight = 0;
-    const uint32_t sizes[3] = {(start.y & 0xFFFFu) * 16u, (start.y >> 16) * 16u, (start.z & 0xFFFFu) * 16u};
-#pragma unroll
-    for (int i = 0; i < AOTO_STREAM_MAX_RING; ++i)
-      if (i < depth && sizes[i] != 0) ss_request(p, ws, sizes[i], lane);
-  }
+  ss_start(p, smem, ws, valid_length, position);
   uint32_t kv_parity = 0;
   bool kv_pending = false;
   const aoto_stream_stage* stages = reinterpret_cast<const aoto_stream_stage*>(smem + p.L.stages);
-  if (p.a.first_attention >= 0 && (int)blockIdx.x < p.a.query_heads && tid < 2 * p.a.head_dim) {
-    // the rotary rows of the step's position: fetched once, off every layer's critical path
-    long long pos = position;
-    if (pos < 0) pos = 0;
-    if (pos >= p.a.table_rows) pos = p.a.table_rows - 1;
-    const int D = p.a.head_dim;
-    const bf16* table = reinterpret_cast<const bf16*>(tid < D ? p.a.cos_table : p.a.sin_table);
-    reinterpret_cast<bf16*>(smem + p.L.rotary)[tid] = table[(size_t)pos * D + (tid < D ? tid : tid - D)];
-  }
+  const WindowShare share = ss_window_share(p, warp, valid_length, smem);
   if (p.a.first_attention >= 0) {
-    ss_request_window(p, stages[p.a.first_attention], warp, lane, valid_length, smem);
+    ss_request_window(p, stages[p.a.first_attention], share, lane);
     kv_pending = true;
   }
 
@@ -970,6 +908,7 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
   best.index = 0x7fffffff;
   const uint32_t* table = reinterpret_cast<const uint32_t*>(smem + p.L.table);
   bool alive = true;
+#pragma unroll 1
   for (int s = 0; s < p.a.stage_count && alive; ++s) {
     const aoto_stream_stage& st = stages[s];
     if (st.kind == AOTO_STAGE_GEMV) {
@@ -983,19 +922,20 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
         ss_st_stamped(payload + (size_t)blockIdx.x * 16 + 8, 0x7fffffffu, p.a.epoch);
       }
     } else if (st.kind == AOTO_STAGE_ATTENTION) {
-      alive = ss_attention<TRACE>(p, st, s, valid_length, kv_parity, kv_pending, smem);
+      alive = ss_attention<TRACE>(p, st, s, share, kv_parity, kv_pending, smem);
     } else if (st.kind == AOTO_STAGE_PICK) {
-      ss_pick<TRACE>(p, s);
+      ss_pick(p, s);
     }
   }
   if (!alive) {
     // a wait ran out: nothing may still be travelling into this CTA's shared memory when it leaves
-    ss_drain(p, ws);
-    if (kv_pending) {
-      const KeyRange r = ss_key_range(p, warp, valid_length);
-      if ((int)blockIdx.x < p.a.query_heads && r.old_keys > 0)
-        ss_mbar_wait(ss_smem(smem + p.L.kvbars) + (uint32_t)warp * 8, kv_parity);
+    while (ws.in_flight > 0) {
+      ss_mbar_wait(ws.bars + ws.slot * 8, ws.parity);
+      ws.slot += 1;
+      if (ws.slot == (uint32_t)p.a.ring_depth) { ws.slot = 0; ws.parity ^= 1u; }
+      ws.in_flight -= 1;
     }
+    if (kv_pending && share.head >= 0 && share.old_keys > 0) ss_mbar_wait(share.bar, kv_parity);
   }
 }
 

@@ -646,8 +646,12 @@ typedef struct aoto_stream_step_args {
   int32_t* status;
   void* scratch;                        /* per-CTA maxima of the ARGMAX stage: 16 bytes per CTA    */
   int64_t scratch_bytes;
-  uint64_t* trace;                      /* optional, uint64[stage_count * 8]: CTA 0's SM cycle counter
-                                           (%clock64) at the eight points decode_step marks          */
+  uint64_t* trace;                      /* optional, uint64[ctas * stage_count * 8]: every CTA's
+                                           %globaltimer (ns) at eight points of every stage it works in
+                                           (GEMV: 0 reached, 1-2 row complete, 3 row staged, 4 first piece
+                                           multiplied, 5 all pieces, 6 shares met, 7 done; ATTENTION: 0
+                                           reached, 1 row polled, 2 rotated, 3 window landed, 4 keys
+                                           attended, 5 warps met, 6 merged, 7 done). Slows the kernel.  */
 } aoto_stream_step_args;
 
 int aoto_sm100_stream_step(const aoto_stream_step_args* args, void* stream);
