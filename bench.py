@@ -491,31 +491,52 @@ def run_ours(args) -> None:
 
 
 def print_stage_trace(runtime, session, token, cache) -> None:
-    """One step with the kernel's trace on: CTA 0 stamps the global timer at eight points of a stage."""
+    """One step with the kernel's trace on, printed stage by stage.
 
-    trace = torch.zeros(session.stage_count * 8, dtype=torch.int64, device=session.device)
+    The streamed kernel records every CTA on the global timer: per stage, when the last CTA had
+    its input, had it staged, had multiplied, and was done - and from those the exchange time
+    (last input minus the previous stage's last `done`) and the work time. The in-place kernel
+    records CTA 0 only.
+    """
+
+    import numpy as np
+
+    streamed = session.kernel_name == "stream_step_kernel"
+    ctas = torch.cuda.get_device_properties(session.device).multi_processor_count if streamed else 1
+    trace = torch.zeros(ctas * session.stage_count * 8, dtype=torch.int64, device=session.device)
     session.token.copy_(token)
     session.caches[0].copy_(cache)
     session.counters.copy_(torch.tensor([PROMPT + 1, 0], dtype=torch.int32))
     for step in range(6):
         session.launch_step(step & 1, trace=trace if step == 5 else None)
     torch.cuda.synchronize()
-    table = trace.cpu().reshape(-1, 8).tolist()
-    origin = table[0][0]
     kinds = [stage.kind for stage in runtime.decode.plan.step_program.stages] + [3]
-    previous_end = origin
-    for index, row in enumerate(table):
-        entered, polled, staged, first_batch, reduced, stored, done, left = row
-        if kinds[index] == 1 and index < len(table) - 2:
-            print(f"stage {index:3d} gemv      at {entered - origin:7d} ns  gap {entered - previous_end:5d} | poll {polled - entered:5d} "
-                  f"stage {staged - polled:5d} first batch {first_batch - staged:5d} rest+reduce {reduced - first_batch:5d} "
-                  f"epilogue {stored - reduced:5d} tail {left - stored:5d}")
-        else:
-            name = {1: "gemv(head)", 2: "attention", 3: "pick"}.get(kinds[index], "?")
-            print(f"stage {index:3d} {name:9s} at {entered - origin:7d} ns  gap {entered - previous_end:5d} | poll {polled - entered:5d} "
-                  f"work {left - polled:6d}")
-        previous_end = left
-    print(f"total {table[-1][7] - origin} ns, status {int(session.status.item())}")
+    names = {1: "gemv", 2: "attention", 3: "pick"}
+    if not streamed:
+        table = trace.cpu().reshape(-1, 8).tolist()
+        origin, previous_end = table[0][0], table[0][0]
+        for index, row in enumerate(table):
+            print(f"stage {index:3d} {names[kinds[index]]:9s} at {row[0] - origin:7d} ns  gap {row[0] - previous_end:5d} | "
+                  f"poll {row[1] - row[0]:5d} work {row[7] - row[1]:6d}")
+            previous_end = row[7]
+        print(f"total {table[-1][7] - origin} ns, status {int(session.status.item())}")
+        return
+    times = trace.cpu().numpy().reshape(ctas, session.stage_count, 8).astype(np.float64)
+    times[times == 0] = np.nan
+    times -= np.nanmin(times)
+    print("stage kind      ctas | last input  staged  multiplied  done | exchange  work   (ns, 256 ns timer)")
+    previous_done = 0.0
+    for index in range(session.stage_count):
+        rows = times[:, index, :]
+        busy = ~np.isnan(rows[:, 2] if kinds[index] == 2 else rows[:, 1])
+        if kinds[index] == 3 or not busy.any():
+            continue
+        rows = rows[busy]
+        last_input, done = np.nanmax(rows[:, 1]), np.nanmax(rows[:, 7])
+        print(f"{index:5d} {names[kinds[index]]:9s} {int(busy.sum()):4d} | {last_input:10.0f} {np.nanmax(rows[:, 3]):7.0f} "
+              f"{np.nanmax(rows[:, 5]):11.0f} {done:5.0f} | {last_input - previous_done:8.0f} {done - last_input:5.0f}")
+        previous_done = done
+    print(f"total {np.nanmax(times):.0f} ns, status {int(session.status.item())}")
 
 
 def run_tp(args) -> None:
