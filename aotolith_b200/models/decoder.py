@@ -416,8 +416,25 @@ def compile_decoder_static_cache(model: torch.nn.Module, *, prompt_length: int, 
     Keyword options: ``codegen_matmul``, ``codegen_attention``, ``autotune``,
     ``quantize`` (group size), ``quantize_bits``, ``family``, ``target``,
     ``memory`` - the reference's (``decoder.py:1090-1145``).
+
+    ``tensor_parallel`` (a process group, or ``True`` for the default one; no reference
+    counterpart) shards the packed decoder over the group's GPUs instead and returns the
+    generation calls of the runtime over the shards (``tensor_parallel.TensorParallelRuntime``).
     """
 
+    sharded = options.pop("tensor_parallel", None)
+    if sharded is not None and sharded is not False:
+        from ..tensor_parallel import compile_tensor_parallel
+
+        unknown = set(options) - {"quantize", "quantize_bits", "family", "target", "device"}
+        if unknown:
+            raise CompilationError(f"options {sorted(unknown)} do not apply to a tensor-parallel compilation")
+        if options.get("target", DEFAULT_TARGET) != DEFAULT_TARGET:
+            raise CompilationError(f"unknown target {options['target']!r}", hint=f"the target is {DEFAULT_TARGET!r}")
+        return compile_tensor_parallel(
+            model, prompt_length=prompt_length, max_new_tokens=max_new_tokens, quantize=options.get("quantize"),
+            quantize_bits=options.get("quantize_bits", 4), family=options.get("family"),
+            tensor_parallel=sharded, device=options.get("device"))
     return _compile_bucket(model, prompt_length=prompt_length, max_new_tokens=max_new_tokens, **options)
 
 

@@ -99,6 +99,16 @@ def pack_weight(weight, group_size: int, bits: int = 4):
 
     import torch
 
+    if isinstance(weight, torch.Tensor) and weight.is_cuda:
+        # a model built on the device is packed there (the same arithmetic, bit for bit)
+        from ..quantize import quantize_torch
+
+        if weight.dim() != 2:
+            raise ValueError(f"a quantized weight must be 2-D, got {tuple(weight.shape)}")
+        if bits not in (4, 8):
+            raise ValueError(f"bits must be 4 or 8, got {bits!r}")
+        words, scales = quantize_torch(weight, group_size, bits)
+        return words, scales.to(weight.dtype)
     if isinstance(weight, torch.Tensor):
         matrix = weight.detach().float().cpu().numpy()
         scale_dtype = weight.dtype

@@ -23,12 +23,13 @@ class _Norm(nn.Module):
 
 
 def _linear(out_features: int, in_features: int, bias: bool, dtype, generator, std: float) -> nn.Linear:
+    device = generator.device
     layer = nn.Linear(in_features, out_features, bias=bias, dtype=dtype, device="meta")
-    layer = layer.to_empty(device="cpu")
+    layer = layer.to_empty(device=device)
     with torch.no_grad():
-        layer.weight.copy_(torch.randn(out_features, in_features, generator=generator, dtype=torch.float32) * std)
+        layer.weight.copy_(torch.randn(out_features, in_features, generator=generator, dtype=torch.float32, device=device) * std)
         if bias:
-            layer.bias.copy_(torch.randn(out_features, generator=generator, dtype=torch.float32) * 0.5)
+            layer.bias.copy_(torch.randn(out_features, generator=generator, dtype=torch.float32, device=device) * 0.5)
     layer.weight.requires_grad_(False)
     if bias:
         layer.bias.requires_grad_(False)
@@ -55,8 +56,14 @@ class SyntheticDecoder(nn.Module):
         dtype: torch.dtype = torch.bfloat16,
         seed: int = 0,
         std: float = 0.02,
+        device: str | torch.device = "cpu",
     ) -> None:
+        """``device``: where the weights are drawn and kept. A model of billions of parameters is
+        built in seconds on a GPU (and minutes on the host); the values depend on the device kind
+        (each has its own generator) and are the same on every GPU of one kind for one seed."""
+
         super().__init__()
+        device = torch.device(device)
         head_dim = head_dim or hidden_size // num_attention_heads
         self.config = SimpleNamespace(
             model_type=model_type, vocab_size=vocab_size, hidden_size=hidden_size,
@@ -66,13 +73,13 @@ class SyntheticDecoder(nn.Module):
             rope_theta=rope_theta, rope_scaling=None, rms_norm_eps=rms_norm_eps,
             hidden_act="silu", layer_types=None, tie_word_embeddings=tie_word_embeddings,
         )
-        generator = torch.Generator().manual_seed(seed)
+        generator = torch.Generator(device=device).manual_seed(seed)
         make = lambda o, i, b=False: _linear(o, i, b, dtype, generator, std)
         self.model = nn.Module()
-        self.model.embed_tokens = nn.Embedding(vocab_size, hidden_size, dtype=dtype)
+        self.model.embed_tokens = nn.Embedding(vocab_size, hidden_size, dtype=dtype, device=device)
         with torch.no_grad():
             self.model.embed_tokens.weight.copy_(
-                torch.randn(vocab_size, hidden_size, generator=generator, dtype=torch.float32) * std
+                torch.randn(vocab_size, hidden_size, generator=generator, dtype=torch.float32, device=device) * std
             )
         self.model.embed_tokens.weight.requires_grad_(False)
         layers = []
@@ -88,45 +95,47 @@ class SyntheticDecoder(nn.Module):
             layer.mlp.up_proj = make(intermediate_size, hidden_size)
             layer.mlp.down_proj = make(hidden_size, intermediate_size)
             layer.mlp.act_fn = nn.SiLU()
-            layer.input_layernorm = _Norm(hidden_size, dtype)
-            layer.post_attention_layernorm = _Norm(hidden_size, dtype)
+            layer.input_layernorm = _Norm(hidden_size, dtype).to(device)
+            layer.post_attention_layernorm = _Norm(hidden_size, dtype).to(device)
             with torch.no_grad():
                 for norm in (layer.input_layernorm, layer.post_attention_layernorm):
-                    norm.weight.add_(torch.randn(hidden_size, generator=generator) * 0.05)
+                    norm.weight.add_(torch.randn(hidden_size, generator=generator, device=device) * 0.05)
             layers.append(layer)
         self.model.layers = nn.ModuleList(layers)
-        self.model.norm = _Norm(hidden_size, dtype)
-        self.lm_head = nn.Linear(hidden_size, vocab_size, bias=False, dtype=dtype, device="meta").to_empty(device="cpu")
+        self.model.norm = _Norm(hidden_size, dtype).to(device)
+        self.lm_head = nn.Linear(hidden_size, vocab_size, bias=False, dtype=dtype, device="meta").to_empty(device=device)
         self.lm_head.weight.requires_grad_(False)
         if tie_word_embeddings:
             self.lm_head.weight = self.model.embed_tokens.weight
         else:
             with torch.no_grad():
                 self.lm_head.weight.copy_(
-                    torch.randn(vocab_size, hidden_size, generator=generator, dtype=torch.float32) * std
+                    torch.randn(vocab_size, hidden_size, generator=generator, dtype=torch.float32, device=device) * std
                 )
         self.eval()
 
 
-def qwen25_05b_shaped(seed: int = 0, *, layers: int = 24, max_position_embeddings: int = 32768) -> SyntheticDecoder:
+def qwen25_05b_shaped(seed: int = 0, *, layers: int = 24, max_position_embeddings: int = 32768,
+                      device: str | torch.device = "cpu") -> SyntheticDecoder:
     """Qwen2.5-0.5B shapes: hidden 896, MLP 4864, 24 layers, 14/2 heads, dim 64, vocab 151936."""
 
     return SyntheticDecoder(
         model_type="qwen2", vocab_size=151936, hidden_size=896, intermediate_size=4864,
         num_hidden_layers=layers, num_attention_heads=14, num_key_value_heads=2, head_dim=64,
         max_position_embeddings=max_position_embeddings, rope_theta=1e6, rms_norm_eps=1e-6,
-        attention_bias=True, tie_word_embeddings=True, seed=seed,
+        attention_bias=True, tie_word_embeddings=True, seed=seed, device=device,
     )
 
 
-def llama3_8b_shaped(seed: int = 0, *, layers: int = 32, max_position_embeddings: int = 8192) -> SyntheticDecoder:
+def llama3_8b_shaped(seed: int = 0, *, layers: int = 32, max_position_embeddings: int = 8192,
+                     device: str | torch.device = "cpu") -> SyntheticDecoder:
     """Llama-3-8B shapes: hidden 4096, MLP 14336, 32 layers, 32/8 heads, dim 128, vocab 128256."""
 
     return SyntheticDecoder(
         model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
         num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
         max_position_embeddings=max_position_embeddings, rope_theta=5e5, rms_norm_eps=1e-5,
-        attention_bias=False, tie_word_embeddings=False, seed=seed,
+        attention_bias=False, tie_word_embeddings=False, seed=seed, device=device,
     )
 
 

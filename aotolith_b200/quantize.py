@@ -117,3 +117,32 @@ def dequantize_int8(packed, scales, group_size: int) -> np.ndarray:
 
     spread = np.repeat(np.asarray(scales, dtype=np.float32), group_size, axis=-1)
     return unpack_codes_int8(packed).astype(np.float32) * spread
+
+
+def quantize_torch(weight, group_size: int = 64, bits: int = 4):
+    """The same packer on a torch tensor, wherever it lives: ``(int32 words, float32 scales)``.
+
+    Every step is the fp32 operation of :func:`_quantize` (``abs`` / ``max`` / divide /
+    round-half-to-even / clip), so the words and scales are bit for bit those of the NumPy
+    packer; ``tests/test_quantize.py`` holds the two against each other. Packing a model that
+    was built on the GPU stays on the GPU.
+    """
+
+    import torch
+
+    per_word = 32 // bits
+    magnitude = (1 << (bits - 1)) - 1
+    matrix = weight.detach().to(torch.float32)
+    if matrix.dim() != 2:
+        raise ValueError(f"quantization expects a 2-D weight, got {tuple(matrix.shape)}")
+    rows, inner = matrix.shape
+    check_group_size(group_size, inner, per_word)
+    grouped = matrix.reshape(rows, inner // group_size, group_size)
+    peak = grouped.abs().amax(dim=2)
+    scale = torch.where(peak > 0, peak, torch.ones_like(peak)) / magnitude
+    codes = torch.round(grouped / scale[..., None]).clamp_(-magnitude - 1, magnitude).to(torch.int64)
+    fields = (codes.reshape(rows, inner // per_word, per_word) & ((1 << bits) - 1))
+    shifts = torch.arange(per_word, dtype=torch.int64, device=matrix.device) * bits
+    words = (fields << shifts).sum(dim=2)  # disjoint bit fields: sum == or
+    words = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32)
+    return words.contiguous(), scale.contiguous()

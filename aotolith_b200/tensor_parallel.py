@@ -36,7 +36,7 @@ import torch
 import torch.distributed as dist
 
 from .errors import CompilationError, PlanInputError
-from .models.adapters import rotary_tables
+from .models.adapters import _rope_settings, rotary_tables
 from .models.quantized import pack_weight
 
 
@@ -145,7 +145,7 @@ class TensorParallelDecoder:
         self.embed = put(model.model.embed_tokens.weight)
         self.final_norm = put(model.model.norm.weight)
         self.lm_head = pack(rows_of(model.lm_head.weight, tp, r))
-        cosine, sine = rotary_tables(self.capacity, self.head_dim, float(config.rope_theta), dtype)
+        cosine, sine = rotary_tables(self.capacity, self.head_dim, _rope_settings(config)[0], dtype)
         self.cosine, self.sine = put(cosine), put(sine)
         self.blocks = []
         for layer in model.model.layers:
@@ -317,3 +317,80 @@ class TensorParallelDecoder:
             else:
                 self._step(step & 1)
         return torch.cat((first, self.generated[:steps - 1].reshape(1, -1)), dim=1)
+
+
+
+class TensorParallelRuntime:
+    """What ``compile_*_static_cache(..., tensor_parallel=group)`` returns on every rank of the group.
+
+    The generation calls of ``DecoderStaticCacheRuntime`` over a sharded decoder: every rank makes
+    the same calls with the same prompt and gets the same tokens. There is no per-rank artifact
+    to ``save`` and no host-visible cache: keys and values stay sharded by head on the ranks'
+    devices.
+    """
+
+    def __init__(self, decoder: TensorParallelDecoder, family: str) -> None:
+        self.decoder = decoder
+        self.family = family
+        self.prompt_length = decoder.prompt_length
+        self.max_new_tokens = decoder.max_new_tokens
+        self.cache_capacity = decoder.capacity
+        self.num_layers = decoder.layers
+        self.world, self.rank = decoder.world, decoder.rank
+
+    @property
+    def device(self) -> torch.device:
+        return self.decoder.device
+
+    def prefill_logits(self, input_ids: Any) -> torch.Tensor:
+        """``[1, vocab]`` logits of the prompt's last position (the caches now hold the prompt)."""
+
+        return self.decoder.prefill(torch.as_tensor(input_ids))
+
+    def greedy_generate(self, input_ids: Any, *, max_new_tokens: int | None = None) -> torch.Tensor:
+        """Greedy tokens ``[1, steps]`` (int64, on this rank's device), the same on every rank."""
+
+        return self.decoder.greedy_generate(torch.as_tensor(input_ids), max_new_tokens=max_new_tokens)
+
+    def close(self) -> None:
+        """Drop the recorded steps; call on every rank before the process group is destroyed."""
+
+        self.decoder.close()
+
+
+def compile_tensor_parallel(model: torch.nn.Module, *, prompt_length: int, max_new_tokens: int, quantize: int | None,
+                            quantize_bits: int = 4, family: str | None = None, tensor_parallel: Any = True,
+                            device: Any = None) -> TensorParallelRuntime:
+    """The sharded counterpart of ``compile_decoder_static_cache``: same model checks, same refusals.
+
+    ``tensor_parallel`` is a process group whose ranks each own one GPU, or ``True`` for the
+    default group. Every rank calls this with the same model (same weights).
+    """
+
+    from .errors import DynamicShapeError, UnsupportedModelError
+    from .models.adapters import _check_activation, _check_attention_is_causal_only, _rope_settings, family_for
+
+    found = family_for(model, require=family)
+    if _rope_settings(model.config)[1]:
+        raise UnsupportedModelError(f"{found.label} RoPE scaling is not supported yet",
+                                    hint="the adapter builds one rotary table from rope_theta")
+    _check_activation(model)
+    _check_attention_is_causal_only(model)
+    if getattr(model, "training", False):
+        raise CompilationError("compile_decoder_static_cache requires model.eval()", hint="call model.eval() first")
+    if prompt_length <= 0 or max_new_tokens < 0:
+        raise CompilationError("prompt_length must be positive and max_new_tokens non-negative",
+                               hint="both are compile-time constants of the plan pair")
+    if prompt_length + max_new_tokens > int(model.config.max_position_embeddings):
+        raise DynamicShapeError(
+            "prompt_length + max_new_tokens exceeds the model's maximum position embeddings "
+            f"({model.config.max_position_embeddings})", hint="shorten the prompt or the generation")
+    if quantize is None or quantize_bits != 4:
+        raise UnsupportedModelError("tensor parallelism shards 4-bit packed decoders", hint="pass quantize=64")
+    if not dist.is_initialized():
+        raise CompilationError("tensor_parallel needs an initialised torch.distributed process group",
+                               hint="launch one process per GPU and call init_process_group('nccl') first")
+    group = None if tensor_parallel is True else tensor_parallel
+    decoder = TensorParallelDecoder(model, prompt_length=prompt_length, max_new_tokens=max_new_tokens,
+                                    group_size=quantize, group=group, device=device)
+    return TensorParallelRuntime(decoder, found.name)

@@ -167,15 +167,18 @@ class ClockSampler:
         }
 
 
-def build_model(workload: str, seed: int):
+def build_model(workload: str, seed: int, device="cpu", **options):
+    """The workload's seeded model. ``device``: where it is drawn (the 8B shape takes minutes on the
+    host and seconds on a GPU; the values depend on the device kind, not on which GPU)."""
+
     from aotolith_b200.models import synthetic
 
     spec = WORKLOADS[workload]
-    return getattr(synthetic, spec["builder"])(seed=seed), spec
+    return getattr(synthetic, spec["builder"])(seed=seed, device=device, **options), spec
 
 
-def seeded_prompt(vocab: int, seed: int) -> torch.Tensor:
-    return torch.randint(0, vocab, (1, PROMPT), generator=torch.Generator().manual_seed(seed), dtype=torch.int64)
+def seeded_prompt(vocab: int, seed: int, length: int | None = None) -> torch.Tensor:
+    return torch.randint(0, vocab, (1, length or PROMPT), generator=torch.Generator().manual_seed(seed), dtype=torch.int64)
 
 
 # ---------------------------------------------------------------------------
@@ -347,15 +350,8 @@ def run_ours(args) -> None:
     import aotolith_b200 as aoto
     from aotolith_b200.models.session import decode_session
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device; the cuda-sm100 target has no CPU path")
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    world, rank, device = start_ranks()
+    local = device.index
 
     model, spec = build_model(args.workload, seed=0)
     compile_fn = aoto.compile_qwen2_static_cache if spec["family"] == "qwen2" else aoto.compile_llama_static_cache
@@ -367,7 +363,8 @@ def run_ours(args) -> None:
     decode_steps = NEW_TOKENS - 1
     # kernel mode: the whole step is one launch of the persistent step kernel; otherwise the
     # per-operation plan plus the step-input and greedy-pick kernels
-    if session.mode == "kernel":
+    kernel_mode, kernel_name = session.mode == "kernel", session.kernel_name
+    if kernel_mode:
         kernels_per_token = 1
     else:
         kernels_per_token = sum(1 for s in runtime.decode.plan.selections if s.is_native) + 2
@@ -437,6 +434,18 @@ def run_ours(args) -> None:
         dist.barrier()
     decode_ms = decode_job.milliseconds
 
+    # With more than one GPU the same command also reports the two workloads that use them
+    # together or at volume: the 8B shape sharded over the ranks (after a checked comparison of the
+    # sharded decoder with the unsharded one) and the bucketed runtime under many requests.
+    extra = {}
+    if world > 1 and args.workload == "qwen25_05b" and not args.skip_multi:
+        del session
+        runtime = None
+        torch.cuda.empty_cache()
+        extra["tp_parity"] = check_tp_parity(world, rank, device)
+        extra["tp"] = measure_tp(world, rank, device, steps=2, warmup=1, with_clocks=False)
+        extra["bucketed"] = measure_bucketed(world, rank, device, per_rank=512, warmup=3, with_clocks=False, model=model)
+
     if rank == 0:
         peak, peak_kind = measured_peaks()
         value = decode_job.per_second
@@ -463,7 +472,7 @@ def run_ours(args) -> None:
             "clocks": clocks,
         }
         step_roofline = {
-            "kernel": f"{session.kernel_name} (one launch = one decode step)" if session.mode == "kernel"
+            "kernel": f"{kernel_name} (one launch = one decode step)" if kernel_mode
             else "per-operation decode plan (CUDA graph of one step)",
             "bound": "hbm", "achieved": achieved_step, "peak": peak, "unit": "GB/s",
             "frac": achieved_step / peak,
@@ -474,12 +483,15 @@ def run_ours(args) -> None:
             "frac_of_8tbs": achieved_step / 8000.0, "peak_source": peak_kind,
             "note": "launch duration = CUDA-event time of the decode loop / launches, inside the timed region",
         }
-        lm_head = time_lm_head(runtime, peak, peak_kind)
-        if session.mode == "kernel":
-            line["roofline"], line["lm_head_roofline"] = step_roofline, lm_head
-        else:
-            line["roofline"], line["step_roofline"] = lm_head, step_roofline
+        line["roofline"] = step_roofline
+        if world == 1:
+            lm_head = time_lm_head(runtime, peak, peak_kind)
+            if kernel_mode:
+                line["lm_head_roofline"] = lm_head
+            else:
+                line["roofline"], line["step_roofline"] = lm_head, step_roofline
         line["prefill"] = prefill_stats
+        line.update(extra)
         if world == 1:
             line["qmatmul_sweep"] = qmatmul_sweep(device, peak, tensor_peak())
         if world == 1 and not args.skip_cpu:
@@ -539,18 +551,10 @@ def print_stage_trace(runtime, session, token, cache) -> None:
     print(f"total {np.nanmax(times):.0f} ns, status {int(session.status.item())}")
 
 
-def run_tp(args) -> None:
-    """One request stream, the model sharded over all ranks (strong scaling).
-
-    Every rank builds the same seeded model on the host and packs only its shard. A step is
-    one request: prefill, then ``new_tokens - 1`` replays of the recorded decode step (kernels
-    plus two NCCL all-reduces per layer).
-    """
+def start_ranks():
+    """``(world, rank, device)`` of this process; joins the NCCL group when there is more than one rank."""
 
     import torch.distributed as dist
-
-    from aotolith_b200 import replicas
-    from aotolith_b200.tensor_parallel import TensorParallelDecoder
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -559,33 +563,52 @@ def run_tp(args) -> None:
         raise SystemExit("bench.py needs a CUDA device; the cuda-sm100 target has no CPU path")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=device)
-    model, spec = build_model(args.workload, seed=0)
-    decoder = TensorParallelDecoder(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS, group_size=GROUP,
+    return world, rank, device
+
+
+def measure_tp(world: int, rank: int, device, steps: int, warmup: int, with_clocks: bool = True) -> dict | None:
+    """One request stream, the Llama-3-8B shape sharded over all ranks (strong scaling).
+
+    Every rank draws the same seeded model on its own GPU and packs only its shard. A step is
+    one request: prefill of 1024 tokens, then 255 replays of the recorded decode step (this
+    library's kernels plus two peer-memory sums per layer). Returns the record on rank 0.
+    """
+
+    import torch.distributed as dist
+
+    from aotolith_b200 import replicas
+    from aotolith_b200.tensor_parallel import TensorParallelDecoder
+
+    spec = WORKLOADS["llama3_8b_tp"]
+    prompt_length, new_tokens = spec["prompt"], spec["new_tokens"]
+    model, _ = build_model("llama3_8b_tp", seed=0, device=device)
+    decoder = TensorParallelDecoder(model, prompt_length=prompt_length, max_new_tokens=new_tokens, group_size=GROUP,
                                     world=world, rank=rank, device=device)
     config = model.config
     del model
-    prompt = seeded_prompt(config.vocab_size, 1).pin_memory()
-    decode_steps = NEW_TOKENS - 1
-    for _ in range(max(args.warmup, 3)):
+    torch.cuda.empty_cache()
+    prompt = seeded_prompt(config.vocab_size, 1, prompt_length).pin_memory()
+    decode_steps = new_tokens - 1
+    for _ in range(warmup):
         decoder.greedy_generate(prompt).cpu()
     torch.cuda.synchronize()
-    sampler = ClockSampler(local)
-    if rank == 0:
+    sampler = ClockSampler(device.index)
+    if rank == 0 and with_clocks:
         sampler.start()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     decode_ms = prefill_ms = 0.0
     e2e_start = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         marks[0].record()
         logits = decoder.prefill(prompt)
         first = decoder.ops.argmax(logits).reshape(1, 1)
         decoder.token.copy_(first)
-        decoder.counters.copy_(torch.tensor([PROMPT + 1, 0], dtype=torch.int32).pin_memory(), non_blocking=True)
+        decoder.counters.copy_(torch.tensor([prompt_length + 1, 0], dtype=torch.int32).pin_memory(), non_blocking=True)
         marks[1].record()
         for step in range(decode_steps):
             decoder.graphs[step & 1].replay()
@@ -594,49 +617,123 @@ def run_tp(args) -> None:
         prefill_ms += marks[0].elapsed_time(marks[1])
         decode_ms += marks[1].elapsed_time(marks[2])
     e2e_wall = time.perf_counter() - e2e_start
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop() if rank == 0 and with_clocks else None
     group_device = device if world > 1 else None
     decode_ms = replicas.job_throughput(0, decode_ms, group_device).milliseconds
     prefill_ms = replicas.job_throughput(0, prefill_ms, group_device).milliseconds
     e2e_ms = replicas.job_throughput(0, e2e_wall * 1e3, group_device).milliseconds
     if world > 1:
         dist.barrier()
-    if rank == 0:
-        peak, peak_kind = measured_peaks()
-        per_token_us = decode_ms * 1e3 / (args.steps * decode_steps)
-        bytes_step = step_bytes(config, PROMPT + 1 + decode_steps // 2)
-        achieved = bytes_step / (per_token_us * 1e-6) / 1e9
-        line = {
-            "metric": "batch-1 decode tok/s (4-bit g64 static cache)", "value": args.steps * decode_steps / (decode_ms / 1e3),
-            "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": e2e_ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": spec["description"], "parallelism": f"tp{world}: column-split q/k/v, gate, up and LM head; "
-                       "row-split o and down; two NCCL all-reduces per layer inside the recorded step",
-                       "step": f"one request: prefill({PROMPT}) + {decode_steps} decode steps; value counts the decode loop only",
-                       "l2": f"inputs larger than L2: {bytes_step / world / 1e6:.0f} MB of packed weights per GPU and token"},
-            "decode_us_per_token": per_token_us,
-            "prefill": {"ms": prefill_ms / args.steps, "tok_s": PROMPT / (prefill_ms / args.steps / 1e3), "tokens": PROMPT},
-            "e2e": {"value": args.steps * NEW_TOKENS / (e2e_ms / 1e3), "unit": "tok/s",
-                    "h2d_bytes_per_step": PROMPT * 8, "d2h_bytes_per_step": NEW_TOKENS * 8},
-            "gpu_launches": None, "clocks": clocks,
-            "roofline": {"kernel": "recorded decode step (per-operation kernels + NCCL)", "bound": "hbm",
-                         "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world),
-                         "traffic": None, "bytes_per_launch": bytes_step, "us_per_launch": per_token_us,
-                         "peak_source": peak_kind, "note": "whole-job bytes over whole-job peak (all GPUs)"},
-        }
-        print(json.dumps(line))
     decoder.close()
+    del decoder
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    peak, peak_kind = measured_peaks()
+    per_token_us = decode_ms * 1e3 / (steps * decode_steps)
+    bytes_step = step_bytes(config, prompt_length + 1 + decode_steps // 2)
+    achieved = bytes_step / (per_token_us * 1e-6) / 1e9
+    return {
+        "metric": "batch-1 decode tok/s (4-bit g64 static cache)", "value": steps * decode_steps / (decode_ms / 1e3),
+        "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": e2e_ms / steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (model drawn on the device from a seed)",
+        "config": {"workload": spec["description"], "parallelism": f"tp{world}: column-split q/k/v, gate, up and LM head; "
+                   "row-split o and down; two peer-memory sums per layer inside the recorded step, NCCL in prefill",
+                   "step": f"one request: prefill({prompt_length}) + {decode_steps} decode steps; value counts the decode loop only",
+                   "l2": f"inputs larger than L2: {bytes_step / world / 1e6:.0f} MB of packed weights per GPU and token"},
+        "decode_us_per_token": per_token_us,
+        "prefill": {"ms": prefill_ms / steps, "tok_s": prompt_length / (prefill_ms / steps / 1e3), "tokens": prompt_length},
+        "e2e": {"value": steps * new_tokens / (e2e_ms / 1e3), "unit": "tok/s",
+                "h2d_bytes_per_step": prompt_length * 8, "d2h_bytes_per_step": new_tokens * 8},
+        "clocks": clocks,
+        "roofline": {"kernel": "recorded decode step (per-operation kernels + peer-memory sums)", "bound": "hbm",
+                     "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world),
+                     "traffic": None, "bytes_per_launch": bytes_step, "us_per_launch": per_token_us,
+                     "peak_source": peak_kind, "note": "whole-job bytes over whole-job peak (all GPUs)"},
+    }
+
+
+def check_tp_parity(world: int, rank: int, device) -> dict | None:
+    """The sharded decoder against the same decoder on one rank, before anything sharded is timed.
+
+    A 2-layer cut of the Llama-3-8B shape (prompt 128, 16 greedy tokens), drawn from one seed on
+    every rank. All ranks run the sharded decoder; rank 0 also runs the unsharded one step by step
+    and compares: the prompt's logits within 1e-2 of max|logit| (the two differ in where partial
+    sums are rounded to bf16), and token for token - a differing token must be a near-tie of the
+    unsharded logits (gap within the same 1e-2), after which the sequences are no longer
+    comparable. A failed check ends the benchmark.
+    """
+
+    import torch.distributed as dist
+
+    from aotolith_b200.tensor_parallel import TensorParallelDecoder
+
+    prompt_length, new_tokens, tolerance = 128, 16, 1e-2
+    model, _ = build_model("llama3_8b", seed=3, device=device, layers=2)
+    sharded = TensorParallelDecoder(model, prompt_length=prompt_length, max_new_tokens=new_tokens, group_size=GROUP,
+                                    world=world, rank=rank, device=device)
+    prompt = seeded_prompt(model.config.vocab_size, 5, prompt_length)
+    got_logits = sharded.prefill(prompt).float().clone()
+    got = sharded.greedy_generate(prompt).reshape(-1).tolist()
+    torch.cuda.synchronize()
+    dist.barrier()
+    sharded.close()
+    record = None
+    if rank == 0:
+        single = TensorParallelDecoder(model, prompt_length=prompt_length, max_new_tokens=new_tokens, group_size=GROUP,
+                                       world=1, rank=0, device=device, peer_exchange=False)
+        logits = single.prefill(prompt).float().clone()
+        scale = float(logits.abs().max())
+        prefill_error = float((got_logits - logits).abs().max()) / scale
+        single.token.copy_(single.ops.argmax(logits).reshape(1, 1))
+        single.counters.copy_(torch.tensor([prompt_length + 1, 0], dtype=torch.int32, device=device))
+        matched, tie_gap = 0, None
+        for step in range(new_tokens):
+            want = int(single.token.item())
+            if got[step] != want:
+                tie_gap = float(logits.reshape(-1)[want] - logits.reshape(-1)[got[step]]) / scale
+                break
+            matched += 1
+            if step + 1 < new_tokens:
+                single._step(step & 1)
+                logits = single.logits.float().clone()
+        ok = prefill_error <= tolerance and (tie_gap is None or tie_gap <= tolerance)
+        record = {"workload": f"2-layer cut of the Llama-3-8B shape, prompt {prompt_length}, {new_tokens} greedy tokens, "
+                              f"tp{world} against one rank",
+                  "prefill_logits_error": prefill_error, "tolerance": tolerance, "tokens_compared": new_tokens,
+                  "tokens_matched": matched, "near_tie_gap_at_first_difference": tie_gap, "ok": ok}
+        single.close()
+        del single
+    del sharded, model
+    torch.cuda.empty_cache()
+    verdict = torch.tensor([1 if record is None or record["ok"] else 0], dtype=torch.int32, device=device)
+    dist.broadcast(verdict, src=0)
+    if not int(verdict.item()):
+        if rank == 0:
+            print(json.dumps({"tp_parity": record}), file=sys.stderr)
+        raise SystemExit("tensor-parallel parity check failed; nothing sharded was timed")
+    return record
+
+
+def run_tp(args) -> None:
+    import torch.distributed as dist
+
+    world, rank, device = start_ranks()
+    line = measure_tp(world, rank, device, args.steps, max(args.warmup, 3))
+    if rank == 0:
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_bucketed(args) -> None:
+def measure_bucketed(world: int, rank: int, device, per_rank: int, warmup: int, with_clocks: bool = True,
+                     model=None) -> dict | None:
     """Independent request streams over a bucketed runtime, one runtime per GPU.
 
     The request list (prompt lengths uniform in [1, 256], ids uniform over the vocabulary) is the
     same seeded list on every rank; rank r serves requests r, r + world, ... through the public
-    call ``greedy_generate(host ids) -> host tokens``. A step is 16 requests per rank.
+    call ``greedy_generate(host ids) -> host tokens``. Returns the record on rank 0.
     """
 
     import torch.distributed as dist
@@ -644,30 +741,22 @@ def run_bucketed(args) -> None:
     import aotolith_b200 as aoto
     from aotolith_b200 import replicas
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device; the cuda-sm100 target has no CPU path")
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    model, spec = build_model(args.workload, seed=0)
+    spec = WORKLOADS["qwen25_05b_bucketed"]
+    if model is None:
+        model, _ = build_model("qwen25_05b_bucketed", seed=0)
     runtime = aoto.compile_qwen2_bucketed(model, prompt_lengths=BUCKETS, max_new_tokens=NEW_TOKENS, quantize=GROUP)
     vocab = model.config.vocab_size
-    per_rank = 16 * args.steps
     generator = torch.Generator().manual_seed(7)
     lengths = torch.randint(1, BUCKETS[-1] + 1, (per_rank * world,), generator=generator).tolist()
     requests = [torch.randint(0, vocab, (1, n), generator=generator, dtype=torch.int64).pin_memory() for n in lengths]
     mine = replicas.shard(requests, world, rank)
-    for ids in [requests[i] for i in range(min(len(requests), 4 * len(BUCKETS)))][: max(args.warmup, 3) * 4]:
+    for ids in requests[: warmup * 4]:
         runtime.greedy_generate(ids).cpu()
     for bucket in BUCKETS:  # every bucket's stepper is recorded before the clock starts
         runtime.greedy_generate(torch.randint(0, vocab, (1, bucket), dtype=torch.int64)).cpu()
     torch.cuda.synchronize()
-    sampler = ClockSampler(local)
-    if rank == 0:
+    sampler = ClockSampler(device.index)
+    if rank == 0 and with_clocks:
         sampler.start()
     if world > 1:
         dist.barrier()
@@ -680,27 +769,40 @@ def run_bucketed(args) -> None:
     end.record()
     torch.cuda.synchronize()
     local_ms = begin.elapsed_time(end)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop() if rank == 0 and with_clocks else None
     job = replicas.job_throughput(generated, local_ms, device if world > 1 else None)
     prompt_tokens = replicas.job_throughput(sum(int(r.numel()) for r in mine), local_ms, device if world > 1 else None).units
     if world > 1:
         dist.barrier()
+    del runtime
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    return {
+        "metric": "bucketed runtime generated tok/s (4-bit g64 static cache, independent request streams)",
+        "value": job.per_second, "unit": "tok/s", "n_gpus": world, "warmup": warmup,
+        "ms_per_request": job.milliseconds / max(per_rank, 1), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": spec["description"], "requests": per_rank * world, "requests_per_gpu": per_rank,
+                   "request": "prefill (left-padded to its bucket) + 64 greedy tokens",
+                   "parallelism": f"{world} independent request stream(s), one bucketed runtime per GPU",
+                   "l2": "inputs larger than L2: 262 MB of packed weights are streamed per token"},
+        "e2e": {"value": job.per_second, "unit": "tok/s",
+                "h2d_bytes_per_request": int(8 * prompt_tokens / max(per_rank * world, 1)),
+                "d2h_bytes_per_request": NEW_TOKENS * 8},
+        "prompt_tok_s": prompt_tokens / (job.milliseconds / 1e3),
+        "clocks": clocks,
+    }
+
+
+def run_bucketed(args) -> None:
+    import torch.distributed as dist
+
+    world, rank, device = start_ranks()
+    line = measure_bucketed(world, rank, device, 16 * args.steps, max(args.warmup, 3))
     if rank == 0:
-        line = {
-            "metric": "bucketed runtime generated tok/s (4-bit g64 static cache, independent request streams)",
-            "value": job.per_second, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": job.milliseconds / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": spec["description"], "requests": per_rank * world,
-                       "step": "16 requests per GPU, each prefill (left-padded to its bucket) + 64 greedy tokens",
-                       "parallelism": f"{world} independent request stream(s), one bucketed runtime per GPU",
-                       "l2": "inputs larger than L2: 262 MB of packed weights are streamed per token"},
-            "e2e": {"value": job.per_second, "unit": "tok/s",
-                    "h2d_bytes_per_step": int(8 * prompt_tokens / max(args.steps, 1) / world),
-                    "d2h_bytes_per_step": 16 * NEW_TOKENS * 8},
-            "prompt_tok_s": prompt_tokens / (job.milliseconds / 1e3),
-            "gpu_launches": None, "clocks": clocks,
-        }
+        line.update(steps=args.steps, ms_per_step=line["ms_per_request"] * 16)
+        line["config"]["step"] = "16 requests per GPU"
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -844,6 +946,8 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="qwen25_05b")
     parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
+    parser.add_argument("--skip-multi", action="store_true",
+                        help="with more than one GPU: leave the tensor-parallel and bucketed records out")
     parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "i8_decoder", "step", "trace", "trace_llama"), default=None,
                         help="run a small fixed case of one kernel for a profiler instead of the benchmark")
     args = parser.parse_args()

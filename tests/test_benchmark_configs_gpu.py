@@ -203,7 +203,11 @@ def test_llama_8b_shaped_layers_through_the_step_kernel(cuda):
         assert rel_err(got_logits, want_logits) < bound, f"step {step}: {rel_err(got_logits, want_logits):.3e} (floor {floor:.3e})"
         assert kl(want_logits, got_logits) < KL_TOL, f"step {step}"
         assert rel_err(got_cache, want_cache) < REL_TOL
-        assert int(picked[0]) == int(want_logits.float().reshape(-1).argmax()), f"gap {top2_gap(want_logits)}"
+        # 128 256 bf16 logits of a random-init model tie at the top (a top-2 gap of exactly 0 occurs): the
+        # token must be the argmax of the kernel's own logits and sit within rounding of the oracle's maximum
+        flat = want_logits.float().reshape(-1)
+        assert int(picked[0]) == int(got_logits.float().argmax())
+        assert float(flat[int(picked[0])]) >= float(flat.max()) - bound * float(flat.abs().max()), f"gap {top2_gap(want_logits)}"
         token, cache = picked.reshape(1, 1), got_cache
 
 

@@ -145,3 +145,27 @@ def test_oracle_int8_packed_matmul_is_dequantise_then_matmul():
     four = Q.dequantize_int4(*Q.quantize_int4(weight, 16), 16)
     eight = Q.dequantize_int8(packed_np, scales_np, 16)
     assert np.abs(eight - weight).max() < np.abs(four - weight).max() / 8
+
+
+def test_torch_packer_is_bit_identical_to_the_numpy_packer():
+    """``quantize_torch`` (used when a model lives on the device) against ``quantize_int4/int8``."""
+
+    import torch
+
+    from aotolith_b200.quantize import quantize_int4, quantize_int8, quantize_torch
+
+    rng = np.random.default_rng(11)
+    for rows, inner, group in ((7, 128, 64), (5, 96, 32), (3, 64, 16)):
+        weight = (rng.standard_normal((rows, inner)) * 0.05).astype(np.float32)
+        weight[0, :group] = 0.0                                   # an all-zero group
+        weight[1, :] = np.where(np.arange(inner) % 2 == 0, 1.0, -1.0) * 0.75
+        weight[2, 3] = weight[2, :group].max() * 0.5              # a value exactly half way between codes
+        for bits, reference in ((4, quantize_int4), (8, quantize_int8)):
+            want_words, want_scales = reference(weight, group)
+            words, scales = quantize_torch(torch.from_numpy(weight), group, bits)
+            assert np.array_equal(words.numpy(), want_words)
+            assert np.array_equal(scales.numpy().view(np.int32), want_scales.view(np.int32))
+    bf16 = torch.from_numpy((rng.standard_normal((6, 256)) * 0.02).astype(np.float32)).bfloat16()
+    words, scales = quantize_torch(bf16, 64, 4)
+    want_words, want_scales = quantize_int4(bf16.float().numpy(), 64)
+    assert np.array_equal(words.numpy(), want_words) and np.array_equal(scales.numpy(), want_scales)

@@ -143,11 +143,19 @@ def _gpu_rank(rank, world, port, out_dir):
         for _ in range(5):
             row.fill_(float(rank + 1))
             decoder.peer.sum_(row)
-        torch.save({"tokens": tokens, "logits": logits, "plain_tokens": plain_tokens, "row": row.float().cpu()},
-                   os.path.join(out_dir, f"gpu{rank}.pt"))
+        # the public route to the same thing: the compile call with a process group
+        import aotolith_b200 as aoto
+
+        runtime = aoto.compile_llama_static_cache(_tiny(), prompt_length=PROMPT, max_new_tokens=NEW, quantize=GROUP,
+                                                  tensor_parallel=dist.group.WORLD)
+        assert (runtime.world, runtime.rank, runtime.cache_capacity) == (world, rank, PROMPT + NEW)
+        compiled_tokens = runtime.greedy_generate(_prompt()).cpu()
+        torch.save({"tokens": tokens, "logits": logits, "plain_tokens": plain_tokens, "row": row.float().cpu(),
+                    "compiled_tokens": compiled_tokens}, os.path.join(out_dir, f"gpu{rank}.pt"))
         dist.barrier()
         decoder.close()
         plain.close()
+        runtime.close()
     finally:
         dist.destroy_process_group()
 
@@ -166,6 +174,7 @@ def test_two_nccl_ranks_generate_what_one_rank_does(cuda, tmp_path):
     assert torch.equal(results[0]["tokens"], results[1]["tokens"])
     for result in results:
         assert torch.equal(result["tokens"], result["plain_tokens"])     # same sum, different transport
+        assert torch.equal(result["tokens"], result["compiled_tokens"])  # the compile option builds the same decoder
         assert torch.equal(result["row"], torch.full((1, 64), 3.0))       # 1 + 2 on every rank
     # partial sums are rounded to bf16 before the all-reduce: logits agree within the toy-model tolerance
     scale = float(want_logits.abs().max())
@@ -173,3 +182,23 @@ def test_two_nccl_ranks_generate_what_one_rank_does(cuda, tmp_path):
     assert torch.equal(results[0]["logits"], results[1]["logits"])
     agree = int((results[0]["tokens"] == want_tokens).sum())
     assert agree >= NEW - 1, (results[0]["tokens"], want_tokens)
+
+
+def test_tensor_parallel_compile_option_refuses_what_the_compiler_refuses():
+    """``compile_llama_static_cache(..., tensor_parallel=...)``: the model checks come before any device work."""
+
+    import aotolith_b200 as aoto
+    from aotolith_b200.errors import CompilationError, DynamicShapeError, UnsupportedModelError
+
+    model = _tiny()
+    with pytest.raises(UnsupportedModelError):
+        aoto.compile_qwen2_static_cache(model, prompt_length=8, max_new_tokens=4, quantize=GROUP, tensor_parallel=True)
+    with pytest.raises(UnsupportedModelError):
+        aoto.compile_llama_static_cache(model, prompt_length=8, max_new_tokens=4, tensor_parallel=True)  # dense
+    with pytest.raises(DynamicShapeError):
+        aoto.compile_llama_static_cache(model, prompt_length=10**6, max_new_tokens=4, quantize=GROUP, tensor_parallel=True)
+    with pytest.raises(CompilationError):
+        aoto.compile_llama_static_cache(model, prompt_length=8, max_new_tokens=4, quantize=GROUP, tensor_parallel=True,
+                                        autotune=True)
+    with pytest.raises(CompilationError, match="process group"):
+        aoto.compile_llama_static_cache(model, prompt_length=8, max_new_tokens=4, quantize=GROUP, tensor_parallel=True)
