@@ -442,9 +442,9 @@ def run_ours(args) -> None:
         del session
         runtime = None
         torch.cuda.empty_cache()
+        extra["bucketed"] = measure_bucketed(world, rank, device, per_rank=512, warmup=3, with_clocks=False, in_child=True)
         extra["tp_parity"] = check_tp_parity(world, rank, device)
         extra["tp"] = measure_tp(world, rank, device, steps=2, warmup=1, with_clocks=False)
-        extra["bucketed"] = measure_bucketed(world, rank, device, per_rank=512, warmup=3, with_clocks=False, model=model)
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
@@ -563,6 +563,9 @@ def start_ranks():
         raise SystemExit("bench.py needs a CUDA device; the cuda-sm100 target has no CPU path")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    # the peer exchange of this library uses plain stores into mapped peer buffers, never multimem:
+    # keep the symmetric-memory buffers off NVLink multicast objects
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=device)
     return world, rank, device
@@ -659,17 +662,19 @@ def check_tp_parity(world: int, rank: int, device) -> dict | None:
 
     A 2-layer cut of the Llama-3-8B shape (prompt 128, 16 greedy tokens), drawn from one seed on
     every rank. All ranks run the sharded decoder; rank 0 also runs the unsharded one step by step
-    and compares: the prompt's logits within 1e-2 of max|logit| (the two differ in where partial
-    sums are rounded to bf16), and token for token - a differing token must be a near-tie of the
-    unsharded logits (gap within the same 1e-2), after which the sequences are no longer
-    comparable. A failed check ends the benchmark.
+    and compares: the prompt's logits within 2e-2 of max|logit|, and token for token - a differing
+    token must be a near-tie of the unsharded logits (gap within the same 2e-2), after which the
+    sequences are no longer comparable. Why 2e-2: both sides are bf16 evaluations of the same
+    packed model that differ in where partial sums are rounded (a sharded o/down product is rounded
+    once per rank before the sum), each is held to 1e-2 against the exact evaluation, and one bf16
+    step at max|logit| is already up to 0.8e-2 of it. A failed check ends the benchmark.
     """
 
     import torch.distributed as dist
 
     from aotolith_b200.tensor_parallel import TensorParallelDecoder
 
-    prompt_length, new_tokens, tolerance = 128, 16, 1e-2
+    prompt_length, new_tokens, tolerance = 128, 16, 2e-2
     model, _ = build_model("llama3_8b", seed=3, device=device, layers=2)
     sharded = TensorParallelDecoder(model, prompt_length=prompt_length, max_new_tokens=new_tokens, group_size=GROUP,
                                     world=world, rank=rank, device=device)
@@ -683,10 +688,11 @@ def check_tp_parity(world: int, rank: int, device) -> dict | None:
     if rank == 0:
         single = TensorParallelDecoder(model, prompt_length=prompt_length, max_new_tokens=new_tokens, group_size=GROUP,
                                        world=1, rank=0, device=device, peer_exchange=False)
-        logits = single.prefill(prompt).float().clone()
+        raw = single.prefill(prompt)
+        logits = raw.float().clone()
         scale = float(logits.abs().max())
         prefill_error = float((got_logits - logits).abs().max()) / scale
-        single.token.copy_(single.ops.argmax(logits).reshape(1, 1))
+        single.token.copy_(single.ops.argmax(raw).reshape(1, 1))
         single.counters.copy_(torch.tensor([prompt_length + 1, 0], dtype=torch.int32, device=device))
         matched, tie_gap = 0, None
         for step in range(new_tokens):
@@ -727,39 +733,30 @@ def run_tp(args) -> None:
         dist.destroy_process_group()
 
 
-def measure_bucketed(world: int, rank: int, device, per_rank: int, warmup: int, with_clocks: bool = True,
-                     model=None) -> dict | None:
-    """Independent request streams over a bucketed runtime, one runtime per GPU.
+def serve_bucketed(shard_world: int, shard_rank: int, device, per_rank: int, warmup: int, model=None) -> dict:
+    """One GPU's share of the bucketed workload, in this process: ``{generated, prompt_tokens, ms}``.
 
     The request list (prompt lengths uniform in [1, 256], ids uniform over the vocabulary) is the
-    same seeded list on every rank; rank r serves requests r, r + world, ... through the public
-    call ``greedy_generate(host ids) -> host tokens``. Returns the record on rank 0.
+    same seeded list of ``per_rank * shard_world`` requests wherever it is built; this process serves
+    requests ``shard_rank, shard_rank + shard_world, ...`` through the public call
+    ``greedy_generate(host ids) -> host tokens`` and times them with CUDA events.
     """
-
-    import torch.distributed as dist
 
     import aotolith_b200 as aoto
     from aotolith_b200 import replicas
 
-    spec = WORKLOADS["qwen25_05b_bucketed"]
     if model is None:
         model, _ = build_model("qwen25_05b_bucketed", seed=0)
     runtime = aoto.compile_qwen2_bucketed(model, prompt_lengths=BUCKETS, max_new_tokens=NEW_TOKENS, quantize=GROUP)
     vocab = model.config.vocab_size
     generator = torch.Generator().manual_seed(7)
-    lengths = torch.randint(1, BUCKETS[-1] + 1, (per_rank * world,), generator=generator).tolist()
+    lengths = torch.randint(1, BUCKETS[-1] + 1, (per_rank * shard_world,), generator=generator).tolist()
     requests = [torch.randint(0, vocab, (1, n), generator=generator, dtype=torch.int64).pin_memory() for n in lengths]
-    mine = replicas.shard(requests, world, rank)
+    mine = replicas.shard(requests, shard_world, shard_rank)
     for ids in requests[: warmup * 4]:
         runtime.greedy_generate(ids).cpu()
     for bucket in BUCKETS:  # every bucket's stepper is recorded before the clock starts
         runtime.greedy_generate(torch.randint(0, vocab, (1, bucket), dtype=torch.int64)).cpu()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(device.index)
-    if rank == 0 and with_clocks:
-        sampler.start()
-    if world > 1:
-        dist.barrier()
     torch.cuda.synchronize()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     begin.record()
@@ -768,13 +765,60 @@ def measure_bucketed(world: int, rank: int, device, per_rank: int, warmup: int, 
         generated += int(runtime.greedy_generate(ids).cpu().numel())
     end.record()
     torch.cuda.synchronize()
-    local_ms = begin.elapsed_time(end)
-    clocks = sampler.stop() if rank == 0 and with_clocks else None
-    job = replicas.job_throughput(generated, local_ms, device if world > 1 else None)
-    prompt_tokens = replicas.job_throughput(sum(int(r.numel()) for r in mine), local_ms, device if world > 1 else None).units
+    return {"generated": generated, "prompt_tokens": sum(int(r.numel()) for r in mine), "ms": begin.elapsed_time(end)}
+
+
+def serve_bucketed_in_child(world: int, rank: int, device, per_rank: int, warmup: int) -> dict:
+    """The same share served by a child process that owns this rank's GPU and joins no process group.
+
+    Independent request streams are deployed as plain single-GPU processes, and that is what is
+    measured: the child is this file run with ``--bucketed-share rank/world``; it sees only this
+    rank's GPU, builds its own runtime and prints ``serve_bucketed``'s figures as one JSON line.
+    """
+
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    physical = visible.split(",")[device.index].strip() if visible else str(device.index)
+    env = {k: v for k, v in os.environ.items()
+           if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "GROUP_RANK", "ROLE_RANK",
+                        "LOCAL_WORLD_SIZE", "ROLE_WORLD_SIZE", "TORCHELASTIC_RUN_ID", "TORCHELASTIC_RESTART_COUNT",
+                        "TORCHELASTIC_MAX_RESTARTS", "TORCHELASTIC_USE_AGENT_STORE", "TORCH_NCCL_ASYNC_ERROR_HANDLING")}
+    env["CUDA_VISIBLE_DEVICES"] = physical
+    command = [sys.executable, str(Path(__file__).resolve()), "--bucketed-share", f"{rank}/{world}",
+               "--requests-per-gpu", str(per_rank), "--warmup", str(warmup)]
+    done = subprocess.run(command, env=env, capture_output=True, text=True, timeout=1800)
+    if done.returncode != 0:
+        raise SystemExit(f"the bucketed child of rank {rank} failed ({done.returncode}):\n{done.stderr[-2000:]}")
+    return json.loads(done.stdout.strip().splitlines()[-1])
+
+
+def measure_bucketed(world: int, rank: int, device, per_rank: int, warmup: int, with_clocks: bool = True,
+                     model=None, in_child: bool = False) -> dict | None:
+    """Independent request streams over a bucketed runtime, one runtime per GPU; the record on rank 0.
+
+    ``in_child``: every rank hands its share to a single-GPU child process (see
+    ``serve_bucketed_in_child``) and only the figures cross the process group.
+    """
+
+    import torch.distributed as dist
+
+    from aotolith_b200 import replicas
+
+    spec = WORKLOADS["qwen25_05b_bucketed"]
+    sampler = ClockSampler(device.index)
+    if rank == 0 and with_clocks:
+        sampler.start()
     if world > 1:
         dist.barrier()
-    del runtime
+    if in_child:
+        share = serve_bucketed_in_child(world, rank, device, per_rank, warmup)
+    else:
+        share = serve_bucketed(world, rank, device, per_rank, warmup, model)
+    clocks = sampler.stop() if rank == 0 and with_clocks else None
+    group_device = device if world > 1 else None
+    job = replicas.job_throughput(share["generated"], share["ms"], group_device)
+    prompt_tokens = replicas.job_throughput(share["prompt_tokens"], share["ms"], group_device).units
+    if world > 1:
+        dist.barrier()
     torch.cuda.empty_cache()
     if rank != 0:
         return None
@@ -785,7 +829,10 @@ def measure_bucketed(world: int, rank: int, device, per_rank: int, warmup: int, 
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": spec["description"], "requests": per_rank * world, "requests_per_gpu": per_rank,
                    "request": "prefill (left-padded to its bucket) + 64 greedy tokens",
-                   "parallelism": f"{world} independent request stream(s), one bucketed runtime per GPU",
+                   "parallelism": f"{world} independent request stream(s), one bucketed runtime per GPU"
+                                  + (", each in a single-GPU process of its own" if in_child else ""),
+                   "timing": "CUDA events around each GPU's whole share (clock samples cover runtime construction too); "
+                             "job = all generated tokens / slowest GPU",
                    "l2": "inputs larger than L2: 262 MB of packed weights are streamed per token"},
         "e2e": {"value": job.per_second, "unit": "tok/s",
                 "h2d_bytes_per_request": int(8 * prompt_tokens / max(per_rank * world, 1)),
@@ -799,13 +846,24 @@ def run_bucketed(args) -> None:
     import torch.distributed as dist
 
     world, rank, device = start_ranks()
-    line = measure_bucketed(world, rank, device, 16 * args.steps, max(args.warmup, 3))
+    line = measure_bucketed(world, rank, device, 16 * args.steps, max(args.warmup, 3), in_child=world > 1)
     if rank == 0:
         line.update(steps=args.steps, ms_per_step=line["ms_per_request"] * 16)
         line["config"]["step"] = "16 requests per GPU"
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_bucketed_share(args) -> None:
+    """Child of ``serve_bucketed_in_child``: one GPU, no process group, one JSON line."""
+
+    shard_rank, shard_world = (int(v) for v in args.bucketed_share.split("/"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the cuda-sm100 target has no CPU path")
+    torch.cuda.set_device(0)
+    share = serve_bucketed(shard_world, shard_rank, torch.device("cuda", 0), args.requests_per_gpu, max(args.warmup, 3))
+    print(json.dumps(share))
 
 
 def run_probe(name: str) -> None:
@@ -950,7 +1008,13 @@ def main() -> None:
                         help="with more than one GPU: leave the tensor-parallel and bucketed records out")
     parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "i8_decoder", "step", "trace", "trace_llama"), default=None,
                         help="run a small fixed case of one kernel for a profiler instead of the benchmark")
+    parser.add_argument("--bucketed-share", default=None, metavar="RANK/WORLD",
+                        help="internal: serve one GPU's share of the bucketed workload and print its figures")
+    parser.add_argument("--requests-per-gpu", type=int, default=512, help="with --bucketed-share")
     args = parser.parse_args()
+    if args.bucketed_share is not None:
+        run_bucketed_share(args)
+        return
     if args.probe is not None:
         run_probe(args.probe)
         return
