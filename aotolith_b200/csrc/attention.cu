@@ -152,6 +152,45 @@ attention_decode_kernel(const AttnParams p) {
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  // The partial results of the kv head's query heads lie next to each other in scratch. They are
+  // staged in this CTA's shared memory (free now) with coalesced loads that are all in flight
+  // together - as many heads at a time as fit - and merged from there: read one by one from L2,
+  // the 3 * splits dependent-latency loads of every output element were most of a long window's
+  // kernel time.
+  const int per_head = p.splits * (D + 2);
+  const int region = (2 * TK * row_bytes) / 4 + G * D + G * TK + G * 2 + TK;  // floats of the dynamic region
+  const float* group = p.scratch + SCRATCH_HEADER_BYTES / 4 + (size_t)kvh * G * per_head;
+  float* staged = reinterpret_cast<float*>(smem4);
+  const int heads_per_round = min(G, region / per_head);
+  if (heads_per_round >= 1) {
+    for (int h0 = 0; h0 < G; h0 += heads_per_round) {
+      const int heads = min(heads_per_round, G - h0);
+      const float* from = group + (size_t)h0 * per_head;
+      __syncthreads();  // the previous round's readers are done with the staging area
+#pragma unroll 8
+      for (int i = tid; i < heads * per_head; i += DECODE_THREADS) staged[i] = __ldcg(from + i);
+      __syncthreads();
+      for (int item = tid; item < heads * D; item += DECODE_THREADS) {
+        const int h = item / D, d = item - h * D;
+        const float* base = staged + h * per_head;
+        float m = -INFINITY;
+        for (int s2 = 0; s2 < p.splits; ++s2) m = fmaxf(m, base[s2 * (D + 2)]);
+        float acc = 0.f, l = 0.f;
+        if (m != -INFINITY) {
+          for (int s2 = 0; s2 < p.splits; ++s2) {
+            const float* part = base + s2 * (D + 2);
+            const float pm = part[0];
+            const float w = (pm == -INFINITY) ? 0.f : expf(pm - m);
+            acc = fmaf(w, part[2 + d], acc);
+            l = fmaf(w, part[1], l);
+          }
+        }
+        p.out[(size_t)(kvh * G + h0 + h) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+      }
+    }
+    return;
+  }
+  // more splits than one head's partials fit in shared memory: merge straight from L2
   for (int item = tid; item < G * D; item += DECODE_THREADS) {
     const int h = item / D, d = item - h * D;
     const int head = kvh * G + h;

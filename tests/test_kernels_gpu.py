@@ -311,7 +311,8 @@ def test_cache_roll_invariants(cuda):
 
 
 @pytest.mark.parametrize("QH,KVH,C,D,valid", [(14, 2, 192, 64, 129), (32, 8, 1280, 128, 1025),
-                                               (4, 2, 12, 8, 5), (14, 2, 192, 64, 192), (8, 8, 2100, 64, 2100)])
+                                               (4, 2, 12, 8, 5), (14, 2, 192, 64, 192), (8, 8, 2100, 64, 2100),
+                                               (4, 2, 8200, 64, 8000)])  # the last: more splits than the staged merge holds
 def test_attention_decode(cuda, QH, KVH, C, D, valid):
     ops = _ops()
     q = activations(100, 1, QH, 1, D)
