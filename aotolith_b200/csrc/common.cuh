@@ -44,6 +44,11 @@ __device__ __forceinline__ uint32_t ldg_nc_u32(const void* ptr) {
   asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(ptr));
   return v;
 }
+__device__ __forceinline__ uint2 ldg_nc_u2(const void* ptr) {
+  uint2 v;
+  asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr));
+  return v;
+}
 __device__ __forceinline__ float ldg_nc_bf16(const __nv_bfloat16* ptr) {
   unsigned short raw;
   asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(raw) : "l"(ptr));

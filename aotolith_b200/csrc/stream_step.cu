@@ -24,14 +24,16 @@ constexpr int SS_MAX_K = 16384;
 constexpr int SS_POLL_LIMIT = 1 << 20;  // rounds of a bounded poll (each is at least one L2 round trip)
 constexpr int SS_PART_SLOTS = AOTO_STREAM_PART_SLOTS + SS_WARPS;  // shared tiles, then one private slot per warp
 constexpr int SS_PART_BYTES = 128;      // [matrix][row] floats of one share
-constexpr int SS_MAX_WINDOW_KEYS = 16;  // keys per warp in the one-CTA-per-head attention form
+constexpr int SS_MAX_WINDOW_KEYS = 16;  // keys per warp whose rows travel into shared memory a layer ahead; a
+                                        // longer window is read from L2 in passes of sixteen keys per warp
 
 // ---------------------------------------------------------------------------
 // shared-memory layout, computed identically on both sides
 // ---------------------------------------------------------------------------
 struct SSLayout {
   uint32_t ring, bars, kvbars, stages, table, work, xs, xsum, part, red, rotary, kv, total;
-  int keys_per_warp;
+  int keys_per_warp;  // rows of a warp's key / value buffers (short window)
+  int long_window;    // the window does not fit the buffers: only the step's own key and value rows are kept
 };
 
 __host__ __device__ inline uint32_t ss_align(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
@@ -60,9 +62,11 @@ __host__ __device__ inline SSLayout ss_layout(int stage_count, int max_k, int de
   off += ss_align(work_bytes, 16);
   L.red = off; off += 64 * 4;
   L.rotary = off; off += has_attention ? (uint32_t)head_dim * 4 : 0;  // cos row, sin row of the step's position
-  L.rotary = off; off += has_attention ? (uint32_t)head_dim * 4 : 0;  // cos row, sin row of the step's position
   L.keys_per_warp = has_attention ? (capacity + SS_WARPS - 1) / SS_WARPS : 0;
-  L.kv = off; off += has_attention ? (uint32_t)SS_WARPS * 2 * L.keys_per_warp * head_dim * 2 : 0;
+  L.long_window = L.keys_per_warp > SS_MAX_WINDOW_KEYS;
+  L.kv = off;
+  if (L.long_window) off += ss_align((uint32_t)2 * head_dim * 2, 16);
+  else off += has_attention ? (uint32_t)SS_WARPS * 2 * L.keys_per_warp * head_dim * 2 : 0;
   L.total = off;
   return L;
 }
@@ -584,13 +588,18 @@ __device__ __noinline__ WindowShare ss_window_share(const SSParams& p, int warp,
   const int owner_k0 = w.first_valid + owner * per;
   w.new_key = kv + (uint32_t)owner * 2 * rows + (uint32_t)(C - 1 - owner_k0) * D * 2;
   w.new_value = w.new_key + rows;
+  if (p.L.long_window) {  // no buffers: the step's own rows only
+    w.kbuf = w.vbuf = 0;
+    w.new_key = kv;
+    w.new_value = kv + (uint32_t)D * 2;
+  }
   return w;
 }
 
 // Request this warp's share of a layer's window: new slot j is old slot j + 1.
 __device__ __forceinline__ void ss_request_window(const SSParams& p, const aoto_stream_stage& st, const WindowShare& w,
                                                   int lane) {
-  if (w.head < 0 || w.old_keys <= 0 || lane != 0) return;
+  if (w.head < 0 || w.old_keys <= 0 || lane != 0 || p.L.long_window) return;
   const int D = p.a.head_dim, C = p.a.capacity;
   const bf16* kin = reinterpret_cast<const bf16*>(st.addend) + ((size_t)w.kvh * C + w.k0 + 1) * D;
   const bf16* vin = kin + (size_t)p.a.kv_heads * C * D;
@@ -608,11 +617,100 @@ __device__ __noinline__ void ss_move_window(const void* cache_in, void* cache_ou
   const uint4* src = reinterpret_cast<const uint4*>(cache_in);
   uint4* dst = reinterpret_cast<uint4*>(cache_out);
   const int per_plane = (capacity - 1) * chunks;
-  for (int plane = 0; plane < planes; ++plane) {
-    const size_t base = (size_t)plane * capacity * chunks;
-    for (int i = me * SS_THREADS + (int)threadIdx.x; i < per_plane; i += movers * SS_THREADS)
-      dst[base + i] = ldg_nc_u4(src + base + chunks + i);
+  const int total = planes * per_plane;  // one flat range: every mover takes an equal share of all planes
+#pragma unroll 2
+  for (int i = me * SS_THREADS + (int)threadIdx.x; i < total; i += movers * SS_THREADS) {
+    const int plane = i / per_plane;
+    const size_t at = (size_t)plane * capacity * chunks + (size_t)(i - plane * per_plane);
+    dst[at] = ldg_nc_u4(src + at + chunks);
   }
+}
+
+// A long window: the warp's keys in passes of sixteen (two lanes per key), rows read from L2 -
+// they were asked for when the stage began - with the running maximum, sum and weighted values
+// of an online softmax. Slot C - 1 is this step's key: its rows are in shared memory. Leaves
+// the warp's (m, l, sums) in its merge row like the short form.
+__device__ __noinline__ void ss_attend_long(const SSParams& p, const aoto_stream_stage& st, const WindowShare& w,
+                                            uint32_t qs, uint32_t weights, uint32_t mine) {
+  const int lane = threadIdx.x & 31;
+  const int D = p.a.head_dim, C = p.a.capacity;
+  const int half = lane & 1, half_chunks = D >> 4, dims = D >> 5;
+  const bf16* kplane = reinterpret_cast<const bf16*>(st.addend) + (size_t)w.kvh * C * D;  // new slot j = old slot j + 1
+  const bf16* vplane = kplane + (size_t)p.a.kv_heads * C * D;
+  const uint32_t qrow = qs + (uint32_t)half * (D >> 1) * 4;
+  float m = -INFINITY, l = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 1
+  for (int c0 = 0; c0 < w.nkeys; c0 += 16) {
+    const int key = c0 + (lane >> 1), slot = w.k0 + key;
+    bool attend = false;
+    if (key < w.nkeys) attend = p.a.window ? slot >= w.first_valid : p.a.mask[slot] != 0;
+    float s = -INFINITY;
+    if (attend) {
+      uint4 kk[8];
+      if (slot == C - 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (i < half_chunks) kk[i] = ss_lds128(w.new_key + (uint32_t)half * D + (uint32_t)i * 16);
+      } else {
+        const uint4* from = reinterpret_cast<const uint4*>(kplane + (size_t)(slot + 1) * D) + half * half_chunks;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (i < half_chunks) kk[i] = ldg_nc_u4(from + i);
+      }
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (i < half_chunks) {
+          const float4 qa = ss_lds128f(qrow + (uint32_t)i * 32), qb = ss_lds128f(qrow + (uint32_t)i * 32 + 16);
+          d0 = fmaf(bf16x2_lo(kk[i].x), qa.x, d0); d1 = fmaf(bf16x2_hi(kk[i].x), qa.y, d1);
+          d2 = fmaf(bf16x2_lo(kk[i].y), qa.z, d2); d3 = fmaf(bf16x2_hi(kk[i].y), qa.w, d3);
+          d0 = fmaf(bf16x2_lo(kk[i].z), qb.x, d0); d1 = fmaf(bf16x2_hi(kk[i].z), qb.y, d1);
+          d2 = fmaf(bf16x2_lo(kk[i].w), qb.z, d2); d3 = fmaf(bf16x2_hi(kk[i].w), qb.w, d3);
+        }
+      }
+      s = (d0 + d1) + (d2 + d3);
+    }
+    const float other = __shfl_xor_sync(0xffffffffu, s, 1);
+    s = attend ? s + other : -INFINITY;
+    const float m_new = fmaxf(m, ss_warp_max(s));
+    const float keep = m == -INFINITY ? 0.f : __expf(m - m_new);
+    const float e = s == -INFINITY ? 0.f : __expf(s - m_new);
+    if (half == 0) ss_stsf(weights + (uint32_t)(lane >> 1) * 4, e);
+    __syncwarp();
+    a0 *= keep; a1 *= keep; a2 *= keep; a3 *= keep; l *= keep;
+    const int count = min(16, w.nkeys - c0);
+    const int from_cache = max(0, min(count, C - 1 - (w.k0 + c0)));  // keys of this pass that are old slots
+    const bf16* vrow = vplane + (size_t)(w.k0 + c0 + 1) * D + lane * dims;
+#pragma unroll 2
+    for (int j = 0; j < from_cache; ++j) {
+      const float wt = ss_ldsf(weights + (uint32_t)j * 4);
+      if (dims == 4) {
+        const uint2 v = ldg_nc_u2(reinterpret_cast<const uint2*>(vrow + (size_t)j * D));
+        a0 = fmaf(wt, bf16x2_lo(v.x), a0); a1 = fmaf(wt, bf16x2_hi(v.x), a1);
+        a2 = fmaf(wt, bf16x2_lo(v.y), a2); a3 = fmaf(wt, bf16x2_hi(v.y), a3);
+      } else {
+        const uint32_t v = ldg_nc_u32(reinterpret_cast<const uint32_t*>(vrow + (size_t)j * D));
+        a0 = fmaf(wt, bf16x2_lo(v), a0); a1 = fmaf(wt, bf16x2_hi(v), a1);
+      }
+      l += wt;
+    }
+    if (from_cache < count) {  // this step's own value row
+      const float wt = ss_ldsf(weights + (uint32_t)from_cache * 4);
+      const uint32_t v0 = ss_lds32(w.new_value + (uint32_t)lane * dims * 2);
+      a0 = fmaf(wt, bf16x2_lo(v0), a0); a1 = fmaf(wt, bf16x2_hi(v0), a1);
+      if (dims == 4) {
+        const uint32_t v1 = ss_lds32(w.new_value + (uint32_t)lane * dims * 2 + 4);
+        a2 = fmaf(wt, bf16x2_lo(v1), a2); a3 = fmaf(wt, bf16x2_hi(v1), a3);
+      }
+      l += wt;
+    }
+    __syncwarp();  // the weights are read: the next pass may overwrite them
+    m = m_new;
+  }
+  if (lane == 0) { ss_stsf(mine, m); ss_stsf(mine + 4, l); }
+  ss_stsf(mine + 8 + (uint32_t)lane * dims * 4, a0);
+  ss_stsf(mine + 12 + (uint32_t)lane * dims * 4, a1);
+  if (dims == 4) { ss_stsf(mine + 16 + (uint32_t)lane * dims * 4, a2); ss_stsf(mine + 20 + (uint32_t)lane * dims * 4, a3); }
 }
 
 template <bool TRACE>
@@ -633,6 +731,17 @@ __device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_strea
   }
 
   const int pairs = D >> 1;
+  if (p.L.long_window && w.old_keys > 0) {
+    // a long window is read from L2: ask for this warp's rows now, the projection this stage
+    // waits for gives them the time to arrive
+    const unsigned char* kin = reinterpret_cast<const unsigned char*>(st.addend) + ((size_t)w.kvh * C + w.k0 + 1) * D * 2;
+    const unsigned char* vin = kin + (size_t)KVH * C * D * 2;
+    const int bytes = w.old_keys * D * 2;
+    for (int o = lane * 128; o < bytes; o += 32 * 128) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(kin + o));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(vin + o));
+    }
+  }
   __syncthreads();  // the previous stage's last readers of the work region are done
   const uint32_t rowv = ss_smem(smem + p.L.work);  // raw q head, k, v of the step: 3 * D floats
   const uint32_t qs = rowv + (uint32_t)3 * D * 4;  // rotated, scaled query: D floats
@@ -695,7 +804,9 @@ __device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_strea
   bool alive = true;
   if (kv_pending && w.old_keys > 0) alive = ss_mbar_wait(w.bar, kv_parity);
   if (TRACE) ss_trace(p, stage_index, 3);
-  {
+  if (p.L.long_window) {
+    ss_attend_long(p, st, w, qs, weights, merge + (uint32_t)warp * (D + 2) * 4);
+  } else {
     const int key = lane >> 1, half = lane & 1;
     const int half_chunks = D >> 4;  // 16-byte chunks of half a row
     float s = -INFINITY;
@@ -784,7 +895,7 @@ __device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_strea
   if (TRACE) ss_trace(p, stage_index, 6);
 
   // the next layer's window starts travelling: every warp is done with its buffers
-  if (st.next_attention >= 0) {
+  if (st.next_attention >= 0 && !p.L.long_window) {
     const aoto_stream_stage* all = reinterpret_cast<const aoto_stream_stage*>(smem + p.L.stages);
     ss_request_window(p, all[st.next_attention], w, lane);
     kv_pending = true;
@@ -898,7 +1009,7 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
   bool kv_pending = false;
   const aoto_stream_stage* stages = reinterpret_cast<const aoto_stream_stage*>(smem + p.L.stages);
   const WindowShare share = ss_window_share(p, warp, valid_length, smem);
-  if (p.a.first_attention >= 0) {
+  if (p.a.first_attention >= 0 && !p.L.long_window) {
     ss_request_window(p, stages[p.a.first_attention], share, lane);
     kv_pending = true;
   }
@@ -948,7 +1059,7 @@ static int ss_check(const aoto_stream_step_args& a, SSLayout* layout) {
     if (a.head_dim != 64 && a.head_dim != 128) return 0;
     if (a.kv_heads <= 0 || a.query_heads <= 0 || a.query_heads % a.kv_heads) return 0;
     if (a.query_heads > a.ctas || a.capacity < 2) return 0;
-    if ((a.capacity + SS_WARPS - 1) / SS_WARPS > SS_MAX_WINDOW_KEYS) return 0;  // longer windows need the split form
+    if (a.capacity > (1 << 20)) return 0;
     if (3 * (a.head_dim >> 1) > SS_THREADS) return 0;
     if ((a.query_start | a.key_start | a.value_start) & 1) return 0;
     if (a.table_rows <= 0) return 0;

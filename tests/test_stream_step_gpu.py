@@ -100,3 +100,48 @@ def test_streamed_kernel_with_wide_heads_and_long_rows(cuda):
     assert rel_err(streamed.final_cache(6), in_place.final_cache(6)) < REL_TOL
     want, _, _ = OracleRuntime(runtime).greedy(prompt, 7)
     assert runtime.greedy_generate(prompt).cpu()[0].tolist() == want
+
+
+@pytest.mark.parametrize("head_dim,prompt_length,new_tokens", [(64, 280, 25), (128, 300, 30), (64, 1000, 40)])
+def test_streamed_kernel_with_a_window_longer_than_its_buffers(cuda, head_dim, prompt_length, new_tokens):
+    """More than sixteen keys a warp: the window is read from L2 in passes with an online softmax.
+
+    Capacities 305, 330 and 1040 (20, 21 and 65 keys per warp, none a multiple of sixteen); the
+    step's own key is the last slot and comes from shared memory. Held to the kernel that reads
+    the weights in place over the whole generation, to the oracle on the first steps.
+    """
+
+    if head_dim == 64:
+        model = qwen25_05b_shaped(seed=12, layers=2, max_position_embeddings=2048)
+        compile_fn, vocab = aoto.compile_qwen2_static_cache, 151936
+    else:
+        model = SyntheticDecoder(
+            model_type="llama", vocab_size=32000, hidden_size=1024, intermediate_size=2816, num_hidden_layers=2,
+            num_attention_heads=8, num_key_value_heads=2, head_dim=128, max_position_embeddings=2048, rope_theta=5e5,
+            rms_norm_eps=1e-5, attention_bias=False, tie_word_embeddings=False, seed=23,
+        )
+        compile_fn, vocab = aoto.compile_llama_static_cache, 32000
+    runtime = compile_fn(model, prompt_length=prompt_length, max_new_tokens=new_tokens, quantize=64)
+    prompt = torch.randint(0, vocab, (1, prompt_length), generator=torch.Generator().manual_seed(18))
+    token, cache = start(runtime, prompt)
+    streamed, in_place = two_sessions(runtime)
+    steps = new_tokens - 1
+    a = streamed.run(token, cache, prompt_length, steps).cpu()
+    b = in_place.run(token, cache, prompt_length, steps).cpu()
+    assert a.tolist() == b.tolist()
+    assert rel_err(streamed.logits, in_place.logits) < REL_TOL
+    assert rel_err(streamed.final_cache(steps), in_place.final_cache(steps)) < REL_TOL
+    streamed.run(token, cache, prompt_length, 1)
+    assert torch.equal(streamed.final_cache(1)[:, :, :, :, :-1], cache[:, :, :, :, 1:])
+    if prompt_length <= 300:
+        want_tokens, trace, _ = OracleRuntime(runtime).greedy(prompt, 3)
+        assert a[:2].tolist() == want_tokens[1:3]
+        streamed.run(token, cache, prompt_length, 1)
+        # the oracle rounds to bf16 where the reference does, and one bf16 step of the largest logit is
+        # already 0.4-0.8 % of it: the yardstick is the oracle's own distance from the unrounded evaluation
+        exact, _ = OracleRuntime(runtime, unrounded=True).decode(token.cpu(), cache.cpu(), prompt_length + 1)
+        rounded, _ = OracleRuntime(runtime).decode(token.cpu(), cache.cpu(), prompt_length + 1)
+        floor = rel_err(rounded, exact)
+        assert rel_err(streamed.logits, exact) <= max(REL_TOL, 1.25 * floor), (rel_err(streamed.logits, exact), floor)
+        assert rel_err(streamed.logits, rounded) < 2.5 * REL_TOL
+        assert rel_err(streamed.logits, trace[1]) < 2.5 * REL_TOL
