@@ -39,7 +39,7 @@ struct SSLayout {
 __host__ __device__ inline uint32_t ss_align(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
 __host__ __device__ inline SSLayout ss_layout(int stage_count, int max_k, int depth, int capacity, int head_dim,
-                                              bool has_attention) {
+                                              bool has_attention, bool force_long = false) {
   SSLayout L;
   uint32_t off = 0;
   L.ring = off; off += (uint32_t)SS_WARPS * depth * SS_SLOT_BYTES;
@@ -63,7 +63,7 @@ __host__ __device__ inline SSLayout ss_layout(int stage_count, int max_k, int de
   L.red = off; off += 64 * 4;
   L.rotary = off; off += has_attention ? (uint32_t)head_dim * 4 : 0;  // cos row, sin row of the step's position
   L.keys_per_warp = has_attention ? (capacity + SS_WARPS - 1) / SS_WARPS : 0;
-  L.long_window = L.keys_per_warp > SS_MAX_WINDOW_KEYS;
+  L.long_window = has_attention && (force_long || L.keys_per_warp > SS_MAX_WINDOW_KEYS);
   L.kv = off;
   if (L.long_window) off += ss_align((uint32_t)2 * head_dim * 2, 16);
   else off += has_attention ? (uint32_t)SS_WARPS * 2 * L.keys_per_warp * head_dim * 2 : 0;
@@ -637,31 +637,51 @@ __device__ __noinline__ void ss_attend_long(const SSParams& p, const aoto_stream
   const int half = lane & 1, half_chunks = D >> 4, dims = D >> 5;
   const bf16* kplane = reinterpret_cast<const bf16*>(st.addend) + (size_t)w.kvh * C * D;  // new slot j = old slot j + 1
   const bf16* vplane = kplane + (size_t)p.a.kv_heads * C * D;
-  const uint32_t qrow = qs + (uint32_t)half * (D >> 1) * 4;
+  const uint32_t qrow = qs + (uint32_t)half * 32;  // the query values of this lane's chunks: eight floats every sixteen
   float m = -INFINITY, l = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll 1
   for (int c0 = 0; c0 < w.nkeys; c0 += 16) {
     const int key = c0 + (lane >> 1), slot = w.k0 + key;
     bool attend = false;
     if (key < w.nkeys) attend = p.a.window ? slot >= w.first_valid : p.a.mask[slot] != 0;
-    float s = -INFINITY;
+    // every load of the pass is issued before anything is computed: the key rows for the scores and
+    // the value rows (which do not depend on the scores) share one trip to L2
+    const int count = min(16, w.nkeys - c0);
+    const int from_cache = max(0, min(count, C - 1 - (w.k0 + c0)));  // keys of this pass that are old slots
+    uint4 kk[8];
+    uint2 vv[16];
     if (attend) {
-      uint4 kk[8];
       if (slot == C - 1) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          if (i < half_chunks) kk[i] = ss_lds128(w.new_key + (uint32_t)half * D + (uint32_t)i * 16);
+          if (i < half_chunks) kk[i] = ss_lds128(w.new_key + (uint32_t)(2 * i + half) * 16);
       } else {
-        const uint4* from = reinterpret_cast<const uint4*>(kplane + (size_t)(slot + 1) * D) + half * half_chunks;
+        // the two lanes of a key take alternate 16-byte chunks of its row: together they use every
+        // 32-byte sector they touch
+        const uint4* from = reinterpret_cast<const uint4*>(kplane + (size_t)(slot + 1) * D) + half;
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          if (i < half_chunks) kk[i] = ldg_nc_u4(from + i);
+          if (i < half_chunks) kk[i] = ldg_nc_u4(from + 2 * i);
       }
+    }
+    {
+      const bf16* vrow = vplane + (size_t)(w.k0 + c0 + 1) * D + lane * dims;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        vv[j] = make_uint2(0u, 0u);
+        if (j < from_cache) {
+          if (dims == 4) vv[j] = ldg_nc_u2(vrow + (size_t)j * D);
+          else vv[j].x = ldg_nc_u32(vrow + (size_t)j * D);
+        }
+      }
+    }
+    float s = -INFINITY;
+    if (attend) {
       float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         if (i < half_chunks) {
-          const float4 qa = ss_lds128f(qrow + (uint32_t)i * 32), qb = ss_lds128f(qrow + (uint32_t)i * 32 + 16);
+          const float4 qa = ss_lds128f(qrow + (uint32_t)i * 64), qb = ss_lds128f(qrow + (uint32_t)i * 64 + 16);
           d0 = fmaf(bf16x2_lo(kk[i].x), qa.x, d0); d1 = fmaf(bf16x2_hi(kk[i].x), qa.y, d1);
           d2 = fmaf(bf16x2_lo(kk[i].y), qa.z, d2); d3 = fmaf(bf16x2_hi(kk[i].y), qa.w, d3);
           d0 = fmaf(bf16x2_lo(kk[i].z), qb.x, d0); d1 = fmaf(bf16x2_hi(kk[i].z), qb.y, d1);
@@ -678,21 +698,14 @@ __device__ __noinline__ void ss_attend_long(const SSParams& p, const aoto_stream
     if (half == 0) ss_stsf(weights + (uint32_t)(lane >> 1) * 4, e);
     __syncwarp();
     a0 *= keep; a1 *= keep; a2 *= keep; a3 *= keep; l *= keep;
-    const int count = min(16, w.nkeys - c0);
-    const int from_cache = max(0, min(count, C - 1 - (w.k0 + c0)));  // keys of this pass that are old slots
-    const bf16* vrow = vplane + (size_t)(w.k0 + c0 + 1) * D + lane * dims;
-#pragma unroll 2
-    for (int j = 0; j < from_cache; ++j) {
-      const float wt = ss_ldsf(weights + (uint32_t)j * 4);
-      if (dims == 4) {
-        const uint2 v = ldg_nc_u2(reinterpret_cast<const uint2*>(vrow + (size_t)j * D));
-        a0 = fmaf(wt, bf16x2_lo(v.x), a0); a1 = fmaf(wt, bf16x2_hi(v.x), a1);
-        a2 = fmaf(wt, bf16x2_lo(v.y), a2); a3 = fmaf(wt, bf16x2_hi(v.y), a3);
-      } else {
-        const uint32_t v = ldg_nc_u32(reinterpret_cast<const uint32_t*>(vrow + (size_t)j * D));
-        a0 = fmaf(wt, bf16x2_lo(v), a0); a1 = fmaf(wt, bf16x2_hi(v), a1);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (j < from_cache) {
+        const float wt = ss_ldsf(weights + (uint32_t)j * 4);
+        a0 = fmaf(wt, bf16x2_lo(vv[j].x), a0); a1 = fmaf(wt, bf16x2_hi(vv[j].x), a1);
+        if (dims == 4) { a2 = fmaf(wt, bf16x2_lo(vv[j].y), a2); a3 = fmaf(wt, bf16x2_hi(vv[j].y), a3); }
+        l += wt;
       }
-      l += wt;
     }
     if (from_cache < count) {  // this step's own value row
       const float wt = ss_ldsf(weights + (uint32_t)from_cache * 4);
@@ -713,7 +726,7 @@ __device__ __noinline__ void ss_attend_long(const SSParams& p, const aoto_stream
   if (dims == 4) { ss_stsf(mine + 16 + (uint32_t)lane * dims * 4, a2); ss_stsf(mine + 20 + (uint32_t)lane * dims * 4, a3); }
 }
 
-template <bool TRACE>
+template <bool TRACE, bool LONG>
 __device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int stage_index,
                                              const WindowShare& w, uint32_t& kv_parity, bool& kv_pending,
                                              unsigned char* smem) {
@@ -731,7 +744,7 @@ __device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_strea
   }
 
   const int pairs = D >> 1;
-  if (p.L.long_window && w.old_keys > 0) {
+  if (LONG && w.old_keys > 0) {
     // a long window is read from L2: ask for this warp's rows now, the projection this stage
     // waits for gives them the time to arrive
     const unsigned char* kin = reinterpret_cast<const unsigned char*>(st.addend) + ((size_t)w.kvh * C + w.k0 + 1) * D * 2;
@@ -802,9 +815,9 @@ __device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_strea
   // every warp attends its keys: two lanes per key for the scores, the lanes split the head
   // dimension for the weighted sum of values
   bool alive = true;
-  if (kv_pending && w.old_keys > 0) alive = ss_mbar_wait(w.bar, kv_parity);
+  if (!LONG && kv_pending && w.old_keys > 0) alive = ss_mbar_wait(w.bar, kv_parity);
   if (TRACE) ss_trace(p, stage_index, 3);
-  if (p.L.long_window) {
+  if constexpr (LONG) {
     ss_attend_long(p, st, w, qs, weights, merge + (uint32_t)warp * (D + 2) * 4);
   } else {
     const int key = lane >> 1, half = lane & 1;
@@ -895,7 +908,7 @@ __device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_strea
   if (TRACE) ss_trace(p, stage_index, 6);
 
   // the next layer's window starts travelling: every warp is done with its buffers
-  if (st.next_attention >= 0 && !p.L.long_window) {
+  if (!LONG && st.next_attention >= 0) {
     const aoto_stream_stage* all = reinterpret_cast<const aoto_stream_stage*>(smem + p.L.stages);
     ss_request_window(p, all[st.next_attention], w, lane);
     kv_pending = true;
@@ -988,7 +1001,7 @@ __device__ __noinline__ void ss_start(const SSParams& p, unsigned char* smem, Wa
     if (i < depth && sizes[i] != 0) ss_request(p, ws, sizes[i], lane);
 }
 
-template <bool TRACE>
+template <bool TRACE, bool LONG>
 __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid_constant__ SSParams p) {
   extern __shared__ uint4 ss_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(ss_raw);
@@ -1009,7 +1022,7 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
   bool kv_pending = false;
   const aoto_stream_stage* stages = reinterpret_cast<const aoto_stream_stage*>(smem + p.L.stages);
   const WindowShare share = ss_window_share(p, warp, valid_length, smem);
-  if (p.a.first_attention >= 0 && !p.L.long_window) {
+  if (!LONG && p.a.first_attention >= 0) {
     ss_request_window(p, stages[p.a.first_attention], share, lane);
     kv_pending = true;
   }
@@ -1033,7 +1046,7 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
         ss_st_stamped(payload + (size_t)blockIdx.x * 16 + 8, 0x7fffffffu, p.a.epoch);
       }
     } else if (st.kind == AOTO_STAGE_ATTENTION) {
-      alive = ss_attention<TRACE>(p, st, s, share, kv_parity, kv_pending, smem);
+      alive = ss_attention<TRACE, LONG>(p, st, s, share, kv_parity, kv_pending, smem);
     } else if (st.kind == AOTO_STAGE_PICK) {
       ss_pick(p, s);
     }
@@ -1065,6 +1078,18 @@ static int ss_check(const aoto_stream_step_args& a, SSLayout* layout) {
     if (a.table_rows <= 0) return 0;
   }
   *layout = ss_layout(a.stage_count, a.max_k, a.ring_depth, a.capacity, a.head_dim, has_attention);
+  if (has_attention && !layout->long_window) {
+    // wide heads and long rows together can leave no room for the per-warp key / value buffers:
+    // the window is then read from L2 as a long one is
+    int device = 0, limit = 227 * 1024;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess) {
+      (void)cudaGetLastError();
+      limit = 227 * 1024;
+    }
+    if ((int64_t)layout->total > (int64_t)limit)
+      *layout = ss_layout(a.stage_count, a.max_k, a.ring_depth, a.capacity, a.head_dim, has_attention, true);
+  }
   return 1;
 }
 
@@ -1102,9 +1127,12 @@ extern "C" int aoto_sm100_stream_step(const aoto_stream_step_args* a, void* stre
   if (!coop || (int64_t)params.L.total > (int64_t)smem_limit) return AOTO_ERR_UNSUPPORTED;
   // two instantiations: the marks of the per-stage timeline cost issue slots, so the kernel that
   // serves requests carries none
-  auto kernel = a->trace != nullptr ? stream_step_kernel<true> : stream_step_kernel<false>;
-  static PerDeviceOnce raised_plain, raised_traced;
-  if (raise_dynamic_smem(kernel, (size_t)smem_limit, a->trace != nullptr ? raised_traced : raised_plain) != AOTO_OK)
+  // and two more for the window form, so that neither carries the other's code
+  const bool traced = a->trace != nullptr, lengthy = params.L.long_window != 0;
+  auto kernel = traced ? (lengthy ? stream_step_kernel<true, true> : stream_step_kernel<true, false>)
+                       : (lengthy ? stream_step_kernel<false, true> : stream_step_kernel<false, false>);
+  static PerDeviceOnce raised[4];
+  if (raise_dynamic_smem(kernel, (size_t)smem_limit, raised[(traced ? 2 : 0) + (lengthy ? 1 : 0)]) != AOTO_OK)
     return AOTO_ERR_LAUNCH;
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, SS_THREADS, params.L.total) != cudaSuccess ||

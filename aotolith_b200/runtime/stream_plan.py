@@ -467,7 +467,9 @@ def device_stream(program, tensors: dict, device: torch.device, ctas: int, ring_
     attention = [i for i, spec in enumerate(program.stages) if spec.kind == N.STAGE_ATTENTION]
     geo = geometry(program)
     heads = geo["query_heads"] if geo is not None else 0
-    dedicated = heads if attention and ctas >= 4 * heads else 0
+    # Head CTAs that take no projection work until the last attention stage shorten every layer's
+    # chain when the heads are few; with many heads the idle multipliers cost more than that saves.
+    dedicated = heads if attention and ctas >= 8 * heads else 0
     layout = layout_streams(shapes, len(program.stages) + 1, ctas, ring_depth, dedicated,
                             attention[-1] if attention else -1)
     stream = fill_stream(layout, shapes, weights, layout.table, device)

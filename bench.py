@@ -353,10 +353,15 @@ def run_ours(args) -> None:
     world, rank, device = start_ranks()
     local = device.index
 
-    model, spec = build_model(args.workload, seed=0)
+    # the 8B shape is drawn on the GPU (seconds instead of minutes on the host); its CPU arm is left out
+    on_device = WORKLOADS[args.workload]["family"] == "llama"
+    model, spec = build_model(args.workload, seed=0, device=device if on_device else "cpu")
     compile_fn = aoto.compile_qwen2_static_cache if spec["family"] == "qwen2" else aoto.compile_llama_static_cache
     runtime = compile_fn(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS, quantize=GROUP)
     config = model.config
+    if on_device:
+        model = None  # the bf16 original is not needed once the packed runtime exists
+        torch.cuda.empty_cache()
     prompt_host = seeded_prompt(config.vocab_size, 1 + rank).pin_memory()
     prompt_dev = prompt_host.to(device)
     session = decode_session(runtime)
@@ -476,9 +481,9 @@ def run_ours(args) -> None:
             else "per-operation decode plan (CUDA graph of one step)",
             "bound": "hbm", "achieved": achieved_step, "peak": peak, "unit": "GB/s",
             "frac": achieved_step / peak,
-            # ncu on the same kernel over a 4-layer cut of this model moved 109.3 MB of DRAM (104.58 read
-            # + 4.73 written) for 104.0 MB of algorithmic bytes; traffic grows with the layers like the bytes
-            "traffic": int(bytes_step * 109.31 / 104.0),
+            # ncu on the same kernel over a 4-layer cut of the 0.5B shape moved 110.77 MB of DRAM (105.68 read
+            # + 5.09 written) for 104.0 MB of algorithmic bytes; traffic grows with the layers like the bytes
+            "traffic": int(bytes_step * 110.77 / 104.0) if args.workload == "qwen25_05b" and kernel_name == "stream_step_kernel" else None,
             "bytes_per_launch": bytes_step, "us_per_launch": per_token_us,
             "frac_of_8tbs": achieved_step / 8000.0, "peak_source": peak_kind,
             "note": "launch duration = CUDA-event time of the decode loop / launches, inside the timed region",
@@ -492,9 +497,9 @@ def run_ours(args) -> None:
                 line["roofline"], line["step_roofline"] = lm_head, step_roofline
         line["prefill"] = prefill_stats
         line.update(extra)
-        if world == 1:
+        if world == 1 and args.workload == "qwen25_05b":
             line["qmatmul_sweep"] = qmatmul_sweep(device, peak, tensor_peak())
-        if world == 1 and not args.skip_cpu:
+        if world == 1 and not args.skip_cpu and not on_device:
             line["cpu_baseline"] = cpu_sample(model, prompt_host, 3)
         print(json.dumps(line))
     if world > 1:
@@ -866,7 +871,7 @@ def run_bucketed_share(args) -> None:
     print(json.dumps(share))
 
 
-def run_probe(name: str) -> None:
+def run_probe(name: str, probe_prompt: int = 0) -> None:
     """Small fixed cases for a profiler: a handful of launches of one kernel, a few GB at most.
 
     ``lm_head``  six packed GEMV launches over three copies of a [151936, 896] weight (RMS norm fused);
@@ -876,8 +881,11 @@ def run_probe(name: str) -> None:
     ``i8_decoder`` one request of the default workload with the decoder packed with eight bits;
     ``step``     a 4-layer Qwen2.5-0.5B-shaped decoder: prefill, then six launches of the step kernel;
     ``trace``    the same, then one more step with the kernel's own per-stage timeline printed;
-    ``trace_llama`` the timeline for a 2-layer cut of the Llama-3-8B shape (prompt 128).
+    ``trace_llama`` the timeline for a 2-layer cut of the Llama-3-8B shape (prompt 128);
+    ``trace_llama_long`` the same with the configuration's window (prompt 1024, 256 new tokens).
     """
+
+    global PROMPT, NEW_TOKENS
 
     from aotolith_b200 import ops
 
@@ -976,10 +984,12 @@ def run_probe(name: str) -> None:
         from aotolith_b200.models.session import decode_session
         from aotolith_b200.models.synthetic import qwen25_05b_shaped
 
-        if name == "trace_llama":
+        if name in ("trace_llama", "trace_llama_long"):
             from aotolith_b200.models.synthetic import llama3_8b_shaped
 
-            model = llama3_8b_shaped(seed=0, layers=2)
+            if name == "trace_llama_long":
+                PROMPT, NEW_TOKENS = (probe_prompt or 1024), 256
+            model = llama3_8b_shaped(seed=0, layers=2, device=device)
             runtime = aoto.compile_llama_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS, quantize=GROUP)
         else:
             model = qwen25_05b_shaped(seed=0, layers=4)
@@ -992,7 +1002,7 @@ def run_probe(name: str) -> None:
         tokens = session.run(token, cache, PROMPT, 6)
         torch.cuda.synchronize()
         print(json.dumps({"probe": name, "mode": session.mode, "tokens": tokens.tolist()}))
-        if name in ("trace", "trace_llama") and session.mode == "kernel":
+        if name in ("trace", "trace_llama", "trace_llama_long") and session.mode == "kernel":
             print_stage_trace(runtime, session, token, cache)
 
 
@@ -1006,8 +1016,10 @@ def main() -> None:
     parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
     parser.add_argument("--skip-multi", action="store_true",
                         help="with more than one GPU: leave the tensor-parallel and bucketed records out")
-    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "i8_decoder", "step", "trace", "trace_llama"), default=None,
+    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "i8_decoder", "step", "trace", "trace_llama",
+                                            "trace_llama_long"), default=None,
                         help="run a small fixed case of one kernel for a profiler instead of the benchmark")
+    parser.add_argument("--probe-prompt", type=int, default=0, help="with --probe trace_llama_long: another prompt length")
     parser.add_argument("--bucketed-share", default=None, metavar="RANK/WORLD",
                         help="internal: serve one GPU's share of the bucketed workload and print its figures")
     parser.add_argument("--requests-per-gpu", type=int, default=512, help="with --bucketed-share")
@@ -1016,7 +1028,7 @@ def main() -> None:
         run_bucketed_share(args)
         return
     if args.probe is not None:
-        run_probe(args.probe)
+        run_probe(args.probe, args.probe_prompt)
         return
     global PROMPT, NEW_TOKENS
     PROMPT = WORKLOADS[args.workload].get("prompt", PROMPT)
