@@ -28,10 +28,10 @@ from .models import (
     compile_qwen2_static_cache,
 )
 from .selection import KernelBenchmark, KernelSelection
-from .tensor_parallel import TensorParallelDecoder
+from .tensor_parallel import StreamedTensorParallelDecoder, TensorParallelDecoder
 
 __all__ = [
-    "TensorParallelDecoder", "ABI_VERSION", "FORMAT_VERSION", "load_compiled_module", "read_artifact_manifest", "save_compiled",
+    "TensorParallelDecoder", "StreamedTensorParallelDecoder", "ABI_VERSION", "FORMAT_VERSION", "load_compiled_module", "read_artifact_manifest", "save_compiled",
     "TARGETS", "Backend", "CudaBackend", "CompilationResult", "CompiledModulePlan", "DType",
     "Graph", "KernelBenchmark", "KernelSelection", "Operation", "TensorType", "Value",
     "backend_for", "compile_callable", "compile_graph", "compile_llama_bucketed",

@@ -177,12 +177,16 @@ class StreamStepArgs(Structure):
         ("token", c_void_p), ("generated", c_void_p), ("counters", c_void_p),
         ("generated_capacity", c_int32), ("window", c_int32),
         ("epoch", ctypes.c_uint32), ("reserved", c_int32),
-        ("status", c_void_p), ("scratch", c_void_p), ("scratch_bytes", c_int64), ("trace", c_void_p),
+        ("status", c_void_p), ("scratch", c_void_p), ("scratch_bytes", c_int64),
+        ("world", c_int32), ("rank", c_int32), ("peer_delta", c_int64 * 8), ("pick_exchange", c_void_p),
+        ("vocab_offset", c_int32), ("reserved2", c_int32),
+        ("trace", c_void_p),
     ]
 
 
 STAGE_GEMV, STAGE_ATTENTION, STAGE_PICK = 1, 2, 3
 STAGE_FLAG_ARGMAX, STAGE_FLAG_WINDOW, STAGE_FLAG_OUT_PLAIN, STAGE_FLAG_X_GATHER = 2, 4, 8, 16
+STAGE_FLAG_TO_PEERS, STAGE_FLAG_X_SUM, STAGE_FLAG_ADDEND_SUM = 32, 64, 128
 STAGE_ADDEND_NONE, STAGE_ADDEND_PLAIN, STAGE_ADDEND_STAMPED, STAGE_ADDEND_GATHER = 0, 1, 2, 3
 
 
@@ -221,6 +225,7 @@ EXPORTS: dict[str, tuple] = {
     "aoto_sm100_stamped_bytes": (c_int64, [c_int64]),
     "aoto_sm100_stream_step": (c_int, [POINTER(StreamStepArgs), c_void_p]),
     "aoto_sm100_stream_step_smem_bytes": (c_int64, [POINTER(StreamStepArgs)]),
+    "aoto_sm100_stream_args_size": (c_int, []),
     "aoto_sm100_stream_step_scratch_bytes": (c_int64, [c_int32]),
     "aoto_sm100_stream_stage_size": (c_int, []),
     "aoto_sm100_kv_cache_append": (c_int, [POINTER(KvAppendArgs), c_void_p]),
@@ -274,6 +279,12 @@ def load() -> ctypes.CDLL:
             raise DeviceError(
                 "the streamed-step stage descriptor of the kernel library and of this binding differ in size "
                 f"({lib.aoto_sm100_stream_stage_size()} vs {ctypes.sizeof(StreamStage)})",
+                hint="rebuild with `python -m aotolith_b200.csrc.build --force`",
+            )
+        if lib.aoto_sm100_stream_args_size() != ctypes.sizeof(StreamStepArgs):
+            raise DeviceError(
+                "the streamed-step arguments of the kernel library and of this binding differ in size "
+                f"({lib.aoto_sm100_stream_args_size()} vs {ctypes.sizeof(StreamStepArgs)})",
                 hint="rebuild with `python -m aotolith_b200.csrc.build --force`",
             )
         if lib.aoto_sm100_abi_version() != ABI_VERSION:

@@ -80,6 +80,22 @@ __device__ __forceinline__ void ss_st_stamped(void* ptr, uint32_t data, uint32_t
   const unsigned long long word = (unsigned long long)data | ((unsigned long long)stamp << 32);
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(ptr), "l"(word) : "memory");
 }
+// the same word for a reader on another GPU
+__device__ __forceinline__ void ss_st_stamped_sys(void* ptr, uint32_t data, uint32_t stamp) {
+  const unsigned long long word = (unsigned long long)data | ((unsigned long long)stamp << 32);
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(ptr), "l"(word) : "memory");
+}
+__device__ __forceinline__ uint4 ss_ld_stamped_pair_sys(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 ss_ld_stamped_sys(const void* ptr) {
+  unsigned long long word;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(ptr) : "memory");
+  return make_uint2((uint32_t)word, (uint32_t)(word >> 32));
+}
 __device__ __forceinline__ uint2 ss_ld_stamped(const void* ptr) {
   unsigned long long word;
   asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(word) : "l"(ptr) : "memory");
@@ -295,6 +311,23 @@ __device__ __noinline__ void ss_publish_best(const SSParams& p, float bv, int bi
   }
 }
 
+// Element n of a stamped addend, polled until it carries the epoch (`rows` > 1: the sum of the rows
+// of an exchanged vector, N values a row). False when the poll ran out.
+__device__ __noinline__ bool ss_stamped_addend(const void* addend, int n, int N, int rows, uint32_t epoch, float& value) {
+  float total = 0.f;
+  for (int r = 0; r < rows; ++r) {
+    const unsigned char* at = reinterpret_cast<const unsigned char*>(addend) + (size_t)r * ((size_t)N * 4) + (size_t)(n >> 1) * 8;
+    uint2 w = rows > 1 ? ss_ld_stamped_sys(at) : ss_ld_stamped(at);
+    for (int polls = 0; w.y != epoch; ++polls) {
+      if (polls > SS_POLL_LIMIT) return false;
+      w = rows > 1 ? ss_ld_stamped_sys(at) : ss_ld_stamped(at);
+    }
+    total += (n & 1) ? bf16x2_hi(w.x) : bf16x2_lo(w.x);
+  }
+  value = rows > 1 ? round_bf16(total) : total;
+  return true;
+}
+
 // Returns false when a wait ran out (every thread of the CTA gets the same answer).
 //
 // Only the work that must be done by every warp is done by every warp: the row is fetched,
@@ -347,12 +380,32 @@ __device__ __forceinline__ bool ss_gemv(const SSParams& p, const aoto_stream_sta
       if (gathers) {
         raw = ldg_nc_u4(reinterpret_cast<const uint4*>(words) + c);
       } else {
-        while (true) {
-          const uint4 a = ss_ld_stamped_pair(words + (size_t)c * 32), b = ss_ld_stamped_pair(words + (size_t)c * 32 + 16);
-          raw = make_uint4(a.x, a.z, b.x, b.z);
-          if (__all_sync(0xffffffffu, a.y == epoch && a.w == epoch && b.y == epoch && b.w == epoch)) break;
-          // a CTA that gave up elsewhere ends every other wait early
-          if (++rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0)) { failed = true; break; }
+        if (stage_flags & AOTO_STAGE_FLAG_X_SUM) {
+          // an exchanged vector: the chunk is the sum of every rank's row, added in rank order in fp32
+          // and rounded once (what an all-reduce of bf16 rows gives)
+          while (true) {
+            float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f, v4 = 0.f, v5 = 0.f, v6 = 0.f, v7 = 0.f;
+            bool here = true;
+#pragma unroll 1
+            for (int r = 0; r < p.a.world; ++r) {
+              const unsigned char* row = words + (size_t)r * ((size_t)K * 4) + (size_t)c * 32;
+              const uint4 a = ss_ld_stamped_pair_sys(row), b = ss_ld_stamped_pair_sys(row + 16);
+              here = here && a.y == epoch && a.w == epoch && b.y == epoch && b.w == epoch;
+              v0 += bf16x2_lo(a.x); v1 += bf16x2_hi(a.x); v2 += bf16x2_lo(a.z); v3 += bf16x2_hi(a.z);
+              v4 += bf16x2_lo(b.x); v5 += bf16x2_hi(b.x); v6 += bf16x2_lo(b.z); v7 += bf16x2_hi(b.z);
+            }
+            raw = make_uint4(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3), pack_bf16x2(v4, v5), pack_bf16x2(v6, v7));
+            if (__all_sync(0xffffffffu, here)) break;
+            if (++rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0)) { failed = true; break; }
+          }
+        } else {
+          while (true) {
+            const uint4 a = ss_ld_stamped_pair(words + (size_t)c * 32), b = ss_ld_stamped_pair(words + (size_t)c * 32 + 16);
+            raw = make_uint4(a.x, a.z, b.x, b.z);
+            if (__all_sync(0xffffffffu, a.y == epoch && a.w == epoch && b.y == epoch && b.w == epoch)) break;
+            // a CTA that gave up elsewhere ends every other wait early
+            if (++rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0)) { failed = true; break; }
+          }
         }
       }
       const uint32_t at = ss_chunk_address(xs, c);
@@ -375,13 +428,7 @@ __device__ __forceinline__ bool ss_gemv(const SSParams& p, const aoto_stream_sta
     const int n = min((tile0 + (int)(duty & 0x7FFFu)) * 16 + lane, N - 1);
     if (addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
       // an intermediate that was produced stages ago: its poll is a formality
-      const unsigned char* at = reinterpret_cast<const unsigned char*>(st.addend) + (size_t)(n >> 1) * 8;
-      uint2 w = ss_ld_stamped(at);
-      for (int polls = 0; w.y != epoch && alive; ++polls) {
-        if (polls > SS_POLL_LIMIT) alive = false;
-        w = ss_ld_stamped(at);
-      }
-      duty_addend = (n & 1) ? bf16x2_hi(w.x) : bf16x2_lo(w.x);
+      alive = ss_stamped_addend(st.addend, n, N, (stage_flags & AOTO_STAGE_FLAG_ADDEND_SUM) ? p.a.world : 1, epoch, duty_addend);
     } else {
       const size_t row = addend_mode == AOTO_STAGE_ADDEND_GATHER ? (size_t)gather_row * N : 0;
       duty_addend = ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + row + n);
@@ -482,9 +529,9 @@ __device__ __forceinline__ bool ss_gemv(const SSParams& p, const aoto_stream_sta
             // whole tiles carry a residual only in large models, where the load hides behind other warps
             const int n = min(finish_tile * 16 + lane, N - 1);
             if (addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
-              const uint2 w = ss_ld_stamped(reinterpret_cast<const unsigned char*>(st.addend) + (size_t)(n >> 1) * 8);
-              if (w.y != epoch) alive = false;  // produced stages ago: absent means something gave up
-              finish_addend = (n & 1) ? bf16x2_hi(w.x) : bf16x2_lo(w.x);
+              if (!ss_stamped_addend(st.addend, n, N, (stage_flags & AOTO_STAGE_FLAG_ADDEND_SUM) ? p.a.world : 1, epoch,
+                                     finish_addend))
+                alive = false;
             } else {
               const size_t row = addend_mode == AOTO_STAGE_ADDEND_GATHER ? (size_t)gather_row * N : 0;
               finish_addend = ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + row + n);
@@ -536,7 +583,16 @@ __device__ __forceinline__ bool ss_gemv(const SSParams& p, const aoto_stream_sta
           if (v != v) v = INFINITY;
           if (v > best.value || (v == best.value && n < best.index)) { best.value = v; best.index = n; }
         } else if ((lane & 1) == 0) {
-          ss_st_stamped(reinterpret_cast<unsigned char*>(st.out) + (size_t)(n >> 1) * 8, bits | (neighbour << 16), epoch);
+          unsigned char* at = reinterpret_cast<unsigned char*>(st.out) + (size_t)(n >> 1) * 8;
+          if (stage_flags & AOTO_STAGE_FLAG_TO_PEERS) {
+            // this rank's row of the exchanged vector, on every rank: plain 8-byte stores over NVLink,
+            // data and stamp in one word
+            at += (size_t)p.a.rank * ((size_t)N * 4);
+#pragma unroll 1
+            for (int q = 0; q < p.a.world; ++q) ss_st_stamped_sys(at + p.a.peer_delta[q], bits | (neighbour << 16), epoch);
+          } else {
+            ss_st_stamped(at, bits | (neighbour << 16), epoch);
+          }
         }
       }
       __syncwarp();  // a warp's own slot is read before its next whole tile overwrites it
@@ -948,6 +1004,40 @@ __device__ __noinline__ void ss_pick(const SSParams& p, int stage_index) {
     const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
     if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
   }
+  if (p.a.world > 1 && !failed) {
+    // every rank holds a slice of the vocabulary: the ranks' best (logit, index in the whole
+    // vocabulary) meet in every rank's exchange slots; the largest wins, the lowest index on ties
+    bi += p.a.vocab_offset;
+    unsigned char* slots = reinterpret_cast<unsigned char*>(p.a.pick_exchange);
+    if (threadIdx.x == 0) {
+#pragma unroll 1
+      for (int q = 0; q < p.a.world; ++q) {
+        unsigned char* at = slots + (size_t)p.a.rank * 16 + p.a.peer_delta[q];
+        ss_st_stamped_sys(at, __float_as_uint(bv), p.a.epoch);
+        ss_st_stamped_sys(at + 8, (uint32_t)bi, p.a.epoch);
+      }
+    }
+    bv = -INFINITY;
+    bi = 0x7fffffff;
+    if ((int)threadIdx.x < p.a.world) {
+      const unsigned char* at = slots + (size_t)threadIdx.x * 16;
+      uint2 a = ss_ld_stamped_sys(at), b = ss_ld_stamped_sys(at + 8);
+      for (int waits = 0; a.y != p.a.epoch || b.y != p.a.epoch; ++waits) {
+        if (waits > SS_POLL_LIMIT || ((waits & 255) == 255 && ss_ld_status(p.a.status) != 0)) { failed = true; break; }
+        a = ss_ld_stamped_sys(at);
+        b = ss_ld_stamped_sys(at + 8);
+      }
+      bv = __uint_as_float(a.x);
+      bi = (int)b.x;
+    }
+    failed = __any_sync(0xffffffffu, failed);
+#pragma unroll 1
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+  }
   if (threadIdx.x == 0 && !failed) {
     p.a.token[0] = (long long)bi;
     if (p.a.counters != nullptr) {
@@ -1067,6 +1157,7 @@ static int ss_check(const aoto_stream_step_args& a, SSLayout* layout) {
   if (a.stage_count <= 0 || a.stage_count >= (int)AOTO_STREAM_NO_STAGE || a.ctas <= 0 || a.ctas > 1024) return 0;
   if (a.ring_depth < 2 || a.ring_depth > AOTO_STREAM_MAX_RING) return 0;
   if (a.max_k <= 0 || a.max_k > SS_MAX_K || (a.max_k & 127)) return 0;
+  if (a.world < 0 || a.world > 8 || (a.world > 1 && (a.rank < 0 || a.rank >= a.world))) return 0;
   const bool has_attention = a.first_attention >= 0;
   if (has_attention) {
     if (a.head_dim != 64 && a.head_dim != 128) return 0;
@@ -1098,6 +1189,7 @@ static int ss_check(const aoto_stream_step_args& a, SSLayout* layout) {
 using namespace aoto;
 
 extern "C" int aoto_sm100_stream_stage_size(void) { return (int)sizeof(aoto_stream_stage); }
+extern "C" int aoto_sm100_stream_args_size(void) { return (int)sizeof(aoto_stream_step_args); }
 
 extern "C" int64_t aoto_sm100_stream_step_scratch_bytes(int32_t ctas) { return ctas > 0 ? (int64_t)ctas * 16 : 0; }
 
@@ -1115,6 +1207,12 @@ extern "C" int aoto_sm100_stream_step(const aoto_stream_step_args* a, void* stre
   if (a->scratch_bytes < aoto_sm100_stream_step_scratch_bytes(a->ctas)) return AOTO_ERR_ARGUMENT;
   SSParams params;
   params.a = *a;
+  if (params.a.world <= 1) {  // one GPU: nothing is exchanged
+    params.a.world = 1;
+    params.a.rank = 0;
+  } else if (!a->pick_exchange) {
+    return AOTO_ERR_ARGUMENT;
+  }
   if (!ss_check(*a, &params.L)) return AOTO_ERR_UNSUPPORTED;
   int device = 0, sms = 0, coop = 0, smem_limit = 0;
   if (cudaGetDevice(&device) != cudaSuccess) {

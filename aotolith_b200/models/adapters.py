@@ -287,7 +287,7 @@ class _QuantizedDecoder(torch.nn.Module):
 
     def _mlp_and_residuals(self, hidden: torch.Tensor, attended: torch.Tensor, index: int) -> torch.Tensor:
         batch, steps = hidden.shape[:2]
-        attended = attended.transpose(1, 2).reshape(batch, steps, self.hidden_size)
+        attended = attended.transpose(1, 2).reshape(batch, steps, self.num_heads * self.head_dim)
         hidden = hidden + F.linear(attended, self._weight("o_proj", index))
         normalized = self._norm(hidden, f"post_attention_norm_{index}")
         gate = F.linear(normalized, self._weight("gate_proj", index))

@@ -33,8 +33,12 @@ STREAM_STEP_DISABLED = False
 class DecodeSession:
     """Static buffers plus either the persistent step kernel or two recorded graphs."""
 
-    def __init__(self, runtime) -> None:
+    def __init__(self, runtime, parallel=None) -> None:
+        """``parallel`` (``tensor_parallel.ShardExchange``): the runtime is one rank's shard of a
+        tensor-parallel decoder; only the streamed kernel has a form for that."""
+
         self.runtime = runtime
+        self.parallel = parallel
         module_plan = runtime.decode
         self.plan = module_plan.plan
         self.device = torch.device(self.plan.device)
@@ -61,6 +65,9 @@ class DecodeSession:
         with torch.cuda.device(device):
             if self.plan.step_program is not None and self._bind_stream():
                 self.mode, self.kernel_name = "kernel", "stream_step_kernel"
+            elif parallel is not None:
+                raise DeviceError("the sharded decode step needs the streamed step kernel, which declined this program",
+                                  hint="group size 64, K a multiple of 128 and head_dim 64 or 128 are required")
             elif self.plan.step_program is not None and self._bind_program():
                 self.mode, self.kernel_name = "kernel", "decode_step_kernel"
             else:
@@ -115,9 +122,14 @@ class DecodeSession:
                     return self.caches[_source].data_ptr() + ref.offset
                 return tensors[ref.key].data_ptr() + ref.offset
 
-            stages = step_program.to_device(sp.stage_array(program, resolve), device)
+            array = sp.stage_array(program, resolve)
+            if self.parallel is not None:
+                self.parallel.route(array, len(program.stages))
+            stages = step_program.to_device(array, device)
             self.programs.append(stages)
             args = sp.base_args(program, ctas, depth)
+            if self.parallel is not None:
+                self.parallel.fill(args, program.vocab)
             args.stages = stages.data_ptr()
             args.cta_table, args.starts, args.duties = table.data_ptr(), starts.data_ptr(), duties.data_ptr()
             args.stream, args.stream_bytes = stream.data_ptr(), stream.numel()

@@ -70,6 +70,7 @@ def _bf16(tensor: torch.Tensor | None, name: str) -> None:
 
 
 _WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+_RETIRED_WORKSPACES: list[torch.Tensor] = []
 
 
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
@@ -84,13 +85,18 @@ def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     recorded launches get a buffer of their own: its zero fill becomes a node of
     the graph that first needed it (and runs again with every replay, which is
     harmless), and the registry keeps the buffer alive after that graph is gone,
-    so later recordings on the same stream can go on using it.
+    so later recordings on the same stream can go on using it. A buffer that has to
+    grow is replaced, never freed: graphs recorded earlier still hold its address
+    (sizes grow geometrically with the largest request, so what is kept stays small).
     """
 
     key = (device.index if device.index is not None else torch.cuda.current_device(),
            torch.cuda.current_stream(device).cuda_stream)
     buffer = _WORKSPACES.get(key)
     if buffer is None or buffer.numel() < nbytes:
+        if buffer is not None:
+            _RETIRED_WORKSPACES.append(buffer)
+            nbytes = max(nbytes, 2 * buffer.numel())
         buffer = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _WORKSPACES[key] = buffer
     return buffer

@@ -309,15 +309,241 @@ class TensorParallelDecoder:
             self._record()
         logits = self.prefill(ids)
         first = self.ops.argmax(logits).reshape(1, 1)
-        self.token.copy_(first)
+        return torch.cat((first, self.decode_after_prefill(first, steps - 1, use_graphs).reshape(1, -1)), dim=1)
+
+    def decode_after_prefill(self, first: torch.Tensor, steps: int, use_graphs: bool = True) -> torch.Tensor:
+        """``steps`` greedy tokens after ``first`` (the prompt's caches are in buffer 0); int64 ``[steps]``."""
+
+        if use_graphs and not self.graphs:
+            self._record()
+        self.token.copy_(first.reshape(1, 1))
         self.counters.copy_(torch.tensor([self.prompt_length + 1, 0], dtype=torch.int32).pin_memory(), non_blocking=True)
-        for step in range(steps - 1):
+        for step in range(steps):
             if use_graphs:
                 self.graphs[step & 1].replay()
             else:
                 self._step(step & 1)
-        return torch.cat((first, self.generated[:steps - 1].reshape(1, -1)), dim=1)
+        return self.generated[:steps]
 
+
+
+# ---------------------------------------------------------------------------
+# the sharded decode step as ONE kernel per rank: compute and exchange in the same launch
+# ---------------------------------------------------------------------------
+
+class _ShardConfig:
+    """Config of one rank's shard: the model's, with the local head counts and MLP width."""
+
+    def __init__(self, config, **changes) -> None:
+        for name in dir(config):
+            if not name.startswith("_") and not callable(getattr(config, name, None)):
+                try:
+                    setattr(self, name, getattr(config, name))
+                except AttributeError:
+                    pass
+        for name, value in changes.items():
+            setattr(self, name, value)
+
+
+def shard_module(model: torch.nn.Module, world: int, rank: int, group_size: int) -> torch.nn.Module:
+    """One rank's shard of ``model`` as a decoder of its own (the module tree the adapters read).
+
+    ``QH/world`` query heads and ``KVH/world`` key/value heads (rows of q/k/v, columns of o),
+    ``I/world`` rows of gate and up (columns of down), ``V/world`` rows of the LM head; embeddings and
+    norms whole. Compiled like any decoder, it computes this rank's PARTIAL o and down products
+    (their K is split), which is why its decode step only makes sense with the exchange of
+    :class:`ShardExchange`. Weights are views of ``model``'s where the slice is contiguous.
+    """
+
+    from torch import nn
+
+    config = model.config
+    heads, kv_heads = int(config.num_attention_heads), int(config.num_key_value_heads)
+    head_dim = int(getattr(config, "head_dim", None) or config.hidden_size // heads)
+    check_divisible("query heads", heads, world)
+    check_divisible("key/value heads", kv_heads, world)
+    check_divisible("MLP width", int(config.intermediate_size), world, group_size)
+    check_divisible("attention width", heads * head_dim, world, group_size)
+    check_divisible("vocabulary", int(config.vocab_size), world)
+
+    def linear(weight: torch.Tensor, bias: torch.Tensor | None = None) -> nn.Module:
+        layer = nn.Module()
+        layer.weight = nn.Parameter(weight.detach().contiguous(), requires_grad=False)
+        layer.bias = None if bias is None else nn.Parameter(bias.detach().contiguous(), requires_grad=False)
+        return layer
+
+    def norm(source: nn.Module) -> nn.Module:
+        layer = nn.Module()
+        layer.weight = nn.Parameter(source.weight.detach(), requires_grad=False)
+        return layer
+
+    shard = nn.Module()
+    shard.config = _ShardConfig(
+        config, num_attention_heads=heads // world, num_key_value_heads=kv_heads // world, head_dim=head_dim,
+        intermediate_size=int(config.intermediate_size) // world, tie_word_embeddings=False)
+    shard.model = nn.Module()
+    shard.model.embed_tokens = nn.Module()
+    shard.model.embed_tokens.weight = nn.Parameter(model.model.embed_tokens.weight.detach(), requires_grad=False)
+    shard.model.norm = norm(model.model.norm)
+    shard.lm_head = linear(rows_of(model.lm_head.weight, world, rank))
+    layers = []
+    q_share, kv_share = heads // world * head_dim, kv_heads // world * head_dim
+    for layer in model.model.layers:
+        attention, mlp = layer.self_attn, layer.mlp
+        block, attn, feed = nn.Module(), nn.Module(), nn.Module()
+
+        def rows(projection, share):
+            bias = None if projection.bias is None else projection.bias[rank * share:(rank + 1) * share]
+            return linear(projection.weight[rank * share:(rank + 1) * share], bias)
+
+        attn.q_proj, attn.k_proj, attn.v_proj = rows(attention.q_proj, q_share), rows(attention.k_proj, kv_share), rows(attention.v_proj, kv_share)
+        attn.o_proj = linear(columns_of(attention.o_proj.weight, world, rank, group_size))
+        feed.gate_proj = linear(rows_of(mlp.gate_proj.weight, world, rank))
+        feed.up_proj = linear(rows_of(mlp.up_proj.weight, world, rank))
+        feed.down_proj = linear(columns_of(mlp.down_proj.weight, world, rank, group_size))
+        feed.act_fn = getattr(mlp, "act_fn", None)
+        block.self_attn, block.mlp = attn, feed
+        block.input_layernorm, block.post_attention_layernorm = norm(layer.input_layernorm), norm(layer.post_attention_layernorm)
+        layers.append(block)
+    shard.model.layers = nn.ModuleList(layers)
+    return shard.eval()
+
+
+def route_exchange(array, stages: int, base: int, vector_bytes: int, row_bytes: int, rank: int) -> int:
+    """Turn the residual stages of a shard's stage array into exchanged ones; returns how many.
+
+    A GEMV stage that adds a residual (stamped or gathered addend) is an o or down projection: its
+    result moves to the next free exchanged vector at ``base`` and is flagged ``TO_PEERS``; every
+    later stage that read the old place as its input gets ``X_SUM``, as its stamped addend
+    ``ADDEND_SUM``. Ranks other than 0 drop the residual: it enters the sum once.
+    """
+
+    from . import _native as N
+
+    moved: dict[int, int] = {}
+    used = 0
+    for index in range(stages):
+        stage = array[index]
+        if stage.kind != N.STAGE_GEMV:
+            continue
+        if stage.x is not None and int(stage.x) in moved and not stage.flags & N.STAGE_FLAG_X_GATHER:
+            stage.x = moved[int(stage.x)]
+            stage.flags |= N.STAGE_FLAG_X_SUM
+        if stage.addend_mode in (N.STAGE_ADDEND_STAMPED, N.STAGE_ADDEND_GATHER):
+            if stage.N * 4 != row_bytes or stage.flags & N.STAGE_FLAG_OUT_PLAIN:
+                raise CompilationError("a residual stage of the shard does not produce a hidden-state row")
+            if stage.addend_mode == N.STAGE_ADDEND_STAMPED and int(stage.addend) in moved:
+                stage.addend = moved[int(stage.addend)]
+                stage.flags |= N.STAGE_FLAG_ADDEND_SUM
+            if rank != 0:
+                stage.addend_mode = N.STAGE_ADDEND_NONE
+                stage.flags &= ~N.STAGE_FLAG_ADDEND_SUM
+            moved[int(stage.out)] = base + used * vector_bytes
+            stage.out = base + used * vector_bytes
+            stage.flags |= N.STAGE_FLAG_TO_PEERS
+            used += 1
+    return used
+
+
+class ShardExchange:
+    """Buffers and rewiring that turn a shard's stage program into this rank's part of a sharded step.
+
+    The o and down projections of a shard are partial products (their K is split over the ranks).
+    In the stage program they are the GEMV stages that add a residual. Their results become
+    *exchanged vectors*: ``world`` rows of stamped words in a buffer every peer can store into
+    (torch symmetric memory); a stage writes its row on EVERY rank, the stages that read the
+    vector add its rows while they stage it. The residual enters the sum once (rank 0). The ranks'
+    best logits meet the same way in the pick stage. No library collective runs in the step.
+    """
+
+    def __init__(self, hidden: int, stages: int, *, group: Any = None, device: Any = None) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.row_bytes = hidden * 4                      # a row of an exchanged vector: hidden / 2 words
+        self.vector_bytes = (self.world * self.row_bytes + 255) // 256 * 256
+        self.vectors = stages                            # upper bound: one per stage
+        self.pick_offset = self.vectors * self.vector_bytes
+        nbytes = self.pick_offset + 256
+        self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.buffer.zero_()
+        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        pointers = [int(p) for p in self.handle.buffer_ptrs]
+        if len(pointers) != self.world or any(p == 0 for p in pointers):
+            raise CompilationError("symmetric memory did not return one mapped buffer per rank")
+        self.deltas = [p - pointers[self.rank] for p in pointers]
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)  # every buffer is zero before any rank stores into it
+
+    def route(self, array, stages: int) -> None:
+        """Rewire one stage array (one cache direction) in place."""
+
+        used = route_exchange(array, stages, self.buffer.data_ptr(), self.vector_bytes, self.row_bytes, self.rank)
+        if used > self.vectors:
+            raise CompilationError("more exchanged vectors than the exchange buffer holds")
+
+    def fill(self, args, local_vocab: int) -> None:
+        args.world, args.rank = self.world, self.rank
+        for q, delta in enumerate(self.deltas):
+            args.peer_delta[q] = delta
+        args.pick_exchange = self.buffer.data_ptr() + self.pick_offset
+        args.vocab_offset = self.rank * local_vocab
+
+
+class StreamedTensorParallelDecoder(TensorParallelDecoder):
+    """Tensor-parallel greedy decoding whose decode step is ONE kernel per rank.
+
+    Prefill is the per-operation path of :class:`TensorParallelDecoder` (NCCL all-reduces of the
+    prompt rows). A decode step is one cooperative launch of the streamed step kernel over this
+    rank's shard: the o and down stages store their partial rows straight into every peer's
+    exchange buffer over NVLink, the stages that consume them add the rows while staging, the
+    ranks' best logits meet in the pick stage - compute and exchange overlap tile by tile, and no
+    collective kernel is launched.
+    """
+
+    def __init__(self, model: torch.nn.Module, *, prompt_length: int, max_new_tokens: int, group_size: int = 64,
+                 world: int | None = None, rank: int | None = None, device: Any = None, group: Any = None) -> None:
+        super().__init__(model, prompt_length=prompt_length, max_new_tokens=max_new_tokens, group_size=group_size,
+                         world=world, rank=rank, device=device, group=group, peer_exchange=False)
+        from .models.adapters import family_for
+        from .models.decoder import compile_decoder_static_cache
+        from .models.session import DecodeSession
+
+        with torch.cuda.device(self.device):
+            shard = shard_module(model, self.world, self.rank, self.group_size)
+            self.shard_runtime = compile_decoder_static_cache(
+                shard, prompt_length=prompt_length, max_new_tokens=max_new_tokens, quantize=self.group_size,
+                family=family_for(model).name)
+            del shard
+            program = self.shard_runtime.decode.plan.step_program
+            if program is None:
+                raise CompilationError("the shard's decode graph has no stage program")
+            self.exchange = None
+            if self.world > 1:
+                self.exchange = ShardExchange(self.hidden, len(program.stages), group=group, device=self.device)
+            self.session = DecodeSession(self.shard_runtime, parallel=self.exchange)
+        # the per-operation copies of the shards are only needed by prefill; the step has its streams
+        self.graphs = []
+
+    def greedy_generate(self, ids: torch.Tensor, *, max_new_tokens: int | None = None, use_graphs: bool = True) -> torch.Tensor:
+        steps = self.max_new_tokens if max_new_tokens is None else int(max_new_tokens)
+        if not 0 < steps <= self.max_new_tokens:
+            raise PlanInputError(f"max_new_tokens must be in [1, {self.max_new_tokens}], got {steps}")
+        logits = self.prefill(ids)
+        first = self.ops.argmax(logits).reshape(1, 1)
+        return torch.cat((first, self.decode_after_prefill(first, steps - 1).reshape(1, -1)), dim=1)
+
+    def decode_after_prefill(self, first: torch.Tensor, steps: int, use_graphs: bool = True) -> torch.Tensor:
+        return self.session.run(first.reshape(1, 1), self.caches[0], self.prompt_length, steps)
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(self.group)  # no rank frees its exchange buffer while a peer may still store into it
+        self.session = None
+        self.exchange = None
 
 
 class TensorParallelRuntime:

@@ -576,24 +576,29 @@ def start_ranks():
     return world, rank, device
 
 
-def measure_tp(world: int, rank: int, device, steps: int, warmup: int, with_clocks: bool = True) -> dict | None:
+def measure_tp(world: int, rank: int, device, steps: int, warmup: int, with_clocks: bool = True,
+               streamed: bool = True) -> dict | None:
     """One request stream, the Llama-3-8B shape sharded over all ranks (strong scaling).
 
     Every rank draws the same seeded model on its own GPU and packs only its shard. A step is
-    one request: prefill of 1024 tokens, then 255 replays of the recorded decode step (this
-    library's kernels plus two peer-memory sums per layer). Returns the record on rank 0.
+    one request: prefill of 1024 tokens (per-operation kernels, NCCL all-reduces of the prompt
+    rows), then 255 decode steps. ``streamed``: a step is ONE launch per rank of the streamed step
+    kernel, which stores the partial o/down rows into every peer's exchange buffer and adds them
+    where they are consumed; otherwise the recorded per-operation step with two peer-memory sums
+    per layer. Returns the record on rank 0.
     """
 
     import torch.distributed as dist
 
     from aotolith_b200 import replicas
-    from aotolith_b200.tensor_parallel import TensorParallelDecoder
+    from aotolith_b200.tensor_parallel import StreamedTensorParallelDecoder, TensorParallelDecoder
 
     spec = WORKLOADS["llama3_8b_tp"]
     prompt_length, new_tokens = spec["prompt"], spec["new_tokens"]
     model, _ = build_model("llama3_8b_tp", seed=0, device=device)
-    decoder = TensorParallelDecoder(model, prompt_length=prompt_length, max_new_tokens=new_tokens, group_size=GROUP,
-                                    world=world, rank=rank, device=device)
+    kind = StreamedTensorParallelDecoder if streamed else TensorParallelDecoder
+    decoder = kind(model, prompt_length=prompt_length, max_new_tokens=new_tokens, group_size=GROUP,
+                   world=world, rank=rank, device=device)
     config = model.config
     del model
     torch.cuda.empty_cache()
@@ -615,13 +620,10 @@ def measure_tp(world: int, rank: int, device, steps: int, warmup: int, with_cloc
         marks[0].record()
         logits = decoder.prefill(prompt)
         first = decoder.ops.argmax(logits).reshape(1, 1)
-        decoder.token.copy_(first)
-        decoder.counters.copy_(torch.tensor([prompt_length + 1, 0], dtype=torch.int32).pin_memory(), non_blocking=True)
         marks[1].record()
-        for step in range(decode_steps):
-            decoder.graphs[step & 1].replay()
+        rest = decoder.decode_after_prefill(first, decode_steps)
         marks[2].record()
-        tokens_host = decoder.generated[:decode_steps].cpu()
+        tokens_host = rest.cpu()
         prefill_ms += marks[0].elapsed_time(marks[1])
         decode_ms += marks[1].elapsed_time(marks[2])
     e2e_wall = time.perf_counter() - e2e_start
@@ -646,8 +648,9 @@ def measure_tp(world: int, rank: int, device, steps: int, warmup: int, with_cloc
         "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": e2e_ms / steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (model drawn on the device from a seed)",
-        "config": {"workload": spec["description"], "parallelism": f"tp{world}: column-split q/k/v, gate, up and LM head; "
-                   "row-split o and down; two peer-memory sums per layer inside the recorded step, NCCL in prefill",
+        "config": {"workload": spec["description"], "parallelism": f"tp{world}: column-split q/k/v, gate, up and LM head; row-split o and down; "
+                   + ("decode step = one streamed-step kernel per rank with peer stores of the partial rows, "
+                      if streamed else "two peer-memory sums per layer inside the recorded step, ") + "NCCL in prefill",
                    "step": f"one request: prefill({prompt_length}) + {decode_steps} decode steps; value counts the decode loop only",
                    "l2": f"inputs larger than L2: {bytes_step / world / 1e6:.0f} MB of packed weights per GPU and token"},
         "decode_us_per_token": per_token_us,
@@ -655,7 +658,8 @@ def measure_tp(world: int, rank: int, device, steps: int, warmup: int, with_cloc
         "e2e": {"value": steps * new_tokens / (e2e_ms / 1e3), "unit": "tok/s",
                 "h2d_bytes_per_step": prompt_length * 8, "d2h_bytes_per_step": new_tokens * 8},
         "clocks": clocks,
-        "roofline": {"kernel": "recorded decode step (per-operation kernels + peer-memory sums)", "bound": "hbm",
+        "roofline": {"kernel": "stream_step_kernel with peer stores (one launch per rank and token)" if streamed
+                     else "recorded decode step (per-operation kernels + peer-memory sums)", "bound": "hbm",
                      "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world),
                      "traffic": None, "bytes_per_launch": bytes_step, "us_per_launch": per_token_us,
                      "peak_source": peak_kind, "note": "whole-job bytes over whole-job peak (all GPUs)"},
@@ -666,7 +670,8 @@ def check_tp_parity(world: int, rank: int, device) -> dict | None:
     """The sharded decoder against the same decoder on one rank, before anything sharded is timed.
 
     A 2-layer cut of the Llama-3-8B shape (prompt 128, 16 greedy tokens), drawn from one seed on
-    every rank. All ranks run the sharded decoder; rank 0 also runs the unsharded one step by step
+    every rank. All ranks run the sharded decoder (per-operation prefill, streamed step kernel with
+    peer stores for the steps); rank 0 also runs the unsharded per-operation one step by step
     and compares: the prompt's logits within 2e-2 of max|logit|, and token for token - a differing
     token must be a near-tie of the unsharded logits (gap within the same 2e-2), after which the
     sequences are no longer comparable. Why 2e-2: both sides are bf16 evaluations of the same
@@ -677,12 +682,12 @@ def check_tp_parity(world: int, rank: int, device) -> dict | None:
 
     import torch.distributed as dist
 
-    from aotolith_b200.tensor_parallel import TensorParallelDecoder
+    from aotolith_b200.tensor_parallel import StreamedTensorParallelDecoder, TensorParallelDecoder
 
     prompt_length, new_tokens, tolerance = 128, 16, 2e-2
     model, _ = build_model("llama3_8b", seed=3, device=device, layers=2)
-    sharded = TensorParallelDecoder(model, prompt_length=prompt_length, max_new_tokens=new_tokens, group_size=GROUP,
-                                    world=world, rank=rank, device=device)
+    sharded = StreamedTensorParallelDecoder(model, prompt_length=prompt_length, max_new_tokens=new_tokens,
+                                            group_size=GROUP, world=world, rank=rank, device=device)
     prompt = seeded_prompt(model.config.vocab_size, 5, prompt_length)
     got_logits = sharded.prefill(prompt).float().clone()
     got = sharded.greedy_generate(prompt).reshape(-1).tolist()
@@ -711,7 +716,7 @@ def check_tp_parity(world: int, rank: int, device) -> dict | None:
                 logits = single.logits.float().clone()
         ok = prefill_error <= tolerance and (tie_gap is None or tie_gap <= tolerance)
         record = {"workload": f"2-layer cut of the Llama-3-8B shape, prompt {prompt_length}, {new_tokens} greedy tokens, "
-                              f"tp{world} against one rank",
+                              f"tp{world} (streamed step kernel with peer stores) against one rank (per-operation kernels)",
                   "prefill_logits_error": prefill_error, "tolerance": tolerance, "tokens_compared": new_tokens,
                   "tokens_matched": matched, "near_tie_gap_at_first_difference": tie_gap, "ok": ok}
         single.close()

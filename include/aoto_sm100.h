@@ -449,6 +449,13 @@ int64_t aoto_sm100_peer_sum_buffer_bytes(int32_t world, int32_t capacity_words);
                                        the input (an embedding folded into the projection)          */
 
 /* how a GEMV stage reads its addend */
+/* Tensor-parallel forms (streamed step kernel only). An exchanged vector of N values is `world`
+ * rows of N/2 stamped words, row r written by rank r; every GPU holds all rows in a buffer its
+ * peers can store into. */
+#define AOTO_STAGE_FLAG_TO_PEERS 32   /* GEMV: `out` is row 0 of an exchanged vector: this rank's result goes
+                                         to row `rank` of the vector on EVERY rank (peer stores)            */
+#define AOTO_STAGE_FLAG_X_SUM 64      /* GEMV: `x` is an exchanged vector: the input is the sum of its rows  */
+#define AOTO_STAGE_FLAG_ADDEND_SUM 128 /* GEMV: the stamped addend is an exchanged vector: sum of its rows   */
 #define AOTO_STAGE_ADDEND_NONE 0
 #define AOTO_STAGE_ADDEND_PLAIN 1   /* constant bf16 vector (a bias)                                */
 #define AOTO_STAGE_ADDEND_STAMPED 2 /* an intermediate in the arena                                 */
@@ -646,6 +653,16 @@ typedef struct aoto_stream_step_args {
   int32_t* status;
   void* scratch;                        /* per-CTA maxima of the ARGMAX stage: 16 bytes per CTA    */
   int64_t scratch_bytes;
+  /* tensor parallelism: one process per GPU runs the same program over its shard. `world` = 1 and
+     everything below zero for a single GPU. peer_delta[q] = (base of rank q's exchange buffer as
+     mapped in this process) - (base of this rank's), so that a local address of the buffer plus
+     peer_delta[q] is the same place on rank q; peer_delta[rank] = 0. Plain stores, no multimem.  */
+  int32_t world, rank;
+  int64_t peer_delta[8];
+  void* pick_exchange;                  /* in the exchange buffer: `world` slots of 16 bytes, slot r = rank
+                                           r's best (logit, global index) of the step                 */
+  int32_t vocab_offset;                 /* index of this rank's first logit in the whole vocabulary   */
+  int32_t reserved2;
   uint64_t* trace;                      /* optional, uint64[ctas * stage_count * 8]: every CTA's
                                            %globaltimer (ns) at eight points of every stage it works in
                                            (GEMV: 0 reached, 1-2 row complete, 3 row staged, 4 first piece
@@ -663,6 +680,7 @@ int aoto_sm100_stream_step(const aoto_stream_step_args* args, void* stream);
 int64_t aoto_sm100_stream_step_smem_bytes(const aoto_stream_step_args* args);
 int64_t aoto_sm100_stream_step_scratch_bytes(int32_t ctas);
 int aoto_sm100_stream_stage_size(void); /* sizeof(aoto_stream_stage), for binding checks */
+int aoto_sm100_stream_args_size(void);  /* sizeof(aoto_stream_step_args), for binding checks */
 
 #ifdef __cplusplus
 }

@@ -124,6 +124,36 @@ def test_world_of_one_matches_the_compiled_runtime(cuda):
     assert torch.equal(eager, want) and torch.equal(replayed, want)
 
 
+def _wide():
+    """Small, but with the group size and row lengths the step kernels take (group 64, K multiples of 128)."""
+
+    from aotolith_b200.models.synthetic import SyntheticDecoder
+
+    return SyntheticDecoder(model_type="llama", vocab_size=1024, hidden_size=512, intermediate_size=1024,
+                            num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=4, head_dim=64,
+                            max_position_embeddings=64, rope_theta=5e5, rms_norm_eps=1e-5, seed=5)
+
+
+def _wide_prompt():
+    return torch.randint(0, 1024, (1, PROMPT), generator=torch.Generator().manual_seed(4))
+
+
+@pytest.mark.gpu
+def test_streamed_decoder_of_one_rank_matches_the_compiled_runtime(cuda):
+    """The shard of a world of one is the whole model: the streamed decoder is the compiled runtime."""
+
+    import aotolith_b200 as aoto
+
+    model = _wide()
+    runtime = aoto.compile_llama_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW, quantize=64)
+    want = runtime.greedy_generate(_wide_prompt()).cpu()
+    decoder = tp.StreamedTensorParallelDecoder(model, prompt_length=PROMPT, max_new_tokens=NEW, group_size=64,
+                                               world=1, rank=0, device=cuda)
+    assert decoder.session.kernel_name == "stream_step_kernel"
+    assert torch.equal(decoder.greedy_generate(_wide_prompt()).cpu(), want)
+    decoder.close()
+
+
 def _gpu_rank(rank, world, port, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
@@ -150,12 +180,27 @@ def _gpu_rank(rank, world, port, out_dir):
                                                   tensor_parallel=dist.group.WORLD)
         assert (runtime.world, runtime.rank, runtime.cache_capacity) == (world, rank, PROMPT + NEW)
         compiled_tokens = runtime.greedy_generate(_prompt()).cpu()
+        # the decode step as ONE kernel per rank that stores its partial rows into the peers
+        wide = _wide()
+        per_operation = tp.TensorParallelDecoder(wide, prompt_length=PROMPT, max_new_tokens=NEW, group_size=64)
+        wide_tokens = per_operation.greedy_generate(_wide_prompt()).cpu()
+        streamed = tp.StreamedTensorParallelDecoder(wide, prompt_length=PROMPT, max_new_tokens=NEW, group_size=64)
+        assert streamed.session.kernel_name == "stream_step_kernel"
+        streamed_tokens = streamed.greedy_generate(_wide_prompt()).cpu()
+        streamed_again = streamed.greedy_generate(_wide_prompt()).cpu()
+        local_logits = streamed.session.logits.float().cpu().reshape(-1)            # this rank's slice, last step
+        share = per_operation.local_vocab
+        want_logits = per_operation.logits.float().cpu().reshape(-1)[rank * share:(rank + 1) * share]
         torch.save({"tokens": tokens, "logits": logits, "plain_tokens": plain_tokens, "row": row.float().cpu(),
-                    "compiled_tokens": compiled_tokens}, os.path.join(out_dir, f"gpu{rank}.pt"))
+                    "compiled_tokens": compiled_tokens, "wide_tokens": wide_tokens, "streamed_tokens": streamed_tokens,
+                    "streamed_again": streamed_again, "streamed_logits": local_logits, "wide_logits": want_logits,
+                    "status": int(streamed.session.status.item())}, os.path.join(out_dir, f"gpu{rank}.pt"))
         dist.barrier()
         decoder.close()
         plain.close()
         runtime.close()
+        per_operation.close()
+        streamed.close()
     finally:
         dist.destroy_process_group()
 
@@ -182,6 +227,15 @@ def test_two_nccl_ranks_generate_what_one_rank_does(cuda, tmp_path):
     assert torch.equal(results[0]["logits"], results[1]["logits"])
     agree = int((results[0]["tokens"] == want_tokens).sum())
     assert agree >= NEW - 1, (results[0]["tokens"], want_tokens)
+    # the streamed step kernel with peer stores against the recorded per-operation step with peer sums
+    for result in results:
+        assert result["status"] == 0
+        assert torch.equal(result["streamed_tokens"], results[0]["streamed_tokens"])   # every rank picks the same token
+        assert torch.equal(result["streamed_tokens"], result["streamed_again"])        # and again on the next request
+        scale = float(result["wide_logits"].abs().max())
+        assert float((result["streamed_logits"] - result["wide_logits"]).abs().max()) <= 2e-2 * scale
+    same = int((results[0]["streamed_tokens"] == results[0]["wide_tokens"]).sum())
+    assert same >= NEW - 1, (results[0]["streamed_tokens"], results[0]["wide_tokens"])
 
 
 def test_tensor_parallel_compile_option_refuses_what_the_compiler_refuses():
@@ -202,3 +256,55 @@ def test_tensor_parallel_compile_option_refuses_what_the_compiler_refuses():
                                         autotune=True)
     with pytest.raises(CompilationError, match="process group"):
         aoto.compile_llama_static_cache(model, prompt_length=8, max_new_tokens=4, quantize=GROUP, tensor_parallel=True)
+
+
+def test_a_shard_compiles_and_its_residual_stages_become_exchanged():
+    """``shard_module`` + ``route_exchange``: the stage program of one rank's shard, rewired on the CPU."""
+
+    import aotolith_b200 as aoto
+    from aotolith_b200 import _native as N
+    from aotolith_b200.models.synthetic import SyntheticDecoder
+    from aotolith_b200.runtime import stream_plan as sp
+
+    model = SyntheticDecoder(model_type="llama", vocab_size=512, hidden_size=256, intermediate_size=512,
+                             num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                             max_position_embeddings=64, seed=3)
+    shard = tp.shard_module(model, 2, 1, 64)
+    assert (shard.config.num_attention_heads, shard.config.num_key_value_heads, shard.config.intermediate_size) == (2, 1, 256)
+    assert torch.equal(shard.lm_head.weight, model.lm_head.weight[256:])
+    assert torch.equal(shard.model.layers[1].self_attn.o_proj.weight, model.model.layers[1].self_attn.o_proj.weight[:, 128:])
+    assert torch.equal(shard.model.layers[0].mlp.down_proj.weight, model.model.layers[0].mlp.down_proj.weight[:, 256:])
+    runtime = aoto.compile_llama_static_cache(shard, prompt_length=8, max_new_tokens=6, quantize=64)
+    program = runtime.decode.plan.step_program
+    assert program is not None and program.vocab == 256
+
+    places: dict = {}
+
+    def resolve(ref):  # distinct fake addresses, 64 KB apart
+        return 0x10000 * (1 + places.setdefault((ref.space, str(ref.key)), len(places))) + ref.offset
+
+    base, vector_bytes, row_bytes = 0x7000_0000, 2048, 256 * 4
+    for rank in (0, 1):
+        array = sp.stage_array(program, resolve)
+        count = len(program.stages)
+        before = [(int(array[i].x or 0), int(array[i].out or 0), int(array[i].addend or 0), array[i].addend_mode)
+                  for i in range(count)]
+        used = tp.route_exchange(array, count, base, vector_bytes, row_bytes, rank)
+        assert used == 4  # o and down of two layers
+        exchanged = [i for i in range(count) if array[i].flags & N.STAGE_FLAG_TO_PEERS]
+        assert [array[i].K for i in exchanged] == [128, 256, 128, 256]
+        assert [int(array[i].out) for i in exchanged] == [base + n * vector_bytes for n in range(4)]
+        for n, i in enumerate(exchanged):
+            # the stage after an exchanged one reads it as a sum; the next residual stage adds it as a sum (rank 0)
+            assert array[i + 1].flags & N.STAGE_FLAG_X_SUM and int(array[i + 1].x) == base + n * vector_bytes
+            if rank == 0:
+                assert array[i].addend_mode == before[i][3]
+                if n > 0:
+                    assert array[i].flags & N.STAGE_FLAG_ADDEND_SUM and int(array[i].addend) == base + (n - 1) * vector_bytes
+            else:
+                assert array[i].addend_mode == N.STAGE_ADDEND_NONE and not array[i].flags & N.STAGE_FLAG_ADDEND_SUM
+        untouched = [i for i in range(count) if i not in exchanged and not array[i].flags & N.STAGE_FLAG_X_SUM]
+        for i in untouched:
+            assert (int(array[i].x or 0), int(array[i].out or 0)) == before[i][:2]
+    with pytest.raises(Exception):
+        tp.route_exchange(sp.stage_array(program, resolve), len(program.stages), base, vector_bytes, row_bytes + 4, 0)
