@@ -156,6 +156,15 @@ def _binary(name):
         attrs = {}
         if name == "add":
             attrs["alpha"] = float(node.kwargs.get("alpha", 1.0))
+        numbers = [isinstance(v, (int, float)) and not isinstance(v, bool) for v in (left, right)]
+        if numbers[0] != numbers[1]:
+            # one tensor and one Python number: the number travels as an attribute, as in the
+            # reference's lowering (``legalize/elementwise.py:693-719``)
+            attrs["scalar"] = left if numbers[0] else right
+            attrs["scalar_position"] = "lhs" if numbers[0] else "rhs"
+            tensor = right if numbers[0] else left
+            lw.ids[node] = lw.emit(name, (lw.arg(tensor),), lw.node_type(node), attrs)
+            return
         lw.ids[node] = lw.emit(name, (lw.arg(left), lw.arg(right)), lw.node_type(node), attrs)
     return handler
 
@@ -168,7 +177,12 @@ def _unary(name):
 
 def _reshape(lw, node):
     out_type = lw.node_type(node)
-    lw.ids[node] = lw.emit("reshape", (lw.arg(node.args[0]),), out_type, {"shape": out_type.shape})
+    # the attribute keeps the shape as the program asked for it (a -1 stays a -1, as in the
+    # reference's graphs); the value's type carries the resolved one
+    asked = node.args[1] if len(node.args) > 1 else out_type.shape
+    if not all(isinstance(d, int) and not isinstance(d, bool) for d in asked):
+        asked = out_type.shape
+    lw.ids[node] = lw.emit("reshape", (lw.arg(node.args[0]),), out_type, {"shape": tuple(int(d) for d in asked)})
 
 
 def _t(lw, node):
@@ -262,9 +276,19 @@ def _getitem(lw, node):
     raise UnsupportedOperationError(f"getitem on {parent.target} is not supported")
 
 
+def _is_empty(node) -> bool:
+    value = getattr(node, "meta", {}).get("val") if isinstance(node, torch.fx.Node) else None
+    return isinstance(value, torch.Tensor) and value.numel() == 0
+
+
 def _cat(lw, node):
-    tensors = node.args[0]
+    # an operand without elements contributes nothing (an empty cache that a model concatenates
+    # its first keys to): it is dropped, and a concatenation of one tensor is that tensor
+    tensors = [t for t in node.args[0] if not _is_empty(t)]
     dim = int(node.args[1]) if len(node.args) > 1 else 0
+    if len(tensors) == 1:
+        lw.ids[node] = lw.arg(tensors[0])
+        return
     lw.ids[node] = lw.emit("cat", tuple(lw.arg(t) for t in tensors), lw.node_type(node), {"dim": dim})
 
 
@@ -366,7 +390,21 @@ def _dequantize_i8(lw, node):
 
 
 def _alias(lw, node):
+    if _is_empty(node):
+        return
     lw.ids[node] = lw.arg(node.args[0])
+
+
+def _arange(lw, node):
+    """``arange(end)`` / ``arange(start, end[, step])`` with Python numbers: an op without inputs."""
+
+    numbers = list(node.args)
+    if not 1 <= len(numbers) <= 3 or not all(isinstance(v, (int, float)) and not isinstance(v, bool) for v in numbers):
+        raise UnsupportedOperationError("arange takes one to three Python numbers on this frontend")
+    start, end, step = (0, numbers[0], 1) if len(numbers) == 1 else (numbers + [1])[:3]
+    if step == 0:
+        raise UnsupportedOperationError("arange.step must be nonzero")
+    lw.ids[node] = lw.emit("arange", (), lw.node_type(node), {"start": start, "end": end, "step": step})
 
 
 HANDLERS = {
@@ -376,6 +414,13 @@ HANDLERS = {
     "aten.mul.Tensor": _binary("mul"),
     "aten.add.Tensor": _binary("add"),
     "aten.neg.default": _unary("neg"),
+    "aten.cos.default": _unary("cos"),
+    "aten.sin.default": _unary("sin"),
+    "aten.arange.default": _arange,
+    "aten.arange.start": _arange,
+    "aten.arange.start_step": _arange,
+    "aten.lift_fresh_copy.default": _alias,
+    "aten.lift_fresh.default": _alias,
     "aten.silu.default": _unary("silu"),
     "aten.view.default": _reshape,
     "aten._unsafe_view.default": _reshape,
@@ -429,6 +474,8 @@ def legalize(traced, promoted_constants: list[Any] | None = None) -> Graph:
             lw.inputs.append(value_id)
             lw.ids[node] = value_id
         elif node.op == "get_attr":
+            if getattr(_constant(traced, node), "numel", lambda: 1)() == 0:
+                continue  # an empty constant: whatever uses it drops it
             if promoted_constants is None:
                 raise UnsupportedOperationError(
                     f"the trace captured tensor {node.target!r} as a constant; pass it as an "

@@ -226,11 +226,65 @@ def _to_device_once(values: Sequence[torch.Tensor], device: torch.device) -> tup
     return tuple(result)
 
 
+def _tensor_leaves(value: Any) -> list[torch.Tensor] | None:
+    """Tensors of a nested tuple/list in reading order (``None`` entries dropped); None if anything else is in it."""
+
+    found: list[torch.Tensor] = []
+    for item in value:
+        if item is None:
+            continue
+        if isinstance(item, torch.Tensor):
+            found.append(item)
+        elif isinstance(item, (tuple, list)):
+            inner = _tensor_leaves(item)
+            if inner is None:
+                return None
+            found.extend(inner)
+        else:
+            return None
+    return found
+
+
+def select_module_output(output: Any, output_key: str | None) -> Any:
+    """What a compiled module returns for the module's raw ``output``.
+
+    The reference's rule (``src/aotolith/compiler.py:843-889``): ``output_key`` names a mapping
+    entry or an attribute; without it a tensor is itself, an object with ``.logits`` (a Hugging Face
+    model output) is its logits, a mapping with one entry is that entry, and a tuple or list is
+    the flat tuple of its tensor leaves.
+    """
+
+    chosen = output
+    if output_key is not None:
+        if isinstance(output, Mapping):
+            if output_key not in output:
+                raise KeyError(f"module output has no key {output_key!r}")
+            chosen = output[output_key]
+        elif hasattr(output, output_key):
+            chosen = getattr(output, output_key)
+        else:
+            raise ValueError(f"module output has no attribute {output_key!r}")
+    elif not isinstance(output, torch.Tensor):
+        if hasattr(output, "logits"):
+            chosen = output.logits
+        elif isinstance(output, Mapping) and len(output) == 1:
+            chosen = next(iter(output.values()))
+    if isinstance(chosen, (tuple, list)):
+        leaves = _tensor_leaves(chosen)
+        if not leaves:
+            raise ValueError("a module's sequence output must be a non-empty tuple or list whose leaves are tensors")
+        return tuple(leaves)
+    if not isinstance(chosen, torch.Tensor):
+        raise ValueError("module output must be a tensor, a tuple/list of tensors, or expose one through output_key")
+    return chosen
+
+
 def compile_module(
     module: torch.nn.Module,
     example_inputs: Sequence[Any],
     *,
     example_kwargs: Mapping[str, Any] | None = None,
+    output_key: str | None = None,
     target: str = DEFAULT_TARGET,
     codegen_matmul: bool = False,
     codegen_attention: bool = False,
@@ -268,7 +322,7 @@ def compile_module(
         call_kwargs = dict(static_kwargs)
         call_kwargs.update(zip(tensor_kwarg_names, flat[n_inputs : n_inputs + n_kwargs]))
         state = dict(zip(state_names, flat[n_inputs + n_kwargs :]))
-        return functional_call(module, state, tuple(flat[:n_inputs]), call_kwargs)
+        return select_module_output(functional_call(module, state, tuple(flat[:n_inputs]), call_kwargs), output_key)
 
     examples = [*positional, *(kwargs[name] for name in tensor_kwarg_names), *state_values]
     examples = [_stand_in(t) if isinstance(t, torch.Tensor) else t for t in examples]

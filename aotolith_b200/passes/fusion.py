@@ -20,7 +20,7 @@ from .rewriter import Rewriter, see_through_reshapes
 #: operations a pointwise region may contain
 POINTWISE_OPS = frozenset(
     {"add", "sub", "mul", "div", "neg", "silu", "sigmoid", "exp", "tanh", "relu", "gelu",
-     "where", "scalar_tensor", "cast"}
+     "where", "scalar_tensor", "cast", "cos", "sin"}
 )
 
 
@@ -128,7 +128,7 @@ def fuse_rope(graph: Graph) -> Graph:
 
     rw = Rewriter(graph)
     for op in list(rw.ops):
-        if op.op != "add" or float(op.attrs.get("alpha", 1.0)) != 1.0:
+        if op.op != "add" or float(op.attrs.get("alpha", 1.0)) != 1.0 or len(op.inputs) != 2:
             continue
         terms = [rw.producer(v) for v in op.inputs]
         if any(t is None or t.op != "mul" for t in terms):
@@ -185,7 +185,7 @@ def fuse_residual_epilogue(graph: Graph) -> Graph:
 
     rw = Rewriter(graph)
     for op in list(rw.ops):
-        if op.op != "add" or float(op.attrs.get("alpha", 1.0)) != 1.0:
+        if op.op != "add" or float(op.attrs.get("alpha", 1.0)) != 1.0 or len(op.inputs) != 2:
             continue
         chosen = None
         for product_id, residual_id in (op.inputs[::-1], op.inputs):

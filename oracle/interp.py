@@ -75,6 +75,10 @@ def _projection(op, args):
 
 def _pointwise(op, args, out_dtype):
     kind = op.op
+    if "scalar" in op.attrs and kind in ("mul", "add"):
+        # one operand is a Python number (``scalar_position`` says which side)
+        number = op.attrs["scalar"]
+        args = [number, args[0]] if op.attrs.get("scalar_position") == "lhs" else [args[0], number]
     if kind == "scalar_tensor":
         return torch.tensor(float(op.attrs["value"]), dtype=out_dtype)
     if kind == "where":
@@ -85,6 +89,10 @@ def _pointwise(op, args, out_dtype):
         return args[0] + float(op.attrs.get("alpha", 1.0)) * args[1] if float(op.attrs.get("alpha", 1.0)) != 1.0 else args[0] + args[1]
     if kind == "neg":
         return -args[0]
+    if kind == "cos":
+        return torch.cos(args[0])
+    if kind == "sin":
+        return torch.sin(args[0])
     if kind == "silu":
         return args[0] / (1.0 + torch.exp(-args[0]))
     if kind == "cast":
@@ -110,6 +118,8 @@ def evaluate(graph, op, env, unrounded: bool = False):
         return local[op.outputs[0]]
     if kind == "embedding":
         return ref.embedding(args[0], args[1])
+    if kind == "arange":
+        return torch.arange(op.attrs["start"], op.attrs["end"], op.attrs["step"], dtype=out_dtype)
     if kind == "reshape":
         return args[0].reshape(out_type.shape)
     if kind == "unsqueeze":

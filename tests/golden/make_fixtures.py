@@ -287,8 +287,59 @@ def write_int8_kat() -> None:
     np.savez_compressed(HERE / "quantize_int8_kat.npz", **mats)
 
 
+def plain_llama():
+    """The tiny Llama of the reference's quick start (``README.md:67-84``): fp32, seeded, and its input."""
+
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(LlamaConfig(
+        vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+        num_key_value_heads=2, max_position_embeddings=16)).eval()
+    ids = torch.randint(0, 128, (1, 4), generator=torch.Generator().manual_seed(1))
+    return model, ids
+
+
+def module_state(model):
+    names = [n for n, _ in model.named_parameters(remove_duplicate=False)] + [n for n, _ in model.named_buffers(remove_duplicate=False)]
+    values = [v.detach() for _, v in model.named_parameters(remove_duplicate=False)]
+    values += [v.detach() for _, v in model.named_buffers(remove_duplicate=False)]
+    return names, values
+
+
+def write_plain_llama() -> None:
+    """A plain Hugging Face model through the REFERENCE's capture and rewrite (no adapter, no packing):
+    the lowered graph, the input ids and the model's own logits."""
+
+    from torch.func import functional_call
+
+    from aotolith.capture import capture_fx
+    from aotolith.compiler import _select_module_output
+    from aotolith.passes import rewrite
+
+    model, ids = plain_llama()
+    names, values = module_state(model)
+
+    def traced(tokens, *state):
+        return _select_module_output(functional_call(model, dict(zip(names, state)), (tokens,), {}), None)
+
+    constants: list = []
+    graph = capture_fx(traced, [ids, *values], promoted_constants=constants)
+    lowered = rewrite(graph)
+    with torch.no_grad():
+        logits = model(ids).logits
+    description = {"graph": canonical_graph(lowered), "captured_ops": len(graph.ops), "constants": len(constants),
+                   "state_names": names}
+    (HERE / "lowered_graph_plain_llama.json").write_text(json.dumps(description, indent=1, sort_keys=True))
+    np.savez_compressed(HERE / "plain_llama_eager.npz", ids=ids.numpy(), logits=logits.numpy())
+    print("plain Llama:", len(graph.ops), "captured,", len(lowered.ops), "lowered operations")
+
+
 def main(reference: str, only: str | None = None) -> None:
     load_reference(reference)
+    if only == "plain":
+        write_plain_llama()
+        return
     if only == "real":
         write_real_shape_cut()
         return
@@ -325,5 +376,5 @@ def main(reference: str, only: str | None = None) -> None:
 
 if __name__ == "__main__":
     if len(sys.argv) not in (2, 3):
-        raise SystemExit("usage: python make_fixtures.py <path of a checkout of the reference project> [int8|real]")
+        raise SystemExit("usage: python make_fixtures.py <path of a checkout of the reference project> [int8|real|plain]")
     main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)
