@@ -334,7 +334,7 @@ __device__ __noinline__ bool ss_stamped_addend(const void* addend, int n, int N,
 // normalised and staged by the warps that own chunks of it (four for K = 896), a tile shared
 // between warps is finished by the one warp whose duty it is, and a warp with nothing to do in
 // a phase waits at the barrier and leaves the issue slots to the others.
-template <bool TRACE>
+template <bool TRACE, bool SHARDED>
 __device__ __forceinline__ bool ss_gemv(const SSParams& p, const aoto_stream_stage& st, int stage_index, uint32_t entry,
                                         WarpStream& ws, Best& best, unsigned char* smem) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -380,7 +380,7 @@ __device__ __forceinline__ bool ss_gemv(const SSParams& p, const aoto_stream_sta
       if (gathers) {
         raw = ldg_nc_u4(reinterpret_cast<const uint4*>(words) + c);
       } else {
-        if (stage_flags & AOTO_STAGE_FLAG_X_SUM) {
+        if (SHARDED && (stage_flags & AOTO_STAGE_FLAG_X_SUM)) {
           // an exchanged vector: the chunk is the sum of every rank's row, added in rank order in fp32
           // and rounded once (what an all-reduce of bf16 rows gives)
           while (true) {
@@ -428,7 +428,8 @@ __device__ __forceinline__ bool ss_gemv(const SSParams& p, const aoto_stream_sta
     const int n = min((tile0 + (int)(duty & 0x7FFFu)) * 16 + lane, N - 1);
     if (addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
       // an intermediate that was produced stages ago: its poll is a formality
-      alive = ss_stamped_addend(st.addend, n, N, (stage_flags & AOTO_STAGE_FLAG_ADDEND_SUM) ? p.a.world : 1, epoch, duty_addend);
+      alive = ss_stamped_addend(st.addend, n, N, (SHARDED && (stage_flags & AOTO_STAGE_FLAG_ADDEND_SUM)) ? p.a.world : 1, epoch,
+                                duty_addend);
     } else {
       const size_t row = addend_mode == AOTO_STAGE_ADDEND_GATHER ? (size_t)gather_row * N : 0;
       duty_addend = ldg_nc_bf16(reinterpret_cast<const bf16*>(st.addend) + row + n);
@@ -529,8 +530,8 @@ __device__ __forceinline__ bool ss_gemv(const SSParams& p, const aoto_stream_sta
             // whole tiles carry a residual only in large models, where the load hides behind other warps
             const int n = min(finish_tile * 16 + lane, N - 1);
             if (addend_mode == AOTO_STAGE_ADDEND_STAMPED) {
-              if (!ss_stamped_addend(st.addend, n, N, (stage_flags & AOTO_STAGE_FLAG_ADDEND_SUM) ? p.a.world : 1, epoch,
-                                     finish_addend))
+              if (!ss_stamped_addend(st.addend, n, N, (SHARDED && (stage_flags & AOTO_STAGE_FLAG_ADDEND_SUM)) ? p.a.world : 1,
+                                     epoch, finish_addend))
                 alive = false;
             } else {
               const size_t row = addend_mode == AOTO_STAGE_ADDEND_GATHER ? (size_t)gather_row * N : 0;
@@ -584,7 +585,7 @@ __device__ __forceinline__ bool ss_gemv(const SSParams& p, const aoto_stream_sta
           if (v > best.value || (v == best.value && n < best.index)) { best.value = v; best.index = n; }
         } else if ((lane & 1) == 0) {
           unsigned char* at = reinterpret_cast<unsigned char*>(st.out) + (size_t)(n >> 1) * 8;
-          if (stage_flags & AOTO_STAGE_FLAG_TO_PEERS) {
+          if (SHARDED && (stage_flags & AOTO_STAGE_FLAG_TO_PEERS)) {
             // this rank's row of the exchanged vector, on every rank: plain 8-byte stores over NVLink,
             // data and stamp in one word
             at += (size_t)p.a.rank * ((size_t)N * 4);
@@ -978,6 +979,7 @@ __device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_strea
 // ---------------------------------------------------------------------------
 // pick stage: CTA 0 polls the per-CTA maxima the ARGMAX stage left
 // ---------------------------------------------------------------------------
+template <bool SHARDED>
 __device__ __noinline__ void ss_pick(const SSParams& p, int stage_index) {
   if (blockIdx.x != 0 || threadIdx.x >= 32) return;
   const unsigned char* payload = reinterpret_cast<const unsigned char*>(p.a.scratch);
@@ -1004,7 +1006,7 @@ __device__ __noinline__ void ss_pick(const SSParams& p, int stage_index) {
     const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
     if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
   }
-  if (p.a.world > 1 && !failed) {
+  if (SHARDED && p.a.world > 1 && !failed) {
     // every rank holds a slice of the vocabulary: the ranks' best (logit, index in the whole
     // vocabulary) meet in every rank's exchange slots; the largest wins, the lowest index on ties
     bi += p.a.vocab_offset;
@@ -1091,7 +1093,7 @@ __device__ __noinline__ void ss_start(const SSParams& p, unsigned char* smem, Wa
     if (i < depth && sizes[i] != 0) ss_request(p, ws, sizes[i], lane);
 }
 
-template <bool TRACE, bool LONG>
+template <bool TRACE, bool LONG, bool SHARDED>
 __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid_constant__ SSParams p) {
   extern __shared__ uint4 ss_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(ss_raw);
@@ -1128,7 +1130,7 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
     if (st.kind == AOTO_STAGE_GEMV) {
       const uint32_t entry = table[s];
       if (((entry >> 16) & 0x7FFFu) != 0) {
-        alive = ss_gemv<TRACE>(p, st, s, entry, ws, best, smem);
+        alive = ss_gemv<TRACE, SHARDED>(p, st, s, entry, ws, best, smem);
       } else if ((st.flags & AOTO_STAGE_FLAG_ARGMAX) && tid == 0) {
         // a CTA without rows of the last projection still answers the pick stage's poll
         unsigned char* payload = reinterpret_cast<unsigned char*>(p.a.scratch);
@@ -1138,7 +1140,7 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
     } else if (st.kind == AOTO_STAGE_ATTENTION) {
       alive = ss_attention<TRACE, LONG>(p, st, s, share, kv_parity, kv_pending, smem);
     } else if (st.kind == AOTO_STAGE_PICK) {
-      ss_pick(p, s);
+      ss_pick<SHARDED>(p, s);
     }
   }
   if (!alive) {
@@ -1226,12 +1228,19 @@ extern "C" int aoto_sm100_stream_step(const aoto_stream_step_args* a, void* stre
   // two instantiations: the marks of the per-stage timeline cost issue slots, so the kernel that
   // serves requests carries none
   // and two more for the window form, so that neither carries the other's code
-  const bool traced = a->trace != nullptr, lengthy = params.L.long_window != 0;
-  auto kernel = traced ? (lengthy ? stream_step_kernel<true, true> : stream_step_kernel<true, false>)
-                       : (lengthy ? stream_step_kernel<false, true> : stream_step_kernel<false, false>);
-  static PerDeviceOnce raised[4];
-  if (raise_dynamic_smem(kernel, (size_t)smem_limit, raised[(traced ? 2 : 0) + (lengthy ? 1 : 0)]) != AOTO_OK)
-    return AOTO_ERR_LAUNCH;
+  const bool traced = a->trace != nullptr, lengthy = params.L.long_window != 0, sharded = params.a.world > 1;
+  // the exchange between GPUs is a third switch: a single GPU's kernel carries none of its code
+  using Kernel = void (*)(const SSParams);
+  static const Kernel kernels[8] = {
+      stream_step_kernel<false, false, false>, stream_step_kernel<false, false, true>,
+      stream_step_kernel<false, true, false>,  stream_step_kernel<false, true, true>,
+      stream_step_kernel<true, false, false>,  stream_step_kernel<true, false, true>,
+      stream_step_kernel<true, true, false>,   stream_step_kernel<true, true, true>,
+  };
+  const int which = (traced ? 4 : 0) + (lengthy ? 2 : 0) + (sharded ? 1 : 0);
+  Kernel kernel = kernels[which];
+  static PerDeviceOnce raised[8];
+  if (raise_dynamic_smem(kernel, (size_t)smem_limit, raised[which]) != AOTO_OK) return AOTO_ERR_LAUNCH;
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, SS_THREADS, params.L.total) != cudaSuccess ||
       per_sm < 1) {
