@@ -158,7 +158,7 @@ class StreamStage(Structure):
         ("N", c_int32), ("K", c_int32),
         ("alpha", c_float), ("beta", c_float), ("rms_norm_eps", c_float),
         ("kind", ctypes.c_uint8), ("epilogue", ctypes.c_uint8), ("addend_mode", ctypes.c_uint8), ("flags", ctypes.c_uint8),
-        ("next_attention", c_int32), ("reserved", c_int32),
+        ("next_attention", c_int32), ("ordinal", c_int32),
     ]
 
 
@@ -176,7 +176,7 @@ class StreamStepArgs(Structure):
         ("x_index", c_void_p), ("x_rows", c_int64),
         ("token", c_void_p), ("generated", c_void_p), ("counters", c_void_p),
         ("generated_capacity", c_int32), ("window", c_int32),
-        ("epoch", ctypes.c_uint32), ("reserved", c_int32),
+        ("epoch", ctypes.c_uint32), ("attention_stages", c_int32),
         ("status", c_void_p), ("scratch", c_void_p), ("scratch_bytes", c_int64),
         ("world", c_int32), ("rank", c_int32), ("peer_delta", c_int64 * 8), ("pick_exchange", c_void_p),
         ("vocab_offset", c_int32), ("reserved2", c_int32),
@@ -226,6 +226,7 @@ EXPORTS: dict[str, tuple] = {
     "aoto_sm100_stream_step": (c_int, [POINTER(StreamStepArgs), c_void_p]),
     "aoto_sm100_stream_step_smem_bytes": (c_int64, [POINTER(StreamStepArgs)]),
     "aoto_sm100_stream_args_size": (c_int, []),
+    "aoto_sm100_stream_step_scratch_bytes_for": (c_int64, [POINTER(StreamStepArgs)]),
     "aoto_sm100_stream_step_scratch_bytes": (c_int64, [c_int32]),
     "aoto_sm100_stream_stage_size": (c_int, []),
     "aoto_sm100_kv_cache_append": (c_int, [POINTER(KvAppendArgs), c_void_p]),

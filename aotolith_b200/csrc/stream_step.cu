@@ -34,12 +34,20 @@ struct SSLayout {
   uint32_t ring, bars, kvbars, stages, table, work, xs, xsum, part, red, rotary, kv, total;
   int keys_per_warp;  // rows of a warp's key / value buffers (short window)
   int long_window;    // the window does not fit the buffers: only the step's own key and value rows are kept
+  int slices_max;     // long window: most slices a kv head's window is cut into (stride of the partial results)
 };
 
 __host__ __device__ inline uint32_t ss_align(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
+__host__ __device__ inline int ss_slices_max(int ctas, int kv_heads, int capacity) {
+  const int by_grid = ctas / (kv_heads > 0 ? kv_heads : 1), by_keys = (capacity + 15) / 16;
+  const int slices = by_grid < by_keys ? by_grid : by_keys;
+  return slices > 1 ? slices : 1;
+}
+
 __host__ __device__ inline SSLayout ss_layout(int stage_count, int max_k, int depth, int capacity, int head_dim,
-                                              bool has_attention, bool force_long = false) {
+                                              bool has_attention, bool force_long = false, int group = 1,
+                                              int slices_max = 1) {
   SSLayout L;
   uint32_t off = 0;
   L.ring = off; off += (uint32_t)SS_WARPS * depth * SS_SLOT_BYTES;
@@ -56,14 +64,24 @@ __host__ __device__ inline SSLayout ss_layout(int stage_count, int max_k, int de
   const uint32_t xsum_bytes = ss_align((uint32_t)(max_k / 128) * 8, 16);
   L.part = L.xsum + xsum_bytes;
   uint32_t work_bytes = xs_bytes + xsum_bytes + (uint32_t)SS_PART_SLOTS * SS_PART_BYTES;
-  const uint32_t attention_bytes =
+  const int keys_per_warp = has_attention ? (capacity + SS_WARPS - 1) / SS_WARPS : 0;
+  const bool long_window = has_attention && (force_long || keys_per_warp > SS_MAX_WINDOW_KEYS);
+  uint32_t attention_bytes =
       has_attention ? (uint32_t)(4 * head_dim + SS_WARPS * (head_dim + 2) + SS_WARPS * 16 + 4 * 16) * 4 : 0;
+  if (long_window) {
+    // raw q (group heads), k, v; rotated q; per (warp, head) results or the staged slices of one head;
+    // per (warp, head) key weights; per-warp factors; per-slice factors
+    const int rows = SS_WARPS * group > slices_max ? SS_WARPS * group : slices_max;
+    attention_bytes = (uint32_t)((2 * group + 2) * head_dim + rows * (head_dim + 2) + SS_WARPS * group * 16 +
+                                 SS_WARPS * 16 + 4 * slices_max) * 4;
+  }
   if (attention_bytes > work_bytes) work_bytes = attention_bytes;
   off += ss_align(work_bytes, 16);
   L.red = off; off += 64 * 4;
   L.rotary = off; off += has_attention ? (uint32_t)head_dim * 4 : 0;  // cos row, sin row of the step's position
-  L.keys_per_warp = has_attention ? (capacity + SS_WARPS - 1) / SS_WARPS : 0;
-  L.long_window = has_attention && (force_long || L.keys_per_warp > SS_MAX_WINDOW_KEYS);
+  L.keys_per_warp = keys_per_warp;
+  L.long_window = long_window;
+  L.slices_max = long_window ? slices_max : 0;
   L.kv = off;
   if (L.long_window) off += ss_align((uint32_t)2 * head_dim * 2, 16);
   else off += has_attention ? (uint32_t)SS_WARPS * 2 * L.keys_per_warp * head_dim * 2 : 0;
@@ -683,107 +701,338 @@ __device__ __noinline__ void ss_move_window(const void* cache_in, void* cache_ou
   }
 }
 
-// A long window: the warp's keys in passes of sixteen (two lanes per key), rows read from L2 -
-// they were asked for when the stage began - with the running maximum, sum and weighted values
-// of an online softmax. Slot C - 1 is this step's key: its rows are in shared memory. Leaves
-// the warp's (m, l, sums) in its merge row like the short form.
-__device__ __noinline__ void ss_attend_long(const SSParams& p, const aoto_stream_stage& st, const WindowShare& w,
-                                            uint32_t qs, uint32_t weights, uint32_t mine) {
-  const int lane = threadIdx.x & 31;
-  const int D = p.a.head_dim, C = p.a.capacity;
+// ---------------------------------------------------------------------------
+// attention stage, long window: a kv head's window spread over many CTAs
+// ---------------------------------------------------------------------------
+// One SM cannot take a long window in from L2 fast enough (a head's 1 280 keys of 128 dims are
+// 655 KB; ~5 us per 128 KB were measured), so the window of every kv head is cut into `slices`
+// runs of keys and CTA (kv head, slice) scores ALL query heads of the group against its run - the
+// key and value rows are read once for the group. Each warp takes a share of the run, in passes of
+// sixteen keys (two lanes per key, alternate 16-byte chunks of the row, every load of a pass
+// issued before anything is computed), up to four heads at a time in registers with an online
+// softmax. The CTA's per-head partial result (max, sum, weighted values) goes out as fp32 stamped
+// words; CTA h < query_heads then polls head h's partials of all slices, merges them and publishes
+// the head's output as the short form does. The step's own key/value (slot C - 1) stay in shared
+// memory; the unit that owns the last slot writes them into the next cache. Afterwards every CTA
+// moves an equal share of the cache window.
+//
+// Every attention stage has a region of partial results of its own: the stamp of a word is the
+// launch's, so a merge could not tell this layer's word from one the previous layer left.
+template <bool TRACE>
+__device__ __noinline__ bool ss_attention_spread(const SSParams& p, const aoto_stream_stage& st, int stage_index,
+                                                 int valid_length, unsigned char* smem) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int D = p.a.head_dim, C = p.a.capacity, KVH = p.a.kv_heads, QH = p.a.query_heads;
+  const int G = QH / KVH, pairs = D >> 1;
+  const int cta = (int)blockIdx.x, ctas = (int)gridDim.x;
+  const uint32_t epoch = p.a.epoch;
+  if (TRACE) ss_trace(p, stage_index, 0);
+
+  // geometry of the step's window (the same on every CTA)
+  const int first_valid = p.a.window ? max(0, C - valid_length) : 0;
+  const int window = C - first_valid;
+  const int slices = max(1, min(min(ctas / KVH, (window + 15) >> 4), p.L.slices_max));
+  const int run = (window + slices - 1) / slices;          // keys of a slice
+  const int last_slice = (C - 1 - first_valid) / run;      // the slice that holds this step's key
+  const bool unit = cta < KVH * slices;
+  const int kvh = unit ? cta / slices : 0, slice = unit ? cta - kvh * slices : 0;
+  const int s0 = min(C, first_valid + slice * run), s1 = min(C, s0 + run);
+  const int per = max(1, (s1 - s0 + SS_WARPS - 1) / SS_WARPS);
+  const int k0 = min(s1, s0 + warp * per), nkeys = unit ? min(s1, k0 + per) - k0 : 0;
+  const bool merges = cta < QH;
+  const size_t head_stride = (size_t)p.L.slices_max * (D + 2) * 8;  // bytes of one head's partials
+  // a region per attention stage: the stamp is the launch's, so words a previous layer of the
+  // same launch left would pass for this layer's
+  unsigned char* partials = reinterpret_cast<unsigned char*>(p.a.scratch) + (size_t)ctas * 16 +
+                            (size_t)st.ordinal * QH * head_stride;
+
+  const uint32_t rowv = ss_smem(smem + p.L.work);                       // raw q (G heads), k, v: (G + 2) * D floats
+  const uint32_t qs = rowv + (uint32_t)(G + 2) * D * 4;                 // rotated, scaled queries: G * D floats
+  const uint32_t merge = qs + (uint32_t)G * D * 4;                      // [warp][head]: m, l, D sums / staged slices
+  const int merge_rows = max(SS_WARPS * G, p.L.slices_max);
+  const uint32_t weights = merge + (uint32_t)merge_rows * (D + 2) * 4;  // [warp][head in group of four][16]
+  const uint32_t factors = weights + (uint32_t)SS_WARPS * G * 64;       // [warp][16]
+  const uint32_t slice_factors = factors + (uint32_t)SS_WARPS * 64;     // [4 warps][slices_max]
+  const uint32_t rotary = ss_smem(smem + p.L.rotary);
+  const uint32_t new_key = ss_smem(smem + p.L.kv), new_value = new_key + (uint32_t)D * 2;
   const int half = lane & 1, half_chunks = D >> 4, dims = D >> 5;
-  const bf16* kplane = reinterpret_cast<const bf16*>(st.addend) + (size_t)w.kvh * C * D;  // new slot j = old slot j + 1
-  const bf16* vplane = kplane + (size_t)p.a.kv_heads * C * D;
-  const uint32_t qrow = qs + (uint32_t)half * 32;  // the query values of this lane's chunks: eight floats every sixteen
-  float m = -INFINITY, l = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  bool failed = false;
+
+  if (unit) {
+    if (nkeys > 0) {  // this warp's rows are asked for now: the projection the stage waits for gives them time
+      const int old = min(k0 + nkeys, C - 1) - k0;
+      const unsigned char* kin = reinterpret_cast<const unsigned char*>(st.addend) + ((size_t)kvh * C + k0 + 1) * D * 2;
+      const unsigned char* vin = kin + (size_t)KVH * C * D * 2;
+      for (int o = lane * 128; o < old * D * 2; o += 32 * 128) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(kin + o));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(vin + o));
+      }
+    }
+    __syncthreads();  // the previous stage's last readers of the work region are done
+    // the group's queries and the kv head's key and value of the step
+    const int words = (G + 2) * pairs;
+    if (tid < ((words + 31) & ~31)) {
+      const bool mine = tid < words;
+      int element = p.a.query_start + kvh * G * D + 2 * tid;
+      if (tid >= (G + 1) * pairs) element = p.a.value_start + kvh * D + 2 * (tid - (G + 1) * pairs);
+      else if (tid >= G * pairs) element = p.a.key_start + kvh * D + 2 * (tid - G * pairs);
+      const unsigned char* at = reinterpret_cast<const unsigned char*>(st.x) + (size_t)(element >> 1) * 8;
 #pragma unroll 1
-  for (int c0 = 0; c0 < w.nkeys; c0 += 16) {
-    const int key = c0 + (lane >> 1), slot = w.k0 + key;
-    bool attend = false;
-    if (key < w.nkeys) attend = p.a.window ? slot >= w.first_valid : p.a.mask[slot] != 0;
-    // every load of the pass is issued before anything is computed: the key rows for the scores and
-    // the value rows (which do not depend on the scores) share one trip to L2
-    const int count = min(16, w.nkeys - c0);
-    const int from_cache = max(0, min(count, C - 1 - (w.k0 + c0)));  // keys of this pass that are old slots
-    uint4 kk[8];
-    uint2 vv[16];
-    if (attend) {
-      if (slot == C - 1) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (i < half_chunks) kk[i] = ss_lds128(w.new_key + (uint32_t)(2 * i + half) * 16);
-      } else {
-        // the two lanes of a key take alternate 16-byte chunks of its row: together they use every
-        // 32-byte sector they touch
-        const uint4* from = reinterpret_cast<const uint4*>(kplane + (size_t)(slot + 1) * D) + half;
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (i < half_chunks) kk[i] = ldg_nc_u4(from + 2 * i);
-      }
-    }
-    {
-      const bf16* vrow = vplane + (size_t)(w.k0 + c0 + 1) * D + lane * dims;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        vv[j] = make_uint2(0u, 0u);
-        if (j < from_cache) {
-          if (dims == 4) vv[j] = ldg_nc_u2(vrow + (size_t)j * D);
-          else vv[j].x = ldg_nc_u32(vrow + (size_t)j * D);
+      for (int rounds = 1;; ++rounds) {
+        const uint2 v = mine ? ss_ld_stamped(at) : make_uint2(0u, epoch);
+        if (v.y == epoch && mine) {
+          ss_stsf(rowv + (uint32_t)tid * 8, bf16x2_lo(v.x));
+          ss_stsf(rowv + (uint32_t)tid * 8 + 4, bf16x2_hi(v.x));
         }
+        if (__all_sync(0xffffffffu, v.y == epoch)) break;
+        if (rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0)) { failed = true; break; }
       }
     }
-    float s = -INFINITY;
-    if (attend) {
-      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (i < half_chunks) {
-          const float4 qa = ss_lds128f(qrow + (uint32_t)i * 64), qb = ss_lds128f(qrow + (uint32_t)i * 64 + 16);
-          d0 = fmaf(bf16x2_lo(kk[i].x), qa.x, d0); d1 = fmaf(bf16x2_hi(kk[i].x), qa.y, d1);
-          d2 = fmaf(bf16x2_lo(kk[i].y), qa.z, d2); d3 = fmaf(bf16x2_hi(kk[i].y), qa.w, d3);
-          d0 = fmaf(bf16x2_lo(kk[i].z), qb.x, d0); d1 = fmaf(bf16x2_hi(kk[i].z), qb.y, d1);
-          d2 = fmaf(bf16x2_lo(kk[i].w), qb.z, d2); d3 = fmaf(bf16x2_hi(kk[i].w), qb.w, d3);
-        }
-      }
-      s = (d0 + d1) + (d2 + d3);
-    }
-    const float other = __shfl_xor_sync(0xffffffffu, s, 1);
-    s = attend ? s + other : -INFINITY;
-    const float m_new = fmaxf(m, ss_warp_max(s));
-    const float keep = m == -INFINITY ? 0.f : __expf(m - m_new);
-    const float e = s == -INFINITY ? 0.f : __expf(s - m_new);
-    if (half == 0) ss_stsf(weights + (uint32_t)(lane >> 1) * 4, e);
-    __syncwarp();
-    a0 *= keep; a1 *= keep; a2 *= keep; a3 *= keep; l *= keep;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      if (j < from_cache) {
-        const float wt = ss_ldsf(weights + (uint32_t)j * 4);
-        a0 = fmaf(wt, bf16x2_lo(vv[j].x), a0); a1 = fmaf(wt, bf16x2_hi(vv[j].x), a1);
-        if (dims == 4) { a2 = fmaf(wt, bf16x2_lo(vv[j].y), a2); a3 = fmaf(wt, bf16x2_hi(vv[j].y), a3); }
-        l += wt;
-      }
-    }
-    if (from_cache < count) {  // this step's own value row
-      const float wt = ss_ldsf(weights + (uint32_t)from_cache * 4);
-      const uint32_t v0 = ss_lds32(w.new_value + (uint32_t)lane * dims * 2);
-      a0 = fmaf(wt, bf16x2_lo(v0), a0); a1 = fmaf(wt, bf16x2_hi(v0), a1);
-      if (dims == 4) {
-        const uint32_t v1 = ss_lds32(w.new_value + (uint32_t)lane * dims * 2 + 4);
-        a2 = fmaf(wt, bf16x2_lo(v1), a2); a3 = fmaf(wt, bf16x2_hi(v1), a3);
-      }
-      l += wt;
-    }
-    __syncwarp();  // the weights are read: the next pass may overwrite them
-    m = m_new;
   }
-  if (lane == 0) { ss_stsf(mine, m); ss_stsf(mine + 4, l); }
-  ss_stsf(mine + 8 + (uint32_t)lane * dims * 4, a0);
-  ss_stsf(mine + 12 + (uint32_t)lane * dims * 4, a1);
-  if (dims == 4) { ss_stsf(mine + 16 + (uint32_t)lane * dims * 4, a2); ss_stsf(mine + 20 + (uint32_t)lane * dims * 4, a3); }
+  if (__syncthreads_or(failed)) {
+    ss_give_up(p, stage_index);
+    return false;
+  }
+  if (TRACE) ss_trace(p, stage_index, 1);
+
+  if (unit) {
+    // rotate the group's queries (bf16 rounding points of the unfused form) and the key
+    const int hd = D >> 1;
+#pragma unroll 1
+    for (int i = tid; i < (G + 1) * D; i += SS_THREADS) {
+      const int d = i % D;
+      const uint32_t cs = ss_lds32(rotary + (uint32_t)(d & ~1) * 2), sn = ss_lds32(rotary + (uint32_t)(D + (d & ~1)) * 2);
+      const float c = (d & 1) ? bf16x2_hi(cs) : bf16x2_lo(cs), sine = (d & 1) ? bf16x2_hi(sn) : bf16x2_lo(sn);
+      const int other = d < hd ? i + hd : i - hd;
+      const float sign = d < hd ? -1.f : 1.f;
+      const float r = round_bf16(round_bf16(ss_ldsf(rowv + (uint32_t)i * 4) * c) +
+                                 round_bf16(sign * ss_ldsf(rowv + (uint32_t)other * 4) * sine));
+      if (i < G * D) {
+        ss_stsf(qs + (uint32_t)i * 4, r * p.a.scale);
+      } else {
+        const uint32_t key_bits = float_to_bf16_bits(r);
+        const uint32_t value_bits = float_to_bf16_bits(ss_ldsf(rowv + (uint32_t)(i + D) * 4));
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(new_key + (uint32_t)d * 2), "h"((unsigned short)key_bits) : "memory");
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(new_value + (uint32_t)d * 2), "h"((unsigned short)value_bits) : "memory");
+        if (slice == last_slice) {
+          bf16* kout = reinterpret_cast<bf16*>(const_cast<void*>(st.norm_weight)) + ((size_t)kvh * C + (C - 1)) * D;
+          kout[d] = __ushort_as_bfloat16((unsigned short)key_bits);
+          kout[(size_t)KVH * C * D + d] = __ushort_as_bfloat16((unsigned short)value_bits);
+        }
+      }
+    }
+    __syncthreads();
+    if (TRACE) ss_trace(p, stage_index, 2);
+
+    // every warp attends its keys, four heads of the group at a time
+    const bf16* kplane = reinterpret_cast<const bf16*>(st.addend) + (size_t)kvh * C * D;  // new slot j = old slot j + 1
+    const bf16* vplane = kplane + (size_t)KVH * C * D;
+    const uint32_t my_weights = weights + (uint32_t)warp * G * 64;
+#pragma unroll 1
+    for (int g0 = 0; g0 < G; g0 += 4) {
+      float m[4], l[4], a[4][4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) { m[h] = -INFINITY; l[h] = 0.f; a[h][0] = a[h][1] = a[h][2] = a[h][3] = 0.f; }
+#pragma unroll 1
+      for (int c0 = 0; c0 < nkeys; c0 += 16) {
+        const int key = c0 + (lane >> 1), slot = k0 + key;
+        bool attend = false;
+        if (key < nkeys) attend = p.a.window ? slot >= first_valid : p.a.mask[slot] != 0;
+        const int count = min(16, nkeys - c0);
+        const int from_cache = max(0, min(count, C - 1 - (k0 + c0)));  // keys of this pass that are old slots
+        uint4 kk[8];
+        uint2 vv[16];
+        if (attend) {
+          if (slot == C - 1) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (i < half_chunks) kk[i] = ss_lds128(new_key + (uint32_t)(2 * i + half) * 16);
+          } else {
+            const uint4* from = reinterpret_cast<const uint4*>(kplane + (size_t)(slot + 1) * D) + half;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (i < half_chunks) kk[i] = ldg_nc_u4(from + 2 * i);
+          }
+        }
+        {
+          const bf16* vrow = vplane + (size_t)(k0 + c0 + 1) * D + lane * dims;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            vv[j] = make_uint2(0u, 0u);
+            if (j < from_cache) {
+              if (dims == 4) vv[j] = ldg_nc_u2(vrow + (size_t)j * D);
+              else vv[j].x = ldg_nc_u32(vrow + (size_t)j * D);
+            }
+          }
+        }
+        float keep[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          keep[h] = 1.f;
+          if (g0 + h < G) {
+            float sc = -INFINITY;
+            if (attend) {
+              const uint32_t qrow = qs + (uint32_t)((g0 + h) * D) * 4 + (uint32_t)half * 32;
+              float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                if (i < half_chunks) {
+                  const float4 qa = ss_lds128f(qrow + (uint32_t)i * 64), qb = ss_lds128f(qrow + (uint32_t)i * 64 + 16);
+                  d0 = fmaf(bf16x2_lo(kk[i].x), qa.x, d0); d1 = fmaf(bf16x2_hi(kk[i].x), qa.y, d1);
+                  d2 = fmaf(bf16x2_lo(kk[i].y), qa.z, d2); d3 = fmaf(bf16x2_hi(kk[i].y), qa.w, d3);
+                  d0 = fmaf(bf16x2_lo(kk[i].z), qb.x, d0); d1 = fmaf(bf16x2_hi(kk[i].z), qb.y, d1);
+                  d2 = fmaf(bf16x2_lo(kk[i].w), qb.z, d2); d3 = fmaf(bf16x2_hi(kk[i].w), qb.w, d3);
+                }
+              }
+              sc = (d0 + d1) + (d2 + d3);
+            }
+            const float other = __shfl_xor_sync(0xffffffffu, sc, 1);
+            sc = attend ? sc + other : -INFINITY;
+            const float m_new = fmaxf(m[h], ss_warp_max(sc));
+            keep[h] = m[h] == -INFINITY ? 0.f : __expf(m[h] - m_new);
+            const float e = sc == -INFINITY ? 0.f : __expf(sc - m_new);
+            if (half == 0) ss_stsf(my_weights + (uint32_t)h * 64 + (uint32_t)(lane >> 1) * 4, e);
+            m[h] = m_new;
+          }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          if (g0 + h < G) {
+            a[h][0] *= keep[h]; a[h][1] *= keep[h]; a[h][2] *= keep[h]; a[h][3] *= keep[h]; l[h] *= keep[h];
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (j < from_cache) {
+            const float v0 = bf16x2_lo(vv[j].x), v1 = bf16x2_hi(vv[j].x), v2 = bf16x2_lo(vv[j].y), v3 = bf16x2_hi(vv[j].y);
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              if (g0 + h < G) {
+                const float wt = ss_ldsf(my_weights + (uint32_t)h * 64 + (uint32_t)j * 4);
+                a[h][0] = fmaf(wt, v0, a[h][0]); a[h][1] = fmaf(wt, v1, a[h][1]);
+                if (dims == 4) { a[h][2] = fmaf(wt, v2, a[h][2]); a[h][3] = fmaf(wt, v3, a[h][3]); }
+                l[h] += wt;
+              }
+            }
+          }
+        }
+        if (from_cache < count) {  // this step's own value row
+          const uint32_t w0 = ss_lds32(new_value + (uint32_t)lane * dims * 2);
+          const uint32_t w1 = dims == 4 ? ss_lds32(new_value + (uint32_t)lane * dims * 2 + 4) : 0u;
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            if (g0 + h < G) {
+              const float wt = ss_ldsf(my_weights + (uint32_t)h * 64 + (uint32_t)from_cache * 4);
+              a[h][0] = fmaf(wt, bf16x2_lo(w0), a[h][0]); a[h][1] = fmaf(wt, bf16x2_hi(w0), a[h][1]);
+              if (dims == 4) { a[h][2] = fmaf(wt, bf16x2_lo(w1), a[h][2]); a[h][3] = fmaf(wt, bf16x2_hi(w1), a[h][3]); }
+              l[h] += wt;
+            }
+          }
+        }
+        __syncwarp();  // the weights are read: the next pass may overwrite them
+      }
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        if (g0 + h < G) {
+          const uint32_t mine = merge + (uint32_t)((warp * G + g0 + h) * (D + 2)) * 4;
+          if (lane == 0) { ss_stsf(mine, m[h]); ss_stsf(mine + 4, l[h]); }
+          ss_stsf(mine + 8 + (uint32_t)lane * dims * 4, a[h][0]);
+          ss_stsf(mine + 12 + (uint32_t)lane * dims * 4, a[h][1]);
+          if (dims == 4) { ss_stsf(mine + 16 + (uint32_t)lane * dims * 4, a[h][2]); ss_stsf(mine + 20 + (uint32_t)lane * dims * 4, a[h][3]); }
+        }
+      }
+    }
+    if (TRACE) ss_trace(p, stage_index, 3);
+    __syncthreads();
+    if (TRACE) ss_trace(p, stage_index, 4);
+
+    // the CTA's result per head: the sixteen warps merged in a fixed order, published as fp32 words
+    // (a warp's thirty-two elements belong to one head, so the sixteen factors are computed once per warp)
+#pragma unroll 1
+    for (int i = tid; i < G * D; i += SS_THREADS) {
+      const int g = i / D, d = i - g * D;
+      const uint32_t row = merge + (uint32_t)(((lane & (SS_WARPS - 1)) * G + g) * (D + 2)) * 4;
+      const float wm = lane < SS_WARPS ? ss_ldsf(row) : -INFINITY;
+      const float wl = lane < SS_WARPS ? ss_ldsf(row + 4) : 0.f;
+      const float mx = ss_warp_max(wm);
+      const float factor = wm == -INFINITY ? 0.f : __expf(wm - mx);
+      const uint32_t mine = factors + (uint32_t)warp * 64;
+      __syncwarp();
+      if (lane < SS_WARPS) ss_stsf(mine + (uint32_t)lane * 4, factor);
+      const float den = warp_sum(factor * wl);
+      __syncwarp();
+      float n0 = 0.f, n1 = 0.f;
+#pragma unroll 2
+      for (int w2 = 0; w2 < SS_WARPS; w2 += 2) {
+        n0 = fmaf(ss_ldsf(mine + (uint32_t)w2 * 4), ss_ldsf(merge + (uint32_t)((w2 * G + g) * (D + 2) + 2 + d) * 4), n0);
+        n1 = fmaf(ss_ldsf(mine + (uint32_t)w2 * 4 + 4), ss_ldsf(merge + (uint32_t)(((w2 + 1) * G + g) * (D + 2) + 2 + d) * 4), n1);
+      }
+      unsigned char* out = partials + (size_t)(kvh * G + g) * head_stride + (size_t)slice * (D + 2) * 8;
+      ss_st_stamped(out + (size_t)(2 + d) * 8, __float_as_uint(n0 + n1), epoch);
+      if (d == 0) {
+        ss_st_stamped(out, __float_as_uint(mx), epoch);
+        ss_st_stamped(out + 8, __float_as_uint(den), epoch);
+      }
+    }
+  }
+  if (TRACE) ss_trace(p, stage_index, 5);
+
+  if (merges) {
+    // head `cta`: its partial results of all slices, merged, and published as the head's output
+    __syncthreads();  // the merge rows are read: the area now stages the slices
+    const unsigned char* from = partials + (size_t)cta * head_stride;
+    const int words = slices * (D + 2);
+    int rounds = 0;
+#pragma unroll 1
+    for (int i = tid; i < words; i += SS_THREADS) {
+      uint2 v = ss_ld_stamped(from + (size_t)i * 8);
+      while (v.y != epoch) {
+        if (++rounds > SS_POLL_LIMIT || ((rounds & 255) == 0 && ss_ld_status(p.a.status) != 0)) { failed = true; break; }
+        v = ss_ld_stamped(from + (size_t)i * 8);
+      }
+      ss_sts32(merge + (uint32_t)i * 4, v.x);
+    }
+    if (__syncthreads_or(failed)) {
+      ss_give_up(p, stage_index);
+      return false;
+    }
+    if (tid < D) {
+      const uint32_t mine = slice_factors + (uint32_t)warp * (uint32_t)p.L.slices_max * 4;
+      float mx = -INFINITY;
+      for (int s2 = lane; s2 < slices; s2 += 32) mx = fmaxf(mx, ss_ldsf(merge + (uint32_t)(s2 * (D + 2)) * 4));
+      mx = ss_warp_max(mx);
+      float den = 0.f;
+      for (int s2 = lane; s2 < slices; s2 += 32) {
+        const float sm = ss_ldsf(merge + (uint32_t)(s2 * (D + 2)) * 4);
+        const float factor = sm == -INFINITY ? 0.f : __expf(sm - mx);
+        ss_stsf(mine + (uint32_t)s2 * 4, factor);
+        den = fmaf(factor, ss_ldsf(merge + (uint32_t)(s2 * (D + 2) + 1) * 4), den);
+      }
+      den = warp_sum(den);
+      __syncwarp();
+      float num = 0.f;
+#pragma unroll 2
+      for (int s2 = 0; s2 < slices; ++s2)
+        num = fmaf(ss_ldsf(mine + (uint32_t)s2 * 4), ss_ldsf(merge + (uint32_t)(s2 * (D + 2) + 2 + tid) * 4), num);
+      const float result = den > 0.f ? __fdividef(num, den) : 0.f;
+      const uint32_t bits = float_to_bf16_bits(result);
+      const uint32_t neighbour = __shfl_down_sync(0xffffffffu, bits, 1);
+      if ((tid & 1) == 0)
+        ss_st_stamped(reinterpret_cast<unsigned char*>(st.out) + ((size_t)cta * pairs + (tid >> 1)) * 8,
+                      bits | (neighbour << 16), epoch);
+    }
+  }
+  if (TRACE) ss_trace(p, stage_index, 6);
+
+  // the cache window: every CTA moves an equal share
+  ss_move_window(st.addend, const_cast<void*>(st.norm_weight), 2 * KVH, C, D >> 3, cta, ctas);
+  __syncthreads();  // the work region is free for the next stage
+  if (TRACE) ss_trace(p, stage_index, 7);
+  return true;
 }
 
-template <bool TRACE, bool LONG>
+template <bool TRACE>
 __device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_stream_stage& st, int stage_index,
                                              const WindowShare& w, uint32_t& kv_parity, bool& kv_pending,
                                              unsigned char* smem) {
@@ -801,17 +1050,6 @@ __device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_strea
   }
 
   const int pairs = D >> 1;
-  if (LONG && w.old_keys > 0) {
-    // a long window is read from L2: ask for this warp's rows now, the projection this stage
-    // waits for gives them the time to arrive
-    const unsigned char* kin = reinterpret_cast<const unsigned char*>(st.addend) + ((size_t)w.kvh * C + w.k0 + 1) * D * 2;
-    const unsigned char* vin = kin + (size_t)KVH * C * D * 2;
-    const int bytes = w.old_keys * D * 2;
-    for (int o = lane * 128; o < bytes; o += 32 * 128) {
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(kin + o));
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(vin + o));
-    }
-  }
   __syncthreads();  // the previous stage's last readers of the work region are done
   const uint32_t rowv = ss_smem(smem + p.L.work);  // raw q head, k, v of the step: 3 * D floats
   const uint32_t qs = rowv + (uint32_t)3 * D * 4;  // rotated, scaled query: D floats
@@ -872,11 +1110,9 @@ __device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_strea
   // every warp attends its keys: two lanes per key for the scores, the lanes split the head
   // dimension for the weighted sum of values
   bool alive = true;
-  if (!LONG && kv_pending && w.old_keys > 0) alive = ss_mbar_wait(w.bar, kv_parity);
+  if (kv_pending && w.old_keys > 0) alive = ss_mbar_wait(w.bar, kv_parity);
   if (TRACE) ss_trace(p, stage_index, 3);
-  if constexpr (LONG) {
-    ss_attend_long(p, st, w, qs, weights, merge + (uint32_t)warp * (D + 2) * 4);
-  } else {
+  {
     const int key = lane >> 1, half = lane & 1;
     const int half_chunks = D >> 4;  // 16-byte chunks of half a row
     float s = -INFINITY;
@@ -965,7 +1201,7 @@ __device__ __forceinline__ bool ss_attention(const SSParams& p, const aoto_strea
   if (TRACE) ss_trace(p, stage_index, 6);
 
   // the next layer's window starts travelling: every warp is done with its buffers
-  if (!LONG && st.next_attention >= 0) {
+  if (st.next_attention >= 0) {
     const aoto_stream_stage* all = reinterpret_cast<const aoto_stream_stage*>(smem + p.L.stages);
     ss_request_window(p, all[st.next_attention], w, lane);
     kv_pending = true;
@@ -1072,7 +1308,7 @@ __device__ __noinline__ void ss_start(const SSParams& p, unsigned char* smem, Wa
     for (int i = 0; i < SS_WARPS; ++i) ss_mbar_init(ss_smem(smem + p.L.kvbars) + i * 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (p.a.first_attention >= 0 && (int)blockIdx.x < p.a.query_heads && tid < 2 * p.a.head_dim) {
+  if (p.a.first_attention >= 0 && ((int)blockIdx.x < p.a.query_heads || p.L.long_window) && tid < 2 * p.a.head_dim) {
     // the rotary rows of the step's position: fetched once, off every layer's critical path
     long long pos = max(0ll, min(position, (long long)p.a.table_rows - 1));
     const int D = p.a.head_dim;
@@ -1138,7 +1374,8 @@ __global__ void __launch_bounds__(SS_THREADS, 1) stream_step_kernel(const __grid
         ss_st_stamped(payload + (size_t)blockIdx.x * 16 + 8, 0x7fffffffu, p.a.epoch);
       }
     } else if (st.kind == AOTO_STAGE_ATTENTION) {
-      alive = ss_attention<TRACE, LONG>(p, st, s, share, kv_parity, kv_pending, smem);
+      if constexpr (LONG) alive = ss_attention_spread<TRACE>(p, st, s, valid_length, smem);
+      else alive = ss_attention<TRACE>(p, st, s, share, kv_parity, kv_pending, smem);
     } else if (st.kind == AOTO_STAGE_PICK) {
       ss_pick<SHARDED>(p, s);
     }
@@ -1168,9 +1405,11 @@ static int ss_check(const aoto_stream_step_args& a, SSLayout* layout) {
     if (a.capacity > (1 << 20)) return 0;
     if (3 * (a.head_dim >> 1) > SS_THREADS) return 0;
     if ((a.query_start | a.key_start | a.value_start) & 1) return 0;
-    if (a.table_rows <= 0) return 0;
+    if (a.table_rows <= 0 || a.attention_stages <= 0) return 0;
   }
-  *layout = ss_layout(a.stage_count, a.max_k, a.ring_depth, a.capacity, a.head_dim, has_attention);
+  const int group = has_attention ? a.query_heads / a.kv_heads : 1;
+  const int slices_max = has_attention ? ss_slices_max(a.ctas, a.kv_heads, a.capacity) : 1;
+  *layout = ss_layout(a.stage_count, a.max_k, a.ring_depth, a.capacity, a.head_dim, has_attention, false, group, slices_max);
   if (has_attention && !layout->long_window) {
     // wide heads and long rows together can leave no room for the per-warp key / value buffers:
     // the window is then read from L2 as a long one is
@@ -1181,9 +1420,20 @@ static int ss_check(const aoto_stream_step_args& a, SSLayout* layout) {
       limit = 227 * 1024;
     }
     if ((int64_t)layout->total > (int64_t)limit)
-      *layout = ss_layout(a.stage_count, a.max_k, a.ring_depth, a.capacity, a.head_dim, has_attention, true);
+      *layout = ss_layout(a.stage_count, a.max_k, a.ring_depth, a.capacity, a.head_dim, has_attention, true, group,
+                          slices_max);
   }
+  // the spread form polls the group's queries, key and value with one thread per stamped word
+  if (layout->long_window && (group + 2) * (a.head_dim >> 1) > SS_THREADS) return 0;
   return 1;
+}
+
+// Scratch the kernel needs: the per-CTA maxima of the pick stage, then (long window) every head's
+// partial attention results of all slices.
+static int64_t ss_scratch_bytes(const aoto_stream_step_args& a, const SSLayout& L) {
+  int64_t need = (int64_t)a.ctas * 16;
+  if (L.long_window) need += (int64_t)a.attention_stages * a.query_heads * L.slices_max * (a.head_dim + 2) * 8;
+  return need;
 }
 
 }  // namespace aoto
@@ -1201,6 +1451,12 @@ extern "C" int64_t aoto_sm100_stream_step_smem_bytes(const aoto_stream_step_args
   return (int64_t)L.total;
 }
 
+extern "C" int64_t aoto_sm100_stream_step_scratch_bytes_for(const aoto_stream_step_args* a) {
+  SSLayout L;
+  if (!a || !ss_check(*a, &L)) return -1;
+  return ss_scratch_bytes(*a, L);
+}
+
 extern "C" int aoto_sm100_stream_step(const aoto_stream_step_args* a, void* stream_) {
   if (!a || !a->stages || !a->cta_table || !a->duties || !a->starts || !a->stream || !a->status || !a->scratch ||
       a->epoch == 0)
@@ -1216,6 +1472,7 @@ extern "C" int aoto_sm100_stream_step(const aoto_stream_step_args* a, void* stre
     return AOTO_ERR_ARGUMENT;
   }
   if (!ss_check(*a, &params.L)) return AOTO_ERR_UNSUPPORTED;
+  if (a->scratch_bytes < ss_scratch_bytes(*a, params.L)) return AOTO_ERR_ARGUMENT;
   int device = 0, sms = 0, coop = 0, smem_limit = 0;
   if (cudaGetDevice(&device) != cudaSuccess) {
     (void)cudaGetLastError();

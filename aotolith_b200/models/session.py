@@ -104,8 +104,12 @@ class DecodeSession:
         self.logits = torch.zeros((1, 1, program.vocab), dtype=torch.bfloat16, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         lib = N.load()
-        self.scratch = torch.zeros(max(int(lib.aoto_sm100_stream_step_scratch_bytes(ctas)), 1 << 12),
-                                   dtype=torch.uint8, device=device)
+        import ctypes
+
+        need = int(lib.aoto_sm100_stream_step_scratch_bytes_for(ctypes.byref(sp.base_args(program, ctas, depth))))
+        if need < 0:
+            return False
+        self.scratch = torch.zeros(max(need, 1 << 12), dtype=torch.uint8, device=device)
         self.stage_count = len(program.stages) + 1
         self._stream_keep = (stream, table, starts, duties)
         self._stream_args = []

@@ -375,6 +375,7 @@ def base_args(program, ctas: int, ring_depth: int) -> N.StreamStepArgs:
     geo = geometry(program)
     attention_stages = [i for i, spec in enumerate(program.stages) if spec.kind == N.STAGE_ATTENTION]
     args.first_attention = attention_stages[0] if attention_stages else -1
+    args.attention_stages = len(attention_stages)
     if geo is not None:
         for key in ("query_heads", "kv_heads", "capacity", "head_dim", "query_start", "key_start", "value_start",
                     "table_rows"):
@@ -425,6 +426,7 @@ def stage_array(program, resolve):
             stage.addend = resolve(spec.refs["cache_in"])
             stage.norm_weight = resolve(spec.refs["cache_out"])
             stage.next_attention = following.get(slot, -1)
+            stage.ordinal = attention.index(slot)
     last = array[len(program.stages) - 1]
     last.flags |= N.STAGE_FLAG_ARGMAX
     array[count - 1].kind = N.STAGE_PICK

@@ -449,9 +449,18 @@ def run_ours(args) -> None:
         del session
         runtime = None
         torch.cuda.empty_cache()
-        extra["bucketed"] = measure_bucketed(world, rank, device, per_rank=512, warmup=3, with_clocks=False, in_child=True)
+        # a record that cannot be made (a shape a kernel declines at this N, say) is reported as such and does
+        # not take the line with it; a failed parity check still ends the run
+        def guarded(name, make):
+            try:
+                extra[name] = make()
+            except Exception as error:  # noqa: BLE001
+                extra[name] = {"error": f"{type(error).__name__}: {error}"[:500]} if rank == 0 else None
+
+        guarded("bucketed", lambda: measure_bucketed(world, rank, device, per_rank=512, warmup=3, with_clocks=False,
+                                                      in_child=True))
         extra["tp_parity"] = check_tp_parity(world, rank, device)
-        extra["tp"] = measure_tp(world, rank, device, steps=2, warmup=1, with_clocks=False)
+        guarded("tp", lambda: measure_tp(world, rank, device, steps=2, warmup=1, with_clocks=False))
 
     if rank == 0:
         peak, peak_kind = measured_peaks()

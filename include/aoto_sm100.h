@@ -616,7 +616,7 @@ typedef struct aoto_stream_stage {
   uint8_t addend_mode;     /* AOTO_STAGE_ADDEND_*                                                  */
   uint8_t flags;           /* AOTO_STAGE_FLAG_*                                                    */
   int32_t next_attention;  /* ATTENTION: index of the next ATTENTION stage, -1 after the last      */
-  int32_t reserved;
+  int32_t ordinal;         /* ATTENTION: how many ATTENTION stages come before this one            */
 } aoto_stream_stage;
 
 typedef struct aoto_stream_step_args {
@@ -649,9 +649,11 @@ typedef struct aoto_stream_step_args {
   int32_t generated_capacity;
   int32_t window;                       /* 1: position and mask come from `counters`               */
   uint32_t epoch;                       /* as for aoto_sm100_decode_step                           */
-  int32_t reserved;
+  int32_t attention_stages;             /* how many ATTENTION stages the program has               */
   int32_t* status;
-  void* scratch;                        /* per-CTA maxima of the ARGMAX stage: 16 bytes per CTA    */
+  void* scratch;                        /* per-CTA maxima of the ARGMAX stage (16 bytes per CTA), then, with a
+                                           long window, every ATTENTION stage's partial results (a region per
+                                           stage: stamps cannot tell the layers of one launch apart)      */
   int64_t scratch_bytes;
   /* tensor parallelism: one process per GPU runs the same program over its shard. `world` = 1 and
      everything below zero for a single GPU. peer_delta[q] = (base of rank q's exchange buffer as
@@ -674,11 +676,18 @@ typedef struct aoto_stream_step_args {
 int aoto_sm100_stream_step(const aoto_stream_step_args* args, void* stream);
 /*
  * Dynamic shared memory the kernel needs for this geometry, or -1 if it has no form for it
- * (K not a multiple of 128 or above 16384, head_dim not 64/128 or a window that does not fit
- * one CTA per query head). Pointers of `args` are ignored.
+ * (K not a multiple of 128 or above 16384, head_dim not 64/128, or a long window with more than
+ * 512 stamped words of queries, key and value per kv head). Pointers of `args` are ignored.
  */
 int64_t aoto_sm100_stream_step_smem_bytes(const aoto_stream_step_args* args);
 int64_t aoto_sm100_stream_step_scratch_bytes(int32_t ctas);
+/*
+ * The same for a given geometry (pointers of `args` are ignored): with a window too long for the
+ * per-warp buffers the kernel spreads every kv head's window over many CTAs and keeps their partial
+ * results in scratch as well. This is the size `scratch_bytes` must cover; -1 if the kernel has
+ * no form for the geometry.
+ */
+int64_t aoto_sm100_stream_step_scratch_bytes_for(const aoto_stream_step_args* args);
 int aoto_sm100_stream_stage_size(void); /* sizeof(aoto_stream_stage), for binding checks */
 int aoto_sm100_stream_args_size(void);  /* sizeof(aoto_stream_step_args), for binding checks */
 
