@@ -72,7 +72,8 @@ __host__ __device__ inline SSLayout ss_layout(int stage_count, int max_k, int de
     // raw q (group heads), k, v; rotated q; per (warp, head) results or the staged slices of one head;
     // per (warp, head) key weights; per-warp factors; per-slice factors
     const int rows = SS_WARPS * group > slices_max ? SS_WARPS * group : slices_max;
-    attention_bytes = (uint32_t)((2 * group + 2) * head_dim + rows * (head_dim + 2) + SS_WARPS * group * 16 +
+    const int weight_heads = group > 4 ? group : 4;  // a warp scores four heads at a time
+    attention_bytes = (uint32_t)((2 * group + 2) * head_dim + rows * (head_dim + 2) + SS_WARPS * weight_heads * 16 +
                                  SS_WARPS * 16 + 4 * slices_max) * 4;
   }
   if (attention_bytes > work_bytes) work_bytes = attention_bytes;
@@ -751,11 +752,12 @@ __device__ __noinline__ bool ss_attention_spread(const SSParams& p, const aoto_s
   const uint32_t merge = qs + (uint32_t)G * D * 4;                      // [warp][head]: m, l, D sums / staged slices
   const int merge_rows = max(SS_WARPS * G, p.L.slices_max);
   const uint32_t weights = merge + (uint32_t)merge_rows * (D + 2) * 4;  // [warp][head in group of four][16]
-  const uint32_t factors = weights + (uint32_t)SS_WARPS * G * 64;       // [warp][16]
+  const int weight_heads = max(G, 4);
+  const uint32_t factors = weights + (uint32_t)SS_WARPS * weight_heads * 64;  // [warp][16]
   const uint32_t slice_factors = factors + (uint32_t)SS_WARPS * 64;     // [4 warps][slices_max]
   const uint32_t rotary = ss_smem(smem + p.L.rotary);
   const uint32_t new_key = ss_smem(smem + p.L.kv), new_value = new_key + (uint32_t)D * 2;
-  const int half = lane & 1, half_chunks = D >> 4, dims = D >> 5;
+  const int dims = D >> 5;
   bool failed = false;
 
   if (unit) {
@@ -824,110 +826,82 @@ __device__ __noinline__ bool ss_attention_spread(const SSParams& p, const aoto_s
     __syncthreads();
     if (TRACE) ss_trace(p, stage_index, 2);
 
-    // every warp attends its keys, four heads of the group at a time
+    // Every warp attends its keys, four heads of the group at a time, eight keys a pass: lane
+    // 4 * key + head scores one (key, head) pair over the whole row (the four lanes of a key read the
+    // same addresses), the eight lanes of a head share its running maximum and sum, and for the
+    // weighted values every lane owns D / 32 dimensions of all four heads. The loops are kept
+    // rolled: this code runs once per layer and warp, and what it costs is fetching it.
     const bf16* kplane = reinterpret_cast<const bf16*>(st.addend) + (size_t)kvh * C * D;  // new slot j = old slot j + 1
     const bf16* vplane = kplane + (size_t)KVH * C * D;
-    const uint32_t my_weights = weights + (uint32_t)warp * G * 64;
+    const unsigned char* own_key = smem + p.L.kv;                      // the step's own rows (slot C - 1)
+    const unsigned char* own_value = own_key + (size_t)D * 2;
+    const uint32_t my_weights = weights + (uint32_t)warp * weight_heads * 64;  // [head of the group of four][8 keys]
+    const int hl = lane & 3, kl = lane >> 2;
 #pragma unroll 1
     for (int g0 = 0; g0 < G; g0 += 4) {
-      float m[4], l[4], a[4][4];
+      const bool has_head = g0 + hl < G;
+      float m = -INFINITY, l = 0.f;   // of head g0 + hl (the same on its eight lanes)
+      float a[4][4];                  // [head of the group][dimension of this lane]
 #pragma unroll
-      for (int h = 0; h < 4; ++h) { m[h] = -INFINITY; l[h] = 0.f; a[h][0] = a[h][1] = a[h][2] = a[h][3] = 0.f; }
+      for (int h = 0; h < 4; ++h) a[h][0] = a[h][1] = a[h][2] = a[h][3] = 0.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < nkeys; c0 += 16) {
-        const int key = c0 + (lane >> 1), slot = k0 + key;
+      for (int c0 = 0; c0 < nkeys; c0 += 8) {
+        const int key = c0 + kl, slot = k0 + key;
         bool attend = false;
-        if (key < nkeys) attend = p.a.window ? slot >= first_valid : p.a.mask[slot] != 0;
-        const int count = min(16, nkeys - c0);
-        const int from_cache = max(0, min(count, C - 1 - (k0 + c0)));  // keys of this pass that are old slots
-        uint4 kk[8];
-        uint2 vv[16];
+        if (key < nkeys && has_head) attend = p.a.window ? slot >= first_valid : p.a.mask[slot] != 0;
+        float sc = -INFINITY;
         if (attend) {
-          if (slot == C - 1) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (i < half_chunks) kk[i] = ss_lds128(new_key + (uint32_t)(2 * i + half) * 16);
-          } else {
-            const uint4* from = reinterpret_cast<const uint4*>(kplane + (size_t)(slot + 1) * D) + half;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (i < half_chunks) kk[i] = ldg_nc_u4(from + 2 * i);
+          const uint4* krow = slot == C - 1 ? reinterpret_cast<const uint4*>(own_key)
+                                            : reinterpret_cast<const uint4*>(kplane + (size_t)(slot + 1) * D);
+          const uint32_t qrow = qs + (uint32_t)((g0 + hl) * D) * 4;
+          float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll 8
+          for (int c = 0; c < (D >> 3); ++c) {
+            const uint4 kk = krow[c];
+            const float4 qa = ss_lds128f(qrow + (uint32_t)c * 32), qb = ss_lds128f(qrow + (uint32_t)c * 32 + 16);
+            d0 = fmaf(bf16x2_lo(kk.x), qa.x, d0); d1 = fmaf(bf16x2_hi(kk.x), qa.y, d1);
+            d2 = fmaf(bf16x2_lo(kk.y), qa.z, d2); d3 = fmaf(bf16x2_hi(kk.y), qa.w, d3);
+            d0 = fmaf(bf16x2_lo(kk.z), qb.x, d0); d1 = fmaf(bf16x2_hi(kk.z), qb.y, d1);
+            d2 = fmaf(bf16x2_lo(kk.w), qb.z, d2); d3 = fmaf(bf16x2_hi(kk.w), qb.w, d3);
           }
+          sc = (d0 + d1) + (d2 + d3);
         }
-        {
-          const bf16* vrow = vplane + (size_t)(k0 + c0 + 1) * D + lane * dims;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            vv[j] = make_uint2(0u, 0u);
-            if (j < from_cache) {
-              if (dims == 4) vv[j] = ldg_nc_u2(vrow + (size_t)j * D);
-              else vv[j].x = ldg_nc_u32(vrow + (size_t)j * D);
-            }
-          }
-        }
-        float keep[4];
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          keep[h] = 1.f;
-          if (g0 + h < G) {
-            float sc = -INFINITY;
-            if (attend) {
-              const uint32_t qrow = qs + (uint32_t)((g0 + h) * D) * 4 + (uint32_t)half * 32;
-              float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                if (i < half_chunks) {
-                  const float4 qa = ss_lds128f(qrow + (uint32_t)i * 64), qb = ss_lds128f(qrow + (uint32_t)i * 64 + 16);
-                  d0 = fmaf(bf16x2_lo(kk[i].x), qa.x, d0); d1 = fmaf(bf16x2_hi(kk[i].x), qa.y, d1);
-                  d2 = fmaf(bf16x2_lo(kk[i].y), qa.z, d2); d3 = fmaf(bf16x2_hi(kk[i].y), qa.w, d3);
-                  d0 = fmaf(bf16x2_lo(kk[i].z), qb.x, d0); d1 = fmaf(bf16x2_hi(kk[i].z), qb.y, d1);
-                  d2 = fmaf(bf16x2_lo(kk[i].w), qb.z, d2); d3 = fmaf(bf16x2_hi(kk[i].w), qb.w, d3);
-                }
-              }
-              sc = (d0 + d1) + (d2 + d3);
-            }
-            const float other = __shfl_xor_sync(0xffffffffu, sc, 1);
-            sc = attend ? sc + other : -INFINITY;
-            const float m_new = fmaxf(m[h], ss_warp_max(sc));
-            keep[h] = m[h] == -INFINITY ? 0.f : __expf(m[h] - m_new);
-            const float e = sc == -INFINITY ? 0.f : __expf(sc - m_new);
-            if (half == 0) ss_stsf(my_weights + (uint32_t)h * 64 + (uint32_t)(lane >> 1) * 4, e);
-            m[h] = m_new;
-          }
-        }
+        // maximum and sum over the eight keys of the head (lanes that differ in bits 2-4)
+        float mc = sc;
+        mc = fmaxf(mc, __shfl_xor_sync(0xffffffffu, mc, 4));
+        mc = fmaxf(mc, __shfl_xor_sync(0xffffffffu, mc, 8));
+        mc = fmaxf(mc, __shfl_xor_sync(0xffffffffu, mc, 16));
+        const float m_new = fmaxf(m, mc);
+        const float keep = m == -INFINITY ? 0.f : __expf(m - m_new);
+        const float e = sc == -INFINITY ? 0.f : __expf(sc - m_new);
+        float es = e;
+        es += __shfl_xor_sync(0xffffffffu, es, 4);
+        es += __shfl_xor_sync(0xffffffffu, es, 8);
+        es += __shfl_xor_sync(0xffffffffu, es, 16);
+        l = fmaf(l, keep, es);
+        m = m_new;
+        ss_stsf(my_weights + (uint32_t)hl * 64 + (uint32_t)kl * 4, e);
         __syncwarp();
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
-          if (g0 + h < G) {
-            a[h][0] *= keep[h]; a[h][1] *= keep[h]; a[h][2] *= keep[h]; a[h][3] *= keep[h]; l[h] *= keep[h];
-          }
+          const float kh = __shfl_sync(0xffffffffu, keep, h);  // lane h holds head g0 + h
+          a[h][0] *= kh; a[h][1] *= kh; a[h][2] *= kh; a[h][3] *= kh;
         }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          if (j < from_cache) {
-            const float v0 = bf16x2_lo(vv[j].x), v1 = bf16x2_hi(vv[j].x), v2 = bf16x2_lo(vv[j].y), v3 = bf16x2_hi(vv[j].y);
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              if (g0 + h < G) {
-                const float wt = ss_ldsf(my_weights + (uint32_t)h * 64 + (uint32_t)j * 4);
-                a[h][0] = fmaf(wt, v0, a[h][0]); a[h][1] = fmaf(wt, v1, a[h][1]);
-                if (dims == 4) { a[h][2] = fmaf(wt, v2, a[h][2]); a[h][3] = fmaf(wt, v3, a[h][3]); }
-                l[h] += wt;
-              }
-            }
-          }
-        }
-        if (from_cache < count) {  // this step's own value row
-          const uint32_t w0 = ss_lds32(new_value + (uint32_t)lane * dims * 2);
-          const uint32_t w1 = dims == 4 ? ss_lds32(new_value + (uint32_t)lane * dims * 2 + 4) : 0u;
+        const int count = min(8, nkeys - c0);
+#pragma unroll 4
+        for (int j = 0; j < count; ++j) {
+          const int vslot = k0 + c0 + j;
+          const unsigned char* vrow = vslot == C - 1 ? own_value
+                                                     : reinterpret_cast<const unsigned char*>(vplane + (size_t)(vslot + 1) * D);
+          uint2 v = make_uint2(0u, 0u);
+          if (dims == 4) v = *reinterpret_cast<const uint2*>(vrow + (size_t)lane * 8);
+          else v.x = *reinterpret_cast<const uint32_t*>(vrow + (size_t)lane * 4);
+          const float v0 = bf16x2_lo(v.x), v1 = bf16x2_hi(v.x), v2 = bf16x2_lo(v.y), v3 = bf16x2_hi(v.y);
 #pragma unroll
           for (int h = 0; h < 4; ++h) {
-            if (g0 + h < G) {
-              const float wt = ss_ldsf(my_weights + (uint32_t)h * 64 + (uint32_t)from_cache * 4);
-              a[h][0] = fmaf(wt, bf16x2_lo(w0), a[h][0]); a[h][1] = fmaf(wt, bf16x2_hi(w0), a[h][1]);
-              if (dims == 4) { a[h][2] = fmaf(wt, bf16x2_lo(w1), a[h][2]); a[h][3] = fmaf(wt, bf16x2_hi(w1), a[h][3]); }
-              l[h] += wt;
-            }
+            const float wt = ss_ldsf(my_weights + (uint32_t)h * 64 + (uint32_t)j * 4);
+            a[h][0] = fmaf(wt, v0, a[h][0]); a[h][1] = fmaf(wt, v1, a[h][1]);
+            a[h][2] = fmaf(wt, v2, a[h][2]); a[h][3] = fmaf(wt, v3, a[h][3]);
           }
         }
         __syncwarp();  // the weights are read: the next pass may overwrite them
@@ -936,7 +910,8 @@ __device__ __noinline__ bool ss_attention_spread(const SSParams& p, const aoto_s
       for (int h = 0; h < 4; ++h) {
         if (g0 + h < G) {
           const uint32_t mine = merge + (uint32_t)((warp * G + g0 + h) * (D + 2)) * 4;
-          if (lane == 0) { ss_stsf(mine, m[h]); ss_stsf(mine + 4, l[h]); }
+          const float mh = __shfl_sync(0xffffffffu, m, h), lh = __shfl_sync(0xffffffffu, l, h);
+          if (lane == 0) { ss_stsf(mine, mh); ss_stsf(mine + 4, lh); }
           ss_stsf(mine + 8 + (uint32_t)lane * dims * 4, a[h][0]);
           ss_stsf(mine + 12 + (uint32_t)lane * dims * 4, a[h][1]);
           if (dims == 4) { ss_stsf(mine + 16 + (uint32_t)lane * dims * 4, a[h][2]); ss_stsf(mine + 20 + (uint32_t)lane * dims * 4, a[h][3]); }

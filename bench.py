@@ -563,6 +563,9 @@ def print_stage_trace(runtime, session, token, cache) -> None:
         last_input, done = np.nanmax(rows[:, 1]), np.nanmax(rows[:, 7])
         print(f"{index:5d} {names[kinds[index]]:9s} {int(busy.sum()):4d} | {last_input:10.0f} {np.nanmax(rows[:, 3]):7.0f} "
               f"{np.nanmax(rows[:, 5]):11.0f} {done:5.0f} | {last_input - previous_done:8.0f} {done - last_input:5.0f}")
+        if kinds[index] == 2:  # the last CTA at each of the stage's eight marks, and the median CTA
+            print("      marks (last CTA)  ", " ".join(f"{np.nanmax(rows[:, m]):7.0f}" for m in range(8)))
+            print("      marks (median CTA)", " ".join(f"{np.nanmedian(rows[:, m]):7.0f}" for m in range(8)))
         previous_done = done
     print(f"total {np.nanmax(times):.0f} ns, status {int(session.status.item())}")
 

@@ -26,6 +26,16 @@ def rel_err(actual, expected):
     return float((actual.float().cpu().reshape(-1) - expected).abs().max()) / max(float(expected.abs().max()), 1e-30)
 
 
+def same_until(a, b) -> int:
+    """Number of leading tokens two generations share."""
+
+    a, b = a.tolist(), b.tolist()
+    for index, (x, y) in enumerate(zip(a, b)):
+        if x != y:
+            return index
+    return min(len(a), len(b))
+
+
 def two_sessions(runtime):
     streamed = DecodeSession(runtime)
     session_module.STREAM_STEP_DISABLED = True
@@ -108,7 +118,7 @@ def test_streamed_kernel_with_wide_heads_and_long_rows(cuda):
 def test_streamed_kernel_with_a_window_longer_than_its_buffers(cuda, head_dim, kv_heads, prompt_length, new_tokens):
     """More than sixteen keys a warp: every kv head's window is spread over many CTAs and merged.
 
-    Capacities 305, 330, 1040, 1024, 720 and 340: groups of seven, four, eight (one kv head: as
+    Capacities 305, 330, 1040, 1024, 720 and 340: groups of seven, four, four again (one kv head: as
     many slices as the window has runs of sixteen keys) and one query head per kv head; windows that
     are nearly full and one that starts at 41 of 340 slots (fewer slices than CTAs per kv head).
     The step's own key is the last slot and comes from shared memory. Held to the kernel that reads
@@ -121,7 +131,8 @@ def test_streamed_kernel_with_a_window_longer_than_its_buffers(cuda, head_dim, k
     else:
         model = SyntheticDecoder(
             model_type="llama", vocab_size=32000, hidden_size=1024, intermediate_size=2816, num_hidden_layers=2,
-            num_attention_heads=8, num_key_value_heads=kv_heads, head_dim=128, max_position_embeddings=2048, rope_theta=5e5,
+            num_attention_heads=4 if kv_heads == 1 else 8, num_key_value_heads=kv_heads, head_dim=128,
+            max_position_embeddings=2048, rope_theta=5e5,
             rms_norm_eps=1e-5, attention_bias=False, tie_word_embeddings=False, seed=23,
         )
         compile_fn, vocab = aoto.compile_llama_static_cache, 32000
@@ -132,9 +143,20 @@ def test_streamed_kernel_with_a_window_longer_than_its_buffers(cuda, head_dim, k
     steps = new_tokens - 1
     a = streamed.run(token, cache, prompt_length, steps).cpu()
     b = in_place.run(token, cache, prompt_length, steps).cpu()
-    assert a.tolist() == b.tolist()
-    assert rel_err(streamed.logits, in_place.logits) < REL_TOL
-    assert rel_err(streamed.final_cache(steps), in_place.final_cache(steps)) < REL_TOL
+    same = same_until(a, b)
+    if same == steps:
+        assert rel_err(streamed.logits, in_place.logits) < REL_TOL
+        assert rel_err(streamed.final_cache(steps), in_place.final_cache(steps)) < REL_TOL
+    else:
+        # a random model's best two logits can tie within rounding: the step where the kernels part must
+        # be such a tie (both kernels are run up to it again: their logits there are what is compared)
+        assert same >= 2
+        streamed.run(token, cache, prompt_length, same + 1)
+        in_place.run(token, cache, prompt_length, same + 1)
+        assert rel_err(streamed.logits, in_place.logits) < REL_TOL
+        logits = in_place.logits.float().reshape(-1)
+        gap = float(logits[int(b[same])] - logits[int(a[same])])
+        assert 0 <= gap <= REL_TOL * float(logits.abs().max()), (same, gap)
     streamed.run(token, cache, prompt_length, 1)
     assert torch.equal(streamed.final_cache(1)[:, :, :, :, :-1], cache[:, :, :, :, 1:])
     if prompt_length <= 300 and new_tokens <= 30:
