@@ -617,6 +617,25 @@ def compile_tensor_parallel(model: torch.nn.Module, *, prompt_length: int, max_n
         raise CompilationError("tensor_parallel needs an initialised torch.distributed process group",
                                hint="launch one process per GPU and call init_process_group('nccl') first")
     group = None if tensor_parallel is True else tensor_parallel
-    decoder = TensorParallelDecoder(model, prompt_length=prompt_length, max_new_tokens=max_new_tokens,
-                                    group_size=quantize, group=group, device=device)
+    settings = dict(prompt_length=prompt_length, max_new_tokens=max_new_tokens, group_size=quantize, group=group,
+                    device=device)
+    if streamed_step_applies(model, dist.get_world_size(group), quantize):
+        decoder = StreamedTensorParallelDecoder(model, **settings)   # the decode step is one kernel per rank
+    else:
+        decoder = TensorParallelDecoder(model, **settings)           # recorded per-operation step
     return TensorParallelRuntime(decoder, found.name)
+
+
+def streamed_step_applies(model: torch.nn.Module, world: int, group_size: int) -> bool:
+    """Whether a rank's shard has the shapes the streamed step kernel takes (decided the same way on every
+    rank, from the model alone): group size 64, every shard's row length a multiple of 128, head
+    dimension 64 or 128."""
+
+    config = model.config
+    heads, kv_heads = int(config.num_attention_heads), int(config.num_key_value_heads)
+    hidden, inner = int(config.hidden_size), int(config.intermediate_size)
+    head_dim = int(getattr(config, "head_dim", None) or hidden // heads)
+    if group_size != 64 or head_dim not in (64, 128) or heads % world or kv_heads % world or inner % world:
+        return False
+    rows = (hidden, heads // world * head_dim, inner // world)   # K of q/k/v, gate, up and the LM head; of o; of down
+    return all(k % 128 == 0 for k in rows) and int(config.vocab_size) % (2 * world) == 0

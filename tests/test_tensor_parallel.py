@@ -308,3 +308,17 @@ def test_a_shard_compiles_and_its_residual_stages_become_exchanged():
             assert (int(array[i].x or 0), int(array[i].out or 0)) == before[i][:2]
     with pytest.raises(Exception):
         tp.route_exchange(sp.stage_array(program, resolve), len(program.stages), base, vector_bytes, row_bytes + 4, 0)
+
+
+def test_which_models_get_the_streamed_sharded_step():
+    from aotolith_b200.models.synthetic import llama3_8b_shaped  # noqa: F401 - shapes only, nothing is built
+
+    assert not tp.streamed_step_applies(_tiny(), 2, GROUP)           # group size 16
+    assert tp.streamed_step_applies(_wide(), 2, 64) and tp.streamed_step_applies(_wide(), 4, 64)
+    assert not tp.streamed_step_applies(_wide(), 8, 64)              # 8 x 64 / 8 = 64 columns of o a rank: not a block
+    assert not tp.streamed_step_applies(_wide(), 3, 64)
+    from types import SimpleNamespace
+
+    big = SimpleNamespace(config=SimpleNamespace(num_attention_heads=32, num_key_value_heads=8, hidden_size=4096,
+                                                 intermediate_size=14336, head_dim=128, vocab_size=128256))
+    assert all(tp.streamed_step_applies(big, world, 64) for world in (1, 2, 4, 8))
