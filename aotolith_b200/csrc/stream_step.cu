@@ -631,7 +631,7 @@ __device__ __forceinline__ bool ss_gemv(const SSParams& p, const aoto_stream_sta
 }
 
 // ---------------------------------------------------------------------------
-// attention stage: one CTA per query head over the whole window
+// attention stage, window in shared memory: one CTA per query head over the whole window
 // ---------------------------------------------------------------------------
 // What a warp of a head CTA needs to know about its share of the window. The same for every
 // layer of a launch (the window length is a property of the step), so it is worked out once.

@@ -554,9 +554,12 @@ int64_t aoto_sm100_stamped_bytes(int64_t count);
  *   block (k = 0..7) covers columns c0+16k..c0+16k+15, so steps 0-3 belong to the first scale
  *   group and steps 4-7 to the second. Rows past N are zero.
  *
- * Layer-wise attention (rope_kv_cache_append + mask + attention, one CTA per query head) takes
- * the cache window the same way: every warp bulk-copies its share of the keys and values of
- * the NEXT layer while the current one is still being computed.
+ * Layer-wise attention (rope_kv_cache_append + mask + attention). A window of at most 256 slots
+ * whose buffers fit is handled by one CTA per query head, which takes the cache window the same
+ * way: every warp bulk-copies its share of the keys and values of the NEXT layer while the current
+ * one is still being computed. A longer window is cut into slices: CTA (kv head, slice) scores
+ * all query heads of the group against its slice, and CTA h merges head h's partial results
+ * (which travel through `scratch`, see aoto_sm100_stream_step_scratch_bytes_for).
  */
 #define AOTO_STREAM_WARPS 16
 #define AOTO_STREAM_BLOCK_BYTES 1088
