@@ -31,6 +31,7 @@ ADDEND_NONE, ADDEND_VECTOR, ADDEND_FULL = 0, 1, 2
 EPILOGUE_NONE, EPILOGUE_SILU_MUL, EPILOGUE_SILU_MUL_PAIRED = 0, 1, 2
 FLAG_PDL = 1
 FLAG_WEIGHT_BITS_8 = 2
+FLAG_WEIGHT_DENSE = 4
 
 
 class QMatmulArgs(Structure):

@@ -418,6 +418,9 @@ def _lower_projection(b: _Builder, index: int, op: Operation) -> None:
         return
 
     weight_id = inputs[base + 1]
+    if weight_id not in b.folded_weights and _is_dense_projection(b, op, weight_id, has_norm, epilogue):
+        _lower_dense_projection(b, index, op, base, rows, out_shape, alpha, beta, epilogue)
+        return
     if weight_id not in b.folded_weights or has_norm or epilogue not in (None, "silu_mul"):
         raise UnsupportedOperationError(
             f"dense {op.op} (operand {weight_id}) has no cuda-sm100 kernel: this target covers "
@@ -445,6 +448,51 @@ def _lower_projection(b: _Builder, index: int, op: Operation) -> None:
              "multi-row projection over a packed weight: unpacked to bf16 on the fly, never stored",
              fn, f"aoto_sm100_qmatmul[{variant}]",
              (("M", rows), ("N", n_rows), ("K", words * (32 // unpack_bits)), ("weight_bits", unpack_bits)))
+
+
+def _is_dense_projection(b: _Builder, op: Operation, weight_id: str, has_norm: bool, epilogue) -> bool:
+    """A dense decoder's projection: ``x @ W^T`` with ``W [N, K]`` a bf16 tensor bound to the plan."""
+
+    if has_norm or epilogue not in (None, "silu_mul", "silu_mul_paired") or not op.attrs.get("transpose_b", False):
+        return False
+    if op.attrs.get("transpose_a", False) or weight_id not in b.graph.inputs:
+        return False
+    shape = b.shape_of(weight_id)
+    return len(shape) == 2 and b.dtype_of(weight_id) == DType.BF16 and shape[1] % 8 == 0
+
+
+def _lower_dense_projection(b: _Builder, index: int, op: Operation, base: int, rows: int, out_shape, alpha: float,
+                            beta: float, epilogue) -> None:
+    """``matmul`` / ``addmm`` over a dense bf16 weight (``quantize=None`` decoders)."""
+
+    is_addmm = op.op == "addmm"
+    inputs = list(op.inputs)
+    paired = epilogue == "silu_mul_paired"
+    second_at = base + 2 if paired else None
+    gate_at = base + 2 if epilogue == "silu_mul" else None
+    expected = base + 2 + (1 if paired or gate_at is not None else 0)
+    if len(inputs) != expected:
+        raise CompilationError(f"dense {op.op} has {len(inputs)} operands, expected {expected}")
+    if paired and rows != 1:
+        raise UnsupportedOperationError("the paired gate/up form of a dense projection takes one activation row")
+    n_rows, inner = b.shape_of(inputs[base + 1])
+
+    def fn(*args, _s=out_shape):
+        out = ops.dmatmul(
+            args[base], args[base + 1], addend=args[0] if is_addmm else None,
+            weight2=args[second_at] if second_at is not None else None,
+            gate=args[gate_at] if gate_at is not None else None, alpha=alpha, beta=beta,
+        )
+        return out.reshape(_s)
+
+    variant = ops.dmatmul_variant(rows, n_rows, inner, paired)
+    if variant == "none":
+        raise UnsupportedOperationError(f"no dense kernel for a projection of {rows} x {inner} onto {n_rows} rows")
+    reason = "dense bf16 weight: a warp per weight row, fp32 accumulate, rounded once"
+    if paired:
+        reason += "; gate/up pair with the SiLU-mul epilogue"
+    b.record(index, op, CUDA_KERNEL, reason, fn, f"aoto_sm100_qmatmul[{variant}]",
+             (("M", rows), ("N", n_rows), ("K", inner), ("weight_bits", 16)))
 
 
 class CudaBackend:

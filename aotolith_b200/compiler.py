@@ -317,11 +317,24 @@ def compile_module(
     state_names, state_values = _module_state(module)
     positional = tuple(example_inputs)
     n_inputs, n_kwargs = len(positional), len(tensor_kwarg_names)
+    last_name: dict[tuple, str] = {}
+    for name, value in zip(state_names, state_values):
+        last_name[(value.data_ptr(), value.dtype, tuple(value.shape), tuple(value.stride()))] = name
+    tied = {}
+    for name, value in zip(state_names, state_values):
+        last = last_name[(value.data_ptr(), value.dtype, tuple(value.shape), tuple(value.stride()))]
+        if last != name and value.numel():
+            tied[name] = last
 
     def traced(*flat):
         call_kwargs = dict(static_kwargs)
         call_kwargs.update(zip(tensor_kwarg_names, flat[n_inputs : n_inputs + n_kwargs]))
         state = dict(zip(state_names, flat[n_inputs + n_kwargs :]))
+        # A tied tensor (an LM head that is the embedding) stays one graph input per name, as in the
+        # reference's plans, and every use reads the input of the last name it is reachable by
+        # (reference: src/aotolith/compiler.py:485-503, whose functional call ties them the same way).
+        for name, last in tied.items():
+            state[name] = state[last]
         return select_module_output(functional_call(module, state, tuple(flat[:n_inputs]), call_kwargs), output_key)
 
     examples = [*positional, *(kwargs[name] for name in tensor_kwarg_names), *state_values]

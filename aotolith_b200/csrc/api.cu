@@ -17,6 +17,9 @@ int qgemm_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
 bool qmatmul_i8_supported(const aoto_qmatmul_args& a);
 int qmatmul_i8_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
 const char* qmatmul_i8_variant(const aoto_qmatmul_args& a);
+bool dmatmul_supported(const aoto_qmatmul_args& a);
+int dmatmul_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
+const char* dmatmul_variant(const aoto_qmatmul_args& a);
 int dequantize_i8_launch(const aoto_dequantize_args& a, cudaStream_t stream);
 }  // namespace aoto
 
@@ -41,19 +44,21 @@ extern "C" const char* aoto_sm100_status_string(int status) {
 extern "C" int aoto_sm100_qmatmul_supported(const aoto_qmatmul_args* a) {
   if (!a) return 0;
   if (qgemv_check(*a, false) != AOTO_OK) return 0;
+  if (a->flags & AOTO_FLAG_WEIGHT_DENSE) return dmatmul_supported(*a) ? 1 : 0;
   if (a->flags & AOTO_FLAG_WEIGHT_BITS_8) return qmatmul_i8_supported(*a) ? 1 : 0;
   if (a->K > 49152) return 0;
   return 1;
 }
 
 extern "C" int64_t aoto_sm100_qmatmul_scratch_bytes(const aoto_qmatmul_args* a) {
-  if (!a || (a->flags & AOTO_FLAG_WEIGHT_BITS_8)) return 0;
+  if (!a || (a->flags & (AOTO_FLAG_WEIGHT_BITS_8 | AOTO_FLAG_WEIGHT_DENSE))) return 0;
   if (qgemm_tc_applies(*a)) return qgemm_tc_scratch_bytes(*a);  // split-K partial tiles
   return 0;
 }
 
 extern "C" const char* aoto_sm100_qmatmul_variant(const aoto_qmatmul_args* a) {
   if (!a) return "none";
+  if (a->flags & AOTO_FLAG_WEIGHT_DENSE) return dmatmul_supported(*a) ? dmatmul_variant(*a) : "none";
   if (a->flags & AOTO_FLAG_WEIGHT_BITS_8) return qmatmul_i8_supported(*a) ? qmatmul_i8_variant(*a) : "none";
   if (qgemm_tc_applies(*a)) return "gemm_tcgen05";
   if (qgemv_stream_applies(*a)) return "qgemv_stream";
@@ -65,6 +70,7 @@ extern "C" int aoto_sm100_qmatmul(const aoto_qmatmul_args* a, void* stream) {
   if (!a) return AOTO_ERR_ARGUMENT;
   const int status = qgemv_check(*a, true);
   if (status != AOTO_OK) return status;
+  if (a->flags & AOTO_FLAG_WEIGHT_DENSE) return dmatmul_launch(*a, (cudaStream_t)stream);
   if (a->flags & AOTO_FLAG_WEIGHT_BITS_8) return qmatmul_i8_launch(*a, (cudaStream_t)stream);
   if (qgemm_tc_applies(*a)) return qgemm_tc_launch(*a, (cudaStream_t)stream);
   if (qgemv_stream_applies(*a)) return qgemv_stream_launch(*a, (cudaStream_t)stream);

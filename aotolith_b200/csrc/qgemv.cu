@@ -253,18 +253,20 @@ static int launch_mma(const GemvParams& p, const GemvPlan& plan, int M, cudaStre
 }
 
 static int check_args(const aoto_qmatmul_args& a, bool pointers) {
-  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.group_size <= 0) return AOTO_ERR_ARGUMENT;
-  if (a.group_size % 8 != 0 || a.K % a.group_size != 0) return AOTO_ERR_ARGUMENT;
+  const bool dense = (a.flags & AOTO_FLAG_WEIGHT_DENSE) != 0;  // bf16 weights: no scales, no groups
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0) return AOTO_ERR_ARGUMENT;
+  if (!dense && (a.group_size <= 0 || a.group_size % 8 != 0 || a.K % a.group_size != 0)) return AOTO_ERR_ARGUMENT;
+  if (dense && (a.flags & AOTO_FLAG_WEIGHT_BITS_8)) return AOTO_ERR_ARGUMENT;
   if (a.addend_kind < AOTO_ADDEND_NONE || a.addend_kind > AOTO_ADDEND_FULL) return AOTO_ERR_ARGUMENT;
   if (a.epilogue < AOTO_EPILOGUE_NONE || a.epilogue > AOTO_EPILOGUE_SILU_MUL_PAIRED) return AOTO_ERR_ARGUMENT;
   if (!pointers) return AOTO_OK;
-  if (!a.x || !a.packed || !a.scales || !a.out) return AOTO_ERR_ARGUMENT;
+  if (!a.x || !a.packed || (!dense && !a.scales) || !a.out) return AOTO_ERR_ARGUMENT;
   if (a.addend_kind != AOTO_ADDEND_NONE && !a.addend) return AOTO_ERR_ARGUMENT;
   if (a.epilogue == AOTO_EPILOGUE_SILU_MUL && !a.gate) return AOTO_ERR_ARGUMENT;
-  if (a.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED && (!a.packed2 || !a.scales2)) return AOTO_ERR_ARGUMENT;
-  if (!aligned_to(a.x, 16) || !aligned_to(a.packed, 16) || !aligned_to(a.scales, 4)) return AOTO_ERR_ARGUMENT;
+  if (a.epilogue == AOTO_EPILOGUE_SILU_MUL_PAIRED && (!a.packed2 || (!dense && !a.scales2))) return AOTO_ERR_ARGUMENT;
+  if (!aligned_to(a.x, 16) || !aligned_to(a.packed, 16) || (!dense && !aligned_to(a.scales, 4))) return AOTO_ERR_ARGUMENT;
   if (a.norm_weight && !aligned_to(a.norm_weight, 16)) return AOTO_ERR_ARGUMENT;
-  if (a.packed2 && (!aligned_to(a.packed2, 16) || !aligned_to(a.scales2, 4))) return AOTO_ERR_ARGUMENT;
+  if (a.packed2 && (!aligned_to(a.packed2, 16) || (!dense && !aligned_to(a.scales2, 4)))) return AOTO_ERR_ARGUMENT;
   return AOTO_OK;
 }
 

@@ -340,3 +340,66 @@ class QuantizedDecoderDecodeModule(_QuantizedDecoder):
             self.cache_capacity, self.head_dim,
         )
         return self._logits(hidden), next_cache
+
+
+# ---------------------------------------------------------------------------
+# dense (unquantised) adapters
+# ---------------------------------------------------------------------------
+
+class _DenseDecoder(_QuantizedDecoder):
+    """The same forward pieces over the model's own bf16 weights.
+
+    Follows the dense adapter of the reference (``src/aotolith/models/decoder.py:282-420``): the
+    adapter keeps the model as a submodule, so the plan's state carries the model's own tensor
+    names; only the per-layer q/k/v weights (and biases) are concatenated once into
+    ``qkv_weight_{i}`` / ``qkv_bias_{i}`` buffers, registered after the rotary tables.
+    """
+
+    def __init__(self, model: torch.nn.Module, *, cache_capacity: int, require: str | None = None) -> None:
+        super().__init__(model, cache_capacity=cache_capacity, group_size=0, weight_bits=4, require=require)
+
+    def _pack(self, model: torch.nn.Module, dtype: torch.dtype) -> None:
+        self.model = model
+        for index, layer in enumerate(model.model.layers):
+            attention = layer.self_attn
+            self.register_buffer(
+                f"qkv_weight_{index}",
+                torch.cat((attention.q_proj.weight, attention.k_proj.weight, attention.v_proj.weight), dim=0).detach(),
+                persistent=False,
+            )
+            bias = _packed_qkv_bias(attention, self.family)
+            if bias is not None:
+                self.register_buffer(f"qkv_bias_{index}", bias, persistent=False)
+            for name, owner in _PER_LAYER:
+                if getattr(getattr(layer, owner), name).bias is not None:
+                    raise UnsupportedModelError(
+                        f"the {name} bias of the {self.family.label} adapter has no place in the decoder graphs")
+
+    @property
+    def embed_tokens_weight(self) -> torch.Tensor:
+        return self.model.model.embed_tokens.weight
+
+    def _weight(self, name: str, index: int) -> torch.Tensor:
+        if name == "qkv":
+            return self.get_buffer(f"qkv_weight_{index}")
+        if name == "lm_head":
+            return self.model.lm_head.weight
+        owner = dict(_PER_LAYER)[name]
+        return getattr(getattr(self.model.model.layers[index], owner), name).weight
+
+    def _norm(self, hidden: torch.Tensor, name: str) -> torch.Tensor:
+        if name == "final_norm":
+            weight = self.model.model.norm.weight
+        else:
+            kind, _, index = name.rpartition("_")
+            layer = self.model.model.layers[int(index)]
+            weight = layer.input_layernorm.weight if kind == "input_norm" else layer.post_attention_layernorm.weight
+        return F.rms_norm(hidden, (hidden.shape[-1],), weight, self.rms_norm_eps)
+
+
+class DecoderPrefillModule(_DenseDecoder, QuantizedDecoderPrefillModule):
+    """Dense prompt pass (``quantize=None``)."""
+
+
+class DecoderDecodeModule(_DenseDecoder, QuantizedDecoderDecodeModule):
+    """Dense decode step (``quantize=None``)."""

@@ -43,7 +43,9 @@ from ..planning import tensor_nbytes
 from ..runtime.plan import MEMORY_POLICIES
 from .adapters import (  # noqa: F401 - re-exported
     FAMILIES,
+    DecoderDecodeModule,
     DecoderFamily,
+    DecoderPrefillModule,
     QuantizedDecoderDecodeModule,
     QuantizedDecoderPrefillModule,
     family_for,
@@ -352,14 +354,15 @@ def _compile_bucket(
         )
     _check_quantize_bits(quantize, quantize_bits)
     if quantize is None:
-        raise UnsupportedModelError(
-            "the cuda-sm100 target compiles 4- and 8-bit packed decoders; dense projections have no "
-            "kernel on it yet",
-            hint="pass quantize=64",
-        )
-    settings = dict(cache_capacity=capacity, group_size=quantize, weight_bits=quantize_bits, require=family)
-    prefill_module = QuantizedDecoderPrefillModule(model, packed_from=_packed_from, **settings).eval()
-    decode_module = QuantizedDecoderDecodeModule(model, packed_from=prefill_module, **settings).eval()
+        # dense bf16 weights: the adapters read the model's own tensors (no packing, no shared packing)
+        if next(model.parameters()).dtype != torch.bfloat16:
+            raise UnsupportedModelError("the cuda-sm100 kernels compute in bfloat16", hint="convert the model with .bfloat16()")
+        prefill_module = DecoderPrefillModule(model, cache_capacity=capacity, require=family).eval()
+        decode_module = DecoderDecodeModule(model, cache_capacity=capacity, require=family).eval()
+    else:
+        settings = dict(cache_capacity=capacity, group_size=quantize, weight_bits=quantize_bits, require=family)
+        prefill_module = QuantizedDecoderPrefillModule(model, packed_from=_packed_from, **settings).eval()
+        decode_module = QuantizedDecoderDecodeModule(model, packed_from=prefill_module, **settings).eval()
     if isinstance(_packed_from, list):
         _packed_from.append(prefill_module)
     options = dict(codegen_matmul=codegen_matmul, codegen_attention=codegen_attention,

@@ -198,6 +198,81 @@ def qmatmul(
     return out
 
 
+def dmatmul(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    *,
+    addend: torch.Tensor | None = None,
+    weight2: torch.Tensor | None = None,
+    gate: torch.Tensor | None = None,
+    alpha: float = 1.0,
+    beta: float = 1.0,
+    out: torch.Tensor | None = None,
+    pdl: bool = False,
+) -> torch.Tensor:
+    """``beta*addend + alpha*(x @ W^T)`` with a dense bf16 ``W [N, K]`` (+ epilogue).
+
+    The unquantised counterpart of :func:`qmatmul`: ``addend`` is a bias ``[N]`` or a residual
+    shaped like the output, ``weight2`` selects the paired ``silu(y)*y2`` form (one row of ``x``),
+    ``gate`` the ``y*silu(gate)`` form. Same entry point, ``AOTO_FLAG_WEIGHT_DENSE``.
+    """
+
+    _need_cuda(x, weight, addend, weight2, gate)
+    _bf16(x, "x"); _bf16(weight, "weight"); _bf16(addend, "addend"); _bf16(weight2, "weight2"); _bf16(gate, "gate")
+    K = x.shape[-1]
+    if weight.dim() != 2 or weight.shape[1] != K:
+        raise PlanInputError(f"x has K={K} but the weight is {tuple(weight.shape)}")
+    if weight2 is not None and tuple(weight2.shape) != tuple(weight.shape):
+        raise PlanInputError("the two weights of the paired form must have one shape")
+    n_rows = weight.shape[0]
+    M = x.numel() // K
+    x2, weight = _dense(x).reshape(M, K), _dense(weight)
+    if out is None:
+        out = torch.empty(tuple(x.shape[:-1]) + (n_rows,), dtype=torch.bfloat16, device=x.device)
+    args = N.QMatmulArgs()
+    args.x, args.packed, args.out = _ptr(x2), _ptr(weight), _ptr(out)
+    args.M, args.N, args.K, args.group_size = M, n_rows, K, K
+    args.alpha, args.beta = alpha, beta
+    args.flags = (N.FLAG_PDL if pdl else 0) | N.FLAG_WEIGHT_DENSE
+    keep = [x2, weight]
+    if addend is not None:
+        addend = _dense(addend)
+        if addend.numel() == n_rows and (M == 1 or addend.dim() == 1):
+            args.addend_kind = N.ADDEND_VECTOR
+        elif addend.numel() == M * n_rows:
+            args.addend_kind = N.ADDEND_FULL
+        else:
+            raise PlanInputError(
+                f"addend of shape {tuple(addend.shape)} is neither a bias [N] nor shaped like the output"
+            )
+        args.addend = _ptr(addend)
+        keep.append(addend)
+    if weight2 is not None:
+        weight2 = _dense(weight2)
+        args.packed2 = _ptr(weight2)
+        args.epilogue = N.EPILOGUE_SILU_MUL_PAIRED
+        keep.append(weight2)
+    elif gate is not None:
+        gate = _dense(gate)
+        if gate.numel() != M * n_rows:
+            raise PlanInputError("gate must be shaped like the output")
+        args.gate = _ptr(gate)
+        args.epilogue = N.EPILOGUE_SILU_MUL
+        keep.append(gate)
+    N.check(N.load().aoto_sm100_qmatmul(ctypes.byref(args), _stream()), "aoto_sm100_qmatmul")
+    return out
+
+
+def dmatmul_variant(M: int, n_rows: int, K: int, paired: bool = False) -> str:
+    """Name of the kernel variant the library would launch for a dense projection of this shape."""
+
+    args = N.QMatmulArgs()
+    args.M, args.N, args.K, args.group_size = M, n_rows, K, K
+    args.flags = N.FLAG_WEIGHT_DENSE
+    args.epilogue = N.EPILOGUE_SILU_MUL_PAIRED if paired else N.EPILOGUE_NONE
+    return N.load().aoto_sm100_qmatmul_variant(ctypes.byref(args)).decode()
+
+
 def qmatmul_variant(M: int, n_rows: int, K: int, group_size: int, paired: bool = False, weight_bits: int = 4) -> str:
     """Name of the kernel variant the library would launch for this shape."""
 

@@ -912,6 +912,8 @@ def run_probe(name: str, probe_prompt: int = 0) -> None:
     ``attention`` six launches of prefill attention, 32 query / 8 kv heads, 1024 x 1024, D = 128, causal mask;
     ``i8``       eight-bit packed projections of the 0.5B shape, timed with CUDA events;
     ``i8_decoder`` one request of the default workload with the decoder packed with eight bits;
+    ``dense``    dense bf16 projections of the 0.5B and 8B shapes, timed with CUDA events;
+    ``dense_decoder`` one request of the default workload with the decoder's bf16 weights as they are;
     ``step``     a 4-layer Qwen2.5-0.5B-shaped decoder: prefill, then six launches of the step kernel;
     ``trace``    the same, then one more step with the kernel's own per-stage timeline printed;
     ``trace_llama`` the timeline for a 2-layer cut of the Llama-3-8B shape (prompt 128);
@@ -976,6 +978,54 @@ def run_probe(name: str, probe_prompt: int = 0) -> None:
             results.append({"K": K, "N": N, "M": M, "variant": ops.qmatmul_variant(M, N, K, GROUP, weight_bits=8),
                             "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1)})
         print(json.dumps({"probe": name, "note": "back-to-back launches over rotating weight copies larger than L2", "results": results}))
+    elif name == "dense":
+        # dense bf16 weights: the projections of one decode step at the 0.5B and 8B shapes, and prompt rows
+        results = []
+        for K, N, M, paired in ((896, 151936, 1, False), (896, 4864, 1, True), (4864, 896, 1, False), (4096, 14336, 1, True),
+                                (14336, 4096, 1, False), (4096, 6144, 1, False), (896, 4864, 8, False), (896, 4864, 128, False)):
+            nbytes = N * K * 2 * (2 if paired else 1)
+            copies = max(2, int(400e6 // nbytes) + 1)
+            weights = [(torch.randn(N, K, device=device, dtype=torch.bfloat16) * 0.02) for _ in range(copies * (2 if paired else 1))]
+            x = torch.randn(M, K, generator=generator).bfloat16().to(device)
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            rounds = 4
+            for i in range(copies * (rounds + 1)):
+                if i == copies:
+                    start.record()
+                ops.dmatmul(x, weights[i % copies], weight2=weights[copies + i % copies] if paired else None, out=out)
+            stop.record()
+            torch.cuda.synchronize()
+            us = start.elapsed_time(stop) * 1e3 / (copies * rounds)
+            results.append({"K": K, "N": N, "M": M, "paired": paired, "variant": ops.dmatmul_variant(M, N, K, paired),
+                            "us": round(us, 2), "gbs": round((nbytes + M * K * 2 + M * N * 2) / us / 1e3, 1)})
+            del weights
+        print(json.dumps({"probe": name, "note": "back-to-back launches over rotating weight copies larger than L2", "results": results}))
+    elif name == "dense_decoder":
+        # the whole decoder with its bf16 weights as they are: one request of the default workload, CUDA events
+        import aotolith_b200 as aoto
+        from aotolith_b200.models.synthetic import qwen25_05b_shaped
+
+        model = qwen25_05b_shaped(seed=0)
+        runtime = aoto.compile_qwen2_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS)
+        prompt = seeded_prompt(model.config.vocab_size, 1).to(device)
+        runtime.greedy_generate(prompt)
+        torch.cuda.synchronize()
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        marks[0].record()
+        logits, compact = runtime.prefill_ids(prompt)
+        cache = runtime.pad_cache(compact)
+        marks[1].record()
+        tokens = runtime.greedy_generate(prompt)
+        marks[2].record()
+        torch.cuda.synchronize()
+        prefill_ms = marks[0].elapsed_time(marks[1])
+        request_ms = marks[1].elapsed_time(marks[2])
+        decode_us = (request_ms - prefill_ms) * 1e3 / (NEW_TOKENS - 1)
+        print(json.dumps({"probe": name, "workload": "Qwen2.5-0.5B-shaped, dense bf16, prompt 128, 64 greedy tokens",
+                          "prefill_ms": round(prefill_ms, 3), "request_ms": round(request_ms, 3),
+                          "decode_us_per_token": round(decode_us, 1), "decode_tok_s": round(1e6 / decode_us, 1),
+                          "tokens": int(tokens.numel())}))
     elif name == "i8_decoder":
         # the whole decoder packed with eight bits: one request of the default workload, timed with CUDA events
         import aotolith_b200 as aoto
@@ -1049,7 +1099,7 @@ def main() -> None:
     parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
     parser.add_argument("--skip-multi", action="store_true",
                         help="with more than one GPU: leave the tensor-parallel and bucketed records out")
-    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "i8_decoder", "step", "trace", "trace_llama",
+    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "i8_decoder", "dense", "dense_decoder", "step", "trace", "trace_llama",
                                             "trace_llama_long"), default=None,
                         help="run a small fixed case of one kernel for a profiler instead of the benchmark")
     parser.add_argument("--probe-prompt", type=int, default=0, help="with --probe trace_llama_long: another prompt length")

@@ -107,6 +107,15 @@ typedef struct aoto_qmatmul_args {
  * (unpack by quantize.py:250-262), and the int8 GEMV codegen/matmul.py:742-929.
  */
 #define AOTO_FLAG_WEIGHT_BITS_8 2
+/*
+ * The weight is NOT packed: `packed` (and `packed2`) are dense bf16 matrices [N,K] as the model
+ * stores them, `scales` and `group_size` are ignored. K must be a multiple of 8 and at most 32768;
+ * no norm prologue (dense graphs keep the norm as its own operation); the paired epilogue needs
+ * M == 1; no workspace. Variants "dgemv" (M == 1) and "dgemm_rows". Replaces: dense
+ * `matmul`/`addmm{transpose_b}`, runtime/mlx_ops/__init__.py:587-619, and the transposed GEMV with
+ * its paired epilogue codegen/matmul.py:269-457.
+ */
+#define AOTO_FLAG_WEIGHT_DENSE 4
 
 int aoto_sm100_qmatmul(const aoto_qmatmul_args* args, void* stream);
 /*

@@ -63,6 +63,14 @@ def _projection(op, args):
     if attrs.get("transpose_b", False):
         right = right.transpose(-1, -2)
     product = (left.float() @ right.float()).to(left.dtype)
+    if epilogue == "silu_mul_paired":
+        # runtime/mlx_ops/__init__.py:589-596: the gate projection first, ``product * (left @ paired /
+        # (1 + exp(-product)))`` in the operands' dtype
+        paired = args[base + 2]
+        if attrs.get("transpose_b", False):
+            paired = paired.transpose(-1, -2)
+        other = (left.float() @ paired.float()).to(left.dtype)
+        return product * (other / (1.0 + torch.exp(-product)))
     if is_addmm:
         product = beta * args[0] + alpha * product
     if epilogue == "silu_mul":

@@ -139,8 +139,11 @@ def toy(family: str):
     return tiny_decoder(FAMILIES[family]["model_type"], seed=FAMILIES[family]["seed"])
 
 
-def run_family(family: str, bits: int):
-    """Lowered graphs and eager outputs of the reference's adapters for one toy decoder."""
+def run_family(family: str, bits: int, dense: bool = False):
+    """Lowered graphs and eager outputs of the reference's adapters for one toy decoder.
+
+    ``dense``: the unquantised adapters (``quantize=None``) instead of the packed ones.
+    """
 
     from torch.func import functional_call
 
@@ -151,8 +154,12 @@ def run_family(family: str, bits: int):
     model = toy(family)
     capacity = PROMPT + NEW
     settings = dict(cache_capacity=capacity, group_size=GROUP, weight_bits=bits, require=family)
-    prefill = D.QuantizedDecoderPrefillModule(model, **settings).eval()
-    decode = D.QuantizedDecoderDecodeModule(model, **settings).eval()
+    if dense:
+        prefill = D.DecoderPrefillModule(model, cache_capacity=capacity, require=family).eval()
+        decode = D.DecoderDecodeModule(model, cache_capacity=capacity, require=family).eval()
+    else:
+        prefill = D.QuantizedDecoderPrefillModule(model, **settings).eval()
+        decode = D.QuantizedDecoderDecodeModule(model, **settings).eval()
 
     def lowered(module, examples):
         state = {**dict(module.named_parameters(remove_duplicate=False)),
@@ -204,9 +211,9 @@ def run_family(family: str, bits: int):
     arrays = dict(prompt=prompt.numpy(), prefill_logits=prefill_logits, step_logits=np.stack(step_logits),
                   tokens=np.array(tokens), final_cache=cache.float().numpy(),
                   padded_prefill_logits=padded_logits.float().numpy())
-    if bits == 4:  # the eight-bit files reuse the weights stored beside the four-bit outputs
+    if bits == 4 and not dense:  # the other files reuse the weights stored beside the four-bit outputs
         arrays.update({f"w::{k}": v.detach().float().numpy() for k, v in model.state_dict().items()})
-    print(family, bits, "bits: tokens", tokens)
+    print(family, "dense" if dense else f"{bits} bits", ": tokens", tokens)
     return entry, arrays
 
 
@@ -335,8 +342,21 @@ def write_plain_llama() -> None:
     print("plain Llama:", len(graph.ops), "captured,", len(lowered.ops), "lowered operations")
 
 
+def write_dense_decoders() -> None:
+    """The unquantised adapters of the reference on the same toy decoders (weights: the four-bit files)."""
+
+    graphs = {}
+    for family in FAMILIES:
+        graphs[family], arrays = run_family(family, 4, dense=True)
+        np.savez_compressed(HERE / f"adapter_eager_dense_{family}.npz", **arrays)
+    (HERE / "lowered_graphs_dense.json").write_text(json.dumps(graphs, indent=1, sort_keys=True))
+
+
 def main(reference: str, only: str | None = None) -> None:
     load_reference(reference)
+    if only == "dense":
+        write_dense_decoders()
+        return
     if only == "plain":
         write_plain_llama()
         return
@@ -376,5 +396,5 @@ def main(reference: str, only: str | None = None) -> None:
 
 if __name__ == "__main__":
     if len(sys.argv) not in (2, 3):
-        raise SystemExit("usage: python make_fixtures.py <path of a checkout of the reference project> [int8|real|plain]")
+        raise SystemExit("usage: python make_fixtures.py <path of a checkout of the reference project> [int8|real|plain|dense]")
     main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)

@@ -102,6 +102,21 @@ def test_qmatmul_queries_are_host_only():
     eight.epilogue = N.EPILOGUE_SILU_MUL_PAIRED                       # the paired form needs a single row
     assert lib.aoto_sm100_qmatmul_supported(ctypes.byref(eight)) == 0
     assert lib.aoto_sm100_dequantize_i8(None, None) == N.ERR_ARGUMENT
+    # a dense bf16 weight (no scales, no groups): rows of whole 16-byte units, one row for the paired form
+    dense = _qargs(1, 1152, 896, 896)
+    dense.flags = N.FLAG_WEIGHT_DENSE
+    assert lib.aoto_sm100_qmatmul_supported(ctypes.byref(dense)) == 1
+    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(dense)) == b"dgemv"
+    assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(dense)) == 0
+    dense.M = 24
+    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(dense)) == b"dgemm_rows"
+    dense.epilogue = N.EPILOGUE_SILU_MUL_PAIRED
+    assert lib.aoto_sm100_qmatmul_supported(ctypes.byref(dense)) == 0
+    odd = _qargs(1, 16, 100, 100)                                      # 100 weights are not whole units
+    odd.flags = N.FLAG_WEIGHT_DENSE
+    assert lib.aoto_sm100_qmatmul_supported(ctypes.byref(odd)) == 0
+    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(odd)) == b"none"
+    assert lib.aoto_sm100_qmatmul(ctypes.byref(dense), None) == N.ERR_ARGUMENT
     # null pointers are refused before anything reaches the CUDA runtime
     assert lib.aoto_sm100_qmatmul(ctypes.byref(_qargs(1, 1152, 896, 64)), None) == N.ERR_ARGUMENT
     assert lib.aoto_sm100_qmatmul(None, None) == N.ERR_ARGUMENT
