@@ -11,7 +11,7 @@
 //               read its own 32-lane quadrant), turn each chunk through shared memory so that
 //               stores, addend and gate run along output rows, and run the epilogue.
 // A ring of four stages decouples the three roles; every hand-over is an mbarrier (TMA bytes,
-// one arrival per dequantising warp, tcgen05.commit). Every wait is bounded: a wait that runs out sets a
+// 256 dequantising threads, tcgen05.commit). Every wait is bounded: a wait that runs out sets a
 // status word, the roles fall through to the common exit and tensor memory is released.
 #include <cuda.h>
 
@@ -152,7 +152,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < TC_STAGES; ++s) {
       tc_bar_init(full_a + s, 1);
-      tc_bar_init(full_b + s, TC_DEQUANT_WARPS);  // one arrival per converting warp
+      tc_bar_init(full_b + s, TC_DEQUANT_WARPS * 32);
       tc_bar_init(empty + s, 1);
     }
     tc_bar_init(accumulated, 1);
@@ -236,9 +236,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
       const uint4 c0 = q0[a];
       const __nv_bfloat162 scale2 = __bfloat162bfloat162(__ushort_as_bfloat16((unsigned short)scale_bits[a]));
       request(a, kb + TC_AHEAD);
-      // lane 0 polls for the warp: the outcome is the same for every lane, so the warp leaves the
-      // loop together or not at all
-      ok = __shfl_sync(0xffffffffu, lane == 0 ? (int)tc_bar_wait(empty + s, (round & 1u) ^ 1u) : 0, 0) != 0;
+      ok = tc_bar_wait(empty + s, (round & 1u) ^ 1u);
       if (!ok) break;
       unsigned char* row = tile_b + (size_t)s * TC_TILE_BYTES + (size_t)r * 128;
       const uint32_t words[4] = {c0.x, c0.y, c0.z, c0.w};
@@ -259,10 +257,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
         *reinterpret_cast<uint4*>(row + ((i ^ (r & 7)) << 4)) = o;
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads through the async proxy
-      // One arrival per warp: 256 arrivals a k block on one barrier word serialise in shared
-      // memory. The warp barrier orders every lane's stores and fence before lane 0's arrival.
-      __syncwarp();
-      if (lane == 0) tc_bar_arrive(full_b + s);
+      tc_bar_arrive(full_b + s);
       }
     }
 
