@@ -21,6 +21,7 @@ The printed JSON line reports
                a launch inside the timed region, against the measured HBM peak;
 * ``lm_head_roofline`` the largest single projection (the LM-head GEMV over the packed
                vocabulary matrix) alone, on rotating weight copies larger than L2;
+* ``bf16``     the same decoder with dense bf16 weights (``quantize=None``), one GPU only;
 * ``cpu_baseline`` the same decoder evaluated eagerly by PyTorch on the host cores
                for a bounded sample (prefill + a few decode steps).
 
@@ -106,6 +107,64 @@ def step_bytes(config, valid_length: int) -> int:
     kv_read = 2 * kvh * d * 2 * valid_length
     kv_write = 2 * kvh * d * 2
     return layers * (qkv + o + gate_up + down + kv_read + kv_write) + head + h * 2
+
+
+def dense_step_bytes(config, valid_length: int) -> int:
+    """Algorithmic HBM bytes of one decode step over dense bf16 weights (two bytes a weight)."""
+
+    h, i, layers = config.hidden_size, config.intermediate_size, config.num_hidden_layers
+    qh, kvh, d, v = config.num_attention_heads, config.num_key_value_heads, config.head_dim, config.vocab_size
+
+    def dense(n, k, extra=0):
+        return n * k * 2 + k * 2 + n * 2 + extra
+
+    qkv = dense((qh + 2 * kvh) * d, h, extra=(qh + 2 * kvh) * d * 2 + 2 * h * 2)   # bias; the norm reads and writes x
+    o = dense(h, qh * d, extra=h * 2)                                              # residual
+    gate_up = 2 * i * h * 2 + h * 2 + i * 2 + 2 * h * 2
+    down = dense(h, i, extra=h * 2)
+    head = dense(v, h, extra=2 * h * 2)
+    kv_read = 2 * kvh * d * 2 * valid_length
+    kv_write = 2 * kvh * d * 2
+    return layers * (qkv + o + gate_up + down + kv_read + kv_write) + head + h * 2
+
+
+def measure_dense(model, prompt_host, device, peak: float, peak_kind: str, requests: int = 3) -> dict:
+    """The same decoder with its bf16 weights as they are (``quantize=None``): the ``bf16`` record.
+
+    One request = prefill + NEW_TOKENS - 1 decode steps through the per-operation plan under a
+    recorded graph; CUDA events around the prompt pass and around whole requests, weights (about
+    1 GB a step) larger than L2.
+    """
+
+    import aotolith_b200 as aoto
+
+    runtime = aoto.models.compile_decoder_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS,
+                                                       target="cuda-sm100")
+    prompt = prompt_host.to(device)
+    for _ in range(3):
+        tokens = runtime.greedy_generate(prompt)
+    torch.cuda.synchronize()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    marks[0].record()
+    for _ in range(requests):
+        runtime.prefill_ids(prompt)
+    marks[1].record()
+    for _ in range(requests):
+        tokens = runtime.greedy_generate(prompt)
+    marks[2].record()
+    torch.cuda.synchronize()
+    prefill_ms = marks[0].elapsed_time(marks[1]) / requests
+    request_ms = marks[1].elapsed_time(marks[2]) / requests
+    decode_us = (request_ms - prefill_ms) * 1e3 / (NEW_TOKENS - 1)
+    nbytes = dense_step_bytes(model.config, PROMPT + 1 + (NEW_TOKENS - 1) // 2)
+    achieved = nbytes / (decode_us * 1e-6) / 1e9
+    kinds = sorted({s.artifact_name for s in runtime.decode.plan.selections if s.kind in ("matmul", "addmm")})
+    return {"workload": "the same decoder with dense bf16 weights (quantize=None), prompt 128, 64 greedy tokens",
+            "value": 1e6 / decode_us, "unit": "tok/s", "decode_us_per_token": decode_us,
+            "prefill": {"ms": prefill_ms, "tok_s": PROMPT / prefill_ms * 1e3},
+            "roofline": {"kernel": "per-operation decode plan over " + ", ".join(kinds), "bound": "hbm", "achieved": achieved,
+                         "peak": peak, "unit": "GB/s", "frac": achieved / peak, "bytes_per_step": nbytes, "peak_source": peak_kind},
+            "tokens": int(tokens.numel())}
 
 
 class ClockSampler:
@@ -514,6 +573,10 @@ def run_ours(args) -> None:
         line.update(extra)
         if world == 1 and args.workload == "qwen25_05b":
             line["qmatmul_sweep"] = qmatmul_sweep(device, peak, tensor_peak())
+            try:
+                line["bf16"] = measure_dense(model, prompt_host, device, peak, peak_kind)
+            except Exception as error:  # noqa: BLE001 - a sub-record must not lose the line
+                line["bf16"] = {"error": f"{type(error).__name__}: {error}"[:500]}
         if world == 1 and not args.skip_cpu and not on_device:
             line["cpu_baseline"] = cpu_sample(model, prompt_host, 3)
         print(json.dumps(line))

@@ -55,3 +55,14 @@ def test_step_bytes_of_the_llama_shape():
     assert _weights(128256, 4096) == 279_085_056
     total = bench.step_bytes(config, 1152)
     assert 32 * layer_weights + 279_085_056 < total < (32 * layer_weights + 279_085_056) * 1.05
+
+
+def test_dense_step_bytes_of_the_qwen_shape():
+    """Two bytes a weight: the ~991 MB a step the reference's bf16 rows stream (``README.md:147-152``)."""
+
+    config = SimpleNamespace(hidden_size=896, intermediate_size=4864, num_hidden_layers=24, num_attention_heads=14,
+                             num_key_value_heads=2, head_dim=64, vocab_size=151936)
+    weights = 2 * (24 * (1152 * 896 + 896 * 896 + 3 * 4864 * 896) + 151936 * 896)
+    assert weights == 987_922_432
+    total = bench.dense_step_bytes(config, 160)
+    assert weights < total < weights * 1.01
