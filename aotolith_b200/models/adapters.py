@@ -342,6 +342,36 @@ class QuantizedDecoderDecodeModule(_QuantizedDecoder):
         return self._logits(hidden), next_cache
 
 
+class QuantizedDecoderRowsModule(_QuantizedDecoder):
+    """``m`` tokens in one step against the rolling cache, with the logits of every row.
+
+    The plan shape the reference names as its next step and does not ship
+    (``docs/host-runtime.md:186-208``: token and position inputs ``[m]`` wide, a mask of ``m``
+    rows, ``m`` rows of logits for a host that verifies proposed tokens). The window moves by
+    ``m`` slots; everything else is the one-token step (``models/decoder.py:586-633``).
+    """
+
+    def forward(self, input_ids, positions, attention_mask, cache):
+        rows = input_ids.shape[1]
+        hidden = F.embedding(input_ids, self.embed_tokens_weight)
+        pairs: list[torch.Tensor] = []
+        for index in range(self.num_layers):
+            query, key, value = self._qkv(hidden, positions, index)
+            pair = torch.cat(
+                (cache[index, :, :, :, rows:, :], torch.stack((key, value), dim=0)), dim=3
+            )
+            attended = F.scaled_dot_product_attention(
+                query, pair[0], pair[1], attn_mask=attention_mask, enable_gqa=True
+            )
+            hidden = self._mlp_and_residuals(hidden, attended, index)
+            pairs.append(pair)
+        next_cache = torch.stack(pairs, dim=0).reshape(
+            self.num_layers, 2, input_ids.shape[0], self.num_key_value_heads,
+            self.cache_capacity, self.head_dim,
+        )
+        return F.linear(self._norm(hidden, "final_norm"), self._weight("lm_head", 0)), next_cache
+
+
 # ---------------------------------------------------------------------------
 # dense (unquantised) adapters
 # ---------------------------------------------------------------------------
@@ -403,3 +433,7 @@ class DecoderPrefillModule(_DenseDecoder, QuantizedDecoderPrefillModule):
 
 class DecoderDecodeModule(_DenseDecoder, QuantizedDecoderDecodeModule):
     """Dense decode step (``quantize=None``)."""
+
+
+class DecoderRowsModule(_DenseDecoder, QuantizedDecoderRowsModule):
+    """Dense step over ``m`` tokens (``quantize=None``)."""

@@ -44,9 +44,11 @@ from ..runtime.plan import MEMORY_POLICIES
 from .adapters import (  # noqa: F401 - re-exported
     FAMILIES,
     DecoderDecodeModule,
+    DecoderRowsModule,
     DecoderFamily,
     DecoderPrefillModule,
     QuantizedDecoderDecodeModule,
+    QuantizedDecoderRowsModule,
     QuantizedDecoderPrefillModule,
     family_for,
 )
@@ -67,6 +69,24 @@ def prefill_mask(length: int, bucket: int) -> np.ndarray:
     query = np.arange(bucket)[:, None]
     key = np.arange(bucket)[None, :]
     return ((key <= query) & (key >= bucket - length))[None, None]
+
+
+def decode_rows_mask(valid_length: int, capacity: int, rows: int) -> np.ndarray:
+    """Boolean ``[1,1,rows,capacity]`` mask of a step over ``rows`` new tokens.
+
+    After the step the cache holds ``valid_length`` tokens in its last ``valid_length`` slots and
+    the new tokens sit in the last ``rows`` of them: row ``j`` admits every slot that holds a token
+    up to its own. With one row this is the reference's ``decode_mask``
+    (``models/decoder.py:960-979``).
+    """
+
+    if rows < 1 or capacity < rows:
+        raise PlanInputError(f"need 1 <= rows <= capacity, got rows={rows}, capacity={capacity}")
+    if not rows <= valid_length <= capacity:
+        raise PlanInputError(f"valid_length must be in [{rows}, {capacity}], got {valid_length}")
+    slot = np.arange(capacity)[None, :]
+    row = np.arange(rows)[:, None]
+    return ((slot >= capacity - valid_length) & (slot <= capacity - rows + row))[None, None]
 
 
 def _mb(value: int) -> str:
@@ -128,6 +148,8 @@ class DecoderStaticCacheRuntime:
     memory: str
     _prefill_mask: torch.Tensor
     _sessions: dict
+    rows: CompiledModulePlan | None = None      # the step over ``decode_rows`` tokens, when one was compiled
+    decode_rows: int = 0
 
     @property
     def device(self) -> torch.device:
@@ -211,6 +233,31 @@ class DecoderStaticCacheRuntime:
             verify_index_bounds=verify_token, memory=self.memory,
         )
 
+    def decode_tokens(
+        self, tokens: Any, cache: torch.Tensor, valid_length: int, *, verify_tokens: bool = True
+    ) -> tuple[torch.Tensor, torch.Tensor]:
+        """One step over ``decode_rows`` tokens: ``(logits [1, rows, vocab], next_cache)``.
+
+        The plan a host that verifies proposed tokens needs (the reference's stated next step,
+        ``docs/host-runtime.md:186-208``): the tokens sit at rotary positions ``valid_length - rows
+        .. valid_length - 1``, row ``j`` attends to everything up to its own token, the window moves
+        by ``rows`` slots and row ``j`` of the logits predicts the token after token ``j``. The
+        weights are streamed once for all rows. A host that accepts fewer than ``rows`` tokens keeps
+        the cache it passed in and replays the accepted ones.
+        """
+
+        if self.rows is None:
+            raise PlanInputError("this runtime has no multi-row step", hint="compile with decode_rows=<m>")
+        count = self.decode_rows
+        if valid_length < count or valid_length > self.cache_capacity:
+            raise PlanInputError(f"valid_length must be in [{count}, {self.cache_capacity}], got {valid_length}")
+        ids = _as_input_ids(tokens, self.device)
+        if tuple(ids.shape) != (1, count):
+            raise PlanInputError(f"expected tokens of shape (1, {count}), got {tuple(ids.shape)}")
+        positions = torch.arange(valid_length - count, valid_length, dtype=torch.int64, device=self.device)[None, :]
+        mask = torch.from_numpy(decode_rows_mask(valid_length, self.cache_capacity, count)).to(self.device)
+        return self.rows(ids, positions, mask, cache, verify_index_bounds=verify_tokens, memory=self.memory)
+
     def greedy_generate(
         self, input_ids: Any, *, max_new_tokens: int | None = None, sync_each_step: bool = False
     ) -> torch.Tensor:
@@ -227,6 +274,8 @@ class DecoderStaticCacheRuntime:
 
     def save(self, prefix: str | Path) -> tuple[Path, Path]:
         path = Path(prefix)
+        if self.rows is not None:
+            self.rows.save(path.with_name(path.name + ".rows.aoto"))
         return (
             self.prefill.save(path.with_name(path.name + ".prefill.aoto")),
             self.decode.save(path.with_name(path.name + ".decode.aoto")),
@@ -245,7 +294,9 @@ class DecoderStaticCacheRuntime:
     def memory_footprint(self) -> DecoderMemoryFootprint:
         cache_bytes = tensor_nbytes(self._cache_tensor_type())
         seen: dict[int, int] = {}
-        for plan in (self.prefill, self.decode):
+        for plan in (self.prefill, self.decode, self.rows):
+            if plan is None:
+                continue
             for tensor in plan._state_values:
                 seen[id(tensor)] = tensor.numel() * tensor.element_size()
         weights = sum(seen.values())
@@ -329,6 +380,7 @@ def _compile_bucket(
     family: str | None = None,
     target: str = DEFAULT_TARGET,
     memory: str = "latency",
+    decode_rows: int = 0,
     _packed_from: Any = None,
 ) -> DecoderStaticCacheRuntime:
     if memory not in MEMORY_POLICIES:
@@ -346,6 +398,11 @@ def _compile_bucket(
             hint="call model.eval() first",
         )
     capacity = prompt_length + max_new_tokens
+    if decode_rows < 0 or decode_rows == 1 or decode_rows > max(max_new_tokens, 0):
+        raise CompilationError(
+            f"decode_rows must be 0 (no multi-row step) or in [2, max_new_tokens], got {decode_rows}",
+            hint="the number of tokens a step consumes is a compile-time constant of its plan",
+        )
     if capacity > int(model.config.max_position_embeddings):
         raise DynamicShapeError(
             "prompt_length + max_new_tokens exceeds the model's maximum position embeddings "
@@ -359,10 +416,13 @@ def _compile_bucket(
             raise UnsupportedModelError("the cuda-sm100 kernels compute in bfloat16", hint="convert the model with .bfloat16()")
         prefill_module = DecoderPrefillModule(model, cache_capacity=capacity, require=family).eval()
         decode_module = DecoderDecodeModule(model, cache_capacity=capacity, require=family).eval()
+        rows_module = DecoderRowsModule(model, cache_capacity=capacity, require=family).eval() if decode_rows else None
     else:
         settings = dict(cache_capacity=capacity, group_size=quantize, weight_bits=quantize_bits, require=family)
         prefill_module = QuantizedDecoderPrefillModule(model, packed_from=_packed_from, **settings).eval()
         decode_module = QuantizedDecoderDecodeModule(model, packed_from=prefill_module, **settings).eval()
+        rows_module = (QuantizedDecoderRowsModule(model, packed_from=prefill_module, **settings).eval()
+                       if decode_rows else None)
     if isinstance(_packed_from, list):
         _packed_from.append(prefill_module)
     options = dict(codegen_matmul=codegen_matmul, codegen_attention=codegen_attention,
@@ -392,7 +452,25 @@ def _compile_bucket(
         ),
         **options,
     )
-    prefill, decode = share_plan_state([prefill, decode])
+    rows = None
+    if rows_module is not None:
+        rows = compile_module(
+            rows_module,
+            (
+                torch.zeros((1, decode_rows), dtype=torch.int64),
+                torch.zeros((1, decode_rows), dtype=torch.int64),
+                torch.ones((1, 1, decode_rows, capacity), dtype=torch.bool),
+                torch.zeros(
+                    (prefill_module.num_layers, 2, 1, prefill_module.num_key_value_heads, capacity,
+                     prefill_module.head_dim),
+                    dtype=dtype,
+                ),
+            ),
+            **options,
+        )
+        prefill, decode, rows = share_plan_state([prefill, decode, rows])
+    else:
+        prefill, decode = share_plan_state([prefill, decode])
     device = torch.device(decode.plan.device)
     runtime = DecoderStaticCacheRuntime(
         prefill=prefill,
@@ -407,8 +485,10 @@ def _compile_bucket(
         memory=memory,
         _prefill_mask=mask.to(device) if torch.cuda.is_available() else mask,
         _sessions={},
+        rows=rows,
+        decode_rows=decode_rows if rows is not None else 0,
     )
-    del prefill_module, decode_module
+    del prefill_module, decode_module, rows_module
     return runtime
 
 
@@ -419,6 +499,10 @@ def compile_decoder_static_cache(model: torch.nn.Module, *, prompt_length: int, 
     Keyword options: ``codegen_matmul``, ``codegen_attention``, ``autotune``,
     ``quantize`` (group size), ``quantize_bits``, ``family``, ``target``,
     ``memory`` - the reference's (``decoder.py:1090-1145``).
+
+    ``decode_rows=m`` (no reference counterpart: the plan shape its ``docs/host-runtime.md:186-208``
+    names as the next step) adds a third plan that consumes ``m`` tokens a step and returns ``m``
+    rows of logits: :meth:`DecoderStaticCacheRuntime.decode_tokens`.
 
     ``tensor_parallel`` (a process group, or ``True`` for the default one; no reference
     counterpart) shards the packed decoder over the group's GPUs instead and returns the

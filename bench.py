@@ -975,6 +975,7 @@ def run_probe(name: str, probe_prompt: int = 0) -> None:
     ``attention`` six launches of prefill attention, 32 query / 8 kv heads, 1024 x 1024, D = 128, causal mask;
     ``i8``       eight-bit packed projections of the 0.5B shape, timed with CUDA events;
     ``i8_decoder`` one request of the default workload with the decoder packed with eight bits;
+    ``rows``     one decode step over eight tokens (``decode_rows=8``) against eight one-token plan calls;
     ``dense``    dense bf16 projections of the 0.5B and 8B shapes, timed with CUDA events;
     ``dense_decoder`` one request of the default workload with the decoder's bf16 weights as they are;
     ``step``     a 4-layer Qwen2.5-0.5B-shaped decoder: prefill, then six launches of the step kernel;
@@ -1089,6 +1090,49 @@ def run_probe(name: str, probe_prompt: int = 0) -> None:
                           "prefill_ms": round(prefill_ms, 3), "request_ms": round(request_ms, 3),
                           "decode_us_per_token": round(decode_us, 1), "decode_tok_s": round(1e6 / decode_us, 1),
                           "tokens": int(tokens.numel())}))
+    elif name == "rows":
+        # a step over eight tokens against eight one-token steps, default workload, CUDA events
+        import aotolith_b200 as aoto
+        from aotolith_b200.models.synthetic import qwen25_05b_shaped
+
+        rows = 8
+        model = qwen25_05b_shaped(seed=0)
+        runtime = aoto.compile_qwen2_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS,
+                                                  quantize=GROUP, decode_rows=rows)
+        prompt = seeded_prompt(model.config.vocab_size, 1).to(device)
+        greedy = runtime.greedy_generate(prompt)                       # the tokens a host would propose
+        logits, compact = runtime.prefill_ids(prompt)
+        cache = runtime.pad_cache(compact)
+        proposed = greedy[:, :rows].contiguous()
+        for _ in range(3):
+            step_logits, _ = runtime.decode_tokens(proposed, cache, PROMPT + rows, verify_tokens=False)
+        torch.cuda.synchronize()
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        repeats = 10
+        marks[0].record()
+        for _ in range(repeats):
+            step_logits, _ = runtime.decode_tokens(proposed, cache, PROMPT + rows, verify_tokens=False)
+        marks[1].record()
+        for _ in range(repeats):
+            single, valid = cache, PROMPT
+            for j in range(rows):
+                valid += 1
+                one_logits, single = runtime.decode_token(proposed[:, j : j + 1], single, valid, verify_token=False)
+        marks[2].record()
+        torch.cuda.synchronize()
+        rows_us = marks[0].elapsed_time(marks[1]) * 1e3 / repeats
+        singles_us = marks[1].elapsed_time(marks[2]) * 1e3 / repeats
+        # row j predicts the token after proposed token j: the greedy continuation, when the proposal was the greedy one
+        predicted = step_logits[0].float().argmax(dim=-1)
+        agree = int((predicted[:-1] == greedy[0, 1:rows]).sum())
+        last_gap = float((step_logits[0, -1].float() - one_logits[0, -1].float()).abs().max() / one_logits.float().abs().max())
+        print(json.dumps({"probe": name, "workload": "Qwen2.5-0.5B-shaped, 4-bit g64, prompt 128: one step over 8 tokens",
+                          "rows": rows, "rows_step_us": round(rows_us, 1), "us_per_token": round(rows_us / rows, 1),
+                          "eight_one_token_plan_calls_us": round(singles_us, 1),
+                          "streamed_step_kernel_us_per_token": "see the bench line (decode_us_per_token)",
+                          "greedy_tokens_confirmed": f"{agree} of {rows - 1}", "last_row_vs_one_token_step": last_gap,
+                          "kernels": sorted({s.artifact_name for s in runtime.rows.plan.selections
+                                             if s.kind in ("matmul", "addmm", "attention")})}))
     elif name == "i8_decoder":
         # the whole decoder packed with eight bits: one request of the default workload, timed with CUDA events
         import aotolith_b200 as aoto
@@ -1162,7 +1206,7 @@ def main() -> None:
     parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
     parser.add_argument("--skip-multi", action="store_true",
                         help="with more than one GPU: leave the tensor-parallel and bucketed records out")
-    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "i8_decoder", "dense", "dense_decoder", "step", "trace", "trace_llama",
+    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "i8_decoder", "dense", "dense_decoder", "rows", "step", "trace", "trace_llama",
                                             "trace_llama_long"), default=None,
                         help="run a small fixed case of one kernel for a profiler instead of the benchmark")
     parser.add_argument("--probe-prompt", type=int, default=0, help="with --probe trace_llama_long: another prompt length")

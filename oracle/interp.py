@@ -228,6 +228,20 @@ class OracleRuntime:
             torch.tensor([[valid_length - 1]], dtype=torch.int64), mask, cache, unrounded=self.unrounded,
         )
 
+    def decode_rows(self, tokens, cache, valid_length):
+        """The step over ``decode_rows`` tokens: positions and mask as the runtime builds them."""
+
+        from aotolith_b200.models.decoder import decode_rows_mask
+
+        rt = self.rt
+        rows = rt.decode_rows
+        mask = torch.from_numpy(decode_rows_mask(valid_length, rt.cache_capacity, rows))
+        return run_module_plan(
+            rt.rows, torch.as_tensor(tokens, dtype=torch.int64).reshape(1, rows),
+            torch.arange(valid_length - rows, valid_length, dtype=torch.int64)[None, :], mask, cache,
+            unrounded=self.unrounded,
+        )
+
     def greedy(self, ids, steps):
         ids = torch.as_tensor(ids, dtype=torch.int64).reshape(1, -1)
         valid = ids.shape[1]

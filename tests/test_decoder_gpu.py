@@ -259,3 +259,56 @@ def test_step_kernel_streams_long_block_lists(cuda):
     want, trace, _ = OracleRuntime(runtime).greedy(prompt, 7)
     got = runtime.greedy_generate(prompt).cpu()[0].tolist()
     assert got == want, f"oracle top-2 gaps: {[top2_gap(t) for t in trace]}"
+
+
+# ---------------------------------------------------------------------------
+# a step over several tokens (decode_rows=m)
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("family,quantize,bits", [("qwen2", 16, 4), ("llama", 16, 4), ("qwen2", 16, 8), ("llama", None, 4)])
+def test_multirow_step_matches_oracle_and_one_token_steps(cuda, family, quantize, bits):
+    """``decode_tokens`` over three proposed tokens: the oracle over the same graph, and three
+    one-token steps of the same runtime (row j = step j, the final caches agree)."""
+
+    import aotolith_b200 as aoto
+    from oracle.interp import OracleRuntime
+    from tests.golden_util import NEW, PROMPT, eager_fixture
+
+    rows = 3
+    model, _ = eager_fixture(family)
+    runtime = aoto.models.compile_decoder_static_cache(
+        model, prompt_length=PROMPT, max_new_tokens=NEW, quantize=quantize, quantize_bits=bits, family=family,
+        decode_rows=rows)
+    oracle = OracleRuntime(runtime)
+    generator = torch.Generator().manual_seed(9)
+    vocab = model.config.vocab_size
+    prompt = torch.randint(0, vocab, (1, PROMPT), generator=generator)
+    tokens = torch.randint(0, vocab, (1, rows), generator=generator)
+    _, compact = runtime.prefill_ids(prompt)
+    cache = runtime.pad_cache(compact)
+    _, want_cache0 = oracle.prefill(prompt)
+
+    def rel(actual, expected):
+        expected = expected.float().cpu()
+        return float((actual.float().cpu() - expected).abs().max() / expected.abs().max().clamp_min(1e-6))
+
+    logits, next_cache = runtime.decode_tokens(tokens, cache, PROMPT + rows)
+    want_logits, want_cache = oracle.decode_rows(tokens, want_cache0, PROMPT + rows)
+    assert tuple(logits.shape) == (1, rows, vocab)
+    assert rel(logits, want_logits) < 2e-2
+    assert rel(next_cache, want_cache) < 2e-2
+    single, valid = cache, PROMPT
+    for j in range(rows):
+        valid += 1
+        one, single = runtime.decode_token(tokens[:, j : j + 1], single, valid)
+        assert rel(logits[:, j, :], one[:, -1, :]) < 2e-2, f"row {j}"
+    assert rel(next_cache, single) < 2e-2
+    # the call is repeatable and continues from its own cache
+    again, _ = runtime.decode_tokens(tokens, cache, PROMPT + rows)
+    assert torch.equal(again, logits)
+    more = torch.randint(0, vocab, (1, rows), generator=generator)
+    logits2, _ = runtime.decode_tokens(more, next_cache, PROMPT + 2 * rows)
+    want2, _ = oracle.decode_rows(more, want_cache, PROMPT + 2 * rows)
+    assert rel(logits2, want2) < 2e-2
+    with pytest.raises(Exception):
+        runtime.decode_tokens(tokens[:, :2], cache, PROMPT + rows)
