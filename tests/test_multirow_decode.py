@@ -137,3 +137,12 @@ def test_refusals():
     assert plain.rows is None and plain.decode_rows == 0
     with pytest.raises(PlanInputError, match="multi-row"):
         plain.decode_tokens(torch.zeros((1, ROWS), dtype=torch.int64), None, PROMPT + ROWS)
+
+
+def test_the_step_is_saved_and_loaded_with_the_runtime(case, tmp_path):
+    runtime = case
+    runtime.save(tmp_path / "decoder")
+    loaded = aoto.load_compiled_module(tmp_path / "decoder.rows.aoto")
+    assert [s.artifact_name for s in loaded.plan.selections] == [s.artifact_name for s in runtime.rows.plan.selections]
+    assert list(loaded.state_names) == list(runtime.rows.state_names)
+    assert tuple(loaded.plan.graph.value(loaded.plan.graph.inputs[0]).type.shape) == (1, ROWS)
