@@ -166,10 +166,16 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  // Launched as a programmatic dependent, this grid may start while its producer still runs: the
+  // packed weights are constants, so their conversion goes ahead; whatever the producer writes
+  // (the activations, addend and gate) and whatever this grid writes is touched only behind a wait
+  // for the producer's completion. The grid after this one may start as early in turn.
+  pdl_release_dependents();
 
   if (warp == 0) {
     // ---- activation tiles by TMA ----
     if (lane == 0) {
+      pdl_wait_for_producers();
       for (int kb = 0; kb < blocks && ok; ++kb) {
         const int s = kb % TC_STAGES;
         const uint32_t round = (uint32_t)(kb / TC_STAGES);
@@ -263,6 +269,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
 
     // epilogue: warp q of a warpgroup may read tensor-memory lanes 32q..32q+31; two warps share
     // a lane quadrant and each takes half of the 128 columns of every tile
+    pdl_wait_for_producers();  // addend, gate, the output and the split-K workspace belong to the stream's order
     if (ok) ok = tc_bar_wait(accumulated, 0u);
     ok = __all_sync(0xffffffffu, ok);  // the epilogue below synchronises the warp: all lanes or none
     const int quadrant = warp & 3;
@@ -524,8 +531,9 @@ int qgemm_tc_launch(const aoto_qmatmul_args& a, cudaStream_t stream) {
   p.addend_kind = a.addend_kind; p.epilogue = a.epilogue;
   p.alpha = a.alpha; p.beta = a.beta;
   dim3 grid(plan.grid_x, plan.grid_y, plan.splits), block(TC_THREADS);
-  if (m_tiles == 2) return launch_kernel(qgemm_tc_kernel<2>, grid, block, tc_smem_bytes(2), stream, false, map, p);
-  return launch_kernel(qgemm_tc_kernel<1>, grid, block, tc_smem_bytes(1), stream, false, map, p);
+  const bool pdl = (a.flags & AOTO_FLAG_PDL) != 0;
+  if (m_tiles == 2) return launch_kernel(qgemm_tc_kernel<2>, grid, block, tc_smem_bytes(2), stream, pdl, map, p);
+  return launch_kernel(qgemm_tc_kernel<1>, grid, block, tc_smem_bytes(1), stream, pdl, map, p);
 }
 
 // Reads and clears the flag a timed-out wait of the tensor-core GEMM sets. Synchronises the

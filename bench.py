@@ -976,6 +976,7 @@ def run_probe(name: str, probe_prompt: int = 0) -> None:
     ``i8``       eight-bit packed projections of the 0.5B shape, timed with CUDA events;
     ``i8_decoder`` one request of the default workload with the decoder packed with eight bits;
     ``rows``     one decode step over eight tokens (``decode_rows=8``) against eight one-token plan calls;
+    ``dense_lm_head`` six dense GEMV launches over two copies of a [151936, 896] bf16 weight;
     ``dense``    dense bf16 projections of the 0.5B and 8B shapes, timed with CUDA events;
     ``dense_decoder`` one request of the default workload with the decoder's bf16 weights as they are;
     ``step``     a 4-layer Qwen2.5-0.5B-shaped decoder: prefill, then six launches of the step kernel;
@@ -1042,6 +1043,16 @@ def run_probe(name: str, probe_prompt: int = 0) -> None:
             results.append({"K": K, "N": N, "M": M, "variant": ops.qmatmul_variant(M, N, K, GROUP, weight_bits=8),
                             "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1)})
         print(json.dumps({"probe": name, "note": "back-to-back launches over rotating weight copies larger than L2", "results": results}))
+    elif name == "dense_lm_head":
+        # six launches of the dense GEMV over two copies of a [151936, 896] bf16 weight (544 MB, larger than L2)
+        N, K = 151936, 896
+        weights = [torch.randn(N, K, device=device, dtype=torch.bfloat16) * 0.02 for _ in range(2)]
+        x = torch.randn(1, K, generator=generator).bfloat16().to(device)
+        out = torch.empty(1, N, dtype=torch.bfloat16, device=device)
+        for i in range(6):
+            ops.dmatmul(x, weights[i % 2], out=out)
+        torch.cuda.synchronize()
+        print(json.dumps({"probe": name, "variant": ops.dmatmul_variant(1, N, K), "max": float(out.float().abs().max())}))
     elif name == "dense":
         # dense bf16 weights: the projections of one decode step at the 0.5B and 8B shapes, and prompt rows
         results = []
@@ -1206,7 +1217,7 @@ def main() -> None:
     parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
     parser.add_argument("--skip-multi", action="store_true",
                         help="with more than one GPU: leave the tensor-parallel and bucketed records out")
-    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "i8_decoder", "dense", "dense_decoder", "rows", "step", "trace", "trace_llama",
+    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "i8_decoder", "dense", "dense_lm_head", "dense_decoder", "rows", "step", "trace", "trace_llama",
                                             "trace_llama_long"), default=None,
                         help="run a small fixed case of one kernel for a profiler instead of the benchmark")
     parser.add_argument("--probe-prompt", type=int, default=0, help="with --probe trace_llama_long: another prompt length")
