@@ -429,21 +429,26 @@ def _lower_projection(b: _Builder, index: int, op: Operation) -> None:
         )
     gate_at = base + 2 if epilogue == "silu_mul" else None
 
+    unpack = b.producer[weight_id]
+    n_rows, words = b.shape_of(unpack.inputs[0])
+    unpack_bits = _UNPACK_BITS[unpack.op]
+    variant = ops.qmatmul_variant(rows, n_rows, words * (32 // unpack_bits), int(unpack.attrs["group_size"]),
+                                  weight_bits=unpack_bits)
+    # The tcgen05 kernel converts its constant weights before it waits for the producer of its
+    # activations, so it is launched as a programmatic dependent: in a recorded plan its start and
+    # the first weight tiles overlap the tail of the kernel before it.
+    dependent = variant == "gemm_tcgen05"
+
     def fn(*args, _s=out_shape):
         weight = args[base + 1]
         out = ops.qmatmul(
             args[base], weight.packed, weight.scales, group_size=weight.group_size,
             addend=args[0] if is_addmm else None,
             gate=args[gate_at] if gate_at is not None else None, alpha=alpha, beta=beta,
-            weight_bits=weight.bits,
+            weight_bits=weight.bits, pdl=dependent,
         )
         return out.reshape(_s)
 
-    unpack = b.producer[weight_id]
-    n_rows, words = b.shape_of(unpack.inputs[0])
-    unpack_bits = _UNPACK_BITS[unpack.op]
-    variant = ops.qmatmul_variant(rows, n_rows, words * (32 // unpack_bits), int(unpack.attrs["group_size"]),
-                                  weight_bits=unpack_bits)
     b.record(index, op, CUDA_KERNEL,
              "multi-row projection over a packed weight: unpacked to bf16 on the fly, never stored",
              fn, f"aoto_sm100_qmatmul[{variant}]",

@@ -188,6 +188,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
   } else if (warp == 1) {
     // ---- tensor-core issue ----
     if (lane == 0) {
+      pdl_wait_for_producers();  // nothing to multiply before the producer is done: wait here, not in bounded polls
       const uint32_t idesc = tc_instruction_descriptor(TC_BM, TC_BN);
       for (int kb = 0; kb < blocks && ok; ++kb) {
         const int s = kb % TC_STAGES;

@@ -106,7 +106,10 @@ def test_qmatmul_queries_are_host_only():
     dense = _qargs(1, 1152, 896, 896)
     dense.flags = N.FLAG_WEIGHT_DENSE
     assert lib.aoto_sm100_qmatmul_supported(ctypes.byref(dense)) == 1
-    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(dense)) == b"dgemv"
+    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(dense)) == b"dgemv_mma"      # one row, K a multiple of 32
+    narrow = _qargs(1, 1152, 72, 72)
+    narrow.flags = N.FLAG_WEIGHT_DENSE
+    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(narrow)) == b"dgemv"         # other K: a warp per weight row
     assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(dense)) == 0
     dense.M = 24
     assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(dense)) == b"dgemm_rows"

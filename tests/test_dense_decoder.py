@@ -55,9 +55,11 @@ def test_lowered_graph_matches_reference(case, which):
 
 def test_every_projection_is_bound_to_the_dense_kernel(case):
     _, runtime, _ = case
-    for plan, variant in ((runtime.decode.plan, "dgemv"), (runtime.prefill.plan, "dgemm_rows")):
+    # one row: the tensor-pipe GEMV (K = 64 or 128 here); the prompt's rows: the row-staging kernel,
+    # and the LM head of the prompt pass reads one row again
+    for plan, variant in ((runtime.decode.plan, "dgemv_mma"), (runtime.prefill.plan, "dgemm_rows")):
         chosen = [s for s in plan.selections if s.kind in ("matmul", "addmm")]
-        assert chosen and all(s.is_native and s.artifact_name in (f"aoto_sm100_qmatmul[{variant}]", "aoto_sm100_qmatmul[dgemv]")
+        assert chosen and all(s.is_native and s.artifact_name in (f"aoto_sm100_qmatmul[{variant}]", "aoto_sm100_qmatmul[dgemv_mma]")
                               for s in chosen)
         assert any(s.artifact_name == f"aoto_sm100_qmatmul[{variant}]" for s in chosen)
         assert all(s.is_native for s in plan.selections if s.kind in ("attention", "rms_norm", "rope_kv_cache_append"))

@@ -41,7 +41,8 @@ def _check(got, rounded, exact):
 
 
 # the benchmarked decoders' projection shapes (0.5B and 8B) beside ragged small ones
-SHAPES = [(896, 1152), (896, 4864), (4864, 896), (4096, 6144), (14336, 4096), (64, 24), (8, 3), (72, 130), (1000, 17)]
+SHAPES = [(896, 1152), (896, 4864), (4864, 896), (4096, 6144), (14336, 4096), (64, 24), (8, 3), (72, 130), (1000, 17),
+          (32, 16), (96, 19), (896, 18947), (32768, 40)]
 
 
 @pytest.mark.parametrize("K,N", SHAPES)
@@ -51,7 +52,8 @@ def test_dmatmul_plain(cuda, K, N, M):
     x, weight = activations(3, M, K), dense_weight(4, N, K)
     got = ops.dmatmul(x.to(cuda), weight.to(cuda)).cpu()
     _check(got, _rounded(x, weight), x.double() @ weight.double().T)
-    assert ops.dmatmul_variant(M, N, K) == ("dgemv" if M == 1 else "dgemm_rows")
+    one_row = "dgemv_mma" if K % 32 == 0 and N >= 16 else "dgemv"
+    assert ops.dmatmul_variant(M, N, K) == (one_row if M == 1 else "dgemm_rows")
 
 
 @pytest.mark.parametrize("K,N", [(896, 1152), (4096, 4096), (64, 24), (72, 130)])
@@ -69,7 +71,7 @@ def test_dmatmul_bias_residual_and_scales(cuda, K, N, M):
            2.0 * residual.double() + 0.5 * exact)
 
 
-@pytest.mark.parametrize("K,N", [(896, 4864), (4096, 14336), (64, 24), (72, 130)])
+@pytest.mark.parametrize("K,N", [(896, 4864), (4096, 14336), (64, 24), (72, 130), (896, 18950), (96, 19)])
 def test_dmatmul_paired_gate_up(cuda, K, N):
     """One row, two weights: ``silu(x W1^T) * (x W2^T)`` as runtime/mlx_ops/__init__.py:589-596 states it."""
 
@@ -82,7 +84,7 @@ def test_dmatmul_paired_gate_up(cuda, K, N):
     rounded = product * (other / (1.0 + torch.exp(-product)))
     assert got.dtype == torch.bfloat16 and got.shape == (1, N)
     assert rel_max_error(got.double(), exact) <= max(EXACT_TOL, 1.25 * rel_max_error(rounded.double(), exact))
-    assert ops.dmatmul_variant(1, N, K, paired=True) == "dgemv"
+    assert ops.dmatmul_variant(1, N, K, paired=True) == ("dgemv_mma" if K % 32 == 0 and K < 2048 else "dgemv")
 
 
 @pytest.mark.parametrize("M", [1, 6])
