@@ -111,7 +111,9 @@ typedef struct aoto_qmatmul_args {
  * The weight is NOT packed: `packed` (and `packed2`) are dense bf16 matrices [N,K] as the model
  * stores them, `scales` and `group_size` are ignored. K must be a multiple of 8 and at most 32768;
  * no norm prologue (dense graphs keep the norm as its own operation); the paired epilogue needs
- * M == 1; no workspace. Variants "dgemv" (M == 1) and "dgemm_rows". Replaces: dense
+ * M == 1; no workspace; operands on 16-byte boundaries. Variants "dgemv_mma" (M == 1, K a multiple
+ * of 32, N >= 16: the multiply-add on the tensor pipe), "dgemv" (other single rows) and
+ * "dgemm_rows". Replaces: dense
  * `matmul`/`addmm{transpose_b}`, runtime/mlx_ops/__init__.py:587-619, and the transposed GEMV with
  * its paired epilogue codegen/matmul.py:269-457.
  */
