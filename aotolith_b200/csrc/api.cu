@@ -8,6 +8,8 @@ int qgemv_check(const aoto_qmatmul_args& a, bool pointers);
 const char* qgemv_variant(const aoto_qmatmul_args& a);
 bool qgemm_applies(const aoto_qmatmul_args& a);
 bool qgemm_tc_applies(const aoto_qmatmul_args& a);
+bool qgemm_rows_applies(const aoto_qmatmul_args& a);
+int qgemm_rows_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
 bool qgemv_stream_applies(const aoto_qmatmul_args& a);
 int qgemv_stream_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
 int qgemm_tc_launch(const aoto_qmatmul_args& a, cudaStream_t stream);
@@ -52,6 +54,7 @@ extern "C" int aoto_sm100_qmatmul_supported(const aoto_qmatmul_args* a) {
 
 extern "C" int64_t aoto_sm100_qmatmul_scratch_bytes(const aoto_qmatmul_args* a) {
   if (!a || (a->flags & (AOTO_FLAG_WEIGHT_BITS_8 | AOTO_FLAG_WEIGHT_DENSE))) return 0;
+  if (qgemm_rows_applies(*a)) return 0;
   if (qgemm_tc_applies(*a)) return qgemm_tc_scratch_bytes(*a);  // split-K partial tiles
   return 0;
 }
@@ -60,6 +63,7 @@ extern "C" const char* aoto_sm100_qmatmul_variant(const aoto_qmatmul_args* a) {
   if (!a) return "none";
   if (a->flags & AOTO_FLAG_WEIGHT_DENSE) return dmatmul_supported(*a) ? dmatmul_variant(*a) : "none";
   if (a->flags & AOTO_FLAG_WEIGHT_BITS_8) return qmatmul_i8_supported(*a) ? qmatmul_i8_variant(*a) : "none";
+  if (qgemm_rows_applies(*a)) return "qgemm_rows";
   if (qgemm_tc_applies(*a)) return "gemm_tcgen05";
   if (qgemv_stream_applies(*a)) return "qgemv_stream";
   if (qgemm_applies(*a)) return "gemm_mma";
@@ -72,6 +76,7 @@ extern "C" int aoto_sm100_qmatmul(const aoto_qmatmul_args* a, void* stream) {
   if (status != AOTO_OK) return status;
   if (a->flags & AOTO_FLAG_WEIGHT_DENSE) return dmatmul_launch(*a, (cudaStream_t)stream);
   if (a->flags & AOTO_FLAG_WEIGHT_BITS_8) return qmatmul_i8_launch(*a, (cudaStream_t)stream);
+  if (qgemm_rows_applies(*a)) return qgemm_rows_launch(*a, (cudaStream_t)stream);
   if (qgemm_tc_applies(*a)) return qgemm_tc_launch(*a, (cudaStream_t)stream);
   if (qgemv_stream_applies(*a)) return qgemv_stream_launch(*a, (cudaStream_t)stream);
   if (qgemm_applies(*a)) return qgemm_launch(*a, (cudaStream_t)stream);

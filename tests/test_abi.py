@@ -83,7 +83,10 @@ def test_qmatmul_queries_are_host_only():
     assert lib.aoto_sm100_qmatmul_supported(ctypes.byref(_qargs(0, 16, 128, 64))) == 0
     assert lib.aoto_sm100_qmatmul_supported(None) == 0
     assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(_qargs(1, 1152, 896, 64))) == b"qgemv_mma"
-    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(_qargs(16, 1152, 896, 64))) == b"gemm_mma"
+    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(_qargs(16, 1152, 896, 64))) == b"qgemm_rows"   # 2..16 rows
+    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(_qargs(24, 1152, 896, 64))) == b"gemm_mma"
+    assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(_qargs(8, 4096, 14336, 64))) == b"gemm_tcgen05"  # staged rows too long
+    assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(_qargs(16, 896, 4864, 64))) == 0
     assert lib.aoto_sm100_qmatmul_variant(ctypes.byref(_qargs(1, 24, 64, 16))) == b"qgemv_generic"
     assert lib.aoto_sm100_qmatmul_scratch_bytes(ctypes.byref(_qargs(1, 1152, 896, 64))) == 0
     # narrow prefill products split K over several CTAs and ask for a workspace of partial tiles:

@@ -143,7 +143,10 @@ def test_qgemv_paired_silu_mul(cuda, K, N):
 
 @pytest.mark.parametrize("M,K,N", [(2, 896, 1152), (16, 896, 1152), (128, 896, 1152), (200, 4864, 896),
                                    (37, 896, 4864), (130, 256, 1000), (5, 64, 24),
-                                   (64, 896, 896), (256, 4864, 896), (128, 64, 72)])
+                                   (64, 896, 896), (256, 4864, 896), (128, 64, 72),
+                                   # few rows: the kernel that shares K among the warps of a CTA
+                                   (8, 896, 4864), (3, 4864, 896), (9, 4864, 896), (16, 128, 40), (7, 896, 18950),
+                                   (4, 4096, 6144), (8, 14336, 4096), (12, 4864, 64), (24, 896, 1152)])
 def test_qmatmul_rows(cuda, M, K, N):
     """Several activation rows (prefill semantics: dequantise, then multiply)."""
 
@@ -153,7 +156,11 @@ def test_qmatmul_rows(cuda, M, K, N):
     x = activations(31, M, K)
     bias = activations(32, N, std=0.5)
     if K % 128 == 0:
-        assert ops.qmatmul_variant(M, N, K, group) == ("gemm_tcgen05" if M >= 64 or (M >= 8 and (N >= 4096 or K >= 2048)) else "gemm_mma")
+        staged = (8 if M <= 8 else 16) * (2 * K + 64) + 8 * (1 if M <= 8 else 2) * 4 * 32 * 4
+        few = 2 <= M <= 16 and N >= 16 and staged <= 200 * 1024
+        assert ops.qmatmul_variant(M, N, K, group) == (
+            "qgemm_rows" if few else
+            "gemm_tcgen05" if M >= 64 or (M >= 8 and (N >= 4096 or K >= 2048)) else "gemm_mma")
     got = ops.qmatmul(x.to(cuda), packed.to(cuda), scales.to(cuda), group_size=group, addend=bias.to(cuda)).cpu()
     want = ref.packed_matmul(x, packed, scales, group, addend=bias)
     assert got.shape == (M, N)
