@@ -971,6 +971,7 @@ def run_probe(name: str, probe_prompt: int = 0) -> None:
     """Small fixed cases for a profiler: a handful of launches of one kernel, a few GB at most.
 
     ``lm_head``  six packed GEMV launches over three copies of a [151936, 896] weight (RMS norm fused);
+    ``rows_gemm`` six launches of the packed product with 16 rows over three copies of a [151936, 896] weight;
     ``gemm``     six packed GEMM launches, K=4096 N=14336 M=1024, over five weight copies;
     ``attention`` six launches of prefill attention, 32 query / 8 kv heads, 1024 x 1024, D = 128, causal mask;
     ``i8``       eight-bit packed projections of the 0.5B shape, timed with CUDA events;
@@ -1002,6 +1003,17 @@ def run_probe(name: str, probe_prompt: int = 0) -> None:
             ops.qmatmul(x, packs[i % 3], scales[i % 3], group_size=GROUP, norm_weight=norm, rms_norm_eps=1e-6, out=out)
         torch.cuda.synchronize()
         print(json.dumps({"probe": name, "variant": ops.qmatmul_variant(1, N, K, GROUP), "max": float(out.float().abs().max())}))
+    elif name == "rows_gemm":
+        # six launches of the packed product with 16 activation rows over three copies of a [151936, 896] weight
+        N, K, M = 151936, 896, 16
+        packs = [torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, generator=generator).to(device) for _ in range(3)]
+        scales = [(torch.rand(N, K // 64, generator=generator) * 0.01 + 0.001).bfloat16().to(device) for _ in range(3)]
+        x = torch.randn(M, K, generator=generator).bfloat16().to(device)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+        for i in range(6):
+            ops.qmatmul(x, packs[i % 3], scales[i % 3], group_size=GROUP, out=out)
+        torch.cuda.synchronize()
+        print(json.dumps({"probe": name, "variant": ops.qmatmul_variant(M, N, K, GROUP), "max": float(out.float().abs().max())}))
     elif name == "attention":
         heads, kv_heads, length, dim = 32, 8, 1024, 128
         q = torch.randn(1, heads, length, dim, generator=generator).bfloat16().to(device)
@@ -1217,7 +1229,7 @@ def main() -> None:
     parser.add_argument("--skip-cpu", action="store_true", help="leave the cpu_baseline object out")
     parser.add_argument("--skip-multi", action="store_true",
                         help="with more than one GPU: leave the tensor-parallel and bucketed records out")
-    parser.add_argument("--probe", choices=("lm_head", "gemm", "attention", "i8", "i8_decoder", "dense", "dense_lm_head", "dense_decoder", "rows", "step", "trace", "trace_llama",
+    parser.add_argument("--probe", choices=("lm_head", "rows_gemm", "gemm", "attention", "i8", "i8_decoder", "dense", "dense_lm_head", "dense_decoder", "rows", "step", "trace", "trace_llama",
                                             "trace_llama_long"), default=None,
                         help="run a small fixed case of one kernel for a profiler instead of the benchmark")
     parser.add_argument("--probe-prompt", type=int, default=0, help="with --probe trace_llama_long: another prompt length")
