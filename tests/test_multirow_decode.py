@@ -146,3 +146,21 @@ def test_the_step_is_saved_and_loaded_with_the_runtime(case, tmp_path):
     assert [s.artifact_name for s in loaded.plan.selections] == [s.artifact_name for s in runtime.rows.plan.selections]
     assert list(loaded.state_names) == list(runtime.rows.state_names)
     assert tuple(loaded.plan.graph.value(loaded.plan.graph.inputs[0]).type.shape) == (1, ROWS)
+
+
+def test_mask_rows_are_the_one_token_masks_of_the_steps_they_replace():
+    """Row j admits what the j-th one-token step would: every token held so far, its own included -
+    ``valid_length - rows + 1 + j`` contiguous slots that end at the row's own slot."""
+
+    rng = np.random.default_rng(3)
+    for _ in range(200):
+        capacity = int(rng.integers(2, 40))
+        rows = int(rng.integers(1, capacity + 1))
+        valid = int(rng.integers(rows, capacity + 1))
+        mask = decode_rows_mask(valid, capacity, rows)[0, 0]
+        assert mask.shape == (rows, capacity)
+        for j in range(rows):
+            admitted = np.flatnonzero(mask[j])
+            own = capacity - rows + j
+            assert admitted.size == valid - rows + 1 + j
+            assert admitted[-1] == own and np.array_equal(admitted, np.arange(own - admitted.size + 1, own + 1))
