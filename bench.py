@@ -22,6 +22,8 @@ The printed JSON line reports
 * ``lm_head_roofline`` the largest single projection (the LM-head GEMV over the packed
                vocabulary matrix) alone, on rotating weight copies larger than L2;
 * ``bf16``     the same decoder with dense bf16 weights (``quantize=None``), one GPU only;
+* ``rows``     one decode step over eight tokens (``decode_rows=8``) against eight one-token
+               plan calls, one GPU only;
 * ``cpu_baseline`` the same decoder evaluated eagerly by PyTorch on the host cores
                for a bounded sample (prefill + a few decode steps).
 
@@ -126,6 +128,52 @@ def dense_step_bytes(config, valid_length: int) -> int:
     kv_read = 2 * kvh * d * 2 * valid_length
     kv_write = 2 * kvh * d * 2
     return layers * (qkv + o + gate_up + down + kv_read + kv_write) + head + h * 2
+
+
+def measure_rows(model, prompt_host, device, rows: int = 8, repeats: int = 10) -> dict:
+    """One decode step over ``rows`` tokens (``decode_rows=rows``) against ``rows`` one-token plan calls.
+
+    The proposed tokens are the greedy ones, so row j of the step must confirm token j + 1. CUDA
+    events over ``repeats`` steps after three untimed ones; weights larger than L2.
+    """
+
+    import aotolith_b200 as aoto
+
+    runtime = aoto.compile_qwen2_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS,
+                                              quantize=GROUP, decode_rows=rows)
+    prompt = prompt_host.to(device)
+    greedy = runtime.greedy_generate(prompt)                       # the tokens a host would propose
+    logits, compact = runtime.prefill_ids(prompt)
+    cache = runtime.pad_cache(compact)
+    proposed = greedy[:, :rows].contiguous()
+    for _ in range(3):
+        step_logits, _ = runtime.decode_tokens(proposed, cache, PROMPT + rows, verify_tokens=False)
+    torch.cuda.synchronize()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    marks[0].record()
+    for _ in range(repeats):
+        step_logits, _ = runtime.decode_tokens(proposed, cache, PROMPT + rows, verify_tokens=False)
+    marks[1].record()
+    for _ in range(repeats):
+        single, valid = cache, PROMPT
+        for j in range(rows):
+            valid += 1
+            one_logits, single = runtime.decode_token(proposed[:, j : j + 1], single, valid, verify_token=False)
+    marks[2].record()
+    torch.cuda.synchronize()
+    rows_us = marks[0].elapsed_time(marks[1]) * 1e3 / repeats
+    singles_us = marks[1].elapsed_time(marks[2]) * 1e3 / repeats
+    # row j predicts the token after proposed token j: the greedy continuation, when the proposal was the greedy one
+    predicted = step_logits[0].float().argmax(dim=-1)
+    agree = int((predicted[:-1] == greedy[0, 1:rows]).sum())
+    last_gap = float((step_logits[0, -1].float() - one_logits[0, -1].float()).abs().max() / one_logits.float().abs().max())
+    return {"workload": f"Qwen2.5-0.5B-shaped, 4-bit g64, prompt 128: one step over {rows} tokens",
+            "rows": rows, "rows_step_us": round(rows_us, 1), "us_per_token": round(rows_us / rows, 1),
+            "value": round(rows * 1e6 / rows_us, 1), "unit": "tok/s verified per step",
+            "one_token_plan_calls_us": round(singles_us, 1),
+            "greedy_tokens_confirmed": f"{agree} of {rows - 1}", "last_row_vs_one_token_step": last_gap,
+            "kernels": sorted({s.artifact_name for s in runtime.rows.plan.selections
+                               if s.kind in ("matmul", "addmm", "attention")})}
 
 
 def measure_dense(model, prompt_host, device, peak: float, peak_kind: str, requests: int = 3) -> dict:
@@ -577,6 +625,10 @@ def run_ours(args) -> None:
                 line["bf16"] = measure_dense(model, prompt_host, device, peak, peak_kind)
             except Exception as error:  # noqa: BLE001 - a sub-record must not lose the line
                 line["bf16"] = {"error": f"{type(error).__name__}: {error}"[:500]}
+            try:
+                line["rows"] = measure_rows(model, prompt_host, device)
+            except Exception as error:  # noqa: BLE001
+                line["rows"] = {"error": f"{type(error).__name__}: {error}"[:500]}
         if world == 1 and not args.skip_cpu and not on_device:
             line["cpu_baseline"] = cpu_sample(model, prompt_host, 3)
         print(json.dumps(line))
@@ -1115,47 +1167,11 @@ def run_probe(name: str, probe_prompt: int = 0) -> None:
                           "tokens": int(tokens.numel())}))
     elif name == "rows":
         # a step over eight tokens against eight one-token steps, default workload, CUDA events
-        import aotolith_b200 as aoto
         from aotolith_b200.models.synthetic import qwen25_05b_shaped
 
-        rows = 8
         model = qwen25_05b_shaped(seed=0)
-        runtime = aoto.compile_qwen2_static_cache(model, prompt_length=PROMPT, max_new_tokens=NEW_TOKENS,
-                                                  quantize=GROUP, decode_rows=rows)
-        prompt = seeded_prompt(model.config.vocab_size, 1).to(device)
-        greedy = runtime.greedy_generate(prompt)                       # the tokens a host would propose
-        logits, compact = runtime.prefill_ids(prompt)
-        cache = runtime.pad_cache(compact)
-        proposed = greedy[:, :rows].contiguous()
-        for _ in range(3):
-            step_logits, _ = runtime.decode_tokens(proposed, cache, PROMPT + rows, verify_tokens=False)
-        torch.cuda.synchronize()
-        marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        repeats = 10
-        marks[0].record()
-        for _ in range(repeats):
-            step_logits, _ = runtime.decode_tokens(proposed, cache, PROMPT + rows, verify_tokens=False)
-        marks[1].record()
-        for _ in range(repeats):
-            single, valid = cache, PROMPT
-            for j in range(rows):
-                valid += 1
-                one_logits, single = runtime.decode_token(proposed[:, j : j + 1], single, valid, verify_token=False)
-        marks[2].record()
-        torch.cuda.synchronize()
-        rows_us = marks[0].elapsed_time(marks[1]) * 1e3 / repeats
-        singles_us = marks[1].elapsed_time(marks[2]) * 1e3 / repeats
-        # row j predicts the token after proposed token j: the greedy continuation, when the proposal was the greedy one
-        predicted = step_logits[0].float().argmax(dim=-1)
-        agree = int((predicted[:-1] == greedy[0, 1:rows]).sum())
-        last_gap = float((step_logits[0, -1].float() - one_logits[0, -1].float()).abs().max() / one_logits.float().abs().max())
-        print(json.dumps({"probe": name, "workload": "Qwen2.5-0.5B-shaped, 4-bit g64, prompt 128: one step over 8 tokens",
-                          "rows": rows, "rows_step_us": round(rows_us, 1), "us_per_token": round(rows_us / rows, 1),
-                          "eight_one_token_plan_calls_us": round(singles_us, 1),
-                          "streamed_step_kernel_us_per_token": "see the bench line (decode_us_per_token)",
-                          "greedy_tokens_confirmed": f"{agree} of {rows - 1}", "last_row_vs_one_token_step": last_gap,
-                          "kernels": sorted({s.artifact_name for s in runtime.rows.plan.selections
-                                             if s.kind in ("matmul", "addmm", "attention")})}))
+        record = measure_rows(model, seeded_prompt(model.config.vocab_size, 1), device)
+        print(json.dumps({"probe": name, **record}))
     elif name == "i8_decoder":
         # the whole decoder packed with eight bits: one request of the default workload, timed with CUDA events
         import aotolith_b200 as aoto
