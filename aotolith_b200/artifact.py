@@ -20,7 +20,6 @@ not called, as with ``compile_module``.
 from __future__ import annotations
 
 import hashlib
-import io
 import json
 import os
 import tempfile

@@ -33,7 +33,7 @@ from .._log import logger
 from ..errors import CompilationError, UnsupportedDTypeError, UnsupportedOperationError
 from ..ir import DType, Graph, Operation
 from ..planning import plan_storage
-from ..runtime.plan import TORCH_DTYPES, CompiledPlan, KernelArtifact, current_context
+from ..runtime.plan import CompiledPlan, KernelArtifact, current_context
 from ..runtime.step_program import build_step_program
 from ..selection import COPY, CUDA_KERNEL, VIEW, KernelSelection
 

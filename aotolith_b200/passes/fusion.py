@@ -14,7 +14,7 @@ Behavioural counterparts of ``src/aotolith/passes/fusion.py``,
 
 from __future__ import annotations
 
-from ..ir import DType, Graph, Operation, TensorType
+from ..ir import Graph, Operation, TensorType
 from .rewriter import Rewriter, see_through_reshapes
 
 #: operations a pointwise region may contain
